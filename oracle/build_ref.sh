@@ -1,0 +1,77 @@
+#!/usr/bin/env bash
+# TEST INFRASTRUCTURE ONLY.
+#
+# Builds the UNMODIFIED reference library (LibNTC) from its own sources, where they lie, into
+# oracle/_ref/libntc_ref.so together with the plain-C driver oracle/ref_harness.cpp.  The result is
+# the parity checker and the benchmark's reference arm; it is never linked into the product.
+#
+# The reference's own CMake build needs network access (FetchContent) and the libdeflate submodule,
+# so the sources are compiled directly with the same definitions and nvcc flags its CMake files set
+# (src/CMakeLists.txt:15-44,120-135): C++17, --expt-relaxed-constexpr --extended-lambda
+# --use_fast_math, separable compilation, CUDA only (no DX12 / Vulkan / prebuilt shaders).
+# Differences from the stock build, none of which touches the decode path:
+#   * target architecture sm_100 instead of the default 75/86/89 list;
+#   * src/GDeflate.cpp is replaced by oracle/gdeflate_stub.cpp (libdeflate sources are absent);
+#   * src/Shaders.cpp is left out, exactly as the stock build does without prebuilt shaders.
+#
+# Usage: oracle/build_ref.sh [reference-source-dir]   (default: $NTC_REFERENCE_DIR or /root/reference)
+set -euo pipefail
+
+HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+REF="${1:-${NTC_REFERENCE_DIR:-/root/reference}}"
+OUT="$HERE/_ref"
+OBJ="$OUT/obj"
+NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
+CXX="${CXX:-g++}"
+JOBS="${JOBS:-$(nproc)}"
+
+if [ ! -f "$REF/src/Inference.cu" ]; then
+    echo "build_ref.sh: reference sources not found under $REF" >&2
+    exit 3
+fi
+
+mkdir -p "$OBJ"
+
+# The reference generates VersionInfo.h from src/VersionInfoTemplate.h at configure time.
+cat > "$OBJ/VersionInfo.h" <<'EOF'
+#define NTC_VERSION_MAJOR 0
+#define NTC_VERSION_MINOR 9
+#define NTC_VERSION_POINT 2
+#define NTC_VERSION_BRANCH "reference"
+#define NTC_VERSION_HASH "unmodified"
+#define NTC_VERSION_FULL "0.9.2 reference-unmodified"
+EOF
+
+DEFS="-DNTC_WITH_CUDA=1 -DNTC_WITH_VULKAN=0 -DNTC_WITH_DX12=0 -DNTC_WITH_PREBUILT_SHADERS=0 \
+-DNTC_STATIC=1 -DNTC_CUDA_MIN_COMPUTE_MAJOR=7 -DNTC_CUDA_MIN_COMPUTE_MINOR=5"
+INCS="-I$OBJ -I$REF/include -I$REF/src -I$REF/external/rapidjson/include -I/usr/local/cuda/include"
+
+CU_SOURCES="Inference Quantizer Regression RegressionFast RegressionStable Optimizer ImageProcessing CudaRandomGen"
+CPP_SOURCES="AdaptiveCompressionSession BinaryChunkBuilder Context CoopVecWeightConverter CudaDeviceGuard \
+Errors FeatureGridHost FeatureGridMath GraphicsResources JsonFileFormat JsonSerialization PublicFunctions \
+SharedTexture Stream TextureMetadata TextureSet TextureSetMetadata ThreadPool WeightLayout"
+
+compile_cu() {
+    "$NVCC" -arch=sm_100 -std=c++17 -O3 --expt-relaxed-constexpr --extended-lambda --use_fast_math \
+        -rdc=true -Xcompiler -fPIC -Xcompiler -fno-strict-aliasing $DEFS $INCS \
+        -c "$REF/src/$1.cu" -o "$OBJ/$1.cu.o"
+}
+compile_cpp() {
+    "$CXX" -std=c++17 -O2 -fPIC -fno-strict-aliasing $DEFS $INCS -c "$2" -o "$OBJ/$1.o"
+}
+export -f compile_cu compile_cpp
+export NVCC CXX DEFS INCS OBJ REF
+
+{
+    for s in $CU_SOURCES; do echo "compile_cu $s"; done
+    for s in $CPP_SOURCES; do echo "compile_cpp $s $REF/src/$s.cpp"; done
+    echo "compile_cpp gdeflate_stub $HERE/gdeflate_stub.cpp"
+    echo "compile_cpp ref_harness $HERE/ref_harness.cpp"
+} | xargs -P "$JOBS" -I{} bash -c '{}'
+
+OBJECTS=""
+for s in $CU_SOURCES; do OBJECTS="$OBJECTS $OBJ/$s.cu.o"; done
+for s in $CPP_SOURCES gdeflate_stub ref_harness; do OBJECTS="$OBJECTS $OBJ/$s.o"; done
+
+"$NVCC" -arch=sm_100 -shared -o "$OUT/libntc_ref.so" $OBJECTS -lcudart_static -lpthread -ldl -lrt
+echo "built $OUT/libntc_ref.so"

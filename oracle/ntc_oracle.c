@@ -1,0 +1,728 @@
+/* TEST INFRASTRUCTURE ONLY: nothing in the product library includes, links or calls this.
+ *
+ * CPU restatement of LibNTC's CUDA decompression path; see ntc_oracle.h for the two numerics.
+ * Scalar code, one texel at a time, work items spread over host threads (pthreads).
+ * Build: see oracle/Makefile (needs -mf16c, -ffp-contract=off).
+ */
+#include "ntc_oracle.h"
+
+#include <immintrin.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <pthread.h>
+#include <stdatomic.h>
+#include <unistd.h>
+
+/* Network geometry: include/libntc/shaders/InferenceConstants.h:26-40, src/MlpDesc.h:25-99. */
+#define MLP_LAYERS 4
+#define MLP_FEATURES 16
+#define MLP_IN 48
+static const int kLayerIn[MLP_LAYERS] = {48, 64, 48, 32};
+static const int kLayerOut[MLP_LAYERS] = {64, 48, 32, 16};
+
+typedef uint16_t h16;
+
+/* ------------------------------------------------------------------------------------------ */
+/* binary16 arithmetic, one IEEE operation per call                                             */
+/* ------------------------------------------------------------------------------------------ */
+
+static inline float h2f(h16 h) { return _cvtsh_ss(h); }
+static inline h16 f2h(float f) { return _cvtss_sh(f, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC); }
+
+static inline uint32_t f_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float f_from_bits(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+/* double -> binary16, round to nearest even in one step: first to binary32 with round-to-odd
+   (24 bits >= 11 + 2 keeps the final rounding correct), then the hardware RNE conversion. */
+static inline h16 d2h(double d)
+{
+    float f = (float)d;
+    if (isfinite(f) && (double)f != d)
+    {
+        uint32_t bits = f_bits(f);
+        if (fabs((double)f) > fabs(d))
+            bits -= 1; /* step toward zero: now the truncated value */
+        bits |= 1;     /* inexact: make it odd */
+        f = f_from_bits(bits);
+    }
+    return f2h(f);
+}
+
+/* The product of two binary16 values is exact in binary32; the sum of two is exact or is rounded
+   harmlessly (24 >= 2*11 + 2), so one binary32 operation plus one conversion is one binary16 op. */
+static inline h16 hmul(h16 a, h16 b) { return f2h(h2f(a) * h2f(b)); }
+static inline h16 hadd(h16 a, h16 b) { return f2h(h2f(a) + h2f(b)); }
+static inline h16 hsub(h16 a, h16 b) { return f2h(h2f(a) - h2f(b)); }
+static inline h16 hfma(h16 a, h16 b, h16 c) { return d2h((double)h2f(a) * (double)h2f(b) + (double)h2f(c)); }
+static inline h16 hfma_sat(h16 a, h16 b, h16 c)
+{
+    double r = (double)h2f(a) * (double)h2f(b) + (double)h2f(c);
+    if (!(r > 0.0)) return 0;          /* NaN and negatives -> +0, as fma.rn.sat.f16 */
+    if (r > 1.0) return 0x3C00;
+    return d2h(r);
+}
+static inline h16 hmin(h16 a, h16 b)
+{
+    float fa = h2f(a), fb = h2f(b);
+    if (isnan(fa)) return b;
+    if (isnan(fb)) return a;
+    return fa < fb ? a : b;
+}
+static inline h16 hmax(h16 a, h16 b)
+{
+    float fa = h2f(a), fb = h2f(b);
+    if (isnan(fa)) return b;
+    if (isnan(fb)) return a;
+    return fa > fb ? a : b;
+}
+static inline h16 hfloor(h16 a) { return f2h(floorf(h2f(a))); }
+static inline h16 hrint(h16 a) { return f2h(nearbyintf(h2f(a))); } /* default mode: nearest even */
+static inline int h_is_special(h16 a) { return (a & 0x7C00) == 0x7C00; } /* src/CudaUtils.h:30-35 */
+
+uint16_t ntco_float_to_half(float value) { return f2h(value); }
+float ntco_half_to_float(uint16_t bits) { return h2f(bits); }
+
+/* ------------------------------------------------------------------------------------------ */
+/* FP8 e4m3 (finite-only format: max 448, 0x7F/0xFF = NaN)                                      */
+/* ------------------------------------------------------------------------------------------ */
+
+float ntco_e4m3_to_float(uint8_t bits)
+{
+    int sign = bits >> 7, exponent = (bits >> 3) & 15, mantissa = bits & 7;
+    float magnitude;
+    if (exponent == 15 && mantissa == 7)
+        magnitude = NAN;
+    else if (exponent == 0)
+        magnitude = ldexpf((float)mantissa, -9);
+    else
+        magnitude = ldexpf(1.0f + (float)mantissa / 8.0f, exponent - 7);
+    return sign ? -magnitude : magnitude;
+}
+
+/* binary16 -> e4m3, round to nearest even, saturating to +-448; NaN -> 0x7F.
+   This is what the reference's RoundHalfToFloatE4M3 does on sm_89 and newer, where it uses the
+   hardware conversion (src/tin/tin_activation.h:44-48). */
+uint8_t ntco_half_to_e4m3(uint16_t bits)
+{
+    float x = h2f(bits);
+    if (isnan(x))
+        return 0x7F;
+    uint8_t sign = (bits & 0x8000) ? 0x80 : 0;
+    float a = fabsf(x);
+    if (a >= 448.0f)   /* includes infinity; values in (448, 464) round to 448 as well */
+        return sign | 0x7E;
+    if (a < 0x1p-6f)
+    {
+        /* subnormal range: multiples of 2^-9 */
+        int q = (int)nearbyintf(a * 512.0f); /* exact scaling, nearest-even */
+        return sign | (uint8_t)q;            /* q == 8 encodes the smallest normal, as it should */
+    }
+    int e;
+    float m = frexpf(a, &e);                 /* a = m * 2^e, m in [0.5, 1) */
+    int q = (int)nearbyintf(m * 16.0f);      /* 4 significant bits: q in [8, 16] */
+    if (q == 16) { q = 8; e += 1; }
+    int exponent = e - 1 + 7;                /* a = (q/8) * 2^(e-1) */
+    if (exponent > 15 || (exponent == 15 && q - 8 == 7))
+        return sign | 0x7E;
+    return sign | (uint8_t)(exponent << 3) | (uint8_t)(q - 8);
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* Geometry                                                                                     */
+/* ------------------------------------------------------------------------------------------ */
+
+static int imax(int a, int b) { return a > b ? a : b; }
+static int imin(int a, int b) { return a < b ? a : b; }
+
+/* src/FeatureGridMath.cpp:47-60 */
+static int lod_to_neural_lod(int lod, int gridScale, int neuralLods)
+{
+    static const int sharedMipsForGridScale[6] = {2, 3, 3, 3, 4, 4};
+    int sharedMips = sharedMipsForGridScale[gridScale - 1];
+    int neuralLod = (lod - sharedMips + 2) & ~1;
+    return imax(0, imin(neuralLod, neuralLods - 2));
+}
+
+/* src/FeatureGridMath.cpp:62-65 */
+static int grid_dimension(int imageDimension, int neuralLod, int gridScale)
+{
+    return imax((imageDimension / gridScale) >> neuralLod, 1);
+}
+
+int ntco_geometry(const NtcoTextureSet* set, NtcoGeometry* out)
+{
+    if (!set || !out || set->width < 1 || set->height < 1 || set->numMips < 1 || set->numMips > NTCO_MAX_MIPS ||
+        set->gridSizeScale < 1 || set->gridSizeScale > 6 || set->numFeatures < 4 || set->numFeatures > 16 ||
+        (set->numFeatures & 3) || set->channels < 2 || set->channels > 16 || (set->channels & 1))
+        return -1;
+    memset(out, 0, sizeof *out);
+
+    /* src/FeatureGridMath.cpp:72-77 and src/FeatureGridHost.cpp:33-37 */
+    int minImageSize = imin(set->width, set->height);
+    int minGridSize = (int)((float)minImageSize / (float)set->gridSizeScale);
+    int theoretical = imax(2, (int)(1.f + floorf(log2f((float)minGridSize)))) & ~1;
+    int lastNeuralMip = lod_to_neural_lod(set->numMips - 1, set->gridSizeScale, NTCO_MAX_NEURAL_MIPS);
+    out->numNeuralMips = imin(theoretical, lastNeuralMip + 2);
+    out->numLayers = (set->numFeatures + 3) / 4;
+
+    uint64_t pixels = 0;
+    for (int m = 0; m < out->numNeuralMips; ++m)
+    {
+        out->latentWidth[m] = grid_dimension(set->width, m, set->gridSizeScale);
+        out->latentHeight[m] = grid_dimension(set->height, m, set->gridSizeScale);
+        out->latentPixelOffset[m] = pixels;
+        pixels += (uint64_t)out->latentWidth[m] * (uint64_t)out->latentHeight[m];
+    }
+    out->latentPixelOffset[out->numNeuralMips] = pixels;
+
+    /* src/TextureSet.cpp:88-101 (mip offsets) and :450-463 (positional constants) */
+    uint64_t texels = 0;
+    for (int mip = 0; mip < set->numMips; ++mip)
+    {
+        int w = imax(1, set->width >> mip), h = imax(1, set->height >> mip);
+        int lod = lod_to_neural_lod(mip, set->gridSizeScale, out->numNeuralMips);
+        out->mipWidth[mip] = w;
+        out->mipHeight[mip] = h;
+        out->neuralLod[mip] = lod;
+        float widthScale = (float)out->latentWidth[lod] / (float)w;
+        float heightScale = (float)out->latentHeight[lod] / (float)h;
+        out->positionScale[mip] = 0.5f * fmaxf(widthScale, heightScale);
+        out->positionLod[mip] = fmaxf(-1.f, fminf(1.f, 0.25f * log2f(out->positionScale[mip])));
+        out->mipTexelOffset[mip] = texels;
+        texels += (uint64_t)w * (uint64_t)h;
+    }
+    out->mipTexelOffset[set->numMips] = texels;
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* Prepared network                                                                             */
+/* ------------------------------------------------------------------------------------------ */
+
+typedef struct Network
+{
+    /* file contents, per layer */
+    const int8_t* wq[MLP_LAYERS];   /* [out][in] bytes: int8, or e4m3 bit patterns */
+    const float* scale[MLP_LAYERS]; /* fp32, NULL for FP8 hidden layers */
+    const int32_t* biasI[MLP_LAYERS];
+    const h16* biasH[MLP_LAYERS];   /* fp16 bias of FP8 hidden layers */
+    int layerIsFp8[MLP_LAYERS];
+    /* decoded FP8 weights (exact) */
+    float wf[MLP_LAYERS][64 * 64];
+    /* binary16 weights and biases as the reference's CUDA path builds them */
+    h16 wh[MLP_LAYERS][64 * 64];
+    h16 bh[MLP_LAYERS][64];
+} Network;
+
+/* Constants of the reference's quantisers: src/tin/tin_mlp.h:42-45, src/tin/tin_activation.h:109-121. */
+static const float kInputScale = 127.5f;
+static const float kActStep = 3.1875f / 255.f; /* 0.0125f */
+static const int kActBias = -113;
+
+static void prepare_network(const NtcoTextureSet* set, int weights, Network* net)
+{
+    memset(net, 0, sizeof *net);
+    const uint8_t* blob = (weights == NTCO_WEIGHTS_INT8) ? set->int8Blob : set->fp8Blob;
+    size_t offset = 0;
+    for (int l = 0; l < MLP_LAYERS; ++l)
+    {
+        net->wq[l] = (const int8_t*)(blob + offset);
+        offset += (size_t)kLayerIn[l] * kLayerOut[l];
+        net->layerIsFp8[l] = (weights == NTCO_WEIGHTS_FP8) && (l < MLP_LAYERS - 1);
+    }
+    if (weights == NTCO_WEIGHTS_INT8)
+    {
+        /* src/WeightLayout.cpp:228-238: all scale vectors, then all bias vectors */
+        for (int l = 0; l < MLP_LAYERS; ++l) { net->scale[l] = (const float*)(blob + offset); offset += 4u * kLayerOut[l]; }
+        for (int l = 0; l < MLP_LAYERS; ++l) { net->biasI[l] = (const int32_t*)(blob + offset); offset += 4u * kLayerOut[l]; }
+    }
+    else
+    {
+        /* src/WeightLayout.cpp:240-255: fp16 biases of layers 0-2, then scale and bias of layer 3 */
+        for (int l = 0; l < MLP_LAYERS - 1; ++l) { net->biasH[l] = (const h16*)(blob + offset); offset += 2u * kLayerOut[l]; }
+        net->scale[MLP_LAYERS - 1] = (const float*)(blob + offset); offset += 4u * kLayerOut[MLP_LAYERS - 1];
+        net->biasI[MLP_LAYERS - 1] = (const int32_t*)(blob + offset);
+    }
+
+    for (int l = 0; l < MLP_LAYERS; ++l)
+    {
+        int in = kLayerIn[l], outc = kLayerOut[l];
+        for (int n = 0; n < outc; ++n)
+        {
+            if (net->layerIsFp8[l])
+            {
+                /* src/Quantizer.cu:384-408: exact e4m3 -> half, bias copied */
+                for (int k = 0; k < in; ++k)
+                {
+                    float w = ntco_e4m3_to_float((uint8_t)net->wq[l][n * in + k]);
+                    net->wf[l][n * in + k] = w;
+                    net->wh[l][n * in + k] = f2h(w);
+                }
+                net->bh[l][n] = net->biasH[l][n];
+            }
+            else
+            {
+                /* src/Quantizer.cu:325-382 (UnquantizeColumnInt8), same fp32 operation order */
+                float layerScale = net->scale[l][n];
+                float layerBias = (float)net->biasI[l][n] * layerScale;
+                layerScale *= (l == 0) ? kInputScale : (1.f / kActStep);
+                int integerWeightSum = 0;
+                for (int k = 0; k < in; ++k)
+                {
+                    int q = net->wq[l][n * in + k];
+                    net->wh[l][n * in + k] = f2h((float)q * layerScale);
+                    integerWeightSum += q;
+                }
+                if (l != 0)
+                    layerBias = fmaf((float)(integerWeightSum * kActBias) * layerScale, kActStep, layerBias);
+                net->bh[l][n] = f2h(layerBias);
+            }
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* Input vector                                                                                 */
+/* ------------------------------------------------------------------------------------------ */
+
+typedef struct MipContext
+{
+    int width, height;
+    float invWidth, invHeight;
+    int hiW, hiH, loW, loH;
+    const uint16_t* hi; /* layer 0 plane of the high-res grid */
+    const uint16_t* lo;
+    size_t hiPlane, loPlane; /* pixels per layer */
+    float positionScale, positionLod;
+    int numLayers, numFeatures, channels;
+} MipContext;
+
+/* src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16 (:568-571) */
+static h16 g_latentValue[16];
+static void init_tables(void)
+{
+    const float quantizationStep = 1.f / 15.f;
+    for (int n = 0; n < 16; ++n)
+        g_latentValue[n] = f2h((float)n * quantizationStep);
+}
+
+/* src/FeatureGridDevice.h:33-98.  The sample position uses a precomputed reciprocal of the mip
+   size (u = (x + 0.5) * (1 / W)); the reference divides under --use_fast_math, which is the same
+   value for power-of-two sizes. */
+static void sample_grid(const uint16_t* plane0, size_t planePixels, int w, int h, int numLayers, float u, float v,
+    int blendFma, h16* out /* numLayers*4 values */)
+{
+    float x = fmaf(u, (float)w, -0.5f);
+    float y = fmaf(v, (float)h, -0.5f);
+    float xbf = floorf(x), ybf = floorf(y);
+    int xb = (int)xbf, yb = (int)ybf;
+    float dx = x - xbf, dy = y - ybf;
+    float dxn = 1.f - dx, dyn = 1.f - dy;
+    h16 w00 = f2h(dxn * dyn), w01 = f2h(dx * dyn), w10 = f2h(dxn * dy), w11 = f2h(dx * dy);
+    if (xb < 0) xb += w;
+    if (yb < 0) yb += h;
+    int x0 = xb % w, y0 = yb % h, x1 = (xb + 1) % w, y1 = (yb + 1) % h;
+    const h16 two = 0x4000, minusOne = 0xBC00;
+
+    for (int layer = 0; layer < numLayers; ++layer)
+    {
+        const uint16_t* plane = plane0 + (size_t)layer * planePixels;
+        uint16_t p00 = plane[(size_t)y0 * w + x0], p01 = plane[(size_t)y0 * w + x1];
+        uint16_t p10 = plane[(size_t)y1 * w + x0], p11 = plane[(size_t)y1 * w + x1];
+        for (int j = 0; j < 4; ++j)
+        {
+            h16 l00 = g_latentValue[(p00 >> (4 * j)) & 15], l01 = g_latentValue[(p01 >> (4 * j)) & 15];
+            h16 l10 = g_latentValue[(p10 >> (4 * j)) & 15], l11 = g_latentValue[(p11 >> (4 * j)) & 15];
+            h16 d;
+            if (blendFma == 2)
+                d = hfma(l11, w11, hfma(l10, w10, hfma(l00, w00, hmul(l01, w01))));
+            else if (blendFma)
+                d = hfma(l11, w11, hfma(l10, w10, hfma(l01, w01, hmul(l00, w00))));
+            else
+                d = hadd(hadd(hadd(hmul(l00, w00), hmul(l01, w01)), hmul(l10, w10)), hmul(l11, w11));
+            out[layer * 4 + j] = hfma(d, two, minusOne); /* d*2 is exact: same value fused or not */
+        }
+    }
+}
+
+/* src/RegressionKernels.h:59-85 */
+static float fracf_(float t) { return t - floorf(t); }
+static void encode_position(float xf, float yf, float lod, h16* out /* 14 values */)
+{
+    int idx = 0;
+    for (int wave = 0; wave < 3; ++wave)
+    {
+        out[idx++] = f2h(fracf_(xf) * 2 - 1);
+        out[idx++] = f2h(fracf_(yf) * 2 - 1);
+        out[idx++] = f2h(fracf_(xf + 0.25f) * 2 - 1);
+        out[idx++] = f2h(fracf_(yf + 0.25f) * 2 - 1);
+        xf *= 2.f;
+        yf *= 2.f;
+    }
+    out[idx++] = f2h(lod);
+    out[idx++] = f2h(lod);
+}
+
+/* src/Inference.cu:46-61: 16 high-res features, 16 low-res features, 14 positional values, 2 zeros */
+static void build_input(const MipContext* mc, int x, int y, int blendFma, h16 in[MLP_IN])
+{
+    memset(in, 0, MLP_IN * sizeof(h16));
+    float u = ((float)x + 0.5f) * mc->invWidth;
+    float v = ((float)y + 0.5f) * mc->invHeight;
+    sample_grid(mc->hi, mc->hiPlane, mc->hiW, mc->hiH, mc->numLayers, u, v, blendFma, in);
+    sample_grid(mc->lo, mc->loPlane, mc->loW, mc->loH, mc->numLayers, u, v, blendFma, in + MLP_FEATURES);
+    encode_position((float)x * mc->positionScale, (float)y * mc->positionScale, mc->positionLod, in + 2 * MLP_FEATURES);
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* Activation and quantisers                                                                    */
+/* ------------------------------------------------------------------------------------------ */
+
+/* src/tin/tin_activation.h:88-92: min(x, 3) * sat(x/3 + 0.5), every operation in binary16 */
+uint16_t ntco_hgelu_clamp_half(uint16_t x)
+{
+    const h16 third = f2h(1 / 3.f), half_ = 0x3800, three = 0x4200;
+    return hmul(hmin(x, three), hfma_sat(third, x, half_));
+}
+
+/* src/tin/tin_mlp.h:25-31: the integer code before it is scaled back; fused = one fma */
+static int input_code_int8(h16 x, int fused)
+{
+    const h16 scale = f2h(kInputScale), halfv = 0x3800;
+    h16 y = fused ? hfma(x, scale, 0xB800 /* -0.5 */) : hsub(hmul(x, scale), halfv);
+    y = hfloor(y);
+    y = hmax(hmin(y, f2h(127.f)), f2h(-127.f));
+    return (int)h2f(y);
+}
+
+/* src/tin/tin_activation.h:94-99: code k = rint(y * 80), the activation is k * 0.0125 */
+static int activation_code_int8(h16 y)
+{
+    h16 k = hrint(hmul(y, f2h(1.f / kActStep)));
+    int code = (int)h2f(k);
+    return imax(-15, imin(240, code));
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* SPEC numerics: exact accumulation                                                            */
+/* ------------------------------------------------------------------------------------------ */
+
+static void mlp_spec(const Network* net, int weights, const h16 in[MLP_IN], h16 out[16])
+{
+    /* Activations travel as int8 codes (Int8 layers) or e4m3 bit patterns (FP8 layers). */
+    int code[64];
+    uint8_t f8[64];
+    int fp8 = (weights == NTCO_WEIGHTS_FP8);
+
+    for (int i = 0; i < MLP_IN; ++i)
+    {
+        if (fp8) f8[i] = ntco_half_to_e4m3(in[i]);
+        else code[i] = input_code_int8(in[i], 1);
+    }
+
+    for (int l = 0; l < MLP_LAYERS; ++l)
+    {
+        int nin = kLayerIn[l], nout = kLayerOut[l];
+        h16 x[64];
+        for (int n = 0; n < nout; ++n)
+        {
+            if (net->layerIsFp8[l])
+            {
+                /* exact products and sum, one rounding to fp32, then binary16, then the fp16 bias */
+                double acc = 0.0;
+                for (int k = 0; k < nin; ++k)
+                    acc += (double)ntco_e4m3_to_float(f8[k]) * (double)net->wf[l][n * nin + k];
+                x[n] = hadd(f2h((float)acc), net->biasH[l][n]);
+            }
+            else
+            {
+                /* include/libntc/shaders/Inference.hlsli:146-165: float(acc + bias) * scale */
+                int32_t acc = net->biasI[l][n];
+                for (int k = 0; k < nin; ++k)
+                    acc += code[k] * (int)net->wq[l][n * nin + k];
+                x[n] = f2h((float)acc * net->scale[l][n]);
+            }
+        }
+        if (l == MLP_LAYERS - 1)
+        {
+            for (int n = 0; n < nout; ++n)
+                out[n] = h_is_special(x[n]) ? 0 : x[n]; /* src/Inference.cu:125-126 */
+            return;
+        }
+        /* layers 0,1 quantise in the run's mode, layer 2 always to int8 (src/Inference.cu:66) */
+        int nextFp8 = fp8 && (l < MLP_LAYERS - 2);
+        for (int n = 0; n < nout; ++n)
+        {
+            h16 y = ntco_hgelu_clamp_half(x[n]);
+            if (nextFp8) f8[n] = ntco_half_to_e4m3(y);
+            else code[n] = activation_code_int8(y) + kActBias;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* REF numerics: binary16 weights, activations and accumulators                                 */
+/* ------------------------------------------------------------------------------------------ */
+
+/* Fixed-point model of a tensor-core dot product with a binary16 accumulator: every addend (the
+   accumulator and the exact products) is aligned to the largest exponent among them and truncated
+   toward zero below 2^(emax - bits); the truncated addends are summed exactly and the sum is
+   rounded once to binary16 (nearest even). */
+static h16 ref_accumulate_aligned(h16 acc, const h16* a, const h16* w, int count, int bits)
+{
+    double addend[17];
+    int n = 0, emax = -1000;
+    addend[n++] = (double)h2f(acc);
+    for (int i = 0; i < count; ++i)
+        addend[n++] = (double)h2f(a[i]) * (double)h2f(w[i]);
+    for (int i = 0; i < n; ++i)
+    {
+        if (!isfinite(addend[i]))
+            return f2h((float)addend[i]);
+        if (addend[i] != 0.0)
+        {
+            int e;
+            frexp(addend[i], &e); /* |x| in [2^(e-1), 2^e) */
+            if (e - 1 > emax) emax = e - 1;
+        }
+    }
+    if (emax == -1000)
+        return 0;
+    double quantum = ldexp(1.0, emax - bits);
+    double sum = 0.0;
+    for (int i = 0; i < n; ++i)
+        sum += trunc(addend[i] / quantum) * quantum; /* exact: power-of-two scaling */
+    return d2h(sum);
+}
+
+static h16 ref_accumulate(h16 acc, const h16* a, const h16* w, int count, int mode)
+{
+    if (mode >= 16)
+        return ref_accumulate_aligned(acc, a, w, count, mode);
+    if (mode == 1)
+    {
+        float s = h2f(acc);
+        for (int i = 0; i < count; ++i)
+            s += h2f(a[i]) * h2f(w[i]);
+        return f2h(s);
+    }
+    double s = (double)h2f(acc);
+    for (int i = 0; i < count; ++i)
+        s += (double)h2f(a[i]) * (double)h2f(w[i]);
+    if (mode == 2)
+    {
+        float f = (float)s;
+        if (fabs((double)f) > fabs(s))
+            f = f_from_bits(f_bits(f) - 1);
+        return f2h(f);
+    }
+    return d2h(s);
+}
+
+static void mlp_ref(const Network* net, const NtcoOptions* opt, const h16 in[MLP_IN], h16 out[16])
+{
+    int fp8 = (opt->weights == NTCO_WEIGHTS_FP8);
+    int chunk = (opt->refAccChunk == 4 || opt->refAccChunk == 8) ? opt->refAccChunk : 16;
+    h16 act[64];
+
+    /* src/tin/tin_mlp.h:22-37 */
+    const h16 invInputScale = f2h(1 / kInputScale);
+    for (int i = 0; i < MLP_IN; ++i)
+    {
+        if (fp8) act[i] = f2h(ntco_e4m3_to_float(ntco_half_to_e4m3(in[i])));
+        else act[i] = hmul(f2h((float)input_code_int8(in[i], opt->refQuantFma)), invInputScale);
+    }
+
+    for (int l = 0; l < MLP_LAYERS; ++l)
+    {
+        int nin = kLayerIn[l], nout = kLayerOut[l];
+        h16 x[64];
+        for (int n = 0; n < nout; ++n)
+        {
+            /* src/tin/tin_mlp.h:71-89: accumulator starts at the bias; src/tin/tin_matrix.h:598-625 */
+            h16 acc = net->bh[l][n];
+            for (int k0 = 0; k0 < nin; k0 += chunk)
+                acc = ref_accumulate(acc, act + k0, &net->wh[l][n * nin + k0], chunk, opt->refAccMode);
+            x[n] = acc;
+        }
+        if (l == MLP_LAYERS - 1)
+        {
+            for (int n = 0; n < nout; ++n)
+                out[n] = h_is_special(x[n]) ? 0 : x[n];
+            return;
+        }
+        int nextFp8 = fp8 && (l < MLP_LAYERS - 2);
+        const h16 step = f2h(kActStep);
+        for (int n = 0; n < nout; ++n)
+        {
+            h16 y = ntco_hgelu_clamp_half(x[n]);
+            if (nextFp8)
+                act[n] = f2h(ntco_e4m3_to_float(ntco_half_to_e4m3(y)));
+            else
+                act[n] = hmul(hrint(hmul(y, f2h(1.f / kActStep))), step); /* tin_activation.h:94-99 */
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* Drivers                                                                                      */
+/* ------------------------------------------------------------------------------------------ */
+
+static int setup_mip(const NtcoTextureSet* set, const NtcoGeometry* geo, int mip, MipContext* mc)
+{
+    int lod = geo->neuralLod[mip];
+    mc->width = geo->mipWidth[mip];
+    mc->height = geo->mipHeight[mip];
+    mc->invWidth = 1.0f / (float)mc->width;
+    mc->invHeight = 1.0f / (float)mc->height;
+    mc->hiW = geo->latentWidth[lod];
+    mc->hiH = geo->latentHeight[lod];
+    /* src/TextureSet.cpp:1816-1817 */
+    mc->loW = imax(mc->hiW >> 1, 1);
+    mc->loH = imax(mc->hiH >> 1, 1);
+    mc->numLayers = geo->numLayers;
+    mc->hiPlane = (size_t)mc->hiW * mc->hiH;
+    mc->loPlane = (size_t)geo->latentWidth[lod + 1] * geo->latentHeight[lod + 1];
+    if (mc->loW != geo->latentWidth[lod + 1] || mc->loH != geo->latentHeight[lod + 1])
+        return -1;
+    mc->hi = set->latents + geo->latentPixelOffset[lod] * (size_t)geo->numLayers;
+    mc->lo = set->latents + geo->latentPixelOffset[lod + 1] * (size_t)geo->numLayers;
+    mc->positionScale = geo->positionScale[mip];
+    mc->positionLod = geo->positionLod[mip];
+    mc->numFeatures = set->numFeatures;
+    mc->channels = set->channels;
+    return 0;
+}
+
+static void decode_texel(const MipContext* mc, const Network* net, const NtcoOptions* opt, int x, int y, h16* out)
+{
+    h16 in[MLP_IN], result[16];
+    int spec = (opt->numerics == NTCO_NUMERICS_SPEC);
+    build_input(mc, x, y, spec ? 2 : opt->refBlendFma, in);
+    if (spec) mlp_spec(net, opt->weights, in, result);
+    else mlp_ref(net, opt, in, result);
+    memcpy(out, result, (size_t)mc->channels * sizeof(h16));
+}
+
+/* Minimal parallel-for: `count` items handed out in blocks through an atomic counter. */
+typedef void (*ItemFn)(void* context, long long item);
+typedef struct ParallelJob
+{
+    ItemFn fn;
+    void* context;
+    long long count, block;
+    atomic_llong next;
+} ParallelJob;
+
+static void* parallel_worker(void* arg)
+{
+    ParallelJob* job = (ParallelJob*)arg;
+    for (;;)
+    {
+        long long begin = atomic_fetch_add(&job->next, job->block);
+        if (begin >= job->count)
+            return NULL;
+        long long end = begin + job->block < job->count ? begin + job->block : job->count;
+        for (long long i = begin; i < end; ++i)
+            job->fn(job->context, i);
+    }
+}
+
+static void parallel_for(const NtcoOptions* opt, long long count, long long block, ItemFn fn, void* context)
+{
+    long online = sysconf(_SC_NPROCESSORS_ONLN);
+    int threads = opt->threads > 0 ? opt->threads : (online > 0 ? (int)online : 1);
+    if (threads > 256) threads = 256;
+    ParallelJob job;
+    job.fn = fn;
+    job.context = context;
+    job.count = count;
+    job.block = block > 0 ? block : 1;
+    atomic_init(&job.next, 0);
+    pthread_t ids[256];
+    int started = 0;
+    for (int t = 1; t < threads; ++t)
+        if (pthread_create(&ids[started], NULL, parallel_worker, &job) == 0)
+            ++started;
+    parallel_worker(&job);
+    for (int t = 0; t < started; ++t)
+        pthread_join(ids[t], NULL);
+}
+
+typedef struct RowJob
+{
+    const MipContext* mc;
+    const Network* net;
+    const NtcoOptions* opt;
+    int y0;
+    uint16_t* out;
+} RowJob;
+
+static void decode_row(void* context, long long item)
+{
+    const RowJob* job = (const RowJob*)context;
+    int y = job->y0 + (int)item;
+    for (int x = 0; x < job->mc->width; ++x)
+        decode_texel(job->mc, job->net, job->opt, x, y, job->out + ((size_t)item * job->mc->width + x) * job->mc->channels);
+}
+
+int ntco_decode_mip(const NtcoTextureSet* set, const NtcoOptions* opt, int mip, int y0, int y1, uint16_t* out)
+{
+    NtcoGeometry geo;
+    if (!opt || !out || ntco_geometry(set, &geo) != 0 || mip < 0 || mip >= set->numMips)
+        return -1;
+    MipContext mc;
+    if (setup_mip(set, &geo, mip, &mc) != 0 || y0 < 0 || y1 > mc.height || y0 > y1)
+        return -1;
+    init_tables();
+    Network* net = (Network*)malloc(sizeof(Network));
+    if (!net)
+        return -1;
+    prepare_network(set, opt->weights, net);
+    RowJob job = {&mc, net, opt, y0, out};
+    parallel_for(opt, y1 - y0, 1, decode_row, &job);
+    free(net);
+    return 0;
+}
+
+typedef struct SampleJob
+{
+    const NtcoTextureSet* set;
+    const MipContext* mips;
+    const Network* net;
+    const NtcoOptions* opt;
+    const float* queries;
+    uint16_t* out;
+} SampleJob;
+
+static void sample_one(void* context, long long q)
+{
+    const SampleJob* job = (const SampleJob*)context;
+    float u = job->queries[3 * q], v = job->queries[3 * q + 1], lod = job->queries[3 * q + 2];
+    int mip = imax(0, imin(job->set->numMips - 1, (int)floorf(lod)));
+    const MipContext* mc = &job->mips[mip];
+    int x = imax(0, imin(mc->width - 1, (int)floorf(u * (float)mc->width)));
+    int y = imax(0, imin(mc->height - 1, (int)floorf(v * (float)mc->height)));
+    decode_texel(mc, job->net, job->opt, x, y, job->out + (size_t)q * mc->channels);
+}
+
+int ntco_sample(const NtcoTextureSet* set, const NtcoOptions* opt, const float* queries, size_t numQueries, uint16_t* out)
+{
+    NtcoGeometry geo;
+    if (!opt || !out || !queries || ntco_geometry(set, &geo) != 0)
+        return -1;
+    MipContext mips[NTCO_MAX_MIPS];
+    for (int m = 0; m < set->numMips; ++m)
+        if (setup_mip(set, &geo, m, &mips[m]) != 0)
+            return -1;
+    init_tables();
+    Network* net = (Network*)malloc(sizeof(Network));
+    if (!net)
+        return -1;
+    prepare_network(set, opt->weights, net);
+    SampleJob job = {set, mips, net, opt, queries, out};
+    parallel_for(opt, (long long)numQueries, 4096, sample_one, &job);
+    free(net);
+    return 0;
+}

@@ -1,0 +1,213 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes bindings for the CPU restatement (libntc_oracle.so) and for
+the unmodified reference library built by build_ref.sh (oracle/_ref/libntc_ref.so).
+
+Only tests, the smoke check and the benchmark's baseline legs may import this module.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from typing import List, Optional
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_LIB = os.path.join(HERE, "libntc_oracle.so")
+REF_LIB = os.path.join(HERE, "_ref", "libntc_ref.so")
+
+MAX_MIPS = 16
+MAX_NEURAL_MIPS = 8
+
+
+class _TextureSet(ctypes.Structure):
+    _fields_ = [("width", ctypes.c_int), ("height", ctypes.c_int), ("channels", ctypes.c_int),
+                ("numMips", ctypes.c_int), ("gridSizeScale", ctypes.c_int), ("numFeatures", ctypes.c_int),
+                ("latents", ctypes.c_void_p), ("int8Blob", ctypes.c_void_p), ("fp8Blob", ctypes.c_void_p)]
+
+
+class Geometry(ctypes.Structure):
+    _fields_ = [("numNeuralMips", ctypes.c_int), ("numLayers", ctypes.c_int),
+                ("latentWidth", ctypes.c_int * MAX_NEURAL_MIPS), ("latentHeight", ctypes.c_int * MAX_NEURAL_MIPS),
+                ("latentPixelOffset", ctypes.c_uint64 * (MAX_NEURAL_MIPS + 1)),
+                ("mipWidth", ctypes.c_int * MAX_MIPS), ("mipHeight", ctypes.c_int * MAX_MIPS),
+                ("neuralLod", ctypes.c_int * MAX_MIPS), ("positionScale", ctypes.c_float * MAX_MIPS),
+                ("positionLod", ctypes.c_float * MAX_MIPS), ("mipTexelOffset", ctypes.c_uint64 * (MAX_MIPS + 1))]
+
+
+class Options(ctypes.Structure):
+    _fields_ = [("weights", ctypes.c_int), ("numerics", ctypes.c_int), ("threads", ctypes.c_int),
+                ("refBlendFma", ctypes.c_int), ("refQuantFma", ctypes.c_int), ("refAccChunk", ctypes.c_int),
+                ("refAccMode", ctypes.c_int), ("refActFma", ctypes.c_int)]
+
+
+WEIGHTS_INT8, WEIGHTS_FP8 = 0, 1
+NUMERICS_SPEC, NUMERICS_REF = 0, 1
+
+_oracle = None
+
+
+def build_oracle() -> None:
+    subprocess.run(["make", "-s", "-C", HERE, "libntc_oracle.so"], check=True)
+
+
+def oracle_lib():
+    global _oracle
+    if _oracle is None:
+        if not os.path.exists(ORACLE_LIB):
+            build_oracle()
+        lib = ctypes.CDLL(ORACLE_LIB)
+        lib.ntco_geometry.argtypes = [ctypes.POINTER(_TextureSet), ctypes.POINTER(Geometry)]
+        lib.ntco_decode_mip.argtypes = [ctypes.POINTER(_TextureSet), ctypes.POINTER(Options), ctypes.c_int,
+                                        ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.ntco_sample.argtypes = [ctypes.POINTER(_TextureSet), ctypes.POINTER(Options), ctypes.c_void_p,
+                                    ctypes.c_size_t, ctypes.c_void_p]
+        lib.ntco_float_to_half.restype = ctypes.c_uint16
+        lib.ntco_float_to_half.argtypes = [ctypes.c_float]
+        lib.ntco_half_to_float.restype = ctypes.c_float
+        lib.ntco_half_to_float.argtypes = [ctypes.c_uint16]
+        lib.ntco_half_to_e4m3.restype = ctypes.c_uint8
+        lib.ntco_half_to_e4m3.argtypes = [ctypes.c_uint16]
+        lib.ntco_e4m3_to_float.restype = ctypes.c_float
+        lib.ntco_e4m3_to_float.argtypes = [ctypes.c_uint8]
+        lib.ntco_hgelu_clamp_half.restype = ctypes.c_uint16
+        lib.ntco_hgelu_clamp_half.argtypes = [ctypes.c_uint16]
+        _oracle = lib
+    return _oracle
+
+
+class OracleSet:
+    """A compressed texture set as the oracle sees it (arrays kept alive by this object)."""
+
+    def __init__(self, geometry, packed_latents: np.ndarray, int8_blob: bytes, fp8_blob: bytes):
+        self.geometry = geometry
+        self._latents = np.ascontiguousarray(packed_latents, dtype=np.uint16)
+        self._int8 = np.frombuffer(int8_blob, dtype=np.uint8).copy()
+        self._fp8 = np.frombuffer(fp8_blob, dtype=np.uint8).copy()
+        self.c = _TextureSet(geometry.width, geometry.height, geometry.channels, geometry.mips,
+                             geometry.grid_scale, geometry.num_features, self._latents.ctypes.data,
+                             self._int8.ctypes.data, self._fp8.ctypes.data)
+
+    @classmethod
+    def from_synthetic(cls, synthetic_set) -> "OracleSet":
+        return cls(synthetic_set.geometry, synthetic_set.packed_latents(), synthetic_set.int8_blob,
+                   synthetic_set.fp8_blob)
+
+    def c_geometry(self) -> Geometry:
+        out = Geometry()
+        if oracle_lib().ntco_geometry(ctypes.byref(self.c), ctypes.byref(out)) != 0:
+            raise ValueError("ntco_geometry rejected the texture set")
+        return out
+
+    def decode_mip(self, mip: int, use_int8: bool, numerics: int = NUMERICS_SPEC, y0: int = 0,
+                   y1: Optional[int] = None, threads: int = 0, **ref_switches) -> np.ndarray:
+        cm = self.geometry.color_mips[mip]
+        y1 = cm.height if y1 is None else y1
+        out = np.empty((y1 - y0, cm.width, self.geometry.channels), dtype=np.uint16)
+        opt = make_options(use_int8, numerics, threads, **ref_switches)
+        rc = oracle_lib().ntco_decode_mip(ctypes.byref(self.c), ctypes.byref(opt), mip, y0, y1, out.ctypes.data)
+        if rc != 0:
+            raise ValueError("ntco_decode_mip failed")
+        return out.view(np.float16)
+
+    def decode_all(self, use_int8: bool, numerics: int = NUMERICS_SPEC, threads: int = 0, **ref_switches) -> List[np.ndarray]:
+        return [self.decode_mip(m, use_int8, numerics, threads=threads, **ref_switches) for m in range(self.geometry.mips)]
+
+    def sample(self, queries: np.ndarray, use_int8: bool, numerics: int = NUMERICS_SPEC, threads: int = 0) -> np.ndarray:
+        queries = np.ascontiguousarray(queries, dtype=np.float32)
+        out = np.empty((queries.shape[0], self.geometry.channels), dtype=np.uint16)
+        opt = make_options(use_int8, numerics, threads)
+        rc = oracle_lib().ntco_sample(ctypes.byref(self.c), ctypes.byref(opt), queries.ctypes.data,
+                                      queries.shape[0], out.ctypes.data)
+        if rc != 0:
+            raise ValueError("ntco_sample failed")
+        return out.view(np.float16)
+
+
+# Switches of the reference-emulating numerics that reproduce the reference kernel's outputs
+# (see tests/golden/README.md for how they were pinned).
+REF_DEFAULTS = dict(refBlendFma=2, refQuantFma=1, refAccChunk=16, refAccMode=25, refActFma=0)
+
+
+def make_options(use_int8: bool, numerics: int, threads: int = 0, **ref_switches) -> Options:
+    switches = dict(REF_DEFAULTS)
+    switches.update(ref_switches)
+    return Options(WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8, numerics, threads, switches["refBlendFma"],
+                   switches["refQuantFma"], switches["refAccChunk"], switches["refAccMode"], switches["refActFma"])
+
+
+# ---------------------------------------------------------------------------------------------
+# The unmodified reference library (needs a GPU to decode)
+# ---------------------------------------------------------------------------------------------
+
+_ref = None
+
+
+def reference_available() -> bool:
+    return os.path.exists(REF_LIB)
+
+
+def reference_lib():
+    global _ref
+    if _ref is None:
+        lib = ctypes.CDLL(REF_LIB)
+        lib.ntcref_last_error.restype = ctypes.c_char_p
+        lib.ntcref_open.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int,
+                                    ctypes.POINTER(ctypes.c_void_p)]
+        lib.ntcref_probe_metadata.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_int)]
+        lib.ntcref_decompress.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
+        lib.ntcref_read_mip.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                        ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+        lib.ntcref_close.argtypes = [ctypes.c_void_p]
+        _ref = lib
+    return _ref
+
+
+def reference_probe(container: bytes) -> List[int]:
+    out = (ctypes.c_int * 8)()
+    lib = reference_lib()
+    rc = lib.ntcref_probe_metadata(container, len(container), out)
+    if rc != 0:
+        raise RuntimeError("reference loader rejected the container: %s" % lib.ntcref_last_error().decode())
+    return list(out)
+
+
+class ReferenceDecoder:
+    """The reference's CUDA decompression of one container, through its public API."""
+
+    def __init__(self, container: bytes, channels: int, device: int = 0):
+        self._lib = reference_lib()
+        self._container = container
+        self._handle = ctypes.c_void_p()
+        rc = self._lib.ntcref_open(container, len(container), device, channels * 2, ctypes.byref(self._handle))
+        if rc != 0:
+            raise RuntimeError("reference open failed: %s" % self._lib.ntcref_last_error().decode())
+        self.channels = channels
+
+    def decompress(self, use_int8: bool) -> float:
+        ms = ctypes.c_float()
+        rc = self._lib.ntcref_decompress(self._handle, 1 if use_int8 else 0, ctypes.byref(ms))
+        if rc != 0:
+            raise RuntimeError("reference Decompress failed: %s" % self._lib.ntcref_last_error().decode())
+        return float(ms.value)
+
+    def read_mip_into(self, mip: int, width: int, height: int, address: int, to_device: bool) -> None:
+        rc = self._lib.ntcref_read_mip(self._handle, mip, 0, self.channels, width, height, address, 1 if to_device else 0)
+        if rc != 0:
+            raise RuntimeError("reference ReadChannels failed: %s" % self._lib.ntcref_last_error().decode())
+
+    def read_mip(self, mip: int, width: int, height: int) -> np.ndarray:
+        out = np.empty((height, width, self.channels), dtype=np.float16)
+        self.read_mip_into(mip, width, height, out.ctypes.data, False)
+        return out
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.ntcref_close(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
