@@ -1,0 +1,126 @@
+/* ntcb.h - C ABI of the B200-native NTC decoder (libntcb200.so).
+ *
+ * This is the drop-in boundary for ONE path of LibNTC: CUDA decompression of a neural-compressed
+ * texture set (latents -> 48-wide input -> 48-64-48-32-16 MLP -> fp16 texels).  Every entry point
+ * takes plain pointers and sizes; each comment names the reference interface it replaces
+ * (paths relative to the reference project root).
+ *
+ * Conventions: functions return 0 (NTCB_OK) or a negative NtcbStatus; ntcb_last_error() returns a
+ * thread-local message for the last failing call on the calling thread (the reference's
+ * ntc::GetLastErrorMessage convention, src/Errors.cpp:21-52).  Nothing throws.  Device work is
+ * issued on the CUDA stream the caller passes (a cudaStream_t cast to void*; NULL = the legacy
+ * default stream the reference always uses).  There is no CPU fallback: without a usable GPU the
+ * compute entry points fail with NTCB_ERR_CUDA.
+ */
+#ifndef NTCB_H
+#define NTCB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NTCB_MAX_MIPS 16         /* NTC_MAX_MIPS, include/libntc/shaders/InferenceConstants.h:22 */
+#define NTCB_MAX_NEURAL_MIPS 8   /* NTC_MAX_NEURAL_MIPS, :24 */
+#define NTCB_INT8_BLOB_BYTES 9472 /* GenericInt8 weight blob, src/WeightLayout.cpp:142-268 */
+#define NTCB_FP8_BLOB_BYTES 8608  /* GenericFP8 weight blob */
+#define NTCB_STAGED_NETWORK_BYTES 11776 /* size of the device image ntcb_stage_network produces */
+#define NTCB_STATUS_WORDS 4
+
+typedef enum NtcbStatus
+{
+    NTCB_OK = 0,
+    NTCB_ERR_INVALID_ARGUMENT = -1, /* ntc::Status::InvalidArgument */
+    NTCB_ERR_CUDA = -2,             /* ntc::Status::CudaError / CudaUnavailable */
+    NTCB_ERR_FILE_UNRECOGNIZED = -3,/* ntc::Status::FileUnrecognized */
+    NTCB_ERR_FILE_INCOMPATIBLE = -4,/* ntc::Status::FileIncompatible */
+    NTCB_ERR_UNSUPPORTED = -5,      /* ntc::Status::Unsupported (e.g. GDeflate-compressed views) */
+    NTCB_ERR_OUT_OF_MEMORY = -6,    /* ntc::Status::OutOfMemory */
+    NTCB_ERR_DEVICE_TIMEOUT = -7,   /* a bounded wait inside a kernel gave up; see the status words */
+    NTCB_ERR_INVALID_STATE = -8,    /* ntc::Status::InvalidState */
+    NTCB_ERR_OUT_OF_RANGE = -9      /* ntc::Status::OutOfRange */
+} NtcbStatus;
+
+/* Which weight set decodes: the `useInt8Weights` argument of ITextureSet::Decompress
+   (include/libntc/ntc.h:933; src/TextureSet.cpp:1812,1826). */
+typedef enum NtcbWeightMode
+{
+    NTCB_WEIGHTS_INT8 = 0, /* GenericInt8: four int8 layers, int32 accumulation */
+    NTCB_WEIGHTS_FP8 = 1   /* GenericFP8: e4m3 layers 0-2 (fp32 accumulation), int8 output layer */
+} NtcbWeightMode;
+
+/* Layout of the decoded texels. */
+typedef enum NtcbOutputLayout
+{
+    /* The reference's internal texture-data layout (src/RegressionKernels.h:36-45,
+       src/ImageProcessing.h:20-33): per mip, half index = y*W*C + (c & ~1)*W + 2*x + (c & 1). */
+    NTCB_LAYOUT_PLANAR_PAIRS = 0,
+    /* Pixel-interleaved [y][x][c], what ITextureSet::ReadChannels(FLOAT16, pixelStride = 2*C)
+       hands back (src/TextureSet.cpp:915-985). */
+    NTCB_LAYOUT_INTERLEAVED = 1
+} NtcbOutputLayout;
+
+/* One colour mip to decode; mirrors the per-mip fields of InferenceKernelParams
+   (src/RegressionCommon.h:55-80) as TextureSet::Decompress fills them (src/TextureSet.cpp:1806-1829). */
+typedef struct NtcbMipDesc
+{
+    int32_t width, height;            /* referenceWidth / referenceHeight */
+    int32_t hiWidth, hiHeight;        /* highResLatentWidth / Height */
+    int32_t loWidth, loHeight;        /* lowResLatentWidth / Height */
+    uint64_t hiOffset, loOffset;      /* element (uint16) offset of layer 0 of each grid in `latents` */
+    uint64_t hiPlane, loPlane;        /* pixels per layer of each grid (distance between layers) */
+    float positionScale, positionLod; /* src/TextureSet.cpp:457-462 */
+    uint64_t outOffset;               /* element (fp16) offset of this mip in `out` */
+    int32_t rowBegin, rowEnd;         /* rows [rowBegin, rowEnd) are decoded: the unit of tile-row sharding */
+} NtcbMipDesc;
+
+/* Everything one decode launch needs; replaces cuda::Inference(InferenceKernelParams) called once
+   per mip (src/Inference.cu:159-165) together with its prologue kernels cuda::UnpackLatents
+   (src/Quantizer.cu:574-586) and cuda::ConvertNetworkFromQuantizedToFp16 (src/Quantizer.cu:462-480),
+   whose work happens inside the decode kernel / ntcb_stage_network. */
+typedef struct NtcbDecodeParams
+{
+    const uint16_t* latents; /* device: BGRA4 latent pixels, for each neural mip, for each layer, rows
+                                (the reference's encoded-pixel order, src/FeatureGridHost.cpp:140-155) */
+    const void* network;     /* device: NTCB_STAGED_NETWORK_BYTES produced by ntcb_stage_network */
+    void* out;               /* device: fp16 texels */
+    uint32_t* status;        /* device: NTCB_STATUS_WORDS words, zeroed by the caller before the launch;
+                                word 0 != 0 after the kernel means a bounded wait expired */
+    int32_t numMips;
+    int32_t numFeatures;     /* 4, 8, 12 or 16 */
+    int32_t channels;        /* even, 2..16 */
+    int32_t weightMode;      /* NtcbWeightMode, must match the staged network */
+    int32_t outputLayout;    /* NtcbOutputLayout */
+    int32_t reserved;
+    NtcbMipDesc mips[NTCB_MAX_MIPS];
+} NtcbDecodeParams;
+
+/* Thread-local message of the last failing call on this thread; never NULL.
+   Replaces ntc::GetLastErrorMessage (include/libntc/ntc.h:1337). */
+const char* ntcb_last_error(void);
+
+/* Textual name of a status code.  Replaces ntc::StatusToString (include/libntc/ntc.h:1341). */
+const char* ntcb_status_string(int status);
+
+/* Host only.  Converts a row-major weight blob as stored in NTC files (GenericInt8,
+   NTCB_INT8_BLOB_BYTES, or GenericFP8, NTCB_FP8_BLOB_BYTES) into the image the decode kernel copies
+   to shared memory: int8 / e4m3 matrices in the tensor core's K-major core-matrix order with K
+   padded to a multiple of 32, fp32 scales, int32 / fp16 biases.  `staged` receives
+   NTCB_STAGED_NETWORK_BYTES; the caller uploads it.  Replaces the weight preparation of
+   cuda::ConvertNetworkFromQuantizedToFp16 (src/Quantizer.cu:325-480). */
+int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void* staged);
+
+/* Decodes the mips (and row ranges) listed in `params` with one kernel launch on `stream`.
+   Asynchronous; the caller synchronises and may then read `status`.  Allocates nothing. */
+int ntcb_decode(const NtcbDecodeParams* params, void* stream);
+
+/* Number of kernel launches this library has issued from the calling process so far
+   (bookkeeping for benchmarks). */
+uint64_t ntcb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

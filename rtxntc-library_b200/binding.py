@@ -1,0 +1,186 @@
+"""ctypes bindings of the C ABI in include/ntcb.h (libntcb200.so) and a thin decoder object that
+keeps a texture set resident on one GPU.
+
+PyTorch is used only for device memory and streams; every computation goes through the C ABI.
+If the shared library is missing or cannot be loaded the import of this module fails: there is no
+fallback path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence, Tuple
+
+import numpy as np
+
+from .geometry import Geometry
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(_HERE, "libntcb200.so")
+
+MAX_MIPS = 16
+STAGED_NETWORK_BYTES = 11776
+STATUS_WORDS = 4
+WEIGHTS_INT8, WEIGHTS_FP8 = 0, 1
+LAYOUT_PLANAR_PAIRS, LAYOUT_INTERLEAVED = 0, 1
+
+
+class MipDesc(ctypes.Structure):
+    _fields_ = [("width", ctypes.c_int32), ("height", ctypes.c_int32),
+                ("hiWidth", ctypes.c_int32), ("hiHeight", ctypes.c_int32),
+                ("loWidth", ctypes.c_int32), ("loHeight", ctypes.c_int32),
+                ("hiOffset", ctypes.c_uint64), ("loOffset", ctypes.c_uint64),
+                ("hiPlane", ctypes.c_uint64), ("loPlane", ctypes.c_uint64),
+                ("positionScale", ctypes.c_float), ("positionLod", ctypes.c_float),
+                ("outOffset", ctypes.c_uint64),
+                ("rowBegin", ctypes.c_int32), ("rowEnd", ctypes.c_int32)]
+
+
+class DecodeParams(ctypes.Structure):
+    _fields_ = [("latents", ctypes.c_void_p), ("network", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("status", ctypes.c_void_p),
+                ("numMips", ctypes.c_int32), ("numFeatures", ctypes.c_int32), ("channels", ctypes.c_int32),
+                ("weightMode", ctypes.c_int32), ("outputLayout", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("mips", MipDesc * MAX_MIPS)]
+
+
+class NtcbError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__("%s (%d): %s" % (lib().ntcb_status_string(code).decode(), code, message))
+        self.code = code
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIBRARY_PATH):
+            raise ImportError("libntcb200.so is not built; run __graft_entry__.build() "
+                              "(make -C rtxntc-library_b200/csrc)")
+        handle = ctypes.CDLL(LIBRARY_PATH)
+        handle.ntcb_last_error.restype = ctypes.c_char_p
+        handle.ntcb_status_string.restype = ctypes.c_char_p
+        handle.ntcb_status_string.argtypes = [ctypes.c_int]
+        handle.ntcb_launch_count.restype = ctypes.c_uint64
+        handle.ntcb_stage_network.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+        handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
+        _lib = handle
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise NtcbError(code, lib().ntcb_last_error().decode())
+
+
+def stage_network(blob: bytes, weight_mode: int) -> np.ndarray:
+    """Host-side conversion of a GenericInt8 / GenericFP8 blob into the kernel's image."""
+    staged = np.zeros(STAGED_NETWORK_BYTES, dtype=np.uint8)
+    source = np.frombuffer(blob, dtype=np.uint8)
+    check(lib().ntcb_stage_network(source.ctypes.data, len(blob), weight_mode, staged.ctypes.data))
+    return staged
+
+
+def out_elements(geo: Geometry) -> int:
+    return geo.total_texels * geo.channels
+
+
+def fill_params(geo: Geometry, latents_ptr: int, network_ptr: int, out_ptr: int, status_ptr: int, weight_mode: int,
+                layout: int = LAYOUT_INTERLEAVED, mips: Optional[Sequence[int]] = None,
+                row_ranges: Optional[dict] = None) -> DecodeParams:
+    """Describes a decode of `mips` (default: all) of a texture set whose latents are resident in
+    the reference's encoded-pixel order.  `row_ranges` maps mip -> (rowBegin, rowEnd)."""
+    params = DecodeParams()
+    params.latents = latents_ptr
+    params.network = network_ptr
+    params.out = out_ptr
+    params.status = status_ptr
+    params.numFeatures = geo.num_features
+    params.channels = geo.channels
+    params.weightMode = weight_mode
+    params.outputLayout = layout
+    selected = list(range(geo.mips)) if mips is None else list(mips)
+    params.numMips = len(selected)
+    for slot, mip in enumerate(selected):
+        cm = geo.color_mips[mip]
+        lod = cm.neural_lod
+        d = params.mips[slot]
+        d.width, d.height = cm.width, cm.height
+        d.hiWidth, d.hiHeight = geo.latent_width[lod], geo.latent_height[lod]
+        d.loWidth, d.loHeight = geo.latent_width[lod + 1], geo.latent_height[lod + 1]
+        d.hiOffset = geo.latent_pixel_offset[lod] * geo.num_layers
+        d.loOffset = geo.latent_pixel_offset[lod + 1] * geo.num_layers
+        d.hiPlane = d.hiWidth * d.hiHeight
+        d.loPlane = d.loWidth * d.loHeight
+        d.positionScale, d.positionLod = cm.position_scale, cm.position_lod
+        d.outOffset = cm.texel_offset * geo.channels
+        begin, end = (0, cm.height) if not row_ranges or mip not in row_ranges else row_ranges[mip]
+        d.rowBegin, d.rowEnd = begin, end
+    return params
+
+
+class ResidentTextureSet:
+    """A compressed texture set uploaded to one GPU: packed latents, both staged networks, an
+    output buffer for the whole mip chain and the status words."""
+
+    def __init__(self, geo: Geometry, packed_latents: np.ndarray, int8_blob: bytes, fp8_blob: bytes,
+                 device: str = "cuda:0", layout: int = LAYOUT_INTERLEAVED, allocate_output: bool = True):
+        import torch
+
+        self.torch = torch
+        self.geometry = geo
+        self.device = torch.device(device)
+        self.layout = layout
+        lib()
+        self.latents = torch.from_numpy(np.ascontiguousarray(packed_latents).view(np.int16)).to(self.device)
+        self.networks = {
+            WEIGHTS_INT8: torch.from_numpy(stage_network(int8_blob, WEIGHTS_INT8)).to(self.device),
+            WEIGHTS_FP8: torch.from_numpy(stage_network(fp8_blob, WEIGHTS_FP8)).to(self.device),
+        }
+        self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=self.device)
+        self.out = torch.empty(out_elements(geo), dtype=torch.float16, device=self.device) if allocate_output else None
+
+    @classmethod
+    def from_synthetic(cls, synthetic_set, **kwargs) -> "ResidentTextureSet":
+        return cls(synthetic_set.geometry, synthetic_set.packed_latents(), synthetic_set.int8_blob,
+                   synthetic_set.fp8_blob, **kwargs)
+
+    def params(self, use_int8: bool, out=None, mips=None, row_ranges=None) -> DecodeParams:
+        mode = WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8
+        out = self.out if out is None else out
+        return fill_params(self.geometry, self.latents.data_ptr(), self.networks[mode].data_ptr(), out.data_ptr(),
+                           self.status.data_ptr(), mode, self.layout, mips, row_ranges)
+
+    def launch(self, params: DecodeParams) -> None:
+        """Queues one decode on torch's current stream of this device."""
+        stream = self.torch.cuda.current_stream(self.device).cuda_stream
+        check(lib().ntcb_decode(ctypes.byref(params), ctypes.c_void_p(stream)))
+
+    def decode(self, use_int8: bool, mips=None, row_ranges=None) -> None:
+        with self.torch.cuda.device(self.device):
+            self.launch(self.params(use_int8, mips=mips, row_ranges=row_ranges))
+
+    def check_status(self) -> None:
+        words = self.status.cpu().numpy()
+        if words[0] != 0:
+            raise NtcbError(-7, "a bounded wait in the decode kernel expired (tile %d, layer %d)" % (words[1], words[2]))
+
+    def mip_view(self, mip: int):
+        """The decoded fp16 texels of one mip as a tensor: [H][W][C] (interleaved layout) or
+        [H][C/2][W][2] (planar-pair layout)."""
+        cm = self.geometry.color_mips[mip]
+        c = self.geometry.channels
+        flat = self.out[cm.texel_offset * c:(cm.texel_offset + cm.width * cm.height) * c]
+        if self.layout == LAYOUT_INTERLEAVED:
+            return flat.view(cm.height, cm.width, c)
+        return flat.view(cm.height, c // 2, cm.width, 2)
+
+    def mip_numpy(self, mip: int) -> np.ndarray:
+        """One decoded mip as a numpy array [H][W][C] regardless of the device layout."""
+        view = self.mip_view(mip).cpu().numpy()
+        if self.layout == LAYOUT_INTERLEAVED:
+            return view
+        h, pairs, w, _ = view.shape
+        return view.transpose(0, 2, 1, 3).reshape(h, w, pairs * 2)

@@ -1,0 +1,616 @@
+// NTC decode kernel for sm_100a: one launch decodes every listed colour mip of a texture set.
+//
+// Work decomposition.  A tile is 32x4 texels; one CTA of 128 threads owns one tile at a time
+// (thread = texel = one row of the tile's 128x{64,48,32,16} GEMM chain = one TMEM lane) and walks
+// the tile list of the whole mip chain with a grid stride.  Several CTAs are resident per SM, so
+// the SIMT phases of one tile overlap the tensor-core phases of the others.
+//
+// Per tile:
+//   1. every thread samples the two latent grids for its texel (packed BGRA4 pixels, nibble ->
+//      binary16 through a 256-entry shared-memory table, bilinear blend in binary16), appends the
+//      positional encoding and quantises the 48 inputs to int8 codes or e4m3, and writes its 64-byte
+//      row of the A operand straight into the tensor core's K-major core-matrix order (a 16-byte
+//      chunk per store, consecutive threads hit consecutive chunks: conflict-free);
+//   2. one thread issues tcgen05.mma (kind::i8 or kind::f8f6f4, M=128, N=64/48/32/16, K=32 per
+//      instruction) against the weights resident in shared memory; accumulators live in TMEM;
+//   3. after the commit arrives on the mbarrier every thread pulls its row of accumulators with
+//      tcgen05.ld, applies bias/scale and the clamped HGELU in packed binary16, re-quantises and
+//      writes the next layer's A operand over the previous one;
+//   4. after the fourth layer the epilogue scales, converts to fp16 and stores.
+//
+// Arithmetic contract (what the CPU checker restates): everything outside the matrix products is
+// done operation by operation as the reference CUDA kernel does it (src/FeatureGridDevice.h:33-98,
+// src/RegressionKernels.h:59-85, src/tin/tin_mlp.h:22-37, src/tin/tin_activation.h:88-104); the
+// matrix products accumulate exactly (int32, or fp32 for e4m3 operands) instead of in binary16.
+//
+// Every wait on the mbarrier is bounded; on expiry the CTA records an error in the status words,
+// skips the remaining tiles, releases its TMEM columns and exits.
+
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "decode_kernel.h"
+
+namespace ntcb
+{
+namespace
+{
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t SharedAddress(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void MbarrierInit(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void FenceBarrierInit()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait: returns false when the barrier did not complete within the spin budget.
+__device__ __forceinline__ bool MbarrierWaitBounded(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    {
+        if (MbarrierTryWait(bar, parity))
+            return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void FenceProxyAsyncShared()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void TcgenFenceBeforeSync()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void TcgenFenceAfterSync()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void TmemAlloc(uint32_t sharedSlot, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sharedSlot), "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void TmemFree(uint32_t address, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 32 bytes of 8-bit operands.
+template <bool kFp8>
+__device__ __forceinline__ void Umma(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
+{
+    if (kFp8)
+    {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmemD),
+            "l"(descA), "l"(descB), "r"(instr), "r"(accumulate)
+            : "memory");
+    }
+    else
+    {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmemD),
+            "l"(descA), "l"(descB), "r"(instr), "r"(accumulate)
+            : "memory");
+    }
+}
+
+__device__ __forceinline__ void UmmaCommit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void TmemLoad16(uint32_t address, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address)
+        : "memory");
+}
+
+__device__ __forceinline__ void TmemLoadWait()
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8x16-byte core matrices; `leadingBytes`
+// separates core matrices along K, `strideBytes` separates 8-row groups along M/N.
+__device__ __forceinline__ uint64_t MakeSmemDescriptor(uint32_t sharedAddress, uint32_t leadingBytes, uint32_t strideBytes)
+{
+    uint64_t desc = 0;
+    desc |= uint64_t((sharedAddress & 0x3FFFF) >> 4);
+    desc |= uint64_t((leadingBytes >> 4) & 0x3FFF) << 16;
+    desc |= uint64_t((strideBytes >> 4) & 0x3FFF) << 32;
+    desc |= uint64_t(1) << 46; // descriptor version of this architecture
+    return desc;               // base offset 0, layout type 0 (no swizzle)
+}
+
+// Instruction descriptor: dense, K-major A and B, M = 128.
+__host__ __device__ constexpr uint32_t MakeInstrDescriptor(bool fp8, int n)
+{
+    // bits 4-5: accumulator format (1 = f32, 2 = s32); bits 7-9 / 10-12: A / B format
+    // (f8f6f4: 0 = e4m3; i8: 1 = signed); bits 17-22: N >> 3; bits 24-28: M >> 4.
+    return (fp8 ? (1u << 4) : (2u << 4)) | (fp8 ? 0u : (1u << 7) | (1u << 10)) | (uint32_t(n >> 3) << 17) |
+           (uint32_t(128 >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Small arithmetic helpers
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t AsU32(__half2 v)
+{
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ __half2 AsHalf2(uint32_t v)
+{
+    return *reinterpret_cast<__half2*>(&v);
+}
+
+// Quantises a pair of network inputs.  Int8: floor(x * 127.5 - 0.5) clamped to +-127
+// (src/tin/tin_mlp.h:25-31), returned as the low bytes of the two 16-bit lanes.  FP8: round to
+// nearest even e4m3, saturating (src/tin/tin_activation.h:44-48), returned as two packed bytes.
+template <bool kFp8>
+__device__ __forceinline__ uint32_t QuantizeInputPair(__half2 x)
+{
+    if (kFp8)
+    {
+        return uint32_t(__nv_cvt_halfraw2_to_fp8x2(static_cast<__half2_raw>(x), __NV_SATFINITE, __NV_E4M3));
+    }
+    else
+    {
+        __half2 y = __hfma2(x, __float2half2_rn(127.5f), __float2half2_rn(-0.5f));
+        y = h2floor(y);
+        y = __hmax2(__hmin2(y, __float2half2_rn(127.f)), __float2half2_rn(-127.f));
+        // integer-valued: adding 1536 puts the two's-complement code in the low byte of each lane
+        return AsU32(__hadd2_rn(y, __float2half2_rn(1536.f)));
+    }
+}
+
+// Two quantised pairs -> four operand bytes.
+template <bool kFp8>
+__device__ __forceinline__ uint32_t PackCodes(uint32_t pair0, uint32_t pair1)
+{
+    return kFp8 ? __byte_perm(pair0, pair1, 0x5410) : __byte_perm(pair0, pair1, 0x6420);
+}
+
+// Clamped HGELU in binary16 (src/tin/tin_activation.h:88-92) followed by re-quantisation:
+// e4m3 when `toFp8`, otherwise the int8 code rint(y * 80) - 113 (src/tin/tin_activation.h:94-99,
+// the -113 offset is folded into the next layer's stored bias, src/Quantizer.cu:176-181).
+template <bool kToFp8>
+__device__ __forceinline__ uint32_t ActivatePair(__half2 x)
+{
+    const __half2 third = __float2half2_rn(1 / 3.f);
+    __half2 t = __hfma2_sat(third, x, __float2half2_rn(0.5f));
+    __half2 m = __hmin2(x, __float2half2_rn(3.f));
+    __half2 y = __hmul2_rn(m, t);
+    if (kToFp8)
+    {
+        return uint32_t(__nv_cvt_halfraw2_to_fp8x2(static_cast<__half2_raw>(y), __NV_SATFINITE, __NV_E4M3));
+    }
+    else
+    {
+        __half2 p = __hmul2_rn(y, __float2half2_rn(80.f));
+        __half2 r = __hadd2_rn(p, __float2half2_rn(1536.f)); // rint(p): ulp is 1 in [1024, 2048)
+        r = __hadd2_rn(r, __float2half2_rn(-113.f));         // exact
+        return AsU32(r);
+    }
+}
+
+struct GridTaps
+{
+    int o00, o01, o10, o11;
+    __half2 w00, w01, w10, w11;
+};
+
+// Bilinear footprint of one texel in one latent grid (src/FeatureGridDevice.h:33-58).
+__device__ __forceinline__ void SetupTaps(float u, float v, int w, int h, GridTaps& taps)
+{
+    float px = __fmaf_rn(u, float(w), -0.5f);
+    float py = __fmaf_rn(v, float(h), -0.5f);
+    float xbf = floorf(px), ybf = floorf(py);
+    float dx = __fsub_rn(px, xbf), dy = __fsub_rn(py, ybf);
+    float dxn = __fsub_rn(1.f, dx), dyn = __fsub_rn(1.f, dy);
+    int xb = int(xbf), yb = int(ybf);
+    // wrap addressing; the sample position is < size - 0.5, so only -1 needs folding
+    int x0 = xb < 0 ? xb + w : xb;
+    int y0 = yb < 0 ? yb + h : yb;
+    int x1 = (x0 + 1 == w) ? 0 : x0 + 1;
+    int y1 = (y0 + 1 == h) ? 0 : y0 + 1;
+    taps.o00 = y0 * w + x0;
+    taps.o01 = y0 * w + x1;
+    taps.o10 = y1 * w + x0;
+    taps.o11 = y1 * w + x1;
+    taps.w00 = __half2half2(__float2half_rn(__fmul_rn(dxn, dyn)));
+    taps.w01 = __half2half2(__float2half_rn(__fmul_rn(dx, dyn)));
+    taps.w10 = __half2half2(__float2half_rn(__fmul_rn(dxn, dy)));
+    taps.w11 = __half2half2(__float2half_rn(__fmul_rn(dx, dy)));
+}
+
+// One latent pixel layer (four 4-bit features) of one grid -> four quantised inputs.
+// Blend order as the reference build evaluates it: fma(l11,w3, fma(l10,w2, fma(l00,w0, l01*w1))).
+template <bool kFp8>
+__device__ __forceinline__ uint32_t SampleLayer(const uint16_t* __restrict__ plane, const GridTaps& taps,
+    const uint32_t* __restrict__ lut)
+{
+    uint32_t p00 = __ldg(plane + taps.o00), p01 = __ldg(plane + taps.o01);
+    uint32_t p10 = __ldg(plane + taps.o10), p11 = __ldg(plane + taps.o11);
+    uint32_t pairs[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+    {
+        __half2 l00 = AsHalf2(lut[(p00 >> (8 * j)) & 0xFF]), l01 = AsHalf2(lut[(p01 >> (8 * j)) & 0xFF]);
+        __half2 l10 = AsHalf2(lut[(p10 >> (8 * j)) & 0xFF]), l11 = AsHalf2(lut[(p11 >> (8 * j)) & 0xFF]);
+        __half2 d = __hmul2_rn(l01, taps.w01);
+        d = __hfma2(l00, taps.w00, d);
+        d = __hfma2(l10, taps.w10, d);
+        d = __hfma2(l11, taps.w11, d);
+        d = __hfma2(d, __float2half2_rn(2.f), __float2half2_rn(-1.f));
+        pairs[j] = QuantizeInputPair<kFp8>(d);
+    }
+    return PackCodes<kFp8>(pairs[0], pairs[1]);
+}
+
+__device__ __forceinline__ float Frac(float t)
+{
+    return __fsub_rn(t, floorf(t));
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+
+
+struct __align__(16) SharedStorage
+{
+    uint8_t network[kStagedNetworkBytes]; // weights in core-matrix order, scales, biases
+    uint8_t operandA[128 * 64];           // A operand of the current layer, core-matrix order
+    uint32_t latentTable[256];            // byte (two nibbles) -> two binary16 latent values
+    uint64_t barrier;
+    uint32_t tmemBase;
+};
+
+struct TileContext
+{
+    int tid;
+    uint32_t tmemBase, tmemLane, barrier, operandA, networkBase;
+    int tile, x, y;
+};
+
+// One layer of the MLP for the CTA's current tile: barrier, MMA issue, wait, then either the
+// activation + re-quantisation into the next A operand (layers 0-2) or the output epilogue
+// (layer 3).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
+template <bool kFp8, int kLayer>
+__device__ __forceinline__ int RunLayer(const KernelParams& params, const KernelMip& mip, SharedStorage& shared,
+    const TileContext& ctx, uint32_t& phase, int& failed)
+{
+    constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
+    constexpr int kK = kLayer == 3 ? 32 : 64;
+    constexpr int kWeightOffset =
+        kLayer == 0 ? kWeightOffset0 : kLayer == 1 ? kWeightOffset1 : kLayer == 2 ? kWeightOffset2 : kWeightOffset3;
+    constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
+    const int tid = ctx.tid;
+
+    // Makes the A operand written before this call visible to the tensor core, orders this thread's
+    // TMEM reads before the next MMA, and agrees on whether any thread gave up waiting.
+    FenceProxyAsyncShared();
+    TcgenFenceBeforeSync();
+    if (__syncthreads_or(failed))
+        return 1;
+
+    if (tid == 0)
+    {
+        TcgenFenceAfterSync();
+        constexpr uint32_t instr = MakeInstrDescriptor(kLayerFp8, kN);
+#pragma unroll
+        for (int kStep = 0; kStep < kK / 32; ++kStep)
+        {
+            // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
+            uint64_t descA = MakeSmemDescriptor(ctx.operandA + kStep * 2 * 2048, 2048, 128);
+            uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
+            Umma<kLayerFp8>(ctx.tmemBase, descA, descB, instr, kStep != 0);
+        }
+        UmmaCommit(ctx.barrier);
+    }
+
+    if (!MbarrierWaitBounded(ctx.barrier, phase))
+    {
+        failed = 1;
+        params.status[0] = kStatusBarrierTimeout;
+        params.status[1] = uint32_t(ctx.tile);
+        params.status[2] = uint32_t(kLayer);
+    }
+    phase ^= 1;
+    TcgenFenceAfterSync();
+
+    const float* scale = reinterpret_cast<const float*>(shared.network + kScaleOffset) + kLayer * 64;
+    const int32_t* biasI = reinterpret_cast<const int32_t*>(shared.network + kBiasOffset) + kLayer * 64;
+    const __half2* biasH = reinterpret_cast<const __half2*>(shared.network + kBiasOffset + kLayer * 256);
+
+    if (kLayer < 3)
+    {
+        uint32_t acc[kN / 16][16];
+#pragma unroll
+        for (int c = 0; c < kN / 16; ++c)
+            TmemLoad16(ctx.tmemLane + c * 16, acc[c]);
+        TmemLoadWait();
+
+        constexpr bool kNextFp8 = kFp8 && kLayer < 2; // layer 2 always re-quantises to int8
+        uint4* rowChunk = reinterpret_cast<uint4*>(shared.operandA) + tid;
+#pragma unroll
+        for (int c = 0; c < kN / 16; ++c)
+        {
+            uint32_t pairs[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+            {
+                const int col = c * 16 + 2 * j;
+                __half2 xh;
+                if (kLayerFp8)
+                {
+                    xh = __floats2half2_rn(__uint_as_float(acc[c][2 * j]), __uint_as_float(acc[c][2 * j + 1]));
+                    xh = __hadd2_rn(xh, biasH[col >> 1]);
+                }
+                else
+                {
+                    // include/libntc/shaders/Inference.hlsli:146-165: float(acc + bias) * scale
+                    float f0 = __fmul_rn(float(int32_t(acc[c][2 * j]) + biasI[col]), scale[col]);
+                    float f1 = __fmul_rn(float(int32_t(acc[c][2 * j + 1]) + biasI[col + 1]), scale[col + 1]);
+                    xh = __floats2half2_rn(f0, f1);
+                }
+                pairs[j] = ActivatePair<kNextFp8>(xh);
+            }
+            rowChunk[c * 128] = make_uint4(PackCodes<kNextFp8>(pairs[0], pairs[1]), PackCodes<kNextFp8>(pairs[2], pairs[3]),
+                                           PackCodes<kNextFp8>(pairs[4], pairs[5]), PackCodes<kNextFp8>(pairs[6], pairs[7]));
+        }
+        if (kLayer == 1)
+            rowChunk[3 * 128] = make_uint4(0, 0, 0, 0); // layer 2 has 48 inputs, K is padded to 64
+    }
+    else
+    {
+        // output epilogue (src/Inference.cu:121-135)
+        uint32_t acc[16];
+        TmemLoad16(ctx.tmemLane, acc);
+        TmemLoadWait();
+        const int x = ctx.x, y = ctx.y;
+        const int channelPairs = params.channels >> 1;
+        const bool inside = x < mip.width && y < mip.rowEnd;
+        __half* out = params.out + mip.outOffset;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            if (j < channelPairs)
+            {
+                float f0 = __fmul_rn(float(int32_t(acc[2 * j]) + biasI[2 * j]), scale[2 * j]);
+                float f1 = __fmul_rn(float(int32_t(acc[2 * j + 1]) + biasI[2 * j + 1]), scale[2 * j + 1]);
+                uint32_t bits = AsU32(__floats2half2_rn(f0, f1));
+                // Inf / NaN -> 0 (src/CudaUtils.h:30-35)
+                if ((bits & 0x7C00u) == 0x7C00u) bits &= 0xFFFF0000u;
+                if ((bits & 0x7C000000u) == 0x7C000000u) bits &= 0x0000FFFFu;
+                if (inside)
+                {
+                    size_t index;
+                    if (params.outputLayout == kLayoutPlanarPairs)
+                        index = (size_t(y) * mip.width * channelPairs + size_t(j) * mip.width + x) * 2;
+                    else
+                        index = (size_t(y) * mip.width + x) * params.channels + 2 * j;
+                    *reinterpret_cast<uint32_t*>(out + index) = bits;
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+template <bool kFp8>
+__global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSm) DecodeKernel(const __grid_constant__ KernelParams params)
+{
+    __shared__ SharedStorage shared;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+
+    // ---- one-time setup -----------------------------------------------------------------
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(params.network);
+        uint4* dst = reinterpret_cast<uint4*>(shared.network);
+        for (int i = tid; i < kStagedNetworkBytes / 16; i += kThreadsPerCta)
+            dst[i] = __ldg(src + i);
+        // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
+        for (int i = tid; i < 256; i += kThreadsPerCta)
+        {
+            __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
+            __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
+            shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
+        }
+        if (tid == 0)
+        {
+            MbarrierInit(SharedAddress(&shared.barrier), 1);
+            FenceBarrierInit();
+        }
+        if (warp == 0)
+            TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
+        FenceProxyAsyncShared(); // the weights are read by the tensor core (async proxy)
+        TcgenFenceBeforeSync();
+        __syncthreads();
+        TcgenFenceAfterSync();
+    }
+    const uint32_t tmemBase = shared.tmemBase;
+    const uint32_t tmemLane = tmemBase + (uint32_t(warp * 32) << 16);
+    const uint32_t barrier = SharedAddress(&shared.barrier);
+    const uint32_t operandA = SharedAddress(shared.operandA);
+    const uint32_t networkBase = SharedAddress(shared.network);
+    uint32_t phase = 0;
+    int failed = 0;   // this thread gave up on a wait
+    int aborted = 0;  // some thread of the CTA did (uniform: comes out of a barrier)
+
+    for (int tile = blockIdx.x; tile < params.totalTiles; tile += gridDim.x)
+    {
+        // ---- locate the tile ------------------------------------------------------------
+        int mipIndex = 0;
+        while (mipIndex + 1 < params.numMips && tile >= params.mips[mipIndex + 1].firstTile)
+            ++mipIndex;
+        const KernelMip& mip = params.mips[mipIndex];
+        const int local = tile - mip.firstTile;
+        const int tileY = local / mip.tilesX;
+        const int tileX = local - tileY * mip.tilesX;
+        const int x = tileX * kTileWidth + lane;
+        const int y = mip.rowBegin + tileY * kTileHeight + warp;
+        // threads past the right / bottom edge compute a clamped texel and store nothing
+        const int xs = min(x, mip.width - 1);
+        const int ys = min(y, mip.rowEnd - 1);
+
+        // ---- 1. network inputs -> A operand ----------------------------------------------
+        {
+            uint32_t words[16];
+            const uint32_t zeroWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(0.f)),
+                                                      QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
+#pragma unroll
+            for (int i = 0; i < 12; ++i)
+                words[i] = zeroWord;
+#pragma unroll
+            for (int i = 12; i < 16; ++i)
+                words[i] = 0; // K padding
+
+            // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
+            const float u = __fmul_rn(__fadd_rn(float(xs), 0.5f), mip.invWidth);
+            const float v = __fmul_rn(__fadd_rn(float(ys), 0.5f), mip.invHeight);
+
+            GridTaps taps;
+            SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
+            const uint16_t* hi = params.latents + mip.hiOffset;
+#pragma unroll
+            for (int layer = 0; layer < 4; ++layer)
+                if (layer < params.numLayers)
+                    words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable);
+
+            SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
+            const uint16_t* lo = params.latents + mip.loOffset;
+#pragma unroll
+            for (int layer = 0; layer < 4; ++layer)
+                if (layer < params.numLayers)
+                    words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable);
+
+            // src/RegressionKernels.h:59-85
+            float xf = __fmul_rn(float(xs), mip.positionScale);
+            float yf = __fmul_rn(float(ys), mip.positionScale);
+#pragma unroll
+            for (int wave = 0; wave < 3; ++wave)
+            {
+                float ex = __fmaf_rn(Frac(xf), 2.f, -1.f), ey = __fmaf_rn(Frac(yf), 2.f, -1.f);
+                float ez = __fmaf_rn(Frac(__fadd_rn(xf, 0.25f)), 2.f, -1.f);
+                float ew = __fmaf_rn(Frac(__fadd_rn(yf, 0.25f)), 2.f, -1.f);
+                words[8 + wave] = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__floats2half2_rn(ex, ey)),
+                                                   QuantizeInputPair<kFp8>(__floats2half2_rn(ez, ew)));
+                xf = __fmul_rn(xf, 2.f);
+                yf = __fmul_rn(yf, 2.f);
+            }
+            words[11] = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(mip.positionLod)),
+                                        QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
+
+            uint4* rowChunk = reinterpret_cast<uint4*>(shared.operandA) + tid;
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk)
+                rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
+        }
+
+        // ---- 2./3./4. the four layers ------------------------------------------------------
+        TileContext ctx;
+        ctx.tid = tid;
+        ctx.tmemBase = tmemBase;
+        ctx.tmemLane = tmemLane;
+        ctx.barrier = barrier;
+        ctx.operandA = operandA;
+        ctx.networkBase = networkBase;
+        ctx.tile = tile;
+        ctx.x = x;
+        ctx.y = y;
+        aborted = RunLayer<kFp8, 0>(params, mip, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 1>(params, mip, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 2>(params, mip, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 3>(params, mip, shared, ctx, phase, failed);
+        if (aborted)
+            break;
+        // No barrier is needed here: step 1 of the next tile only writes the A operand, which the
+        // last MMA of this tile (already complete) was the last to read, and the barrier at the top
+        // of the next layer loop orders this tile's TMEM reads before the next MMA.
+    }
+
+    // ---- teardown -------------------------------------------------------------------------
+    TcgenFenceBeforeSync();
+    aborted = __syncthreads_or(failed);
+    if (aborted && tid == 0)
+        (void)MbarrierWaitBounded(barrier, phase ^ 1); // one more bounded chance for work in flight to drain
+    __syncthreads();
+    if (warp == 0)
+        TmemFree(tmemBase, kTmemColumns);
+}
+
+} // namespace
+
+cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
+{
+    if (fp8)
+        DecodeKernel<true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+    else
+        DecodeKernel<false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+    return cudaGetLastError();
+}
+
+cudaError_t DecodeOccupancy(bool fp8, int* ctasPerSm)
+{
+    if (fp8)
+        return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctasPerSm, DecodeKernel<true>, kThreadsPerCta, 0);
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctasPerSm, DecodeKernel<false>, kThreadsPerCta, 0);
+}
+
+} // namespace ntcb

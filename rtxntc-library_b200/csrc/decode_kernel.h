@@ -1,0 +1,63 @@
+// Internal interface between the C ABI (ntcb.cu) and the sm_100a decode kernel (decode_kernel.cu).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ntcb
+{
+
+constexpr int kTileWidth = 32;
+constexpr int kTileHeight = 4;
+constexpr int kThreadsPerCta = kTileWidth * kTileHeight; // one thread per texel of a tile
+constexpr int kCtasPerSm = 4;
+constexpr int kTmemColumns = 64;           // widest accumulator (layer 0: 64 outputs)
+constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait is declared expired
+
+// Image of the network in shared memory (produced on the host by ntcb_stage_network).
+// Weight matrix of layer l: N_l rows (outputs) x K_l bytes (inputs, padded to a multiple of 32) in
+// K-major core-matrix order: byte (n, k) lives at (k / 16) * (N_l * 16) + n * 16 + (k % 16).
+constexpr int kWeightOffset0 = 0;     // 64 x 64
+constexpr int kWeightOffset1 = 4096;  // 48 x 64
+constexpr int kWeightOffset2 = 7168;  // 32 x 64
+constexpr int kWeightOffset3 = 9216;  // 16 x 32
+constexpr int kScaleOffset = 9728;    // float[4][64]
+constexpr int kBiasOffset = 10752;    // per layer 256 bytes: int32[64] (int8 layers) or half[64] (e4m3 layers)
+constexpr int kStagedNetworkBytes = 11776;
+
+constexpr uint32_t kStatusBarrierTimeout = 1;
+
+constexpr int kLayoutPlanarPairs = 0;
+constexpr int kLayoutInterleaved = 1;
+
+struct KernelMip
+{
+    int width, height;
+    int rowBegin, rowEnd;
+    int hiWidth, hiHeight, loWidth, loHeight;
+    unsigned long long hiOffset, loOffset, hiPlane, loPlane;
+    unsigned long long outOffset;
+    float invWidth, invHeight;
+    float positionScale, positionLod;
+    int firstTile, tilesX;
+};
+
+struct KernelParams
+{
+    const uint16_t* latents;
+    const uint8_t* network;
+    __half* out;
+    uint32_t* status;
+    int numMips;
+    int numLayers;
+    int channels;
+    int outputLayout;
+    int totalTiles;
+    KernelMip mips[16];
+};
+
+cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
+cudaError_t DecodeOccupancy(bool fp8, int* ctasPerSm);
+
+} // namespace ntcb

@@ -1,0 +1,314 @@
+// C ABI of the decoder: argument checking, weight staging and the kernel launch.
+// The declarations and the reference interfaces they stand in for are in include/ntcb.h.
+
+#include "ntcb.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "decode_kernel.h"
+#include "error.h"
+
+namespace ntcb
+{
+
+thread_local char g_lastError[1024] = "";
+std::atomic<uint64_t> g_launchCount{0};
+
+void SetError(const char* format, ...)
+{
+    va_list args;
+    va_start(args, format);
+    vsnprintf(g_lastError, sizeof g_lastError, format, args);
+    va_end(args);
+}
+
+void ClearError()
+{
+    g_lastError[0] = 0;
+}
+
+int CudaFailure(const char* call, cudaError_t error)
+{
+    // same wording as the reference's SetCudaErrorMessage (src/Errors.cpp:43-46)
+    SetError("Call to %s failed, error code = %s.", call, cudaGetErrorName(error));
+    return NTCB_ERR_CUDA;
+}
+
+void CountLaunch()
+{
+    g_launchCount.fetch_add(1, std::memory_order_relaxed);
+}
+
+namespace
+{
+
+constexpr int kLayerInputs[4] = {48, 64, 48, 32};
+constexpr int kLayerOutputs[4] = {64, 48, 32, 16};
+constexpr int kLayerPaddedK[4] = {64, 64, 64, 32};
+constexpr int kWeightOffsets[4] = {kWeightOffset0, kWeightOffset1, kWeightOffset2, kWeightOffset3};
+
+// Number of CTAs that fill the current device, cached per device.
+int ResidentCtas(bool fp8, int* outCtas)
+{
+    static std::atomic<int> cache[64][2];
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaGetDevice", err);
+    if (device >= 0 && device < 64)
+    {
+        int cached = cache[device][fp8 ? 1 : 0].load(std::memory_order_relaxed);
+        if (cached > 0)
+        {
+            *outCtas = cached;
+            return NTCB_OK;
+        }
+    }
+    int sms = 0, perSm = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaDeviceGetAttribute", err);
+    err = DecodeOccupancy(fp8, &perSm);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaOccupancyMaxActiveBlocksPerMultiprocessor", err);
+    if (perSm < 1)
+    {
+        SetError("The decode kernel cannot be resident on this device (compute capability 10.0 required).");
+        return NTCB_ERR_CUDA;
+    }
+    // TMEM holds 512 columns per SM; every CTA takes kTmemColumns for its whole lifetime.
+    const int tmemLimit = 512 / kTmemColumns;
+    if (perSm > tmemLimit)
+        perSm = tmemLimit;
+    *outCtas = sms * perSm;
+    if (device >= 0 && device < 64)
+        cache[device][fp8 ? 1 : 0].store(*outCtas, std::memory_order_relaxed);
+    return NTCB_OK;
+}
+
+} // namespace
+} // namespace ntcb
+
+using namespace ntcb;
+
+extern "C"
+{
+
+const char* ntcb_last_error(void)
+{
+    return g_lastError;
+}
+
+const char* ntcb_status_string(int status)
+{
+    switch (status)
+    {
+    case NTCB_OK: return "Ok";
+    case NTCB_ERR_INVALID_ARGUMENT: return "InvalidArgument";
+    case NTCB_ERR_CUDA: return "CudaError";
+    case NTCB_ERR_FILE_UNRECOGNIZED: return "FileUnrecognized";
+    case NTCB_ERR_FILE_INCOMPATIBLE: return "FileIncompatible";
+    case NTCB_ERR_UNSUPPORTED: return "Unsupported";
+    case NTCB_ERR_OUT_OF_MEMORY: return "OutOfMemory";
+    case NTCB_ERR_DEVICE_TIMEOUT: return "DeviceTimeout";
+    case NTCB_ERR_INVALID_STATE: return "InvalidState";
+    case NTCB_ERR_OUT_OF_RANGE: return "OutOfRange";
+    default: return "Unknown";
+    }
+}
+
+uint64_t ntcb_launch_count(void)
+{
+    return g_launchCount.load(std::memory_order_relaxed);
+}
+
+int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void* staged)
+{
+    if (!blob || !staged)
+    {
+        SetError("ntcb_stage_network: blob and staged must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const bool fp8 = weightMode == NTCB_WEIGHTS_FP8;
+    if (weightMode != NTCB_WEIGHTS_INT8 && weightMode != NTCB_WEIGHTS_FP8)
+    {
+        SetError("ntcb_stage_network: unknown weight mode %d.", weightMode);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const size_t expected = fp8 ? NTCB_FP8_BLOB_BYTES : NTCB_INT8_BLOB_BYTES;
+    if (blobBytes != expected)
+    {
+        SetError("ntcb_stage_network: the %s weight blob must be %zu bytes, got %zu.", fp8 ? "GenericFP8" : "GenericInt8",
+            expected, blobBytes);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+
+    const uint8_t* src = static_cast<const uint8_t*>(blob);
+    uint8_t* dst = static_cast<uint8_t*>(staged);
+    memset(dst, 0, kStagedNetworkBytes);
+
+    // Weight matrices: row-major [out][in] bytes in the file (src/Quantizer.cu:144-146), laid out
+    // one after another (src/WeightLayout.cpp:170-176) -> K-major core matrices, K zero-padded.
+    size_t offset = 0;
+    for (int layer = 0; layer < 4; ++layer)
+    {
+        const int nin = kLayerInputs[layer], nout = kLayerOutputs[layer];
+        uint8_t* w = dst + kWeightOffsets[layer];
+        for (int n = 0; n < nout; ++n)
+            for (int k = 0; k < nin; ++k)
+                w[(k / 16) * (nout * 16) + n * 16 + (k % 16)] = src[offset + size_t(n) * nin + k];
+        (void)kLayerPaddedK;
+        offset += size_t(nin) * nout;
+    }
+
+    float* scale = reinterpret_cast<float*>(dst + kScaleOffset);
+    for (int i = 0; i < 4 * 64; ++i)
+        scale[i] = 1.f;
+    if (!fp8)
+    {
+        // all fp32 scale vectors, then all int32 bias vectors (src/WeightLayout.cpp:228-238)
+        for (int layer = 0; layer < 4; ++layer)
+        {
+            memcpy(scale + layer * 64, src + offset, 4u * kLayerOutputs[layer]);
+            offset += 4u * kLayerOutputs[layer];
+        }
+        for (int layer = 0; layer < 4; ++layer)
+        {
+            memcpy(dst + kBiasOffset + layer * 256, src + offset, 4u * kLayerOutputs[layer]);
+            offset += 4u * kLayerOutputs[layer];
+        }
+    }
+    else
+    {
+        // fp16 biases of layers 0-2, then the fp32 scale and int32 bias of the int8 output layer
+        // (src/WeightLayout.cpp:240-255)
+        for (int layer = 0; layer < 3; ++layer)
+        {
+            memcpy(dst + kBiasOffset + layer * 256, src + offset, 2u * kLayerOutputs[layer]);
+            offset += 2u * kLayerOutputs[layer];
+        }
+        memcpy(scale + 3 * 64, src + offset, 4u * 16);
+        offset += 4u * 16;
+        memcpy(dst + kBiasOffset + 3 * 256, src + offset, 4u * 16);
+        offset += 4u * 16;
+    }
+    if (offset != expected)
+    {
+        SetError("ntcb_stage_network: internal layout mismatch.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    ClearError();
+    return NTCB_OK;
+}
+
+int ntcb_decode(const NtcbDecodeParams* p, void* stream)
+{
+    if (!p || !p->latents || !p->network || !p->out || !p->status)
+    {
+        SetError("ntcb_decode: params, latents, network, out and status must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (p->numMips < 1 || p->numMips > NTCB_MAX_MIPS)
+    {
+        SetError("ntcb_decode: numMips (%d) must be 1..%d.", p->numMips, NTCB_MAX_MIPS);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (p->numFeatures < 4 || p->numFeatures > 16 || (p->numFeatures & 3))
+    {
+        SetError("ntcb_decode: numFeatures (%d) must be 4, 8, 12 or 16.", p->numFeatures);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (p->channels < 2 || p->channels > 16 || (p->channels & 1))
+    {
+        SetError("ntcb_decode: channels (%d) must be even and 2..16.", p->channels);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (p->weightMode != NTCB_WEIGHTS_INT8 && p->weightMode != NTCB_WEIGHTS_FP8)
+    {
+        SetError("ntcb_decode: unknown weight mode %d.", p->weightMode);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (p->outputLayout != NTCB_LAYOUT_PLANAR_PAIRS && p->outputLayout != NTCB_LAYOUT_INTERLEAVED)
+    {
+        SetError("ntcb_decode: unknown output layout %d.", p->outputLayout);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if ((reinterpret_cast<uintptr_t>(p->network) & 15) || (reinterpret_cast<uintptr_t>(p->out) & 3) ||
+        (reinterpret_cast<uintptr_t>(p->latents) & 1))
+    {
+        SetError("ntcb_decode: network must be 16-byte aligned, out 4-byte aligned, latents 2-byte aligned.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+
+    KernelParams k{};
+    k.latents = p->latents;
+    k.network = static_cast<const uint8_t*>(p->network);
+    k.out = static_cast<__half*>(p->out);
+    k.status = p->status;
+    k.numLayers = p->numFeatures / 4;
+    k.channels = p->channels;
+    k.outputLayout = p->outputLayout;
+    long long tiles = 0;
+    int used = 0;
+    for (int i = 0; i < p->numMips; ++i)
+    {
+        const NtcbMipDesc& m = p->mips[i];
+        if (m.width < 1 || m.height < 1 || m.hiWidth < 1 || m.hiHeight < 1 || m.loWidth < 1 || m.loHeight < 1 ||
+            m.rowBegin < 0 || m.rowEnd > m.height || m.rowBegin > m.rowEnd || (m.outOffset & 1) ||
+            m.hiPlane < uint64_t(m.hiWidth) * m.hiHeight || m.loPlane < uint64_t(m.loWidth) * m.loHeight)
+        {
+            SetError("ntcb_decode: mip %d has invalid dimensions, row range or offsets.", i);
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        if (m.rowBegin == m.rowEnd)
+            continue; // nothing of this mip belongs to this launch
+        KernelMip& km = k.mips[used++];
+        km.width = m.width;
+        km.height = m.height;
+        km.rowBegin = m.rowBegin;
+        km.rowEnd = m.rowEnd;
+        km.hiWidth = m.hiWidth;
+        km.hiHeight = m.hiHeight;
+        km.loWidth = m.loWidth;
+        km.loHeight = m.loHeight;
+        km.hiOffset = m.hiOffset;
+        km.loOffset = m.loOffset;
+        km.hiPlane = m.hiPlane;
+        km.loPlane = m.loPlane;
+        km.outOffset = m.outOffset;
+        km.invWidth = 1.0f / float(m.width);
+        km.invHeight = 1.0f / float(m.height);
+        km.positionScale = m.positionScale;
+        km.positionLod = m.positionLod;
+        km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
+        km.firstTile = int(tiles);
+        tiles += (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
+        if (tiles > 0x7FFFFFFF)
+        {
+            SetError("ntcb_decode: too many tiles for one launch.");
+            return NTCB_ERR_OUT_OF_RANGE;
+        }
+    }
+    ClearError();
+    if (used == 0)
+        return NTCB_OK;
+    k.numMips = used;
+    k.totalTiles = int(tiles);
+
+    const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
+    int resident = 0;
+    int rc = ResidentCtas(fp8, &resident);
+    if (rc != NTCB_OK)
+        return rc;
+    const int ctas = k.totalTiles < resident ? k.totalTiles : resident;
+    cudaError_t err = LaunchDecode(k, fp8, ctas, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess)
+        return CudaFailure("DecodeKernel launch", err);
+    CountLaunch();
+    return NTCB_OK;
+}
+
+} // extern "C"
