@@ -116,6 +116,109 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
    Asynchronous; the caller synchronises and may then read `status`.  Allocates nothing. */
 int ntcb_decode(const NtcbDecodeParams* params, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Texture-set level: the same path as the reference's host objects drive it.
+ * ------------------------------------------------------------------------------------------ */
+
+typedef struct NtcbContext NtcbContext;       /* stands in for ntc::IContext  (include/libntc/ntc.h:1123-1276) */
+typedef struct NtcbTextureSet NtcbTextureSet; /* stands in for ntc::ITextureSet (include/libntc/ntc.h:855-945) */
+
+/* ntc::TextureSetDesc + ntc::LatentShape (include/libntc/ntc.h:131-177) and the derived counts. */
+typedef struct NtcbTextureSetDesc
+{
+    int32_t width, height, channels, mips;
+    int32_t gridSizeScale, numFeatures;
+    int32_t numNeuralMips, numLayers;
+    uint64_t totalTexels;
+} NtcbTextureSetDesc;
+
+/* Creation options; the reference's TextureSetFeatures (include/libntc/ntc.h:179-199) sizes staging
+   and training buffers that this decoder does not have. */
+typedef struct NtcbTextureSetFeatures
+{
+    int32_t outputLayout; /* NtcbOutputLayout of the internal decoded-texel buffer (default interleaved) */
+    int32_t reserved;
+} NtcbTextureSetFeatures;
+
+/* ntc::DecompressionStats (include/libntc/ntc.h:810-816); the loss fields need a resident
+   reference image, which a decoder-only texture set never has, so only the timing is kept. */
+typedef struct NtcbDecompressionStats
+{
+    float gpuTimeMilliseconds; /* device time of the decode launch, as the reference times its mip loop */
+} NtcbDecompressionStats;
+
+#define NTCB_ADDRESS_SPACE_HOST 0   /* ntc::AddressSpace::Host */
+#define NTCB_ADDRESS_SPACE_DEVICE 1 /* ntc::AddressSpace::Device */
+#define NTCB_CHANNEL_FORMAT_FLOAT16 3 /* ntc::ChannelFormat::FLOAT16 */
+
+/* ntc::ReadChannelsParameters (include/libntc/ntc.h:689-730), the fields this path uses. */
+typedef struct NtcbReadChannelsParams
+{
+    int32_t mipLevel, firstChannel, numChannels;
+    int32_t addressSpace;  /* NTCB_ADDRESS_SPACE_* */
+    void* pOutData;
+    int32_t width, height; /* must equal the mip's size */
+    int32_t channelFormat; /* NTCB_CHANNEL_FORMAT_FLOAT16 */
+    int32_t reserved;
+    size_t pixelStride, rowPitch; /* bytes */
+} NtcbReadChannelsParams;
+
+/* Host only, no GPU needed.  Parses and validates an NTC container and reports what it holds.
+   Replaces IContext::CreateTextureSetMetadataFromStream + ITextureSetMetadata::GetDesc /
+   GetLatentShape (include/libntc/ntc.h:1161, 546-552; src/Context.cpp:236-283). */
+int ntcb_probe_container(const void* data, size_t size, NtcbTextureSetDesc* outDesc);
+
+/* Creates a decoder context on a CUDA device.  Replaces ntc::CreateContext
+   (include/libntc/ntc.h:1330, src/PublicFunctions.cpp:62-162).  Fails with NTCB_ERR_CUDA when the
+   device is not usable or is not compute capability 10.x. */
+int ntcb_context_create(int cudaDevice, NtcbContext** outContext);
+
+/* Replaces ntc::DestroyContext (include/libntc/ntc.h:1333).  Texture sets must be destroyed first. */
+void ntcb_context_destroy(NtcbContext* context);
+
+/* Loads a compressed texture set from an NTC container in host memory and allocates its device
+   buffers.  Replaces IContext::CreateCompressedTextureSetFromMemory (include/libntc/ntc.h:1171,
+   src/Context.cpp:295-366, src/TextureSet.cpp:154-294).  `features` may be NULL. */
+int ntcb_texture_set_create_from_memory(NtcbContext* context, const void* data, size_t size,
+    const NtcbTextureSetFeatures* features, NtcbTextureSet** outTextureSet);
+
+/* Same from a file.  Replaces IContext::CreateCompressedTextureSetFromFile (include/libntc/ntc.h:1176). */
+int ntcb_texture_set_create_from_file(NtcbContext* context, const char* fileName,
+    const NtcbTextureSetFeatures* features, NtcbTextureSet** outTextureSet);
+
+/* Replaces IContext::DestroyTextureSet (include/libntc/ntc.h:1153). */
+void ntcb_texture_set_destroy(NtcbTextureSet* textureSet);
+
+/* Replaces ITextureSetMetadata::GetDesc / GetLatentShape (include/libntc/ntc.h:546-552). */
+int ntcb_texture_set_get_desc(const NtcbTextureSet* textureSet, NtcbTextureSetDesc* outDesc);
+
+/* Uploads the compressed data (as the reference does on every call for a set loaded from a file,
+   src/TextureSet.cpp:1691-1757) and decodes every mip into the internal texel buffer with ONE
+   kernel launch.  With `stats` the call waits for the GPU and reports the device time; without it
+   the work is only queued.  Replaces ITextureSet::Decompress (include/libntc/ntc.h:933,
+   src/TextureSet.cpp:1664-1897). */
+int ntcb_texture_set_decompress(NtcbTextureSet* textureSet, NtcbDecompressionStats* stats, int useInt8Weights);
+
+/* Same, restricted to rows [rowRanges[2*m], rowRanges[2*m+1]) of each mip m: the unit of
+   tile-row sharding across GPUs.  No counterpart in the reference, which always decodes whole mips
+   on the CUDA path (its graphics path takes a rectangle, include/libntc/ntc.h:1029-1034). */
+int ntcb_texture_set_decompress_rows(NtcbTextureSet* textureSet, const int32_t* rowRanges, NtcbDecompressionStats* stats,
+    int useInt8Weights);
+
+/* Copies decoded channels of one mip to host or device memory, pixel-interleaved with the given
+   strides, and returns when the data is there.  Replaces ITextureSet::ReadChannels
+   (include/libntc/ntc.h:902, src/TextureSet.cpp:915-985) for ChannelFormat::FLOAT16; the other
+   channel formats report NTCB_ERR_UNSUPPORTED. */
+int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadChannelsParams* params);
+
+/* Device address and size in bytes of one decoded mip in the internal layout: the counterpart of
+   TextureSet::GetTextureDataSlice (src/TextureSet.cpp:1958-1983) for callers that consume the
+   texels on the GPU. */
+int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void** outPointer, size_t* outBytes);
+
+/* Waits for everything queued on the texture set's stream. */
+int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet);
+
 /* Number of kernel launches this library has issued from the calling process so far
    (bookkeeping for benchmarks). */
 uint64_t ntcb_launch_count(void);

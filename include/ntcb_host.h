@@ -1,0 +1,75 @@
+// ntcb_host.h - C++ host interface of the B200-native NTC decoder.
+//
+// The classes mirror, for the decompression path only, the reference's public host interface
+// (include/libntc/ntc.h): the same method names, argument meaning and error convention, so code
+// written against ntc::IContext / ntc::ITextureSet ports by changing the namespace.  Every method
+// is a thin layer over the C ABI in ntcb.h (which is what foreign-language bindings use).
+//
+//   ntc::CreateContext / DestroyContext                 -> ntcb::CreateContext / DestroyContext
+//   IContext::CreateCompressedTextureSetFromMemory/File -> same names
+//   IContext::DestroyTextureSet                         -> same name
+//   ITextureSet::GetDesc / GetLatentShape               -> same names
+//   ITextureSet::Decompress(stats, useInt8Weights)      -> same name, same default (FP8 weights)
+//   ITextureSet::ReadChannels(params)                   -> same name (ChannelFormat::FLOAT16)
+//
+// Status values are the NtcbStatus codes of ntcb.h; ntcb::GetLastErrorMessage() returns the
+// thread-local message of the last failing call, like ntc::GetLastErrorMessage().
+#pragma once
+
+#include "ntcb.h"
+
+namespace ntcb
+{
+
+using Status = int; // NtcbStatus
+
+struct TextureSetDesc // ntc::TextureSetDesc, include/libntc/ntc.h:158-177
+{
+    int width = 0, height = 0, channels = 0, mips = 1;
+};
+
+struct LatentShape // ntc::LatentShape, include/libntc/ntc.h:131-156
+{
+    int gridSizeScale = 4, numFeatures = 16;
+};
+
+struct ContextParameters // ntc::ContextParameters, include/libntc/ntc.h:1278-1305 (CUDA part)
+{
+    int cudaDevice = 0;
+};
+
+using TextureSetFeatures = NtcbTextureSetFeatures;
+using DecompressionStats = NtcbDecompressionStats;
+using ReadChannelsParameters = NtcbReadChannelsParams;
+
+class ITextureSet
+{
+public:
+    virtual TextureSetDesc const& GetDesc() const = 0;
+    virtual LatentShape const& GetLatentShape() const = 0;
+    virtual Status Decompress(DecompressionStats* pOutStats, bool useInt8Weights = false) = 0;
+    // rowRanges: [mips][2] = {rowBegin, rowEnd} per mip (tile-row sharding); NULL = whole mips
+    virtual Status DecompressRows(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights = false) = 0;
+    virtual Status ReadChannels(ReadChannelsParameters const& params) = 0;
+    virtual Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) = 0;
+    virtual Status Synchronize() = 0;
+    virtual ~ITextureSet() = default;
+};
+
+class IContext
+{
+public:
+    virtual Status CreateCompressedTextureSetFromMemory(void const* pData, size_t size, TextureSetFeatures const& features,
+        ITextureSet** pOutTextureSet) const = 0;
+    virtual Status CreateCompressedTextureSetFromFile(char const* fileName, TextureSetFeatures const& features,
+        ITextureSet** pOutTextureSet) const = 0;
+    virtual void DestroyTextureSet(ITextureSet* textureSet) const = 0;
+    virtual ~IContext() = default;
+};
+
+Status CreateContext(IContext** pOutContext, ContextParameters const& params);
+void DestroyContext(IContext* context);
+inline const char* GetLastErrorMessage() { return ntcb_last_error(); }
+inline const char* StatusToString(Status status) { return ntcb_status_string(status); }
+
+} // namespace ntcb

@@ -44,6 +44,32 @@ class DecodeParams(ctypes.Structure):
                 ("mips", MipDesc * MAX_MIPS)]
 
 
+class TextureSetDesc(ctypes.Structure):
+    _fields_ = [("width", ctypes.c_int32), ("height", ctypes.c_int32), ("channels", ctypes.c_int32),
+                ("mips", ctypes.c_int32), ("gridSizeScale", ctypes.c_int32), ("numFeatures", ctypes.c_int32),
+                ("numNeuralMips", ctypes.c_int32), ("numLayers", ctypes.c_int32), ("totalTexels", ctypes.c_uint64)]
+
+
+class TextureSetFeatures(ctypes.Structure):
+    _fields_ = [("outputLayout", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class DecompressionStats(ctypes.Structure):
+    _fields_ = [("gpuTimeMilliseconds", ctypes.c_float)]
+
+
+class ReadChannelsParams(ctypes.Structure):
+    _fields_ = [("mipLevel", ctypes.c_int32), ("firstChannel", ctypes.c_int32), ("numChannels", ctypes.c_int32),
+                ("addressSpace", ctypes.c_int32), ("pOutData", ctypes.c_void_p),
+                ("width", ctypes.c_int32), ("height", ctypes.c_int32),
+                ("channelFormat", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("pixelStride", ctypes.c_size_t), ("rowPitch", ctypes.c_size_t)]
+
+
+ADDRESS_SPACE_HOST, ADDRESS_SPACE_DEVICE = 0, 1
+CHANNEL_FORMAT_FLOAT16 = 3
+
+
 class NtcbError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__("%s (%d): %s" % (lib().ntcb_status_string(code).decode(), code, message))
@@ -66,6 +92,25 @@ def lib():
         handle.ntcb_launch_count.restype = ctypes.c_uint64
         handle.ntcb_stage_network.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
+        handle.ntcb_probe_container.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetDesc)]
+        handle.ntcb_context_create.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]
+        handle.ntcb_context_destroy.argtypes = [ctypes.c_void_p]
+        handle.ntcb_context_destroy.restype = None
+        handle.ntcb_texture_set_create_from_memory.argtypes = [
+            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetFeatures),
+            ctypes.POINTER(ctypes.c_void_p)]
+        handle.ntcb_texture_set_create_from_file.argtypes = [
+            ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(TextureSetFeatures), ctypes.POINTER(ctypes.c_void_p)]
+        handle.ntcb_texture_set_destroy.argtypes = [ctypes.c_void_p]
+        handle.ntcb_texture_set_destroy.restype = None
+        handle.ntcb_texture_set_get_desc.argtypes = [ctypes.c_void_p, ctypes.POINTER(TextureSetDesc)]
+        handle.ntcb_texture_set_decompress.argtypes = [ctypes.c_void_p, ctypes.POINTER(DecompressionStats), ctypes.c_int]
+        handle.ntcb_texture_set_decompress_rows.argtypes = [
+            ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(DecompressionStats), ctypes.c_int]
+        handle.ntcb_texture_set_read_channels.argtypes = [ctypes.c_void_p, ctypes.POINTER(ReadChannelsParams)]
+        handle.ntcb_texture_set_device_mip.argtypes = [
+            ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t)]
+        handle.ntcb_texture_set_synchronize.argtypes = [ctypes.c_void_p]
         _lib = handle
     return _lib
 
@@ -81,6 +126,14 @@ def stage_network(blob: bytes, weight_mode: int) -> np.ndarray:
     source = np.frombuffer(blob, dtype=np.uint8)
     check(lib().ntcb_stage_network(source.ctypes.data, len(blob), weight_mode, staged.ctypes.data))
     return staged
+
+
+def probe_container(container: bytes) -> TextureSetDesc:
+    """Host-only validation of an NTC container; raises NtcbError with the loader's message."""
+    desc = TextureSetDesc()
+    buffer = np.frombuffer(container, dtype=np.uint8)
+    check(lib().ntcb_probe_container(buffer.ctypes.data, len(container), ctypes.byref(desc)))
+    return desc
 
 
 def out_elements(geo: Geometry) -> int:
@@ -184,3 +237,78 @@ class ResidentTextureSet:
             return view
         h, pairs, w, _ = view.shape
         return view.transpose(0, 2, 1, 3).reshape(h, w, pairs * 2)
+
+
+class Context:
+    """ntcb_context_*: a decoder context on one CUDA device (the counterpart of ntc::IContext)."""
+
+    def __init__(self, device: int = 0):
+        self.handle = ctypes.c_void_p()
+        check(lib().ntcb_context_create(device, ctypes.byref(self.handle)))
+        self.device = device
+
+    def create_texture_set(self, container: bytes, layout: int = LAYOUT_INTERLEAVED) -> "TextureSet":
+        return TextureSet(self, container, layout)
+
+    def close(self) -> None:
+        if self.handle:
+            lib().ntcb_context_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+
+
+class TextureSet:
+    """ntcb_texture_set_*: a compressed texture set loaded from an NTC container (the counterpart
+    of ntc::ITextureSet for decompression)."""
+
+    def __init__(self, context: Context, container: bytes, layout: int = LAYOUT_INTERLEAVED):
+        self.context = context
+        self.handle = ctypes.c_void_p()
+        features = TextureSetFeatures(layout, 0)
+        buffer = np.frombuffer(container, dtype=np.uint8)
+        check(lib().ntcb_texture_set_create_from_memory(context.handle, buffer.ctypes.data, len(container),
+                                                        ctypes.byref(features), ctypes.byref(self.handle)))
+        self.desc = TextureSetDesc()
+        check(lib().ntcb_texture_set_get_desc(self.handle, ctypes.byref(self.desc)))
+
+    def mip_size(self, mip: int) -> Tuple[int, int]:
+        return max(1, self.desc.width >> mip), max(1, self.desc.height >> mip)
+
+    def decompress(self, use_int8: bool, with_stats: bool = False, row_ranges=None) -> Optional[float]:
+        stats = DecompressionStats()
+        stats_ref = ctypes.byref(stats) if with_stats else None
+        if row_ranges is None:
+            check(lib().ntcb_texture_set_decompress(self.handle, stats_ref, 1 if use_int8 else 0))
+        else:
+            flat = (ctypes.c_int32 * (2 * self.desc.mips))(*[v for pair in row_ranges for v in pair])
+            check(lib().ntcb_texture_set_decompress_rows(self.handle, flat, stats_ref, 1 if use_int8 else 0))
+        return float(stats.gpuTimeMilliseconds) if with_stats else None
+
+    def read_channels_into(self, mip: int, address: int, to_device: bool = False, first_channel: int = 0,
+                           num_channels: Optional[int] = None, pixel_stride: Optional[int] = None,
+                           row_pitch: Optional[int] = None) -> None:
+        w, h = self.mip_size(mip)
+        n = self.desc.channels - first_channel if num_channels is None else num_channels
+        params = ReadChannelsParams()
+        params.mipLevel, params.firstChannel, params.numChannels = mip, first_channel, n
+        params.addressSpace = ADDRESS_SPACE_DEVICE if to_device else ADDRESS_SPACE_HOST
+        params.pOutData = address
+        params.width, params.height = w, h
+        params.channelFormat = CHANNEL_FORMAT_FLOAT16
+        params.pixelStride = 2 * n if pixel_stride is None else pixel_stride
+        params.rowPitch = params.pixelStride * w if row_pitch is None else row_pitch
+        check(lib().ntcb_texture_set_read_channels(self.handle, ctypes.byref(params)))
+
+    def read_mip(self, mip: int, first_channel: int = 0, num_channels: Optional[int] = None) -> np.ndarray:
+        w, h = self.mip_size(mip)
+        n = self.desc.channels - first_channel if num_channels is None else num_channels
+        out = np.empty((h, w, n), dtype=np.float16)
+        self.read_channels_into(mip, out.ctypes.data, False, first_channel, n)
+        return out
+
+    def synchronize(self) -> None:
+        check(lib().ntcb_texture_set_synchronize(self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            lib().ntcb_texture_set_destroy(self.handle)
+            self.handle = ctypes.c_void_p()

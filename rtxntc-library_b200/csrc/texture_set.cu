@@ -1,0 +1,827 @@
+// Host objects of the decoder: a context bound to one CUDA device and texture sets that own the
+// device buffers of one compressed set (packed latents, the two staged networks, the decoded
+// texels).  They implement the C++ interface of include/ntcb_host.h and the texture-set level of
+// the C ABI in include/ntcb.h, following the reference's host driver for this path
+// (src/PublicFunctions.cpp:62-162, src/Context.cpp:295-366, src/TextureSet.cpp:81-152, 154-294,
+// 915-985, 1664-1897).
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "container.h"
+#include "decode_kernel.h"
+#include "error.h"
+#include "ntcb.h"
+#include "ntcb_host.h"
+
+namespace ntcb
+{
+namespace
+{
+
+// Sets and restores the calling thread's current device around an API call, like the reference's
+// CudaDeviceGuard (src/CudaDeviceGuard.cpp:21-61).
+class DeviceGuard
+{
+public:
+    explicit DeviceGuard(int device)
+    {
+        m_ok = cudaGetDevice(&m_previous) == cudaSuccess;
+        if (m_ok && m_previous != device)
+        {
+            cudaError_t err = cudaSetDevice(device);
+            if (err != cudaSuccess)
+            {
+                CudaFailure("cudaSetDevice", err);
+                m_ok = false;
+            }
+            else
+                m_switched = true;
+        }
+        else if (!m_ok)
+            SetError("Call to cudaGetDevice failed.");
+    }
+    ~DeviceGuard()
+    {
+        if (m_switched)
+            cudaSetDevice(m_previous);
+    }
+    bool Success() const { return m_ok; }
+
+private:
+    int m_previous = 0;
+    bool m_ok = false, m_switched = false;
+};
+
+// Gathers `numChannels` channels of one decoded mip into a pixel-interleaved destination with
+// arbitrary strides (the FLOAT16 -> FLOAT16 case of the reference's CopyImageKernel,
+// src/ImageProcessing.cu:220-277).  One thread per texel.
+__global__ void ReadChannelsKernel(const __half* __restrict__ src, int layout, int width, int height, int channels,
+    int firstChannel, int numChannels, uint8_t* __restrict__ dst, size_t pixelStride, size_t rowPitch)
+{
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    const int y = blockIdx.y * blockDim.y + threadIdx.y;
+    if (x >= width || y >= height)
+        return;
+    __half* out = reinterpret_cast<__half*>(dst + size_t(y) * rowPitch + size_t(x) * pixelStride);
+    for (int c = 0; c < numChannels; ++c)
+    {
+        const int channel = firstChannel + c;
+        size_t index;
+        if (layout == kLayoutPlanarPairs)
+            index = size_t(y) * width * channels + size_t(channel & ~1) * width + size_t(x) * 2 + (channel & 1);
+        else
+            index = (size_t(y) * width + x) * channels + channel;
+        out[c] = src[index];
+    }
+}
+
+class Context;
+
+class TextureSet final : public ITextureSet
+{
+public:
+    TextureSet(const Context* context, int device, cudaStream_t stream) : m_context(context), m_device(device), m_stream(stream) {}
+    ~TextureSet() override { Release(); }
+
+    Status Initialize(LoadedSet&& loaded, const TextureSetFeatures& features);
+    void Release();
+
+    TextureSetDesc const& GetDesc() const override { return m_desc; }
+    LatentShape const& GetLatentShape() const override { return m_latentShape; }
+    Status Decompress(DecompressionStats* pOutStats, bool useInt8Weights) override
+    {
+        return DecompressRows(nullptr, pOutStats, useInt8Weights);
+    }
+    Status DecompressRows(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights) override;
+    Status ReadChannels(ReadChannelsParameters const& params) override;
+    Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) override;
+    Status Synchronize() override;
+
+    const SetGeometry& Geometry() const { return m_geometry; }
+
+private:
+    Status CheckKernelStatus();
+
+    const Context* m_context;
+    int m_device;
+    cudaStream_t m_stream;
+    SetGeometry m_geometry;
+    TextureSetDesc m_desc;
+    LatentShape m_latentShape;
+    int m_layout = NTCB_LAYOUT_INTERLEAVED;
+    bool m_hasInt8 = false, m_hasFp8 = false;
+
+    // pinned host image of everything Decompress uploads: latents, then the two staged networks
+    uint8_t* m_hostUpload = nullptr;
+    uint8_t* m_deviceUpload = nullptr;
+    size_t m_uploadBytes = 0, m_latentBytes = 0;
+    __half* m_texels = nullptr;
+    size_t m_texelBytes = 0;
+    uint32_t* m_status = nullptr;
+    uint32_t* m_hostStatus = nullptr; // pinned
+    uint8_t* m_staging = nullptr;     // grown on demand by ReadChannels to host with padded strides
+    size_t m_stagingBytes = 0;
+    cudaEvent_t m_eventStart = nullptr, m_eventStop = nullptr;
+    bool m_decoded = false;
+};
+
+class Context final : public IContext
+{
+public:
+    explicit Context(int device) : m_device(device) {}
+    ~Context() override
+    {
+        if (m_stream)
+        {
+            DeviceGuard guard(m_device);
+            cudaStreamDestroy(m_stream);
+        }
+    }
+
+    Status Initialize()
+    {
+        int count = 0;
+        cudaError_t err = cudaGetDeviceCount(&count);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaGetDeviceCount", err);
+        if (m_device < 0 || m_device >= count)
+        {
+            SetError("CUDA device %d does not exist (%d devices are visible).", m_device, count);
+            return NTCB_ERR_CUDA;
+        }
+        int major = 0;
+        err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, m_device);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaDeviceGetAttribute", err);
+        if (major != 10)
+        {
+            SetError("CUDA device %d has compute capability %d.x; the decoder needs 10.x (tcgen05, tensor memory).", m_device,
+                major);
+            return NTCB_ERR_CUDA;
+        }
+        DeviceGuard guard(m_device);
+        if (!guard.Success())
+            return NTCB_ERR_CUDA;
+        err = cudaStreamCreateWithFlags(&m_stream, cudaStreamNonBlocking);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaStreamCreateWithFlags", err);
+        ClearError();
+        return NTCB_OK;
+    }
+
+    Status CreateCompressedTextureSetFromMemory(void const* pData, size_t size, TextureSetFeatures const& features,
+        ITextureSet** pOutTextureSet) const override
+    {
+        if (!pOutTextureSet)
+        {
+            SetError("pOutTextureSet is NULL.");
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        *pOutTextureSet = nullptr;
+        LoadedSet loaded;
+        Status status = LoadContainer(pData, size, loaded);
+        if (status != NTCB_OK)
+            return status;
+        DeviceGuard guard(m_device);
+        if (!guard.Success())
+            return NTCB_ERR_CUDA;
+        TextureSet* set = new (std::nothrow) TextureSet(this, m_device, m_stream);
+        if (!set)
+        {
+            SetError("Out of host memory.");
+            return NTCB_ERR_OUT_OF_MEMORY;
+        }
+        status = set->Initialize(std::move(loaded), features);
+        if (status != NTCB_OK)
+        {
+            delete set;
+            return status;
+        }
+        *pOutTextureSet = set;
+        ClearError();
+        return NTCB_OK;
+    }
+
+    Status CreateCompressedTextureSetFromFile(char const* fileName, TextureSetFeatures const& features,
+        ITextureSet** pOutTextureSet) const override
+    {
+        if (!fileName)
+        {
+            SetError("fileName is NULL.");
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        FILE* file = fopen(fileName, "rb");
+        if (!file)
+        {
+            SetError("Cannot open file '%s'.", fileName);
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        }
+        std::vector<uint8_t> data;
+        bool ok = fseek(file, 0, SEEK_END) == 0;
+        long length = ok ? ftell(file) : -1;
+        ok = ok && length >= 0 && fseek(file, 0, SEEK_SET) == 0;
+        if (ok)
+        {
+            data.resize(size_t(length));
+            ok = fread(data.data(), 1, data.size(), file) == data.size();
+        }
+        fclose(file);
+        if (!ok)
+        {
+            SetError("Cannot read file '%s'.", fileName);
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        }
+        return CreateCompressedTextureSetFromMemory(data.data(), data.size(), features, pOutTextureSet);
+    }
+
+    void DestroyTextureSet(ITextureSet* textureSet) const override
+    {
+        if (!textureSet)
+            return;
+        DeviceGuard guard(m_device);
+        delete textureSet;
+    }
+
+private:
+    int m_device;
+    cudaStream_t m_stream = nullptr;
+};
+
+Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& features)
+{
+    m_geometry = loaded.geometry;
+    m_desc.width = m_geometry.width;
+    m_desc.height = m_geometry.height;
+    m_desc.channels = m_geometry.channels;
+    m_desc.mips = m_geometry.mips;
+    m_latentShape.gridSizeScale = m_geometry.gridSizeScale;
+    m_latentShape.numFeatures = m_geometry.numFeatures;
+    if (features.outputLayout != NTCB_LAYOUT_PLANAR_PAIRS && features.outputLayout != NTCB_LAYOUT_INTERLEAVED)
+    {
+        SetError("Unknown output layout %d.", features.outputLayout);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    m_layout = features.outputLayout;
+    m_hasInt8 = !loaded.int8Blob.empty();
+    m_hasFp8 = !loaded.fp8Blob.empty();
+
+    // upload image: latents (padded to 16 bytes), then the Int8 and the FP8 network images
+    m_latentBytes = (loaded.latents.size() * 2 + 15) & ~size_t(15);
+    m_uploadBytes = m_latentBytes + 2 * size_t(kStagedNetworkBytes);
+    cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&m_hostUpload), m_uploadBytes, cudaHostAllocDefault);
+    if (err != cudaSuccess)
+    {
+        SetError("Failed to allocate %zu bytes of pinned host memory for the compressed data.", m_uploadBytes);
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
+    memset(m_hostUpload, 0, m_uploadBytes);
+    memcpy(m_hostUpload, loaded.latents.data(), loaded.latents.size() * 2);
+    if (m_hasInt8)
+    {
+        Status status = ntcb_stage_network(loaded.int8Blob.data(), loaded.int8Blob.size(), NTCB_WEIGHTS_INT8,
+            m_hostUpload + m_latentBytes);
+        if (status != NTCB_OK)
+            return status;
+    }
+    if (m_hasFp8)
+    {
+        Status status = ntcb_stage_network(loaded.fp8Blob.data(), loaded.fp8Blob.size(), NTCB_WEIGHTS_FP8,
+            m_hostUpload + m_latentBytes + kStagedNetworkBytes);
+        if (status != NTCB_OK)
+            return status;
+    }
+
+    err = cudaMalloc(reinterpret_cast<void**>(&m_deviceUpload), m_uploadBytes);
+    if (err != cudaSuccess)
+    {
+        SetError("Failed to allocate %zu bytes of device memory for the compressed data.", m_uploadBytes);
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
+    m_texelBytes = size_t(m_geometry.TotalTexels()) * m_geometry.channels * sizeof(__half);
+    err = cudaMalloc(reinterpret_cast<void**>(&m_texels), m_texelBytes);
+    if (err != cudaSuccess)
+    {
+        SetError("Failed to allocate %zu bytes of device memory for the decoded texture data.", m_texelBytes);
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
+    err = cudaMalloc(reinterpret_cast<void**>(&m_status), NTCB_STATUS_WORDS * sizeof(uint32_t));
+    if (err == cudaSuccess)
+        err = cudaHostAlloc(reinterpret_cast<void**>(&m_hostStatus), NTCB_STATUS_WORDS * sizeof(uint32_t), cudaHostAllocDefault);
+    if (err != cudaSuccess)
+    {
+        SetError("Failed to allocate the status words.");
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
+    err = cudaEventCreate(&m_eventStart);
+    if (err == cudaSuccess)
+        err = cudaEventCreate(&m_eventStop);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaEventCreate", err);
+    return NTCB_OK;
+}
+
+void TextureSet::Release()
+{
+    if (m_stream)
+        cudaStreamSynchronize(m_stream);
+    if (m_eventStart) cudaEventDestroy(m_eventStart);
+    if (m_eventStop) cudaEventDestroy(m_eventStop);
+    if (m_staging) cudaFree(m_staging);
+    if (m_status) cudaFree(m_status);
+    if (m_hostStatus) cudaFreeHost(m_hostStatus);
+    if (m_texels) cudaFree(m_texels);
+    if (m_deviceUpload) cudaFree(m_deviceUpload);
+    if (m_hostUpload) cudaFreeHost(m_hostUpload);
+    m_eventStart = m_eventStop = nullptr;
+    m_staging = nullptr;
+    m_status = nullptr;
+    m_hostStatus = nullptr;
+    m_texels = nullptr;
+    m_deviceUpload = nullptr;
+    m_hostUpload = nullptr;
+}
+
+Status TextureSet::CheckKernelStatus()
+{
+    if (m_hostStatus[0] != 0)
+    {
+        SetError("A bounded wait inside the decode kernel expired (code %u, tile %u, layer %u).", m_hostStatus[0],
+            m_hostStatus[1], m_hostStatus[2]);
+        return NTCB_ERR_DEVICE_TIMEOUT;
+    }
+    return NTCB_OK;
+}
+
+Status TextureSet::DecompressRows(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights)
+{
+    if (useInt8Weights ? !m_hasInt8 : !m_hasFp8)
+    {
+        SetError("The texture set has no %s network; it cannot be decompressed with these weights.",
+            useInt8Weights ? "Int8" : "FP8");
+        return NTCB_ERR_INVALID_STATE;
+    }
+    if (pOutStats)
+        memset(pOutStats, 0, sizeof *pOutStats);
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+
+    // upload the encoded latents and the network weights, as the reference does on every
+    // Decompress of a loaded set (src/TextureSet.cpp:1691-1757)
+    cudaError_t err = cudaMemcpyAsync(m_deviceUpload, m_hostUpload, m_uploadBytes, cudaMemcpyHostToDevice, m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaMemcpyAsync (compressed data)", err);
+    err = cudaMemsetAsync(m_status, 0, NTCB_STATUS_WORDS * sizeof(uint32_t), m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaMemsetAsync (status)", err);
+
+    NtcbDecodeParams params{};
+    params.latents = reinterpret_cast<const uint16_t*>(m_deviceUpload);
+    params.network = m_deviceUpload + m_latentBytes + (useInt8Weights ? 0 : kStagedNetworkBytes);
+    params.out = m_texels;
+    params.status = m_status;
+    params.numMips = m_geometry.mips;
+    params.numFeatures = m_geometry.numFeatures;
+    params.channels = m_geometry.channels;
+    params.weightMode = useInt8Weights ? NTCB_WEIGHTS_INT8 : NTCB_WEIGHTS_FP8;
+    params.outputLayout = m_layout;
+    for (int mip = 0; mip < m_geometry.mips; ++mip)
+    {
+        // the per-mip parameters TextureSet::Decompress fills (src/TextureSet.cpp:1806-1829)
+        const int lod = m_geometry.neuralLod[mip];
+        NtcbMipDesc& d = params.mips[mip];
+        d.width = m_geometry.mipWidth[mip];
+        d.height = m_geometry.mipHeight[mip];
+        d.hiWidth = m_geometry.latentWidth[lod];
+        d.hiHeight = m_geometry.latentHeight[lod];
+        d.loWidth = m_geometry.latentWidth[lod + 1];
+        d.loHeight = m_geometry.latentHeight[lod + 1];
+        d.hiOffset = m_geometry.latentPixelOffset[lod] * m_geometry.numLayers;
+        d.loOffset = m_geometry.latentPixelOffset[lod + 1] * m_geometry.numLayers;
+        d.hiPlane = uint64_t(d.hiWidth) * d.hiHeight;
+        d.loPlane = uint64_t(d.loWidth) * d.loHeight;
+        d.positionScale = m_geometry.positionScale[mip];
+        d.positionLod = m_geometry.positionLod[mip];
+        d.outOffset = m_geometry.mipTexelOffset[mip] * m_geometry.channels;
+        d.rowBegin = rowRanges ? rowRanges[2 * mip] : 0;
+        d.rowEnd = rowRanges ? rowRanges[2 * mip + 1] : d.height;
+        if (d.rowBegin < 0 || d.rowEnd > d.height || d.rowBegin > d.rowEnd)
+        {
+            SetError("Row range [%d, %d) of mip %d is outside the mip (height %d).", d.rowBegin, d.rowEnd, mip, d.height);
+            return NTCB_ERR_OUT_OF_RANGE;
+        }
+    }
+
+    if (pOutStats)
+    {
+        err = cudaEventRecord(m_eventStart, m_stream);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaEventRecord (1)", err);
+    }
+    Status status = ntcb_decode(&params, m_stream);
+    if (status != NTCB_OK)
+        return status;
+    m_decoded = true;
+    if (pOutStats)
+    {
+        err = cudaEventRecord(m_eventStop, m_stream);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaEventRecord (2)", err);
+    }
+    err = cudaMemcpyAsync(m_hostStatus, m_status, NTCB_STATUS_WORDS * sizeof(uint32_t), cudaMemcpyDeviceToHost, m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaMemcpyAsync (status)", err);
+    if (pOutStats)
+    {
+        err = cudaStreamSynchronize(m_stream);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaStreamSynchronize", err);
+        cudaEventElapsedTime(&pOutStats->gpuTimeMilliseconds, m_eventStart, m_eventStop);
+        status = CheckKernelStatus();
+        if (status != NTCB_OK)
+            return status;
+    }
+    ClearError();
+    return NTCB_OK;
+}
+
+Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
+{
+    if (!params.pOutData)
+    {
+        SetError("pOutData is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    // argument checks of ValidateReadWriteChannelsArgs (src/TextureSet.cpp:1899-1956)
+    if (params.mipLevel < 0 || params.mipLevel >= m_geometry.mips)
+    {
+        SetError("mipLevel (%d) must be between 0 and %d.", params.mipLevel, m_geometry.mips - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (params.firstChannel < 0 || params.firstChannel >= m_geometry.channels)
+    {
+        SetError("firstChannel (%d) must be between 0 and %d.", params.firstChannel, m_geometry.channels - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (params.numChannels < 1 || params.numChannels > m_geometry.channels - params.firstChannel)
+    {
+        SetError("For the provided firstChannel (%d), numChannels (%d) must be between 1 and %d.", params.firstChannel,
+            params.numChannels, m_geometry.channels - params.firstChannel);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    const int width = m_geometry.mipWidth[params.mipLevel], height = m_geometry.mipHeight[params.mipLevel];
+    if (params.width != width || params.height != height)
+    {
+        SetError("width (%d) and height (%d) must match the mip's dimensions (%dx%d).", params.width, params.height, width,
+            height);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (params.channelFormat != NTCB_CHANNEL_FORMAT_FLOAT16)
+    {
+        SetError("Only ChannelFormat::FLOAT16 is implemented by ReadChannels.");
+        return NTCB_ERR_UNSUPPORTED;
+    }
+    if (params.pixelStride < size_t(params.numChannels) * 2 || params.rowPitch < params.pixelStride * size_t(width) ||
+        (params.pixelStride & 1) || (params.rowPitch & 1))
+    {
+        SetError("pixelStride (%zu) must hold numChannels fp16 values and rowPitch (%zu) a row of pixels; both must be even.",
+            params.pixelStride, params.rowPitch);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (params.addressSpace != NTCB_ADDRESS_SPACE_HOST && params.addressSpace != NTCB_ADDRESS_SPACE_DEVICE)
+    {
+        SetError("Unknown address space %d.", params.addressSpace);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (!m_decoded)
+    {
+        SetError("The texture set has not been decompressed yet.");
+        return NTCB_ERR_INVALID_STATE;
+    }
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+
+    const __half* mipData = m_texels + m_geometry.mipTexelOffset[params.mipLevel] * m_geometry.channels;
+    const size_t bytes = size_t(height) * params.rowPitch;
+    const bool toHost = params.addressSpace == NTCB_ADDRESS_SPACE_HOST;
+    const bool direct = m_layout == NTCB_LAYOUT_INTERLEAVED && params.firstChannel == 0 &&
+                        params.numChannels == m_geometry.channels && params.pixelStride == size_t(m_geometry.channels) * 2 &&
+                        params.rowPitch == params.pixelStride * size_t(width);
+    cudaError_t err;
+    if (direct)
+    {
+        // the request is the internal layout: one copy, no conversion pass
+        err = cudaMemcpyAsync(params.pOutData, mipData, bytes, toHost ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice,
+            m_stream);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaMemcpyAsync (texels)", err);
+    }
+    else
+    {
+        uint8_t* target = static_cast<uint8_t*>(params.pOutData);
+        if (toHost)
+        {
+            if (m_stagingBytes < bytes)
+            {
+                cudaStreamSynchronize(m_stream);
+                if (m_staging)
+                    cudaFree(m_staging);
+                m_staging = nullptr;
+                m_stagingBytes = 0;
+                err = cudaMalloc(reinterpret_cast<void**>(&m_staging), bytes);
+                if (err != cudaSuccess)
+                {
+                    SetError("Failed to allocate %zu bytes of device memory for the staging buffer.", bytes);
+                    return NTCB_ERR_OUT_OF_MEMORY;
+                }
+                m_stagingBytes = bytes;
+            }
+            target = m_staging;
+            if (params.rowPitch > params.pixelStride * size_t(width) || params.pixelStride > size_t(params.numChannels) * 2)
+            {
+                // gaps are not written by the kernel: hand back zeros there, as the reference does
+                err = cudaMemsetAsync(m_staging, 0, bytes, m_stream);
+                if (err != cudaSuccess)
+                    return CudaFailure("cudaMemsetAsync (staging)", err);
+            }
+        }
+        dim3 block(32, 8);
+        dim3 grid((width + block.x - 1) / block.x, (height + block.y - 1) / block.y);
+        ReadChannelsKernel<<<grid, block, 0, m_stream>>>(mipData, m_layout, width, height, m_geometry.channels,
+            params.firstChannel, params.numChannels, target, params.pixelStride, params.rowPitch);
+        err = cudaGetLastError();
+        if (err != cudaSuccess)
+            return CudaFailure("ReadChannelsKernel launch", err);
+        CountLaunch();
+        if (toHost)
+        {
+            err = cudaMemcpyAsync(params.pOutData, m_staging, bytes, cudaMemcpyDeviceToHost, m_stream);
+            if (err != cudaSuccess)
+                return CudaFailure("cudaMemcpyAsync (staging)", err);
+        }
+    }
+    err = cudaStreamSynchronize(m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamSynchronize", err);
+    Status status = CheckKernelStatus();
+    if (status != NTCB_OK)
+        return status;
+    ClearError();
+    return NTCB_OK;
+}
+
+Status TextureSet::GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes)
+{
+    if (mipLevel < 0 || mipLevel >= m_geometry.mips || !outPointer || !outBytes)
+    {
+        SetError("mipLevel (%d) must be between 0 and %d and the output pointers must not be NULL.", mipLevel,
+            m_geometry.mips - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    *outPointer = m_texels + m_geometry.mipTexelOffset[mipLevel] * m_geometry.channels;
+    *outBytes = size_t(m_geometry.mipWidth[mipLevel]) * m_geometry.mipHeight[mipLevel] * m_geometry.channels * sizeof(__half);
+    ClearError();
+    return NTCB_OK;
+}
+
+Status TextureSet::Synchronize()
+{
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+    cudaError_t err = cudaStreamSynchronize(m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamSynchronize", err);
+    if (m_decoded)
+    {
+        Status status = CheckKernelStatus();
+        if (status != NTCB_OK)
+            return status;
+    }
+    ClearError();
+    return NTCB_OK;
+}
+
+} // namespace
+
+Status CreateContext(IContext** pOutContext, ContextParameters const& params)
+{
+    if (!pOutContext)
+    {
+        SetError("pOutContext is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    *pOutContext = nullptr;
+    Context* context = new (std::nothrow) Context(params.cudaDevice);
+    if (!context)
+    {
+        SetError("Out of host memory.");
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
+    Status status = context->Initialize();
+    if (status != NTCB_OK)
+    {
+        delete context;
+        return status;
+    }
+    *pOutContext = context;
+    return NTCB_OK;
+}
+
+void DestroyContext(IContext* context)
+{
+    delete context;
+}
+
+} // namespace ntcb
+
+// ---------------------------------------------------------------------------------------------
+// C ABI wrappers
+// ---------------------------------------------------------------------------------------------
+
+struct NtcbContext
+{
+    ntcb::IContext* impl;
+};
+
+struct NtcbTextureSet
+{
+    ntcb::ITextureSet* impl;
+    const ntcb::IContext* owner;
+};
+
+extern "C"
+{
+
+static void FillDesc(const ntcb::SetGeometry& geo, NtcbTextureSetDesc* outDesc)
+{
+    outDesc->width = geo.width;
+    outDesc->height = geo.height;
+    outDesc->channels = geo.channels;
+    outDesc->mips = geo.mips;
+    outDesc->gridSizeScale = geo.gridSizeScale;
+    outDesc->numFeatures = geo.numFeatures;
+    outDesc->numNeuralMips = geo.numNeuralMips;
+    outDesc->numLayers = geo.numLayers;
+    outDesc->totalTexels = geo.TotalTexels();
+}
+
+int ntcb_probe_container(const void* data, size_t size, NtcbTextureSetDesc* outDesc)
+{
+    if (!outDesc)
+    {
+        ntcb::SetError("outDesc is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    ntcb::LoadedSet loaded;
+    int status = ntcb::LoadContainer(data, size, loaded);
+    if (status != NTCB_OK)
+        return status;
+    FillDesc(loaded.geometry, outDesc);
+    return NTCB_OK;
+}
+
+int ntcb_context_create(int cudaDevice, NtcbContext** outContext)
+{
+    if (!outContext)
+    {
+        ntcb::SetError("outContext is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    *outContext = nullptr;
+    ntcb::ContextParameters params;
+    params.cudaDevice = cudaDevice;
+    ntcb::IContext* impl = nullptr;
+    int status = ntcb::CreateContext(&impl, params);
+    if (status != NTCB_OK)
+        return status;
+    *outContext = new NtcbContext{impl};
+    return NTCB_OK;
+}
+
+void ntcb_context_destroy(NtcbContext* context)
+{
+    if (!context)
+        return;
+    ntcb::DestroyContext(context->impl);
+    delete context;
+}
+
+static int WrapTextureSet(NtcbContext* context, ntcb::ITextureSet* impl, NtcbTextureSet** outTextureSet)
+{
+    *outTextureSet = new NtcbTextureSet{impl, context->impl};
+    return NTCB_OK;
+}
+
+int ntcb_texture_set_create_from_memory(NtcbContext* context, const void* data, size_t size,
+    const NtcbTextureSetFeatures* features, NtcbTextureSet** outTextureSet)
+{
+    if (!context || !outTextureSet)
+    {
+        ntcb::SetError("context and outTextureSet must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    *outTextureSet = nullptr;
+    NtcbTextureSetFeatures defaults{NTCB_LAYOUT_INTERLEAVED, 0};
+    ntcb::ITextureSet* impl = nullptr;
+    int status = context->impl->CreateCompressedTextureSetFromMemory(data, size, features ? *features : defaults, &impl);
+    if (status != NTCB_OK)
+        return status;
+    return WrapTextureSet(context, impl, outTextureSet);
+}
+
+int ntcb_texture_set_create_from_file(NtcbContext* context, const char* fileName, const NtcbTextureSetFeatures* features,
+    NtcbTextureSet** outTextureSet)
+{
+    if (!context || !outTextureSet)
+    {
+        ntcb::SetError("context and outTextureSet must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    *outTextureSet = nullptr;
+    NtcbTextureSetFeatures defaults{NTCB_LAYOUT_INTERLEAVED, 0};
+    ntcb::ITextureSet* impl = nullptr;
+    int status = context->impl->CreateCompressedTextureSetFromFile(fileName, features ? *features : defaults, &impl);
+    if (status != NTCB_OK)
+        return status;
+    return WrapTextureSet(context, impl, outTextureSet);
+}
+
+void ntcb_texture_set_destroy(NtcbTextureSet* textureSet)
+{
+    if (!textureSet)
+        return;
+    textureSet->owner->DestroyTextureSet(textureSet->impl);
+    delete textureSet;
+}
+
+int ntcb_texture_set_get_desc(const NtcbTextureSet* textureSet, NtcbTextureSetDesc* outDesc)
+{
+    if (!textureSet || !outDesc)
+    {
+        ntcb::SetError("textureSet and outDesc must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    FillDesc(static_cast<const ntcb::TextureSet*>(textureSet->impl)->Geometry(), outDesc);
+    return NTCB_OK;
+}
+
+int ntcb_texture_set_decompress(NtcbTextureSet* textureSet, NtcbDecompressionStats* stats, int useInt8Weights)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->Decompress(stats, useInt8Weights != 0);
+}
+
+int ntcb_texture_set_decompress_rows(NtcbTextureSet* textureSet, const int32_t* rowRanges, NtcbDecompressionStats* stats,
+    int useInt8Weights)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->DecompressRows(rowRanges, stats, useInt8Weights != 0);
+}
+
+int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadChannelsParams* params)
+{
+    if (!textureSet || !params)
+    {
+        ntcb::SetError("textureSet and params must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->ReadChannels(*params);
+}
+
+int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void** outPointer, size_t* outBytes)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->GetDeviceMip(mipLevel, outPointer, outBytes);
+}
+
+int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->Synchronize();
+}
+
+} // extern "C"

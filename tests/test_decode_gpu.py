@@ -1,0 +1,254 @@
+"""Parity of the sm_100a decode path, through the C ABI, against the CPU restatement and against
+outputs of the unmodified reference decoder.
+
+Bars (integer / byte work is bit-exact; floating point carries its tolerance here):
+  * kernel vs the CPU restatement of its arithmetic contract (exact accumulation): identical bits,
+    both weight modes (the FP8 layers accumulate e4m3 products in fp32 inside the tensor core; an
+    occasional last-bit difference in that sum may flip one binary16 rounding, so FP8 mode allows
+    <= 1 value in 100,000 to differ - none did on the fixtures);
+  * kernel vs the reference's own CUDA decode (golden fixtures and a live run when oracle/_ref is
+    present): >= 50 dB PSNR (peak = the reference's value range) on networks with O(1)
+    pre-activations.  The reference accumulates in binary16 and rounds after every 16 products;
+    that rounding flips 8-bit activation codes, which bounds the agreement any exact-accumulating
+    decoder can reach (the CPU restatement shows the same distance, test_oracle_golden.py).
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from conftest import load_golden, psnr_db
+
+import __graft_entry__ as entry
+
+entry.load_package()
+from rtxntc_library_b200 import binding, container, synthetic  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN_CASES = ["sq64_g2_f8_unit", "sq64_g2_f8_bench", "r96x40_g3_f12_unit", "sq128_g4_f12_2bit_bench",
+                "sq128_g4_f12_2bit_unit", "r128x64_g4_f16_unit", "r33x17_g1_f4_unit", "sq128_g6_f8_unit",
+                "sq64_g5_f16_mip0_unit"]
+
+
+def _sync():
+    import torch
+
+    torch.cuda.synchronize()
+
+
+def _assert_matches_contract(decoded, expected, use_int8, what):
+    different = int((decoded.view(np.uint16) != expected.view(np.uint16)).sum())
+    allowed = 0 if use_int8 else max(0, decoded.size // 100000)
+    assert different <= allowed, "%s: %d of %d values differ from the CPU restatement" % (what, different, decoded.size)
+
+
+@pytest.mark.parametrize("layout", [binding.LAYOUT_INTERLEAVED, binding.LAYOUT_PLANAR_PAIRS])
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_kernel_matches_contract_and_reference_on_golden_sets(oracle, golden_index, name, layout):
+    fixture = load_golden(name)
+    geo, latents, int8_blob, fp8_blob = container.read_container(fixture["container"].tobytes())
+    packed = np.concatenate([p.reshape(-1) for p in latents])
+    checker = oracle.OracleSet(geo, packed, int8_blob, fp8_blob)
+    resident = binding.ResidentTextureSet(geo, packed, int8_blob, fp8_blob, layout=layout)
+    for mode in golden_index[name]["modes"]:
+        use_int8 = mode == "int8"
+        resident.out.fill_(float("nan"))
+        resident.decode(use_int8)
+        _sync()
+        resident.check_status()
+        for mip in range(geo.mips):
+            decoded = resident.mip_numpy(mip)
+            _assert_matches_contract(decoded, checker.decode_mip(mip, use_int8, oracle.NUMERICS_SPEC), use_int8,
+                                     "%s %s mip %d" % (name, mode, mip))
+        if golden_index[name]["network"] == "unit":
+            reference = fixture["%s_mip0" % mode].view(np.float16)
+            assert psnr_db(resident.mip_numpy(0), reference) >= 50.0
+
+
+RANDOM_SPECS = [
+    # width, height, channels, mips (0 = full chain), grid scale, features
+    (1, 1, 2, 1, 1, 4), (2, 3, 1, 0, 1, 8), (31, 5, 3, 0, 2, 12), (32, 4, 4, 1, 3, 16), (33, 9, 5, 0, 4, 4),
+    (100, 37, 7, 0, 5, 8), (257, 129, 9, 0, 6, 12), (64, 256, 11, 0, 1, 16), (512, 64, 13, 0, 2, 4),
+    (320, 200, 15, 0, 3, 8), (200, 320, 16, 0, 4, 12), (96, 96, 12, 4, 5, 16), (1000, 10, 2, 0, 6, 16),
+]
+
+
+@pytest.mark.parametrize("shape", RANDOM_SPECS)
+@pytest.mark.parametrize("network", ["unit", "benchmark"])
+def test_kernel_matches_contract_on_ragged_shapes(oracle, shape, network):
+    """Every grid scale and feature count, odd channel counts, sizes that are not multiples of the
+    32x4 tile, one-texel mips, width != height."""
+    w, h, c, mips, g, f = shape
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(w, h, c, mips, g, f, seed=w * 7 + h, network=network))
+    geo = data.geometry
+    checker = oracle.OracleSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(data)
+    for use_int8 in (True, False):
+        resident.out.fill_(float("nan"))
+        resident.decode(use_int8)
+        _sync()
+        resident.check_status()
+        for mip in range(geo.mips):
+            _assert_matches_contract(resident.mip_numpy(mip), checker.decode_mip(mip, use_int8, oracle.NUMERICS_SPEC),
+                                     use_int8, "%s mip %d" % (shape, mip))
+
+
+def test_row_ranges_tile_rows_and_guard_bands(oracle):
+    """Decoding a mip in row bands (the unit of tile-row sharding) gives the same bits as one
+    whole decode, writes nothing outside its band, and leaves canaries around the buffer intact."""
+    import torch
+
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(160, 90, 6, 0, 2, 8, seed=21, network="unit"))
+    geo = data.geometry
+    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident.decode(True)
+    _sync()
+    whole = resident.out.clone()
+
+    elements = binding.out_elements(geo)
+    guard = 4096
+    padded = torch.full((elements + 2 * guard,), -7.0, dtype=torch.float16, device=resident.device)
+    band = padded[guard:guard + elements]
+    bands = {0: [(0, 13), (13, 14), (14, 64), (64, 90)], 1: [(0, 45)], 2: [(5, 22)]}
+    for mip, ranges in bands.items():
+        for begin, end in ranges:
+            params = resident.params(True, out=band, mips=[mip], row_ranges={mip: (begin, end)})
+            resident.launch(params)
+    _sync()
+    resident.check_status()
+    result = padded.cpu().numpy()
+    assert (result[:guard] == -7.0).all() and (result[guard + elements:] == -7.0).all()
+    expected = whole.cpu().numpy()
+    c = geo.channels
+    for mip, cm in enumerate(geo.color_mips):
+        rows = np.zeros(cm.height, dtype=bool)
+        for begin, end in bands.get(mip, []):
+            rows[begin:end] = True
+        got = result[guard + cm.texel_offset * c:guard + (cm.texel_offset + cm.width * cm.height) * c].reshape(cm.height, -1)
+        want = expected[cm.texel_offset * c:(cm.texel_offset + cm.width * cm.height) * c].reshape(cm.height, -1)
+        assert np.array_equal(got[rows].view(np.uint16), want[rows].view(np.uint16))
+        assert (got[~rows] == -7.0).all()
+
+
+def test_texture_set_api_decompress_and_read_channels(oracle):
+    """The texture-set level of the C ABI: load from a container in host memory, Decompress,
+    ReadChannels with full, subset and padded requests, to host and to device memory, for both
+    internal layouts."""
+    import torch
+
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(96, 40, 6, 0, 3, 12, seed=5, network="unit"))
+    geo = data.geometry
+    checker = oracle.OracleSet.from_synthetic(data)
+    context = binding.Context(0)
+    try:
+        for layout in (binding.LAYOUT_INTERLEAVED, binding.LAYOUT_PLANAR_PAIRS):
+            texture_set = context.create_texture_set(data.container, layout)
+            assert (texture_set.desc.width, texture_set.desc.channels, texture_set.desc.mips) == (96, 6, geo.mips)
+            with pytest.raises(binding.NtcbError) as error:
+                texture_set.read_mip(0)
+            assert error.value.code == -8  # InvalidState: nothing decompressed yet
+            for use_int8 in (True, False):
+                milliseconds = texture_set.decompress(use_int8, with_stats=True)
+                assert milliseconds > 0
+                for mip in range(geo.mips):
+                    expected = checker.decode_mip(mip, use_int8, oracle.NUMERICS_SPEC)
+                    assert np.array_equal(texture_set.read_mip(mip).view(np.uint16), expected.view(np.uint16))
+                expected = checker.decode_mip(0, use_int8, oracle.NUMERICS_SPEC)
+                # channel subset
+                assert np.array_equal(texture_set.read_mip(0, 1, 3).view(np.uint16), expected[:, :, 1:4].view(np.uint16))
+                # padded strides into host memory: gaps come back as zeros
+                w, h = texture_set.mip_size(0)
+                padded = np.full((h, w + 3, 8), 5.0, dtype=np.float16)
+                texture_set.read_channels_into(0, padded.ctypes.data, False, 2, 4, pixel_stride=16, row_pitch=(w + 3) * 16)
+                assert np.array_equal(padded[:, :w, :4].view(np.uint16), expected[:, :, 2:6].view(np.uint16))
+                assert (padded[:, :w, 4:] == 0).all() and (padded[:, w:, :] == 0).all()
+                # device destination
+                target = torch.zeros((h, w, geo.channels), dtype=torch.float16, device="cuda:0")
+                texture_set.read_channels_into(0, target.data_ptr(), True)
+                assert np.array_equal(target.cpu().numpy().view(np.uint16), expected.view(np.uint16))
+            # argument errors follow the reference's conventions
+            for kwargs, code in (({"first_channel": 6}, -9), ({"num_channels": 7}, -9), ({"pixel_stride": 2}, -1)):
+                with pytest.raises(binding.NtcbError) as error:
+                    texture_set.read_channels_into(0, target.data_ptr(), True, **kwargs)
+                assert error.value.code == code
+            with pytest.raises(binding.NtcbError):
+                texture_set.read_channels_into(geo.mips, target.data_ptr(), True)
+            # row-sharded decompress
+            ranges = [(0, cm.height // 2) for cm in geo.color_mips]
+            texture_set.decompress(True, row_ranges=ranges)
+            texture_set.synchronize()
+            texture_set.close()
+    finally:
+        context.close()
+
+
+def test_live_reference_comparison(oracle):
+    """Runs the unmodified reference decoder (oracle/_ref) on this GPU next to ours on a set the
+    fixtures do not contain."""
+    if not oracle.reference_available():
+        pytest.skip("oracle/_ref/libntc_ref.so is not built")
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(256, 192, 8, 0, 4, 8, seed=77, network="unit"))
+    geo = data.geometry
+    reference = oracle.ReferenceDecoder(data.container, geo.channels)
+    resident = binding.ResidentTextureSet.from_synthetic(data)
+    checker = oracle.OracleSet.from_synthetic(data)
+    try:
+        for use_int8 in (True, False):
+            reference.decompress(use_int8)
+            resident.decode(use_int8)
+            _sync()
+            for mip in (0, 1, 2):
+                cm = geo.color_mips[mip]
+                theirs = reference.read_mip(mip, cm.width, cm.height)
+                ours = resident.mip_numpy(mip)
+                assert psnr_db(ours, theirs) >= 50.0
+                # and the reference-emulating CPU numerics reproduce the live reference
+                emulated = checker.decode_mip(mip, use_int8, oracle.NUMERICS_REF)
+                different = int((emulated.view(np.uint16) != theirs.view(np.uint16)).sum())
+                assert different <= max(2, theirs.size * 2e-4)
+    finally:
+        reference.close()
+
+
+def test_full_size_properties_of_the_pbr_configuration(oracle):
+    """4096x4096, 12 channels, 13 mips, FP8: the CPU restatement cannot decode 22 M texels in
+    seconds, so the full-size check uses properties: a second decode reproduces the first bit for
+    bit, a row-banded decode reproduces the whole decode, and 20,000 randomly chosen texels over all
+    mips agree with the CPU restatement."""
+    import torch
+
+    data = synthetic.make_texture_set(synthetic.config_spec(1))
+    geo = data.geometry
+    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident.decode(False)
+    _sync()
+    resident.check_status()
+    first = resident.out.clone()
+    resident.out.zero_()
+    bands = {mip: (0, cm.height) for mip, cm in enumerate(geo.color_mips)}
+    for part in range(8):  # mip 0..2 in eight row bands, as eight GPUs would share them
+        ranges = {}
+        for mip in (0, 1, 2):
+            h = geo.color_mips[mip].height
+            ranges[mip] = (part * h // 8, (part + 1) * h // 8)
+        resident.launch(resident.params(False, mips=[0, 1, 2], row_ranges=ranges))
+    resident.launch(resident.params(False, mips=list(range(3, geo.mips)), row_ranges=bands))
+    _sync()
+    resident.check_status()
+    assert torch.equal(first.view(torch.int16), resident.out.view(torch.int16))
+
+    checker = oracle.OracleSet.from_synthetic(data)
+    queries = synthetic.make_queries(20000, max_lod=geo.mips - 0.001, seed=9)
+    expected = checker.sample(queries, False, oracle.NUMERICS_SPEC)
+    c = geo.channels
+    flat = first.cpu().numpy()
+    mismatched = 0
+    for q, want in zip(queries, expected):
+        mip = int(np.floor(q[2]))
+        cm = geo.color_mips[mip]
+        x = min(cm.width - 1, int(np.floor(np.float32(q[0]) * np.float32(cm.width))))
+        y = min(cm.height - 1, int(np.floor(np.float32(q[1]) * np.float32(cm.height))))
+        start = (cm.texel_offset + y * cm.width + x) * c
+        mismatched += int(not np.array_equal(flat[start:start + c].view(np.uint16), want.view(np.uint16)))
+    assert mismatched == 0

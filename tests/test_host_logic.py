@@ -1,0 +1,214 @@
+"""Host-side logic that needs no GPU: geometry, the container writer/reader pair, the C ABI's
+exports and argument checking, and weight staging."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+
+entry.load_package()
+from rtxntc_library_b200 import binding, container, geometry, synthetic  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+SHAPES = [(64, 64, 4, 0, 2, 8), (96, 40, 6, 0, 3, 12), (4096, 4096, 12, 0, 4, 12), (2048, 2048, 8, 0, 4, 8),
+          (8192, 8192, 16, 0, 4, 16), (1024, 1024, 4, 1, 2, 8), (33, 17, 1, 0, 1, 4), (7, 300, 3, 0, 6, 16),
+          (1, 1, 2, 1, 1, 4), (500, 500, 5, 3, 5, 8)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_python_geometry_matches_c_restatement(oracle, shape):
+    w, h, c, mips, g, f = shape
+    spec = synthetic.TextureSetSpec(w, h, c, mips, g, f, seed=0)
+    geo = spec.geometry()
+    dummy = np.zeros(geo.total_latent_pixels * geo.num_layers, dtype=np.uint16)
+    cgeo = oracle.OracleSet(geo, dummy, bytes(geometry.INT8_BLOB_BYTES), bytes(geometry.FP8_BLOB_BYTES)).c_geometry()
+    assert cgeo.numNeuralMips == geo.num_neural_mips and cgeo.numLayers == geo.num_layers
+    assert list(cgeo.latentWidth[:geo.num_neural_mips]) == geo.latent_width
+    assert list(cgeo.latentHeight[:geo.num_neural_mips]) == geo.latent_height
+    for mip, cm in enumerate(geo.color_mips):
+        assert (cgeo.mipWidth[mip], cgeo.mipHeight[mip], cgeo.neuralLod[mip]) == (cm.width, cm.height, cm.neural_lod)
+        assert cgeo.positionScale[mip] == np.float32(cm.position_scale)
+        assert abs(cgeo.positionLod[mip] - cm.position_lod) <= 1e-6
+        assert cgeo.mipTexelOffset[mip] == cm.texel_offset
+
+
+def test_known_geometry_of_the_pbr_configuration():
+    """4096x4096, grid scale 4: eight neural mips from 1024^2 down; mips 0-2 read neural LOD 0,
+    3-4 LOD 2, 5-6 LOD 4, 7-12 LOD 6 (src/FeatureGridMath.cpp:47-76)."""
+    geo = synthetic.config_spec(1).geometry()
+    assert geo.mips == 13 and geo.num_neural_mips == 8 and geo.num_layers == 3
+    assert geo.latent_width == [1024, 512, 256, 128, 64, 32, 16, 8]
+    assert [cm.neural_lod for cm in geo.color_mips] == [0, 0, 0, 2, 2, 4, 4, 6, 6, 6, 6, 6, 6]
+    assert [cm.position_scale for cm in geo.color_mips[:3]] == [0.125, 0.25, 0.5]
+    assert geo.total_texels == 22369621
+    assert geo.encoded_latent_bytes == 8388480
+
+
+def test_container_round_trip_and_probe():
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(96, 40, 5, 0, 3, 12, seed=5, network="unit"))
+    geo, latents, int8_blob, fp8_blob = container.read_container(data.container)
+    assert (geo.width, geo.height, geo.channels, geo.mips) == (96, 40, 6, 7)
+    assert int8_blob == data.int8_blob and fp8_blob == data.fp8_blob
+    assert all(np.array_equal(a, b) for a, b in zip(latents, data.latents))
+    desc = binding.probe_container(data.container)
+    assert (desc.width, desc.height, desc.channels, desc.mips) == (96, 40, 6, 7)
+    assert (desc.gridSizeScale, desc.numFeatures, desc.numNeuralMips, desc.numLayers) == (3, 12, 4, 3)
+    assert desc.totalTexels == geo.total_texels
+
+
+def test_reference_loader_accepts_the_container(oracle):
+    """Needs oracle/_ref (built where the reference sources are); metadata only, no GPU."""
+    if not oracle.reference_available():
+        pytest.skip("oracle/_ref/libntc_ref.so is not built")
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 0, 2, 8, seed=3))
+    assert oracle.reference_probe(data.container) == [64, 64, 4, 7, 2, 8, 6, 0]
+
+
+def patch_document(data: bytes, edit) -> bytes:
+    """Rewrites a container with its JSON document passed through `edit` (header sizes updated)."""
+    import json
+    import struct
+
+    signature, version, json_offset, json_size, binary_offset, binary_size = struct.unpack_from("<IIQQQQ", data, 0)
+    document = json.loads(data[json_offset:json_offset + json_size].rstrip(b"\0"))
+    edit(document)
+    text = json.dumps(document, separators=(",", ":")).encode() + b"\0"
+    new_binary_offset = (40 + len(text) + 3) & ~3
+    out = bytearray(struct.pack("<IIQQQQ", signature, version, 40, len(text), new_binary_offset, binary_size))
+    out += text
+    out += bytes(new_binary_offset - len(out))
+    out += data[binary_offset:binary_offset + binary_size]
+    return bytes(out)
+
+
+def _set(path, value):
+    def edit(document):
+        node = document
+        for key in path[:-1]:
+            node = node[key]
+        node[path[-1]] = value
+    return edit
+
+
+@pytest.mark.parametrize("damage,code", [
+    (lambda b: b[:30], -3),
+    (lambda b: b"XXXX" + b[4:], -3),
+    (lambda b: b[:4] + b"\x01\x02\x00\x00" + b[8:], -3),
+    (lambda b: b[:len(b) - 100], -3),
+    (lambda b: patch_document(b, _set(["schemaVersion"], 2)), -3),
+    (lambda b: patch_document(b, _set(["latentShape", "numFeatures"], 9)), -9),
+    (lambda b: patch_document(b, _set(["mlpVersions", 0, "weightLayout"], "ColumnMajor")), -3),
+    (lambda b: patch_document(b, _set(["mlpVersions", 1, "layers", 0, "biasType"], "Int32")), -3),
+    (lambda b: patch_document(b, _set(["mlpVersions", 0, "layers", 0, "inputChannels"], 32)), -3),
+    (lambda b: patch_document(b, _set(["colorMips", 0, "latentMip"], 4)), -3),
+    (lambda b: patch_document(b, _set(["latents", 1, "width"], 17)), -3),
+    (lambda b: patch_document(b, _set(["views", 3, "offset"], 2)), -3),
+    (lambda b: patch_document(b, _set(["views", 3, "storedSize"], 1 << 40)), -3),
+    (lambda b: patch_document(b, _set(["width"], 0)), -9),
+])
+def test_container_errors_are_reported(damage, code):
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 0, 2, 8, seed=3)).container
+    with pytest.raises(binding.NtcbError) as error:
+        binding.probe_container(damage(data))
+    assert error.value.code == code
+    assert str(error.value)
+
+
+def test_patch_document_keeps_a_valid_container_valid():
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 0, 2, 8, seed=3)).container
+    assert binding.probe_container(patch_document(data, lambda document: None)).width == 64
+
+
+def test_smaller_hidden_layers_are_zero_expanded():
+    """A file may carry narrower hidden layers; they land in the top-left corner of the full
+    matrices (src/TextureSetMetadata.cpp:660-713)."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 0, 2, 8, seed=3)).container
+
+    def narrow(document):
+        layers = document["mlpVersions"][0]["layers"]
+        layers[0]["outputChannels"] = 48
+        layers[1]["inputChannels"] = 48
+    assert binding.probe_container(patch_document(data, narrow)).width == 64
+
+
+def test_compressed_views_are_refused():
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 0, 2, 8, seed=3)).container
+    damaged = patch_document(data, _set(["views", 0, "compression"], "GDeflate"))
+    with pytest.raises(binding.NtcbError) as error:
+        binding.probe_container(damaged)
+    assert error.value.code == -5  # Unsupported
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "ntcb.h")).read()
+    declared = set(re.findall(r"\b(ntcb_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 15
+    lib = binding.lib()
+    for name in sorted(declared):
+        assert hasattr(lib, name), "libntcb200.so does not export " + name
+
+
+def test_weight_staging_layout():
+    """K-major core-matrix order: byte (n, k) of layer l at (k / 16) * (N * 16) + n * 16 + k % 16."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=3))
+    offsets = [0, 4096, 7168, 9216]
+    for blob, mode in ((data.int8_blob, binding.WEIGHTS_INT8), (data.fp8_blob, binding.WEIGHTS_FP8)):
+        staged = binding.stage_network(blob, mode)
+        source = np.frombuffer(blob, dtype=np.uint8)
+        position = 0
+        for layer, (nin, nout) in enumerate(zip(geometry.MLP_LAYER_INPUTS, geometry.MLP_LAYER_OUTPUTS)):
+            weights = source[position:position + nin * nout].reshape(nout, nin)
+            position += nin * nout
+            padded_k = 32 if layer == 3 else 64
+            for n in (0, 7, 8, nout - 1):
+                for k in (0, 15, 16, 31, nin - 1):
+                    assert staged[offsets[layer] + (k // 16) * nout * 16 + n * 16 + k % 16] == weights[n, k]
+            if padded_k > nin:  # zero padding of K
+                for n in range(nout):
+                    assert staged[offsets[layer] + (nin // 16) * nout * 16 + n * 16] == 0
+        scales = staged[9728:9728 + 1024].view(np.float32).reshape(4, 64)
+        if mode == binding.WEIGHTS_INT8:
+            assert np.array_equal(scales[0], source[8192:8192 + 256].view(np.float32))
+            assert np.array_equal(staged[10752:10752 + 256].view(np.int32), source[8832:8832 + 256].view(np.int32))
+        else:
+            assert np.array_equal(scales[3, :16], source[8480:8544].view(np.float32))
+            assert np.array_equal(staged[10752:10752 + 128].view(np.float16), source[8192:8320].view(np.float16))
+
+
+def test_stage_network_rejects_wrong_sizes():
+    with pytest.raises(binding.NtcbError) as error:
+        binding.stage_network(bytes(100), binding.WEIGHTS_INT8)
+    assert error.value.code == -1
+
+
+def test_decode_validates_arguments_before_touching_the_gpu():
+    lib = binding.lib()
+    params = binding.DecodeParams()
+    assert lib.ntcb_decode(ctypes.byref(params), None) == -1
+    assert b"NULL" in lib.ntcb_last_error()
+    geo = synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=0).geometry()
+    good = binding.fill_params(geo, 0x1000, 0x2000, 0x3000, 0x4000, binding.WEIGHTS_INT8)
+    good.channels = 5
+    assert lib.ntcb_decode(ctypes.byref(good), None) == -1
+    good.channels = 4
+    good.mips[0].rowEnd = 100
+    assert lib.ntcb_decode(ctypes.byref(good), None) == -1
+
+
+def test_no_cpu_fallback():
+    """Without a usable GPU the compute entry points fail with a CUDA error instead of computing
+    on the host."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    lib = binding.lib()
+    handle = ctypes.c_void_p()
+    assert lib.ntcb_context_create(0, ctypes.byref(handle)) == -2
+    geo = synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=0).geometry()
+    params = binding.fill_params(geo, 0x1000, 0x2000, 0x3000, 0x4000, binding.WEIGHTS_INT8)
+    assert lib.ntcb_decode(ctypes.byref(params), None) == -2
