@@ -219,6 +219,11 @@ int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void**
 /* Waits for everything queued on the texture set's stream. */
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet);
 
+/* Number of CTAs the decode kernel keeps resident on the current device for a weight mode (the
+   grid size of large launches): SM count x resident CTAs per SM, the latter bounded by registers,
+   shared memory and tensor-memory columns.  For benchmarks and tests. */
+int ntcb_decode_resident_ctas(int weightMode, int* outCtas);
+
 /* Number of kernel launches this library has issued from the calling process so far
    (bookkeeping for benchmarks). */
 uint64_t ntcb_launch_count(void);

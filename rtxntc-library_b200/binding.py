@@ -92,6 +92,7 @@ def lib():
         handle.ntcb_launch_count.restype = ctypes.c_uint64
         handle.ntcb_stage_network.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
+        handle.ntcb_decode_resident_ctas.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         handle.ntcb_probe_container.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetDesc)]
         handle.ntcb_context_create.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]
         handle.ntcb_context_destroy.argtypes = [ctypes.c_void_p]

@@ -308,12 +308,30 @@ __device__ __forceinline__ float Frac(float t)
 // The kernel
 // ---------------------------------------------------------------------------------------------
 
+// Per-tile lookup tables: the bilinear tap position and weights are separable in x and y, and so
+// is the positional encoding, so they are computed once per tile column / row instead of once per
+// texel.
+struct __align__(16) TileTables
+{
+    // per grid (0 = high-res, 1 = low-res) and tile column: footprint x index, dx, 1 - dx
+    int4 colTap[2][kTileWidth];
+    // per grid and tile row: footprint y index, dy, 1 - dy
+    int4 rowTap[2][kTileHeight];
+    // positional-encoding operand bytes: x = {X0 w0, X1 w0, X0 w1, X1 w1}, y = {X0 w2, X1 w2, 0, 0}
+    uint2 colEnc[kTileWidth];
+    uint2 rowEnc[kTileHeight];
+    int footWidth[2];  // footprint width in latent pixels, per grid
+    uint32_t lodWord;  // operand bytes of inputs 44..47: lod, lod, 0, 0
+    uint32_t pad;
+};
 
 struct __align__(16) SharedStorage
 {
     uint8_t network[kStagedNetworkBytes]; // weights in core-matrix order, scales, biases
     uint8_t operandA[128 * 64];           // A operand of the current layer, core-matrix order
+    uint8_t footprint[2][kFootprintBytes]; // unpacked latents of the tile's footprint, per grid
     uint32_t latentTable[256];            // byte (two nibbles) -> two binary16 latent values
+    TileTables tables;
     uint64_t barrier;
     uint32_t tmemBase;
 };
@@ -324,6 +342,157 @@ struct TileContext
     uint32_t tmemBase, tmemLane, barrier, operandA, networkBase;
     int tile, x, y;
 };
+
+// One axis of the bilinear footprint (src/FeatureGridDevice.h:35-45): base tap index (before
+// wrapping) and the fractional offset of a texel coordinate in a latent grid of `size` pixels.
+__device__ __forceinline__ void AxisTap(int texel, float invExtent, int size, int& base, float& frac)
+{
+    const float u = __fmul_rn(__fadd_rn(float(texel), 0.5f), invExtent);
+    const float p = __fmaf_rn(u, float(size), -0.5f);
+    const float b = floorf(p);
+    base = int(b);
+    frac = __fsub_rn(p, b);
+}
+
+// Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory
+// (nibbles unpacked to binary16 once per latent pixel instead of once per texel and tap).
+// Warps 0 and 2 work on the high-res grid, warps 1 and 3 on the low-res grid.
+template <bool kFp8>
+__device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, SharedStorage& shared,
+    int tileX0, int tileY0, int lane, int warp)
+{
+    const int grid = warp & 1;
+    const int gw = grid ? mip.loWidth : mip.hiWidth;
+    const int gh = grid ? mip.loHeight : mip.hiHeight;
+
+    int xb, yb;
+    float dx, dy;
+    AxisTap(min(tileX0 + lane, mip.width - 1), mip.invWidth, gw, xb, dx);
+    AxisTap(min(tileY0 + (lane & 3), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
+    const int fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
+    const int fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
+    const int footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
+    const int footH = __shfl_sync(0xFFFFFFFFu, yb, 3) - fy0 + 2;
+
+    if (warp < 2)
+    {
+        shared.tables.colTap[grid][lane] = make_int4(xb - fx0, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
+        if (lane < kTileHeight)
+            shared.tables.rowTap[grid][lane] = make_int4(yb - fy0, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
+        if (lane == 0)
+            shared.tables.footWidth[grid] = footW;
+    }
+    else
+    {
+        // positional encoding (src/RegressionKernels.h:59-85): warp 2 the x part per column, warp 3
+        // the y part per row, quantised exactly as the per-texel inputs would be
+        const bool rows = warp == 3;
+        const int coordinate = rows ? min(tileY0 + (lane & 3), mip.rowEnd - 1) : min(tileX0 + lane, mip.width - 1);
+        float f = __fmul_rn(float(coordinate), mip.positionScale);
+        uint32_t q[3];
+#pragma unroll
+        for (int wave = 0; wave < 3; ++wave)
+        {
+            const float e0 = __fmaf_rn(Frac(f), 2.f, -1.f);
+            const float e1 = __fmaf_rn(Frac(__fadd_rn(f, 0.25f)), 2.f, -1.f);
+            q[wave] = QuantizeInputPair<kFp8>(__floats2half2_rn(e0, e1));
+            f = __fmul_rn(f, 2.f);
+        }
+        const uint2 enc = make_uint2(PackCodes<kFp8>(q[0], q[1]), PackCodes<kFp8>(q[2], 0));
+        if (!rows)
+            shared.tables.colEnc[lane] = enc;
+        else if (lane < kTileHeight)
+            shared.tables.rowEnc[lane] = enc;
+        if (rows && lane == 4)
+            shared.tables.lodWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(mip.positionLod)),
+                                                   QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
+    }
+
+    if (mip.staged)
+    {
+        // footprint pixel p = fy * footW + fx, handed out over the 64 threads that share this grid
+        const int count = footW * footH;
+        const uint32_t magic = (1u << 20) / uint32_t(footW) + 1; // p / footW == (p * magic) >> 20 for p < 2048
+        const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
+        const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
+        uint8_t* foot = shared.footprint[grid];
+        for (int p = lane + 32 * (warp >> 1); p < count; p += 64)
+        {
+            const int fy = int((uint32_t(p) * magic) >> 20);
+            const int fx = p - fy * footW;
+            // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
+            int gx = fx0 + fx, gy = fy0 + fy;
+            gx += gx < 0 ? gw : 0;
+            gx -= gx >= gw ? gw : 0;
+            gy += gy < 0 ? gh : 0;
+            gy -= gy >= gh ? gh : 0;
+            const uint16_t* src = plane0 + size_t(gy) * gw + gx;
+            uint2* dst = reinterpret_cast<uint2*>(foot + (size_t(p) << mip.strideShift));
+#pragma unroll
+            for (int layer = 0; layer < 4; ++layer)
+            {
+                if (layer < params.numLayers)
+                {
+                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
+                    dst[layer] = make_uint2(shared.latentTable[pixel & 0xFF], shared.latentTable[pixel >> 8]);
+                }
+            }
+        }
+    }
+}
+
+// Four quantised inputs of one latent layer from the four staged taps.
+// Blend order as the reference build evaluates it: fma(l11,w3, fma(l10,w2, fma(l00,w0, l01*w1))).
+template <bool kFp8>
+__device__ __forceinline__ uint32_t BlendLayer(uint2 l00, uint2 l01, uint2 l10, uint2 l11, __half2 w00, __half2 w01,
+    __half2 w10, __half2 w11)
+{
+    const __half2 two = __float2half2_rn(2.f), minusOne = __float2half2_rn(-1.f);
+    __half2 a = __hmul2_rn(AsHalf2(l01.x), w01);
+    __half2 b = __hmul2_rn(AsHalf2(l01.y), w01);
+    a = __hfma2(AsHalf2(l00.x), w00, a);
+    b = __hfma2(AsHalf2(l00.y), w00, b);
+    a = __hfma2(AsHalf2(l10.x), w10, a);
+    b = __hfma2(AsHalf2(l10.y), w10, b);
+    a = __hfma2(AsHalf2(l11.x), w11, a);
+    b = __hfma2(AsHalf2(l11.y), w11, b);
+    a = __hfma2(a, two, minusOne);
+    b = __hfma2(b, two, minusOne);
+    return PackCodes<kFp8>(QuantizeInputPair<kFp8>(a), QuantizeInputPair<kFp8>(b));
+}
+
+// Inputs 0..15 or 16..31 of one texel from the staged footprint of one grid.
+template <bool kFp8>
+__device__ __forceinline__ void GatherGrid(const KernelParams& params, const KernelMip& mip, const SharedStorage& shared,
+    int grid, int lane, int warp, uint32_t* words)
+{
+    const int4 col = shared.tables.colTap[grid][lane];
+    const int4 row = shared.tables.rowTap[grid][warp];
+    const int footW = shared.tables.footWidth[grid];
+    const float dx = __int_as_float(col.y), dxn = __int_as_float(col.z);
+    const float dy = __int_as_float(row.y), dyn = __int_as_float(row.z);
+    // src/FeatureGridDevice.h:46-49
+    const __half2 wTop = __floats2half2_rn(__fmul_rn(dxn, dyn), __fmul_rn(dx, dyn));
+    const __half2 wBottom = __floats2half2_rn(__fmul_rn(dxn, dy), __fmul_rn(dx, dy));
+    const __half2 w00 = __low2half2(wTop), w01 = __high2half2(wTop);
+    const __half2 w10 = __low2half2(wBottom), w11 = __high2half2(wBottom);
+
+    const int stride = 1 << mip.strideShift;
+    const uint8_t* tap00 = shared.footprint[grid] + (size_t(row.x * footW + col.x) << mip.strideShift);
+    const uint8_t* tap10 = tap00 + (size_t(footW) << mip.strideShift);
+#pragma unroll
+    for (int layer = 0; layer < 4; ++layer)
+    {
+        if (layer < params.numLayers)
+        {
+            const uint2 l00 = *reinterpret_cast<const uint2*>(tap00 + layer * 8);
+            const uint2 l01 = *reinterpret_cast<const uint2*>(tap00 + stride + layer * 8);
+            const uint2 l10 = *reinterpret_cast<const uint2*>(tap10 + layer * 8);
+            const uint2 l11 = *reinterpret_cast<const uint2*>(tap10 + stride + layer * 8);
+            words[layer] = BlendLayer<kFp8>(l00, l01, l10, l11, w00, w01, w10, w11);
+        }
+    }
+}
 
 // One layer of the MLP for the CTA's current tile: barrier, MMA issue, wait, then either the
 // activation + re-quantisation into the next A operand (layers 0-2) or the output epilogue
@@ -377,39 +546,50 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
 
     if (kLayer < 3)
     {
-        uint32_t acc[kN / 16][16];
-#pragma unroll
-        for (int c = 0; c < kN / 16; ++c)
-            TmemLoad16(ctx.tmemLane + c * 16, acc[c]);
-        TmemLoadWait();
-
         constexpr bool kNextFp8 = kFp8 && kLayer < 2; // layer 2 always re-quantises to int8
         uint4* rowChunk = reinterpret_cast<uint4*>(shared.operandA) + tid;
+        // 32 accumulator columns at a time keeps the register footprint small
 #pragma unroll
-        for (int c = 0; c < kN / 16; ++c)
+        for (int half = 0; half < (kN + 31) / 32; ++half)
         {
-            uint32_t pairs[8];
+            constexpr int kChunksTotal = kN / 16;
+            const int firstChunk = half * 2;
+            uint32_t acc[2][16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int c = 0; c < 2; ++c)
+                if (firstChunk + c < kChunksTotal)
+                    TmemLoad16(ctx.tmemLane + (firstChunk + c) * 16, acc[c]);
+            TmemLoadWait();
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
             {
-                const int col = c * 16 + 2 * j;
-                __half2 xh;
-                if (kLayerFp8)
+                if (firstChunk + c < kChunksTotal)
                 {
-                    xh = __floats2half2_rn(__uint_as_float(acc[c][2 * j]), __uint_as_float(acc[c][2 * j + 1]));
-                    xh = __hadd2_rn(xh, biasH[col >> 1]);
+                    uint32_t pairs[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                    {
+                        const int colIndex = (firstChunk + c) * 16 + 2 * j;
+                        __half2 xh;
+                        if (kLayerFp8)
+                        {
+                            xh = __floats2half2_rn(__uint_as_float(acc[c][2 * j]), __uint_as_float(acc[c][2 * j + 1]));
+                            xh = __hadd2_rn(xh, biasH[colIndex >> 1]);
+                        }
+                        else
+                        {
+                            // include/libntc/shaders/Inference.hlsli:146-165: float(acc + bias) * scale
+                            float f0 = __fmul_rn(float(int32_t(acc[c][2 * j]) + biasI[colIndex]), scale[colIndex]);
+                            float f1 = __fmul_rn(float(int32_t(acc[c][2 * j + 1]) + biasI[colIndex + 1]), scale[colIndex + 1]);
+                            xh = __floats2half2_rn(f0, f1);
+                        }
+                        pairs[j] = ActivatePair<kNextFp8>(xh);
+                    }
+                    rowChunk[(firstChunk + c) * 128] =
+                        make_uint4(PackCodes<kNextFp8>(pairs[0], pairs[1]), PackCodes<kNextFp8>(pairs[2], pairs[3]),
+                                   PackCodes<kNextFp8>(pairs[4], pairs[5]), PackCodes<kNextFp8>(pairs[6], pairs[7]));
                 }
-                else
-                {
-                    // include/libntc/shaders/Inference.hlsli:146-165: float(acc + bias) * scale
-                    float f0 = __fmul_rn(float(int32_t(acc[c][2 * j]) + biasI[col]), scale[col]);
-                    float f1 = __fmul_rn(float(int32_t(acc[c][2 * j + 1]) + biasI[col + 1]), scale[col + 1]);
-                    xh = __floats2half2_rn(f0, f1);
-                }
-                pairs[j] = ActivatePair<kNextFp8>(xh);
             }
-            rowChunk[c * 128] = make_uint4(PackCodes<kNextFp8>(pairs[0], pairs[1]), PackCodes<kNextFp8>(pairs[2], pairs[3]),
-                                           PackCodes<kNextFp8>(pairs[4], pairs[5]), PackCodes<kNextFp8>(pairs[6], pairs[7]));
         }
         if (kLayer == 1)
             rowChunk[3 * 128] = make_uint4(0, 0, 0, 0); // layer 2 has 48 inputs, K is padded to 64
@@ -451,7 +631,7 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
 }
 
 template <bool kFp8>
-__global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSm) DecodeKernel(const __grid_constant__ KernelParams params)
+__global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8) DecodeKernel(const __grid_constant__ KernelParams params)
 {
     __shared__ SharedStorage shared;
 
@@ -485,77 +665,88 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSm) DecodeKernel(const
         TcgenFenceAfterSync();
     }
     const uint32_t tmemBase = shared.tmemBase;
-    const uint32_t tmemLane = tmemBase + (uint32_t(warp * 32) << 16);
-    const uint32_t barrier = SharedAddress(&shared.barrier);
-    const uint32_t operandA = SharedAddress(shared.operandA);
-    const uint32_t networkBase = SharedAddress(shared.network);
     uint32_t phase = 0;
     int failed = 0;   // this thread gave up on a wait
     int aborted = 0;  // some thread of the CTA did (uniform: comes out of a barrier)
 
+    TileContext ctx;
+    ctx.tid = tid;
+    ctx.tmemBase = tmemBase;
+    ctx.tmemLane = tmemBase + (uint32_t(warp * 32) << 16);
+    ctx.barrier = SharedAddress(&shared.barrier);
+    ctx.operandA = SharedAddress(shared.operandA);
+    ctx.networkBase = SharedAddress(shared.network);
+
+    int mipIndex = 0;
     for (int tile = blockIdx.x; tile < params.totalTiles; tile += gridDim.x)
     {
-        // ---- locate the tile ------------------------------------------------------------
-        int mipIndex = 0;
+        // ---- locate the tile (tiles are visited in increasing order) ----------------------
         while (mipIndex + 1 < params.numMips && tile >= params.mips[mipIndex + 1].firstTile)
             ++mipIndex;
         const KernelMip& mip = params.mips[mipIndex];
         const int local = tile - mip.firstTile;
         const int tileY = local / mip.tilesX;
         const int tileX = local - tileY * mip.tilesX;
-        const int x = tileX * kTileWidth + lane;
-        const int y = mip.rowBegin + tileY * kTileHeight + warp;
-        // threads past the right / bottom edge compute a clamped texel and store nothing
-        const int xs = min(x, mip.width - 1);
-        const int ys = min(y, mip.rowEnd - 1);
+        const int tileX0 = tileX * kTileWidth;
+        const int tileY0 = mip.rowBegin + tileY * kTileHeight;
+        const int x = tileX0 + lane;
+        const int y = tileY0 + warp;
+        ctx.tile = tile;
+        ctx.x = x;
+        ctx.y = y;
 
         // ---- 1. network inputs -> A operand ----------------------------------------------
+        // The tables and footprints of the previous tile were last read before that tile's first
+        // layer barrier, so they may be overwritten here.
+        PrepareTile<kFp8>(params, mip, shared, tileX0, tileY0, lane, warp);
+        __syncthreads();
         {
             uint32_t words[16];
             const uint32_t zeroWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(0.f)),
                                                       QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
 #pragma unroll
-            for (int i = 0; i < 12; ++i)
-                words[i] = zeroWord;
+            for (int i = 0; i < 8; ++i)
+                words[i] = zeroWord; // unused feature slots hold quantised zeros (src/Inference.cu:49)
 #pragma unroll
             for (int i = 12; i < 16; ++i)
                 words[i] = 0; // K padding
 
-            // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
-            const float u = __fmul_rn(__fadd_rn(float(xs), 0.5f), mip.invWidth);
-            const float v = __fmul_rn(__fadd_rn(float(ys), 0.5f), mip.invHeight);
-
-            GridTaps taps;
-            SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
-            const uint16_t* hi = params.latents + mip.hiOffset;
-#pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
-                if (layer < params.numLayers)
-                    words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable);
-
-            SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
-            const uint16_t* lo = params.latents + mip.loOffset;
-#pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
-                if (layer < params.numLayers)
-                    words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable);
-
-            // src/RegressionKernels.h:59-85
-            float xf = __fmul_rn(float(xs), mip.positionScale);
-            float yf = __fmul_rn(float(ys), mip.positionScale);
-#pragma unroll
-            for (int wave = 0; wave < 3; ++wave)
+            if (mip.staged)
             {
-                float ex = __fmaf_rn(Frac(xf), 2.f, -1.f), ey = __fmaf_rn(Frac(yf), 2.f, -1.f);
-                float ez = __fmaf_rn(Frac(__fadd_rn(xf, 0.25f)), 2.f, -1.f);
-                float ew = __fmaf_rn(Frac(__fadd_rn(yf, 0.25f)), 2.f, -1.f);
-                words[8 + wave] = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__floats2half2_rn(ex, ey)),
-                                                   QuantizeInputPair<kFp8>(__floats2half2_rn(ez, ew)));
-                xf = __fmul_rn(xf, 2.f);
-                yf = __fmul_rn(yf, 2.f);
+                GatherGrid<kFp8>(params, mip, shared, 0, lane, warp, words);
+                GatherGrid<kFp8>(params, mip, shared, 1, lane, warp, words + 4);
             }
-            words[11] = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(mip.positionLod)),
-                                        QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
+            else
+            {
+                // footprint too large to stage (strong minification): read the taps from global memory
+                // threads past the right / bottom edge compute a clamped texel and store nothing
+                const int xs = min(x, mip.width - 1);
+                const int ys = min(y, mip.rowEnd - 1);
+                // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
+                const float u = __fmul_rn(__fadd_rn(float(xs), 0.5f), mip.invWidth);
+                const float v = __fmul_rn(__fadd_rn(float(ys), 0.5f), mip.invHeight);
+                GridTaps taps;
+                SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
+                const uint16_t* hi = params.latents + mip.hiOffset;
+#pragma unroll
+                for (int layer = 0; layer < 4; ++layer)
+                    if (layer < params.numLayers)
+                        words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable);
+                SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
+                const uint16_t* lo = params.latents + mip.loOffset;
+#pragma unroll
+                for (int layer = 0; layer < 4; ++layer)
+                    if (layer < params.numLayers)
+                        words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable);
+            }
+
+            // positional encoding: interleave the column's x bytes with the row's y bytes
+            const uint2 cx = shared.tables.colEnc[lane];
+            const uint2 ry = shared.tables.rowEnc[warp];
+            words[8] = __byte_perm(cx.x, ry.x, 0x5140);
+            words[9] = __byte_perm(cx.x, ry.x, 0x7362);
+            words[10] = __byte_perm(cx.y, ry.y, 0x5140);
+            words[11] = shared.tables.lodWord;
 
             uint4* rowChunk = reinterpret_cast<uint4*>(shared.operandA) + tid;
 #pragma unroll
@@ -564,32 +755,23 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSm) DecodeKernel(const
         }
 
         // ---- 2./3./4. the four layers ------------------------------------------------------
-        TileContext ctx;
-        ctx.tid = tid;
-        ctx.tmemBase = tmemBase;
-        ctx.tmemLane = tmemLane;
-        ctx.barrier = barrier;
-        ctx.operandA = operandA;
-        ctx.networkBase = networkBase;
-        ctx.tile = tile;
-        ctx.x = x;
-        ctx.y = y;
         aborted = RunLayer<kFp8, 0>(params, mip, shared, ctx, phase, failed);
         if (!aborted) aborted = RunLayer<kFp8, 1>(params, mip, shared, ctx, phase, failed);
         if (!aborted) aborted = RunLayer<kFp8, 2>(params, mip, shared, ctx, phase, failed);
         if (!aborted) aborted = RunLayer<kFp8, 3>(params, mip, shared, ctx, phase, failed);
         if (aborted)
             break;
-        // No barrier is needed here: step 1 of the next tile only writes the A operand, which the
-        // last MMA of this tile (already complete) was the last to read, and the barrier at the top
-        // of the next layer loop orders this tile's TMEM reads before the next MMA.
+        // No barrier is needed here: the next tile's preparation writes tables and footprints that
+        // were last read before this tile's first layer barrier, and its A operand is written after
+        // the barrier that follows the preparation; the last MMA of this tile (already complete) was
+        // the last reader of the A operand.
     }
 
     // ---- teardown -------------------------------------------------------------------------
     TcgenFenceBeforeSync();
     aborted = __syncthreads_or(failed);
     if (aborted && tid == 0)
-        (void)MbarrierWaitBounded(barrier, phase ^ 1); // one more bounded chance for work in flight to drain
+        (void)MbarrierWaitBounded(ctx.barrier, phase ^ 1); // one more bounded chance for work in flight to drain
     __syncthreads();
     if (warp == 0)
         TmemFree(tmemBase, kTmemColumns);
@@ -604,13 +786,6 @@ cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStr
     else
         DecodeKernel<false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
     return cudaGetLastError();
-}
-
-cudaError_t DecodeOccupancy(bool fp8, int* ctasPerSm)
-{
-    if (fp8)
-        return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctasPerSm, DecodeKernel<true>, kThreadsPerCta, 0);
-    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctasPerSm, DecodeKernel<false>, kThreadsPerCta, 0);
 }
 
 } // namespace ntcb

@@ -11,9 +11,11 @@ namespace ntcb
 constexpr int kTileWidth = 32;
 constexpr int kTileHeight = 4;
 constexpr int kThreadsPerCta = kTileWidth * kTileHeight; // one thread per texel of a tile
-constexpr int kCtasPerSm = 4;
+constexpr int kCtasPerSmInt8 = 5;  // resident CTAs per SM the two kernel variants are compiled for
+constexpr int kCtasPerSmFp8 = 6;
 constexpr int kTmemColumns = 64;           // widest accumulator (layer 0: 64 outputs)
 constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait is declared expired
+constexpr int kFootprintBytes = 6656;      // shared memory per latent grid for a tile's unpacked footprint
 
 // Image of the network in shared memory (produced on the host by ntcb_stage_network).
 // Weight matrix of layer l: N_l rows (outputs) x K_l bytes (inputs, padded to a multiple of 32) in
@@ -41,6 +43,8 @@ struct KernelMip
     float invWidth, invHeight;
     float positionScale, positionLod;
     int firstTile, tilesX;
+    int staged;      // the tile footprints of both grids fit into shared memory
+    int strideShift; // log2 of the bytes per staged latent pixel (8 bytes per layer, rounded up to a power of two)
 };
 
 struct KernelParams
@@ -58,6 +62,5 @@ struct KernelParams
 };
 
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
-cudaError_t DecodeOccupancy(bool fp8, int* ctasPerSm);
 
 } // namespace ntcb

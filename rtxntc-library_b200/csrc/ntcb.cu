@@ -67,22 +67,25 @@ int ResidentCtas(bool fp8, int* outCtas)
             return NTCB_OK;
         }
     }
-    int sms = 0, perSm = 0;
+    int sms = 0, major = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (err == cudaSuccess)
+        err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
     if (err != cudaSuccess)
         return CudaFailure("cudaDeviceGetAttribute", err);
-    err = DecodeOccupancy(fp8, &perSm);
-    if (err != cudaSuccess)
-        return CudaFailure("cudaOccupancyMaxActiveBlocksPerMultiprocessor", err);
-    if (perSm < 1)
+    if (major != 10)
     {
-        SetError("The decode kernel cannot be resident on this device (compute capability 10.0 required).");
+        SetError("The decode kernel needs a device of compute capability 10.x (tcgen05, tensor memory); device %d is %d.x.",
+            device, major);
         return NTCB_ERR_CUDA;
     }
-    // TMEM holds 512 columns per SM; every CTA takes kTmemColumns for its whole lifetime.
-    const int tmemLimit = 512 / kTmemColumns;
-    if (perSm > tmemLimit)
-        perSm = tmemLimit;
+    // The kernel is compiled for kCtasPerSmInt8 / kCtasPerSmFp8 resident CTAs (__launch_bounds__), each of which holds
+    // kTmemColumns of the SM's 512 tensor-memory columns for its whole lifetime.  (The runtime's
+    // occupancy query reports one CTA per SM for kernels that allocate tensor memory, so it is not
+    // used here.)
+    static_assert(kCtasPerSmInt8 * kTmemColumns <= 512 && kCtasPerSmFp8 * kTmemColumns <= 512,
+        "resident CTAs must fit into tensor memory");
+    const int perSm = fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
     *outCtas = sms * perSm;
     if (device >= 0 && device < 64)
         cache[device][fp8 ? 1 : 0].store(*outCtas, std::memory_order_relaxed);
@@ -123,6 +126,16 @@ const char* ntcb_status_string(int status)
 uint64_t ntcb_launch_count(void)
 {
     return g_launchCount.load(std::memory_order_relaxed);
+}
+
+int ntcb_decode_resident_ctas(int weightMode, int* outCtas)
+{
+    if (!outCtas || (weightMode != NTCB_WEIGHTS_INT8 && weightMode != NTCB_WEIGHTS_FP8))
+    {
+        SetError("ntcb_decode_resident_ctas: invalid arguments.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return ResidentCtas(weightMode == NTCB_WEIGHTS_FP8, outCtas);
 }
 
 int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void* staged)
@@ -283,6 +296,15 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         km.invHeight = 1.0f / float(m.height);
         km.positionScale = m.positionScale;
         km.positionLod = m.positionLod;
+        // Largest footprint a 32x4 tile can have in each grid: the tap index of the last column minus
+        // that of the first is at most floor(31 * grid / mip) + 1 (rows: 3), plus the second tap.
+        const int layers = p->numFeatures / 4;
+        km.strideShift = layers == 1 ? 3 : layers == 2 ? 4 : 5;
+        const long long capacity = kFootprintBytes >> km.strideShift;
+        auto footprint = [](int grid, int mip, int span) { return (long long)((long long)span * grid / mip) + 3; };
+        const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, kTileHeight - 1);
+        const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, kTileHeight - 1);
+        km.staged = (hiPixels <= capacity && loPixels <= capacity) ? 1 : 0;
         km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
         km.firstTile = int(tiles);
         tiles += (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
