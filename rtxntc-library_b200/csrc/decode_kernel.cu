@@ -1,9 +1,10 @@
 // NTC decode kernel for sm_100a: one launch decodes every listed colour mip of a texture set.
 //
-// Work decomposition.  A tile is 32x4 texels; one CTA of 128 threads owns one tile at a time
-// (thread = texel = one row of the tile's 128x{64,48,32,16} GEMM chain = one TMEM lane) and walks
-// the tile list of the whole mip chain with a grid stride.  Several CTAs are resident per SM, so
-// the SIMT phases of one tile overlap the tensor-core phases of the others.
+// Work decomposition.  A tile is 32x8 texels; one CTA of 256 threads owns one tile at a time
+// (thread = texel) and walks the tile list of the whole mip chain with a grid stride.  The tile is
+// two 128-row GEMM chains (rows 0-3 and rows 4-7 of the tile; a thread's texel is one row of its
+// half's 128x{64,48,32,16} chain and one TMEM lane), issued together.  Several CTAs are resident
+// per SM, so the SIMT phases of one tile overlap the tensor-core phases of the others.
 //
 // Per tile:
 //   1. every thread samples the two latent grids for its texel (packed BGRA4 pixels, nibble ->
@@ -328,20 +329,15 @@ struct __align__(16) TileTables
 struct __align__(16) SharedStorage
 {
     uint8_t network[kStagedNetworkBytes]; // weights in core-matrix order, scales, biases
-    uint8_t operandA[128 * 64];           // A operand of the current layer, core-matrix order
-    uint8_t footprint[2][kFootprintBytes]; // unpacked latents of the tile's footprint, per grid
+    uint8_t operandA[2 * kOperandBytes];  // A operands of the current layer (top half, bottom half), core-matrix order
+    uint8_t footprintHi[kFootprintHiBytes]; // unpacked latents of the tile's footprint in the high-res grid
+    uint8_t footprintLo[kFootprintLoBytes]; // ... and in the low-res grid
     uint32_t latentTable[256];            // byte (two nibbles) -> two binary16 latent values
     TileTables tables;
-    uint64_t barrier;
+    uint64_t barrier;                     // MMA completion
     uint32_t tmemBase;
 };
 
-struct TileContext
-{
-    int tid;
-    uint32_t tmemBase, tmemLane, barrier, operandA, networkBase;
-    int tile, x, y;
-};
 
 // One axis of the bilinear footprint (src/FeatureGridDevice.h:35-45): base tap index (before
 // wrapping) and the fractional offset of a texel coordinate in a latent grid of `size` pixels.
@@ -356,7 +352,7 @@ __device__ __forceinline__ void AxisTap(int texel, float invExtent, int size, in
 
 // Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory
 // (nibbles unpacked to binary16 once per latent pixel instead of once per texel and tap).
-// Warps 0 and 2 work on the high-res grid, warps 1 and 3 on the low-res grid.
+// Even warps work on the high-res grid, odd warps on the low-res grid.
 template <bool kFp8>
 __device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, SharedStorage& shared,
     int tileX0, int tileY0, int lane, int warp)
@@ -368,11 +364,11 @@ __device__ __forceinline__ void PrepareTile(const KernelParams& params, const Ke
     int xb, yb;
     float dx, dy;
     AxisTap(min(tileX0 + lane, mip.width - 1), mip.invWidth, gw, xb, dx);
-    AxisTap(min(tileY0 + (lane & 3), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
+    AxisTap(min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
     const int fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
     const int fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
     const int footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
-    const int footH = __shfl_sync(0xFFFFFFFFu, yb, 3) - fy0 + 2;
+    const int footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
 
     if (warp < 2)
     {
@@ -382,12 +378,12 @@ __device__ __forceinline__ void PrepareTile(const KernelParams& params, const Ke
         if (lane == 0)
             shared.tables.footWidth[grid] = footW;
     }
-    else
+    else if (warp < 4)
     {
         // positional encoding (src/RegressionKernels.h:59-85): warp 2 the x part per column, warp 3
         // the y part per row, quantised exactly as the per-texel inputs would be
         const bool rows = warp == 3;
-        const int coordinate = rows ? min(tileY0 + (lane & 3), mip.rowEnd - 1) : min(tileX0 + lane, mip.width - 1);
+        const int coordinate = rows ? min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1) : min(tileX0 + lane, mip.width - 1);
         float f = __fmul_rn(float(coordinate), mip.positionScale);
         uint32_t q[3];
 #pragma unroll
@@ -403,20 +399,20 @@ __device__ __forceinline__ void PrepareTile(const KernelParams& params, const Ke
             shared.tables.colEnc[lane] = enc;
         else if (lane < kTileHeight)
             shared.tables.rowEnc[lane] = enc;
-        if (rows && lane == 4)
+        if (rows && lane == kTileHeight)
             shared.tables.lodWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(mip.positionLod)),
                                                    QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
     }
 
     if (mip.staged)
     {
-        // footprint pixel p = fy * footW + fx, handed out over the 64 threads that share this grid
+        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
         const int count = footW * footH;
         const uint32_t magic = (1u << 20) / uint32_t(footW) + 1; // p / footW == (p * magic) >> 20 for p < 2048
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
-        uint8_t* foot = shared.footprint[grid];
-        for (int p = lane + 32 * (warp >> 1); p < count; p += 64)
+        uint8_t* foot = grid ? shared.footprintLo : shared.footprintHi;
+        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
         {
             const int fy = int((uint32_t(p) * magic) >> 20);
             const int fx = p - fy * footW;
@@ -464,10 +460,10 @@ __device__ __forceinline__ uint32_t BlendLayer(uint2 l00, uint2 l01, uint2 l10, 
 // Inputs 0..15 or 16..31 of one texel from the staged footprint of one grid.
 template <bool kFp8>
 __device__ __forceinline__ void GatherGrid(const KernelParams& params, const KernelMip& mip, const SharedStorage& shared,
-    int grid, int lane, int warp, uint32_t* words)
+    int grid, int lane, int tileRow, uint32_t* words)
 {
     const int4 col = shared.tables.colTap[grid][lane];
-    const int4 row = shared.tables.rowTap[grid][warp];
+    const int4 row = shared.tables.rowTap[grid][tileRow];
     const int footW = shared.tables.footWidth[grid];
     const float dx = __int_as_float(col.y), dxn = __int_as_float(col.z);
     const float dy = __int_as_float(row.y), dyn = __int_as_float(row.z);
@@ -478,7 +474,7 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
     const __half2 w10 = __low2half2(wBottom), w11 = __high2half2(wBottom);
 
     const int stride = 1 << mip.strideShift;
-    const uint8_t* tap00 = shared.footprint[grid] + (size_t(row.x * footW + col.x) << mip.strideShift);
+    const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (size_t(row.x * footW + col.x) << mip.strideShift);
     const uint8_t* tap10 = tap00 + (size_t(footW) << mip.strideShift);
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
@@ -494,11 +490,23 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
     }
 }
 
-// One layer of the MLP for the CTA's current tile: barrier, MMA issue, wait, then either the
-// activation + re-quantisation into the next A operand (layers 0-2) or the output epilogue
-// (layer 3).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
+struct TileContext
+{
+    int tid;
+    uint32_t tmemBase; // TMEM address of the CTA's accumulators: columns [0,64) top half, [64,128) bottom half
+    uint32_t tmemLane; // ... of this thread's half at this thread's lane
+    uint32_t barrier;  // shared address of the MMA-completion mbarrier
+    uint32_t operandA; // shared address of the A operands (top half, then bottom half)
+    uint4* rowChunk;   // this thread's 16-byte slot in chunk 0 of its half's A operand
+    uint32_t networkBase;
+    int tile, x, y;
+};
+
+// One layer of the MLP for the CTA's current tile: barrier, MMA issue (both halves), wait, then
+// either the activation + re-quantisation into the next A operand (layers 0-2) or the output
+// epilogue (layer 3).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
 template <bool kFp8, int kLayer>
-__device__ __forceinline__ int RunLayer(const KernelParams& params, const KernelMip& mip, SharedStorage& shared,
+__device__ __forceinline__ int RunLayer(const KernelParams& params, const KernelMip& mip, const SharedStorage& shared,
     const TileContext& ctx, uint32_t& phase, int& failed)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
@@ -506,26 +514,30 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
     constexpr int kWeightOffset =
         kLayer == 0 ? kWeightOffset0 : kLayer == 1 ? kWeightOffset1 : kLayer == 2 ? kWeightOffset2 : kWeightOffset3;
     constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
-    const int tid = ctx.tid;
 
-    // Makes the A operand written before this call visible to the tensor core, orders this thread's
-    // TMEM reads before the next MMA, and agrees on whether any thread gave up waiting.
+    // Makes the A operand written before this call visible to the tensor core, orders every
+    // thread's TMEM reads of the previous layer before the accumulators are overwritten, and agrees
+    // on whether any thread gave up waiting.
     FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
     if (__syncthreads_or(failed))
         return 1;
 
-    if (tid == 0)
+    if (ctx.tid == 0)
     {
         TcgenFenceAfterSync();
         constexpr uint32_t instr = MakeInstrDescriptor(kLayerFp8, kN);
 #pragma unroll
-        for (int kStep = 0; kStep < kK / 32; ++kStep)
+        for (int half = 0; half < 2; ++half)
         {
-            // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
-            uint64_t descA = MakeSmemDescriptor(ctx.operandA + kStep * 2 * 2048, 2048, 128);
-            uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
-            Umma<kLayerFp8>(ctx.tmemBase, descA, descB, instr, kStep != 0);
+#pragma unroll
+            for (int kStep = 0; kStep < kK / 32; ++kStep)
+            {
+                // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
+                uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes + kStep * 2 * 2048, 2048, 128);
+                uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
+                Umma<kLayerFp8>(ctx.tmemBase + half * kTmemColumnsPerHalf, descA, descB, instr, kStep != 0);
+            }
         }
         UmmaCommit(ctx.barrier);
     }
@@ -547,13 +559,13 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
     if (kLayer < 3)
     {
         constexpr bool kNextFp8 = kFp8 && kLayer < 2; // layer 2 always re-quantises to int8
-        uint4* rowChunk = reinterpret_cast<uint4*>(shared.operandA) + tid;
+        uint4* rowChunk = ctx.rowChunk;
         // 32 accumulator columns at a time keeps the register footprint small
 #pragma unroll
-        for (int half = 0; half < (kN + 31) / 32; ++half)
+        for (int part = 0; part < (kN + 31) / 32; ++part)
         {
             constexpr int kChunksTotal = kN / 16;
-            const int firstChunk = half * 2;
+            const int firstChunk = part * 2;
             uint32_t acc[2][16];
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -630,6 +642,64 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
     return 0;
 }
 
+// The 48 network inputs of one texel -> its 64-byte row of the A operand (K-major core matrices:
+// 16-byte chunk j of row r lives at j * 2048 + r * 16).
+template <bool kFp8>
+__device__ __forceinline__ void BuildInputs(const KernelParams& params, const KernelMip& mip, const SharedStorage& shared,
+    const TileContext& ctx, int lane, int tileRow)
+{
+    uint32_t words[16];
+    const uint32_t zeroWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(0.f)),
+                                              QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        words[i] = zeroWord; // unused feature slots hold quantised zeros (src/Inference.cu:49)
+#pragma unroll
+    for (int i = 12; i < 16; ++i)
+        words[i] = 0; // K padding
+
+    if (mip.staged)
+    {
+        GatherGrid<kFp8>(params, mip, shared, 0, lane, tileRow, words);
+        GatherGrid<kFp8>(params, mip, shared, 1, lane, tileRow, words + 4);
+    }
+    else
+    {
+        // footprint too large to stage (strong minification): read the taps from global memory;
+        // threads past the right / bottom edge compute a clamped texel and store nothing
+        const int xs = min(ctx.x, mip.width - 1);
+        const int ys = min(ctx.y, mip.rowEnd - 1);
+        // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
+        const float u = __fmul_rn(__fadd_rn(float(xs), 0.5f), mip.invWidth);
+        const float v = __fmul_rn(__fadd_rn(float(ys), 0.5f), mip.invHeight);
+        GridTaps taps;
+        SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
+        const uint16_t* hi = params.latents + mip.hiOffset;
+#pragma unroll
+        for (int layer = 0; layer < 4; ++layer)
+            if (layer < params.numLayers)
+                words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable);
+        SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
+        const uint16_t* lo = params.latents + mip.loOffset;
+#pragma unroll
+        for (int layer = 0; layer < 4; ++layer)
+            if (layer < params.numLayers)
+                words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable);
+    }
+
+    // positional encoding: interleave the column's x bytes with the row's y bytes
+    const uint2 cx = shared.tables.colEnc[lane];
+    const uint2 ry = shared.tables.rowEnc[tileRow];
+    words[8] = __byte_perm(cx.x, ry.x, 0x5140);
+    words[9] = __byte_perm(cx.x, ry.x, 0x7362);
+    words[10] = __byte_perm(cx.y, ry.y, 0x5140);
+    words[11] = shared.tables.lodWord;
+
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk)
+        ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
+}
+
 template <bool kFp8>
 __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8) DecodeKernel(const __grid_constant__ KernelParams params)
 {
@@ -637,7 +707,8 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
-    const int warp = tid >> 5;
+    const int warp = tid >> 5;      // = the thread's row of the tile
+    const int half = warp >> 2;     // 0: rows 0-3 of the tile, 1: rows 4-7
 
     // ---- one-time setup -----------------------------------------------------------------
     {
@@ -672,9 +743,11 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
     TileContext ctx;
     ctx.tid = tid;
     ctx.tmemBase = tmemBase;
-    ctx.tmemLane = tmemBase + (uint32_t(warp * 32) << 16);
+    // a warp may only touch the TMEM lanes 32 * (warp % 4) .. + 31
+    ctx.tmemLane = tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
     ctx.barrier = SharedAddress(&shared.barrier);
     ctx.operandA = SharedAddress(shared.operandA);
+    ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
 
     int mipIndex = 0;
@@ -689,70 +762,17 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
         const int tileX = local - tileY * mip.tilesX;
         const int tileX0 = tileX * kTileWidth;
         const int tileY0 = mip.rowBegin + tileY * kTileHeight;
-        const int x = tileX0 + lane;
-        const int y = tileY0 + warp;
         ctx.tile = tile;
-        ctx.x = x;
-        ctx.y = y;
+        ctx.x = tileX0 + lane;
+        ctx.y = tileY0 + warp;
 
-        // ---- 1. network inputs -> A operand ----------------------------------------------
-        // The tables and footprints of the previous tile were last read before that tile's first
-        // layer barrier, so they may be overwritten here.
+        // ---- 1. tables and latent footprints of the tile, then the A operand -----------------
+        // The previous tile's tables and footprints were last read before its first layer
+        // barrier, so they may be overwritten here; its A operand was last read by its last MMA,
+        // which every thread has waited for.
         PrepareTile<kFp8>(params, mip, shared, tileX0, tileY0, lane, warp);
         __syncthreads();
-        {
-            uint32_t words[16];
-            const uint32_t zeroWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(0.f)),
-                                                      QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                words[i] = zeroWord; // unused feature slots hold quantised zeros (src/Inference.cu:49)
-#pragma unroll
-            for (int i = 12; i < 16; ++i)
-                words[i] = 0; // K padding
-
-            if (mip.staged)
-            {
-                GatherGrid<kFp8>(params, mip, shared, 0, lane, warp, words);
-                GatherGrid<kFp8>(params, mip, shared, 1, lane, warp, words + 4);
-            }
-            else
-            {
-                // footprint too large to stage (strong minification): read the taps from global memory
-                // threads past the right / bottom edge compute a clamped texel and store nothing
-                const int xs = min(x, mip.width - 1);
-                const int ys = min(y, mip.rowEnd - 1);
-                // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
-                const float u = __fmul_rn(__fadd_rn(float(xs), 0.5f), mip.invWidth);
-                const float v = __fmul_rn(__fadd_rn(float(ys), 0.5f), mip.invHeight);
-                GridTaps taps;
-                SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
-                const uint16_t* hi = params.latents + mip.hiOffset;
-#pragma unroll
-                for (int layer = 0; layer < 4; ++layer)
-                    if (layer < params.numLayers)
-                        words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable);
-                SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
-                const uint16_t* lo = params.latents + mip.loOffset;
-#pragma unroll
-                for (int layer = 0; layer < 4; ++layer)
-                    if (layer < params.numLayers)
-                        words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable);
-            }
-
-            // positional encoding: interleave the column's x bytes with the row's y bytes
-            const uint2 cx = shared.tables.colEnc[lane];
-            const uint2 ry = shared.tables.rowEnc[warp];
-            words[8] = __byte_perm(cx.x, ry.x, 0x5140);
-            words[9] = __byte_perm(cx.x, ry.x, 0x7362);
-            words[10] = __byte_perm(cx.y, ry.y, 0x5140);
-            words[11] = shared.tables.lodWord;
-
-            uint4* rowChunk = reinterpret_cast<uint4*>(shared.operandA) + tid;
-#pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk)
-                rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
-        }
+        BuildInputs<kFp8>(params, mip, shared, ctx, lane, warp);
 
         // ---- 2./3./4. the four layers ------------------------------------------------------
         aborted = RunLayer<kFp8, 0>(params, mip, shared, ctx, phase, failed);
@@ -761,10 +781,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
         if (!aborted) aborted = RunLayer<kFp8, 3>(params, mip, shared, ctx, phase, failed);
         if (aborted)
             break;
-        // No barrier is needed here: the next tile's preparation writes tables and footprints that
-        // were last read before this tile's first layer barrier, and its A operand is written after
-        // the barrier that follows the preparation; the last MMA of this tile (already complete) was
-        // the last reader of the A operand.
     }
 
     // ---- teardown -------------------------------------------------------------------------

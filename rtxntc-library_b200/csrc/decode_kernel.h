@@ -9,13 +9,16 @@ namespace ntcb
 {
 
 constexpr int kTileWidth = 32;
-constexpr int kTileHeight = 4;
+constexpr int kTileHeight = 8;      // a tile is two 32x4 halves, each a 128-row GEMM chain
 constexpr int kThreadsPerCta = kTileWidth * kTileHeight; // one thread per texel of a tile
-constexpr int kCtasPerSmInt8 = 5;  // resident CTAs per SM the two kernel variants are compiled for
-constexpr int kCtasPerSmFp8 = 6;
-constexpr int kTmemColumns = 64;           // widest accumulator (layer 0: 64 outputs)
+constexpr int kOperandBytes = 128 * 64; // A operand of one half: 128 rows x 64 bytes
+constexpr int kCtasPerSmInt8 = 3;  // resident CTAs per SM the two kernel variants are compiled for
+constexpr int kCtasPerSmFp8 = 4;
+constexpr int kTmemColumnsPerHalf = 64;    // widest accumulator (layer 0: 64 outputs)
+constexpr int kTmemColumns = 2 * kTmemColumnsPerHalf;
 constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait is declared expired
-constexpr int kFootprintBytes = 6656;      // shared memory per latent grid for a tile's unpacked footprint
+constexpr int kFootprintHiBytes = 11264;   // shared memory for a tile's unpacked footprint in the high-res grid
+constexpr int kFootprintLoBytes = 4096;    // ... and in the low-res grid (half the resolution)
 
 // Image of the network in shared memory (produced on the host by ntcb_stage_network).
 // Weight matrix of layer l: N_l rows (outputs) x K_l bytes (inputs, padded to a multiple of 32) in

@@ -296,15 +296,15 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         km.invHeight = 1.0f / float(m.height);
         km.positionScale = m.positionScale;
         km.positionLod = m.positionLod;
-        // Largest footprint a 32x4 tile can have in each grid: the tap index of the last column minus
-        // that of the first is at most floor(31 * grid / mip) + 1 (rows: 3), plus the second tap.
+        // Largest footprint a tile can have in each grid: the tap index of the last column (row) minus
+        // that of the first is at most floor(31 (7) * grid / mip) + 1, plus the second tap.
         const int layers = p->numFeatures / 4;
         km.strideShift = layers == 1 ? 3 : layers == 2 ? 4 : 5;
-        const long long capacity = kFootprintBytes >> km.strideShift;
+        const long long hiCapacity = kFootprintHiBytes >> km.strideShift, loCapacity = kFootprintLoBytes >> km.strideShift;
         auto footprint = [](int grid, int mip, int span) { return (long long)((long long)span * grid / mip) + 3; };
         const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, kTileHeight - 1);
         const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, kTileHeight - 1);
-        km.staged = (hiPixels <= capacity && loPixels <= capacity) ? 1 : 0;
+        km.staged = (hiPixels <= hiCapacity && loPixels <= loCapacity) ? 1 : 0;
         km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
         km.firstTile = int(tiles);
         tiles += (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
