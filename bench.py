@@ -48,8 +48,8 @@ WORKLOAD = ("PBR texture set 4096x4096, 12 channels, 13 mips, latent shape {grid
             "FP8 e4m3 hidden layers + int8 output layer")
 
 # DRAM bytes per launch of the decode kernel on this workload (dram__bytes_read.sum +
-# dram__bytes_write.sum from the ncu capture summarised in profiles/); None until captured.
-MEASURED_TRAFFIC_BYTES = None
+# dram__bytes_write.sum from the ncu capture summarised in profiles/).
+MEASURED_TRAFFIC_BYTES = 492.5e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
 
 
 def measured_peak_gbs():
