@@ -408,7 +408,8 @@ __device__ __forceinline__ void PrepareTile(const KernelParams& params, const Ke
     {
         // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
         const int count = footW * footH;
-        const uint32_t magic = (1u << 20) / uint32_t(footW) + 1; // p / footW == (p * magic) >> 20 for p < 2048
+        // p / footW == (p * magic) >> 20 for p < 2048; the IEEE quotient of 2^20 / footW floors exactly
+        const uint32_t magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
         uint8_t* foot = grid ? shared.footprintLo : shared.footprintHi;
@@ -468,10 +469,9 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
     const float dx = __int_as_float(col.y), dxn = __int_as_float(col.z);
     const float dy = __int_as_float(row.y), dyn = __int_as_float(row.z);
     // src/FeatureGridDevice.h:46-49
-    const __half2 wTop = __floats2half2_rn(__fmul_rn(dxn, dyn), __fmul_rn(dx, dyn));
-    const __half2 wBottom = __floats2half2_rn(__fmul_rn(dxn, dy), __fmul_rn(dx, dy));
-    const __half2 w00 = __low2half2(wTop), w01 = __high2half2(wTop);
-    const __half2 w10 = __low2half2(wBottom), w11 = __high2half2(wBottom);
+    const float f00 = __fmul_rn(dxn, dyn), f01 = __fmul_rn(dx, dyn), f10 = __fmul_rn(dxn, dy), f11 = __fmul_rn(dx, dy);
+    const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
+    const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
 
     const int stride = 1 << mip.strideShift;
     const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (size_t(row.x * footW + col.x) << mip.strideShift);
@@ -612,10 +612,9 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
         uint32_t acc[16];
         TmemLoad16(ctx.tmemLane, acc);
         TmemLoadWait();
-        const int x = ctx.x, y = ctx.y;
         const int channelPairs = params.channels >> 1;
-        const bool inside = x < mip.width && y < mip.rowEnd;
-        __half* out = params.out + mip.outOffset;
+        uint32_t bits[8];
+        uint32_t special = 0; // bit 15 / 31 set when a value has an all-ones exponent
 #pragma unroll
         for (int j = 0; j < 8; ++j)
         {
@@ -623,20 +622,38 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
             {
                 float f0 = __fmul_rn(float(int32_t(acc[2 * j]) + biasI[2 * j]), scale[2 * j]);
                 float f1 = __fmul_rn(float(int32_t(acc[2 * j + 1]) + biasI[2 * j + 1]), scale[2 * j + 1]);
-                uint32_t bits = AsU32(__floats2half2_rn(f0, f1));
-                // Inf / NaN -> 0 (src/CudaUtils.h:30-35)
-                if ((bits & 0x7C00u) == 0x7C00u) bits &= 0xFFFF0000u;
-                if ((bits & 0x7C000000u) == 0x7C000000u) bits &= 0x0000FFFFu;
-                if (inside)
+                bits[j] = AsU32(__floats2half2_rn(f0, f1));
+                special |= (bits[j] & 0x7C007C00u) + 0x04000400u;
+            }
+        }
+        if (special & 0x80008000u)
+        {
+            // Inf / NaN -> 0 (src/CudaUtils.h:30-35); rare, so kept off the common path
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+            {
+                if (j < channelPairs)
                 {
-                    size_t index;
-                    if (params.outputLayout == kLayoutPlanarPairs)
-                        index = (size_t(y) * mip.width * channelPairs + size_t(j) * mip.width + x) * 2;
-                    else
-                        index = (size_t(y) * mip.width + x) * params.channels + 2 * j;
-                    *reinterpret_cast<uint32_t*>(out + index) = bits;
+                    if ((bits[j] & 0x7C00u) == 0x7C00u) bits[j] &= 0xFFFF0000u;
+                    if ((bits[j] & 0x7C000000u) == 0x7C000000u) bits[j] &= 0x0000FFFFu;
                 }
             }
+        }
+        if (ctx.x < mip.width && ctx.y < mip.rowEnd)
+        {
+            // element index inside the mip fits 32 bits (at most 2^14 x 2^14 texels x 16 channels would
+            // not, but the format's 16 mips x 16 channels at 8192^2 is 2^30)
+            const bool planar = params.outputLayout == kLayoutPlanarPairs;
+            const uint32_t texel = uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x);
+            const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
+                                          : texel * uint32_t(params.channels);
+            const uint32_t step = planar ? 2u * uint32_t(mip.width) : 2u; // elements between channel pairs
+            uint32_t* out = reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first);
+            const uint32_t stepWords = step >> 1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j < channelPairs)
+                    out[j * stepWords] = bits[j];
         }
     }
     return 0;
@@ -758,7 +775,8 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
             ++mipIndex;
         const KernelMip& mip = params.mips[mipIndex];
         const int local = tile - mip.firstTile;
-        const int tileY = local / mip.tilesX;
+        // local / tilesX through a precomputed reciprocal (exact while local * tilesX < 2^32)
+        const int tileY = mip.tilesX == 1 ? local : int(__umulhi(uint32_t(local), mip.tilesXMagic));
         const int tileX = local - tileY * mip.tilesX;
         const int tileX0 = tileX * kTileWidth;
         const int tileY0 = mip.rowBegin + tileY * kTileHeight;

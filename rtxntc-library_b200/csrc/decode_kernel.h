@@ -46,6 +46,7 @@ struct KernelMip
     float invWidth, invHeight;
     float positionScale, positionLod;
     int firstTile, tilesX;
+    unsigned tilesXMagic; // ceil(2^32 / tilesX) for tilesX > 1: local / tilesX == umulhi(local, magic) while local * tilesX < 2^32
     int staged;      // the tile footprints of both grids fit into shared memory
     int strideShift; // log2 of the bytes per staged latent pixel (8 bytes per layer, rounded up to a power of two)
 };

@@ -306,8 +306,15 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, kTileHeight - 1);
         km.staged = (hiPixels <= hiCapacity && loPixels <= loCapacity) ? 1 : 0;
         km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
+        km.tilesXMagic = km.tilesX == 1 ? 0u : unsigned((0x100000000ull + km.tilesX - 1) / km.tilesX);
         km.firstTile = int(tiles);
-        tiles += (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
+        const long long mipTiles = (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
+        if (mipTiles * km.tilesX >= 0x100000000ll)
+        {
+            SetError("ntcb_decode: mip %d is too large for one launch.", i);
+            return NTCB_ERR_OUT_OF_RANGE;
+        }
+        tiles += mipTiles;
         if (tiles > 0x7FFFFFFF)
         {
             SetError("ntcb_decode: too many tiles for one launch.");
