@@ -19,6 +19,10 @@ The JSON line reports
   roofline  algorithmic bytes of one launch / its mean duration against the measured HBM copy peak;
   cpu_baseline  the scalar CPU restatement of the same arithmetic on this machine's cores.
 
+`--config 0|2|3` time the other benchmark configurations (1024^2 single mip; 64 sets of 2048^2
+sharded by set; 8192^2 sharded by tile rows - the last two split a fixed job over the ranks, strong
+scaling); they report the device-resident figure only.
+
 The reference arm runs the reference's own CUDA decoder (LibNTC has no CPU decoder) through its
 public API on the same GPU and reports the end-to-end figure as its value, so that the two arms'
 `e2e` values compare like with like; its kernel-only figure is given beside it.
@@ -76,7 +80,7 @@ class ClockSampler:
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.process = None
 
@@ -172,102 +176,164 @@ def cpu_baseline(synthetic_set) -> dict:
             "sample": "rows 0..%d of mip 0 (%d texels, %.1f s)" % (rows - 1, texels, elapsed)}
 
 
+WORKLOADS = {
+    0: "single texture set 1024x1024, 4 channels, mip 0 only, latent shape {2, 8 features}, int8 weights",
+    1: WORKLOAD,
+    2: "64 texture sets 2048x2048, 8 channels, 12 mips each, latent shape {4, 8 features}, int8 weights, sharded by set",
+    3: "texture set 8192x8192, 16 channels, 14 mips, latent shape {4, 16 features}, int8 weights, sharded by tile rows",
+}
+
+
+def build_launches(config: int, rank: int, world: int, device, binding, synthetic, sharding):
+    """The decode launches one rank issues per step: [(resident set, params)], the texels they
+    produce on this rank, the texels of the whole job, algorithmic bytes of this rank's step and
+    the synthetic set used for the CPU baseline."""
+    launches, texels, alg_bytes = [], 0, 0
+    if config in (0, 1):
+        spec = synthetic.config_spec(config)
+        spec.seed += 1000 * rank  # every rank decodes its own texture set (weak scaling)
+        data = synthetic.make_texture_set(spec)
+        resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device))
+        launches.append((resident, resident.params(data.use_int8)))
+        texels = data.geometry.total_texels
+        alg_bytes = texels * data.geometry.channels * 2 + data.geometry.encoded_latent_bytes + binding.STAGED_NETWORK_BYTES
+        return launches, texels, texels * world, alg_bytes, data, "weak"
+    if config == 2:
+        specs = [synthetic.config_spec(2, i) for i in range(64)]
+        geometries = [spec.geometry() for spec in specs]
+        plan = sharding.plan_batch(geometries, world)[rank]
+        by_set = {}
+        for unit in plan:
+            by_set.setdefault(unit.set_index, set()).update(unit.mips)
+        first = None
+        for index, mips in sorted(by_set.items()):
+            data = synthetic.make_texture_set(specs[index])
+            first = first or data
+            resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device))
+            launches.append((resident, resident.params(True, mips=sorted(mips))))
+            done = sum(data.geometry.color_mips[m].width * data.geometry.color_mips[m].height for m in mips)
+            texels += done
+            alg_bytes += done * data.geometry.channels * 2 + data.geometry.encoded_latent_bytes + binding.STAGED_NETWORK_BYTES
+        return launches, texels, sum(g.total_texels for g in geometries), alg_bytes, first, "strong"
+    if config == 3:
+        data = synthetic.make_texture_set(synthetic.config_spec(3))
+        geo = data.geometry
+        ranges = sharding.plan_rows(geo, world)[rank]
+        resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device))
+        mips = [m for m, (b, e) in enumerate(ranges) if e > b]
+        launches.append((resident, resident.params(True, mips=mips, row_ranges={m: ranges[m] for m in mips})))
+        texels = sharding.texels_of_rows(geo, ranges)
+        alg_bytes = texels * geo.channels * 2 + geo.encoded_latent_bytes + binding.STAGED_NETWORK_BYTES
+        return launches, texels, geo.total_texels, alg_bytes, data, "strong"
+    raise ValueError("unknown configuration")
+
+
 def run_ours(args) -> dict:
     import torch
 
     entry.load_package()
-    from rtxntc_library_b200 import binding, synthetic
+    from rtxntc_library_b200 import binding, sharding, synthetic
 
     rank, local_rank, world, dist = dist_setup(args.gpus)
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
 
-    spec = synthetic.config_spec(1)
-    spec.seed = 1 + 1000 * rank  # every rank decodes its own texture set
-    data = synthetic.make_texture_set(spec)
+    launches, texels, job_texels, algorithmic_bytes, data, scaling = build_launches(
+        args.config, rank, world, device, binding, synthetic, sharding)
     geo = data.geometry
-    texels = geo.total_texels
     use_int8 = data.use_int8
 
     # ---- device-resident throughput -------------------------------------------------------
-    resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device))
-    params = resident.params(use_int8)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
-    for _ in range(args.warmup):
-        resident.launch(params)
-    torch.cuda.synchronize()
-    resident.check_status()
 
+    def step():
+        for resident, params in launches:
+            resident.launch(params)
+
+    # nvidia-smi needs a moment before its first sample: start it ahead of the warm-up so that the
+    # (short) timed region is covered
     sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.5)
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    for resident, _ in launches:
+        resident.check_status()
+
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     launches_before = binding.lib().ntcb_launch_count()
     barrier_sync(dist, torch)
-    if rank == 0:
-        sampler.start()
     wall_start = time.perf_counter()
-    for step in range(args.steps):
-        flush.fill_(step & 0xFF)  # evict L2 between steps (not inside the per-step events)
-        starts[step].record()
-        resident.launch(params)
-        stops[step].record()
+    for index in range(args.steps):
+        flush.fill_(index & 0xFF)  # evict L2 between steps (not inside the per-step events)
+        starts[index].record()
+        step()
+        stops[index].record()
     barrier_sync(dist, torch)
     wall = time.perf_counter() - wall_start
     clocks = sampler.stop() if rank == 0 else None
-    launches = binding.lib().ntcb_launch_count() - launches_before
-    resident.check_status()
+    launch_count = binding.lib().ntcb_launch_count() - launches_before
+    for resident, _ in launches:
+        resident.check_status()
     step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
     device_seconds = reduce_max(dist, torch, sum(step_ms) / 1e3, device)
-    total_launches = int(reduce_sum(dist, torch, float(launches), device))
-    value = world * texels * args.steps / device_seconds / 1e9
+    total_launches = int(reduce_sum(dist, torch, float(launch_count), device))
+    value = job_texels * args.steps / device_seconds / 1e9
 
     # ---- end to end through the texture-set API with host buffers ---------------------------
-    del resident, flush
-    torch.cuda.empty_cache()
-    context = binding.Context(local_rank)
-    texture_set = context.create_texture_set(data.container)
-    host_out = torch.empty(texels * geo.channels, dtype=torch.float16).pin_memory()
-    base = host_out.data_ptr()
+    e2e = None
+    if args.config in (0, 1):
+        launches.clear()
+        del flush
+        torch.cuda.empty_cache()
+        context = binding.Context(local_rank)
+        texture_set = context.create_texture_set(data.container)
+        host_out = torch.empty(texels * geo.channels, dtype=torch.float16).pin_memory()
+        base = host_out.data_ptr()
 
-    def e2e_step():
-        texture_set.decompress(use_int8)
-        for mip, cm in enumerate(geo.color_mips):
-            texture_set.read_channels_into(mip, base + cm.texel_offset * geo.channels * 2)
+        def e2e_step():
+            texture_set.decompress(use_int8)
+            for mip, cm in enumerate(geo.color_mips):
+                texture_set.read_channels_into(mip, base + cm.texel_offset * geo.channels * 2)
 
-    for _ in range(max(1, min(args.warmup, 3))):
-        e2e_step()
-    barrier_sync(dist, torch)
-    e2e_start = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    texture_set.synchronize()
-    e2e_seconds = reduce_max(dist, torch, time.perf_counter() - e2e_start, device)
-    barrier_sync(dist, torch)
-    e2e_value = world * texels * args.steps / e2e_seconds / 1e9
-    h2d = geo.encoded_latent_bytes + 2 * binding.STAGED_NETWORK_BYTES
-    d2h = texels * geo.channels * 2
-    texture_set.close()
-    context.close()
+        for _ in range(max(1, min(args.warmup, 3))):
+            e2e_step()
+        barrier_sync(dist, torch)
+        e2e_start = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        texture_set.synchronize()
+        e2e_seconds = reduce_max(dist, torch, time.perf_counter() - e2e_start, device)
+        barrier_sync(dist, torch)
+        e2e = {"value": world * texels * args.steps / e2e_seconds / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": geo.encoded_latent_bytes + 2 * binding.STAGED_NETWORK_BYTES,
+               "d2h_bytes_per_step": texels * geo.channels * 2}
+        texture_set.close()
+        context.close()
 
-    # ---- roofline of the decode kernel -----------------------------------------------------
+    # ---- roofline of the decode kernel (this rank's launches of one step) ---------------------
     peak, peak_kind = measured_peak_gbs()
-    algorithmic_bytes = texels * geo.channels * 2 + geo.encoded_latent_bytes + binding.STAGED_NETWORK_BYTES
-    launch_seconds = statistics.mean(step_ms) / 1e3
-    achieved = algorithmic_bytes / launch_seconds / 1e9
+    step_seconds = statistics.mean(step_ms) / 1e3
+    achieved = algorithmic_bytes / step_seconds / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": MEASURED_TRAFFIC_BYTES, "peak_source": "%s copy bandwidth" % peak_kind,
-                "algorithmic_bytes_per_launch": algorithmic_bytes}
-
+                "traffic": MEASURED_TRAFFIC_BYTES if args.config == 1 else None,
+                "peak_source": "%s copy bandwidth" % peak_kind, "algorithmic_bytes_per_step": algorithmic_bytes,
+                "launches_per_step": len(step_ms) and launch_count // max(1, args.steps)}
+    dtype = ("fp8_e4m3 x fp8_e4m3 -> f32 (layers 0-2), s8 x s8 -> s32 (layer 3), f16 activations" if not use_int8
+             else "s8 x s8 -> s32 (all layers), f16 activations")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": device_seconds * 1e3 / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (layers 0-2), s8 x s8 -> s32 (layer 3), f16 activations",
+        "ms_per_step": device_seconds * 1e3 / args.steps, "higher_is_better": True, "scaling": scaling,
+        "vs_baseline": None, "dtype": dtype,
         "data": "synthetic (seeded latents and weights of the configuration's shape)",
-        "config": {"workload": WORKLOAD, "texels_per_step_per_gpu": texels, "texture_sets": world,
-                   "parallelism": "one texture set per GPU, no collective", "launches_per_step": 1,
-                   "l2": "256 MiB written between steps, outside the per-step events; the 537 MB output also exceeds L2"},
-        "clocks": clocks, "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": total_launches, "roofline": roofline, "wall_seconds_timed_region": wall,
+        "config": {"workload": WORKLOADS[args.config], "texels_per_step": job_texels, "texels_per_step_this_rank": texels,
+                   "parallelism": "sharded by texture set / tile rows, no collective",
+                   "l2": "256 MiB written between steps, outside the per-step events; each step's output also exceeds L2"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": total_launches, "roofline": roofline,
+        "wall_seconds_timed_region": wall,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(data)
@@ -312,6 +378,7 @@ def run_reference(args) -> dict:
     sampler = ClockSampler(0)
     torch.cuda.synchronize()
     sampler.start()
+    time.sleep(0.5)
     start = time.perf_counter()
     for _ in range(args.steps):
         step()
@@ -342,10 +409,12 @@ def run_reference(args) -> dict:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3],
+                        help="benchmark configuration; 1 (the default) is the one the metric is quoted on")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     line = run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -3,4 +3,4 @@
 The directory name is not a Python identifier; load it with `__graft_entry__.load_package()` (or
 importlib) under the module name `rtxntc_library_b200`.
 """
-from . import container, geometry, synthetic  # noqa: F401
+from . import container, geometry, sharding, synthetic  # noqa: F401
