@@ -116,6 +116,31 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
    Asynchronous; the caller synchronises and may then read `status`.  Allocates nothing. */
 int ntcb_decode(const NtcbDecodeParams* params, void* stream);
 
+/* Inference on sample: evaluates individual texels instead of whole mips.  Query q is
+   (u, v, lod) = queries[3q .. 3q+2]; it selects mip = clamp(floor(lod), 0, numMips - 1) and the texel
+   x = min(floor(u * width), width - 1), y = min(floor(v * height), height - 1) of that mip, which is
+   decoded exactly as ntcb_decode would decode it; out[q * channels + c] receives the fp16 channels.
+   The reference exposes this only to shaders, as NtcSampleTextureSet(texel, mipLevel)
+   (include/libntc/shaders/Inference.hlsli:282-357) fed by IContext::MakeInferenceData
+   (src/Context.cpp:864-922); the (u, v, lod) -> (texel, mip) rule above is this library's. */
+typedef struct NtcbSampleParams
+{
+    const uint16_t* latents; /* device, as in NtcbDecodeParams */
+    const void* network;     /* device, as in NtcbDecodeParams */
+    const float* queries;    /* device: numQueries x 3 floats */
+    void* out;               /* device: numQueries x channels fp16 */
+    uint32_t* status;        /* device: NTCB_STATUS_WORDS zeroed words */
+    uint64_t numQueries;
+    int32_t numMips;
+    int32_t numFeatures;
+    int32_t channels;
+    int32_t weightMode;
+    NtcbMipDesc mips[NTCB_MAX_MIPS]; /* outOffset, rowBegin and rowEnd are ignored */
+} NtcbSampleParams;
+
+/* One kernel launch on `stream` for all queries.  Asynchronous; allocates nothing. */
+int ntcb_sample(const NtcbSampleParams* params, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Texture-set level: the same path as the reference's host objects drive it.
  * ------------------------------------------------------------------------------------------ */

@@ -44,6 +44,13 @@ class DecodeParams(ctypes.Structure):
                 ("mips", MipDesc * MAX_MIPS)]
 
 
+class SampleParams(ctypes.Structure):
+    _fields_ = [("latents", ctypes.c_void_p), ("network", ctypes.c_void_p), ("queries", ctypes.c_void_p),
+                ("out", ctypes.c_void_p), ("status", ctypes.c_void_p), ("numQueries", ctypes.c_uint64),
+                ("numMips", ctypes.c_int32), ("numFeatures", ctypes.c_int32), ("channels", ctypes.c_int32),
+                ("weightMode", ctypes.c_int32), ("mips", MipDesc * MAX_MIPS)]
+
+
 class TextureSetDesc(ctypes.Structure):
     _fields_ = [("width", ctypes.c_int32), ("height", ctypes.c_int32), ("channels", ctypes.c_int32),
                 ("mips", ctypes.c_int32), ("gridSizeScale", ctypes.c_int32), ("numFeatures", ctypes.c_int32),
@@ -92,6 +99,7 @@ def lib():
         handle.ntcb_launch_count.restype = ctypes.c_uint64
         handle.ntcb_stage_network.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
+        handle.ntcb_sample.argtypes = [ctypes.POINTER(SampleParams), ctypes.c_void_p]
         handle.ntcb_decode_resident_ctas.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         handle.ntcb_probe_container.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetDesc)]
         handle.ntcb_context_create.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]
@@ -215,6 +223,27 @@ class ResidentTextureSet:
     def decode(self, use_int8: bool, mips=None, row_ranges=None) -> None:
         with self.torch.cuda.device(self.device):
             self.launch(self.params(use_int8, mips=mips, row_ranges=row_ranges))
+
+    def sample(self, queries, use_int8: bool):
+        """Inference on sample: `queries` is a float32 CUDA tensor [n][3] of (u, v, lod); returns a
+        float16 CUDA tensor [n][channels].  Queued on torch's current stream."""
+        torch = self.torch
+        mode = WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8
+        queries = queries.contiguous()
+        out = torch.empty((queries.shape[0], self.geometry.channels), dtype=torch.float16, device=self.device)
+        decode = fill_params(self.geometry, self.latents.data_ptr(), self.networks[mode].data_ptr(), out.data_ptr(),
+                             self.status.data_ptr(), mode)
+        params = SampleParams()
+        params.latents, params.network, params.queries = decode.latents, decode.network, queries.data_ptr()
+        params.out, params.status, params.numQueries = out.data_ptr(), decode.status, queries.shape[0]
+        params.numMips, params.numFeatures, params.channels = decode.numMips, decode.numFeatures, decode.channels
+        params.weightMode = mode
+        for i in range(decode.numMips):
+            params.mips[i] = decode.mips[i]
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            check(lib().ntcb_sample(ctypes.byref(params), ctypes.c_void_p(stream)))
+        return out
 
     def check_status(self) -> None:
         words = self.status.cpu().numpy()

@@ -500,13 +500,15 @@ struct TileContext
     uint4* rowChunk;   // this thread's 16-byte slot in chunk 0 of its half's A operand
     uint32_t networkBase;
     int tile, x, y;
+    uint32_t* out;          // where this thread's first channel pair goes (nullptr: store nothing)
+    uint32_t outStepWords;  // 32-bit words between consecutive channel pairs
 };
 
 // One layer of the MLP for the CTA's current tile: barrier, MMA issue (both halves), wait, then
 // either the activation + re-quantisation into the next A operand (layers 0-2) or the output
 // epilogue (layer 3).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
 template <bool kFp8, int kLayer>
-__device__ __forceinline__ int RunLayer(const KernelParams& params, const KernelMip& mip, const SharedStorage& shared,
+__device__ __forceinline__ int RunLayer(uint32_t* status, int channels, const SharedStorage& shared,
     const TileContext& ctx, uint32_t& phase, int& failed)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
@@ -545,9 +547,9 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
     if (!MbarrierWaitBounded(ctx.barrier, phase))
     {
         failed = 1;
-        params.status[0] = kStatusBarrierTimeout;
-        params.status[1] = uint32_t(ctx.tile);
-        params.status[2] = uint32_t(kLayer);
+        status[0] = kStatusBarrierTimeout;
+        status[1] = uint32_t(ctx.tile);
+        status[2] = uint32_t(kLayer);
     }
     phase ^= 1;
     TcgenFenceAfterSync();
@@ -612,7 +614,7 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
         uint32_t acc[16];
         TmemLoad16(ctx.tmemLane, acc);
         TmemLoadWait();
-        const int channelPairs = params.channels >> 1;
+        const int channelPairs = channels >> 1;
         uint32_t bits[8];
         uint32_t special = 0; // bit 15 / 31 set when a value has an all-ones exponent
 #pragma unroll
@@ -639,24 +641,38 @@ __device__ __forceinline__ int RunLayer(const KernelParams& params, const Kernel
                 }
             }
         }
-        if (ctx.x < mip.width && ctx.y < mip.rowEnd)
+        if (ctx.out)
         {
-            // element index inside the mip fits 32 bits (at most 2^14 x 2^14 texels x 16 channels would
-            // not, but the format's 16 mips x 16 channels at 8192^2 is 2^30)
-            const bool planar = params.outputLayout == kLayoutPlanarPairs;
-            const uint32_t texel = uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x);
-            const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
-                                          : texel * uint32_t(params.channels);
-            const uint32_t step = planar ? 2u * uint32_t(mip.width) : 2u; // elements between channel pairs
-            uint32_t* out = reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first);
-            const uint32_t stepWords = step >> 1;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 if (j < channelPairs)
-                    out[j * stepWords] = bits[j];
+                    ctx.out[j * ctx.outStepWords] = bits[j];
         }
     }
     return 0;
+}
+
+// Inputs 0..31 of one texel with the taps read straight from global memory.
+template <bool kFp8>
+__device__ __forceinline__ void SampleGridsDirect(const uint16_t* __restrict__ latents, int numLayers, const KernelMip& mip,
+    int x, int y, const uint32_t* __restrict__ latentTable, uint32_t* words)
+{
+    // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
+    const float u = __fmul_rn(__fadd_rn(float(x), 0.5f), mip.invWidth);
+    const float v = __fmul_rn(__fadd_rn(float(y), 0.5f), mip.invHeight);
+    GridTaps taps;
+    SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
+    const uint16_t* hi = latents + mip.hiOffset;
+#pragma unroll
+    for (int layer = 0; layer < 4; ++layer)
+        if (layer < numLayers)
+            words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, latentTable);
+    SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
+    const uint16_t* lo = latents + mip.loOffset;
+#pragma unroll
+    for (int layer = 0; layer < 4; ++layer)
+        if (layer < numLayers)
+            words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, latentTable);
 }
 
 // The 48 network inputs of one texel -> its 64-byte row of the A operand (K-major core matrices:
@@ -684,24 +700,8 @@ __device__ __forceinline__ void BuildInputs(const KernelParams& params, const Ke
     {
         // footprint too large to stage (strong minification): read the taps from global memory;
         // threads past the right / bottom edge compute a clamped texel and store nothing
-        const int xs = min(ctx.x, mip.width - 1);
-        const int ys = min(ctx.y, mip.rowEnd - 1);
-        // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
-        const float u = __fmul_rn(__fadd_rn(float(xs), 0.5f), mip.invWidth);
-        const float v = __fmul_rn(__fadd_rn(float(ys), 0.5f), mip.invHeight);
-        GridTaps taps;
-        SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
-        const uint16_t* hi = params.latents + mip.hiOffset;
-#pragma unroll
-        for (int layer = 0; layer < 4; ++layer)
-            if (layer < params.numLayers)
-                words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable);
-        SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
-        const uint16_t* lo = params.latents + mip.loOffset;
-#pragma unroll
-        for (int layer = 0; layer < 4; ++layer)
-            if (layer < params.numLayers)
-                words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable);
+        SampleGridsDirect<kFp8>(params.latents, params.numLayers, mip, min(ctx.x, mip.width - 1), min(ctx.y, mip.rowEnd - 1),
+            shared.latentTable, words);
     }
 
     // positional encoding: interleave the column's x bytes with the row's y bytes
@@ -783,6 +783,15 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
         ctx.tile = tile;
         ctx.x = tileX0 + lane;
         ctx.y = tileY0 + warp;
+        {
+            // element index inside the mip fits 32 bits (8192^2 texels x 16 channels is 2^30)
+            const bool planar = params.outputLayout == kLayoutPlanarPairs;
+            const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
+                                          : (uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x)) * uint32_t(params.channels);
+            const bool inside = ctx.x < mip.width && ctx.y < mip.rowEnd;
+            ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
+            ctx.outStepWords = planar ? uint32_t(mip.width) : 1u; // channel pairs are 2 * width or 2 elements apart
+        }
 
         // ---- 1. tables and latent footprints of the tile, then the A operand -----------------
         // The previous tile's tables and footprints were last read before its first layer
@@ -793,10 +802,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
         BuildInputs<kFp8>(params, mip, shared, ctx, lane, warp);
 
         // ---- 2./3./4. the four layers ------------------------------------------------------
-        aborted = RunLayer<kFp8, 0>(params, mip, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 1>(params, mip, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 2>(params, mip, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 3>(params, mip, shared, ctx, phase, failed);
+        aborted = RunLayer<kFp8, 0>(params.status, params.channels, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 1>(params.status, params.channels, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 2>(params.status, params.channels, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 3>(params.status, params.channels, shared, ctx, phase, failed);
         if (aborted)
             break;
     }
@@ -811,7 +820,135 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
         TmemFree(tmemBase, kTmemColumns);
 }
 
+// Inference on sample: one thread per query (u, v, lod) -> the texel (mip = clamp(floor(lod)),
+// x = min(floor(u * W), W - 1), y likewise) is evaluated exactly as the decode kernel evaluates it
+// (the reference's NtcSampleTextureSet takes an integer texel and mip and runs the same network,
+// include/libntc/shaders/Inference.hlsli:282-357).  Queries are incoherent, so the taps are read
+// straight from global memory; a tile is 256 consecutive queries, i.e. two 128-row GEMM chains.
+template <bool kFp8>
+__global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8) SampleKernel(const __grid_constant__ SampleParams params)
+{
+    __shared__ SharedStorage shared;
+    __shared__ KernelMip mipTable[16];
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int half = warp >> 2;
+
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(params.network);
+        uint4* dst = reinterpret_cast<uint4*>(shared.network);
+        for (int i = tid; i < kStagedNetworkBytes / 16; i += kThreadsPerCta)
+            dst[i] = __ldg(src + i);
+        for (int i = tid; i < 256; i += kThreadsPerCta)
+        {
+            __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
+            __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
+            shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
+        }
+        if (tid < params.numMips)
+            mipTable[tid] = params.mips[tid];
+        if (tid == 0)
+        {
+            MbarrierInit(SharedAddress(&shared.barrier), 1);
+            FenceBarrierInit();
+        }
+        if (warp == 0)
+            TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
+        FenceProxyAsyncShared();
+        TcgenFenceBeforeSync();
+        __syncthreads();
+        TcgenFenceAfterSync();
+    }
+    const uint32_t tmemBase = shared.tmemBase;
+    uint32_t phase = 0;
+    int failed = 0, aborted = 0;
+
+    TileContext ctx;
+    ctx.tid = tid;
+    ctx.tmemBase = tmemBase;
+    ctx.tmemLane = tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
+    ctx.barrier = SharedAddress(&shared.barrier);
+    ctx.operandA = SharedAddress(shared.operandA);
+    ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
+    ctx.networkBase = SharedAddress(shared.network);
+    ctx.outStepWords = 1;
+
+    const unsigned long long tiles = (params.numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
+    for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x)
+    {
+        const unsigned long long query = tile * kThreadsPerCta + tid;
+        const bool valid = query < params.numQueries;
+        const unsigned long long q = valid ? query : params.numQueries - 1;
+        const float u = __ldg(params.queries + 3 * q), v = __ldg(params.queries + 3 * q + 1), lod = __ldg(params.queries + 3 * q + 2);
+        const int mipIndex = max(0, min(params.numMips - 1, int(floorf(lod))));
+        const KernelMip& mip = mipTable[mipIndex];
+        const int x = max(0, min(mip.width - 1, int(floorf(__fmul_rn(u, float(mip.width))))));
+        const int y = max(0, min(mip.height - 1, int(floorf(__fmul_rn(v, float(mip.height))))));
+        ctx.tile = int(tile);
+        ctx.x = x;
+        ctx.y = y;
+        ctx.out = valid ? reinterpret_cast<uint32_t*>(params.out + query * params.channels) : nullptr;
+
+        {
+            uint32_t words[16];
+            const uint32_t zeroWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(0.f)),
+                                                      QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                words[i] = zeroWord;
+#pragma unroll
+            for (int i = 12; i < 16; ++i)
+                words[i] = 0;
+            SampleGridsDirect<kFp8>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
+            // src/RegressionKernels.h:59-85
+            float xf = __fmul_rn(float(x), mip.positionScale);
+            float yf = __fmul_rn(float(y), mip.positionScale);
+#pragma unroll
+            for (int wave = 0; wave < 3; ++wave)
+            {
+                const float ex = __fmaf_rn(Frac(xf), 2.f, -1.f), ey = __fmaf_rn(Frac(yf), 2.f, -1.f);
+                const float ez = __fmaf_rn(Frac(__fadd_rn(xf, 0.25f)), 2.f, -1.f);
+                const float ew = __fmaf_rn(Frac(__fadd_rn(yf, 0.25f)), 2.f, -1.f);
+                words[8 + wave] = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__floats2half2_rn(ex, ey)),
+                                                   QuantizeInputPair<kFp8>(__floats2half2_rn(ez, ew)));
+                xf = __fmul_rn(xf, 2.f);
+                yf = __fmul_rn(yf, 2.f);
+            }
+            words[11] = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(mip.positionLod)),
+                                        QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk)
+                ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
+        }
+
+        aborted = RunLayer<kFp8, 0>(params.status, params.channels, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 1>(params.status, params.channels, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 2>(params.status, params.channels, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 3>(params.status, params.channels, shared, ctx, phase, failed);
+        if (aborted)
+            break;
+    }
+
+    TcgenFenceBeforeSync();
+    aborted = __syncthreads_or(failed);
+    if (aborted && tid == 0)
+        (void)MbarrierWaitBounded(ctx.barrier, phase ^ 1);
+    __syncthreads();
+    if (warp == 0)
+        TmemFree(tmemBase, kTmemColumns);
+}
+
 } // namespace
+
+cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream)
+{
+    if (fp8)
+        SampleKernel<true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+    else
+        SampleKernel<false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+    return cudaGetLastError();
+}
 
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
 {

@@ -65,6 +65,21 @@ struct KernelParams
     KernelMip mips[16];
 };
 
+struct SampleParams
+{
+    const uint16_t* latents;
+    const uint8_t* network;
+    const float* queries; // [numQueries][3]: u, v, lod
+    __half* out;          // [numQueries][channels]
+    uint32_t* status;
+    unsigned long long numQueries;
+    int numMips;
+    int numLayers;
+    int channels;
+    KernelMip mips[16];
+};
+
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
+cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream);
 
 } // namespace ntcb

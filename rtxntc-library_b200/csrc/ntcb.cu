@@ -50,6 +50,46 @@ constexpr int kLayerOutputs[4] = {64, 48, 32, 16};
 constexpr int kLayerPaddedK[4] = {64, 64, 64, 32};
 constexpr int kWeightOffsets[4] = {kWeightOffset0, kWeightOffset1, kWeightOffset2, kWeightOffset3};
 
+bool ValidMip(const NtcbMipDesc& m)
+{
+    return !(m.width < 1 || m.height < 1 || m.hiWidth < 1 || m.hiHeight < 1 || m.loWidth < 1 || m.loHeight < 1 ||
+             m.rowBegin < 0 || m.rowEnd > m.height || m.rowBegin > m.rowEnd || (m.outOffset & 1) ||
+             m.hiPlane < uint64_t(m.hiWidth) * m.hiHeight || m.loPlane < uint64_t(m.loWidth) * m.loHeight);
+}
+
+// The kernel's view of one mip (everything but its place in the tile list).
+void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km)
+{
+    km.width = m.width;
+    km.height = m.height;
+    km.rowBegin = m.rowBegin;
+    km.rowEnd = m.rowEnd;
+    km.hiWidth = m.hiWidth;
+    km.hiHeight = m.hiHeight;
+    km.loWidth = m.loWidth;
+    km.loHeight = m.loHeight;
+    km.hiOffset = m.hiOffset;
+    km.loOffset = m.loOffset;
+    km.hiPlane = m.hiPlane;
+    km.loPlane = m.loPlane;
+    km.outOffset = m.outOffset;
+    km.invWidth = 1.0f / float(m.width);
+    km.invHeight = 1.0f / float(m.height);
+    km.positionScale = m.positionScale;
+    km.positionLod = m.positionLod;
+    // Largest footprint a tile can have in each grid: the tap index of the last column (row) minus
+    // that of the first is at most floor(31 (7) * grid / mip) + 1, plus the second tap.
+    km.strideShift = layers == 1 ? 3 : layers == 2 ? 4 : 5;
+    const long long hiCapacity = kFootprintHiBytes >> km.strideShift, loCapacity = kFootprintLoBytes >> km.strideShift;
+    auto footprint = [](int grid, int mip, int span) { return (long long)((long long)span * grid / mip) + 3; };
+    const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, kTileHeight - 1);
+    const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, kTileHeight - 1);
+    km.staged = (hiPixels <= hiCapacity && loPixels <= loCapacity) ? 1 : 0;
+    km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
+    km.tilesXMagic = km.tilesX == 1 ? 0u : unsigned((0x100000000ull + km.tilesX - 1) / km.tilesX);
+    km.firstTile = 0;
+}
+
 // Number of CTAs that fill the current device, cached per device.
 int ResidentCtas(bool fp8, int* outCtas)
 {
@@ -269,9 +309,7 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
     for (int i = 0; i < p->numMips; ++i)
     {
         const NtcbMipDesc& m = p->mips[i];
-        if (m.width < 1 || m.height < 1 || m.hiWidth < 1 || m.hiHeight < 1 || m.loWidth < 1 || m.loHeight < 1 ||
-            m.rowBegin < 0 || m.rowEnd > m.height || m.rowBegin > m.rowEnd || (m.outOffset & 1) ||
-            m.hiPlane < uint64_t(m.hiWidth) * m.hiHeight || m.loPlane < uint64_t(m.loWidth) * m.loHeight)
+        if (!ValidMip(m))
         {
             SetError("ntcb_decode: mip %d has invalid dimensions, row range or offsets.", i);
             return NTCB_ERR_INVALID_ARGUMENT;
@@ -279,34 +317,7 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         if (m.rowBegin == m.rowEnd)
             continue; // nothing of this mip belongs to this launch
         KernelMip& km = k.mips[used++];
-        km.width = m.width;
-        km.height = m.height;
-        km.rowBegin = m.rowBegin;
-        km.rowEnd = m.rowEnd;
-        km.hiWidth = m.hiWidth;
-        km.hiHeight = m.hiHeight;
-        km.loWidth = m.loWidth;
-        km.loHeight = m.loHeight;
-        km.hiOffset = m.hiOffset;
-        km.loOffset = m.loOffset;
-        km.hiPlane = m.hiPlane;
-        km.loPlane = m.loPlane;
-        km.outOffset = m.outOffset;
-        km.invWidth = 1.0f / float(m.width);
-        km.invHeight = 1.0f / float(m.height);
-        km.positionScale = m.positionScale;
-        km.positionLod = m.positionLod;
-        // Largest footprint a tile can have in each grid: the tap index of the last column (row) minus
-        // that of the first is at most floor(31 (7) * grid / mip) + 1, plus the second tap.
-        const int layers = p->numFeatures / 4;
-        km.strideShift = layers == 1 ? 3 : layers == 2 ? 4 : 5;
-        const long long hiCapacity = kFootprintHiBytes >> km.strideShift, loCapacity = kFootprintLoBytes >> km.strideShift;
-        auto footprint = [](int grid, int mip, int span) { return (long long)((long long)span * grid / mip) + 3; };
-        const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, kTileHeight - 1);
-        const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, kTileHeight - 1);
-        km.staged = (hiPixels <= hiCapacity && loPixels <= loCapacity) ? 1 : 0;
-        km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
-        km.tilesXMagic = km.tilesX == 1 ? 0u : unsigned((0x100000000ull + km.tilesX - 1) / km.tilesX);
+        FillKernelMip(m, p->numFeatures / 4, km);
         km.firstTile = int(tiles);
         const long long mipTiles = (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
         if (mipTiles * km.tilesX >= 0x100000000ll)
@@ -336,6 +347,66 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
     cudaError_t err = LaunchDecode(k, fp8, ctas, static_cast<cudaStream_t>(stream));
     if (err != cudaSuccess)
         return CudaFailure("DecodeKernel launch", err);
+    CountLaunch();
+    return NTCB_OK;
+}
+
+int ntcb_sample(const NtcbSampleParams* p, void* stream)
+{
+    if (!p || !p->latents || !p->network || !p->status || ((!p->queries || !p->out) && p->numQueries))
+    {
+        SetError("ntcb_sample: params, latents, network, queries, out and status must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (p->numMips < 1 || p->numMips > NTCB_MAX_MIPS || p->numFeatures < 4 || p->numFeatures > 16 || (p->numFeatures & 3) ||
+        p->channels < 2 || p->channels > 16 || (p->channels & 1) ||
+        (p->weightMode != NTCB_WEIGHTS_INT8 && p->weightMode != NTCB_WEIGHTS_FP8))
+    {
+        SetError("ntcb_sample: invalid mip count, feature count, channel count or weight mode.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if ((reinterpret_cast<uintptr_t>(p->network) & 15) || (reinterpret_cast<uintptr_t>(p->out) & 3) ||
+        (reinterpret_cast<uintptr_t>(p->queries) & 3))
+    {
+        SetError("ntcb_sample: network must be 16-byte aligned, out and queries 4-byte aligned.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    SampleParams k{};
+    k.latents = p->latents;
+    k.network = static_cast<const uint8_t*>(p->network);
+    k.queries = p->queries;
+    k.out = static_cast<__half*>(p->out);
+    k.status = p->status;
+    k.numQueries = p->numQueries;
+    k.numMips = p->numMips;
+    k.numLayers = p->numFeatures / 4;
+    k.channels = p->channels;
+    for (int i = 0; i < p->numMips; ++i)
+    {
+        NtcbMipDesc m = p->mips[i];
+        m.rowBegin = 0;
+        m.rowEnd = m.height;
+        m.outOffset = 0;
+        if (!ValidMip(m))
+        {
+            SetError("ntcb_sample: mip %d has invalid dimensions or offsets.", i);
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        FillKernelMip(m, k.numLayers, k.mips[i]);
+    }
+    ClearError();
+    if (p->numQueries == 0)
+        return NTCB_OK;
+    const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
+    int resident = 0;
+    int rc = ResidentCtas(fp8, &resident);
+    if (rc != NTCB_OK)
+        return rc;
+    const unsigned long long tiles = (p->numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
+    const int ctas = tiles < (unsigned long long)resident ? int(tiles) : resident;
+    cudaError_t err = LaunchSample(k, fp8, ctas, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess)
+        return CudaFailure("SampleKernel launch", err);
     CountLaunch();
     return NTCB_OK;
 }
