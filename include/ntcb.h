@@ -244,6 +244,36 @@ int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void**
 /* Waits for everything queued on the texture set's stream. */
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet);
 
+/* Size of the staging area built into the library for ntcb_read_channels_to_host_noalloc. */
+#define NTCB_NOALLOC_STAGING_BYTES (4u << 20)
+
+/* Reads decoded channels of one mip into HOST memory without allocating anything.
+   (No counterpart in the reference: its ReadChannels stages through a buffer that the texture set
+   allocates at creation, src/TextureSet.cpp:123-131.)
+
+   Who this is for: ntcb_texture_set_read_channels grows a device staging buffer with cudaMalloc the
+   first time a host read needs a layout conversion (a channel subset, padded strides, or the
+   planar-pair internal layout).  Some callers must not reach cudaMalloc: code on a frame or
+   streaming thread where an allocation's implicit device synchronisation is a stall, code that
+   runs under a fixed memory budget handed out up front, or code inside a region where allocation
+   is simply forbidden by the host application.  This variant runs the same gather kernel into a
+   4 MiB array that is part of the library image (each GPU that loads the library carries it until
+   the process exits), then copies to `hostDestination` and waits for `stream`.
+
+   `deviceMip` is the device address of one decoded mip (ntcb_texture_set_device_mip, or the `out`
+   buffer given to ntcb_decode plus the mip's offset) in `layout` with `channels` channels;
+   firstChannel / numChannels / pixelStride / rowPitch mean what they mean in NtcbReadChannelsParams.
+   height * rowPitch must not exceed NTCB_NOALLOC_STAGING_BYTES, otherwise NTCB_ERR_OUT_OF_RANGE is
+   returned and nothing is done: read a large mip in row bands (offset `deviceMip` by whole rows
+   for the interleaved layout) or channel groups.
+
+   The first call on a device looks up the array's device address; make that call before any
+   stream capture begins.  Every call uses the same array, which keeps the previous call's
+   contents (gaps are cleared when a request has gaps): two calls whose GPU work overlaps - on
+   different streams or from different threads - race on it, so serialise them. */
+int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int width, int height, int channels,
+    int firstChannel, int numChannels, void* hostDestination, size_t pixelStride, size_t rowPitch, void* stream);
+
 /* Number of CTAs the decode kernel keeps resident on the current device for a weight mode (the
    grid size of large launches): SM count x resident CTAs per SM, the latter bounded by registers,
    shared memory and tensor-memory columns.  For benchmarks and tests. */

@@ -120,6 +120,9 @@ def lib():
         handle.ntcb_texture_set_device_mip.argtypes = [
             ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t)]
         handle.ntcb_texture_set_synchronize.argtypes = [ctypes.c_void_p]
+        handle.ntcb_read_channels_to_host_noalloc.argtypes = [
+            ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+            ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p]
         _lib = handle
     return _lib
 
@@ -334,6 +337,12 @@ class TextureSet:
         out = np.empty((h, w, n), dtype=np.float16)
         self.read_channels_into(mip, out.ctypes.data, False, first_channel, n)
         return out
+
+    def device_mip(self, mip: int) -> Tuple[int, int]:
+        """Device address and size in bytes of one decoded mip in the internal layout."""
+        pointer, size = ctypes.c_void_p(), ctypes.c_size_t()
+        check(lib().ntcb_texture_set_device_mip(self.handle, mip, ctypes.byref(pointer), ctypes.byref(size)))
+        return int(pointer.value), int(size.value)
 
     def synchronize(self) -> None:
         check(lib().ntcb_texture_set_synchronize(self.handle))

@@ -81,6 +81,37 @@ __global__ void ReadChannelsKernel(const __half* __restrict__ src, int layout, i
     }
 }
 
+// Staging area of ntcb_read_channels_to_host_noalloc: part of the library image, so every GPU
+// that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_noAllocStaging[NTCB_NOALLOC_STAGING_BYTES];
+
+// Device address of g_noAllocStaging on the current device.  In host code the array's name is
+// only a handle for the runtime, not a pointer a kernel can use: the address has to be asked for,
+// once per device, with that device current.
+int NoAllocStagingAddress(unsigned char** outPointer)
+{
+    static unsigned char* cache[64] = {};
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaGetDevice", err);
+    if (device < 0 || device >= 64)
+    {
+        SetError("CUDA device index %d is out of the supported range.", device);
+        return NTCB_ERR_CUDA;
+    }
+    if (!cache[device])
+    {
+        void* address = nullptr;
+        err = cudaGetSymbolAddress(&address, g_noAllocStaging);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaGetSymbolAddress", err);
+        cache[device] = static_cast<unsigned char*>(address);
+    }
+    *outPointer = cache[device];
+    return NTCB_OK;
+}
+
 class Context;
 
 class TextureSet final : public ITextureSet
@@ -822,6 +853,73 @@ int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet)
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     return textureSet->impl->Synchronize();
+}
+
+int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int width, int height, int channels,
+    int firstChannel, int numChannels, void* hostDestination, size_t pixelStride, size_t rowPitch, void* stream)
+{
+    using namespace ntcb;
+    if (!deviceMip || !hostDestination)
+    {
+        SetError("deviceMip and hostDestination must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if ((layout != NTCB_LAYOUT_PLANAR_PAIRS && layout != NTCB_LAYOUT_INTERLEAVED) || width < 1 || height < 1 ||
+        channels < 2 || channels > 16 || (channels & 1))
+    {
+        SetError("Invalid layout (%d), size (%dx%d) or channel count (%d).", layout, width, height, channels);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (firstChannel < 0 || firstChannel >= channels || numChannels < 1 || numChannels > channels - firstChannel)
+    {
+        SetError("For the provided firstChannel (%d), numChannels (%d) must be between 1 and %d.", firstChannel, numChannels,
+            channels - firstChannel);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (pixelStride < size_t(numChannels) * 2 || rowPitch < pixelStride * size_t(width) || (pixelStride & 1) || (rowPitch & 1))
+    {
+        SetError("pixelStride (%zu) must hold numChannels fp16 values and rowPitch (%zu) a row of pixels; both must be even.",
+            pixelStride, rowPitch);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const size_t bytes = size_t(height) * rowPitch;
+    if (bytes > size_t(NTCB_NOALLOC_STAGING_BYTES))
+    {
+        SetError("The request needs %zu bytes of staging, more than the %zu bytes this entry point owns; read fewer rows "
+                 "or channels per call, or use ntcb_texture_set_read_channels.",
+            bytes, size_t(NTCB_NOALLOC_STAGING_BYTES));
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    unsigned char* staging = nullptr;
+    int status = NoAllocStagingAddress(&staging);
+    if (status != NTCB_OK)
+        return status;
+    cudaStream_t cudaStream = static_cast<cudaStream_t>(stream);
+    cudaError_t err;
+    if (rowPitch > pixelStride * size_t(width) || pixelStride > size_t(numChannels) * 2)
+    {
+        // the array keeps what the previous call left there: the gaps the kernel does not write must
+        // read as zeros
+        err = cudaMemsetAsync(staging, 0, bytes, cudaStream);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaMemsetAsync (staging)", err);
+    }
+    dim3 block(32, 8);
+    dim3 grid((width + block.x - 1) / block.x, (height + block.y - 1) / block.y);
+    ReadChannelsKernel<<<grid, block, 0, cudaStream>>>(static_cast<const __half*>(deviceMip), layout, width, height, channels,
+        firstChannel, numChannels, staging, pixelStride, rowPitch);
+    err = cudaGetLastError();
+    if (err != cudaSuccess)
+        return CudaFailure("ReadChannelsKernel launch", err);
+    CountLaunch();
+    err = cudaMemcpyAsync(hostDestination, staging, bytes, cudaMemcpyDeviceToHost, cudaStream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaMemcpyAsync (staging)", err);
+    err = cudaStreamSynchronize(cudaStream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamSynchronize", err);
+    ClearError();
+    return NTCB_OK;
 }
 
 } // extern "C"
