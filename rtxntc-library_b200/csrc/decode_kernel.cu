@@ -504,12 +504,10 @@ struct TileContext
     uint32_t outStepWords;  // 32-bit words between consecutive channel pairs
 };
 
-// One layer of the MLP for the CTA's current tile: barrier, MMA issue (both halves), wait, then
-// either the activation + re-quantisation into the next A operand (layers 0-2) or the output
-// epilogue (layer 3).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
+// First half of a layer of the MLP for the CTA's current tile: barrier and MMA issue (both halves
+// of the tile).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
 template <bool kFp8, int kLayer>
-__device__ __forceinline__ int RunLayer(uint32_t* status, int channels, const SharedStorage& shared,
-    const TileContext& ctx, uint32_t& phase, int& failed)
+__device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
     constexpr int kK = kLayer == 3 ? 32 : 64;
@@ -543,6 +541,17 @@ __device__ __forceinline__ int RunLayer(uint32_t* status, int channels, const Sh
         }
         UmmaCommit(ctx.barrier);
     }
+    return 0;
+}
+
+// Second half of a layer: waits for the MMA, then applies the activation and writes the next
+// layer's A operand (layers 0-2) or runs the output epilogue (layer 3).
+template <bool kFp8, int kLayer>
+__device__ __forceinline__ void ConsumeLayer(uint32_t* status, int channels, const SharedStorage& shared,
+    const TileContext& ctx, uint32_t& phase, int& failed)
+{
+    constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
+    constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
 
     if (!MbarrierWaitBounded(ctx.barrier, phase))
     {
@@ -649,6 +658,15 @@ __device__ __forceinline__ int RunLayer(uint32_t* status, int channels, const Sh
                     ctx.out[j * ctx.outStepWords] = bits[j];
         }
     }
+}
+
+template <bool kFp8, int kLayer>
+__device__ __forceinline__ int RunLayer(uint32_t* status, int channels, const SharedStorage& shared,
+    const TileContext& ctx, uint32_t& phase, int& failed)
+{
+    if (IssueLayer<kFp8, kLayer>(ctx, failed))
+        return 1;
+    ConsumeLayer<kFp8, kLayer>(status, channels, shared, ctx, phase, failed);
     return 0;
 }
 
@@ -767,22 +785,41 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
 
-    int mipIndex = 0;
-    for (int tile = blockIdx.x; tile < params.totalTiles; tile += gridDim.x)
+    // Position of a tile in its mip.
+    struct TilePlace
     {
-        // ---- locate the tile (tiles are visited in increasing order) ----------------------
-        while (mipIndex + 1 < params.numMips && tile >= params.mips[mipIndex + 1].firstTile)
-            ++mipIndex;
-        const KernelMip& mip = params.mips[mipIndex];
+        int mipIndex, tileX0, tileY0;
+    };
+    auto locate = [&](int tile, int fromMip) {
+        // tiles are visited in increasing order, so the search resumes at the current mip
+        TilePlace place;
+        place.mipIndex = fromMip;
+        while (place.mipIndex + 1 < params.numMips && tile >= params.mips[place.mipIndex + 1].firstTile)
+            ++place.mipIndex;
+        const KernelMip& mip = params.mips[place.mipIndex];
         const int local = tile - mip.firstTile;
         // local / tilesX through a precomputed reciprocal (exact while local * tilesX < 2^32)
         const int tileY = mip.tilesX == 1 ? local : int(__umulhi(uint32_t(local), mip.tilesXMagic));
-        const int tileX = local - tileY * mip.tilesX;
-        const int tileX0 = tileX * kTileWidth;
-        const int tileY0 = mip.rowBegin + tileY * kTileHeight;
+        place.tileX0 = (local - tileY * mip.tilesX) * kTileWidth;
+        place.tileY0 = mip.rowBegin + tileY * kTileHeight;
+        return place;
+    };
+
+    int tile = blockIdx.x;
+    TilePlace place{0, 0, 0};
+    if (tile < params.totalTiles)
+    {
+        // ---- tables and latent footprints of the first tile -----------------------------------
+        place = locate(tile, 0);
+        PrepareTile<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        __syncthreads();
+    }
+    while (tile < params.totalTiles)
+    {
+        const KernelMip& mip = params.mips[place.mipIndex];
         ctx.tile = tile;
-        ctx.x = tileX0 + lane;
-        ctx.y = tileY0 + warp;
+        ctx.x = place.tileX0 + lane;
+        ctx.y = place.tileY0 + warp;
         {
             // element index inside the mip fits 32 bits (8192^2 texels x 16 channels is 2^30)
             const bool planar = params.outputLayout == kLayoutPlanarPairs;
@@ -793,21 +830,31 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
             ctx.outStepWords = planar ? uint32_t(mip.width) : 1u; // channel pairs are 2 * width or 2 elements apart
         }
 
-        // ---- 1. tables and latent footprints of the tile, then the A operand -----------------
-        // The previous tile's tables and footprints were last read before its first layer
-        // barrier, so they may be overwritten here; its A operand was last read by its last MMA,
-        // which every thread has waited for.
-        PrepareTile<kFp8>(params, mip, shared, tileX0, tileY0, lane, warp);
-        __syncthreads();
+        // ---- 1. this tile's network inputs -> A operand (the last MMA that read the A operand has
+        //         completed: every thread waited for it) -------------------------------------------
         BuildInputs<kFp8>(params, mip, shared, ctx, lane, warp);
 
-        // ---- 2./3./4. the four layers ------------------------------------------------------
-        aborted = RunLayer<kFp8, 0>(params.status, params.channels, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 1>(params.status, params.channels, shared, ctx, phase, failed);
+        // ---- 2. layer 0; while the tensor core works on it, prepare the NEXT tile: its tables and
+        //         footprints replace this tile's, which nobody reads after the barrier inside
+        //         IssueLayer, and the global-memory latency of the footprint hides behind the MMA ----
+        aborted = IssueLayer<kFp8, 0>(ctx, failed);
+        if (aborted)
+            break;
+        const int nextTile = tile + int(gridDim.x);
+        if (nextTile < params.totalTiles)
+        {
+            place = locate(nextTile, place.mipIndex);
+            PrepareTile<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        }
+        ConsumeLayer<kFp8, 0>(params.status, params.channels, shared, ctx, phase, failed);
+
+        // ---- 3./4. layers 1-3 (their barriers also order the next tile's tables before its use) ---
+        aborted = RunLayer<kFp8, 1>(params.status, params.channels, shared, ctx, phase, failed);
         if (!aborted) aborted = RunLayer<kFp8, 2>(params.status, params.channels, shared, ctx, phase, failed);
         if (!aborted) aborted = RunLayer<kFp8, 3>(params.status, params.channels, shared, ctx, phase, failed);
         if (aborted)
             break;
+        tile = nextTile;
     }
 
     // ---- teardown -------------------------------------------------------------------------
