@@ -12,7 +12,7 @@ constexpr int kTileWidth = 32;
 constexpr int kTileHeight = 8;      // a tile is two 32x4 halves, each a 128-row GEMM chain
 constexpr int kThreadsPerCta = kTileWidth * kTileHeight; // one thread per texel of a tile
 constexpr int kOperandBytes = 128 * 64; // A operand of one half: 128 rows x 64 bytes
-constexpr int kCtasPerSmInt8 = 3;  // resident CTAs per SM the two kernel variants are compiled for
+constexpr int kCtasPerSmInt8 = 4;  // resident CTAs per SM the two kernel variants are compiled for
 constexpr int kCtasPerSmFp8 = 4;
 constexpr int kTmemColumnsPerHalf = 64;    // widest accumulator (layer 0: 64 outputs)
 constexpr int kTmemColumns = 2 * kTmemColumnsPerHalf;
