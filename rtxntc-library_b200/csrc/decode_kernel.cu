@@ -220,7 +220,15 @@ __device__ __forceinline__ uint32_t QuantizeInputPair(__half2 x)
 template <bool kFp8>
 __device__ __forceinline__ uint32_t PackCodes(uint32_t pair0, uint32_t pair1)
 {
-    return kFp8 ? __byte_perm(pair0, pair1, 0x5410) : __byte_perm(pair0, pair1, 0x6420);
+    if (kFp8)
+    {
+        // pair0 | pair1 << 16 (both are 16-bit values) as an integer multiply-add: it runs on the FMA
+        // pipe, leaving the busier ALU pipe to the conversions and min/max
+        uint32_t packed;
+        asm("mad.lo.u32 %0, %1, 65536, %2;" : "=r"(packed) : "r"(pair1), "r"(pair0));
+        return packed;
+    }
+    return __byte_perm(pair0, pair1, 0x6420);
 }
 
 // Clamped HGELU in binary16 (src/tin/tin_activation.h:88-92) followed by re-quantisation:
