@@ -406,6 +406,34 @@ def run_reference(args) -> dict:
     }
 
 
+def run_profile_case(case: str) -> int:
+    """A few bare launches of the decode kernel on a small square set, for a profiler to capture.
+
+    `case` is SIZE:MODE:LAUNCHES, e.g. 2048:fp8:2: a SIZE x SIZE 12-channel set with a full mip chain (output
+    larger than L2 from 2048 up, a few hundred MB on the device), MODE fp8 or int8.  Prints a plain line, not
+    the benchmark's JSON line: a figure taken under a profiler is not a benchmark value.
+    """
+    import torch
+
+    size, mode, launches = case.split(":")
+    entry.load_package()
+    from rtxntc_library_b200 import binding, synthetic
+
+    spec = synthetic.TextureSetSpec(int(size), int(size), 12, 0, 4, 12, seed=1, weights=mode, latent_alphabet="2bit-even")
+    data = synthetic.make_texture_set(spec)
+    resident = binding.ResidentTextureSet.from_synthetic(data)
+    params = resident.params(mode == "int8")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(int(launches)):
+        start.record()
+        resident.launch(params)
+        stop.record()
+    torch.cuda.synchronize()
+    resident.check_status()
+    print("profile case %s: %d texels, last launch %.3f ms" % (case, data.geometry.total_texels, start.elapsed_time(stop)))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -415,7 +443,11 @@ def main() -> int:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3],
                         help="benchmark configuration; 1 (the default) is the one the metric is quoted on")
+    parser.add_argument("--profile-case", metavar="SIZE:MODE:LAUNCHES",
+                        help="only launch the decode kernel LAUNCHES times on a small SIZE^2 set (fp8 or int8) and exit")
     args = parser.parse_args()
+    if args.profile_case:
+        return run_profile_case(args.profile_case)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:
