@@ -22,6 +22,7 @@
 extern "C" {
 #endif
 
+#define NTCB_MAX_CHANNELS 16     /* NTC_MAX_CHANNELS, include/libntc/shaders/InferenceConstants.h:23 */
 #define NTCB_MAX_MIPS 16         /* NTC_MAX_MIPS, include/libntc/shaders/InferenceConstants.h:22 */
 #define NTCB_MAX_NEURAL_MIPS 8   /* NTC_MAX_NEURAL_MIPS, :24 */
 #define NTCB_INT8_BLOB_BYTES 9472 /* GenericInt8 weight blob, src/WeightLayout.cpp:142-268 */
@@ -62,6 +63,34 @@ typedef enum NtcbOutputLayout
     NTCB_LAYOUT_INTERLEAVED = 1
 } NtcbOutputLayout;
 
+/* ntc::ChannelFormat (include/libntc/ntc.h:227-236) */
+#define NTCB_CHANNEL_FORMAT_UNORM8 1
+#define NTCB_CHANNEL_FORMAT_UNORM16 2
+#define NTCB_CHANNEL_FORMAT_FLOAT16 3
+#define NTCB_CHANNEL_FORMAT_FLOAT32 4
+#define NTCB_CHANNEL_FORMAT_UINT32 5
+/* ntc::ColorSpace (include/libntc/ntc.h:251-256) */
+#define NTCB_COLOR_SPACE_LINEAR 0
+#define NTCB_COLOR_SPACE_SRGB 1
+#define NTCB_COLOR_SPACE_HLG 2
+
+/* How decoded fp16 channels become the client's pixel components: the arithmetic of the
+   reference's CopyImageKernel on its way out of a texture set (src/ImageProcessing.cu:86-164,
+   220-266; src/CudaUtils.h:63-184).  Each pixel gets `components` values of `channelFormat`,
+   tightly interleaved: component c < numChannels is channel firstChannel + c, taken out of
+   srcColorSpaces[c], encoded to dstColorSpaces[c], dithered (UNORM formats, when useDithering) and
+   rounded; the components past numChannels are 0, component 3 is 1. */
+typedef struct NtcbOutputConversion
+{
+    int32_t channelFormat;  /* NTCB_CHANNEL_FORMAT_* */
+    int32_t components;     /* 1..16 */
+    int32_t firstChannel, numChannels;
+    int32_t useDithering;
+    int32_t reserved;
+    uint8_t srcColorSpaces[NTCB_MAX_CHANNELS]; /* per requested channel: the colour space it is stored in */
+    uint8_t dstColorSpaces[NTCB_MAX_CHANNELS]; /* per requested channel: the colour space to encode to */
+} NtcbOutputConversion;
+
 /* One colour mip to decode; mirrors the per-mip fields of InferenceKernelParams
    (src/RegressionCommon.h:55-80) as TextureSet::Decompress fills them (src/TextureSet.cpp:1806-1829). */
 typedef struct NtcbMipDesc
@@ -85,16 +114,23 @@ typedef struct NtcbDecodeParams
     const uint16_t* latents; /* device: BGRA4 latent pixels, for each neural mip, for each layer, rows
                                 (the reference's encoded-pixel order, src/FeatureGridHost.cpp:140-155) */
     const void* network;     /* device: NTCB_STAGED_NETWORK_BYTES produced by ntcb_stage_network */
-    void* out;               /* device: fp16 texels */
+    void* out;               /* device: fp16 texels, or converted pixels when `conversion` is set */
     uint32_t* status;        /* device: NTCB_STATUS_WORDS words, zeroed by the caller before the launch;
                                 word 0 != 0 after the kernel means a bounded wait expired */
     int32_t numMips;
     int32_t numFeatures;     /* 4, 8, 12 or 16 */
     int32_t channels;        /* even, 2..16 */
     int32_t weightMode;      /* NtcbWeightMode, must match the staged network */
-    int32_t outputLayout;    /* NtcbOutputLayout */
+    int32_t outputLayout;    /* NtcbOutputLayout (ignored when `conversion` is set) */
     int32_t reserved;
     NtcbMipDesc mips[NTCB_MAX_MIPS];
+    /* NULL: fp16 texels in `outputLayout`.  Otherwise the kernel's epilogue converts every texel as
+       ITextureSet::ReadChannels would after Decompress (src/TextureSet.cpp:915-985) and writes
+       pixel-interleaved rows without padding: the fp16 copy of the texels is never stored.  In this
+       mode mips[i].outOffset counts components of the channel format (bytes / bytes-per-component)
+       and must be a multiple of `components`; the dither pattern of a mip is seeded per pixel with
+       x + y * width, as a full-mip ReadChannels does. */
+    const NtcbOutputConversion* conversion;
 } NtcbDecodeParams;
 
 /* Thread-local message of the last failing call on this thread; never NULL.
@@ -174,18 +210,20 @@ typedef struct NtcbDecompressionStats
 
 #define NTCB_ADDRESS_SPACE_HOST 0   /* ntc::AddressSpace::Host */
 #define NTCB_ADDRESS_SPACE_DEVICE 1 /* ntc::AddressSpace::Device */
-#define NTCB_CHANNEL_FORMAT_FLOAT16 3 /* ntc::ChannelFormat::FLOAT16 */
 
-/* ntc::ReadChannelsParameters (include/libntc/ntc.h:689-730), the fields this path uses. */
+/* ntc::ReadChannelsParameters (include/libntc/ntc.h:689-730).  The source page is always the
+   decoded output. */
 typedef struct NtcbReadChannelsParams
 {
     int32_t mipLevel, firstChannel, numChannels;
     int32_t addressSpace;  /* NTCB_ADDRESS_SPACE_* */
     void* pOutData;
-    int32_t width, height; /* must equal the mip's size */
-    int32_t channelFormat; /* NTCB_CHANNEL_FORMAT_FLOAT16 */
-    int32_t reserved;
-    size_t pixelStride, rowPitch; /* bytes */
+    int32_t width, height; /* must equal the mip's size (the reference's bilinear resize is not offered) */
+    int32_t channelFormat; /* NTCB_CHANNEL_FORMAT_* */
+    int32_t useDithering;  /* nonzero: hash-based dither before rounding to UNORM8 / UNORM16 */
+    size_t pixelStride, rowPitch; /* bytes; pixelStride / bytes-per-component components are written per
+                                     pixel, those past numChannels as 0 (component 3: 1) */
+    const int32_t* dstColorSpaces; /* numChannels NTCB_COLOR_SPACE_* values, or NULL for all Linear */
 } NtcbReadChannelsParams;
 
 /* Host only, no GPU needed.  Parses and validates an NTC container and reports what it holds.
@@ -230,10 +268,23 @@ int ntcb_texture_set_decompress(NtcbTextureSet* textureSet, NtcbDecompressionSta
 int ntcb_texture_set_decompress_rows(NtcbTextureSet* textureSet, const int32_t* rowRanges, NtcbDecompressionStats* stats,
     int useInt8Weights);
 
-/* Copies decoded channels of one mip to host or device memory, pixel-interleaved with the given
-   strides, and returns when the data is there.  Replaces ITextureSet::ReadChannels
-   (include/libntc/ntc.h:902, src/TextureSet.cpp:915-985) for ChannelFormat::FLOAT16; the other
-   channel formats report NTCB_ERR_UNSUPPORTED. */
+/* Decompress followed by ReadChannels of every mip, fused: one kernel launch decodes the texels and
+   writes them in the client's format (no reference counterpart as one call; it stands in for
+   ITextureSet::Decompress, include/libntc/ntc.h:933, plus one ITextureSet::ReadChannels per mip,
+   :902, and gives the same bytes).  `destination` (NTCB_ADDRESS_SPACE_*) receives the mips one after
+   the other - mip m starts at byte (texels of the mips before it) x components x bytes-per-component -
+   each as rows of pixels without padding.  conversion->srcColorSpaces is ignored: the colour space
+   each channel is stored in comes from the container.  The set's fp16 texels are not produced, so
+   this call does not make ntcb_texture_set_read_channels usable.  Returns when the data is there. */
+int ntcb_texture_set_decompress_converted(NtcbTextureSet* textureSet, NtcbDecompressionStats* stats, int useInt8Weights,
+    const NtcbOutputConversion* conversion, int addressSpace, void* destination, size_t destinationBytes);
+
+/* Converts decoded channels of one mip to the requested channel format and colour spaces, writes
+   them pixel-interleaved with the given strides to host or device memory, and returns when the data
+   is there.  Replaces ITextureSet::ReadChannels (include/libntc/ntc.h:902, src/TextureSet.cpp:915-985)
+   and the CopyImageKernel behind it (src/ImageProcessing.cu:220-277).  Each channel is first taken
+   out of the colour space the container stores it in (channels[].colorSpace), then encoded to its
+   destination colour space. */
 int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadChannelsParams* params);
 
 /* Device address and size in bytes of one decoded mip in the internal layout: the counterpart of
@@ -243,6 +294,23 @@ int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void**
 
 /* Waits for everything queued on the texture set's stream. */
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet);
+
+/* One decoded mip (fp16, device memory, `layout`, `channels` channels per texel) converted into
+   pixel-interleaved client data in device memory with the given strides: the kernel behind
+   ntcb_texture_set_read_channels, for callers that hold the decoded texels themselves.  Replaces
+   cuda::CopyImage (src/ImageProcessing.cu:268-277) for the 1:1, texture-set-to-client direction.
+   Queued on `stream`; returns without waiting. */
+typedef struct NtcbConvertParams
+{
+    const void* deviceMip;
+    int32_t layout;          /* NtcbOutputLayout of deviceMip */
+    int32_t width, height, channels;
+    int32_t reserved;
+    void* deviceDestination;
+    size_t pixelStride, rowPitch; /* bytes */
+    NtcbOutputConversion conversion; /* components * bytes-per-component must not exceed pixelStride */
+} NtcbConvertParams;
+int ntcb_convert_channels(const NtcbConvertParams* params, void* stream);
 
 /* Size of the staging area built into the library for ntcb_read_channels_to_host_noalloc. */
 #define NTCB_NOALLOC_STAGING_BYTES (4u << 20)

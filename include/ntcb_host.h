@@ -50,6 +50,12 @@ public:
     virtual Status Decompress(DecompressionStats* pOutStats, bool useInt8Weights = false) = 0;
     // rowRanges: [mips][2] = {rowBegin, rowEnd} per mip (tile-row sharding); NULL = whole mips
     virtual Status DecompressRows(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights = false) = 0;
+    // Decompress and ReadChannels of every mip fused into one kernel launch: `destination` (host or
+    // device) receives the mips one after the other, each as rows of pixels of conversion.components
+    // values of conversion.channelFormat without padding; the fp16 texels are not stored.
+    // conversion.srcColorSpaces is ignored (the container's channel colour spaces apply).
+    virtual Status DecompressConverted(DecompressionStats* pOutStats, bool useInt8Weights,
+        NtcbOutputConversion const& conversion, int addressSpace, void* destination, size_t destinationBytes) = 0;
     virtual Status ReadChannels(ReadChannelsParameters const& params) = 0;
     virtual Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) = 0;
     virtual Status Synchronize() = 0;

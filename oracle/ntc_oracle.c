@@ -726,3 +726,171 @@ int ntco_sample(const NtcoTextureSet* set, const NtcoOptions* opt, const float* 
     free(net);
     return 0;
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * ReadChannels: output formats, colour spaces, dithering
+ * ------------------------------------------------------------------------------------------- */
+
+/* src/CudaUtils.h:92-108 */
+static float srgb_encode(float linear)
+{
+    return (linear <= 0.0031308f) ? linear * 12.92f : 1.055f * powf(linear, 1.0f / 2.4f) - 0.055f;
+}
+static float srgb_decode(float encoded)
+{
+    return (encoded <= 0.04045f) ? encoded / 12.92f : powf((encoded + 0.055f) / 1.055f, 2.4f);
+}
+
+/* src/CudaUtils.h:63-89 */
+static const float kHlgA = 0.17883277f, kHlgB = 0.28466892f, kHlgC = 0.55991073f;
+static float hlg_encode(float e)
+{
+    float sign = (e < 0.f) ? -1.f : 1.f;
+    e = fabsf(e);
+    return (e < 1.f) ? 0.5f * sqrtf(e) * sign : (kHlgA * logf(e - kHlgB) + kHlgC) * sign;
+}
+static float hlg_decode(float h)
+{
+    float sign = (h < 0.f) ? -1.f : 1.f;
+    h = fabsf(h);
+    return (h < 0.5f) ? 4.f * h * h * sign : (expf((h - kHlgC) / kHlgA) + kHlgB) * sign;
+}
+
+static float colorspace_decode(int space, float v) /* src/ImageProcessing.cu:86-98 */
+{
+    return space == 1 ? srgb_decode(v) : space == 2 ? hlg_decode(v) : v;
+}
+static float colorspace_encode(int space, float v) /* src/ImageProcessing.cu:100-112 */
+{
+    return space == 1 ? srgb_encode(v) : space == 2 ? hlg_encode(v) : v;
+}
+
+/* src/CudaUtils.h:111-184: per-pixel generator, Jenkins hash of the pixel index as seed, one
+   Murmur3 round per draw with the draw counter as key. */
+static uint32_t jenkins_hash(uint32_t a)
+{
+    a = (a + 0x7ed55d16u) + (a << 12);
+    a = (a ^ 0xc761c23cu) ^ (a >> 19);
+    a = (a + 0x165667b1u) + (a << 5);
+    a = (a + 0xd3a2646cu) ^ (a << 9);
+    a = (a + 0xfd7046c5u) + (a << 3);
+    a = (a ^ 0xb55a4f09u) ^ (a >> 16);
+    return a;
+}
+static uint32_t rotl32(uint32_t x, int r) { return (x << r) | (x >> (32 - r)); }
+static uint32_t murmur3_draw(uint32_t seed, uint32_t index)
+{
+    uint32_t k = index * 0xcc9e2d51u;
+    k = rotl32(k, 15) * 0x1b873593u;
+    uint32_t hash = seed ^ k;
+    hash = rotl32(hash, 13) * 5u + 0xe6546b64u;
+    hash ^= 4u;
+    hash ^= hash >> 16;
+    hash *= 0x85ebca6bu;
+    hash ^= hash >> 13;
+    hash *= 0xc2b2ae35u;
+    hash ^= hash >> 16;
+    return hash;
+}
+static float uint_to_unit_float(uint32_t v) /* NextFloat: [0, 1) from the low 23 bits */
+{
+    uint32_t bits = (v & 0x7fffffu) | 0x3f800000u;
+    float f;
+    memcpy(&f, &bits, 4);
+    return f - 1.f;
+}
+
+static int bytes_per_component(int format) /* src/TextureSet.cpp GetBytesPerPixelComponent */
+{
+    switch (format)
+    {
+    case 1: return 1;
+    case 2: case 3: return 2;
+    case 4: case 5: return 4;
+    default: return 0;
+    }
+}
+
+/* src/ImageProcessing.cu:139-164 */
+static void write_component(uint8_t* dst, int ch, int format, int space, float value, float dither)
+{
+    value = colorspace_encode(space, value);
+    switch (format)
+    {
+    case 1:
+    {
+        value += dither / 255.f;
+        float r = roundf(value * 255.f);
+        r = r < 255.f ? r : 255.f; /* NaN -> 255 as min(255, NaN) gives */
+        r = r > 0.f ? r : 0.f;
+        dst[ch] = (uint8_t)r;
+        break;
+    }
+    case 2:
+    {
+        value += dither / 65535.f;
+        float r = roundf(value * 65535.f);
+        r = r < 65535.f ? r : 65535.f;
+        r = r > 0.f ? r : 0.f;
+        uint16_t u = (uint16_t)r;
+        memcpy(dst + 2 * ch, &u, 2);
+        break;
+    }
+    case 3:
+    {
+        float c = value < 65504.f ? value : 65504.f;
+        c = c > -65504.f ? c : -65504.f;
+        uint16_t h = f2h(c);
+        memcpy(dst + 2 * ch, &h, 2);
+        break;
+    }
+    case 4:
+        memcpy(dst + 4 * ch, &value, 4);
+        break;
+    case 5:
+    {
+        float c = value > 0.f ? value : 0.f;
+        uint32_t u = c >= 4294967296.f ? 0xffffffffu : (uint32_t)c;
+        memcpy(dst + 4 * ch, &u, 4);
+        break;
+    }
+    }
+}
+
+int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* p, uint8_t* out)
+{
+    if (!texels || !p || !out)
+        return -1;
+    const int componentBytes = bytes_per_component(p->channelFormat);
+    if (!componentBytes || p->width <= 0 || p->height <= 0 || p->firstChannel < 0 || p->numChannels < 1 ||
+        p->firstChannel + p->numChannels > p->channels || p->pixelStride < 1 || p->rowPitch < p->pixelStride)
+        return -1;
+    const int dstChannels = (int)(p->pixelStride / (size_t)componentBytes); /* src/TextureSet.cpp:957 */
+    for (int y = 0; y < p->height; ++y)
+    {
+        for (int x = 0; x < p->width; ++x)
+        {
+            const uint16_t* src = texels + ((size_t)y * p->width + x) * p->channels + p->firstChannel;
+            uint8_t* dst = out + (size_t)y * p->rowPitch + (size_t)x * p->pixelStride;
+            const uint32_t seed = jenkins_hash((uint32_t)x + (uint32_t)y * (uint32_t)p->width);
+            uint32_t draw = 1;
+            for (int ch = 0; ch < dstChannels; ++ch)
+            {
+                float value;
+                if (ch < p->numChannels)
+                {
+                    const int srcSpace = p->srcColorSpaces ? p->srcColorSpaces[p->firstChannel + ch] : 0;
+                    value = colorspace_decode(srcSpace, h2f(src[ch]));
+                }
+                else
+                    value = ch == 3 ? 1.f : 0.f; /* src/ImageProcessing.cu:166-170 */
+                float dither = 0.f;
+                if (p->useDithering)
+                    dither = uint_to_unit_float(murmur3_draw(seed, draw++)) - 0.5f;
+                const int dstSpace = (ch < p->numChannels && p->dstColorSpaces) ? p->dstColorSpaces[ch] : 0;
+                write_component(dst, ch, p->channelFormat, dstSpace, value, dither);
+            }
+        }
+    }
+    return 0;
+}

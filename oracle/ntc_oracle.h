@@ -103,6 +103,29 @@ int ntco_decode_mip(const NtcoTextureSet* set, const NtcoOptions* opt, int mip, 
 int ntco_sample(const NtcoTextureSet* set, const NtcoOptions* opt, const float* queries /* [n][3] */,
     size_t numQueries, uint16_t* out);
 
+/* ITextureSet::ReadChannels on a decoded mip without resizing (src/TextureSet.cpp:915-985 calling
+   CopyImageKernel, src/ImageProcessing.cu:220-266): converts channels [firstChannel, firstChannel +
+   numChannels) of `texels` (fp16 bit patterns, interleaved [y][x][channels]) to `channelFormat`
+   (ntc::ChannelFormat values: 1 UNORM8, 2 UNORM16, 3 FLOAT16, 4 FLOAT32, 5 UINT32) and writes
+   pixelStride / bytesPerComponent components per pixel; components beyond numChannels get 0, or 1
+   for component 3.  Colour spaces are ntc::ColorSpace values (0 Linear, 1 sRGB, 2 HLG):
+   srcColorSpaces per channel of the set, dstColorSpaces per requested channel, NULL = all Linear.
+   The transfer functions are evaluated with the C library in binary32; the reference's kernel is
+   built with --use_fast_math (src/CMakeLists.txt:33), so its sRGB / HLG results and its dither
+   offsets can differ from these in the last bits.  Bytes of `out` outside the written components
+   are left alone.  Returns 0, or -1 on invalid arguments. */
+typedef struct NtcoReadChannels
+{
+    int width, height, channels;
+    int firstChannel, numChannels;
+    int channelFormat;
+    size_t pixelStride, rowPitch;
+    const int* srcColorSpaces;
+    const int* dstColorSpaces;
+    int useDithering;
+} NtcoReadChannels;
+int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* params, uint8_t* out);
+
 /* Element helpers exposed for unit tests. */
 uint16_t ntco_float_to_half(float value);
 float ntco_half_to_float(uint16_t bits);

@@ -47,6 +47,44 @@ NUMERICS_SPEC, NUMERICS_REF = 0, 1
 _oracle = None
 
 
+class ReadChannels(ctypes.Structure):
+    _fields_ = [("width", ctypes.c_int), ("height", ctypes.c_int), ("channels", ctypes.c_int),
+                ("firstChannel", ctypes.c_int), ("numChannels", ctypes.c_int), ("channelFormat", ctypes.c_int),
+                ("pixelStride", ctypes.c_size_t), ("rowPitch", ctypes.c_size_t),
+                ("srcColorSpaces", ctypes.POINTER(ctypes.c_int)), ("dstColorSpaces", ctypes.POINTER(ctypes.c_int)),
+                ("useDithering", ctypes.c_int)]
+
+
+FORMAT_DTYPES = {1: np.uint8, 2: np.uint16, 3: np.float16, 4: np.float32, 5: np.uint32}  # ntc::ChannelFormat
+
+
+def read_channels(texels: np.ndarray, channel_format: int, first_channel: int = 0, num_channels: Optional[int] = None,
+                  components: Optional[int] = None, src_color_spaces=None, dst_color_spaces=None,
+                  use_dithering: bool = False) -> np.ndarray:
+    """ReadChannels restated on the CPU: `texels` is a decoded mip [h][w][channels] (float16);
+    returns [h][w][components] in the channel format's dtype."""
+    texels = np.ascontiguousarray(texels, dtype=np.float16)
+    h, w, channels = texels.shape
+    n = channels - first_channel if num_channels is None else num_channels
+    count = n if components is None else components
+    dtype = np.dtype(FORMAT_DTYPES[channel_format])
+    out = np.zeros((h, w, count), dtype=dtype)
+    p = ReadChannels()
+    p.width, p.height, p.channels, p.firstChannel, p.numChannels, p.channelFormat = w, h, channels, first_channel, n, channel_format
+    p.pixelStride, p.rowPitch = count * dtype.itemsize, count * dtype.itemsize * w
+    keep = []
+    if src_color_spaces is not None:
+        keep.append((ctypes.c_int * channels)(*src_color_spaces))
+        p.srcColorSpaces = ctypes.cast(keep[-1], ctypes.POINTER(ctypes.c_int))
+    if dst_color_spaces is not None:
+        keep.append((ctypes.c_int * n)(*dst_color_spaces))
+        p.dstColorSpaces = ctypes.cast(keep[-1], ctypes.POINTER(ctypes.c_int))
+    p.useDithering = 1 if use_dithering else 0
+    if oracle_lib().ntco_read_channels(texels.ctypes.data, ctypes.byref(p), out.ctypes.data) != 0:
+        raise ValueError("ntco_read_channels rejected its arguments")
+    return out
+
+
 def build_oracle() -> None:
     subprocess.run(["make", "-s", "-C", HERE, "libntc_oracle.so"], check=True)
 
@@ -62,6 +100,7 @@ def oracle_lib():
                                         ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         lib.ntco_sample.argtypes = [ctypes.POINTER(_TextureSet), ctypes.POINTER(Options), ctypes.c_void_p,
                                     ctypes.c_size_t, ctypes.c_void_p]
+        lib.ntco_read_channels.argtypes = [ctypes.c_void_p, ctypes.POINTER(ReadChannels), ctypes.c_void_p]
         lib.ntco_float_to_half.restype = ctypes.c_uint16
         lib.ntco_float_to_half.argtypes = [ctypes.c_float]
         lib.ntco_half_to_float.restype = ctypes.c_float
@@ -158,6 +197,9 @@ def reference_lib():
         lib.ntcref_decompress.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
         lib.ntcref_read_mip.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                         ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+        lib.ntcref_read_channels.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                             ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t,
+                                             ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_void_p]
         lib.ntcref_close.argtypes = [ctypes.c_void_p]
         _ref = lib
     return _ref
@@ -175,11 +217,13 @@ def reference_probe(container: bytes) -> List[int]:
 class ReferenceDecoder:
     """The reference's CUDA decompression of one container, through its public API."""
 
-    def __init__(self, container: bytes, channels: int, device: int = 0):
+    def __init__(self, container: bytes, channels: int, device: int = 0, staging_bytes_per_pixel: Optional[int] = None):
         self._lib = reference_lib()
         self._container = container
         self._handle = ctypes.c_void_p()
-        rc = self._lib.ntcref_open(container, len(container), device, channels * 2, ctypes.byref(self._handle))
+        # the reference sizes its ReadChannels staging buffer from TextureSetFeatures::stagingBytesPerPixel
+        staging = channels * 2 if staging_bytes_per_pixel is None else staging_bytes_per_pixel
+        rc = self._lib.ntcref_open(container, len(container), device, staging, ctypes.byref(self._handle))
         if rc != 0:
             raise RuntimeError("reference open failed: %s" % self._lib.ntcref_last_error().decode())
         self.channels = channels
@@ -199,6 +243,24 @@ class ReferenceDecoder:
     def read_mip(self, mip: int, width: int, height: int) -> np.ndarray:
         out = np.empty((height, width, self.channels), dtype=np.float16)
         self.read_mip_into(mip, width, height, out.ctypes.data, False)
+        return out
+
+    def read_channels(self, mip: int, width: int, height: int, channel_format: int, first_channel: int = 0,
+                      num_channels: Optional[int] = None, components: Optional[int] = None, dst_color_spaces=None,
+                      use_dithering: bool = False) -> np.ndarray:
+        """ITextureSet::ReadChannels of the reference in any channel format, to host memory."""
+        n = self.channels - first_channel if num_channels is None else num_channels
+        count = n if components is None else components
+        dtype = np.dtype(FORMAT_DTYPES[channel_format])
+        out = np.zeros((height, width, count), dtype=dtype)
+        spaces = None
+        if dst_color_spaces is not None:
+            spaces = (ctypes.c_int * n)(*dst_color_spaces)
+        rc = self._lib.ntcref_read_channels(self._handle, mip, first_channel, n, width, height, channel_format,
+                                            count * dtype.itemsize, count * dtype.itemsize * width, spaces,
+                                            1 if use_dithering else 0, out.ctypes.data)
+        if rc != 0:
+            raise RuntimeError("reference ReadChannels failed: %s" % self._lib.ntcref_last_error().decode())
         return out
 
     def close(self) -> None:

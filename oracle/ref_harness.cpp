@@ -180,6 +180,40 @@ int ntcref_read_mip(void* opaque, int mipLevel, int firstChannel, int numChannel
     return 0;
 }
 
+// The general form of ITextureSet::ReadChannels on the decoded page: any channel format
+// (ntc::ChannelFormat value), strides, destination colour spaces (ntc::ColorSpace values, one per
+// channel, or NULL for Linear) and dithering; host destination.
+int ntcref_read_channels(void* opaque, int mipLevel, int firstChannel, int numChannels, int width, int height,
+    int channelFormat, size_t pixelStride, size_t rowPitch, const int* dstColorSpaces, int useDithering, void* destination)
+{
+    g_error[0] = 0;
+    RefHandle* handle = static_cast<RefHandle*>(opaque);
+    ntc::ColorSpace spaces[NTC_MAX_CHANNELS] = {};
+    for (int i = 0; i < numChannels && i < NTC_MAX_CHANNELS && dstColorSpaces; ++i)
+        spaces[i] = ntc::ColorSpace(dstColorSpaces[i]);
+    ntc::ReadChannelsParameters params;
+    params.page = ntc::TextureDataPage::Output;
+    params.mipLevel = mipLevel;
+    params.firstChannel = firstChannel;
+    params.numChannels = numChannels;
+    params.pOutData = static_cast<unsigned char*>(destination);
+    params.addressSpace = ntc::AddressSpace::Host;
+    params.width = width;
+    params.height = height;
+    params.pixelStride = pixelStride;
+    params.rowPitch = rowPitch;
+    params.channelFormat = ntc::ChannelFormat(channelFormat);
+    params.dstColorSpaces = dstColorSpaces ? spaces : nullptr;
+    params.useDithering = useDithering != 0;
+    ntc::Status status = handle->textureSet->ReadChannels(params);
+    if (status != ntc::Status::Ok)
+    {
+        SetError("ReadChannels", status);
+        return int(status);
+    }
+    return 0;
+}
+
 void ntcref_close(void* opaque)
 {
     RefHandle* handle = static_cast<RefHandle*>(opaque);

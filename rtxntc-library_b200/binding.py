@@ -36,12 +36,42 @@ class MipDesc(ctypes.Structure):
                 ("rowBegin", ctypes.c_int32), ("rowEnd", ctypes.c_int32)]
 
 
+class OutputConversion(ctypes.Structure):
+    _fields_ = [("channelFormat", ctypes.c_int32), ("components", ctypes.c_int32),
+                ("firstChannel", ctypes.c_int32), ("numChannels", ctypes.c_int32),
+                ("useDithering", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("srcColorSpaces", ctypes.c_uint8 * 16), ("dstColorSpaces", ctypes.c_uint8 * 16)]
+
+
+def make_conversion(channel_format: int, num_channels: int, first_channel: int = 0, components: Optional[int] = None,
+                    src_color_spaces=None, dst_color_spaces=None, use_dithering: bool = False) -> OutputConversion:
+    """Channels [first_channel, first_channel + num_channels) -> pixels of `components` values
+    (default num_channels) of `channel_format`; colour spaces are given per requested channel."""
+    conversion = OutputConversion()
+    conversion.channelFormat = channel_format
+    conversion.components = num_channels if components is None else components
+    conversion.firstChannel, conversion.numChannels = first_channel, num_channels
+    conversion.useDithering = 1 if use_dithering else 0
+    for i, space in enumerate(src_color_spaces or []):
+        conversion.srcColorSpaces[i] = space
+    for i, space in enumerate(dst_color_spaces or []):
+        conversion.dstColorSpaces[i] = space
+    return conversion
+
+
 class DecodeParams(ctypes.Structure):
     _fields_ = [("latents", ctypes.c_void_p), ("network", ctypes.c_void_p), ("out", ctypes.c_void_p),
                 ("status", ctypes.c_void_p),
                 ("numMips", ctypes.c_int32), ("numFeatures", ctypes.c_int32), ("channels", ctypes.c_int32),
                 ("weightMode", ctypes.c_int32), ("outputLayout", ctypes.c_int32), ("reserved", ctypes.c_int32),
-                ("mips", MipDesc * MAX_MIPS)]
+                ("mips", MipDesc * MAX_MIPS), ("conversion", ctypes.POINTER(OutputConversion))]
+
+
+class ConvertParams(ctypes.Structure):
+    _fields_ = [("deviceMip", ctypes.c_void_p), ("layout", ctypes.c_int32), ("width", ctypes.c_int32),
+                ("height", ctypes.c_int32), ("channels", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("deviceDestination", ctypes.c_void_p), ("pixelStride", ctypes.c_size_t), ("rowPitch", ctypes.c_size_t),
+                ("conversion", OutputConversion)]
 
 
 class SampleParams(ctypes.Structure):
@@ -69,12 +99,17 @@ class ReadChannelsParams(ctypes.Structure):
     _fields_ = [("mipLevel", ctypes.c_int32), ("firstChannel", ctypes.c_int32), ("numChannels", ctypes.c_int32),
                 ("addressSpace", ctypes.c_int32), ("pOutData", ctypes.c_void_p),
                 ("width", ctypes.c_int32), ("height", ctypes.c_int32),
-                ("channelFormat", ctypes.c_int32), ("reserved", ctypes.c_int32),
-                ("pixelStride", ctypes.c_size_t), ("rowPitch", ctypes.c_size_t)]
+                ("channelFormat", ctypes.c_int32), ("useDithering", ctypes.c_int32),
+                ("pixelStride", ctypes.c_size_t), ("rowPitch", ctypes.c_size_t),
+                ("dstColorSpaces", ctypes.POINTER(ctypes.c_int32))]
 
 
 ADDRESS_SPACE_HOST, ADDRESS_SPACE_DEVICE = 0, 1
-CHANNEL_FORMAT_FLOAT16 = 3
+# ntc::ChannelFormat and ntc::ColorSpace values
+CHANNEL_FORMAT_UNORM8, CHANNEL_FORMAT_UNORM16, CHANNEL_FORMAT_FLOAT16, CHANNEL_FORMAT_FLOAT32, CHANNEL_FORMAT_UINT32 = 1, 2, 3, 4, 5
+COLOR_SPACE_LINEAR, COLOR_SPACE_SRGB, COLOR_SPACE_HLG = 0, 1, 2
+CHANNEL_FORMAT_DTYPES = {CHANNEL_FORMAT_UNORM8: np.uint8, CHANNEL_FORMAT_UNORM16: np.uint16, CHANNEL_FORMAT_FLOAT16: np.float16,
+                         CHANNEL_FORMAT_FLOAT32: np.float32, CHANNEL_FORMAT_UINT32: np.uint32}
 
 
 class NtcbError(RuntimeError):
@@ -117,6 +152,10 @@ def lib():
         handle.ntcb_texture_set_decompress_rows.argtypes = [
             ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(DecompressionStats), ctypes.c_int]
         handle.ntcb_texture_set_read_channels.argtypes = [ctypes.c_void_p, ctypes.POINTER(ReadChannelsParams)]
+        handle.ntcb_texture_set_decompress_converted.argtypes = [
+            ctypes.c_void_p, ctypes.POINTER(DecompressionStats), ctypes.c_int, ctypes.POINTER(OutputConversion), ctypes.c_int,
+            ctypes.c_void_p, ctypes.c_size_t]
+        handle.ntcb_convert_channels.argtypes = [ctypes.POINTER(ConvertParams), ctypes.c_void_p]
         handle.ntcb_texture_set_device_mip.argtypes = [
             ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t)]
         handle.ntcb_texture_set_synchronize.argtypes = [ctypes.c_void_p]
@@ -154,10 +193,14 @@ def out_elements(geo: Geometry) -> int:
 
 def fill_params(geo: Geometry, latents_ptr: int, network_ptr: int, out_ptr: int, status_ptr: int, weight_mode: int,
                 layout: int = LAYOUT_INTERLEAVED, mips: Optional[Sequence[int]] = None,
-                row_ranges: Optional[dict] = None) -> DecodeParams:
+                row_ranges: Optional[dict] = None, conversion: Optional[OutputConversion] = None) -> DecodeParams:
     """Describes a decode of `mips` (default: all) of a texture set whose latents are resident in
-    the reference's encoded-pixel order.  `row_ranges` maps mip -> (rowBegin, rowEnd)."""
+    the reference's encoded-pixel order.  `row_ranges` maps mip -> (rowBegin, rowEnd).  With
+    `conversion` the kernel writes converted pixels (mip after mip, no padding) instead of fp16."""
     params = DecodeParams()
+    if conversion is not None:
+        params._conversion = conversion  # keeps the pointee alive as long as the parameters
+        params.conversion = ctypes.pointer(conversion)
     params.latents = latents_ptr
     params.network = network_ptr
     params.out = out_ptr
@@ -180,10 +223,36 @@ def fill_params(geo: Geometry, latents_ptr: int, network_ptr: int, out_ptr: int,
         d.hiPlane = d.hiWidth * d.hiHeight
         d.loPlane = d.loWidth * d.loHeight
         d.positionScale, d.positionLod = cm.position_scale, cm.position_lod
-        d.outOffset = cm.texel_offset * geo.channels
+        d.outOffset = cm.texel_offset * (geo.channels if conversion is None else conversion.components)
         begin, end = (0, cm.height) if not row_ranges or mip not in row_ranges else row_ranges[mip]
         d.rowBegin, d.rowEnd = begin, end
     return params
+
+
+def convert_channels(texels, conversion: OutputConversion, layout: int = LAYOUT_INTERLEAVED, width: Optional[int] = None,
+                     height: Optional[int] = None, channels: Optional[int] = None):
+    """Runs the ReadChannels conversion kernel on decoded texels that the caller holds: `texels` is
+    a CUDA float16 tensor, [height][width][channels] for the interleaved layout (the sizes are then
+    taken from its shape).  Returns a CUDA tensor [height][width][components] of the channel
+    format's element type (uint16 / uint32 data as int16 / int32 bit patterns)."""
+    import torch
+
+    if layout == LAYOUT_INTERLEAVED and width is None:
+        height, width, channels = texels.shape
+    dtype = {CHANNEL_FORMAT_UNORM8: torch.uint8, CHANNEL_FORMAT_UNORM16: torch.int16, CHANNEL_FORMAT_FLOAT16: torch.float16,
+             CHANNEL_FORMAT_FLOAT32: torch.float32, CHANNEL_FORMAT_UINT32: torch.int32}[conversion.channelFormat]
+    out = torch.zeros((height, width, conversion.components), dtype=dtype, device=texels.device)
+    params = ConvertParams()
+    params.deviceMip = texels.data_ptr()
+    params.layout, params.width, params.height, params.channels = layout, width, height, channels
+    params.deviceDestination = out.data_ptr()
+    params.pixelStride = conversion.components * out.element_size()
+    params.rowPitch = params.pixelStride * width
+    params.conversion = conversion
+    with torch.cuda.device(texels.device):
+        stream = torch.cuda.current_stream(texels.device).cuda_stream
+        check(lib().ntcb_convert_channels(ctypes.byref(params), ctypes.c_void_p(stream)))
+    return out
 
 
 class ResidentTextureSet:
@@ -212,11 +281,23 @@ class ResidentTextureSet:
         return cls(synthetic_set.geometry, synthetic_set.packed_latents(), synthetic_set.int8_blob,
                    synthetic_set.fp8_blob, **kwargs)
 
-    def params(self, use_int8: bool, out=None, mips=None, row_ranges=None) -> DecodeParams:
+    def params(self, use_int8: bool, out=None, mips=None, row_ranges=None, conversion=None) -> DecodeParams:
         mode = WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8
         out = self.out if out is None else out
         return fill_params(self.geometry, self.latents.data_ptr(), self.networks[mode].data_ptr(), out.data_ptr(),
-                           self.status.data_ptr(), mode, self.layout, mips, row_ranges)
+                           self.status.data_ptr(), mode, self.layout, mips, row_ranges, conversion)
+
+    def decode_converted(self, use_int8: bool, conversion: OutputConversion, mips=None, row_ranges=None):
+        """Decode with the converting epilogue into a fresh device buffer covering the whole mip
+        chain; returns it as a flat CUDA tensor of the channel format's element type (uint32 data
+        comes back as int32 bit patterns)."""
+        torch = self.torch
+        dtype = {CHANNEL_FORMAT_UNORM8: torch.uint8, CHANNEL_FORMAT_UNORM16: torch.int16, CHANNEL_FORMAT_FLOAT16: torch.float16,
+                 CHANNEL_FORMAT_FLOAT32: torch.float32, CHANNEL_FORMAT_UINT32: torch.int32}[conversion.channelFormat]
+        out = torch.zeros(self.geometry.total_texels * conversion.components, dtype=dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            self.launch(self.params(use_int8, out=out, mips=mips, row_ranges=row_ranges, conversion=conversion))
+        return out
 
     def launch(self, params: DecodeParams) -> None:
         """Queues one decode on torch's current stream of this device."""
@@ -288,6 +369,12 @@ class Context:
             lib().ntcb_context_destroy(self.handle)
             self.handle = ctypes.c_void_p()
 
+    def __enter__(self) -> "Context":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
 
 class TextureSet:
     """ntcb_texture_set_*: a compressed texture set loaded from an NTC container (the counterpart
@@ -318,25 +405,64 @@ class TextureSet:
 
     def read_channels_into(self, mip: int, address: int, to_device: bool = False, first_channel: int = 0,
                            num_channels: Optional[int] = None, pixel_stride: Optional[int] = None,
-                           row_pitch: Optional[int] = None) -> None:
+                           row_pitch: Optional[int] = None, channel_format: int = CHANNEL_FORMAT_FLOAT16,
+                           dst_color_spaces=None, use_dithering: bool = False) -> None:
         w, h = self.mip_size(mip)
         n = self.desc.channels - first_channel if num_channels is None else num_channels
+        component = np.dtype(CHANNEL_FORMAT_DTYPES.get(channel_format, np.float16)).itemsize
         params = ReadChannelsParams()
         params.mipLevel, params.firstChannel, params.numChannels = mip, first_channel, n
         params.addressSpace = ADDRESS_SPACE_DEVICE if to_device else ADDRESS_SPACE_HOST
         params.pOutData = address
         params.width, params.height = w, h
-        params.channelFormat = CHANNEL_FORMAT_FLOAT16
-        params.pixelStride = 2 * n if pixel_stride is None else pixel_stride
+        params.channelFormat = channel_format
+        params.useDithering = 1 if use_dithering else 0
+        params.pixelStride = component * n if pixel_stride is None else pixel_stride
         params.rowPitch = params.pixelStride * w if row_pitch is None else row_pitch
+        spaces = None
+        if dst_color_spaces is not None:
+            spaces = (ctypes.c_int32 * len(dst_color_spaces))(*dst_color_spaces)
+            params.dstColorSpaces = ctypes.cast(spaces, ctypes.POINTER(ctypes.c_int32))
         check(lib().ntcb_texture_set_read_channels(self.handle, ctypes.byref(params)))
 
-    def read_mip(self, mip: int, first_channel: int = 0, num_channels: Optional[int] = None) -> np.ndarray:
+    def read_mip(self, mip: int, first_channel: int = 0, num_channels: Optional[int] = None,
+                 channel_format: int = CHANNEL_FORMAT_FLOAT16, dst_color_spaces=None, use_dithering: bool = False,
+                 components: Optional[int] = None) -> np.ndarray:
+        """One decoded mip as [height][width][components] in the given channel format; `components`
+        (default: the number of channels read) above that number adds the default components."""
         w, h = self.mip_size(mip)
         n = self.desc.channels - first_channel if num_channels is None else num_channels
-        out = np.empty((h, w, n), dtype=np.float16)
-        self.read_channels_into(mip, out.ctypes.data, False, first_channel, n)
+        dtype = np.dtype(CHANNEL_FORMAT_DTYPES[channel_format])
+        count = n if components is None else components
+        out = np.empty((h, w, count), dtype=dtype)
+        self.read_channels_into(mip, out.ctypes.data, False, first_channel, n, count * dtype.itemsize, None, channel_format,
+                                dst_color_spaces, use_dithering)
         return out
+
+    def decompress_converted(self, conversion: OutputConversion, use_int8: bool = False, want_stats: bool = False,
+                             device_address: Optional[int] = None):
+        """Decompress + ReadChannels of every mip in one launch.  Returns (list of per-mip host arrays
+        [h][w][components], gpu milliseconds or None); with `device_address` the pixels go to that
+        device buffer instead and the list is empty."""
+        dtype = np.dtype(CHANNEL_FORMAT_DTYPES.get(conversion.channelFormat, np.uint8))  # the library rejects unknown formats
+        total = self.desc.totalTexels * max(conversion.components, 1)
+        stats = DecompressionStats()
+        stats_ref = ctypes.byref(stats) if want_stats else None
+        if device_address is not None:
+            check(lib().ntcb_texture_set_decompress_converted(self.handle, stats_ref, 1 if use_int8 else 0,
+                                                               ctypes.byref(conversion), ADDRESS_SPACE_DEVICE, device_address,
+                                                               total * dtype.itemsize))
+            return [], (stats.gpuTimeMilliseconds if want_stats else None)
+        flat = np.empty(total, dtype=dtype)
+        check(lib().ntcb_texture_set_decompress_converted(self.handle, stats_ref, 1 if use_int8 else 0, ctypes.byref(conversion),
+                                                           ADDRESS_SPACE_HOST, flat.ctypes.data, flat.nbytes))
+        mips, offset = [], 0
+        for mip in range(self.desc.mips):
+            w, h = self.mip_size(mip)
+            count = w * h * conversion.components
+            mips.append(flat[offset:offset + count].reshape(h, w, conversion.components))
+            offset += count
+        return mips, (stats.gpuTimeMilliseconds if want_stats else None)
 
     def device_mip(self, mip: int) -> Tuple[int, int]:
         """Device address and size in bytes of one decoded mip in the internal layout."""

@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import json
 import struct
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -84,10 +84,15 @@ class _BinaryChunk:
         return bytes(self.data)
 
 
-def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: bytes, fp8_blob: bytes) -> bytes:
+COLOR_SPACE_NAMES = ("Linear", "sRGB", "HLG")  # ntc::ColorSpace values 0, 1, 2
+
+
+def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: bytes, fp8_blob: bytes,
+                    channel_color_spaces: Optional[Sequence[int]] = None) -> bytes:
     """Serialises one compressed texture set.
 
-    latents[m] is the u16 array [layers][height][width] of neural mip m.
+    latents[m] is the u16 array [layers][height][width] of neural mip m.  channel_color_spaces, when
+    given, holds one ntc::ColorSpace value per channel (the colour space the channel was stored in).
     """
     chunk = _BinaryChunk()
     latent_entries = []
@@ -113,6 +118,10 @@ def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: byt
     mlp_versions = [mlp_entry(split_int8_blob(int8_blob), False), mlp_entry(split_fp8_blob(fp8_blob), True)]
     color_mips = [{"width": cm.width, "height": cm.height, "latentMip": cm.neural_lod,
                    "positionLod": cm.position_lod, "positionScale": cm.position_scale} for cm in geo.color_mips]
+    channel_entries = []
+    if channel_color_spaces is not None:
+        assert len(channel_color_spaces) == geo.channels
+        channel_entries = [{} if space == 0 else {"colorSpace": COLOR_SPACE_NAMES[space]} for space in channel_color_spaces]
     document = {
         "schemaVersion": 3,
         "width": geo.width,
@@ -122,7 +131,7 @@ def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: byt
         "latentShape": {"numFeatures": geo.num_features},
         "mlpVersions": mlp_versions,
         "textures": [],
-        "channels": [],
+        "channels": channel_entries,
         "latents": latent_entries,
         "colorMips": color_mips,
         "views": chunk.views,

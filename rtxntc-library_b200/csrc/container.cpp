@@ -545,6 +545,40 @@ int LoadContainer(const void* data, size_t size, LoadedSet& out)
         // does (src/TextureSet.cpp:450-463); the stored values only serve the graphics path.
     }
 
+    // channel headers: the colour space each channel was stored in (src/TextureSetMetadata.cpp:479-495)
+    for (int c = 0; c < kMaxChannels; ++c)
+        out.channelColorSpaces[c] = 0;
+    const std::vector<json::Value>* channelHeaders = GetArray(document, "channels");
+    if (channelHeaders && !channelHeaders->empty())
+    {
+        if (channelHeaders->size() != size_t(numChannels) && channelHeaders->size() != size_t(geo.channels))
+        {
+            SetError("The file describes %d texture channels while %d are expected", int(channelHeaders->size()), geo.channels);
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        }
+        for (size_t c = 0; c < channelHeaders->size(); ++c)
+        {
+            const json::Value& entry = (*channelHeaders)[c];
+            std::string space;
+            if (entry.kind != json::Kind::Object)
+            {
+                SetError("Document: 'channels' must hold objects.");
+                return NTCB_ERR_FILE_UNRECOGNIZED;
+            }
+            if (!GetString(entry, "colorSpace", space) || space == "Linear")
+                out.channelColorSpaces[c] = 0;
+            else if (space == "sRGB")
+                out.channelColorSpaces[c] = 1;
+            else if (space == "HLG")
+                out.channelColorSpaces[c] = 2;
+            else
+            {
+                SetError("Channel %zu has an unknown color space '%s'.", c, space.c_str());
+                return NTCB_ERR_FILE_UNRECOGNIZED;
+            }
+        }
+    }
+
     // latent planes -> device order
     out.latents.resize(size_t(geo.TotalLatentPixels()) * geo.numLayers);
     for (int m = 0; m < geo.numNeuralMips; ++m)

@@ -46,6 +46,7 @@ struct LoadedSet
     std::vector<uint16_t> latents;
     std::vector<uint8_t> int8Blob; // GenericInt8, empty when the file has no Int8 network
     std::vector<uint8_t> fp8Blob;  // GenericFP8, empty when the file has no FloatE4M3 network
+    int channelColorSpaces[kMaxChannels] = {}; // ntc::ColorSpace each channel is stored in (0 Linear, 1 sRGB, 2 HLG)
 };
 
 // Parses a container held in memory.  Returns an NtcbStatus and sets the thread-local error

@@ -33,6 +33,7 @@
 #include <stdint.h>
 
 #include "decode_kernel.h"
+#include "output_convert.cuh"
 
 namespace ntcb
 {
@@ -508,8 +509,10 @@ struct TileContext
     uint4* rowChunk;   // this thread's 16-byte slot in chunk 0 of its half's A operand
     uint32_t networkBase;
     int tile, x, y;
-    uint32_t* out;          // where this thread's first channel pair goes (nullptr: store nothing)
-    uint32_t outStepWords;  // 32-bit words between consecutive channel pairs
+    uint32_t* out;          // where this thread's first channel pair goes (nullptr: store nothing); with a
+                            // converting epilogue: the address of the thread's pixel in the client's format
+    uint32_t outStepWords;  // 32-bit words between consecutive channel pairs; with a converting epilogue:
+                            // the pixel's linear index in its mip (the dither seed)
 };
 
 // First half of a layer of the MLP for the CTA's current tile: barrier and MMA issue (both halves
@@ -554,10 +557,73 @@ __device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
 
 // Second half of a layer: waits for the MMA, then applies the activation and writes the next
 // layer's A operand (layers 0-2) or runs the output epilogue (layer 3).
-template <bool kFp8, int kLayer>
-__device__ __forceinline__ void ConsumeLayer(uint32_t* status, int channels, const SharedStorage& shared,
+// Converting epilogue: the thread's (scrubbed) fp16 channel pairs -> the pixel in the client's
+// format, stored at ctx.out.  What ITextureSet::ReadChannels would produce from the stored texels
+// (src/TextureSet.cpp:915-985, src/ImageProcessing.cu:220-266).
+__device__ __forceinline__ void StoreConverted(const OutputConversion& conversion, int firstChannel, int numChannels,
+    const TileContext& ctx, const uint32_t (&bits)[8])
+{
+    // The channels are picked with a run-time index: park them in the thread's own slots of the A
+    // operand, which the tensor core has finished reading (layer 3's MMA has completed).
+    uint4* slot = ctx.rowChunk;
+    slot[0] = make_uint4(bits[0], bits[1], bits[2], bits[3]);
+    slot[128] = make_uint4(bits[4], bits[5], bits[6], bits[7]);
+    const unsigned char* parked = reinterpret_cast<const unsigned char*>(slot);
+
+    const int componentBytes = BytesPerComponent(conversion.format);
+    const int perWord = 4 / componentBytes;
+    const int pixelBytes = conversion.dstChannels * componentBytes;
+    const uint32_t seed = conversion.dither ? DitherSeed(ctx.outStepWords) : 0u;
+    unsigned char* pixel = reinterpret_cast<unsigned char*>(ctx.out);
+    // the pixel's address is a multiple of its size: it decides the widest store
+    const int storeBytes = (pixelBytes & 3) == 0 ? 4 : (pixelBytes & 1) == 0 ? 2 : 1;
+
+    for (int first = 0; first < conversion.dstChannels; first += perWord)
+    {
+        uint32_t word = 0;
+        int count = 0;
+        for (int k = 0; k < perWord; ++k)
+        {
+            const int c = first + k;
+            if (c >= conversion.dstChannels)
+                break;
+            const float dither = conversion.dither ? DitherDraw(seed, uint32_t(c) + 1u) : 0.f;
+            uint32_t component;
+            if (c < numChannels)
+            {
+                const int channel = firstChannel + c;
+                const __half texel = *reinterpret_cast<const __half*>(parked + (channel >> 3) * 2048 + (channel & 7) * 2);
+                component = ConvertComponent(conversion, c, texel, dither);
+            }
+            else
+                component = DefaultComponent(conversion, c, dither);
+            word |= component << (8 * componentBytes * k);
+            ++count;
+        }
+        unsigned char* at = pixel + first * componentBytes;
+        const int bytes = count * componentBytes;
+        if (storeBytes == 4)
+            *reinterpret_cast<uint32_t*>(at) = word;
+        else if (storeBytes == 2)
+        {
+            *reinterpret_cast<uint16_t*>(at) = uint16_t(word);
+            if (bytes > 2)
+                *reinterpret_cast<uint16_t*>(at + 2) = uint16_t(word >> 16);
+        }
+        else
+        {
+            for (int b = 0; b < bytes; ++b)
+                at[b] = (unsigned char)(word >> (8 * b));
+        }
+    }
+}
+
+template <bool kFp8, int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedStorage& shared,
     const TileContext& ctx, uint32_t& phase, int& failed)
 {
+    uint32_t* const status = params.status;
+    const int channels = params.channels;
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
     constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
 
@@ -658,7 +724,16 @@ __device__ __forceinline__ void ConsumeLayer(uint32_t* status, int channels, con
                 }
             }
         }
-        if (ctx.out)
+        if constexpr (kConvert)
+        {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j >= channelPairs)
+                    bits[j] = 0;
+            if (ctx.out)
+                StoreConverted(params.conversion, params.firstChannel, params.numChannels, ctx, bits);
+        }
+        else if (ctx.out)
         {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -668,13 +743,13 @@ __device__ __forceinline__ void ConsumeLayer(uint32_t* status, int channels, con
     }
 }
 
-template <bool kFp8, int kLayer>
-__device__ __forceinline__ int RunLayer(uint32_t* status, int channels, const SharedStorage& shared,
+template <bool kFp8, int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ int RunLayer(const Params& params, const SharedStorage& shared,
     const TileContext& ctx, uint32_t& phase, int& failed)
 {
     if (IssueLayer<kFp8, kLayer>(ctx, failed))
         return 1;
-    ConsumeLayer<kFp8, kLayer>(status, channels, shared, ctx, phase, failed);
+    ConsumeLayer<kFp8, kLayer, kConvert>(params, shared, ctx, phase, failed);
     return 0;
 }
 
@@ -743,8 +818,9 @@ __device__ __forceinline__ void BuildInputs(const KernelParams& params, const Ke
         ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
 }
 
-template <bool kFp8>
-__global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8) DecodeKernel(const __grid_constant__ KernelParams params)
+template <bool kFp8, bool kConvert>
+__global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConverting : kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8)
+    DecodeKernel(const __grid_constant__ KernelParams params)
 {
     __shared__ SharedStorage shared;
 
@@ -834,8 +910,20 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
             const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
                                           : (uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x)) * uint32_t(params.channels);
             const bool inside = ctx.x < mip.width && ctx.y < mip.rowEnd;
-            ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
-            ctx.outStepWords = planar ? uint32_t(mip.width) : 1u; // channel pairs are 2 * width or 2 elements apart
+            if constexpr (kConvert)
+            {
+                // pixels of dstChannels components, rows without padding; outOffset counts components
+                const uint32_t pixelIndex = uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x);
+                const size_t component = size_t(mip.outOffset) + size_t(pixelIndex) * size_t(params.conversion.dstChannels);
+                unsigned char* bytes = reinterpret_cast<unsigned char*>(params.out) + component * BytesPerComponent(params.conversion.format);
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(bytes) : nullptr;
+                ctx.outStepWords = pixelIndex;
+            }
+            else
+            {
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
+                ctx.outStepWords = planar ? uint32_t(mip.width) : 1u; // channel pairs are 2 * width or 2 elements apart
+            }
         }
 
         // ---- 1. this tile's network inputs -> A operand (the last MMA that read the A operand has
@@ -854,12 +942,12 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
             place = locate(nextTile, place.mipIndex);
             PrepareTile<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
         }
-        ConsumeLayer<kFp8, 0>(params.status, params.channels, shared, ctx, phase, failed);
+        ConsumeLayer<kFp8, 0, false>(params, shared, ctx, phase, failed);
 
         // ---- 3./4. layers 1-3 (their barriers also order the next tile's tables before its use) ---
-        aborted = RunLayer<kFp8, 1>(params.status, params.channels, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 2>(params.status, params.channels, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 3>(params.status, params.channels, shared, ctx, phase, failed);
+        aborted = RunLayer<kFp8, 1, false>(params, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 2, false>(params, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 3, kConvert>(params, shared, ctx, phase, failed);
         if (aborted)
             break;
         tile = nextTile;
@@ -977,10 +1065,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
                 ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
         }
 
-        aborted = RunLayer<kFp8, 0>(params.status, params.channels, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 1>(params.status, params.channels, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 2>(params.status, params.channels, shared, ctx, phase, failed);
-        if (!aborted) aborted = RunLayer<kFp8, 3>(params.status, params.channels, shared, ctx, phase, failed);
+        aborted = RunLayer<kFp8, 0, false>(params, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 1, false>(params, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 2, false>(params, shared, ctx, phase, failed);
+        if (!aborted) aborted = RunLayer<kFp8, 3, false>(params, shared, ctx, phase, failed);
         if (aborted)
             break;
     }
@@ -1007,10 +1095,17 @@ cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStr
 
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
 {
-    if (fp8)
-        DecodeKernel<true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+    if (params.convert)
+    {
+        if (fp8)
+            DecodeKernel<true, true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+        else
+            DecodeKernel<false, true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+    }
+    else if (fp8)
+        DecodeKernel<true, false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
     else
-        DecodeKernel<false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
+        DecodeKernel<false, false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
     return cudaGetLastError();
 }
 

@@ -5,6 +5,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "output_convert.cuh"
+
+struct NtcbOutputConversion; // include/ntcb.h
+
 namespace ntcb
 {
 
@@ -14,6 +18,7 @@ constexpr int kThreadsPerCta = kTileWidth * kTileHeight; // one thread per texel
 constexpr int kOperandBytes = 128 * 64; // A operand of one half: 128 rows x 64 bytes
 constexpr int kCtasPerSmInt8 = 4;  // resident CTAs per SM the two kernel variants are compiled for
 constexpr int kCtasPerSmFp8 = 4;
+constexpr int kCtasPerSmConverting = 3; // ... and the variants with a converting epilogue (either weight mode)
 constexpr int kTmemColumnsPerHalf = 64;    // widest accumulator (layer 0: 64 outputs)
 constexpr int kTmemColumns = 2 * kTmemColumnsPerHalf;
 constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait is declared expired
@@ -62,6 +67,10 @@ struct KernelParams
     int channels;
     int outputLayout;
     int totalTiles;
+    // converting epilogue (convert != 0): `out` receives pixels in the client's format instead of fp16 texels
+    int convert;
+    int firstChannel, numChannels; // channels the converted pixel starts with
+    OutputConversion conversion;
     KernelMip mips[16];
 };
 
@@ -78,6 +87,10 @@ struct SampleParams
     int channels;
     KernelMip mips[16];
 };
+
+// Checks a client's conversion request (NtcbOutputConversion of the C ABI) against a texture set of
+// `channels` channels and packs it for the kernels; returns an NtcbStatus.
+int MakeOutputConversion(const ::NtcbOutputConversion& request, int channels, OutputConversion& out);
 
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
 cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream);

@@ -50,10 +50,11 @@ constexpr int kLayerOutputs[4] = {64, 48, 32, 16};
 constexpr int kLayerPaddedK[4] = {64, 64, 64, 32};
 constexpr int kWeightOffsets[4] = {kWeightOffset0, kWeightOffset1, kWeightOffset2, kWeightOffset3};
 
-bool ValidMip(const NtcbMipDesc& m)
+// `pairedOutput`: the launch stores fp16 channel pairs as 32-bit words, so a mip must start on one.
+bool ValidMip(const NtcbMipDesc& m, bool pairedOutput)
 {
     return !(m.width < 1 || m.height < 1 || m.hiWidth < 1 || m.hiHeight < 1 || m.loWidth < 1 || m.loHeight < 1 ||
-             m.rowBegin < 0 || m.rowEnd > m.height || m.rowBegin > m.rowEnd || (m.outOffset & 1) ||
+             m.rowBegin < 0 || m.rowEnd > m.height || m.rowBegin > m.rowEnd || (pairedOutput && (m.outOffset & 1)) ||
              m.hiPlane < uint64_t(m.hiWidth) * m.hiHeight || m.loPlane < uint64_t(m.loWidth) * m.loHeight);
 }
 
@@ -90,17 +91,66 @@ void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km)
     km.firstTile = 0;
 }
 
-// Number of CTAs that fill the current device, cached per device.
-int ResidentCtas(bool fp8, int* outCtas)
+} // namespace
+
+// Checks a client's conversion request against a texture set of `channels` channels and packs it
+// for the kernels.
+int MakeOutputConversion(const NtcbOutputConversion& request, int channels, OutputConversion& out)
 {
-    static std::atomic<int> cache[64][2];
+    out = OutputConversion{};
+    if (BytesPerComponent(request.channelFormat) == 0)
+    {
+        SetError("Unknown channel format %d.", request.channelFormat);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (request.components < 1 || request.components > NTCB_MAX_CHANNELS)
+    {
+        SetError("components (%d) must be between 1 and %d.", request.components, NTCB_MAX_CHANNELS);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (request.firstChannel < 0 || request.firstChannel >= channels)
+    {
+        SetError("firstChannel (%d) must be between 0 and %d.", request.firstChannel, channels - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (request.numChannels < 1 || request.numChannels > channels - request.firstChannel)
+    {
+        SetError("For the provided firstChannel (%d), numChannels (%d) must be between 1 and %d.", request.firstChannel,
+            request.numChannels, channels - request.firstChannel);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    out.format = request.channelFormat;
+    out.dstChannels = request.components;
+    out.dither = request.useDithering != 0;
+    for (int c = 0; c < request.numChannels; ++c)
+    {
+        if (request.srcColorSpaces[c] > NTCB_COLOR_SPACE_HLG || request.dstColorSpaces[c] > NTCB_COLOR_SPACE_HLG)
+        {
+            SetError("Channel %d names an unknown color space (%d -> %d).", c, int(request.srcColorSpaces[c]),
+                int(request.dstColorSpaces[c]));
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        out.srcSpaces |= uint32_t(request.srcColorSpaces[c]) << (2 * c);
+        out.dstSpaces |= uint32_t(request.dstColorSpaces[c]) << (2 * c);
+    }
+    return NTCB_OK;
+}
+
+namespace
+{
+
+// Number of CTAs that fill the current device, cached per device.
+int ResidentCtas(bool fp8, bool converting, int* outCtas)
+{
+    static std::atomic<int> cache[64][3];
+    const int variant = converting ? 2 : fp8 ? 1 : 0;
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess)
         return CudaFailure("cudaGetDevice", err);
     if (device >= 0 && device < 64)
     {
-        int cached = cache[device][fp8 ? 1 : 0].load(std::memory_order_relaxed);
+        int cached = cache[device][variant].load(std::memory_order_relaxed);
         if (cached > 0)
         {
             *outCtas = cached;
@@ -123,12 +173,13 @@ int ResidentCtas(bool fp8, int* outCtas)
     // kTmemColumns of the SM's 512 tensor-memory columns for its whole lifetime.  (The runtime's
     // occupancy query reports one CTA per SM for kernels that allocate tensor memory, so it is not
     // used here.)
-    static_assert(kCtasPerSmInt8 * kTmemColumns <= 512 && kCtasPerSmFp8 * kTmemColumns <= 512,
+    static_assert(kCtasPerSmInt8 * kTmemColumns <= 512 && kCtasPerSmFp8 * kTmemColumns <= 512 &&
+                      kCtasPerSmConverting * kTmemColumns <= 512,
         "resident CTAs must fit into tensor memory");
-    const int perSm = fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
+    const int perSm = converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
     *outCtas = sms * perSm;
     if (device >= 0 && device < 64)
-        cache[device][fp8 ? 1 : 0].store(*outCtas, std::memory_order_relaxed);
+        cache[device][variant].store(*outCtas, std::memory_order_relaxed);
     return NTCB_OK;
 }
 
@@ -175,7 +226,7 @@ int ntcb_decode_resident_ctas(int weightMode, int* outCtas)
         SetError("ntcb_decode_resident_ctas: invalid arguments.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return ResidentCtas(weightMode == NTCB_WEIGHTS_FP8, outCtas);
+    return ResidentCtas(weightMode == NTCB_WEIGHTS_FP8, false, outCtas);
 }
 
 int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void* staged)
@@ -297,6 +348,15 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
     }
 
     KernelParams k{};
+    if (p->conversion)
+    {
+        int rc = MakeOutputConversion(*p->conversion, p->channels, k.conversion);
+        if (rc != NTCB_OK)
+            return rc;
+        k.convert = 1;
+        k.firstChannel = p->conversion->firstChannel;
+        k.numChannels = p->conversion->numChannels;
+    }
     k.latents = p->latents;
     k.network = static_cast<const uint8_t*>(p->network);
     k.out = static_cast<__half*>(p->out);
@@ -309,9 +369,15 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
     for (int i = 0; i < p->numMips; ++i)
     {
         const NtcbMipDesc& m = p->mips[i];
-        if (!ValidMip(m))
+        if (!ValidMip(m, k.convert == 0))
         {
             SetError("ntcb_decode: mip %d has invalid dimensions, row range or offsets.", i);
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        if (k.convert && m.outOffset % uint64_t(k.conversion.dstChannels))
+        {
+            SetError("ntcb_decode: outOffset of mip %d must be a multiple of the %d components of a converted pixel.", i,
+                k.conversion.dstChannels);
             return NTCB_ERR_INVALID_ARGUMENT;
         }
         if (m.rowBegin == m.rowEnd)
@@ -340,7 +406,7 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
 
     const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
     int resident = 0;
-    int rc = ResidentCtas(fp8, &resident);
+    int rc = ResidentCtas(fp8, k.convert != 0, &resident);
     if (rc != NTCB_OK)
         return rc;
     const int ctas = k.totalTiles < resident ? k.totalTiles : resident;
@@ -387,7 +453,7 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
         m.rowBegin = 0;
         m.rowEnd = m.height;
         m.outOffset = 0;
-        if (!ValidMip(m))
+        if (!ValidMip(m, false))
         {
             SetError("ntcb_sample: mip %d has invalid dimensions or offsets.", i);
             return NTCB_ERR_INVALID_ARGUMENT;
@@ -399,7 +465,7 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
         return NTCB_OK;
     const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
     int resident = 0;
-    int rc = ResidentCtas(fp8, &resident);
+    int rc = ResidentCtas(fp8, false, &resident);
     if (rc != NTCB_OK)
         return rc;
     const unsigned long long tiles = (p->numQueries + kThreadsPerCta - 1) / kThreadsPerCta;

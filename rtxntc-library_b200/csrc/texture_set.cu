@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -17,6 +18,7 @@
 #include "decode_kernel.h"
 #include "error.h"
 #include "ntcb.h"
+#include "output_convert.cuh"
 #include "ntcb_host.h"
 
 namespace ntcb
@@ -58,27 +60,52 @@ private:
     bool m_ok = false, m_switched = false;
 };
 
-// Gathers `numChannels` channels of one decoded mip into a pixel-interleaved destination with
-// arbitrary strides (the FLOAT16 -> FLOAT16 case of the reference's CopyImageKernel,
-// src/ImageProcessing.cu:220-277).  One thread per texel.
+// Converts `numChannels` channels of one decoded mip into a pixel-interleaved destination with
+// arbitrary strides: the 1:1 case of the reference's CopyImageKernel (src/ImageProcessing.cu:220-266)
+// with the decoded fp16 texels as source.  One thread per texel.
 __global__ void ReadChannelsKernel(const __half* __restrict__ src, int layout, int width, int height, int channels,
-    int firstChannel, int numChannels, uint8_t* __restrict__ dst, size_t pixelStride, size_t rowPitch)
+    int firstChannel, int numChannels, OutputConversion conversion, uint8_t* __restrict__ dst, size_t pixelStride,
+    size_t rowPitch)
 {
     const int x = blockIdx.x * blockDim.x + threadIdx.x;
     const int y = blockIdx.y * blockDim.y + threadIdx.y;
     if (x >= width || y >= height)
         return;
-    __half* out = reinterpret_cast<__half*>(dst + size_t(y) * rowPitch + size_t(x) * pixelStride);
-    for (int c = 0; c < numChannels; ++c)
+    uint8_t* out = dst + size_t(y) * rowPitch + size_t(x) * pixelStride;
+    const uint32_t seed = conversion.dither ? DitherSeed(uint32_t(x) + uint32_t(y) * uint32_t(width)) : 0u;
+    const int componentBytes = BytesPerComponent(conversion.format);
+    for (int c = 0; c < conversion.dstChannels; ++c)
     {
-        const int channel = firstChannel + c;
-        size_t index;
-        if (layout == kLayoutPlanarPairs)
-            index = size_t(y) * width * channels + size_t(channel & ~1) * width + size_t(x) * 2 + (channel & 1);
+        const float dither = conversion.dither ? DitherDraw(seed, uint32_t(c) + 1u) : 0.f;
+        uint32_t bits;
+        if (c < numChannels)
+        {
+            const int channel = firstChannel + c;
+            size_t index;
+            if (layout == kLayoutPlanarPairs)
+                index = size_t(y) * width * channels + size_t(channel & ~1) * width + size_t(x) * 2 + (channel & 1);
+            else
+                index = (size_t(y) * width + x) * channels + channel;
+            bits = ConvertComponent(conversion, c, src[index], dither);
+        }
         else
-            index = (size_t(y) * width + x) * channels + channel;
-        out[c] = src[index];
+            bits = DefaultComponent(conversion, c, dither);
+        if (componentBytes == 1)
+            out[c] = uint8_t(bits);
+        else if (componentBytes == 2)
+            reinterpret_cast<uint16_t*>(out)[c] = uint16_t(bits);
+        else
+            reinterpret_cast<uint32_t*>(out)[c] = bits;
     }
+}
+
+// Plain FLOAT16 read-out: linear to linear, no dithering.
+OutputConversion Float16Conversion(size_t pixelStride)
+{
+    OutputConversion conversion{};
+    conversion.format = kFormatFloat16;
+    conversion.dstChannels = int(std::min<size_t>(pixelStride / 2, size_t(kMaxChannels)));
+    return conversion;
 }
 
 // Staging area of ntcb_read_channels_to_host_noalloc: part of the library image, so every GPU
@@ -130,6 +157,8 @@ public:
         return DecompressRows(nullptr, pOutStats, useInt8Weights);
     }
     Status DecompressRows(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights) override;
+    Status DecompressConverted(DecompressionStats* pOutStats, bool useInt8Weights, NtcbOutputConversion const& conversion,
+        int addressSpace, void* destination, size_t destinationBytes) override;
     Status ReadChannels(ReadChannelsParameters const& params) override;
     Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) override;
     Status Synchronize() override;
@@ -138,6 +167,9 @@ public:
 
 private:
     Status CheckKernelStatus();
+    Status GrowStaging(size_t bytes);
+    Status DecodeInto(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights,
+        const NtcbOutputConversion* conversion, void* deviceOut);
 
     const Context* m_context;
     int m_device;
@@ -156,6 +188,7 @@ private:
     size_t m_texelBytes = 0;
     uint32_t* m_status = nullptr;
     uint32_t* m_hostStatus = nullptr; // pinned
+    int m_channelColorSpaces[kMaxChannels] = {}; // ntc::ColorSpace each channel is stored in (from the container)
     uint8_t* m_staging = nullptr;     // grown on demand by ReadChannels to host with padded strides
     size_t m_stagingBytes = 0;
     cudaEvent_t m_eventStart = nullptr, m_eventStop = nullptr;
@@ -299,6 +332,8 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     m_layout = features.outputLayout;
+    for (int c = 0; c < kMaxChannels; ++c)
+        m_channelColorSpaces[c] = loaded.channelColorSpaces[c];
     m_hasInt8 = !loaded.int8Blob.empty();
     m_hasFp8 = !loaded.fp8Blob.empty();
 
@@ -391,6 +426,101 @@ Status TextureSet::CheckKernelStatus()
 
 Status TextureSet::DecompressRows(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights)
 {
+    Status status = DecodeInto(rowRanges, pOutStats, useInt8Weights, nullptr, m_texels);
+    if (status == NTCB_OK)
+        m_decoded = true;
+    return status;
+}
+
+Status TextureSet::DecompressConverted(DecompressionStats* pOutStats, bool useInt8Weights,
+    NtcbOutputConversion const& requested, int addressSpace, void* destination, size_t destinationBytes)
+{
+    if (!destination)
+    {
+        SetError("destination is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (addressSpace != NTCB_ADDRESS_SPACE_HOST && addressSpace != NTCB_ADDRESS_SPACE_DEVICE)
+    {
+        SetError("Unknown address space %d.", addressSpace);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    // the colour space each channel is stored in comes from the container, as in ReadChannels
+    NtcbOutputConversion conversion = requested;
+    OutputConversion packed;
+    Status status = MakeOutputConversion(conversion, m_geometry.channels, packed);
+    if (status != NTCB_OK)
+        return status;
+    for (int c = 0; c < conversion.numChannels; ++c)
+        conversion.srcColorSpaces[c] = uint8_t(m_channelColorSpaces[conversion.firstChannel + c]);
+    const size_t pixelBytes = size_t(conversion.components) * size_t(BytesPerComponent(conversion.channelFormat));
+    const size_t bytes = size_t(m_geometry.TotalTexels()) * pixelBytes;
+    if (destinationBytes < bytes)
+    {
+        SetError("The destination holds %zu bytes, the converted mip chain needs %zu.", destinationBytes, bytes);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    const bool toHost = addressSpace == NTCB_ADDRESS_SPACE_HOST;
+    if (!toHost && (reinterpret_cast<uintptr_t>(destination) & 3))
+    {
+        SetError("A device destination must be 4-byte aligned.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+    void* target = destination;
+    if (toHost)
+    {
+        status = GrowStaging(bytes);
+        if (status != NTCB_OK)
+            return status;
+        target = m_staging;
+    }
+    status = DecodeInto(nullptr, pOutStats, useInt8Weights, &conversion, target);
+    if (status != NTCB_OK)
+        return status;
+    cudaError_t err;
+    if (toHost)
+    {
+        err = cudaMemcpyAsync(destination, m_staging, bytes, cudaMemcpyDeviceToHost, m_stream);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaMemcpyAsync (converted texels)", err);
+    }
+    err = cudaStreamSynchronize(m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamSynchronize", err);
+    status = CheckKernelStatus();
+    if (status != NTCB_OK)
+        return status;
+    ClearError();
+    return NTCB_OK;
+}
+
+Status TextureSet::GrowStaging(size_t bytes)
+{
+    if (m_stagingBytes >= bytes)
+        return NTCB_OK;
+    cudaStreamSynchronize(m_stream);
+    if (m_staging)
+        cudaFree(m_staging);
+    m_staging = nullptr;
+    m_stagingBytes = 0;
+    cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&m_staging), bytes);
+    if (err != cudaSuccess)
+    {
+        SetError("Failed to allocate %zu bytes of device memory for the staging buffer.", bytes);
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
+    m_stagingBytes = bytes;
+    return NTCB_OK;
+}
+
+// One decode launch of all mips (or of a row range per mip) into `deviceOut`: fp16 texels in the
+// set's layout, or converted pixels (mip after mip, rows without padding) when `conversion` is set.
+Status TextureSet::DecodeInto(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights,
+    const NtcbOutputConversion* conversion, void* deviceOut)
+{
     if (useInt8Weights ? !m_hasInt8 : !m_hasFp8)
     {
         SetError("The texture set has no %s network; it cannot be decompressed with these weights.",
@@ -415,7 +545,8 @@ Status TextureSet::DecompressRows(const int32_t* rowRanges, DecompressionStats* 
     NtcbDecodeParams params{};
     params.latents = reinterpret_cast<const uint16_t*>(m_deviceUpload);
     params.network = m_deviceUpload + m_latentBytes + (useInt8Weights ? 0 : kStagedNetworkBytes);
-    params.out = m_texels;
+    params.out = deviceOut;
+    params.conversion = conversion;
     params.status = m_status;
     params.numMips = m_geometry.mips;
     params.numFeatures = m_geometry.numFeatures;
@@ -439,7 +570,7 @@ Status TextureSet::DecompressRows(const int32_t* rowRanges, DecompressionStats* 
         d.loPlane = uint64_t(d.loWidth) * d.loHeight;
         d.positionScale = m_geometry.positionScale[mip];
         d.positionLod = m_geometry.positionLod[mip];
-        d.outOffset = m_geometry.mipTexelOffset[mip] * m_geometry.channels;
+        d.outOffset = m_geometry.mipTexelOffset[mip] * uint64_t(conversion ? conversion->components : m_geometry.channels);
         d.rowBegin = rowRanges ? rowRanges[2 * mip] : 0;
         d.rowEnd = rowRanges ? rowRanges[2 * mip + 1] : d.height;
         if (d.rowBegin < 0 || d.rowEnd > d.height || d.rowBegin > d.rowEnd)
@@ -458,7 +589,6 @@ Status TextureSet::DecompressRows(const int32_t* rowRanges, DecompressionStats* 
     Status status = ntcb_decode(&params, m_stream);
     if (status != NTCB_OK)
         return status;
-    m_decoded = true;
     if (pOutStats)
     {
         err = cudaEventRecord(m_eventStop, m_stream);
@@ -513,18 +643,37 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
             height);
         return NTCB_ERR_OUT_OF_RANGE;
     }
-    if (params.channelFormat != NTCB_CHANNEL_FORMAT_FLOAT16)
+    const size_t componentBytes = size_t(BytesPerComponent(params.channelFormat));
+    if (componentBytes == 0)
     {
-        SetError("Only ChannelFormat::FLOAT16 is implemented by ReadChannels.");
-        return NTCB_ERR_UNSUPPORTED;
-    }
-    if (params.pixelStride < size_t(params.numChannels) * 2 || params.rowPitch < params.pixelStride * size_t(width) ||
-        (params.pixelStride & 1) || (params.rowPitch & 1))
-    {
-        SetError("pixelStride (%zu) must hold numChannels fp16 values and rowPitch (%zu) a row of pixels; both must be even.",
-            params.pixelStride, params.rowPitch);
+        SetError("Unknown channel format %d.", params.channelFormat);
         return NTCB_ERR_INVALID_ARGUMENT;
     }
+    if (params.pixelStride < componentBytes || params.rowPitch < params.pixelStride * size_t(width) ||
+        params.pixelStride % componentBytes || params.rowPitch % componentBytes ||
+        (params.addressSpace == NTCB_ADDRESS_SPACE_DEVICE && reinterpret_cast<uintptr_t>(params.pOutData) % componentBytes))
+    {
+        SetError("pixelStride (%zu) must hold at least one %zu-byte component and rowPitch (%zu) a row of pixels; both, and a "
+                 "device destination, must be multiples of the component size.",
+            params.pixelStride, componentBytes, params.rowPitch);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    OutputConversion conversion{};
+    conversion.format = params.channelFormat;
+    conversion.dstChannels = int(std::min<size_t>(params.pixelStride / componentBytes, size_t(kMaxChannels))); // src/TextureSet.cpp:957
+    conversion.dither = params.useDithering != 0;
+    for (int c = 0; c < params.numChannels; ++c)
+    {
+        const int dstSpace = params.dstColorSpaces ? params.dstColorSpaces[c] : NTCB_COLOR_SPACE_LINEAR;
+        if (dstSpace < NTCB_COLOR_SPACE_LINEAR || dstSpace > NTCB_COLOR_SPACE_HLG)
+        {
+            SetError("dstColorSpaces[%d] (%d) is not a known color space.", c, dstSpace);
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        conversion.srcSpaces |= uint32_t(m_channelColorSpaces[params.firstChannel + c]) << (2 * c);
+        conversion.dstSpaces |= uint32_t(dstSpace) << (2 * c);
+    }
+    const bool plainCopy = params.channelFormat == NTCB_CHANNEL_FORMAT_FLOAT16 && conversion.srcSpaces == conversion.dstSpaces;
     if (params.addressSpace != NTCB_ADDRESS_SPACE_HOST && params.addressSpace != NTCB_ADDRESS_SPACE_DEVICE)
     {
         SetError("Unknown address space %d.", params.addressSpace);
@@ -542,7 +691,7 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
     const __half* mipData = m_texels + m_geometry.mipTexelOffset[params.mipLevel] * m_geometry.channels;
     const size_t bytes = size_t(height) * params.rowPitch;
     const bool toHost = params.addressSpace == NTCB_ADDRESS_SPACE_HOST;
-    const bool direct = m_layout == NTCB_LAYOUT_INTERLEAVED && params.firstChannel == 0 &&
+    const bool direct = plainCopy && m_layout == NTCB_LAYOUT_INTERLEAVED && params.firstChannel == 0 &&
                         params.numChannels == m_geometry.channels && params.pixelStride == size_t(m_geometry.channels) * 2 &&
                         params.rowPitch == params.pixelStride * size_t(width);
     cudaError_t err;
@@ -559,23 +708,12 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
         uint8_t* target = static_cast<uint8_t*>(params.pOutData);
         if (toHost)
         {
-            if (m_stagingBytes < bytes)
-            {
-                cudaStreamSynchronize(m_stream);
-                if (m_staging)
-                    cudaFree(m_staging);
-                m_staging = nullptr;
-                m_stagingBytes = 0;
-                err = cudaMalloc(reinterpret_cast<void**>(&m_staging), bytes);
-                if (err != cudaSuccess)
-                {
-                    SetError("Failed to allocate %zu bytes of device memory for the staging buffer.", bytes);
-                    return NTCB_ERR_OUT_OF_MEMORY;
-                }
-                m_stagingBytes = bytes;
-            }
+            Status grown = GrowStaging(bytes);
+            if (grown != NTCB_OK)
+                return grown;
             target = m_staging;
-            if (params.rowPitch > params.pixelStride * size_t(width) || params.pixelStride > size_t(params.numChannels) * 2)
+            if (params.rowPitch > params.pixelStride * size_t(width) ||
+                params.pixelStride > size_t(conversion.dstChannels) * componentBytes)
             {
                 // gaps are not written by the kernel: hand back zeros there, as the reference does
                 err = cudaMemsetAsync(m_staging, 0, bytes, m_stream);
@@ -586,7 +724,7 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
         dim3 block(32, 8);
         dim3 grid((width + block.x - 1) / block.x, (height + block.y - 1) / block.y);
         ReadChannelsKernel<<<grid, block, 0, m_stream>>>(mipData, m_layout, width, height, m_geometry.channels,
-            params.firstChannel, params.numChannels, target, params.pixelStride, params.rowPitch);
+            params.firstChannel, params.numChannels, conversion, target, params.pixelStride, params.rowPitch);
         err = cudaGetLastError();
         if (err != cudaSuccess)
             return CudaFailure("ReadChannelsKernel launch", err);
@@ -825,6 +963,18 @@ int ntcb_texture_set_decompress_rows(NtcbTextureSet* textureSet, const int32_t* 
     return textureSet->impl->DecompressRows(rowRanges, stats, useInt8Weights != 0);
 }
 
+int ntcb_texture_set_decompress_converted(NtcbTextureSet* textureSet, NtcbDecompressionStats* stats, int useInt8Weights,
+    const NtcbOutputConversion* conversion, int addressSpace, void* destination, size_t destinationBytes)
+{
+    if (!textureSet || !conversion)
+    {
+        ntcb::SetError("textureSet and conversion must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->DecompressConverted(stats, useInt8Weights != 0, *conversion, addressSpace, destination,
+        destinationBytes);
+}
+
 int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadChannelsParams* params)
 {
     if (!textureSet || !params)
@@ -907,7 +1057,7 @@ int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int wi
     dim3 block(32, 8);
     dim3 grid((width + block.x - 1) / block.x, (height + block.y - 1) / block.y);
     ReadChannelsKernel<<<grid, block, 0, cudaStream>>>(static_cast<const __half*>(deviceMip), layout, width, height, channels,
-        firstChannel, numChannels, staging, pixelStride, rowPitch);
+        firstChannel, numChannels, Float16Conversion(pixelStride), staging, pixelStride, rowPitch);
     err = cudaGetLastError();
     if (err != cudaSuccess)
         return CudaFailure("ReadChannelsKernel launch", err);
@@ -918,6 +1068,50 @@ int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int wi
     err = cudaStreamSynchronize(cudaStream);
     if (err != cudaSuccess)
         return CudaFailure("cudaStreamSynchronize", err);
+    ClearError();
+    return NTCB_OK;
+}
+
+int ntcb_convert_channels(const NtcbConvertParams* params, void* stream)
+{
+    using namespace ntcb;
+    if (!params || !params->deviceMip || !params->deviceDestination)
+    {
+        SetError("ntcb_convert_channels: params, deviceMip and deviceDestination must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if ((params->layout != NTCB_LAYOUT_PLANAR_PAIRS && params->layout != NTCB_LAYOUT_INTERLEAVED) || params->width < 1 ||
+        params->height < 1 || params->channels < 2 || params->channels > NTCB_MAX_CHANNELS || (params->channels & 1))
+    {
+        SetError("Invalid layout (%d), size (%dx%d) or channel count (%d).", params->layout, params->width, params->height,
+            params->channels);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    OutputConversion conversion;
+    int status = MakeOutputConversion(params->conversion, params->channels, conversion);
+    if (status != NTCB_OK)
+        return status;
+    const size_t componentBytes = size_t(BytesPerComponent(conversion.format));
+    if (params->pixelStride < size_t(conversion.dstChannels) * componentBytes ||
+        params->rowPitch < params->pixelStride * size_t(params->width) || params->pixelStride % componentBytes ||
+        params->rowPitch % componentBytes || reinterpret_cast<uintptr_t>(params->deviceDestination) % componentBytes ||
+        (reinterpret_cast<uintptr_t>(params->deviceMip) & 1))
+    {
+        SetError("pixelStride (%zu) must hold %d components of %zu bytes and rowPitch (%zu) a row of pixels; strides and "
+                 "addresses must be multiples of the component size.",
+            params->pixelStride, conversion.dstChannels, componentBytes, params->rowPitch);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    dim3 block(32, 8);
+    dim3 grid((params->width + block.x - 1) / block.x, (params->height + block.y - 1) / block.y);
+    ReadChannelsKernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(params->deviceMip),
+        params->layout, params->width, params->height, params->channels, params->conversion.firstChannel,
+        params->conversion.numChannels, conversion, static_cast<uint8_t*>(params->deviceDestination), params->pixelStride,
+        params->rowPitch);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess)
+        return CudaFailure("ReadChannelsKernel launch", err);
+    CountLaunch();
     ClearError();
     return NTCB_OK;
 }

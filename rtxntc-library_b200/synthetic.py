@@ -84,11 +84,13 @@ class SyntheticSet:
     int8_blob: bytes
     fp8_blob: bytes
     _container: Optional[bytes] = None
+    channel_color_spaces: Optional[List[int]] = None  # ntc::ColorSpace per channel; None = all Linear
 
     @property
     def container(self) -> bytes:
         if self._container is None:
-            self._container = write_container(self.geometry, self.latents, self.int8_blob, self.fp8_blob)
+            self._container = write_container(self.geometry, self.latents, self.int8_blob, self.fp8_blob,
+                                              self.channel_color_spaces)
         return self._container
 
     @property

@@ -157,7 +157,7 @@ def test_texture_set_api_decompress_and_read_channels(oracle):
                 expected = checker.decode_mip(0, use_int8, oracle.NUMERICS_SPEC)
                 # channel subset
                 assert np.array_equal(texture_set.read_mip(0, 1, 3).view(np.uint16), expected[:, :, 1:4].view(np.uint16))
-                # padded strides into host memory: gaps come back as zeros
+                # padded strides into host memory: the components past the requested channels and the row gaps are zeros
                 w, h = texture_set.mip_size(0)
                 padded = np.full((h, w + 3, 8), 5.0, dtype=np.float16)
                 texture_set.read_channels_into(0, padded.ctypes.data, False, 2, 4, pixel_stride=16, row_pitch=(w + 3) * 16)
@@ -168,7 +168,8 @@ def test_texture_set_api_decompress_and_read_channels(oracle):
                 texture_set.read_channels_into(0, target.data_ptr(), True)
                 assert np.array_equal(target.cpu().numpy().view(np.uint16), expected.view(np.uint16))
             # argument errors follow the reference's conventions
-            for kwargs, code in (({"first_channel": 6}, -9), ({"num_channels": 7}, -9), ({"pixel_stride": 2}, -1)):
+            for kwargs, code in (({"first_channel": 6}, -9), ({"num_channels": 7}, -9), ({"pixel_stride": 1}, -1),
+                                 ({"pixel_stride": 6, "row_pitch": 5}, -1)):
                 with pytest.raises(binding.NtcbError) as error:
                     texture_set.read_channels_into(0, target.data_ptr(), True, **kwargs)
                 assert error.value.code == code
