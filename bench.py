@@ -19,6 +19,10 @@ The JSON line reports
   roofline  algorithmic bytes of one launch / its mean duration against the measured HBM copy peak;
   cpu_baseline  the scalar CPU restatement of the same arithmetic on this machine's cores.
 
+  e2e_unorm8  the end-to-end job with UNORM8 pixels as the client's format: the decode kernel's
+            converting epilogue writes them, so the read-back is half as large (informational; the
+            reference arm reports Decompress + ReadChannels(UNORM8) beside it).
+
 `--config 0|2|3` time the other benchmark configurations (1024^2 single mip; 64 sets of 2048^2
 sharded by set; 8192^2 sharded by tile rows - the last two split a fixed job over the ranks, strong
 scaling); they report the device-resident figure only.
@@ -53,7 +57,7 @@ WORKLOAD = ("PBR texture set 4096x4096, 12 channels, 13 mips, latent shape {grid
 
 # DRAM bytes per launch of the decode kernel on this workload (dram__bytes_read.sum +
 # dram__bytes_write.sum from the ncu capture summarised in profiles/).
-MEASURED_TRAFFIC_BYTES = 492.5e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
+MEASURED_TRAFFIC_BYTES = 491.3e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
 
 
 def measured_peak_gbs():
@@ -285,6 +289,7 @@ def run_ours(args) -> dict:
 
     # ---- end to end through the texture-set API with host buffers ---------------------------
     e2e = None
+    e2e_unorm8 = None
     if args.config in (0, 1):
         launches.clear()
         del flush
@@ -311,6 +316,28 @@ def run_ours(args) -> dict:
         e2e = {"value": world * texels * args.steps / e2e_seconds / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": geo.encoded_latent_bytes + 2 * binding.STAGED_NETWORK_BYTES,
                "d2h_bytes_per_step": texels * geo.channels * 2}
+        if args.config == 1:
+            # the same job with UNORM8 pixels as the client's format: one fused launch writes them, the
+            # read-back is half the size (the reference arm runs Decompress + ReadChannels(UNORM8))
+            conversion = binding.make_conversion(binding.CHANNEL_FORMAT_UNORM8, geo.channels)
+            host_bytes = torch.empty(texels * geo.channels, dtype=torch.uint8).pin_memory()
+
+            def unorm8_step():
+                binding.check(binding.lib().ntcb_texture_set_decompress_converted(
+                    texture_set.handle, None, 1 if use_int8 else 0, ctypes.byref(conversion), binding.ADDRESS_SPACE_HOST,
+                    host_bytes.data_ptr(), host_bytes.numel()))
+
+            for _ in range(2):
+                unorm8_step()
+            barrier_sync(dist, torch)
+            unorm8_start = time.perf_counter()
+            for _ in range(args.steps):
+                unorm8_step()
+            unorm8_seconds = reduce_max(dist, torch, time.perf_counter() - unorm8_start, device)
+            barrier_sync(dist, torch)
+            e2e_unorm8 = {"value": world * texels * args.steps / unorm8_seconds / 1e9, "unit": UNIT,
+                          "h2d_bytes_per_step": e2e["h2d_bytes_per_step"], "d2h_bytes_per_step": texels * geo.channels,
+                          "path": "ntcb_texture_set_decompress_converted(UNORM8, all channels, Linear) to pinned host memory"}
         texture_set.close()
         context.close()
 
@@ -335,6 +362,8 @@ def run_ours(args) -> dict:
         "clocks": clocks, "e2e": e2e, "gpu_launches": total_launches, "roofline": roofline,
         "wall_seconds_timed_region": wall,
     }
+    if e2e_unorm8 is not None:
+        line["e2e_unorm8"] = e2e_unorm8
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(data)
     if dist is not None:
@@ -385,6 +414,23 @@ def run_reference(args) -> dict:
     torch.cuda.synchronize()
     seconds = time.perf_counter() - start
     clocks = sampler.stop()
+
+    # the same job with UNORM8 pixels as the client's format
+    host_bytes = torch.empty(texels * geo.channels, dtype=torch.uint8).pin_memory()
+
+    def unorm8_step():
+        decoder.decompress(data.use_int8)
+        for mip, cm in enumerate(geo.color_mips):
+            decoder.read_channels_into(mip, cm.width, cm.height, 1, geo.channels,
+                                       host_bytes.data_ptr() + cm.texel_offset * geo.channels)
+
+    unorm8_step()
+    torch.cuda.synchronize()
+    unorm8_start = time.perf_counter()
+    for _ in range(args.steps):
+        unorm8_step()
+    torch.cuda.synchronize()
+    unorm8_seconds = time.perf_counter() - unorm8_start
     decoder.close()
     value = texels * args.steps / seconds / 1e9
     kernel_value = texels / (statistics.mean(kernel_ms) / 1e3) / 1e9
@@ -399,6 +445,8 @@ def run_reference(args) -> dict:
                            + ("; the other %d ranks idle" % (world - 1) if world > 1 else "")},
         "clocks": clocks,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e_unorm8": {"value": texels * args.steps / unorm8_seconds / 1e9, "unit": UNIT,
+                       "path": "per step Decompress + ReadChannels(UNORM8, Host) of every mip"},
         "kernel_only": {"value": kernel_value, "unit": UNIT, "ms": statistics.mean(kernel_ms),
                         "source": "DecompressionStats::gpuTimeMilliseconds (mip loop only; upload, unpack and weight conversion excluded)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 0, "kind": "reference",

@@ -245,6 +245,14 @@ class ReferenceDecoder:
         self.read_mip_into(mip, width, height, out.ctypes.data, False)
         return out
 
+    def read_channels_into(self, mip: int, width: int, height: int, channel_format: int, components: int, address: int) -> None:
+        """ReadChannels of every channel, linear, undithered, tightly packed, to host memory at `address`."""
+        item = np.dtype(FORMAT_DTYPES[channel_format]).itemsize
+        rc = self._lib.ntcref_read_channels(self._handle, mip, 0, self.channels, width, height, channel_format,
+                                            components * item, components * item * width, None, 0, address)
+        if rc != 0:
+            raise RuntimeError("reference ReadChannels failed: %s" % self._lib.ntcref_last_error().decode())
+
     def read_channels(self, mip: int, width: int, height: int, channel_format: int, first_channel: int = 0,
                       num_channels: Optional[int] = None, components: Optional[int] = None, dst_color_spaces=None,
                       use_dithering: bool = False) -> np.ndarray:

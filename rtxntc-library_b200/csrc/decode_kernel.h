@@ -18,7 +18,7 @@ constexpr int kThreadsPerCta = kTileWidth * kTileHeight; // one thread per texel
 constexpr int kOperandBytes = 128 * 64; // A operand of one half: 128 rows x 64 bytes
 constexpr int kCtasPerSmInt8 = 4;  // resident CTAs per SM the two kernel variants are compiled for
 constexpr int kCtasPerSmFp8 = 4;
-constexpr int kCtasPerSmConverting = 3; // ... and the variants with a converting epilogue (either weight mode)
+constexpr int kCtasPerSmConverting = 4; // ... and the variants with a converting epilogue (either weight mode)
 constexpr int kTmemColumnsPerHalf = 64;    // widest accumulator (layer 0: 64 outputs)
 constexpr int kTmemColumns = 2 * kTmemColumnsPerHalf;
 constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait is declared expired

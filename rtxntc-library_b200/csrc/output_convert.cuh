@@ -170,6 +170,18 @@ __device__ __forceinline__ float DitherDraw(uint32_t seed, uint32_t index)
     return AddFtz(AddFtz(__uint_as_float((hash & 0x7fffffu) | 0x3f800000u), -1.f), -0.5f);
 }
 
+// max(0, min(limit, roundf(x))) as an integer, for limit < 2^23.  roundf (half away from zero)
+// equals floor(x + 0.5) computed in binary32 for every x >= 0 except the largest float below 0.5,
+// where the sum rounds up to 1; negative x and NaN give 0 here (the reference's std::min / std::max
+// give `limit` for NaN, which only a NaN texel could produce: decoded texels are scrubbed).
+__device__ __forceinline__ uint32_t RoundToCode(float x, float limit)
+{
+    float shifted = AddFtz(x, 0.5f);
+    if (x == 0.49999997f)
+        shifted = 0.f;
+    return __float2uint_rd(fminf(shifted, limit + 0.5f));
+}
+
 // The quantising half of WriteImageChannel (src/ImageProcessing.cu:139-164) after the colour-space
 // encode: the component's bit pattern in the low BytesPerComponent(format) bytes of the result.
 __device__ __forceinline__ uint32_t QuantizeComponent(int format, float value, float dither)
@@ -178,10 +190,10 @@ __device__ __forceinline__ uint32_t QuantizeComponent(int format, float value, f
     {
     case kFormatUnorm8:
         value = AddFtz(value, ApproxDivide(dither, 255.f));
-        return uint32_t(fmaxf(0.f, fminf(255.f, roundf(MulFtz(value, 255.f)))));
+        return RoundToCode(MulFtz(value, 255.f), 255.f);
     case kFormatUnorm16:
         value = AddFtz(value, ApproxDivide(dither, 65535.f));
-        return uint32_t(fmaxf(0.f, fminf(65535.f, roundf(MulFtz(value, 65535.f)))));
+        return RoundToCode(MulFtz(value, 65535.f), 65535.f);
     case kFormatFloat16:
         return uint32_t(__half_as_ushort(__float2half_rn(fmaxf(-65504.f, fminf(65504.f, value)))));
     case kFormatFloat32:
