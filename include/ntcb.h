@@ -27,7 +27,7 @@ extern "C" {
 #define NTCB_MAX_NEURAL_MIPS 8   /* NTC_MAX_NEURAL_MIPS, :24 */
 #define NTCB_INT8_BLOB_BYTES 9472 /* GenericInt8 weight blob, src/WeightLayout.cpp:142-268 */
 #define NTCB_FP8_BLOB_BYTES 8608  /* GenericFP8 weight blob */
-#define NTCB_STAGED_NETWORK_BYTES 11776 /* size of the device image ntcb_stage_network produces */
+#define NTCB_STAGED_NETWORK_BYTES 14864 /* size of the device image ntcb_stage_network produces */
 #define NTCB_STATUS_WORDS 4
 
 typedef enum NtcbStatus

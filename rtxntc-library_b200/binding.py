@@ -19,7 +19,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.path.join(_HERE, "libntcb200.so")
 
 MAX_MIPS = 16
-STAGED_NETWORK_BYTES = 11776
+STAGED_NETWORK_BYTES = 14864
 STATUS_WORDS = 4
 WEIGHTS_INT8, WEIGHTS_FP8 = 0, 1
 LAYOUT_PLANAR_PAIRS, LAYOUT_INTERLEAVED = 0, 1

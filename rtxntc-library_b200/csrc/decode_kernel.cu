@@ -32,6 +32,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "decode_kernel.h"
 #include "output_convert.cuh"
 
@@ -235,6 +237,8 @@ __device__ __forceinline__ uint32_t PackCodes(uint32_t pair0, uint32_t pair1)
 // Clamped HGELU in binary16 (src/tin/tin_activation.h:88-92) followed by re-quantisation:
 // e4m3 when `toFp8`, otherwise the int8 code rint(y * 80) - 113 (src/tin/tin_activation.h:94-99,
 // the -113 offset is folded into the next layer's stored bias, src/Quantizer.cu:176-181).
+// y * 80 lies in [-15, 240], so 113 is the only offset that fits int8; being odd, it cannot be
+// merged into the even magic addend without changing how ties round.
 template <bool kToFp8>
 __device__ __forceinline__ uint32_t ActivatePair(__half2 x)
 {
@@ -339,6 +343,7 @@ struct __align__(16) SharedStorage
 {
     uint8_t network[kStagedNetworkBytes]; // weights in core-matrix order, scales, biases
     uint8_t operandA[2 * kOperandBytes];  // A operands of the current layer (top half, bottom half), core-matrix order
+    uint8_t biasRegion[kBiasRegionBytes]; // constant A operand of the bias K step of int8 layers 1 and 3
     uint8_t footprintHi[kFootprintHiBytes]; // unpacked latents of the tile's footprint in the high-res grid
     uint8_t footprintLo[kFootprintLoBytes]; // ... and in the low-res grid
     uint32_t latentTable[256];            // byte (two nibbles) -> two binary16 latent values
@@ -508,6 +513,7 @@ struct TileContext
     uint32_t operandA; // shared address of the A operands (top half, then bottom half)
     uint4* rowChunk;   // this thread's 16-byte slot in chunk 0 of its half's A operand
     uint32_t networkBase;
+    uint32_t biasRegion; // shared address of the constant A operand of the bias K step
     int tile, x, y;
     uint32_t* out;          // where this thread's first channel pair goes (nullptr: store nothing); with a
                             // converting epilogue: the address of the thread's pixel in the client's format
@@ -525,6 +531,7 @@ __device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
     constexpr int kWeightOffset =
         kLayer == 0 ? kWeightOffset0 : kLayer == 1 ? kWeightOffset1 : kLayer == 2 ? kWeightOffset2 : kWeightOffset3;
     constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
+    constexpr bool kBiasStep = !kLayerFp8 && kLayer != 0; // one more K step: the bias slots
 
     // Makes the A operand written before this call visible to the tensor core, orders every
     // thread's TMEM reads of the previous layer before the accumulators are overwritten, and agrees
@@ -548,6 +555,12 @@ __device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
                 uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes + kStep * 2 * 2048, 2048, 128);
                 uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
                 Umma<kLayerFp8>(ctx.tmemBase + half * kTmemColumnsPerHalf, descA, descB, instr, kStep != 0);
+            }
+            if (kBiasStep)
+            {
+                uint64_t descA = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
+                uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + (kK / 32) * 2 * kN * 16, kN * 16, 128);
+                Umma<kLayerFp8>(ctx.tmemBase + half * kTmemColumnsPerHalf, descA, descB, instr, 1);
             }
         }
         UmmaCommit(ctx.barrier);
@@ -720,8 +733,8 @@ __device__ __forceinline__ void StoreConverted(const OutputConversion& conversio
     }
 }
 
-template <bool kFp8, int kLayer, bool kConvert, typename Params>
-__device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedStorage& shared,
+template <bool kFp8, int kLayer, bool kConvert, bool kBiasTable, typename Params>
+__device__ __forceinline__ void ConsumeLayerImpl(const Params& params, const SharedStorage& shared,
     const TileContext& ctx, uint32_t& phase, int& failed)
 {
     uint32_t* const status = params.status;
@@ -778,8 +791,8 @@ __device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedS
                         else
                         {
                             // include/libntc/shaders/Inference.hlsli:146-165: float(acc + bias) * scale
-                            float f0 = __fmul_rn(float(int32_t(acc[c][2 * j]) + biasI[colIndex]), scale[colIndex]);
-                            float f1 = __fmul_rn(float(int32_t(acc[c][2 * j + 1]) + biasI[colIndex + 1]), scale[colIndex + 1]);
+                            float f0 = __fmul_rn(float(int32_t(acc[c][2 * j]) + (kBiasTable ? biasI[colIndex] : 0)), scale[colIndex]);
+                            float f1 = __fmul_rn(float(int32_t(acc[c][2 * j + 1]) + (kBiasTable ? biasI[colIndex + 1] : 0)), scale[colIndex + 1]);
                             xh = __floats2half2_rn(f0, f1);
                         }
                         pairs[j] = ActivatePair<kNextFp8>(xh);
@@ -791,7 +804,11 @@ __device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedS
             }
         }
         if (kLayer == 1)
-            rowChunk[3 * 128] = make_uint4(0, 0, 0, 0); // layer 2 has 48 inputs, K is padded to 64
+        {
+            // layer 2 has 48 inputs, K is padded to 64: zeros (e4m3) or the bias slots' inputs (int8)
+            const uint32_t fill = kFp8 ? 0u : kBiasSlotValue * 0x01010101u;
+            rowChunk[3 * 128] = make_uint4(fill, fill, fill, kFp8 ? 0u : ((fill & 0x00FFFFFFu) | 0x01000000u));
+        }
     }
     else
     {
@@ -807,8 +824,8 @@ __device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedS
         {
             if (j < channelPairs)
             {
-                float f0 = __fmul_rn(float(int32_t(acc[2 * j]) + biasI[2 * j]), scale[2 * j]);
-                float f1 = __fmul_rn(float(int32_t(acc[2 * j + 1]) + biasI[2 * j + 1]), scale[2 * j + 1]);
+                float f0 = __fmul_rn(float(int32_t(acc[2 * j]) + (kBiasTable ? biasI[2 * j] : 0)), scale[2 * j]);
+                float f1 = __fmul_rn(float(int32_t(acc[2 * j + 1]) + (kBiasTable ? biasI[2 * j + 1] : 0)), scale[2 * j + 1]);
                 bits[j] = AsU32(__floats2half2_rn(f0, f1));
                 special |= (bits[j] & 0x7C007C00u) + 0x04000400u;
             }
@@ -843,6 +860,19 @@ __device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedS
                     ctx.out[j * ctx.outStepWords] = bits[j];
         }
     }
+}
+
+// Second half of a layer.  An int8 layer's bias is part of the accumulator already (bias slots of
+// the matrix product) unless the staged network says that it has to come from the table.
+template <bool kFp8, int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedStorage& shared,
+    const TileContext& ctx, uint32_t& phase, int& failed)
+{
+    constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
+    if (!kLayerFp8 && (*reinterpret_cast<const uint32_t*>(shared.network + kFlagsOffset) & kFlagBiasTable))
+        ConsumeLayerImpl<kFp8, kLayer, kConvert, true>(params, shared, ctx, phase, failed);
+    else
+        ConsumeLayerImpl<kFp8, kLayer, kConvert, false>(params, shared, ctx, phase, failed);
 }
 
 template <bool kFp8, int kLayer, bool kConvert, typename Params>
@@ -890,9 +920,10 @@ __device__ __forceinline__ void BuildInputs(const KernelParams& params, const Ke
 #pragma unroll
     for (int i = 0; i < 8; ++i)
         words[i] = zeroWord; // unused feature slots hold quantised zeros (src/Inference.cu:49)
-#pragma unroll
-    for (int i = 12; i < 16; ++i)
-        words[i] = 0; // K padding
+    // K padding: zeros for e4m3 operands; for int8 operands the constant inputs of the bias slots
+    const uint32_t slotFill = kFp8 ? 0u : kBiasSlotValue * 0x01010101u;
+    words[12] = words[13] = words[14] = slotFill;
+    words[15] = kFp8 ? 0u : ((slotFill & 0x00FFFFFFu) | 0x01000000u);
 
     if (mip.staged)
     {
@@ -924,7 +955,9 @@ template <bool kFp8, bool kConvert>
 __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConverting : kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8)
     DecodeKernel(const __grid_constant__ KernelParams params)
 {
-    __shared__ SharedStorage shared;
+    // more than the 48 KB a kernel may declare statically: passed as dynamic shared memory at launch
+    extern __shared__ __align__(16) unsigned char dynamicShared[];
+    SharedStorage& shared = *reinterpret_cast<SharedStorage*>(dynamicShared);
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -943,6 +976,13 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
             __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
             __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
             shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
+        }
+        // constant inputs of the bias K step: 31 slots of kBiasSlotValue and a last slot of 1 per row
+        for (int i = tid; i < kBiasRegionBytes / 16; i += kThreadsPerCta)
+        {
+            const uint32_t fill = kBiasSlotValue * 0x01010101u;
+            reinterpret_cast<uint4*>(shared.biasRegion)[i] =
+                make_uint4(fill, fill, fill, i < 128 ? fill : ((fill & 0x00FFFFFFu) | 0x01000000u));
         }
         if (tid == 0)
         {
@@ -970,6 +1010,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
+    ctx.biasRegion = SharedAddress(shared.biasRegion);
 
     // Position of a tile in its mip.
     struct TilePlace
@@ -1073,7 +1114,9 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
 template <bool kFp8>
 __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8) SampleKernel(const __grid_constant__ SampleParams params)
 {
-    __shared__ SharedStorage shared;
+    // more than the 48 KB a kernel may declare statically: passed as dynamic shared memory at launch
+    extern __shared__ __align__(16) unsigned char dynamicShared[];
+    SharedStorage& shared = *reinterpret_cast<SharedStorage*>(dynamicShared);
     __shared__ KernelMip mipTable[16];
 
     const int tid = threadIdx.x;
@@ -1093,6 +1136,13 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
         }
         if (tid < params.numMips)
             mipTable[tid] = params.mips[tid];
+        // constant inputs of the bias K step: 31 slots of kBiasSlotValue and a last slot of 1 per row
+        for (int i = tid; i < kBiasRegionBytes / 16; i += kThreadsPerCta)
+        {
+            const uint32_t fill = kBiasSlotValue * 0x01010101u;
+            reinterpret_cast<uint4*>(shared.biasRegion)[i] =
+                make_uint4(fill, fill, fill, i < 128 ? fill : ((fill & 0x00FFFFFFu) | 0x01000000u));
+        }
         if (tid == 0)
         {
             MbarrierInit(SharedAddress(&shared.barrier), 1);
@@ -1117,6 +1167,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
+    ctx.biasRegion = SharedAddress(shared.biasRegion);
     ctx.outStepWords = 1;
 
     const unsigned long long tiles = (params.numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
@@ -1142,9 +1193,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
 #pragma unroll
             for (int i = 0; i < 8; ++i)
                 words[i] = zeroWord;
-#pragma unroll
-            for (int i = 12; i < 16; ++i)
-                words[i] = 0;
+            // K padding: zeros (e4m3) or the constant inputs of the bias slots (int8)
+            const uint32_t slotFill = kFp8 ? 0u : kBiasSlotValue * 0x01010101u;
+            words[12] = words[13] = words[14] = slotFill;
+            words[15] = kFp8 ? 0u : ((slotFill & 0x00FFFFFFu) | 0x01000000u);
             SampleGridsDirect<kFp8>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
             // src/RegressionKernels.h:59-85
             float xf = __fmul_rn(float(x), mip.positionScale);
@@ -1184,31 +1236,54 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
         TmemFree(tmemBase, kTmemColumns);
 }
 
+
+
+// Lets `kernel` use sizeof(SharedStorage) bytes of dynamic shared memory on the current device
+// (needed once per device and kernel; remembered per device).
+template <typename Kernel>
+cudaError_t AllowSharedStorage(Kernel kernel, std::atomic<unsigned long long>& doneMask)
+{
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess)
+        return err;
+    const unsigned long long bit = 1ull << (device & 63);
+    if (doneMask.load(std::memory_order_acquire) & bit)
+        return cudaSuccess;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(SharedStorage)));
+    if (err == cudaSuccess)
+        doneMask.fetch_or(bit, std::memory_order_release);
+    return err;
+}
+
+template <typename Kernel, typename Params>
+cudaError_t LaunchWithSharedStorage(Kernel kernel, std::atomic<unsigned long long>& doneMask, const Params& params, int ctas,
+    cudaStream_t stream)
+{
+    cudaError_t err = AllowSharedStorage(kernel, doneMask);
+    if (err != cudaSuccess)
+        return err;
+    kernel<<<ctas, kThreadsPerCta, sizeof(SharedStorage), stream>>>(params);
+    return cudaGetLastError();
+}
+
 } // namespace
 
 cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream)
 {
-    if (fp8)
-        SampleKernel<true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
-    else
-        SampleKernel<false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
-    return cudaGetLastError();
+    static std::atomic<unsigned long long> done[2];
+    return fp8 ? LaunchWithSharedStorage(SampleKernel<true>, done[1], params, ctas, stream)
+               : LaunchWithSharedStorage(SampleKernel<false>, done[0], params, ctas, stream);
 }
 
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
 {
+    static std::atomic<unsigned long long> done[4];
     if (params.convert)
-    {
-        if (fp8)
-            DecodeKernel<true, true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
-        else
-            DecodeKernel<false, true><<<ctas, kThreadsPerCta, 0, stream>>>(params);
-    }
-    else if (fp8)
-        DecodeKernel<true, false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
-    else
-        DecodeKernel<false, false><<<ctas, kThreadsPerCta, 0, stream>>>(params);
-    return cudaGetLastError();
+        return fp8 ? LaunchWithSharedStorage(DecodeKernel<true, true>, done[3], params, ctas, stream)
+                   : LaunchWithSharedStorage(DecodeKernel<false, true>, done[2], params, ctas, stream);
+    return fp8 ? LaunchWithSharedStorage(DecodeKernel<true, false>, done[1], params, ctas, stream)
+               : LaunchWithSharedStorage(DecodeKernel<false, false>, done[0], params, ctas, stream);
 }
 
 } // namespace ntcb

@@ -28,13 +28,25 @@ constexpr int kFootprintLoBytes = 4096;    // ... and in the low-res grid (half 
 // Image of the network in shared memory (produced on the host by ntcb_stage_network).
 // Weight matrix of layer l: N_l rows (outputs) x K_l bytes (inputs, padded to a multiple of 32) in
 // K-major core-matrix order: byte (n, k) lives at (k / 16) * (N_l * 16) + n * 16 + (k % 16).
-constexpr int kWeightOffset0 = 0;     // 64 x 64
-constexpr int kWeightOffset1 = 4096;  // 48 x 64
-constexpr int kWeightOffset2 = 7168;  // 32 x 64
-constexpr int kWeightOffset3 = 9216;  // 16 x 32
-constexpr int kScaleOffset = 9728;    // float[4][64]
-constexpr int kBiasOffset = 10752;    // per layer 256 bytes: int32[64] (int8 layers) or half[64] (e4m3 layers)
-constexpr int kStagedNetworkBytes = 11776;
+//
+// Int8 layers carry their int32 bias inside the matrix product: the A operand holds constant
+// inputs (kBiasSlotValue; 1 in the last slot of each K step) in K slots past the real inputs, and
+// the weight rows hold a decomposition of the bias over those slots, so that sum(weights * inputs)
+// already includes it.  Layers 0 and 2 have 16 such slots in the padding of their 48 inputs;
+// layers 1, 2 and 3 get one more K step of 32 slots whose A operand is a constant region of shared
+// memory.  When a bias does not fit, the whole network falls back to the bias table
+// (kFlagBiasTable).
+constexpr int kWeightOffset0 = 0;      // 64 x 64
+constexpr int kWeightOffset1 = 4096;   // 48 x 96 (64 inputs + 32 bias slots)
+constexpr int kWeightOffset2 = 8704;   // 32 x 96 (48 inputs + 16 + 32 bias slots)
+constexpr int kWeightOffset3 = 11776;  // 16 x 64 (32 inputs + 32 bias slots)
+constexpr int kScaleOffset = 12800;    // float[4][64]
+constexpr int kBiasOffset = 13824;     // per layer 256 bytes: int32[64] (int8 layers) or half[64] (e4m3 layers)
+constexpr int kFlagsOffset = 14848;    // uint32[4]: word 0 = kFlag* bits
+constexpr int kStagedNetworkBytes = 14864;
+constexpr uint32_t kFlagBiasTable = 1; // int8 layers add their bias from the table (the bias slots hold zero weights)
+constexpr int kBiasSlotValue = 127;
+constexpr int kBiasRegionBytes = 128 * 32; // constant A operand of the extra K step: 128 rows x 32 slots
 
 constexpr uint32_t kStatusBarrierTimeout = 1;
 

@@ -6,6 +6,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "decode_kernel.h"
@@ -47,7 +48,7 @@ namespace
 
 constexpr int kLayerInputs[4] = {48, 64, 48, 32};
 constexpr int kLayerOutputs[4] = {64, 48, 32, 16};
-constexpr int kLayerPaddedK[4] = {64, 64, 64, 32};
+constexpr int kBiasSlots[4] = {16, 32, 48, 32};    // K slots that carry the bias of an int8 layer
 constexpr int kWeightOffsets[4] = {kWeightOffset0, kWeightOffset1, kWeightOffset2, kWeightOffset3};
 
 // `pairedOutput`: the launch stores fp16 channel pairs as 32-bit words, so a mip must start on one.
@@ -263,14 +264,17 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
         uint8_t* w = dst + kWeightOffsets[layer];
         for (int n = 0; n < nout; ++n)
             for (int k = 0; k < nin; ++k)
-                w[(k / 16) * (nout * 16) + n * 16 + (k % 16)] = src[offset + size_t(n) * nin + k];
-        (void)kLayerPaddedK;
+            {
+                const uint8_t byte = src[offset + size_t(n) * nin + k];
+                w[(k / 16) * (nout * 16) + n * 16 + (k % 16)] = byte;
+            }
         offset += size_t(nin) * nout;
     }
 
     float* scale = reinterpret_cast<float*>(dst + kScaleOffset);
     for (int i = 0; i < 4 * 64; ++i)
         scale[i] = 1.f;
+    int32_t fileBias[4][64] = {};
     if (!fp8)
     {
         // all fp32 scale vectors, then all int32 bias vectors (src/WeightLayout.cpp:228-238)
@@ -281,7 +285,7 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
         }
         for (int layer = 0; layer < 4; ++layer)
         {
-            memcpy(dst + kBiasOffset + layer * 256, src + offset, 4u * kLayerOutputs[layer]);
+            memcpy(fileBias[layer], src + offset, 4u * kLayerOutputs[layer]);
             offset += 4u * kLayerOutputs[layer];
         }
     }
@@ -296,9 +300,68 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
         }
         memcpy(scale + 3 * 64, src + offset, 4u * 16);
         offset += 4u * 16;
-        memcpy(dst + kBiasOffset + 3 * 256, src + offset, 4u * 16);
+        memcpy(fileBias[3], src + offset, 4u * 16);
         offset += 4u * 16;
     }
+
+    // Int8 layers: the bias the kernel needs, and its decomposition over the bias slots.
+    bool fits = true;
+    int32_t bias[4][64] = {};
+    for (int layer = fp8 ? 3 : 0; layer < 4; ++layer)
+    {
+        for (int n = 0; n < kLayerOutputs[layer]; ++n)
+        {
+            const long long adjusted = fileBias[layer][n];
+            if (adjusted > 0x7FFFFFFFll || adjusted < -0x7FFFFFFFll)
+            {
+                SetError("ntcb_stage_network: the bias of output %d of layer %d is out of range.", n, layer);
+                return NTCB_ERR_OUT_OF_RANGE;
+            }
+            bias[layer][n] = int32_t(adjusted);
+            const int slots = kBiasSlots[layer];
+            // (layer 2's 48 slots span two K steps: one of them is the first step's input-1 slot)
+            if (std::llabs(adjusted) > (long long)kBiasSlotValue * 127 * (slots - (slots > 32 ? 2 : 1)) + 63)
+                fits = false;
+        }
+    }
+    uint32_t* flags = reinterpret_cast<uint32_t*>(dst + kFlagsOffset);
+    for (int layer = fp8 ? 3 : 0; layer < 4; ++layer)
+    {
+        const int nout = kLayerOutputs[layer];
+        if (!fits)
+        {
+            memcpy(dst + kBiasOffset + layer * 256, bias[layer], 4u * nout);
+            continue;
+        }
+        uint8_t* w = dst + kWeightOffsets[layer];
+        const int firstSlot = kLayerInputs[layer]; // layers 0 and 2: the 16 padding slots of their 48 inputs come first
+        for (int n = 0; n < nout; ++n)
+        {
+            // bias = kBiasSlotValue * q + r with |r| <= 63; q spread over the first slots - 1 slots in
+            // steps of at most 127, r in the last slot (whose input is 1)
+            const int value = bias[layer][n];
+            int q = (value >= 0 ? value + kBiasSlotValue / 2 : value - kBiasSlotValue / 2) / kBiasSlotValue;
+            const int r = value - q * kBiasSlotValue;
+            for (int slot = 0; slot < kBiasSlots[layer]; ++slot)
+            {
+                // the constant input is 1 in the last slot of a K step and kBiasSlotValue elsewhere; the
+                // remainder goes to the last slot of all, the other slots of input 1 stay empty
+                const int k = firstSlot + slot;
+                int part;
+                if (slot == kBiasSlots[layer] - 1)
+                    part = r;
+                else if ((k & 31) == 31)
+                    part = 0;
+                else
+                {
+                    part = q > 127 ? 127 : q < -127 ? -127 : q;
+                    q -= part;
+                }
+                w[(k / 16) * (nout * 16) + n * 16 + (k % 16)] = uint8_t(int8_t(part));
+            }
+        }
+    }
+    flags[0] = fits ? 0u : kFlagBiasTable;
     if (offset != expected)
     {
         SetError("ntcb_stage_network: internal layout mismatch.");

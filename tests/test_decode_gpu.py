@@ -94,6 +94,38 @@ def test_kernel_matches_contract_on_ragged_shapes(oracle, shape, network):
                                      use_int8, "%s mip %d" % (shape, mip))
 
 
+def test_biases_too_large_for_the_matrix_product_come_from_the_table(oracle):
+    """Int8 layers normally carry their bias in spare K slots of the matrix product; a bias that does
+    not fit there switches the network to the bias table.  Both paths must give the contract's bits,
+    also at the largest bias that still fits and at negative extremes."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(96, 40, 6, 0, 3, 12, seed=77, network="unit"))
+    geo = data.geometry
+    packed = data.packed_latents()
+    limit = 127 * 127 * 31 + 63  # what the 32 bias slots of layers 1 and 3 can carry
+    for delta in (limit, limit + 1, -limit, -limit - 1):
+        int8_blob = bytearray(data.int8_blob)
+        table = np.frombuffer(bytes(int8_blob[8192 + 640:8192 + 1280]), dtype=np.int32).copy()
+        table[64 + 5] = delta      # layer 1, output 5
+        table[144 + 2] = -delta    # layer 3, output 2
+        int8_blob[8192 + 640:8192 + 1280] = table.tobytes()
+        fp8_blob = bytearray(data.fp8_blob)
+        last = np.frombuffer(bytes(fp8_blob[8544:8608]), dtype=np.int32).copy()
+        last[3] = delta
+        fp8_blob[8544:8608] = last.tobytes()
+        staged = binding.stage_network(bytes(int8_blob), binding.WEIGHTS_INT8)
+        assert staged[14848:14852].view(np.uint32)[0] == (1 if abs(delta) > limit else 0)
+        checker = oracle.OracleSet(geo, packed, bytes(int8_blob), bytes(fp8_blob))
+        resident = binding.ResidentTextureSet(geo, packed, bytes(int8_blob), bytes(fp8_blob))
+        for use_int8 in (True, False):
+            resident.out.fill_(float("nan"))
+            resident.decode(use_int8)
+            _sync()
+            resident.check_status()
+            for mip in (0, geo.mips - 1):
+                _assert_matches_contract(resident.mip_numpy(mip), checker.decode_mip(mip, use_int8, oracle.NUMERICS_SPEC),
+                                         use_int8, "bias %d mip %d" % (delta, mip))
+
+
 def test_row_ranges_tile_rows_and_guard_bands(oracle):
     """Decoding a mip in row bands (the unit of tile-row sharding) gives the same bits as one
     whole decode, writes nothing outside its band, and leaves canaries around the buffer intact."""

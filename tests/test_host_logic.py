@@ -152,31 +152,78 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), "libntcb200.so does not export " + name
 
 
+STAGED_WEIGHT_OFFSETS = [0, 4096, 8704, 11776]
+STAGED_K = [64, 96, 96, 64]          # real inputs, then the slots that carry an int8 layer's bias
+STAGED_SCALES, STAGED_BIASES, STAGED_FLAGS = 12800, 13824, 14848
+
+
+def _staged_matrix(staged, layer, nout):
+    k = np.arange(STAGED_K[layer])
+    n = np.arange(nout)[:, None]
+    index = STAGED_WEIGHT_OFFSETS[layer] + (k // 16) * nout * 16 + n * 16 + k % 16
+    return staged[index].view(np.int8).astype(np.int64)
+
+
+def _file_biases(source, mode):
+    """int32 biases of the int8 layers as the weight blob stores them: {layer: values}."""
+    if mode == binding.WEIGHTS_INT8:
+        table = source[8192 + 640:8192 + 1280].view(np.int32)
+        bounds = np.cumsum([0] + list(geometry.MLP_LAYER_OUTPUTS))
+        return {layer: table[bounds[layer]:bounds[layer + 1]].astype(np.int64) for layer in range(4)}
+    return {3: source[8544:8608].view(np.int32).astype(np.int64)}
+
+
 def test_weight_staging_layout():
-    """K-major core-matrix order: byte (n, k) of layer l at (k / 16) * (N * 16) + n * 16 + k % 16."""
+    """K-major core-matrix order: byte (n, k) of layer l at (k / 16) * (N * 16) + n * 16 + k % 16;
+    the K slots past an int8 layer's inputs hold a decomposition of its bias over the constant
+    inputs 127 (1 in the last slot of each 32-slot K step)."""
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=3))
-    offsets = [0, 4096, 7168, 9216]
     for blob, mode in ((data.int8_blob, binding.WEIGHTS_INT8), (data.fp8_blob, binding.WEIGHTS_FP8)):
         staged = binding.stage_network(blob, mode)
+        assert staged.size == binding.STAGED_NETWORK_BYTES
         source = np.frombuffer(blob, dtype=np.uint8)
+        biases = _file_biases(source, mode)
+        assert staged[STAGED_FLAGS:STAGED_FLAGS + 4].view(np.uint32)[0] == 0  # every bias fits its slots
         position = 0
         for layer, (nin, nout) in enumerate(zip(geometry.MLP_LAYER_INPUTS, geometry.MLP_LAYER_OUTPUTS)):
-            weights = source[position:position + nin * nout].reshape(nout, nin)
+            weights = source[position:position + nin * nout].view(np.int8).reshape(nout, nin)
             position += nin * nout
-            padded_k = 32 if layer == 3 else 64
-            for n in (0, 7, 8, nout - 1):
-                for k in (0, 15, 16, 31, nin - 1):
-                    assert staged[offsets[layer] + (k // 16) * nout * 16 + n * 16 + k % 16] == weights[n, k]
-            if padded_k > nin:  # zero padding of K
-                for n in range(nout):
-                    assert staged[offsets[layer] + (nin // 16) * nout * 16 + n * 16] == 0
-        scales = staged[9728:9728 + 1024].view(np.float32).reshape(4, 64)
+            matrix = _staged_matrix(staged, layer, nout)
+            assert np.array_equal(matrix[:, :nin], weights)
+            constants = np.where(np.arange(STAGED_K[layer]) % 32 == 31, 1, 127)[nin:]
+            if layer in biases:
+                assert np.array_equal(matrix[:, nin:] @ constants, biases[layer]), layer
+                assert np.abs(matrix[:, nin:]).max() <= 127
+            else:
+                assert not matrix[:, nin:].any()  # e4m3 layers: zero padding
+        scales = staged[STAGED_SCALES:STAGED_SCALES + 1024].view(np.float32).reshape(4, 64)
         if mode == binding.WEIGHTS_INT8:
             assert np.array_equal(scales[0], source[8192:8192 + 256].view(np.float32))
-            assert np.array_equal(staged[10752:10752 + 256].view(np.int32), source[8832:8832 + 256].view(np.int32))
+            assert not staged[STAGED_BIASES:STAGED_BIASES + 1024].any()  # the table is only the fallback
         else:
             assert np.array_equal(scales[3, :16], source[8480:8544].view(np.float32))
-            assert np.array_equal(staged[10752:10752 + 128].view(np.float16), source[8192:8320].view(np.float16))
+            assert np.array_equal(staged[STAGED_BIASES:STAGED_BIASES + 128].view(np.float16), source[8192:8320].view(np.float16))
+
+
+def test_weight_staging_falls_back_to_the_bias_table():
+    """A bias too large for its slots switches the whole network to the table."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=3))
+    blob = bytearray(data.int8_blob)
+    table = np.frombuffer(bytes(blob[8192 + 640:8192 + 1280]), dtype=np.int32).copy()
+    table[64 + 5] = 127 * 127 * 31 + 64  # one more than layer 1's 32 slots can carry
+    blob[8192 + 640:8192 + 1280] = table.tobytes()
+    staged = binding.stage_network(bytes(blob), binding.WEIGHTS_INT8)
+    assert staged[STAGED_FLAGS:STAGED_FLAGS + 4].view(np.uint32)[0] == 1
+    stored = staged[STAGED_BIASES:STAGED_BIASES + 1024].view(np.int32).reshape(4, 64)
+    assert np.array_equal(stored[1, :48], table[64:112]) and np.array_equal(stored[3, :16], table[144:160])
+    for layer, (nin, nout) in enumerate(zip(geometry.MLP_LAYER_INPUTS, geometry.MLP_LAYER_OUTPUTS)):
+        assert not _staged_matrix(staged, layer, nout)[:, nin:].any()
+    table[64 + 5] -= 1  # the largest value that still fits
+    blob[8192 + 640:8192 + 1280] = table.tobytes()
+    staged = binding.stage_network(bytes(blob), binding.WEIGHTS_INT8)
+    assert staged[STAGED_FLAGS:STAGED_FLAGS + 4].view(np.uint32)[0] == 0
+    constants = np.where(np.arange(96) % 32 == 31, 1, 127)[64:]
+    assert (_staged_matrix(staged, 1, 48)[5, 64:] @ constants) == table[64 + 5]
 
 
 def test_stage_network_rejects_wrong_sizes():
