@@ -76,6 +76,21 @@ __device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
     return done != 0;
 }
 
+// Announces `bytes` of asynchronous copies that will complete on the barrier, and arrives on it.
+__device__ __forceinline__ void MbarrierArriveExpectTx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// TMA bulk copy global -> shared memory of this CTA (addresses and size multiples of 16 bytes);
+// completion is signalled on the barrier.
+__device__ __forceinline__ void BulkCopyToShared(uint32_t dstShared, const void* srcGlobal, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dstShared), "l"(srcGlobal), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // Bounded wait: returns false when the barrier did not complete within the spin budget.
 __device__ __forceinline__ bool MbarrierWaitBounded(uint32_t bar, uint32_t parity)
 {
@@ -339,16 +354,18 @@ struct __align__(16) TileTables
     uint32_t pad;
 };
 
-struct __align__(16) SharedStorage
+struct __align__(128) SharedStorage
 {
     uint8_t network[kStagedNetworkBytes]; // weights in core-matrix order, scales, biases
-    uint8_t operandA[2 * kOperandBytes];  // A operands of the current layer (top half, bottom half), core-matrix order
-    uint8_t biasRegion[kBiasRegionBytes]; // constant A operand of the bias K step of int8 layers 1 and 3
+    // the tensor core reads operands as 128-byte core matrices: keep them on 128-byte lines
+    alignas(128) uint8_t operandA[2 * kOperandBytes];  // A operands of the current layer (top half, bottom half), core-matrix order
+    alignas(128) uint8_t biasRegion[kBiasRegionBytes]; // constant A operand of the bias K step of the int8 layers
     uint8_t footprintHi[kFootprintHiBytes]; // unpacked latents of the tile's footprint in the high-res grid
     uint8_t footprintLo[kFootprintLoBytes]; // ... and in the low-res grid
     uint32_t latentTable[256];            // byte (two nibbles) -> two binary16 latent values
     TileTables tables;
     uint64_t barrier;                     // MMA completion
+    uint64_t loadBarrier;                 // arrival of the network image (bulk copy)
     uint32_t tmemBase;
 };
 
@@ -531,7 +548,7 @@ __device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
     constexpr int kWeightOffset =
         kLayer == 0 ? kWeightOffset0 : kLayer == 1 ? kWeightOffset1 : kLayer == 2 ? kWeightOffset2 : kWeightOffset3;
     constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
-    constexpr bool kBiasStep = !kLayerFp8 && kLayer != 0; // one more K step: the bias slots
+    constexpr bool kBiasStep = !kFp8 && kLayer != 0; // Int8 mode: one more K step, the bias slots
 
     // Makes the A operand written before this call visible to the tensor core, orders every
     // thread's TMEM reads of the previous layer before the accumulators are overwritten, and agrees
@@ -868,8 +885,8 @@ template <bool kFp8, int kLayer, bool kConvert, typename Params>
 __device__ __forceinline__ void ConsumeLayer(const Params& params, const SharedStorage& shared,
     const TileContext& ctx, uint32_t& phase, int& failed)
 {
-    constexpr bool kLayerFp8 = kFp8 && kLayer < 3;
-    if (!kLayerFp8 && (*reinterpret_cast<const uint32_t*>(shared.network + kFlagsOffset) & kFlagBiasTable))
+    // (FP8 mode has a single int8 layer of 16 outputs: it keeps the table)
+    if (kFp8 || (*reinterpret_cast<const uint32_t*>(shared.network + kFlagsOffset) & kFlagBiasTable))
         ConsumeLayerImpl<kFp8, kLayer, kConvert, true>(params, shared, ctx, phase, failed);
     else
         ConsumeLayerImpl<kFp8, kLayer, kConvert, false>(params, shared, ctx, phase, failed);
@@ -951,12 +968,67 @@ __device__ __forceinline__ void BuildInputs(const KernelParams& params, const Ke
         ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
 }
 
+// One-time setup of a CTA: the network image arrives by one TMA bulk copy while the threads fill
+// the constant tables, set up the barriers and allocate tensor memory.  Returns nonzero, uniformly
+// over the CTA, when some thread gave up waiting for the image (status words written, one more
+// bounded wait for the copy done, tensor memory released): the caller returns at once.
+__device__ __forceinline__ int SetupCta(SharedStorage& shared, const uint8_t* network, uint32_t* status, int tid, int warp)
+{
+    // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
+    for (int i = tid; i < 256; i += kThreadsPerCta)
+    {
+        __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
+        __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
+        shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
+    }
+    // constant inputs of the bias K step: 31 slots of kBiasSlotValue and a last slot of 1 per row
+    for (int i = tid; i < kBiasRegionBytes / 16; i += kThreadsPerCta)
+    {
+        const uint32_t fill = kBiasSlotValue * 0x01010101u;
+        reinterpret_cast<uint4*>(shared.biasRegion)[i] =
+            make_uint4(fill, fill, fill, i < 128 ? fill : ((fill & 0x00FFFFFFu) | 0x01000000u));
+    }
+    const uint32_t loadBarrier = SharedAddress(&shared.loadBarrier);
+    if (tid == 0)
+    {
+        MbarrierInit(SharedAddress(&shared.barrier), 1);
+        MbarrierInit(loadBarrier, 1);
+        FenceBarrierInit();
+        MbarrierArriveExpectTx(loadBarrier, kStagedNetworkBytes);
+        BulkCopyToShared(SharedAddress(shared.network), network, kStagedNetworkBytes, loadBarrier);
+    }
+    if (warp == 0)
+        TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
+    FenceProxyAsyncShared(); // the bias region is read by the tensor core (async proxy)
+    TcgenFenceBeforeSync();
+    __syncthreads();         // also publishes the barriers' initialisation
+    TcgenFenceAfterSync();
+    int failed = 0;
+    if (!MbarrierWaitBounded(loadBarrier, 0))
+    {
+        failed = 1;
+        status[0] = kStatusBarrierTimeout;
+        status[1] = 0xFFFFFFFFu; // no tile: the network image did not arrive
+        status[2] = 0xFFFFFFFFu;
+    }
+    if (__syncthreads_or(failed))
+    {
+        if (tid == 0)
+            (void)MbarrierWaitBounded(loadBarrier, 0);
+        __syncthreads();
+        if (warp == 0)
+            TmemFree(shared.tmemBase, kTmemColumns);
+        return 1;
+    }
+    return 0;
+}
+
 template <bool kFp8, bool kConvert>
 __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConverting : kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8)
     DecodeKernel(const __grid_constant__ KernelParams params)
 {
     // more than the 48 KB a kernel may declare statically: passed as dynamic shared memory at launch
-    extern __shared__ __align__(16) unsigned char dynamicShared[];
+    extern __shared__ __align__(128) unsigned char dynamicShared[];
     SharedStorage& shared = *reinterpret_cast<SharedStorage*>(dynamicShared);
 
     const int tid = threadIdx.x;
@@ -964,41 +1036,11 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
     const int warp = tid >> 5;      // = the thread's row of the tile
     const int half = warp >> 2;     // 0: rows 0-3 of the tile, 1: rows 4-7
 
-    // ---- one-time setup -----------------------------------------------------------------
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(params.network);
-        uint4* dst = reinterpret_cast<uint4*>(shared.network);
-        for (int i = tid; i < kStagedNetworkBytes / 16; i += kThreadsPerCta)
-            dst[i] = __ldg(src + i);
-        // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
-        for (int i = tid; i < 256; i += kThreadsPerCta)
-        {
-            __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
-            __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
-            shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
-        }
-        // constant inputs of the bias K step: 31 slots of kBiasSlotValue and a last slot of 1 per row
-        for (int i = tid; i < kBiasRegionBytes / 16; i += kThreadsPerCta)
-        {
-            const uint32_t fill = kBiasSlotValue * 0x01010101u;
-            reinterpret_cast<uint4*>(shared.biasRegion)[i] =
-                make_uint4(fill, fill, fill, i < 128 ? fill : ((fill & 0x00FFFFFFu) | 0x01000000u));
-        }
-        if (tid == 0)
-        {
-            MbarrierInit(SharedAddress(&shared.barrier), 1);
-            FenceBarrierInit();
-        }
-        if (warp == 0)
-            TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
-        FenceProxyAsyncShared(); // the weights are read by the tensor core (async proxy)
-        TcgenFenceBeforeSync();
-        __syncthreads();
-        TcgenFenceAfterSync();
-    }
+    if (SetupCta(shared, params.network, params.status, tid, warp))
+        return;
+    int failed = 0;   // this thread gave up on a wait
     const uint32_t tmemBase = shared.tmemBase;
     uint32_t phase = 0;
-    int failed = 0;   // this thread gave up on a wait
     int aborted = 0;  // some thread of the CTA did (uniform: comes out of a barrier)
 
     TileContext ctx;
@@ -1115,7 +1157,7 @@ template <bool kFp8>
 __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPerSmInt8) SampleKernel(const __grid_constant__ SampleParams params)
 {
     // more than the 48 KB a kernel may declare statically: passed as dynamic shared memory at launch
-    extern __shared__ __align__(16) unsigned char dynamicShared[];
+    extern __shared__ __align__(128) unsigned char dynamicShared[];
     SharedStorage& shared = *reinterpret_cast<SharedStorage*>(dynamicShared);
     __shared__ KernelMip mipTable[16];
 
@@ -1123,41 +1165,14 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
     const int warp = tid >> 5;
     const int half = warp >> 2;
 
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(params.network);
-        uint4* dst = reinterpret_cast<uint4*>(shared.network);
-        for (int i = tid; i < kStagedNetworkBytes / 16; i += kThreadsPerCta)
-            dst[i] = __ldg(src + i);
-        for (int i = tid; i < 256; i += kThreadsPerCta)
-        {
-            __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
-            __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
-            shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
-        }
-        if (tid < params.numMips)
-            mipTable[tid] = params.mips[tid];
-        // constant inputs of the bias K step: 31 slots of kBiasSlotValue and a last slot of 1 per row
-        for (int i = tid; i < kBiasRegionBytes / 16; i += kThreadsPerCta)
-        {
-            const uint32_t fill = kBiasSlotValue * 0x01010101u;
-            reinterpret_cast<uint4*>(shared.biasRegion)[i] =
-                make_uint4(fill, fill, fill, i < 128 ? fill : ((fill & 0x00FFFFFFu) | 0x01000000u));
-        }
-        if (tid == 0)
-        {
-            MbarrierInit(SharedAddress(&shared.barrier), 1);
-            FenceBarrierInit();
-        }
-        if (warp == 0)
-            TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
-        FenceProxyAsyncShared();
-        TcgenFenceBeforeSync();
-        __syncthreads();
-        TcgenFenceAfterSync();
-    }
+    // the mip descriptions are indexed per thread: a copy in shared memory (visible after the barrier inside SetupCta)
+    if (tid < params.numMips)
+        mipTable[tid] = params.mips[tid];
+    if (SetupCta(shared, params.network, params.status, tid, warp))
+        return;
+    int failed = 0, aborted = 0;
     const uint32_t tmemBase = shared.tmemBase;
     uint32_t phase = 0;
-    int failed = 0, aborted = 0;
 
     TileContext ctx;
     ctx.tid = tid;

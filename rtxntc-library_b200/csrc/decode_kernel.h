@@ -35,7 +35,8 @@ constexpr int kFootprintLoBytes = 4096;    // ... and in the low-res grid (half 
 // already includes it.  Layers 0 and 2 have 16 such slots in the padding of their 48 inputs;
 // layers 1, 2 and 3 get one more K step of 32 slots whose A operand is a constant region of shared
 // memory.  When a bias does not fit, the whole network falls back to the bias table
-// (kFlagBiasTable).
+// (kFlagBiasTable).  The FP8 network, whose only int8 layer is the 16-output last one, always uses
+// the table.
 constexpr int kWeightOffset0 = 0;      // 64 x 64
 constexpr int kWeightOffset1 = 4096;   // 48 x 96 (64 inputs + 32 bias slots)
 constexpr int kWeightOffset2 = 8704;   // 32 x 96 (48 inputs + 16 + 32 bias slots)

@@ -305,7 +305,7 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
     }
 
     // Int8 layers: the bias the kernel needs, and its decomposition over the bias slots.
-    bool fits = true;
+    bool fits = !fp8; // the FP8 network's only int8 layer (16 outputs) keeps the table
     int32_t bias[4][64] = {};
     for (int layer = fp8 ? 3 : 0; layer < 4; ++layer)
     {

@@ -95,9 +95,10 @@ def test_kernel_matches_contract_on_ragged_shapes(oracle, shape, network):
 
 
 def test_biases_too_large_for_the_matrix_product_come_from_the_table(oracle):
-    """Int8 layers normally carry their bias in spare K slots of the matrix product; a bias that does
-    not fit there switches the network to the bias table.  Both paths must give the contract's bits,
-    also at the largest bias that still fits and at negative extremes."""
+    """The layers of an Int8 network normally carry their bias in spare K slots of the matrix product;
+    a bias that does not fit there switches the network to the bias table.  Both paths must give the
+    contract's bits, also at the largest bias that still fits and at negative extremes (the FP8
+    network, decoded alongside, always takes its int8 output layer's bias from the table)."""
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(96, 40, 6, 0, 3, 12, seed=77, network="unit"))
     geo = data.geometry
     packed = data.packed_latents()

@@ -182,8 +182,10 @@ def test_weight_staging_layout():
         staged = binding.stage_network(blob, mode)
         assert staged.size == binding.STAGED_NETWORK_BYTES
         source = np.frombuffer(blob, dtype=np.uint8)
-        biases = _file_biases(source, mode)
-        assert staged[STAGED_FLAGS:STAGED_FLAGS + 4].view(np.uint32)[0] == 0  # every bias fits its slots
+        # Int8 networks carry their biases in the matrix product (every bias of this set fits its slots);
+        # the FP8 network's single int8 layer keeps the table
+        biases = _file_biases(source, mode) if mode == binding.WEIGHTS_INT8 else {}
+        assert staged[STAGED_FLAGS:STAGED_FLAGS + 4].view(np.uint32)[0] == (0 if mode == binding.WEIGHTS_INT8 else 1)
         position = 0
         for layer, (nin, nout) in enumerate(zip(geometry.MLP_LAYER_INPUTS, geometry.MLP_LAYER_OUTPUTS)):
             weights = source[position:position + nin * nout].view(np.int8).reshape(nout, nin)
@@ -203,6 +205,7 @@ def test_weight_staging_layout():
         else:
             assert np.array_equal(scales[3, :16], source[8480:8544].view(np.float32))
             assert np.array_equal(staged[STAGED_BIASES:STAGED_BIASES + 128].view(np.float16), source[8192:8320].view(np.float16))
+            assert np.array_equal(staged[STAGED_BIASES + 768:STAGED_BIASES + 832].view(np.int32), source[8544:8608].view(np.int32))
 
 
 def test_weight_staging_falls_back_to_the_bias_table():
