@@ -457,19 +457,23 @@ def run_reference(args) -> dict:
 def run_profile_case(case: str) -> int:
     """A few bare launches of the decode kernel on a small square set, for a profiler to capture.
 
-    `case` is SIZE:MODE:LAUNCHES, e.g. 2048:fp8:2: a SIZE x SIZE 12-channel set with a full mip chain (output
-    larger than L2 from 2048 up, a few hundred MB on the device), MODE fp8 or int8.  Prints a plain line, not
-    the benchmark's JSON line: a figure taken under a profiler is not a benchmark value.
+    `case` is SIZE:MODE:LAUNCHES[:NUMERICS], e.g. 2048:fp8:2: a SIZE x SIZE 12-channel set with a full mip chain
+    (output larger than L2 from 2048 up, a few hundred MB on the device), MODE fp8 or int8, NUMERICS reference
+    (default) or exact.  Prints a plain line, not the benchmark's JSON line: a figure taken under a
+    profiler is not a benchmark value.
     """
     import torch
 
-    size, mode, launches = case.split(":")
+    fields = case.split(":")
+    size, mode, launches = fields[:3]
+    numerics = fields[3] if len(fields) > 3 else "reference"
     entry.load_package()
     from rtxntc_library_b200 import binding, synthetic
 
     spec = synthetic.TextureSetSpec(int(size), int(size), 12, 0, 4, 12, seed=1, weights=mode, latent_alphabet="2bit-even")
     data = synthetic.make_texture_set(spec)
-    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(
+        data, numerics=binding.NUMERICS_EXACT if numerics == "exact" else binding.NUMERICS_REFERENCE)
     params = resident.params(mode == "int8")
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(int(launches)):

@@ -28,6 +28,7 @@ extern "C" {
 #define NTCB_INT8_BLOB_BYTES 9472 /* GenericInt8 weight blob, src/WeightLayout.cpp:142-268 */
 #define NTCB_FP8_BLOB_BYTES 8608  /* GenericFP8 weight blob */
 #define NTCB_STAGED_NETWORK_BYTES 14864 /* size of the device image ntcb_stage_network produces */
+#define NTCB_STAGED_REFERENCE_NETWORK_BYTES 21504 /* ... and of the one ntcb_stage_network_reference produces */
 #define NTCB_STATUS_WORDS 4
 
 typedef enum NtcbStatus
@@ -43,6 +44,18 @@ typedef enum NtcbStatus
     NTCB_ERR_INVALID_STATE = -8,    /* ntc::Status::InvalidState */
     NTCB_ERR_OUT_OF_RANGE = -9      /* ntc::Status::OutOfRange */
 } NtcbStatus;
+
+/* How the matrix products of the decoder network are accumulated.
+   REFERENCE (the default everywhere): binary16 weights, activations and accumulators rounded once per
+   16 products, as the reference's CUDA decoder does (src/Inference.cu:46-136,
+   src/tin/tin_mma.h:126-163): the output reproduces that decoder's bit for bit.
+   EXACT: int8 x int8 -> int32 and e4m3 x e4m3 -> fp32 without intermediate rounding, as the
+   reference's integer inference path does (include/libntc/shaders/Inference.hlsli:133-182). */
+typedef enum NtcbNumerics
+{
+    NTCB_NUMERICS_REFERENCE = 0,
+    NTCB_NUMERICS_EXACT = 1
+} NtcbNumerics;
 
 /* Which weight set decodes: the `useInt8Weights` argument of ITextureSet::Decompress
    (include/libntc/ntc.h:933; src/TextureSet.cpp:1812,1826). */
@@ -113,7 +126,9 @@ typedef struct NtcbDecodeParams
 {
     const uint16_t* latents; /* device: BGRA4 latent pixels, for each neural mip, for each layer, rows
                                 (the reference's encoded-pixel order, src/FeatureGridHost.cpp:140-155) */
-    const void* network;     /* device: NTCB_STAGED_NETWORK_BYTES produced by ntcb_stage_network */
+    const void* network;     /* device: NTCB_STAGED_REFERENCE_NETWORK_BYTES produced by
+                                ntcb_stage_network_reference (NTCB_NUMERICS_REFERENCE), or NTCB_STAGED_NETWORK_BYTES
+                                produced by ntcb_stage_network (NTCB_NUMERICS_EXACT) */
     void* out;               /* device: fp16 texels, or converted pixels when `conversion` is set */
     uint32_t* status;        /* device: NTCB_STATUS_WORDS words, zeroed by the caller before the launch;
                                 word 0 != 0 after the kernel means a bounded wait expired */
@@ -122,7 +137,7 @@ typedef struct NtcbDecodeParams
     int32_t channels;        /* even, 2..16 */
     int32_t weightMode;      /* NtcbWeightMode, must match the staged network */
     int32_t outputLayout;    /* NtcbOutputLayout (ignored when `conversion` is set) */
-    int32_t reserved;
+    int32_t numerics;        /* NtcbNumerics */
     NtcbMipDesc mips[NTCB_MAX_MIPS];
     /* NULL: fp16 texels in `outputLayout`.  Otherwise the kernel's epilogue converts every texel as
        ITextureSet::ReadChannels would after Decompress (src/TextureSet.cpp:915-985) and writes
@@ -140,13 +155,19 @@ const char* ntcb_last_error(void);
 /* Textual name of a status code.  Replaces ntc::StatusToString (include/libntc/ntc.h:1341). */
 const char* ntcb_status_string(int status);
 
-/* Host only.  Converts a row-major weight blob as stored in NTC files (GenericInt8,
-   NTCB_INT8_BLOB_BYTES, or GenericFP8, NTCB_FP8_BLOB_BYTES) into the image the decode kernel copies
-   to shared memory: int8 / e4m3 matrices in the tensor core's K-major core-matrix order with K
+/* Host only, for NTCB_NUMERICS_EXACT.  Converts a row-major weight blob as stored in NTC files
+   (GenericInt8, NTCB_INT8_BLOB_BYTES, or GenericFP8, NTCB_FP8_BLOB_BYTES) into the image the decode
+   kernel copies to shared memory: int8 / e4m3 matrices in the tensor core's K-major core-matrix order with K
    padded to a multiple of 32, fp32 scales, int32 / fp16 biases.  `staged` receives
    NTCB_STAGED_NETWORK_BYTES; the caller uploads it.  Replaces the weight preparation of
    cuda::ConvertNetworkFromQuantizedToFp16 (src/Quantizer.cu:325-480). */
 int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void* staged);
+
+/* Host only.  The same for NTCB_NUMERICS_REFERENCE: rebuilds the binary16 weights and biases exactly
+   as cuda::ConvertNetworkFromQuantizedToFp16 does (UnquantizeColumnInt8 / UnquantizeColumnFP8,
+   src/Quantizer.cu:325-408, same fp32 operation order) and lays them out for the binary16 tensor-core
+   path.  `staged` receives NTCB_STAGED_REFERENCE_NETWORK_BYTES. */
+int ntcb_stage_network_reference(const void* blob, size_t blobBytes, int weightMode, void* staged);
 
 /* Decodes the mips (and row ranges) listed in `params` with one kernel launch on `stream`.
    Asynchronous; the caller synchronises and may then read `status`.  Allocates nothing. */
@@ -198,7 +219,7 @@ typedef struct NtcbTextureSetDesc
 typedef struct NtcbTextureSetFeatures
 {
     int32_t outputLayout; /* NtcbOutputLayout of the internal decoded-texel buffer (default interleaved) */
-    int32_t reserved;
+    int32_t numerics;     /* NtcbNumerics used by Decompress (default: the reference's) */
 } NtcbTextureSetFeatures;
 
 /* ntc::DecompressionStats (include/libntc/ntc.h:810-816); the loss fields need a resident

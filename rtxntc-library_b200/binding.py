@@ -20,6 +20,8 @@ LIBRARY_PATH = os.path.join(_HERE, "libntcb200.so")
 
 MAX_MIPS = 16
 STAGED_NETWORK_BYTES = 14864
+STAGED_REFERENCE_NETWORK_BYTES = 21504
+NUMERICS_REFERENCE, NUMERICS_EXACT = 0, 1  # NtcbNumerics: the reference's binary16 accumulation (default) / exact accumulation
 STATUS_WORDS = 4
 WEIGHTS_INT8, WEIGHTS_FP8 = 0, 1
 LAYOUT_PLANAR_PAIRS, LAYOUT_INTERLEAVED = 0, 1
@@ -63,7 +65,7 @@ class DecodeParams(ctypes.Structure):
     _fields_ = [("latents", ctypes.c_void_p), ("network", ctypes.c_void_p), ("out", ctypes.c_void_p),
                 ("status", ctypes.c_void_p),
                 ("numMips", ctypes.c_int32), ("numFeatures", ctypes.c_int32), ("channels", ctypes.c_int32),
-                ("weightMode", ctypes.c_int32), ("outputLayout", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("weightMode", ctypes.c_int32), ("outputLayout", ctypes.c_int32), ("numerics", ctypes.c_int32),
                 ("mips", MipDesc * MAX_MIPS), ("conversion", ctypes.POINTER(OutputConversion))]
 
 
@@ -88,7 +90,7 @@ class TextureSetDesc(ctypes.Structure):
 
 
 class TextureSetFeatures(ctypes.Structure):
-    _fields_ = [("outputLayout", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+    _fields_ = [("outputLayout", ctypes.c_int32), ("numerics", ctypes.c_int32)]
 
 
 class DecompressionStats(ctypes.Structure):
@@ -133,6 +135,7 @@ def lib():
         handle.ntcb_status_string.argtypes = [ctypes.c_int]
         handle.ntcb_launch_count.restype = ctypes.c_uint64
         handle.ntcb_stage_network.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+        handle.ntcb_stage_network_reference.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
         handle.ntcb_sample.argtypes = [ctypes.POINTER(SampleParams), ctypes.c_void_p]
         handle.ntcb_decode_resident_ctas.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
@@ -171,10 +174,15 @@ def check(code: int) -> None:
         raise NtcbError(code, lib().ntcb_last_error().decode())
 
 
-def stage_network(blob: bytes, weight_mode: int) -> np.ndarray:
-    """Host-side conversion of a GenericInt8 / GenericFP8 blob into the kernel's image."""
-    staged = np.zeros(STAGED_NETWORK_BYTES, dtype=np.uint8)
+def stage_network(blob: bytes, weight_mode: int, numerics: int = NUMERICS_REFERENCE) -> np.ndarray:
+    """Host-side conversion of a GenericInt8 / GenericFP8 blob into the image of the kernel that
+    implements `numerics`."""
     source = np.frombuffer(blob, dtype=np.uint8)
+    if numerics == NUMERICS_REFERENCE:
+        staged = np.zeros(STAGED_REFERENCE_NETWORK_BYTES, dtype=np.uint8)
+        check(lib().ntcb_stage_network_reference(source.ctypes.data, len(blob), weight_mode, staged.ctypes.data))
+        return staged
+    staged = np.zeros(STAGED_NETWORK_BYTES, dtype=np.uint8)
     check(lib().ntcb_stage_network(source.ctypes.data, len(blob), weight_mode, staged.ctypes.data))
     return staged
 
@@ -260,7 +268,8 @@ class ResidentTextureSet:
     output buffer for the whole mip chain and the status words."""
 
     def __init__(self, geo: Geometry, packed_latents: np.ndarray, int8_blob: bytes, fp8_blob: bytes,
-                 device: str = "cuda:0", layout: int = LAYOUT_INTERLEAVED, allocate_output: bool = True):
+                 device: str = "cuda:0", layout: int = LAYOUT_INTERLEAVED, allocate_output: bool = True,
+                 numerics: int = NUMERICS_REFERENCE):
         import torch
 
         self.torch = torch
@@ -269,9 +278,12 @@ class ResidentTextureSet:
         self.layout = layout
         lib()
         self.latents = torch.from_numpy(np.ascontiguousarray(packed_latents).view(np.int16)).to(self.device)
+        self.numerics = numerics
+        self._blobs = {WEIGHTS_INT8: int8_blob, WEIGHTS_FP8: fp8_blob}
+        self._exact_networks = {}
         self.networks = {
-            WEIGHTS_INT8: torch.from_numpy(stage_network(int8_blob, WEIGHTS_INT8)).to(self.device),
-            WEIGHTS_FP8: torch.from_numpy(stage_network(fp8_blob, WEIGHTS_FP8)).to(self.device),
+            WEIGHTS_INT8: torch.from_numpy(stage_network(int8_blob, WEIGHTS_INT8, numerics)).to(self.device),
+            WEIGHTS_FP8: torch.from_numpy(stage_network(fp8_blob, WEIGHTS_FP8, numerics)).to(self.device),
         }
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=self.device)
         self.out = torch.empty(out_elements(geo), dtype=torch.float16, device=self.device) if allocate_output else None
@@ -284,8 +296,10 @@ class ResidentTextureSet:
     def params(self, use_int8: bool, out=None, mips=None, row_ranges=None, conversion=None) -> DecodeParams:
         mode = WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8
         out = self.out if out is None else out
-        return fill_params(self.geometry, self.latents.data_ptr(), self.networks[mode].data_ptr(), out.data_ptr(),
-                           self.status.data_ptr(), mode, self.layout, mips, row_ranges, conversion)
+        params = fill_params(self.geometry, self.latents.data_ptr(), self.networks[mode].data_ptr(), out.data_ptr(),
+                             self.status.data_ptr(), mode, self.layout, mips, row_ranges, conversion)
+        params.numerics = self.numerics
+        return params
 
     def decode_converted(self, use_int8: bool, conversion: OutputConversion, mips=None, row_ranges=None):
         """Decode with the converting epilogue into a fresh device buffer covering the whole mip
@@ -310,12 +324,19 @@ class ResidentTextureSet:
 
     def sample(self, queries, use_int8: bool):
         """Inference on sample: `queries` is a float32 CUDA tensor [n][3] of (u, v, lod); returns a
-        float16 CUDA tensor [n][channels].  Queued on torch's current stream."""
+        float16 CUDA tensor [n][channels].  Queued on torch's current stream.  The sample kernel
+        computes with exact accumulation whatever the numerics of this object."""
         torch = self.torch
         mode = WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8
         queries = queries.contiguous()
         out = torch.empty((queries.shape[0], self.geometry.channels), dtype=torch.float16, device=self.device)
-        decode = fill_params(self.geometry, self.latents.data_ptr(), self.networks[mode].data_ptr(), out.data_ptr(),
+        if self.numerics == NUMERICS_EXACT:
+            network = self.networks[mode]
+        else:
+            if mode not in self._exact_networks:
+                self._exact_networks[mode] = torch.from_numpy(stage_network(self._blobs[mode], mode, NUMERICS_EXACT)).to(self.device)
+            network = self._exact_networks[mode]
+        decode = fill_params(self.geometry, self.latents.data_ptr(), network.data_ptr(), out.data_ptr(),
                              self.status.data_ptr(), mode)
         params = SampleParams()
         params.latents, params.network, params.queries = decode.latents, decode.network, queries.data_ptr()
@@ -361,8 +382,9 @@ class Context:
         check(lib().ntcb_context_create(device, ctypes.byref(self.handle)))
         self.device = device
 
-    def create_texture_set(self, container: bytes, layout: int = LAYOUT_INTERLEAVED) -> "TextureSet":
-        return TextureSet(self, container, layout)
+    def create_texture_set(self, container: bytes, layout: int = LAYOUT_INTERLEAVED,
+                           numerics: int = NUMERICS_REFERENCE) -> "TextureSet":
+        return TextureSet(self, container, layout, numerics)
 
     def close(self) -> None:
         if self.handle:
@@ -380,10 +402,10 @@ class TextureSet:
     """ntcb_texture_set_*: a compressed texture set loaded from an NTC container (the counterpart
     of ntc::ITextureSet for decompression)."""
 
-    def __init__(self, context: Context, container: bytes, layout: int = LAYOUT_INTERLEAVED):
+    def __init__(self, context: Context, container: bytes, layout: int = LAYOUT_INTERLEAVED, numerics: int = NUMERICS_REFERENCE):
         self.context = context
         self.handle = ctypes.c_void_p()
-        features = TextureSetFeatures(layout, 0)
+        features = TextureSetFeatures(layout, numerics)
         buffer = np.frombuffer(container, dtype=np.uint8)
         check(lib().ntcb_texture_set_create_from_memory(context.handle, buffer.ctypes.data, len(container),
                                                         ctypes.byref(features), ctypes.byref(self.handle)))

@@ -35,7 +35,9 @@
 #include <atomic>
 
 #include "decode_kernel.h"
+#include "kernel_parts.cuh"
 #include "output_convert.cuh"
+#include "epilogue_convert.cuh"
 
 namespace ntcb
 {
@@ -45,89 +47,6 @@ namespace
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t SharedAddress(const void* p)
-{
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void MbarrierInit(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void FenceBarrierInit()
-{
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-
-__device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
-{
-    uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
-// Announces `bytes` of asynchronous copies that will complete on the barrier, and arrives on it.
-__device__ __forceinline__ void MbarrierArriveExpectTx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-// TMA bulk copy global -> shared memory of this CTA (addresses and size multiples of 16 bytes);
-// completion is signalled on the barrier.
-__device__ __forceinline__ void BulkCopyToShared(uint32_t dstShared, const void* srcGlobal, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dstShared), "l"(srcGlobal), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-// Bounded wait: returns false when the barrier did not complete within the spin budget.
-__device__ __forceinline__ bool MbarrierWaitBounded(uint32_t bar, uint32_t parity)
-{
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
-    {
-        if (MbarrierTryWait(bar, parity))
-            return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void FenceProxyAsyncShared()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-__device__ __forceinline__ void TcgenFenceBeforeSync()
-{
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ void TcgenFenceAfterSync()
-{
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ void TmemAlloc(uint32_t sharedSlot, uint32_t columns)
-{
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sharedSlot), "r"(columns)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void TmemFree(uint32_t address, uint32_t columns)
-{
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
-}
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 32 bytes of 8-bit operands.
 template <bool kFp8>
@@ -157,40 +76,6 @@ __device__ __forceinline__ void Umma(uint32_t tmemD, uint64_t descA, uint64_t de
     }
 }
 
-__device__ __forceinline__ void UmmaCommit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// 16 consecutive 32-bit columns of this thread's TMEM lane.
-__device__ __forceinline__ void TmemLoad16(uint32_t address, uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(address)
-        : "memory");
-}
-
-__device__ __forceinline__ void TmemLoadWait()
-{
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, K-major, no swizzle: 8x16-byte core matrices; `leadingBytes`
-// separates core matrices along K, `strideBytes` separates 8-row groups along M/N.
-__device__ __forceinline__ uint64_t MakeSmemDescriptor(uint32_t sharedAddress, uint32_t leadingBytes, uint32_t strideBytes)
-{
-    uint64_t desc = 0;
-    desc |= uint64_t((sharedAddress & 0x3FFFF) >> 4);
-    desc |= uint64_t((leadingBytes >> 4) & 0x3FFF) << 16;
-    desc |= uint64_t((strideBytes >> 4) & 0x3FFF) << 32;
-    desc |= uint64_t(1) << 46; // descriptor version of this architecture
-    return desc;               // base offset 0, layout type 0 (no swizzle)
-}
-
 // Instruction descriptor: dense, K-major A and B, M = 128.
 __host__ __device__ constexpr uint32_t MakeInstrDescriptor(bool fp8, int n)
 {
@@ -203,16 +88,6 @@ __host__ __device__ constexpr uint32_t MakeInstrDescriptor(bool fp8, int n)
 // ---------------------------------------------------------------------------------------------
 // Small arithmetic helpers
 // ---------------------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t AsU32(__half2 v)
-{
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-__device__ __forceinline__ __half2 AsHalf2(uint32_t v)
-{
-    return *reinterpret_cast<__half2*>(&v);
-}
 
 // Quantises a pair of network inputs.  Int8: floor(x * 127.5 - 0.5) clamped to +-127
 // (src/tin/tin_mlp.h:25-31), returned as the low bytes of the two 16-bit lanes.  FP8: round to
@@ -274,36 +149,6 @@ __device__ __forceinline__ uint32_t ActivatePair(__half2 x)
     }
 }
 
-struct GridTaps
-{
-    int o00, o01, o10, o11;
-    __half2 w00, w01, w10, w11;
-};
-
-// Bilinear footprint of one texel in one latent grid (src/FeatureGridDevice.h:33-58).
-__device__ __forceinline__ void SetupTaps(float u, float v, int w, int h, GridTaps& taps)
-{
-    float px = __fmaf_rn(u, float(w), -0.5f);
-    float py = __fmaf_rn(v, float(h), -0.5f);
-    float xbf = floorf(px), ybf = floorf(py);
-    float dx = __fsub_rn(px, xbf), dy = __fsub_rn(py, ybf);
-    float dxn = __fsub_rn(1.f, dx), dyn = __fsub_rn(1.f, dy);
-    int xb = int(xbf), yb = int(ybf);
-    // wrap addressing; the sample position is < size - 0.5, so only -1 needs folding
-    int x0 = xb < 0 ? xb + w : xb;
-    int y0 = yb < 0 ? yb + h : yb;
-    int x1 = (x0 + 1 == w) ? 0 : x0 + 1;
-    int y1 = (y0 + 1 == h) ? 0 : y0 + 1;
-    taps.o00 = y0 * w + x0;
-    taps.o01 = y0 * w + x1;
-    taps.o10 = y1 * w + x0;
-    taps.o11 = y1 * w + x1;
-    taps.w00 = __half2half2(__float2half_rn(__fmul_rn(dxn, dyn)));
-    taps.w01 = __half2half2(__float2half_rn(__fmul_rn(dx, dyn)));
-    taps.w10 = __half2half2(__float2half_rn(__fmul_rn(dxn, dy)));
-    taps.w11 = __half2half2(__float2half_rn(__fmul_rn(dx, dy)));
-}
-
 // One latent pixel layer (four 4-bit features) of one grid -> four quantised inputs.
 // Blend order as the reference build evaluates it: fma(l11,w3, fma(l10,w2, fma(l00,w0, l01*w1))).
 template <bool kFp8>
@@ -326,11 +171,6 @@ __device__ __forceinline__ uint32_t SampleLayer(const uint16_t* __restrict__ pla
         pairs[j] = QuantizeInputPair<kFp8>(d);
     }
     return PackCodes<kFp8>(pairs[0], pairs[1]);
-}
-
-__device__ __forceinline__ float Frac(float t)
-{
-    return __fsub_rn(t, floorf(t));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -369,17 +209,6 @@ struct __align__(128) SharedStorage
     uint32_t tmemBase;
 };
 
-
-// One axis of the bilinear footprint (src/FeatureGridDevice.h:35-45): base tap index (before
-// wrapping) and the fractional offset of a texel coordinate in a latent grid of `size` pixels.
-__device__ __forceinline__ void AxisTap(int texel, float invExtent, int size, int& base, float& frac)
-{
-    const float u = __fmul_rn(__fadd_rn(float(texel), 0.5f), invExtent);
-    const float p = __fmaf_rn(u, float(size), -0.5f);
-    const float b = floorf(p);
-    base = int(b);
-    frac = __fsub_rn(p, b);
-}
 
 // Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory
 // (nibbles unpacked to binary16 once per latent pixel instead of once per texel and tap).
@@ -587,169 +416,6 @@ __device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
 
 // Second half of a layer: waits for the MMA, then applies the activation and writes the next
 // layer's A operand (layers 0-2) or runs the output epilogue (layer 3).
-// Stores `bytes` bytes of a pixel held in `words` (little endian) at `pixel`, whose address and
-// size are both multiples of the widest store used.
-template <int kMaxWords>
-__device__ __forceinline__ void StorePixel(unsigned char* pixel, const uint32_t (&words)[kMaxWords], int bytes)
-{
-    if ((bytes & 15) == 0 && kMaxWords >= 4)
-    {
-#pragma unroll
-        for (int w = 0; w + 3 < kMaxWords; w += 4)
-            if (w * 4 < bytes)
-                *reinterpret_cast<uint4*>(pixel + w * 4) = make_uint4(words[w], words[w + 1], words[w + 2], words[w + 3]);
-    }
-    else if ((bytes & 7) == 0 && kMaxWords >= 2)
-    {
-#pragma unroll
-        for (int w = 0; w + 1 < kMaxWords; w += 2)
-            if (w * 4 < bytes)
-                *reinterpret_cast<uint2*>(pixel + w * 4) = make_uint2(words[w], words[w + 1]);
-    }
-    else if ((bytes & 3) == 0)
-    {
-#pragma unroll
-        for (int w = 0; w < kMaxWords; ++w)
-            if (w * 4 < bytes)
-                *reinterpret_cast<uint32_t*>(pixel + w * 4) = words[w];
-    }
-    else if ((bytes & 1) == 0)
-    {
-#pragma unroll
-        for (int h = 0; h < kMaxWords * 2; ++h)
-            if (h * 2 < bytes)
-                *reinterpret_cast<uint16_t*>(pixel + h * 2) = uint16_t(words[h >> 1] >> (16 * (h & 1)));
-    }
-    else
-    {
-#pragma unroll
-        for (int b = 0; b < kMaxWords * 4; ++b)
-            if (b < bytes)
-                pixel[b] = (unsigned char)(words[b >> 2] >> (8 * (b & 3)));
-    }
-}
-
-// Converting epilogue for one channel format: pairs[j] holds the requested channels 2j and 2j + 1
-// as (scrubbed) binary16; the pixel goes to ctx.out.  What ITextureSet::ReadChannels would produce
-// from the stored texels (src/TextureSet.cpp:915-985, src/ImageProcessing.cu:220-266).
-template <int kFormat>
-__device__ __forceinline__ void ConvertPixel(const OutputConversion& conversion, int numChannels, const TileContext& ctx,
-    const uint32_t (&pairs)[8])
-{
-    constexpr int kBytes = kFormat == kFormatUnorm8 ? 1 : (kFormat == kFormatUnorm16 || kFormat == kFormatFloat16) ? 2 : 4;
-    constexpr int kPerWord = 4 / kBytes;
-    constexpr int kMaxWords = 16 / kPerWord;
-    const int components = conversion.dstChannels;
-    uint32_t words[kMaxWords];
-#pragma unroll
-    for (int w = 0; w < kMaxWords; ++w)
-        words[w] = 0;
-
-    const bool plain = (conversion.srcSpaces | conversion.dstSpaces) == 0 && !conversion.dither;
-    if (kFormat == kFormatUnorm8 && plain)
-    {
-        // Linear, undithered UNORM8: round(clamp(v) * 255).  The product of a binary16 value and 255 is
-        // exact in binary32 and its only tie inside [0, 255] is 127.5 (v = 0.5), which rounds to 128
-        // both to nearest-even and away from zero, so adding 1.5 * 2^23 leaves the reference's
-        // roundf() result in the low byte.  (Decoded texels are finite: the epilogue scrubs Inf / NaN.)
-        const __half2 one = __float2half2_rn(1.f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-        {
-            if (2 * j < components)
-            {
-                const float2 v = __half22float2(__hmul2_sat(AsHalf2(pairs[j]), one));
-                uint32_t lo = __float_as_uint(__fmaf_rn(v.x, 255.f, 12582912.f));
-                uint32_t hi = __float_as_uint(__fmaf_rn(v.y, 255.f, 12582912.f));
-                // components past the requested channels: 0, component 3: 255
-                if (2 * j >= numChannels) lo = (2 * j == 3) ? 255u : 0u;
-                if (2 * j + 1 >= numChannels) hi = (2 * j + 1 == 3) ? 255u : 0u;
-                if (2 * j + 1 >= components) hi = 0u;
-                // byte 0 of each holds the code; an odd pair lands in the upper half of its word
-                words[j >> 1] = (j & 1) ? __byte_perm(words[j >> 1], __byte_perm(lo, hi, 0x0040), 0x5410)
-                                        : (__byte_perm(lo, hi, 0x0040) & 0xFFFFu);
-            }
-        }
-    }
-    else if (plain)
-    {
-        // linear and undithered in another format: no colour-space branches, no generator
-#pragma unroll
-        for (int c = 0; c < 16; ++c)
-        {
-            if (c < components)
-            {
-                const __half2 pair = AsHalf2(pairs[c >> 1]);
-                float value = __half2float((c & 1) ? __high2half(pair) : __low2half(pair));
-                if (c >= numChannels)
-                    value = c == 3 ? 1.f : 0.f;
-                words[c / kPerWord] |= QuantizeComponent(kFormat, value, 0.f) << (8 * kBytes * (c % kPerWord));
-            }
-        }
-    }
-    else
-    {
-        const uint32_t seed = conversion.dither ? DitherSeed(ctx.outStepWords) : 0u;
-#pragma unroll
-        for (int c = 0; c < 16; ++c)
-        {
-            if (c < components)
-            {
-                const float dither = conversion.dither ? DitherDraw(seed, uint32_t(c) + 1u) : 0.f;
-                const __half2 pair = AsHalf2(pairs[c >> 1]);
-                const __half texel = (c & 1) ? __high2half(pair) : __low2half(pair);
-                uint32_t component;
-                if (c < numChannels)
-                {
-                    float value = __half2float(texel);
-                    const int srcSpace = (conversion.srcSpaces >> (2 * c)) & 3;
-                    const int dstSpace = (conversion.dstSpaces >> (2 * c)) & 3;
-                    if (srcSpace | dstSpace)
-                        value = EncodeColorSpace(dstSpace, DecodeColorSpace(srcSpace, value));
-                    component = QuantizeComponent(kFormat, value, dither);
-                }
-                else
-                    component = QuantizeComponent(kFormat, c == 3 ? 1.f : 0.f, dither);
-                words[c / kPerWord] |= component << (8 * kBytes * (c % kPerWord));
-            }
-        }
-    }
-    StorePixel<kMaxWords>(reinterpret_cast<unsigned char*>(ctx.out), words, components * kBytes);
-}
-
-// Converting epilogue: the thread's (scrubbed) fp16 channel pairs -> the pixel in the client's
-// format, stored at ctx.out.
-__device__ __forceinline__ void StoreConverted(const OutputConversion& conversion, int firstChannel, int numChannels,
-    const TileContext& ctx, uint32_t (&bits)[8])
-{
-    if (firstChannel != 0)
-    {
-        // Re-base the channels so that the first requested one sits in bits[0]: park them in the
-        // thread's own slots of the A operand, which the tensor core has finished reading (layer 3's
-        // MMA has completed), and read them back from the shifted position.
-        uint4* slot = ctx.rowChunk;
-        slot[0] = make_uint4(bits[0], bits[1], bits[2], bits[3]);
-        slot[128] = make_uint4(bits[4], bits[5], bits[6], bits[7]);
-        const unsigned char* parked = reinterpret_cast<const unsigned char*>(slot);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-        {
-            const int c0 = firstChannel + 2 * j, c1 = c0 + 1;
-            const uint32_t lo = c0 < 16 ? *reinterpret_cast<const uint16_t*>(parked + (c0 >> 3) * 2048 + (c0 & 7) * 2) : 0u;
-            const uint32_t hi = c1 < 16 ? *reinterpret_cast<const uint16_t*>(parked + (c1 >> 3) * 2048 + (c1 & 7) * 2) : 0u;
-            bits[j] = lo | (hi << 16);
-        }
-    }
-    switch (conversion.format)
-    {
-    case kFormatUnorm8: ConvertPixel<kFormatUnorm8>(conversion, numChannels, ctx, bits); break;
-    case kFormatUnorm16: ConvertPixel<kFormatUnorm16>(conversion, numChannels, ctx, bits); break;
-    case kFormatFloat16: ConvertPixel<kFormatFloat16>(conversion, numChannels, ctx, bits); break;
-    case kFormatFloat32: ConvertPixel<kFormatFloat32>(conversion, numChannels, ctx, bits); break;
-    default: ConvertPixel<kFormatUint32>(conversion, numChannels, ctx, bits); break;
-    }
-}
-
 template <bool kFp8, int kLayer, bool kConvert, bool kBiasTable, typename Params>
 __device__ __forceinline__ void ConsumeLayerImpl(const Params& params, const SharedStorage& shared,
     const TileContext& ctx, uint32_t& phase, int& failed)

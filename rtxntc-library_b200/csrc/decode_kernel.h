@@ -49,6 +49,26 @@ constexpr uint32_t kFlagBiasTable = 1; // int8 layers add their bias from the ta
 constexpr int kBiasSlotValue = 127;
 constexpr int kBiasRegionBytes = 128 * 32; // constant A operand of the extra K step: 128 rows x 32 slots
 
+// Image of the network for the reference-numerics kernel (produced by ntcb_stage_network_reference):
+// binary16 weights as the reference's CUDA path rebuilds them from the file
+// (src/Quantizer.cu:325-408), K-major core matrices of 8 halves (element (n, k) of layer l at
+// (k / 8) * (N_l * 16) + n * 16 + (k % 8) * 2), followed per layer by the operand of the "bias
+// step": an N_l x 16 matrix whose column 0 is the binary16 bias.  Multiplied by a constant A operand
+// whose rows are (1, 0, ..., 0), it sets the accumulators to the bias exactly, as the reference
+// initialises its accumulator fragments (src/tin/tin_mlp.h:71-89).
+constexpr int kRefWeightOffset0 = 0;       // 64 x 48 halves
+constexpr int kRefWeightOffset1 = 6144;    // 48 x 64
+constexpr int kRefWeightOffset2 = 12288;   // 32 x 48
+constexpr int kRefWeightOffset3 = 15360;   // 16 x 32
+constexpr int kRefBiasOffset0 = 16384;     // 64 x 16 halves
+constexpr int kRefBiasOffset1 = 18432;     // 48 x 16
+constexpr int kRefBiasOffset2 = 19968;     // 32 x 16
+constexpr int kRefBiasOffset3 = 20992;     // 16 x 16
+constexpr int kRefNetworkBytes = 21504;
+constexpr int kRefOperandBytes = 128 * 128; // A operand of one half: 128 rows x 64 halves
+constexpr int kRefFootprintHiBytes = 8192;  // the binary16 operands leave less room for the high-res footprint
+constexpr int kCtasPerSmRef = 3;
+
 constexpr uint32_t kStatusBarrierTimeout = 1;
 
 constexpr int kLayoutPlanarPairs = 0;
@@ -106,6 +126,8 @@ struct SampleParams
 int MakeOutputConversion(const ::NtcbOutputConversion& request, int channels, OutputConversion& out);
 
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
+// The reference-numerics kernel (decode_kernel_ref.cu): params.network is a kRefNetworkBytes image.
+cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
 cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream);
 
 } // namespace ntcb

@@ -1,0 +1,723 @@
+// NTC decode kernel for sm_100a with the REFERENCE'S numerics: binary16 weights, binary16
+// activations and binary16 accumulators that are rounded once per 16 products, as LibNTC's own CUDA
+// decoder computes (src/Inference.cu:46-136, src/tin/tin_mlp.h:22-89, src/tin/tin_mma.h:126-163).
+//
+// tcgen05.mma kind::f16 with a binary16 accumulator format (K = 16 per instruction) rounds exactly
+// like the legacy wmma m16n16k16 path the reference is built on, so this kernel reproduces the
+// reference's output bit for bit while keeping the structure of the exact-accumulation kernel in
+// decode_kernel.cu: a 32x8 texel tile per CTA of 256 threads (thread = texel), two 128-row GEMM
+// chains per tile, weights resident in shared memory, accumulators in tensor memory.
+//
+// What differs from decode_kernel.cu:
+//   * the A operand holds binary16 values (the de-quantised network inputs / activations), 128 bytes
+//     per row, written by the threads in K-major core-matrix order: 16-byte chunk j (8 halves) of
+//     row r at j * 2048 + r * 16;
+//   * each layer starts with a "bias step": an MMA whose A operand is a constant region with rows
+//     (1, 0, ..., 0) and whose B operand holds the bias in column 0, which sets the accumulators to
+//     the binary16 bias exactly; the K = 16 steps of the layer then accumulate onto it;
+//   * the accumulators come back as binary16 (tcgen05.ld ... pack::16b: two per register), ready for
+//     the packed-half activation; there is no scale, no integer bias, no conversion;
+//   * activations are re-quantised and immediately de-quantised (e4m3, or the int8 grid k * 0.0125),
+//     as the reference does (src/tin/tin_activation.h:44-48, 94-99).
+//
+// Every wait on an mbarrier is bounded, as in decode_kernel.cu.
+
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "decode_kernel.h"
+#include "kernel_parts.cuh"
+#include "output_convert.cuh"
+#include "epilogue_convert.cuh"
+
+namespace ntcb
+{
+namespace
+{
+
+// D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
+__device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(tmemD),
+        "l"(descA), "l"(descB), "r"(instr), "r"(accumulate)
+        : "memory");
+}
+
+// Instruction descriptor: dense, K-major A and B in binary16 (format 0), binary16 accumulators
+// (format 0), M = 128; bits 17-22: N >> 3; bits 24-28: M >> 4.
+__host__ __device__ constexpr uint32_t MakeInstrDescriptorF16(int n)
+{
+    return (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+}
+
+// 32 consecutive binary16 accumulators of this thread's TMEM lane, two per register (an
+// accumulator occupies the low half of a 32-bit TMEM cell; pack::16b joins adjacent columns).
+__device__ __forceinline__ void TmemLoadPacked16(uint32_t address, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.pack::16b.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address)
+        : "memory");
+}
+
+// 16 consecutive binary16 accumulators, two per register.
+__device__ __forceinline__ void TmemLoadPacked8(uint32_t address, uint32_t (&r)[8])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.pack::16b.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+        : "r"(address)
+        : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Quantisers (value in, de-quantised value out)
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ __half2 RoundTripE4m3(__half2 x)
+{
+    // src/tin/tin_activation.h:44-48: round to nearest even e4m3, saturating, and back to binary16
+    const __nv_fp8x2_storage_t codes = __nv_cvt_halfraw2_to_fp8x2(static_cast<__half2_raw>(x), __NV_SATFINITE, __NV_E4M3);
+    return __half2(__nv_cvt_fp8x2_to_halfraw2(codes, __NV_E4M3));
+}
+
+// A pair of network inputs as the first layer sees them.  Int8: floor(x * 127.5 - 0.5) clamped to
+// +-127, times 1 / 127.5 (src/tin/tin_mlp.h:22-37).  FP8: rounded to e4m3.
+template <bool kFp8>
+__device__ __forceinline__ __half2 QuantizeInputRef(__half2 x)
+{
+    if (kFp8)
+        return RoundTripE4m3(x);
+    __half2 y = __hfma2(x, __float2half2_rn(127.5f), __float2half2_rn(-0.5f));
+    y = h2floor(y);
+    y = __hmax2(__hmin2(y, __float2half2_rn(127.f)), __float2half2_rn(-127.f));
+    return __hmul2_rn(y, __float2half2_rn(1.f / 127.5f));
+}
+
+// Clamped HGELU in binary16 (src/tin/tin_activation.h:88-92) followed by the quantiser of the next
+// layer's inputs: e4m3, or the int8 grid rint(y * 80) * 0.0125 (src/tin/tin_activation.h:94-99).
+template <bool kToFp8>
+__device__ __forceinline__ uint32_t ActivateRef(uint32_t bits)
+{
+    const __half2 x = AsHalf2(bits);
+    const __half2 third = __float2half2_rn(1 / 3.f);
+    const __half2 t = __hfma2_sat(third, x, __float2half2_rn(0.5f));
+    const __half2 m = __hmin2(x, __float2half2_rn(3.f));
+    const __half2 y = __hmul2_rn(m, t);
+    if (kToFp8)
+        return AsU32(RoundTripE4m3(y));
+    const __half2 p = __hmul2_rn(y, __float2half2_rn(80.f));
+    // rint(p), p in [-15, 240]: the binary16 spacing is 1 in [1024, 2048)
+    __half2 r = __hadd2_rn(p, __float2half2_rn(1536.f));
+    r = __hadd2_rn(r, __float2half2_rn(-1536.f));
+    return AsU32(__hmul2_rn(r, __float2half2_rn(3.1875f / 255.f)));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Shared memory
+// ---------------------------------------------------------------------------------------------
+
+// Per-tile lookup tables (separable in x and y, computed once per tile column / row).
+struct __align__(16) RefTileTables
+{
+    int4 colTap[2][kTileWidth];   // per grid and column: footprint x index, dx, 1 - dx
+    int4 rowTap[2][kTileHeight];  // per grid and row: footprint y index, dy, 1 - dy
+    // positional encoding as quantised binary16 pairs: word w = (wave w phase 0, wave w phase 0.25)
+    uint4 colEnc[kTileWidth];
+    uint4 rowEnc[kTileHeight];
+    int footWidth[2];
+    uint32_t lodPair;   // (lod, lod)
+    uint32_t zeroPair;  // (quantised 0, quantised 0)
+};
+
+struct __align__(128) RefSharedStorage
+{
+    uint8_t network[kRefNetworkBytes];                     // binary16 weights and bias-step operands
+    alignas(128) uint8_t operandA[2 * kRefOperandBytes];   // A operands of the current layer (top half, bottom half)
+    alignas(128) uint8_t biasRegion[128 * 32];             // constant A operand of the bias step: rows (1, 0 x 15)
+    uint8_t footprintHi[kRefFootprintHiBytes];
+    uint8_t footprintLo[kFootprintLoBytes];
+    uint32_t latentTable[256];
+    RefTileTables tables;
+    uint64_t barrier;      // MMA completion
+    uint64_t loadBarrier;  // arrival of the network image
+    uint32_t tmemBase;
+};
+
+struct RefTileContext
+{
+    int tid;
+    uint32_t tmemBase, tmemLane, barrier, operandA, networkBase, biasRegion;
+    uint4* rowChunk; // this thread's 16-byte slot in chunk 0 of its half's A operand
+    int tile, x, y;
+    uint32_t* out;
+    uint32_t outStepWords;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Inputs
+// ---------------------------------------------------------------------------------------------
+
+// Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory.
+// Even warps work on the high-res grid, odd warps on the low-res grid.
+template <bool kFp8>
+__device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const KernelMip& mip, RefSharedStorage& shared,
+    int tileX0, int tileY0, int lane, int warp)
+{
+    const int grid = warp & 1;
+    const int gw = grid ? mip.loWidth : mip.hiWidth;
+    const int gh = grid ? mip.loHeight : mip.hiHeight;
+
+    int xb, yb;
+    float dx, dy;
+    AxisTap(min(tileX0 + lane, mip.width - 1), mip.invWidth, gw, xb, dx);
+    AxisTap(min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
+    const int fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
+    const int fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
+    const int footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
+    const int footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
+
+    if (warp < 2)
+    {
+        shared.tables.colTap[grid][lane] = make_int4(xb - fx0, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
+        if (lane < kTileHeight)
+            shared.tables.rowTap[grid][lane] = make_int4(yb - fy0, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
+        if (lane == 0)
+            shared.tables.footWidth[grid] = footW;
+    }
+    else if (warp < 4)
+    {
+        // positional encoding (src/RegressionKernels.h:59-85): warp 2 the x part per column, warp 3
+        // the y part per row, quantised exactly as the per-texel inputs would be
+        const bool rows = warp == 3;
+        const int coordinate = rows ? min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1) : min(tileX0 + lane, mip.width - 1);
+        float f = __fmul_rn(float(coordinate), mip.positionScale);
+        uint32_t q[3];
+#pragma unroll
+        for (int wave = 0; wave < 3; ++wave)
+        {
+            const float e0 = __fmaf_rn(Frac(f), 2.f, -1.f);
+            const float e1 = __fmaf_rn(Frac(__fadd_rn(f, 0.25f)), 2.f, -1.f);
+            q[wave] = AsU32(QuantizeInputRef<kFp8>(__floats2half2_rn(e0, e1)));
+            f = __fmul_rn(f, 2.f);
+        }
+        if (!rows)
+            shared.tables.colEnc[lane] = make_uint4(q[0], q[1], q[2], 0);
+        else if (lane < kTileHeight)
+            shared.tables.rowEnc[lane] = make_uint4(q[0], q[1], q[2], 0);
+        if (rows && lane == kTileHeight)
+        {
+            shared.tables.lodPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(mip.positionLod)));
+            shared.tables.zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
+        }
+    }
+
+    if (mip.staged)
+    {
+        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
+        const int count = footW * footH;
+        // p / footW == (p * magic) >> 20 for p < 2048; the IEEE quotient of 2^20 / footW floors exactly
+        const uint32_t magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
+        const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
+        const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
+        uint8_t* foot = grid ? shared.footprintLo : shared.footprintHi;
+        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
+        {
+            const int fy = int((uint32_t(p) * magic) >> 20);
+            const int fx = p - fy * footW;
+            // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
+            int gx = fx0 + fx, gy = fy0 + fy;
+            gx += gx < 0 ? gw : 0;
+            gx -= gx >= gw ? gw : 0;
+            gy += gy < 0 ? gh : 0;
+            gy -= gy >= gh ? gh : 0;
+            const uint16_t* src = plane0 + size_t(gy) * gw + gx;
+            uint2* dst = reinterpret_cast<uint2*>(foot + (size_t(p) << mip.strideShift));
+#pragma unroll
+            for (int layer = 0; layer < 4; ++layer)
+            {
+                if (layer < params.numLayers)
+                {
+                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
+                    dst[layer] = make_uint2(shared.latentTable[pixel & 0xFF], shared.latentTable[pixel >> 8]);
+                }
+            }
+        }
+    }
+}
+
+// Four inputs of one latent layer from the four taps, as two binary16 pairs.
+// Blend order as the reference build evaluates it: fma(l11,w3, fma(l10,w2, fma(l00,w0, l01*w1))).
+template <bool kFp8>
+__device__ __forceinline__ void BlendLayerRef(uint2 l00, uint2 l01, uint2 l10, uint2 l11, __half2 w00, __half2 w01,
+    __half2 w10, __half2 w11, uint32_t* words)
+{
+    const __half2 two = __float2half2_rn(2.f), minusOne = __float2half2_rn(-1.f);
+    __half2 a = __hmul2_rn(AsHalf2(l01.x), w01);
+    __half2 b = __hmul2_rn(AsHalf2(l01.y), w01);
+    a = __hfma2(AsHalf2(l00.x), w00, a);
+    b = __hfma2(AsHalf2(l00.y), w00, b);
+    a = __hfma2(AsHalf2(l10.x), w10, a);
+    b = __hfma2(AsHalf2(l10.y), w10, b);
+    a = __hfma2(AsHalf2(l11.x), w11, a);
+    b = __hfma2(AsHalf2(l11.y), w11, b);
+    a = __hfma2(a, two, minusOne);
+    b = __hfma2(b, two, minusOne);
+    words[0] = AsU32(QuantizeInputRef<kFp8>(a));
+    words[1] = AsU32(QuantizeInputRef<kFp8>(b));
+}
+
+// Inputs 0..15 or 16..31 of one texel (eight binary16 pairs) from the staged footprint of one grid.
+template <bool kFp8>
+__device__ __forceinline__ void GatherGridRef(const KernelParams& params, const KernelMip& mip, const RefSharedStorage& shared,
+    int grid, int lane, int tileRow, uint32_t* words)
+{
+    const int4 col = shared.tables.colTap[grid][lane];
+    const int4 row = shared.tables.rowTap[grid][tileRow];
+    const int footW = shared.tables.footWidth[grid];
+    const float dx = __int_as_float(col.y), dxn = __int_as_float(col.z);
+    const float dy = __int_as_float(row.y), dyn = __int_as_float(row.z);
+    // src/FeatureGridDevice.h:46-49
+    const float f00 = __fmul_rn(dxn, dyn), f01 = __fmul_rn(dx, dyn), f10 = __fmul_rn(dxn, dy), f11 = __fmul_rn(dx, dy);
+    const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
+    const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
+
+    const int stride = 1 << mip.strideShift;
+    const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (size_t(row.x * footW + col.x) << mip.strideShift);
+    const uint8_t* tap10 = tap00 + (size_t(footW) << mip.strideShift);
+#pragma unroll
+    for (int layer = 0; layer < 4; ++layer)
+    {
+        if (layer < params.numLayers)
+        {
+            const uint2 l00 = *reinterpret_cast<const uint2*>(tap00 + layer * 8);
+            const uint2 l01 = *reinterpret_cast<const uint2*>(tap00 + stride + layer * 8);
+            const uint2 l10 = *reinterpret_cast<const uint2*>(tap10 + layer * 8);
+            const uint2 l11 = *reinterpret_cast<const uint2*>(tap10 + stride + layer * 8);
+            BlendLayerRef<kFp8>(l00, l01, l10, l11, w00, w01, w10, w11, words + 2 * layer);
+        }
+    }
+}
+
+// One latent layer of one grid with the taps read straight from global memory.
+template <bool kFp8>
+__device__ __forceinline__ void SampleLayerRef(const uint16_t* __restrict__ plane, const GridTaps& taps,
+    const uint32_t* __restrict__ lut, uint32_t* words)
+{
+    const uint32_t p00 = __ldg(plane + taps.o00), p01 = __ldg(plane + taps.o01);
+    const uint32_t p10 = __ldg(plane + taps.o10), p11 = __ldg(plane + taps.o11);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+    {
+        const __half2 l00 = AsHalf2(lut[(p00 >> (8 * j)) & 0xFF]), l01 = AsHalf2(lut[(p01 >> (8 * j)) & 0xFF]);
+        const __half2 l10 = AsHalf2(lut[(p10 >> (8 * j)) & 0xFF]), l11 = AsHalf2(lut[(p11 >> (8 * j)) & 0xFF]);
+        __half2 d = __hmul2_rn(l01, taps.w01);
+        d = __hfma2(l00, taps.w00, d);
+        d = __hfma2(l10, taps.w10, d);
+        d = __hfma2(l11, taps.w11, d);
+        d = __hfma2(d, __float2half2_rn(2.f), __float2half2_rn(-1.f));
+        words[j] = AsU32(QuantizeInputRef<kFp8>(d));
+    }
+}
+
+// The 48 network inputs of one texel as 24 binary16 pairs -> its 96-byte row of the A operand.
+template <bool kFp8>
+__device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const KernelMip& mip, const RefSharedStorage& shared,
+    const RefTileContext& ctx, int lane, int tileRow)
+{
+    uint32_t words[24];
+    const uint32_t zeroPair = shared.tables.zeroPair;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+        words[i] = zeroPair; // unused feature slots hold quantised zeros (src/Inference.cu:49)
+
+    if (mip.staged)
+    {
+        GatherGridRef<kFp8>(params, mip, shared, 0, lane, tileRow, words);
+        GatherGridRef<kFp8>(params, mip, shared, 1, lane, tileRow, words + 8);
+    }
+    else
+    {
+        // footprint too large to stage: read the taps from global memory; threads past the right /
+        // bottom edge compute a clamped texel and store nothing
+        const int x = min(ctx.x, mip.width - 1), y = min(ctx.y, mip.rowEnd - 1);
+        const float u = __fmul_rn(__fadd_rn(float(x), 0.5f), mip.invWidth);
+        const float v = __fmul_rn(__fadd_rn(float(y), 0.5f), mip.invHeight);
+        GridTaps taps;
+        SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
+        const uint16_t* hi = params.latents + mip.hiOffset;
+#pragma unroll
+        for (int layer = 0; layer < 4; ++layer)
+            if (layer < params.numLayers)
+                SampleLayerRef<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable, words + 2 * layer);
+        SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
+        const uint16_t* lo = params.latents + mip.loOffset;
+#pragma unroll
+        for (int layer = 0; layer < 4; ++layer)
+            if (layer < params.numLayers)
+                SampleLayerRef<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable, words + 8 + 2 * layer);
+    }
+
+    // positional encoding: per wave the inputs (x phase 0, y phase 0, x phase 0.25, y phase 0.25)
+    const uint4 cx = shared.tables.colEnc[lane];
+    const uint4 ry = shared.tables.rowEnc[tileRow];
+    words[16] = __byte_perm(cx.x, ry.x, 0x5410);
+    words[17] = __byte_perm(cx.x, ry.x, 0x7632);
+    words[18] = __byte_perm(cx.y, ry.y, 0x5410);
+    words[19] = __byte_perm(cx.y, ry.y, 0x7632);
+    words[20] = __byte_perm(cx.z, ry.z, 0x5410);
+    words[21] = __byte_perm(cx.z, ry.z, 0x7632);
+    words[22] = shared.tables.lodPair;
+    words[23] = zeroPair;
+
+#pragma unroll
+    for (int chunk = 0; chunk < 6; ++chunk)
+        ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layers
+// ---------------------------------------------------------------------------------------------
+
+// First half of a layer for the CTA's current tile: barrier and MMA issue (both halves of the
+// tile).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
+template <int kLayer>
+__device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int failed)
+{
+    constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
+    constexpr int kK = kLayer == 0 ? 48 : kLayer == 1 ? 64 : kLayer == 2 ? 48 : 32;
+    constexpr int kWeightOffset =
+        kLayer == 0 ? kRefWeightOffset0 : kLayer == 1 ? kRefWeightOffset1 : kLayer == 2 ? kRefWeightOffset2 : kRefWeightOffset3;
+    constexpr int kBiasOffset =
+        kLayer == 0 ? kRefBiasOffset0 : kLayer == 1 ? kRefBiasOffset1 : kLayer == 2 ? kRefBiasOffset2 : kRefBiasOffset3;
+
+    // Makes the A operand written before this call visible to the tensor core, orders every
+    // thread's TMEM reads of the previous layer before the accumulators are overwritten, and agrees
+    // on whether any thread gave up waiting.
+    FenceProxyAsyncShared();
+    TcgenFenceBeforeSync();
+    if (__syncthreads_or(failed))
+        return 1;
+
+    if (ctx.tid == 0)
+    {
+        TcgenFenceAfterSync();
+        constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+        {
+            const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
+            // accumulators := bias (rows (1, 0, ...) times the bias column: exact)
+            UmmaF16(accumulators, MakeSmemDescriptor(ctx.biasRegion, 2048, 128),
+                MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128), instr, 0);
+#pragma unroll
+            for (int kStep = 0; kStep < kK / 16; ++kStep)
+            {
+                // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
+                const uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kRefOperandBytes + kStep * 2 * 2048, 2048, 128);
+                const uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
+                UmmaF16(accumulators, descA, descB, instr, 1);
+            }
+        }
+        UmmaCommit(ctx.barrier);
+    }
+    return 0;
+}
+
+// Second half of a layer: waits for the MMA, then applies the activation and writes the next
+// layer's A operand (layers 0-2) or stores the texel (layer 3).
+template <bool kFp8, int kLayer, bool kConvert>
+__device__ __forceinline__ void ConsumeLayerRef(const KernelParams& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+{
+    constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
+
+    if (!MbarrierWaitBounded(ctx.barrier, phase))
+    {
+        failed = 1;
+        params.status[0] = kStatusBarrierTimeout;
+        params.status[1] = uint32_t(ctx.tile);
+        params.status[2] = uint32_t(kLayer);
+    }
+    phase ^= 1;
+    TcgenFenceAfterSync();
+
+    if (kLayer < 3)
+    {
+        constexpr bool kNextFp8 = kFp8 && kLayer < 2; // layer 2 always re-quantises to the int8 grid
+        uint4* rowChunk = ctx.rowChunk;
+        // 32 accumulators (16 registers) at a time; the last part of the 48-wide layer has 16
+#pragma unroll
+        for (int part = 0; part < (kN + 31) / 32; ++part)
+        {
+            if (part * 32 + 32 <= kN)
+            {
+                uint32_t acc[16];
+                TmemLoadPacked16(ctx.tmemLane + part * 32, acc);
+                TmemLoadWait();
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    rowChunk[(part * 4 + c) * 128] =
+                        make_uint4(ActivateRef<kNextFp8>(acc[4 * c]), ActivateRef<kNextFp8>(acc[4 * c + 1]),
+                                   ActivateRef<kNextFp8>(acc[4 * c + 2]), ActivateRef<kNextFp8>(acc[4 * c + 3]));
+            }
+            else
+            {
+                uint32_t acc[8];
+                TmemLoadPacked8(ctx.tmemLane + part * 32, acc);
+                TmemLoadWait();
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                    rowChunk[(part * 4 + c) * 128] =
+                        make_uint4(ActivateRef<kNextFp8>(acc[4 * c]), ActivateRef<kNextFp8>(acc[4 * c + 1]),
+                                   ActivateRef<kNextFp8>(acc[4 * c + 2]), ActivateRef<kNextFp8>(acc[4 * c + 3]));
+            }
+        }
+    }
+    else
+    {
+        // output (src/Inference.cu:121-135): the accumulators are the channels
+        uint32_t bits[8];
+        TmemLoadPacked8(ctx.tmemLane, bits);
+        TmemLoadWait();
+        const int channelPairs = params.channels >> 1;
+        uint32_t special = 0; // bit 15 / 31 set when a value has an all-ones exponent
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < channelPairs)
+                special |= (bits[j] & 0x7C007C00u) + 0x04000400u;
+        if (special & 0x80008000u)
+        {
+            // Inf / NaN -> 0 (src/CudaUtils.h:30-35); rare, so kept off the common path
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+            {
+                if (j < channelPairs)
+                {
+                    if ((bits[j] & 0x7C00u) == 0x7C00u) bits[j] &= 0xFFFF0000u;
+                    if ((bits[j] & 0x7C000000u) == 0x7C000000u) bits[j] &= 0x0000FFFFu;
+                }
+            }
+        }
+        if constexpr (kConvert)
+        {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j >= channelPairs)
+                    bits[j] = 0;
+            if (ctx.out)
+                StoreConverted(params.conversion, params.firstChannel, params.numChannels, ctx, bits);
+        }
+        else if (ctx.out)
+        {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j < channelPairs)
+                    ctx.out[j * ctx.outStepWords] = bits[j];
+        }
+    }
+}
+
+template <bool kFp8, int kLayer, bool kConvert>
+__device__ __forceinline__ int RunLayerRef(const KernelParams& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+{
+    if (IssueLayerRef<kLayer>(ctx, failed))
+        return 1;
+    ConsumeLayerRef<kFp8, kLayer, kConvert>(params, ctx, phase, failed);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+
+template <bool kFp8, bool kConvert>
+__global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRef) DecodeKernelRef(const __grid_constant__ KernelParams params)
+{
+    extern __shared__ __align__(128) unsigned char dynamicShared[];
+    RefSharedStorage& shared = *reinterpret_cast<RefSharedStorage*>(dynamicShared);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;      // = the thread's row of the tile
+    const int half = warp >> 2;     // 0: rows 0-3 of the tile, 1: rows 4-7
+
+    // ---- one-time setup: the network image arrives by one TMA bulk copy while the threads fill
+    //      the constant tables -------------------------------------------------------------------
+    // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
+    for (int i = tid; i < 256; i += kThreadsPerCta)
+    {
+        __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
+        __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
+        shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
+    }
+    // constant A operand of the bias step: every row is (1, 0 x 15); chunk 0 of row r at r * 16
+    for (int i = tid; i < 128 * 32 / 16; i += kThreadsPerCta)
+        reinterpret_cast<uint4*>(shared.biasRegion)[i] = make_uint4(i < 128 ? 0x00003C00u : 0u, 0u, 0u, 0u);
+    const uint32_t loadBarrier = SharedAddress(&shared.loadBarrier);
+    if (tid == 0)
+    {
+        MbarrierInit(SharedAddress(&shared.barrier), 1);
+        MbarrierInit(loadBarrier, 1);
+        FenceBarrierInit();
+        MbarrierArriveExpectTx(loadBarrier, kRefNetworkBytes);
+        BulkCopyToShared(SharedAddress(shared.network), params.network, kRefNetworkBytes, loadBarrier);
+    }
+    if (warp == 0)
+        TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
+    FenceProxyAsyncShared(); // the bias region is read by the tensor core (async proxy)
+    TcgenFenceBeforeSync();
+    __syncthreads();
+    TcgenFenceAfterSync();
+    int failed = 0;   // this thread gave up on a wait
+    if (!MbarrierWaitBounded(loadBarrier, 0))
+    {
+        failed = 1;
+        params.status[0] = kStatusBarrierTimeout;
+        params.status[1] = 0xFFFFFFFFu; // no tile: the network image did not arrive
+        params.status[2] = 0xFFFFFFFFu;
+    }
+    const uint32_t tmemBase = shared.tmemBase;
+    uint32_t phase = 0;
+    int aborted = 0;  // some thread of the CTA gave up (uniform: comes out of a barrier)
+
+    RefTileContext ctx;
+    ctx.tid = tid;
+    ctx.tmemBase = tmemBase;
+    // a warp may only touch the TMEM lanes 32 * (warp % 4) .. + 31
+    ctx.tmemLane = tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
+    ctx.barrier = SharedAddress(&shared.barrier);
+    ctx.operandA = SharedAddress(shared.operandA);
+    ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kRefOperandBytes) + (tid & 127);
+    ctx.networkBase = SharedAddress(shared.network);
+    ctx.biasRegion = SharedAddress(shared.biasRegion);
+
+    struct TilePlace
+    {
+        int mipIndex, tileX0, tileY0;
+    };
+    auto locate = [&](int tile, int fromMip) {
+        TilePlace place;
+        place.mipIndex = fromMip;
+        while (place.mipIndex + 1 < params.numMips && tile >= params.mips[place.mipIndex + 1].firstTile)
+            ++place.mipIndex;
+        const KernelMip& mip = params.mips[place.mipIndex];
+        const int local = tile - mip.firstTile;
+        const int tileY = mip.tilesX == 1 ? local : int(__umulhi(uint32_t(local), mip.tilesXMagic));
+        place.tileX0 = (local - tileY * mip.tilesX) * kTileWidth;
+        place.tileY0 = mip.rowBegin + tileY * kTileHeight;
+        return place;
+    };
+
+    int tile = blockIdx.x;
+    TilePlace place{0, 0, 0};
+    if (tile < params.totalTiles)
+    {
+        place = locate(tile, 0);
+        PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        __syncthreads();
+    }
+    while (tile < params.totalTiles)
+    {
+        const KernelMip& mip = params.mips[place.mipIndex];
+        ctx.tile = tile;
+        ctx.x = place.tileX0 + lane;
+        ctx.y = place.tileY0 + warp;
+        {
+            // element index inside the mip fits 32 bits (8192^2 texels x 16 channels is 2^30)
+            const bool planar = params.outputLayout == kLayoutPlanarPairs;
+            const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
+                                          : (uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x)) * uint32_t(params.channels);
+            const bool inside = ctx.x < mip.width && ctx.y < mip.rowEnd;
+            if constexpr (kConvert)
+            {
+                // pixels of dstChannels components, rows without padding; outOffset counts components
+                const uint32_t pixelIndex = uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x);
+                const size_t component = size_t(mip.outOffset) + size_t(pixelIndex) * size_t(params.conversion.dstChannels);
+                unsigned char* bytes = reinterpret_cast<unsigned char*>(params.out) + component * BytesPerComponent(params.conversion.format);
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(bytes) : nullptr;
+                ctx.outStepWords = pixelIndex;
+            }
+            else
+            {
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
+                ctx.outStepWords = planar ? uint32_t(mip.width) : 1u;
+            }
+        }
+
+        BuildInputsRef<kFp8>(params, mip, shared, ctx, lane, warp);
+
+        // layer 0; while the tensor core works on it, prepare the NEXT tile (its tables and
+        // footprints replace this tile's, which nobody reads after the barrier inside IssueLayerRef)
+        aborted = IssueLayerRef<0>(ctx, failed);
+        if (aborted)
+            break;
+        const int nextTile = tile + int(gridDim.x);
+        if (nextTile < params.totalTiles)
+        {
+            place = locate(nextTile, place.mipIndex);
+            PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        }
+        ConsumeLayerRef<kFp8, 0, false>(params, ctx, phase, failed);
+
+        aborted = RunLayerRef<kFp8, 1, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 2, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 3, kConvert>(params, ctx, phase, failed);
+        if (aborted)
+            break;
+        tile = nextTile;
+    }
+
+    // ---- teardown -------------------------------------------------------------------------
+    TcgenFenceBeforeSync();
+    aborted = __syncthreads_or(failed);
+    if (aborted && tid == 0)
+    {
+        // one more bounded chance for work in flight (the MMA, the network image's copy) to drain
+        (void)MbarrierWaitBounded(ctx.barrier, phase ^ 1);
+        (void)MbarrierWaitBounded(loadBarrier, 0);
+    }
+    __syncthreads();
+    if (warp == 0)
+        TmemFree(tmemBase, kTmemColumns);
+}
+
+} // namespace
+
+cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
+{
+    static std::atomic<unsigned long long> done[4];
+    auto launch = [&](auto kernel, std::atomic<unsigned long long>& doneMask) -> cudaError_t {
+        int device = 0;
+        cudaError_t err = cudaGetDevice(&device);
+        if (err != cudaSuccess)
+            return err;
+        const unsigned long long bit = 1ull << (device & 63);
+        if (!(doneMask.load(std::memory_order_acquire) & bit))
+        {
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefSharedStorage)));
+            if (err != cudaSuccess)
+                return err;
+            doneMask.fetch_or(bit, std::memory_order_release);
+        }
+        kernel<<<ctas, kThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
+        return cudaGetLastError();
+    };
+    if (params.convert)
+        return fp8 ? launch(DecodeKernelRef<true, true>, done[3]) : launch(DecodeKernelRef<false, true>, done[2]);
+    return fp8 ? launch(DecodeKernelRef<true, false>, done[1]) : launch(DecodeKernelRef<false, false>, done[0]);
+}
+
+} // namespace ntcb

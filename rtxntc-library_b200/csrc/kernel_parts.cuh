@@ -1,0 +1,191 @@
+// Building blocks shared by the decode kernels (decode_kernel.cu: exact accumulation;
+// decode_kernel_ref.cu: the reference's binary16 accumulation): PTX wrappers for mbarriers, tensor
+// memory and the TMA bulk copy, the shared-memory matrix descriptor, and the bilinear tap setup.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "decode_kernel.h"
+
+namespace ntcb
+{
+namespace
+{
+
+__device__ __forceinline__ uint32_t SharedAddress(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void MbarrierInit(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void FenceBarrierInit()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Announces `bytes` of asynchronous copies that will complete on the barrier, and arrives on it.
+__device__ __forceinline__ void MbarrierArriveExpectTx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// TMA bulk copy global -> shared memory of this CTA (addresses and size multiples of 16 bytes);
+// completion is signalled on the barrier.
+__device__ __forceinline__ void BulkCopyToShared(uint32_t dstShared, const void* srcGlobal, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dstShared), "l"(srcGlobal), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Bounded wait: returns false when the barrier did not complete within the spin budget.
+__device__ __forceinline__ bool MbarrierWaitBounded(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    {
+        if (MbarrierTryWait(bar, parity))
+            return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void FenceProxyAsyncShared()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void TcgenFenceBeforeSync()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void TcgenFenceAfterSync()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void TmemAlloc(uint32_t sharedSlot, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sharedSlot), "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void TmemFree(uint32_t address, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void UmmaCommit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void TmemLoad16(uint32_t address, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address)
+        : "memory");
+}
+
+__device__ __forceinline__ void TmemLoadWait()
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8x16-byte core matrices; `leadingBytes`
+// separates core matrices along K, `strideBytes` separates 8-row groups along M/N.
+__device__ __forceinline__ uint64_t MakeSmemDescriptor(uint32_t sharedAddress, uint32_t leadingBytes, uint32_t strideBytes)
+{
+    uint64_t desc = 0;
+    desc |= uint64_t((sharedAddress & 0x3FFFF) >> 4);
+    desc |= uint64_t((leadingBytes >> 4) & 0x3FFF) << 16;
+    desc |= uint64_t((strideBytes >> 4) & 0x3FFF) << 32;
+    desc |= uint64_t(1) << 46; // descriptor version of this architecture
+    return desc;               // base offset 0, layout type 0 (no swizzle)
+}
+
+__device__ __forceinline__ uint32_t AsU32(__half2 v)
+{
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ __half2 AsHalf2(uint32_t v)
+{
+    return *reinterpret_cast<__half2*>(&v);
+}
+
+struct GridTaps
+{
+    int o00, o01, o10, o11;
+    __half2 w00, w01, w10, w11;
+};
+
+// Bilinear footprint of one texel in one latent grid (src/FeatureGridDevice.h:33-58).
+__device__ __forceinline__ void SetupTaps(float u, float v, int w, int h, GridTaps& taps)
+{
+    float px = __fmaf_rn(u, float(w), -0.5f);
+    float py = __fmaf_rn(v, float(h), -0.5f);
+    float xbf = floorf(px), ybf = floorf(py);
+    float dx = __fsub_rn(px, xbf), dy = __fsub_rn(py, ybf);
+    float dxn = __fsub_rn(1.f, dx), dyn = __fsub_rn(1.f, dy);
+    int xb = int(xbf), yb = int(ybf);
+    // wrap addressing; the sample position is < size - 0.5, so only -1 needs folding
+    int x0 = xb < 0 ? xb + w : xb;
+    int y0 = yb < 0 ? yb + h : yb;
+    int x1 = (x0 + 1 == w) ? 0 : x0 + 1;
+    int y1 = (y0 + 1 == h) ? 0 : y0 + 1;
+    taps.o00 = y0 * w + x0;
+    taps.o01 = y0 * w + x1;
+    taps.o10 = y1 * w + x0;
+    taps.o11 = y1 * w + x1;
+    taps.w00 = __half2half2(__float2half_rn(__fmul_rn(dxn, dyn)));
+    taps.w01 = __half2half2(__float2half_rn(__fmul_rn(dx, dyn)));
+    taps.w10 = __half2half2(__float2half_rn(__fmul_rn(dxn, dy)));
+    taps.w11 = __half2half2(__float2half_rn(__fmul_rn(dx, dy)));
+}
+
+__device__ __forceinline__ float Frac(float t)
+{
+    return __fsub_rn(t, floorf(t));
+}
+
+// One axis of the bilinear footprint (src/FeatureGridDevice.h:35-45): base tap index (before
+// wrapping) and the fractional offset of a texel coordinate in a latent grid of `size` pixels.
+__device__ __forceinline__ void AxisTap(int texel, float invExtent, int size, int& base, float& frac)
+{
+    const float u = __fmul_rn(__fadd_rn(float(texel), 0.5f), invExtent);
+    const float p = __fmaf_rn(u, float(size), -0.5f);
+    const float b = floorf(p);
+    base = int(b);
+    frac = __fsub_rn(p, b);
+}
+
+} // namespace
+} // namespace ntcb

@@ -9,6 +9,10 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cmath>
+
 #include "decode_kernel.h"
 #include "error.h"
 
@@ -50,6 +54,8 @@ constexpr int kLayerInputs[4] = {48, 64, 48, 32};
 constexpr int kLayerOutputs[4] = {64, 48, 32, 16};
 constexpr int kBiasSlots[4] = {16, 32, 48, 32};    // K slots that carry the bias of an int8 layer
 constexpr int kWeightOffsets[4] = {kWeightOffset0, kWeightOffset1, kWeightOffset2, kWeightOffset3};
+constexpr int kRefWeightOffsets[4] = {kRefWeightOffset0, kRefWeightOffset1, kRefWeightOffset2, kRefWeightOffset3};
+constexpr int kRefBiasOffsets[4] = {kRefBiasOffset0, kRefBiasOffset1, kRefBiasOffset2, kRefBiasOffset3};
 
 // `pairedOutput`: the launch stores fp16 channel pairs as 32-bit words, so a mip must start on one.
 bool ValidMip(const NtcbMipDesc& m, bool pairedOutput)
@@ -60,7 +66,7 @@ bool ValidMip(const NtcbMipDesc& m, bool pairedOutput)
 }
 
 // The kernel's view of one mip (everything but its place in the tile list).
-void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km)
+void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km, int footprintHiBytes = kFootprintHiBytes)
 {
     km.width = m.width;
     km.height = m.height;
@@ -82,7 +88,7 @@ void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km)
     // Largest footprint a tile can have in each grid: the tap index of the last column (row) minus
     // that of the first is at most floor(31 (7) * grid / mip) + 1, plus the second tap.
     km.strideShift = layers == 1 ? 3 : layers == 2 ? 4 : 5;
-    const long long hiCapacity = kFootprintHiBytes >> km.strideShift, loCapacity = kFootprintLoBytes >> km.strideShift;
+    const long long hiCapacity = footprintHiBytes >> km.strideShift, loCapacity = kFootprintLoBytes >> km.strideShift;
     auto footprint = [](int grid, int mip, int span) { return (long long)((long long)span * grid / mip) + 3; };
     const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, kTileHeight - 1);
     const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, kTileHeight - 1);
@@ -141,10 +147,10 @@ namespace
 {
 
 // Number of CTAs that fill the current device, cached per device.
-int ResidentCtas(bool fp8, bool converting, int* outCtas)
+int ResidentCtas(bool fp8, bool converting, int* outCtas, bool reference = false)
 {
-    static std::atomic<int> cache[64][3];
-    const int variant = converting ? 2 : fp8 ? 1 : 0;
+    static std::atomic<int> cache[64][4];
+    const int variant = reference ? 3 : converting ? 2 : fp8 ? 1 : 0;
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess)
@@ -177,7 +183,7 @@ int ResidentCtas(bool fp8, bool converting, int* outCtas)
     static_assert(kCtasPerSmInt8 * kTmemColumns <= 512 && kCtasPerSmFp8 * kTmemColumns <= 512 &&
                       kCtasPerSmConverting * kTmemColumns <= 512,
         "resident CTAs must fit into tensor memory");
-    const int perSm = converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
+    const int perSm = reference ? kCtasPerSmRef : converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
     *outCtas = sms * perSm;
     if (device >= 0 && device < 64)
         cache[device][variant].store(*outCtas, std::memory_order_relaxed);
@@ -371,6 +377,106 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
     return NTCB_OK;
 }
 
+int ntcb_stage_network_reference(const void* blob, size_t blobBytes, int weightMode, void* staged)
+{
+    if (!blob || !staged)
+    {
+        SetError("ntcb_stage_network_reference: blob and staged must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const bool fp8 = weightMode == NTCB_WEIGHTS_FP8;
+    if (weightMode != NTCB_WEIGHTS_INT8 && weightMode != NTCB_WEIGHTS_FP8)
+    {
+        SetError("ntcb_stage_network_reference: unknown weight mode %d.", weightMode);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const size_t expected = fp8 ? NTCB_FP8_BLOB_BYTES : NTCB_INT8_BLOB_BYTES;
+    if (blobBytes != expected)
+    {
+        SetError("ntcb_stage_network_reference: the %s weight blob must be %zu bytes, got %zu.",
+            fp8 ? "GenericFP8" : "GenericInt8", expected, blobBytes);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const uint8_t* src = static_cast<const uint8_t*>(blob);
+    uint8_t* dst = static_cast<uint8_t*>(staged);
+    memset(dst, 0, kRefNetworkBytes);
+
+    // where the sections of the blob start (src/WeightLayout.cpp:170-176, 228-255)
+    size_t weightStart[4], offset = 0;
+    for (int layer = 0; layer < 4; ++layer)
+    {
+        weightStart[layer] = offset;
+        offset += size_t(kLayerInputs[layer]) * kLayerOutputs[layer];
+    }
+    const uint8_t* scaleStart[4] = {};
+    const uint8_t* biasStart[4] = {};
+    if (!fp8)
+    {
+        for (int layer = 0; layer < 4; ++layer) { scaleStart[layer] = src + offset; offset += 4u * kLayerOutputs[layer]; }
+        for (int layer = 0; layer < 4; ++layer) { biasStart[layer] = src + offset; offset += 4u * kLayerOutputs[layer]; }
+    }
+    else
+    {
+        for (int layer = 0; layer < 3; ++layer) { biasStart[layer] = src + offset; offset += 2u * kLayerOutputs[layer]; }
+        scaleStart[3] = src + offset; offset += 4u * 16;
+        biasStart[3] = src + offset; offset += 4u * 16;
+    }
+    if (offset != expected)
+    {
+        SetError("ntcb_stage_network_reference: internal layout mismatch.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+
+    const float inputScale = 127.5f;             // tin::InputQuant::scale (src/tin/tin_mlp.h:42-45)
+    const float activationStep = 3.1875f / 255.f; // tin::ActHGELUClamp::step (src/tin/tin_activation.h:109-121)
+    const int activationBias = -113;             // tin::ActHGELUClamp::bias
+    auto halfBits = [](float value) { return static_cast<__half_raw>(__float2half_rn(value)).x; };
+    for (int layer = 0; layer < 4; ++layer)
+    {
+        const int nin = kLayerInputs[layer], nout = kLayerOutputs[layer];
+        uint16_t* weights = reinterpret_cast<uint16_t*>(dst + kRefWeightOffsets[layer]);
+        uint16_t* biasStep = reinterpret_cast<uint16_t*>(dst + kRefBiasOffsets[layer]);
+        const bool layerFp8 = fp8 && layer < 3;
+        for (int n = 0; n < nout; ++n)
+        {
+            uint16_t bias;
+            if (layerFp8)
+            {
+                // UnquantizeColumnFP8 (src/Quantizer.cu:384-408): e4m3 -> binary16 is exact; the bias is copied
+                for (int k = 0; k < nin; ++k)
+                {
+                    const __half_raw w = __nv_cvt_fp8_to_halfraw(src[weightStart[layer] + size_t(n) * nin + k], __NV_E4M3);
+                    weights[(k / 8) * (nout * 8) + n * 8 + (k % 8)] = w.x;
+                }
+                memcpy(&bias, biasStart[layer] + 2u * n, 2);
+            }
+            else
+            {
+                // UnquantizeColumnInt8 (src/Quantizer.cu:325-382), same fp32 operation order
+                float layerScale;
+                int32_t integerBias;
+                memcpy(&layerScale, scaleStart[layer] + 4u * n, 4);
+                memcpy(&integerBias, biasStart[layer] + 4u * n, 4);
+                float layerBias = float(integerBias) * layerScale;
+                layerScale *= (layer == 0) ? inputScale : (1.f / activationStep);
+                int integerWeightSum = 0;
+                for (int k = 0; k < nin; ++k)
+                {
+                    const int q = int8_t(src[weightStart[layer] + size_t(n) * nin + k]);
+                    weights[(k / 8) * (nout * 8) + n * 8 + (k % 8)] = halfBits(float(q) * layerScale);
+                    integerWeightSum += q;
+                }
+                if (layer != 0)
+                    layerBias = fmaf(float(integerWeightSum * activationBias) * layerScale, activationStep, layerBias);
+                bias = halfBits(layerBias);
+            }
+            biasStep[n * 8] = bias; // column 0 of the N x 16 bias-step operand
+        }
+    }
+    ClearError();
+    return NTCB_OK;
+}
+
 int ntcb_decode(const NtcbDecodeParams* p, void* stream)
 {
     if (!p || !p->latents || !p->network || !p->out || !p->status)
@@ -410,6 +516,12 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         return NTCB_ERR_INVALID_ARGUMENT;
     }
 
+    if (p->numerics != NTCB_NUMERICS_EXACT && p->numerics != NTCB_NUMERICS_REFERENCE)
+    {
+        SetError("ntcb_decode: unknown numerics %d.", p->numerics);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const bool reference = p->numerics == NTCB_NUMERICS_REFERENCE;
     KernelParams k{};
     if (p->conversion)
     {
@@ -446,7 +558,7 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         if (m.rowBegin == m.rowEnd)
             continue; // nothing of this mip belongs to this launch
         KernelMip& km = k.mips[used++];
-        FillKernelMip(m, p->numFeatures / 4, km);
+        FillKernelMip(m, p->numFeatures / 4, km, reference ? kRefFootprintHiBytes : kFootprintHiBytes);
         km.firstTile = int(tiles);
         const long long mipTiles = (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
         if (mipTiles * km.tilesX >= 0x100000000ll)
@@ -469,11 +581,11 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
 
     const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
     int resident = 0;
-    int rc = ResidentCtas(fp8, k.convert != 0, &resident);
+    int rc = ResidentCtas(fp8, k.convert != 0, &resident, reference);
     if (rc != NTCB_OK)
         return rc;
     const int ctas = k.totalTiles < resident ? k.totalTiles : resident;
-    cudaError_t err = LaunchDecode(k, fp8, ctas, static_cast<cudaStream_t>(stream));
+    cudaError_t err = reference ? LaunchDecodeRef(k, fp8, ctas, static_cast<cudaStream_t>(stream)) : LaunchDecode(k, fp8, ctas, static_cast<cudaStream_t>(stream));
     if (err != cudaSuccess)
         return CudaFailure("DecodeKernel launch", err);
     CountLaunch();

@@ -178,6 +178,8 @@ private:
     TextureSetDesc m_desc;
     LatentShape m_latentShape;
     int m_layout = NTCB_LAYOUT_INTERLEAVED;
+    int m_numerics = NTCB_NUMERICS_EXACT;
+    size_t m_networkBytes = 0; // size of one staged network image (depends on the numerics)
     bool m_hasInt8 = false, m_hasFp8 = false;
 
     // pinned host image of everything Decompress uploads: latents, then the two staged networks
@@ -332,6 +334,13 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     m_layout = features.outputLayout;
+    if (features.numerics != NTCB_NUMERICS_EXACT && features.numerics != NTCB_NUMERICS_REFERENCE)
+    {
+        SetError("Unknown numerics %d.", features.numerics);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    m_numerics = features.numerics;
+    m_networkBytes = m_numerics == NTCB_NUMERICS_REFERENCE ? size_t(kRefNetworkBytes) : size_t(kStagedNetworkBytes);
     for (int c = 0; c < kMaxChannels; ++c)
         m_channelColorSpaces[c] = loaded.channelColorSpaces[c];
     m_hasInt8 = !loaded.int8Blob.empty();
@@ -339,7 +348,7 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
 
     // upload image: latents (padded to 16 bytes), then the Int8 and the FP8 network images
     m_latentBytes = (loaded.latents.size() * 2 + 15) & ~size_t(15);
-    m_uploadBytes = m_latentBytes + 2 * size_t(kStagedNetworkBytes);
+    m_uploadBytes = m_latentBytes + 2 * m_networkBytes;
     cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&m_hostUpload), m_uploadBytes, cudaHostAllocDefault);
     if (err != cudaSuccess)
     {
@@ -350,15 +359,16 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
     memcpy(m_hostUpload, loaded.latents.data(), loaded.latents.size() * 2);
     if (m_hasInt8)
     {
-        Status status = ntcb_stage_network(loaded.int8Blob.data(), loaded.int8Blob.size(), NTCB_WEIGHTS_INT8,
-            m_hostUpload + m_latentBytes);
+        auto stage = m_numerics == NTCB_NUMERICS_REFERENCE ? ntcb_stage_network_reference : ntcb_stage_network;
+        Status status = stage(loaded.int8Blob.data(), loaded.int8Blob.size(), NTCB_WEIGHTS_INT8, m_hostUpload + m_latentBytes);
         if (status != NTCB_OK)
             return status;
     }
     if (m_hasFp8)
     {
-        Status status = ntcb_stage_network(loaded.fp8Blob.data(), loaded.fp8Blob.size(), NTCB_WEIGHTS_FP8,
-            m_hostUpload + m_latentBytes + kStagedNetworkBytes);
+        auto stage = m_numerics == NTCB_NUMERICS_REFERENCE ? ntcb_stage_network_reference : ntcb_stage_network;
+        Status status = stage(loaded.fp8Blob.data(), loaded.fp8Blob.size(), NTCB_WEIGHTS_FP8,
+            m_hostUpload + m_latentBytes + m_networkBytes);
         if (status != NTCB_OK)
             return status;
     }
@@ -544,7 +554,8 @@ Status TextureSet::DecodeInto(const int32_t* rowRanges, DecompressionStats* pOut
 
     NtcbDecodeParams params{};
     params.latents = reinterpret_cast<const uint16_t*>(m_deviceUpload);
-    params.network = m_deviceUpload + m_latentBytes + (useInt8Weights ? 0 : kStagedNetworkBytes);
+    params.network = m_deviceUpload + m_latentBytes + (useInt8Weights ? 0 : m_networkBytes);
+    params.numerics = m_numerics;
     params.out = deviceOut;
     params.conversion = conversion;
     params.status = m_status;

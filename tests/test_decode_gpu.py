@@ -1,7 +1,15 @@
-"""Parity of the sm_100a decode path, through the C ABI, against the CPU restatement and against
-outputs of the unmodified reference decoder.
+"""Parity of the sm_100a decode path, through the C ABI, against outputs of the unmodified reference
+decoder and against the CPU restatement.
 
-Bars (integer / byte work is bit-exact; floating point carries its tolerance here):
+The library decodes with one of two numerics (NtcbNumerics):
+  * REFERENCE (the default): binary16 weights, activations and accumulators, as the reference's CUDA
+    decoder.  Bar: IDENTICAL BITS to what the reference decoded - every value of every golden
+    fixture, and a live run of the reference library when oracle/_ref is present.  (The CPU
+    restatement of these numerics models the tensor core's internal rounding and agrees with the
+    reference in 99.998 % of values; against it the kernel is allowed 2 differences in 10,000.)
+  * EXACT: exact accumulation, the reference's integer-path arithmetic.
+
+Bars for EXACT (integer / byte work is bit-exact; floating point carries its tolerance here):
   * kernel vs the CPU restatement of its arithmetic contract (exact accumulation): identical bits,
     both weight modes (the FP8 layers accumulate e4m3 products in fp32 inside the tensor core; an
     occasional last-bit difference in that sum may flip one binary16 rounding, so FP8 mode allows
@@ -37,10 +45,60 @@ def _sync():
     torch.cuda.synchronize()
 
 
+EXACT, REFERENCE = binding.NUMERICS_EXACT, binding.NUMERICS_REFERENCE
+BOTH_NUMERICS = pytest.mark.parametrize("numerics", [REFERENCE, EXACT], ids=["reference", "exact"])
+
+
 def _assert_matches_contract(decoded, expected, use_int8, what):
     different = int((decoded.view(np.uint16) != expected.view(np.uint16)).sum())
     allowed = 0 if use_int8 else max(0, decoded.size // 100000)
     assert different <= allowed, "%s: %d of %d values differ from the CPU restatement" % (what, different, decoded.size)
+
+
+def _restated(oracle, checker, mip, use_int8, numerics):
+    """The CPU restatement of the kernel that implements `numerics`."""
+    if numerics == EXACT:
+        return checker.decode_mip(mip, use_int8, oracle.NUMERICS_SPEC)
+    return checker.decode_mip(mip, use_int8, oracle.NUMERICS_REF, **oracle.REF_DEFAULTS)
+
+
+class _Tally:
+    """Mismatch budget of a whole test against the CPU restatement: none for exact int8 work, one in
+    100,000 for exact FP8 work, two in 10,000 for the emulated reference numerics."""
+
+    def __init__(self, numerics):
+        self.numerics, self.values, self.different = numerics, 0, 0
+
+    def add(self, decoded, expected, use_int8, what):
+        if self.numerics == EXACT:
+            _assert_matches_contract(decoded, expected, use_int8, what)
+            return
+        assert decoded.shape == expected.shape, what
+        self.values += decoded.size
+        self.different += int((decoded.view(np.uint16) != expected.view(np.uint16)).sum())
+
+    def check(self):
+        assert self.different <= max(2, self.values * 2e-4), "%d of %d values differ" % (self.different, self.values)
+
+
+@pytest.mark.parametrize("layout", [binding.LAYOUT_INTERLEAVED, binding.LAYOUT_PLANAR_PAIRS])
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_reference_numerics_reproduce_the_reference_bit_for_bit(golden_index, name, layout):
+    """Every value the unmodified reference decoded (both weight modes, every mip) comes out of the
+    default kernel with identical bits."""
+    fixture = load_golden(name)
+    geo, latents, int8_blob, fp8_blob = container.read_container(fixture["container"].tobytes())
+    packed = np.concatenate([p.reshape(-1) for p in latents])
+    resident = binding.ResidentTextureSet(geo, packed, int8_blob, fp8_blob, layout=layout)
+    assert resident.numerics == REFERENCE
+    for mode in golden_index[name]["modes"]:
+        resident.out.fill_(float("nan"))
+        resident.decode(mode == "int8")
+        _sync()
+        resident.check_status()
+        for mip in range(geo.mips):
+            reference = fixture["%s_mip%d" % (mode, mip)]
+            assert np.array_equal(resident.mip_numpy(mip).view(np.uint16), reference), "%s %s mip %d" % (name, mode, mip)
 
 
 @pytest.mark.parametrize("layout", [binding.LAYOUT_INTERLEAVED, binding.LAYOUT_PLANAR_PAIRS])
@@ -50,7 +108,7 @@ def test_kernel_matches_contract_and_reference_on_golden_sets(oracle, golden_ind
     geo, latents, int8_blob, fp8_blob = container.read_container(fixture["container"].tobytes())
     packed = np.concatenate([p.reshape(-1) for p in latents])
     checker = oracle.OracleSet(geo, packed, int8_blob, fp8_blob)
-    resident = binding.ResidentTextureSet(geo, packed, int8_blob, fp8_blob, layout=layout)
+    resident = binding.ResidentTextureSet(geo, packed, int8_blob, fp8_blob, layout=layout, numerics=EXACT)
     for mode in golden_index[name]["modes"]:
         use_int8 = mode == "int8"
         resident.out.fill_(float("nan"))
@@ -74,28 +132,31 @@ RANDOM_SPECS = [
 ]
 
 
+@BOTH_NUMERICS
 @pytest.mark.parametrize("shape", RANDOM_SPECS)
 @pytest.mark.parametrize("network", ["unit", "benchmark"])
-def test_kernel_matches_contract_on_ragged_shapes(oracle, shape, network):
+def test_kernel_matches_contract_on_ragged_shapes(oracle, shape, network, numerics):
     """Every grid scale and feature count, odd channel counts, sizes that are not multiples of the
     32x4 tile, one-texel mips, width != height."""
     w, h, c, mips, g, f = shape
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(w, h, c, mips, g, f, seed=w * 7 + h, network=network))
     geo = data.geometry
     checker = oracle.OracleSet.from_synthetic(data)
-    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
+    tally = _Tally(numerics)
     for use_int8 in (True, False):
         resident.out.fill_(float("nan"))
         resident.decode(use_int8)
         _sync()
         resident.check_status()
         for mip in range(geo.mips):
-            _assert_matches_contract(resident.mip_numpy(mip), checker.decode_mip(mip, use_int8, oracle.NUMERICS_SPEC),
-                                     use_int8, "%s mip %d" % (shape, mip))
+            tally.add(resident.mip_numpy(mip), _restated(oracle, checker, mip, use_int8, numerics), use_int8,
+                      "%s mip %d" % (shape, mip))
+    tally.check()
 
 
 def test_biases_too_large_for_the_matrix_product_come_from_the_table(oracle):
-    """The layers of an Int8 network normally carry their bias in spare K slots of the matrix product;
+    """Exact numerics.  The layers of an Int8 network normally carry their bias in spare K slots of the matrix product;
     a bias that does not fit there switches the network to the bias table.  Both paths must give the
     contract's bits, also at the largest bias that still fits and at negative extremes (the FP8
     network, decoded alongside, always takes its int8 output layer's bias from the table)."""
@@ -113,10 +174,10 @@ def test_biases_too_large_for_the_matrix_product_come_from_the_table(oracle):
         last = np.frombuffer(bytes(fp8_blob[8544:8608]), dtype=np.int32).copy()
         last[3] = delta
         fp8_blob[8544:8608] = last.tobytes()
-        staged = binding.stage_network(bytes(int8_blob), binding.WEIGHTS_INT8)
+        staged = binding.stage_network(bytes(int8_blob), binding.WEIGHTS_INT8, EXACT)
         assert staged[14848:14852].view(np.uint32)[0] == (1 if abs(delta) > limit else 0)
         checker = oracle.OracleSet(geo, packed, bytes(int8_blob), bytes(fp8_blob))
-        resident = binding.ResidentTextureSet(geo, packed, bytes(int8_blob), bytes(fp8_blob))
+        resident = binding.ResidentTextureSet(geo, packed, bytes(int8_blob), bytes(fp8_blob), numerics=EXACT)
         for use_int8 in (True, False):
             resident.out.fill_(float("nan"))
             resident.decode(use_int8)
@@ -127,14 +188,15 @@ def test_biases_too_large_for_the_matrix_product_come_from_the_table(oracle):
                                          use_int8, "bias %d mip %d" % (delta, mip))
 
 
-def test_row_ranges_tile_rows_and_guard_bands(oracle):
+@BOTH_NUMERICS
+def test_row_ranges_tile_rows_and_guard_bands(oracle, numerics):
     """Decoding a mip in row bands (the unit of tile-row sharding) gives the same bits as one
     whole decode, writes nothing outside its band, and leaves canaries around the buffer intact."""
     import torch
 
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(160, 90, 6, 0, 2, 8, seed=21, network="unit"))
     geo = data.geometry
-    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
     resident.decode(True)
     _sync()
     whole = resident.out.clone()
@@ -176,7 +238,17 @@ def test_texture_set_api_decompress_and_read_channels(oracle):
     context = binding.Context(0)
     try:
         for layout in (binding.LAYOUT_INTERLEAVED, binding.LAYOUT_PLANAR_PAIRS):
-            texture_set = context.create_texture_set(data.container, layout)
+            # the default numerics are the reference's: same bits as the kernel-level decode
+            default_set = context.create_texture_set(data.container, layout)
+            resident = binding.ResidentTextureSet.from_synthetic(data)
+            for use_int8 in (True, False):
+                default_set.decompress(use_int8)
+                resident.decode(use_int8)
+                _sync()
+                for mip in range(geo.mips):
+                    assert np.array_equal(default_set.read_mip(mip).view(np.uint16), resident.mip_numpy(mip).view(np.uint16))
+            default_set.close()
+            texture_set = context.create_texture_set(data.container, layout, EXACT)
             assert (texture_set.desc.width, texture_set.desc.channels, texture_set.desc.mips) == (96, 6, geo.mips)
             with pytest.raises(binding.NtcbError) as error:
                 texture_set.read_mip(0)
@@ -225,13 +297,20 @@ def test_live_reference_comparison(oracle):
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(256, 192, 8, 0, 4, 8, seed=77, network="unit"))
     geo = data.geometry
     reference = oracle.ReferenceDecoder(data.container, geo.channels)
-    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=EXACT)
+    identical = binding.ResidentTextureSet.from_synthetic(data, numerics=REFERENCE)
     checker = oracle.OracleSet.from_synthetic(data)
     try:
         for use_int8 in (True, False):
             reference.decompress(use_int8)
             resident.decode(use_int8)
+            identical.decode(use_int8)
             _sync()
+            for mip in range(geo.mips):
+                cm = geo.color_mips[mip]
+                theirs = reference.read_mip(mip, cm.width, cm.height)
+                # the reference's numerics: identical bits
+                assert np.array_equal(identical.mip_numpy(mip).view(np.uint16), theirs.view(np.uint16))
             for mip in (0, 1, 2):
                 cm = geo.color_mips[mip]
                 theirs = reference.read_mip(mip, cm.width, cm.height)
@@ -245,7 +324,8 @@ def test_live_reference_comparison(oracle):
         reference.close()
 
 
-def test_full_size_properties_of_the_pbr_configuration(oracle):
+@BOTH_NUMERICS
+def test_full_size_properties_of_the_pbr_configuration(oracle, numerics):
     """4096x4096, 12 channels, 13 mips, FP8: the CPU restatement cannot decode 22 M texels in
     seconds, so the full-size check uses properties: a second decode reproduces the first bit for
     bit, a row-banded decode reproduces the whole decode, and 20,000 randomly chosen texels over all
@@ -254,7 +334,7 @@ def test_full_size_properties_of_the_pbr_configuration(oracle):
 
     data = synthetic.make_texture_set(synthetic.config_spec(1))
     geo = data.geometry
-    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
     resident.decode(False)
     _sync()
     resident.check_status()
@@ -274,7 +354,8 @@ def test_full_size_properties_of_the_pbr_configuration(oracle):
 
     checker = oracle.OracleSet.from_synthetic(data)
     queries = synthetic.make_queries(20000, max_lod=geo.mips - 0.001, seed=9)
-    expected = checker.sample(queries, False, oracle.NUMERICS_SPEC)
+    expected = (checker.sample(queries, False, oracle.NUMERICS_SPEC) if numerics == EXACT
+                else checker.sample(queries, False, oracle.NUMERICS_REF))
     c = geo.channels
     flat = first.cpu().numpy()
     mismatched = 0
@@ -285,7 +366,7 @@ def test_full_size_properties_of_the_pbr_configuration(oracle):
         y = min(cm.height - 1, int(np.floor(np.float32(q[1]) * np.float32(cm.height))))
         start = (cm.texel_offset + y * cm.width + x) * c
         mismatched += int(not np.array_equal(flat[start:start + c].view(np.uint16), want.view(np.uint16)))
-    assert mismatched == 0
+    assert mismatched <= (0 if numerics == EXACT else 8)  # the CPU model of the reference's rounding is 99.998 % exact
 
 
 @pytest.mark.parametrize("shape", [(96, 40, 6, 0, 3, 12), (256, 256, 12, 0, 4, 12), (33, 17, 2, 0, 1, 4)])
@@ -298,7 +379,7 @@ def test_inference_on_sample_matches_contract(oracle, shape):
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(w, h, c, mips, g, f, seed=3, network="unit"))
     geo = data.geometry
     checker = oracle.OracleSet.from_synthetic(data)
-    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=EXACT)
     queries = synthetic.make_queries(5000, max_lod=geo.mips + 0.5, seed=9)
     queries[:8] = [[0, 0, 0], [0.999999, 0.999999, 0], [0.5, 0.5, -1.0], [0.25, 0.75, 99.0], [1.0, 1.0, 1.0],
                    [0.0, 1.0, geo.mips - 1], [0.3, 0.6, 1.999], [0.7, 0.1, 2.0]]

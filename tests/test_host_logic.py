@@ -179,7 +179,7 @@ def test_weight_staging_layout():
     inputs 127 (1 in the last slot of each 32-slot K step)."""
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=3))
     for blob, mode in ((data.int8_blob, binding.WEIGHTS_INT8), (data.fp8_blob, binding.WEIGHTS_FP8)):
-        staged = binding.stage_network(blob, mode)
+        staged = binding.stage_network(blob, mode, binding.NUMERICS_EXACT)
         assert staged.size == binding.STAGED_NETWORK_BYTES
         source = np.frombuffer(blob, dtype=np.uint8)
         # Int8 networks carry their biases in the matrix product (every bias of this set fits its slots);
@@ -215,7 +215,7 @@ def test_weight_staging_falls_back_to_the_bias_table():
     table = np.frombuffer(bytes(blob[8192 + 640:8192 + 1280]), dtype=np.int32).copy()
     table[64 + 5] = 127 * 127 * 31 + 64  # one more than layer 1's 32 slots can carry
     blob[8192 + 640:8192 + 1280] = table.tobytes()
-    staged = binding.stage_network(bytes(blob), binding.WEIGHTS_INT8)
+    staged = binding.stage_network(bytes(blob), binding.WEIGHTS_INT8, binding.NUMERICS_EXACT)
     assert staged[STAGED_FLAGS:STAGED_FLAGS + 4].view(np.uint32)[0] == 1
     stored = staged[STAGED_BIASES:STAGED_BIASES + 1024].view(np.int32).reshape(4, 64)
     assert np.array_equal(stored[1, :48], table[64:112]) and np.array_equal(stored[3, :16], table[144:160])
@@ -223,16 +223,65 @@ def test_weight_staging_falls_back_to_the_bias_table():
         assert not _staged_matrix(staged, layer, nout)[:, nin:].any()
     table[64 + 5] -= 1  # the largest value that still fits
     blob[8192 + 640:8192 + 1280] = table.tobytes()
-    staged = binding.stage_network(bytes(blob), binding.WEIGHTS_INT8)
+    staged = binding.stage_network(bytes(blob), binding.WEIGHTS_INT8, binding.NUMERICS_EXACT)
     assert staged[STAGED_FLAGS:STAGED_FLAGS + 4].view(np.uint32)[0] == 0
     constants = np.where(np.arange(96) % 32 == 31, 1, 127)[64:]
     assert (_staged_matrix(staged, 1, 48)[5, 64:] @ constants) == table[64 + 5]
 
 
+def test_reference_network_staging():
+    """The binary16 image of the reference-numerics kernel: weights rebuilt as the reference's
+    ConvertNetworkFromQuantizedToFp16 does, in K-major core matrices of 8 halves (element (n, k) of
+    layer l at byte (k / 8) * (N * 16) + n * 16 + (k % 8) * 2), and per layer an N x 16 bias-step operand
+    with the binary16 bias in column 0."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=3))
+    weight_offsets, bias_offsets = [0, 6144, 12288, 15360], [16384, 18432, 19968, 20992]
+    for blob, mode in ((data.int8_blob, binding.WEIGHTS_INT8), (data.fp8_blob, binding.WEIGHTS_FP8)):
+        staged = binding.stage_network(blob, mode)  # the default numerics are the reference's
+        assert staged.size == binding.STAGED_REFERENCE_NETWORK_BYTES == 21504
+        halves = staged.view(np.float16)
+        source = np.frombuffer(blob, dtype=np.uint8)
+        position = 0
+        for layer, (nin, nout) in enumerate(zip(geometry.MLP_LAYER_INPUTS, geometry.MLP_LAYER_OUTPUTS)):
+            raw = source[position:position + nin * nout].reshape(nout, nin)
+            position += nin * nout
+            k = np.arange(nin)
+            n = np.arange(nout)[:, None]
+            matrix = halves[(weight_offsets[layer] + (k // 8) * nout * 16 + n * 16 + (k % 8) * 2) // 2].astype(np.float32)
+            layer_is_fp8 = mode == binding.WEIGHTS_FP8 and layer < 3
+            if layer_is_fp8:
+                expected = np.array([[synthetic.e4m3_to_float(int(v)) for v in row] for row in raw], dtype=np.float32)
+                bias = source[8192 + 2 * sum(geometry.MLP_LAYER_OUTPUTS[:layer]):][:2 * nout].view(np.float16)
+            else:
+                if mode == binding.WEIGHTS_INT8:
+                    first = sum(geometry.MLP_LAYER_OUTPUTS[:layer])
+                    scale = source[8192 + 4 * first:][:4 * nout].view(np.float32)
+                    integer_bias = source[8192 + 640 + 4 * first:][:4 * nout].view(np.int32)
+                else:
+                    scale = source[8480:8544].view(np.float32)
+                    integer_bias = source[8544:8608].view(np.int32)
+                # src/Quantizer.cu:325-382, the same fp32 operation order
+                layer_bias = integer_bias.astype(np.float32) * scale
+                step = np.float32(3.1875) / np.float32(255)
+                layer_scale = scale * (np.float32(127.5) if layer == 0 else np.float32(1) / step)
+                weights = raw.view(np.int8).astype(np.float32)
+                expected = (weights * layer_scale[:, None]).astype(np.float16).astype(np.float32)
+                if layer != 0:
+                    sums = raw.view(np.int8).astype(np.int64).sum(axis=1)
+                    product = (sums * -113).astype(np.float32) * layer_scale
+                    layer_bias = (product.astype(np.float64) * np.float64(step) + layer_bias.astype(np.float64)).astype(np.float32)  # one rounding: fma
+                bias = layer_bias.astype(np.float16)
+            assert np.array_equal(matrix, expected), (mode, layer)
+            step_operand = halves[bias_offsets[layer] // 2:bias_offsets[layer] // 2 + nout * 16].reshape(2, nout, 8)
+            assert np.array_equal(step_operand[0, :, 0].view(np.uint16), bias.view(np.uint16)), (mode, layer)
+            assert not step_operand[0, :, 1:].any() and not step_operand[1].any()
+
+
 def test_stage_network_rejects_wrong_sizes():
-    with pytest.raises(binding.NtcbError) as error:
-        binding.stage_network(bytes(100), binding.WEIGHTS_INT8)
-    assert error.value.code == -1
+    for numerics in (binding.NUMERICS_REFERENCE, binding.NUMERICS_EXACT):
+        with pytest.raises(binding.NtcbError) as error:
+            binding.stage_network(bytes(100), binding.WEIGHTS_INT8, numerics)
+        assert error.value.code == -1
 
 
 def test_decode_validates_arguments_before_touching_the_gpu():

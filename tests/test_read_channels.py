@@ -195,7 +195,8 @@ def test_read_channels_and_fused_epilogue_agree_with_the_restatement(oracle, cas
 
 
 @pytest.mark.gpu
-def test_fused_epilogue_on_ragged_shapes_row_ranges_and_fp8(oracle):
+@pytest.mark.parametrize("numerics", [binding.NUMERICS_REFERENCE, binding.NUMERICS_EXACT], ids=["reference", "exact"])
+def test_fused_epilogue_on_ragged_shapes_row_ranges_and_fp8(oracle, numerics):
     """Kernel level: the converting epilogue through ntcb_decode on sizes that are no multiple of
     the tile, in FP8 mode, in two row bands; against the conversion kernel run on the fp16 decode."""
     import torch
@@ -203,7 +204,7 @@ def test_fused_epilogue_on_ragged_shapes_row_ranges_and_fp8(oracle):
     spec = synthetic.TextureSetSpec(203, 77, 10, 0, 3, 12, seed=31, network="unit")
     data = synthetic.make_texture_set(spec)
     geo = data.geometry
-    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
     for use_int8 in (False, True):
         resident.decode(use_int8)
         torch.cuda.synchronize()
