@@ -57,7 +57,7 @@ WORKLOAD = ("PBR texture set 4096x4096, 12 channels, 13 mips, latent shape {grid
 
 # DRAM bytes per launch of the decode kernel on this workload (dram__bytes_read.sum +
 # dram__bytes_write.sum from the ncu capture summarised in profiles/).
-MEASURED_TRAFFIC_BYTES = 491.3e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
+MEASURED_TRAFFIC_BYTES = 492.3e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
 
 
 def measured_peak_gbs():
@@ -188,7 +188,7 @@ WORKLOADS = {
 }
 
 
-def build_launches(config: int, rank: int, world: int, device, binding, synthetic, sharding):
+def build_launches(config: int, rank: int, world: int, device, binding, synthetic, sharding, numerics: int):
     """The decode launches one rank issues per step: [(resident set, params)], the texels they
     produce on this rank, the texels of the whole job, algorithmic bytes of this rank's step and
     the synthetic set used for the CPU baseline."""
@@ -197,7 +197,7 @@ def build_launches(config: int, rank: int, world: int, device, binding, syntheti
         spec = synthetic.config_spec(config)
         spec.seed += 1000 * rank  # every rank decodes its own texture set (weak scaling)
         data = synthetic.make_texture_set(spec)
-        resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device))
+        resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device), numerics=numerics)
         launches.append((resident, resident.params(data.use_int8)))
         texels = data.geometry.total_texels
         alg_bytes = texels * data.geometry.channels * 2 + data.geometry.encoded_latent_bytes + binding.STAGED_NETWORK_BYTES
@@ -213,7 +213,7 @@ def build_launches(config: int, rank: int, world: int, device, binding, syntheti
         for index, mips in sorted(by_set.items()):
             data = synthetic.make_texture_set(specs[index])
             first = first or data
-            resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device))
+            resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device), numerics=numerics)
             launches.append((resident, resident.params(True, mips=sorted(mips))))
             done = sum(data.geometry.color_mips[m].width * data.geometry.color_mips[m].height for m in mips)
             texels += done
@@ -223,7 +223,7 @@ def build_launches(config: int, rank: int, world: int, device, binding, syntheti
         data = synthetic.make_texture_set(synthetic.config_spec(3))
         geo = data.geometry
         ranges = sharding.plan_rows(geo, world)[rank]
-        resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device))
+        resident = binding.ResidentTextureSet.from_synthetic(data, device=str(device), numerics=numerics)
         mips = [m for m, (b, e) in enumerate(ranges) if e > b]
         launches.append((resident, resident.params(True, mips=mips, row_ranges={m: ranges[m] for m in mips})))
         texels = sharding.texels_of_rows(geo, ranges)
@@ -242,8 +242,9 @@ def run_ours(args) -> dict:
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
 
+    numerics = binding.NUMERICS_EXACT if args.numerics == "exact" else binding.NUMERICS_REFERENCE
     launches, texels, job_texels, algorithmic_bytes, data, scaling = build_launches(
-        args.config, rank, world, device, binding, synthetic, sharding)
+        args.config, rank, world, device, binding, synthetic, sharding, numerics)
     geo = data.geometry
     use_int8 = data.use_int8
 
@@ -295,7 +296,7 @@ def run_ours(args) -> dict:
         del flush
         torch.cuda.empty_cache()
         context = binding.Context(local_rank)
-        texture_set = context.create_texture_set(data.container)
+        texture_set = context.create_texture_set(data.container, numerics=numerics)
         host_out = torch.empty(texels * geo.channels, dtype=torch.float16).pin_memory()
         base = host_out.data_ptr()
 
@@ -349,14 +350,19 @@ def run_ours(args) -> dict:
                 "traffic": MEASURED_TRAFFIC_BYTES if args.config == 1 else None,
                 "peak_source": "%s copy bandwidth" % peak_kind, "algorithmic_bytes_per_step": algorithmic_bytes,
                 "launches_per_step": len(step_ms) and launch_count // max(1, args.steps)}
-    dtype = ("fp8_e4m3 x fp8_e4m3 -> f32 (layers 0-2), s8 x s8 -> s32 (layer 3), f16 activations" if not use_int8
-             else "s8 x s8 -> s32 (all layers), f16 activations")
+    if numerics == binding.NUMERICS_REFERENCE:
+        dtype = ("f16 x f16 -> f16 (tcgen05 kind::f16, binary16 accumulators rounded per 16 products: the reference's own "
+                 "arithmetic on %s weights, reproduced bit for bit)" % ("int8" if use_int8 else "e4m3 / int8"))
+    else:
+        dtype = ("fp8_e4m3 x fp8_e4m3 -> f32 (layers 0-2), s8 x s8 -> s32 (layer 3), f16 activations" if not use_int8
+                 else "s8 x s8 -> s32 (all layers), f16 activations")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": device_seconds * 1e3 / args.steps, "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": dtype,
         "data": "synthetic (seeded latents and weights of the configuration's shape)",
-        "config": {"workload": WORKLOADS[args.config], "texels_per_step": job_texels, "texels_per_step_this_rank": texels,
+        "config": {"workload": WORKLOADS[args.config], "numerics": "reference" if numerics == binding.NUMERICS_REFERENCE else "exact",
+                   "texels_per_step": job_texels, "texels_per_step_this_rank": texels,
                    "parallelism": "sharded by texture set / tile rows, no collective",
                    "l2": "256 MiB written between steps, outside the per-step events; each step's output also exceeds L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": total_launches, "roofline": roofline,
@@ -495,7 +501,9 @@ def main() -> int:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3],
                         help="benchmark configuration; 1 (the default) is the one the metric is quoted on")
-    parser.add_argument("--profile-case", metavar="SIZE:MODE:LAUNCHES",
+    parser.add_argument("--numerics", default="reference", choices=["reference", "exact"],
+                        help="reference (default): binary16 accumulation, the reference decoder's bits; exact: exact accumulation")
+    parser.add_argument("--profile-case", metavar="SIZE:MODE:LAUNCHES[:NUMERICS]",
                         help="only launch the decode kernel LAUNCHES times on a small SIZE^2 set (fp8 or int8) and exit")
     args = parser.parse_args()
     if args.profile_case:

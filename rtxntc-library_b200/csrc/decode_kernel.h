@@ -65,8 +65,16 @@ constexpr int kRefBiasOffset1 = 18432;     // 48 x 16
 constexpr int kRefBiasOffset2 = 19968;     // 32 x 16
 constexpr int kRefBiasOffset3 = 20992;     // 16 x 16
 constexpr int kRefNetworkBytes = 21504;
-constexpr int kRefOperandBytes = 128 * 128; // A operand of one half: 128 rows x 64 halves
+constexpr int kRefOperandBytes = 128 * 128; // A operand of one 128-row GEMM chain: 128 rows x 64 halves
+// Tile of the reference-numerics kernel: kRefChains 128-row chains (32 x 4 texels each) per CTA.
+// Two chains (32x8 texels, 256 threads) at three CTAs per SM measured faster than four chains
+// (32x16, 512 threads) at two.
+constexpr int kRefChains = 2;
+constexpr int kRefTileHeight = 4 * kRefChains;
+constexpr int kRefThreadsPerCta = 128 * kRefChains;
+constexpr int kRefTmemColumns = kRefChains * kTmemColumnsPerHalf;
 constexpr int kRefFootprintHiBytes = 8192;  // the binary16 operands leave less room for the high-res footprint
+constexpr int kRefFootprintLoBytes = 4096;
 constexpr int kCtasPerSmRef = 3;
 
 constexpr uint32_t kStatusBarrierTimeout = 1;

@@ -134,10 +134,10 @@ __device__ __forceinline__ uint32_t ActivateRef(uint32_t bits)
 struct __align__(16) RefTileTables
 {
     int4 colTap[2][kTileWidth];   // per grid and column: footprint x index, dx, 1 - dx
-    int4 rowTap[2][kTileHeight];  // per grid and row: footprint y index, dy, 1 - dy
+    int4 rowTap[2][kRefTileHeight];  // per grid and row: footprint y index, dy, 1 - dy
     // positional encoding as quantised binary16 pairs: word w = (wave w phase 0, wave w phase 0.25)
     uint4 colEnc[kTileWidth];
-    uint4 rowEnc[kTileHeight];
+    uint4 rowEnc[kRefTileHeight];
     int footWidth[2];
     uint32_t lodPair;   // (lod, lod)
     uint32_t zeroPair;  // (quantised 0, quantised 0)
@@ -146,13 +146,13 @@ struct __align__(16) RefTileTables
 struct __align__(128) RefSharedStorage
 {
     uint8_t network[kRefNetworkBytes];                     // binary16 weights and bias-step operands
-    alignas(128) uint8_t operandA[2 * kRefOperandBytes];   // A operands of the current layer (top half, bottom half)
+    alignas(128) uint8_t operandA[kRefChains * kRefOperandBytes]; // A operands of the current layer, one per chain
     alignas(128) uint8_t biasRegion[128 * 32];             // constant A operand of the bias step: rows (1, 0 x 15)
     uint8_t footprintHi[kRefFootprintHiBytes];
-    uint8_t footprintLo[kFootprintLoBytes];
+    uint8_t footprintLo[kRefFootprintLoBytes];
     uint32_t latentTable[256];
     RefTileTables tables;
-    uint64_t barrier;      // MMA completion
+    uint64_t barrier[kRefChains]; // MMA completion, per chain: a chain's threads go on as soon as their accumulators are ready
     uint64_t loadBarrier;  // arrival of the network image
     uint32_t tmemBase;
 };
@@ -160,7 +160,9 @@ struct __align__(128) RefSharedStorage
 struct RefTileContext
 {
     int tid;
-    uint32_t tmemBase, tmemLane, barrier, operandA, networkBase, biasRegion;
+    uint32_t tmemBase, tmemLane, operandA, networkBase, biasRegion;
+    uint32_t barrierBase; // shared address of the chains' MMA-completion mbarriers
+    uint32_t barrier;     // ... of this thread's chain
     uint4* rowChunk; // this thread's 16-byte slot in chunk 0 of its half's A operand
     int tile, x, y;
     uint32_t* out;
@@ -184,16 +186,16 @@ __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const
     int xb, yb;
     float dx, dy;
     AxisTap(min(tileX0 + lane, mip.width - 1), mip.invWidth, gw, xb, dx);
-    AxisTap(min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
+    AxisTap(min(tileY0 + (lane & (kRefTileHeight - 1)), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
     const int fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
     const int fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
     const int footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
-    const int footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
+    const int footH = __shfl_sync(0xFFFFFFFFu, yb, kRefTileHeight - 1) - fy0 + 2;
 
     if (warp < 2)
     {
         shared.tables.colTap[grid][lane] = make_int4(xb - fx0, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
-        if (lane < kTileHeight)
+        if (lane < kRefTileHeight)
             shared.tables.rowTap[grid][lane] = make_int4(yb - fy0, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
         if (lane == 0)
             shared.tables.footWidth[grid] = footW;
@@ -203,7 +205,7 @@ __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const
         // positional encoding (src/RegressionKernels.h:59-85): warp 2 the x part per column, warp 3
         // the y part per row, quantised exactly as the per-texel inputs would be
         const bool rows = warp == 3;
-        const int coordinate = rows ? min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1) : min(tileX0 + lane, mip.width - 1);
+        const int coordinate = rows ? min(tileY0 + (lane & (kRefTileHeight - 1)), mip.rowEnd - 1) : min(tileX0 + lane, mip.width - 1);
         float f = __fmul_rn(float(coordinate), mip.positionScale);
         uint32_t q[3];
 #pragma unroll
@@ -216,9 +218,9 @@ __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const
         }
         if (!rows)
             shared.tables.colEnc[lane] = make_uint4(q[0], q[1], q[2], 0);
-        else if (lane < kTileHeight)
+        else if (lane < kRefTileHeight)
             shared.tables.rowEnc[lane] = make_uint4(q[0], q[1], q[2], 0);
-        if (rows && lane == kTileHeight)
+        if (rows && lane == kRefTileHeight)
         {
             shared.tables.lodPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(mip.positionLod)));
             shared.tables.zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
@@ -234,7 +236,7 @@ __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
         uint8_t* foot = grid ? shared.footprintLo : shared.footprintHi;
-        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
+        for (int p = lane + 32 * (warp >> 1); p < count; p += kRefThreadsPerCta / 2)
         {
             const int fy = int((uint32_t(p) * magic) >> 20);
             const int fx = p - fy * footW;
@@ -392,7 +394,7 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
 // Layers
 // ---------------------------------------------------------------------------------------------
 
-// First half of a layer for the CTA's current tile: barrier and MMA issue (both halves of the
+// First half of a layer for the CTA's current tile: barrier and MMA issue (all chains of the
 // tile).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
 template <int kLayer>
 __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int failed)
@@ -417,7 +419,7 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
         TcgenFenceAfterSync();
         constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
 #pragma unroll
-        for (int half = 0; half < 2; ++half)
+        for (int half = 0; half < kRefChains; ++half)
         {
             const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
             // accumulators := bias (rows (1, 0, ...) times the bias column: exact)
@@ -431,8 +433,9 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
                 const uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
                 UmmaF16(accumulators, descA, descB, instr, 1);
             }
+            // arrives once everything issued so far has completed: this chain's accumulators are ready
+            UmmaCommit(ctx.barrierBase + half * 8);
         }
-        UmmaCommit(ctx.barrier);
     }
     return 0;
 }
@@ -544,7 +547,7 @@ __device__ __forceinline__ int RunLayerRef(const KernelParams& params, const Ref
 // ---------------------------------------------------------------------------------------------
 
 template <bool kFp8, bool kConvert>
-__global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRef) DecodeKernelRef(const __grid_constant__ KernelParams params)
+__global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernelRef(const __grid_constant__ KernelParams params)
 {
     extern __shared__ __align__(128) unsigned char dynamicShared[];
     RefSharedStorage& shared = *reinterpret_cast<RefSharedStorage*>(dynamicShared);
@@ -552,31 +555,32 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRef) DecodeKernelRef
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;      // = the thread's row of the tile
-    const int half = warp >> 2;     // 0: rows 0-3 of the tile, 1: rows 4-7
+    const int half = warp >> 2;     // the 128-row chain of this thread: rows 4 * half .. + 3 of the tile
 
     // ---- one-time setup: the network image arrives by one TMA bulk copy while the threads fill
     //      the constant tables -------------------------------------------------------------------
     // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
-    for (int i = tid; i < 256; i += kThreadsPerCta)
+    for (int i = tid; i < 256; i += kRefThreadsPerCta)
     {
         __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
         __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
         shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
     }
     // constant A operand of the bias step: every row is (1, 0 x 15); chunk 0 of row r at r * 16
-    for (int i = tid; i < 128 * 32 / 16; i += kThreadsPerCta)
+    for (int i = tid; i < 128 * 32 / 16; i += kRefThreadsPerCta)
         reinterpret_cast<uint4*>(shared.biasRegion)[i] = make_uint4(i < 128 ? 0x00003C00u : 0u, 0u, 0u, 0u);
     const uint32_t loadBarrier = SharedAddress(&shared.loadBarrier);
     if (tid == 0)
     {
-        MbarrierInit(SharedAddress(&shared.barrier), 1);
+        for (int chain = 0; chain < kRefChains; ++chain)
+            MbarrierInit(SharedAddress(&shared.barrier[chain]), 1);
         MbarrierInit(loadBarrier, 1);
         FenceBarrierInit();
         MbarrierArriveExpectTx(loadBarrier, kRefNetworkBytes);
         BulkCopyToShared(SharedAddress(shared.network), params.network, kRefNetworkBytes, loadBarrier);
     }
     if (warp == 0)
-        TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
+        TmemAlloc(SharedAddress(&shared.tmemBase), kRefTmemColumns);
     FenceProxyAsyncShared(); // the bias region is read by the tensor core (async proxy)
     TcgenFenceBeforeSync();
     __syncthreads();
@@ -598,7 +602,8 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRef) DecodeKernelRef
     ctx.tmemBase = tmemBase;
     // a warp may only touch the TMEM lanes 32 * (warp % 4) .. + 31
     ctx.tmemLane = tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
-    ctx.barrier = SharedAddress(&shared.barrier);
+    ctx.barrierBase = SharedAddress(&shared.barrier[0]);
+    ctx.barrier = ctx.barrierBase + half * 8;
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kRefOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
@@ -617,7 +622,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRef) DecodeKernelRef
         const int local = tile - mip.firstTile;
         const int tileY = mip.tilesX == 1 ? local : int(__umulhi(uint32_t(local), mip.tilesXMagic));
         place.tileX0 = (local - tileY * mip.tilesX) * kTileWidth;
-        place.tileY0 = mip.rowBegin + tileY * kTileHeight;
+        place.tileY0 = mip.rowBegin + tileY * kRefTileHeight;
         return place;
     };
 
@@ -686,12 +691,13 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRef) DecodeKernelRef
     if (aborted && tid == 0)
     {
         // one more bounded chance for work in flight (the MMA, the network image's copy) to drain
-        (void)MbarrierWaitBounded(ctx.barrier, phase ^ 1);
+        for (int chain = 0; chain < kRefChains; ++chain)
+            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phase ^ 1);
         (void)MbarrierWaitBounded(loadBarrier, 0);
     }
     __syncthreads();
     if (warp == 0)
-        TmemFree(tmemBase, kTmemColumns);
+        TmemFree(tmemBase, kRefTmemColumns);
 }
 
 } // namespace
@@ -712,7 +718,7 @@ cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cuda
                 return err;
             doneMask.fetch_or(bit, std::memory_order_release);
         }
-        kernel<<<ctas, kThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
+        kernel<<<ctas, kRefThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
         return cudaGetLastError();
     };
     if (params.convert)

@@ -66,7 +66,8 @@ bool ValidMip(const NtcbMipDesc& m, bool pairedOutput)
 }
 
 // The kernel's view of one mip (everything but its place in the tile list).
-void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km, int footprintHiBytes = kFootprintHiBytes)
+void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km, int footprintHiBytes = kFootprintHiBytes,
+    int footprintLoBytes = kFootprintLoBytes, int tileHeight = kTileHeight)
 {
     km.width = m.width;
     km.height = m.height;
@@ -88,10 +89,10 @@ void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km, int footprin
     // Largest footprint a tile can have in each grid: the tap index of the last column (row) minus
     // that of the first is at most floor(31 (7) * grid / mip) + 1, plus the second tap.
     km.strideShift = layers == 1 ? 3 : layers == 2 ? 4 : 5;
-    const long long hiCapacity = footprintHiBytes >> km.strideShift, loCapacity = kFootprintLoBytes >> km.strideShift;
+    const long long hiCapacity = footprintHiBytes >> km.strideShift, loCapacity = footprintLoBytes >> km.strideShift;
     auto footprint = [](int grid, int mip, int span) { return (long long)((long long)span * grid / mip) + 3; };
-    const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, kTileHeight - 1);
-    const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, kTileHeight - 1);
+    const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, tileHeight - 1);
+    const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, tileHeight - 1);
     km.staged = (hiPixels <= hiCapacity && loPixels <= loCapacity) ? 1 : 0;
     km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
     km.tilesXMagic = km.tilesX == 1 ? 0u : unsigned((0x100000000ull + km.tilesX - 1) / km.tilesX);
@@ -181,7 +182,7 @@ int ResidentCtas(bool fp8, bool converting, int* outCtas, bool reference = false
     // occupancy query reports one CTA per SM for kernels that allocate tensor memory, so it is not
     // used here.)
     static_assert(kCtasPerSmInt8 * kTmemColumns <= 512 && kCtasPerSmFp8 * kTmemColumns <= 512 &&
-                      kCtasPerSmConverting * kTmemColumns <= 512,
+                      kCtasPerSmConverting * kTmemColumns <= 512 && kCtasPerSmRef * kRefTmemColumns <= 512,
         "resident CTAs must fit into tensor memory");
     const int perSm = reference ? kCtasPerSmRef : converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
     *outCtas = sms * perSm;
@@ -558,9 +559,13 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         if (m.rowBegin == m.rowEnd)
             continue; // nothing of this mip belongs to this launch
         KernelMip& km = k.mips[used++];
-        FillKernelMip(m, p->numFeatures / 4, km, reference ? kRefFootprintHiBytes : kFootprintHiBytes);
+        const int tileHeight = reference ? kRefTileHeight : kTileHeight;
+        if (reference)
+            FillKernelMip(m, p->numFeatures / 4, km, kRefFootprintHiBytes, kRefFootprintLoBytes, kRefTileHeight);
+        else
+            FillKernelMip(m, p->numFeatures / 4, km);
         km.firstTile = int(tiles);
-        const long long mipTiles = (long long)km.tilesX * ((m.rowEnd - m.rowBegin + kTileHeight - 1) / kTileHeight);
+        const long long mipTiles = (long long)km.tilesX * ((m.rowEnd - m.rowBegin + tileHeight - 1) / tileHeight);
         if (mipTiles * km.tilesX >= 0x100000000ll)
         {
             SetError("ntcb_decode: mip %d is too large for one launch.", i);
