@@ -192,6 +192,8 @@ typedef struct NtcbSampleParams
     int32_t numFeatures;
     int32_t channels;
     int32_t weightMode;
+    int32_t numerics;        /* NtcbNumerics; selects the network image as in NtcbDecodeParams */
+    int32_t reserved;
     NtcbMipDesc mips[NTCB_MAX_MIPS]; /* outOffset, rowBegin and rowEnd are ignored */
 } NtcbSampleParams;
 

@@ -80,7 +80,8 @@ class SampleParams(ctypes.Structure):
     _fields_ = [("latents", ctypes.c_void_p), ("network", ctypes.c_void_p), ("queries", ctypes.c_void_p),
                 ("out", ctypes.c_void_p), ("status", ctypes.c_void_p), ("numQueries", ctypes.c_uint64),
                 ("numMips", ctypes.c_int32), ("numFeatures", ctypes.c_int32), ("channels", ctypes.c_int32),
-                ("weightMode", ctypes.c_int32), ("mips", MipDesc * MAX_MIPS)]
+                ("weightMode", ctypes.c_int32), ("numerics", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("mips", MipDesc * MAX_MIPS)]
 
 
 class TextureSetDesc(ctypes.Structure):
@@ -279,8 +280,6 @@ class ResidentTextureSet:
         lib()
         self.latents = torch.from_numpy(np.ascontiguousarray(packed_latents).view(np.int16)).to(self.device)
         self.numerics = numerics
-        self._blobs = {WEIGHTS_INT8: int8_blob, WEIGHTS_FP8: fp8_blob}
-        self._exact_networks = {}
         self.networks = {
             WEIGHTS_INT8: torch.from_numpy(stage_network(int8_blob, WEIGHTS_INT8, numerics)).to(self.device),
             WEIGHTS_FP8: torch.from_numpy(stage_network(fp8_blob, WEIGHTS_FP8, numerics)).to(self.device),
@@ -324,18 +323,12 @@ class ResidentTextureSet:
 
     def sample(self, queries, use_int8: bool):
         """Inference on sample: `queries` is a float32 CUDA tensor [n][3] of (u, v, lod); returns a
-        float16 CUDA tensor [n][channels].  Queued on torch's current stream.  The sample kernel
-        computes with exact accumulation whatever the numerics of this object."""
+        float16 CUDA tensor [n][channels].  Queued on torch's current stream."""
         torch = self.torch
         mode = WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8
         queries = queries.contiguous()
         out = torch.empty((queries.shape[0], self.geometry.channels), dtype=torch.float16, device=self.device)
-        if self.numerics == NUMERICS_EXACT:
-            network = self.networks[mode]
-        else:
-            if mode not in self._exact_networks:
-                self._exact_networks[mode] = torch.from_numpy(stage_network(self._blobs[mode], mode, NUMERICS_EXACT)).to(self.device)
-            network = self._exact_networks[mode]
+        network = self.networks[mode]
         decode = fill_params(self.geometry, self.latents.data_ptr(), network.data_ptr(), out.data_ptr(),
                              self.status.data_ptr(), mode)
         params = SampleParams()
@@ -343,6 +336,7 @@ class ResidentTextureSet:
         params.out, params.status, params.numQueries = out.data_ptr(), decode.status, queries.shape[0]
         params.numMips, params.numFeatures, params.channels = decode.numMips, decode.numFeatures, decode.channels
         params.weightMode = mode
+        params.numerics = self.numerics
         for i in range(decode.numMips):
             params.mips[i] = decode.mips[i]
         with torch.cuda.device(self.device):

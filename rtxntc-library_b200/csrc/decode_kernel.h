@@ -136,6 +136,7 @@ int MakeOutputConversion(const ::NtcbOutputConversion& request, int channels, Ou
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
 // The reference-numerics kernel (decode_kernel_ref.cu): params.network is a kRefNetworkBytes image.
 cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream);
+cudaError_t LaunchSampleRef(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream);
 cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream);
 
 } // namespace ntcb

@@ -442,8 +442,8 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
 
 // Second half of a layer: waits for the MMA, then applies the activation and writes the next
 // layer's A operand (layers 0-2) or stores the texel (layer 3).
-template <bool kFp8, int kLayer, bool kConvert>
-__device__ __forceinline__ void ConsumeLayerRef(const KernelParams& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+template <bool kFp8, int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
@@ -533,8 +533,8 @@ __device__ __forceinline__ void ConsumeLayerRef(const KernelParams& params, cons
     }
 }
 
-template <bool kFp8, int kLayer, bool kConvert>
-__device__ __forceinline__ int RunLayerRef(const KernelParams& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+template <bool kFp8, int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ int RunLayerRef(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
 {
     if (IssueLayerRef<kLayer>(ctx, failed))
         return 1;
@@ -542,23 +542,11 @@ __device__ __forceinline__ int RunLayerRef(const KernelParams& params, const Ref
     return 0;
 }
 
-// ---------------------------------------------------------------------------------------------
-// The kernel
-// ---------------------------------------------------------------------------------------------
-
-template <bool kFp8, bool kConvert>
-__global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernelRef(const __grid_constant__ KernelParams params)
+// One-time setup of a CTA: the network image arrives by one TMA bulk copy while the threads fill
+// the constant tables, set up the barriers and allocate tensor memory.  Returns nonzero in every
+// thread that gave up waiting for the image (status words written).
+__device__ __forceinline__ int SetupCtaRef(RefSharedStorage& shared, const uint8_t* network, uint32_t* status, int tid, int warp)
 {
-    extern __shared__ __align__(128) unsigned char dynamicShared[];
-    RefSharedStorage& shared = *reinterpret_cast<RefSharedStorage*>(dynamicShared);
-
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;      // = the thread's row of the tile
-    const int half = warp >> 2;     // the 128-row chain of this thread: rows 4 * half .. + 3 of the tile
-
-    // ---- one-time setup: the network image arrives by one TMA bulk copy while the threads fill
-    //      the constant tables -------------------------------------------------------------------
     // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
     for (int i = tid; i < 256; i += kRefThreadsPerCta)
     {
@@ -577,7 +565,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
         MbarrierInit(loadBarrier, 1);
         FenceBarrierInit();
         MbarrierArriveExpectTx(loadBarrier, kRefNetworkBytes);
-        BulkCopyToShared(SharedAddress(shared.network), params.network, kRefNetworkBytes, loadBarrier);
+        BulkCopyToShared(SharedAddress(shared.network), network, kRefNetworkBytes, loadBarrier);
     }
     if (warp == 0)
         TmemAlloc(SharedAddress(&shared.tmemBase), kRefTmemColumns);
@@ -585,14 +573,51 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
     TcgenFenceBeforeSync();
     __syncthreads();
     TcgenFenceAfterSync();
-    int failed = 0;   // this thread gave up on a wait
+    int failed = 0;
     if (!MbarrierWaitBounded(loadBarrier, 0))
     {
         failed = 1;
-        params.status[0] = kStatusBarrierTimeout;
-        params.status[1] = 0xFFFFFFFFu; // no tile: the network image did not arrive
-        params.status[2] = 0xFFFFFFFFu;
+        status[0] = kStatusBarrierTimeout;
+        status[1] = 0xFFFFFFFFu; // no tile: the network image did not arrive
+        status[2] = 0xFFFFFFFFu;
     }
+    return failed;
+}
+
+// End of a CTA: agrees on whether anything went wrong, gives work in flight one more bounded chance
+// to drain, and releases the tensor memory.
+__device__ __forceinline__ void TeardownCtaRef(RefSharedStorage& shared, const RefTileContext& ctx, uint32_t phase, int failed,
+    int tid, int warp)
+{
+    TcgenFenceBeforeSync();
+    const int aborted = __syncthreads_or(failed);
+    if (aborted && tid == 0)
+    {
+        for (int chain = 0; chain < kRefChains; ++chain)
+            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phase ^ 1);
+        (void)MbarrierWaitBounded(SharedAddress(&shared.loadBarrier), 0);
+    }
+    __syncthreads();
+    if (warp == 0)
+        TmemFree(ctx.tmemBase, kRefTmemColumns);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernels
+// ---------------------------------------------------------------------------------------------
+
+template <bool kFp8, bool kConvert>
+__global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernelRef(const __grid_constant__ KernelParams params)
+{
+    extern __shared__ __align__(128) unsigned char dynamicShared[];
+    RefSharedStorage& shared = *reinterpret_cast<RefSharedStorage*>(dynamicShared);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;      // = the thread's row of the tile
+    const int half = warp >> 2;     // the 128-row chain of this thread: rows 4 * half .. + 3 of the tile
+
+    int failed = SetupCtaRef(shared, params.network, params.status, tid, warp); // this thread gave up on a wait
     const uint32_t tmemBase = shared.tmemBase;
     uint32_t phase = 0;
     int aborted = 0;  // some thread of the CTA gave up (uniform: comes out of a barrier)
@@ -685,19 +710,109 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
         tile = nextTile;
     }
 
-    // ---- teardown -------------------------------------------------------------------------
-    TcgenFenceBeforeSync();
-    aborted = __syncthreads_or(failed);
-    if (aborted && tid == 0)
+    TeardownCtaRef(shared, ctx, phase, failed, tid, warp);
+}
+
+// Inference on sample with the reference's numerics: one thread per query (u, v, lod) -> the texel
+// (mip = clamp(floor(lod)), x = min(floor(u * W), W - 1), y likewise) is evaluated exactly as the
+// decode kernel evaluates it; the taps are read straight from global memory.
+template <bool kFp8>
+__global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernelRef(const __grid_constant__ SampleParams params)
+{
+    extern __shared__ __align__(128) unsigned char dynamicShared[];
+    RefSharedStorage& shared = *reinterpret_cast<RefSharedStorage*>(dynamicShared);
+    __shared__ KernelMip mipTable[16];
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int half = warp >> 2;
+
+    // the mip descriptions are indexed per thread: a copy in shared memory (visible after the barrier inside SetupCtaRef)
+    if (tid < params.numMips)
+        mipTable[tid] = params.mips[tid];
+    int failed = SetupCtaRef(shared, params.network, params.status, tid, warp);
+    int aborted = 0;
+    uint32_t phase = 0;
+
+    RefTileContext ctx;
+    ctx.tid = tid;
+    ctx.tmemBase = shared.tmemBase;
+    ctx.tmemLane = ctx.tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
+    ctx.barrierBase = SharedAddress(&shared.barrier[0]);
+    ctx.barrier = ctx.barrierBase + half * 8;
+    ctx.operandA = SharedAddress(shared.operandA);
+    ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kRefOperandBytes) + (tid & 127);
+    ctx.networkBase = SharedAddress(shared.network);
+    ctx.biasRegion = SharedAddress(shared.biasRegion);
+    ctx.outStepWords = 1;
+
+    const uint32_t zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
+    const unsigned long long tiles = (params.numQueries + kRefThreadsPerCta - 1) / kRefThreadsPerCta;
+    for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x)
     {
-        // one more bounded chance for work in flight (the MMA, the network image's copy) to drain
-        for (int chain = 0; chain < kRefChains; ++chain)
-            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phase ^ 1);
-        (void)MbarrierWaitBounded(loadBarrier, 0);
+        const unsigned long long query = tile * kRefThreadsPerCta + tid;
+        const bool valid = query < params.numQueries;
+        const unsigned long long q = valid ? query : params.numQueries - 1;
+        const float u = __ldg(params.queries + 3 * q), v = __ldg(params.queries + 3 * q + 1), lod = __ldg(params.queries + 3 * q + 2);
+        const int mipIndex = max(0, min(params.numMips - 1, int(floorf(lod))));
+        const KernelMip& mip = mipTable[mipIndex];
+        const int x = max(0, min(mip.width - 1, int(floorf(__fmul_rn(u, float(mip.width))))));
+        const int y = max(0, min(mip.height - 1, int(floorf(__fmul_rn(v, float(mip.height))))));
+        ctx.tile = int(tile);
+        ctx.x = x;
+        ctx.y = y;
+        ctx.out = valid ? reinterpret_cast<uint32_t*>(params.out + query * params.channels) : nullptr;
+
+        {
+            uint32_t words[24];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                words[i] = zeroPair; // unused feature slots hold quantised zeros (src/Inference.cu:49)
+            // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
+            const float su = __fmul_rn(__fadd_rn(float(x), 0.5f), mip.invWidth);
+            const float sv = __fmul_rn(__fadd_rn(float(y), 0.5f), mip.invHeight);
+            GridTaps taps;
+            SetupTaps(su, sv, mip.hiWidth, mip.hiHeight, taps);
+            const uint16_t* hi = params.latents + mip.hiOffset;
+#pragma unroll
+            for (int layer = 0; layer < 4; ++layer)
+                if (layer < params.numLayers)
+                    SampleLayerRef<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable, words + 2 * layer);
+            SetupTaps(su, sv, mip.loWidth, mip.loHeight, taps);
+            const uint16_t* lo = params.latents + mip.loOffset;
+#pragma unroll
+            for (int layer = 0; layer < 4; ++layer)
+                if (layer < params.numLayers)
+                    SampleLayerRef<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable, words + 8 + 2 * layer);
+            // src/RegressionKernels.h:59-85: per wave the inputs (x phase 0, y phase 0, x phase 0.25, y phase 0.25)
+            float xf = __fmul_rn(float(x), mip.positionScale);
+            float yf = __fmul_rn(float(y), mip.positionScale);
+#pragma unroll
+            for (int wave = 0; wave < 3; ++wave)
+            {
+                const float ex = __fmaf_rn(Frac(xf), 2.f, -1.f), ey = __fmaf_rn(Frac(yf), 2.f, -1.f);
+                const float ez = __fmaf_rn(Frac(__fadd_rn(xf, 0.25f)), 2.f, -1.f);
+                const float ew = __fmaf_rn(Frac(__fadd_rn(yf, 0.25f)), 2.f, -1.f);
+                words[16 + 2 * wave] = AsU32(QuantizeInputRef<kFp8>(__floats2half2_rn(ex, ey)));
+                words[17 + 2 * wave] = AsU32(QuantizeInputRef<kFp8>(__floats2half2_rn(ez, ew)));
+                xf = __fmul_rn(xf, 2.f);
+                yf = __fmul_rn(yf, 2.f);
+            }
+            words[22] = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(mip.positionLod)));
+            words[23] = zeroPair;
+#pragma unroll
+            for (int chunk = 0; chunk < 6; ++chunk)
+                ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
+        }
+
+        aborted = RunLayerRef<kFp8, 0, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 1, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 2, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 3, false>(params, ctx, phase, failed);
+        if (aborted)
+            break;
     }
-    __syncthreads();
-    if (warp == 0)
-        TmemFree(tmemBase, kRefTmemColumns);
+    TeardownCtaRef(shared, ctx, phase, failed, tid, warp);
 }
 
 } // namespace
@@ -724,6 +839,28 @@ cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cuda
     if (params.convert)
         return fp8 ? launch(DecodeKernelRef<true, true>, done[3]) : launch(DecodeKernelRef<false, true>, done[2]);
     return fp8 ? launch(DecodeKernelRef<true, false>, done[1]) : launch(DecodeKernelRef<false, false>, done[0]);
+}
+
+cudaError_t LaunchSampleRef(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream)
+{
+    static std::atomic<unsigned long long> done[2];
+    auto launch = [&](auto kernel, std::atomic<unsigned long long>& doneMask) -> cudaError_t {
+        int device = 0;
+        cudaError_t err = cudaGetDevice(&device);
+        if (err != cudaSuccess)
+            return err;
+        const unsigned long long bit = 1ull << (device & 63);
+        if (!(doneMask.load(std::memory_order_acquire) & bit))
+        {
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefSharedStorage)));
+            if (err != cudaSuccess)
+                return err;
+            doneMask.fetch_or(bit, std::memory_order_release);
+        }
+        kernel<<<ctas, kRefThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
+        return cudaGetLastError();
+    };
+    return fp8 ? launch(SampleKernelRef<true>, done[1]) : launch(SampleKernelRef<false>, done[0]);
 }
 
 } // namespace ntcb

@@ -611,6 +611,12 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
         SetError("ntcb_sample: invalid mip count, feature count, channel count or weight mode.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
+    if (p->numerics != NTCB_NUMERICS_EXACT && p->numerics != NTCB_NUMERICS_REFERENCE)
+    {
+        SetError("ntcb_sample: unknown numerics %d.", p->numerics);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const bool reference = p->numerics == NTCB_NUMERICS_REFERENCE;
     if ((reinterpret_cast<uintptr_t>(p->network) & 15) || (reinterpret_cast<uintptr_t>(p->out) & 3) ||
         (reinterpret_cast<uintptr_t>(p->queries) & 3))
     {
@@ -645,12 +651,14 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
         return NTCB_OK;
     const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
     int resident = 0;
-    int rc = ResidentCtas(fp8, false, &resident);
+    int rc = ResidentCtas(fp8, false, &resident, reference);
     if (rc != NTCB_OK)
         return rc;
-    const unsigned long long tiles = (p->numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
+    const unsigned long long perCta = reference ? kRefThreadsPerCta : kThreadsPerCta;
+    const unsigned long long tiles = (p->numQueries + perCta - 1) / perCta;
     const int ctas = tiles < (unsigned long long)resident ? int(tiles) : resident;
-    cudaError_t err = LaunchSample(k, fp8, ctas, static_cast<cudaStream_t>(stream));
+    cudaError_t err = reference ? LaunchSampleRef(k, fp8, ctas, static_cast<cudaStream_t>(stream))
+                                : LaunchSample(k, fp8, ctas, static_cast<cudaStream_t>(stream));
     if (err != cudaSuccess)
         return CudaFailure("SampleKernel launch", err);
     CountLaunch();

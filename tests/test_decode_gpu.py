@@ -369,17 +369,19 @@ def test_full_size_properties_of_the_pbr_configuration(oracle, numerics):
     assert mismatched <= (0 if numerics == EXACT else 8)  # the CPU model of the reference's rounding is 99.998 % exact
 
 
+@BOTH_NUMERICS
 @pytest.mark.parametrize("shape", [(96, 40, 6, 0, 3, 12), (256, 256, 12, 0, 4, 12), (33, 17, 2, 0, 1, 4)])
-def test_inference_on_sample_matches_contract(oracle, shape):
-    """Random (u, v, lod) queries: every answer equals the CPU restatement of the selected texel
-    (bit-exact, as for whole-mip decode) and equals the entry of the fully decoded mip chain."""
+def test_inference_on_sample_matches_contract(oracle, shape, numerics):
+    """Random (u, v, lod) queries: every answer equals the entry of the fully decoded mip chain (so,
+    with the default numerics, the reference's bits) and the CPU restatement of the selected texel
+    (bit-exact for exact accumulation, within the CPU model's accuracy for the reference numerics)."""
     import torch
 
     w, h, c, mips, g, f = shape
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(w, h, c, mips, g, f, seed=3, network="unit"))
     geo = data.geometry
     checker = oracle.OracleSet.from_synthetic(data)
-    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=EXACT)
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
     queries = synthetic.make_queries(5000, max_lod=geo.mips + 0.5, seed=9)
     queries[:8] = [[0, 0, 0], [0.999999, 0.999999, 0], [0.5, 0.5, -1.0], [0.25, 0.75, 99.0], [1.0, 1.0, 1.0],
                    [0.0, 1.0, geo.mips - 1], [0.3, 0.6, 1.999], [0.7, 0.1, 2.0]]
@@ -388,11 +390,16 @@ def test_inference_on_sample_matches_contract(oracle, shape):
         got = resident.sample(device_queries, use_int8).cpu().numpy()
         _sync()
         resident.check_status()
-        expected = checker.sample(queries, use_int8, oracle.NUMERICS_SPEC)
-        assert np.array_equal(got.view(np.uint16), expected.view(np.uint16))
+        if numerics == EXACT:
+            expected = checker.sample(queries, use_int8, oracle.NUMERICS_SPEC)
+            assert np.array_equal(got.view(np.uint16), expected.view(np.uint16))
+        else:
+            expected = checker.sample(queries, use_int8, oracle.NUMERICS_REF)
+            different = int((got.view(np.uint16) != expected.view(np.uint16)).sum())
+            assert different <= max(2, got.size * 2e-4)
         resident.decode(use_int8)
         _sync()
-        for q in (0, 1, 2, 3, 100, 4999):
+        for q in range(0, 5000, 7):
             mip = int(max(0, min(geo.mips - 1, np.floor(queries[q, 2]))))
             cm = geo.color_mips[mip]
             x = int(max(0, min(cm.width - 1, np.floor(np.float32(queries[q, 0]) * np.float32(cm.width)))))
