@@ -434,6 +434,7 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
                 UmmaF16(accumulators, descA, descB, instr, 1);
             }
             // arrives once everything issued so far has completed: this chain's accumulators are ready
+            // (one issuing thread for both chains measured faster than one per chain)
             UmmaCommit(ctx.barrierBase + half * 8);
         }
     }
@@ -461,33 +462,26 @@ __device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefT
     {
         constexpr bool kNextFp8 = kFp8 && kLayer < 2; // layer 2 always re-quantises to the int8 grid
         uint4* rowChunk = ctx.rowChunk;
-        // 32 accumulators (16 registers) at a time; the last part of the 48-wide layer has 16
-#pragma unroll
-        for (int part = 0; part < (kN + 31) / 32; ++part)
+        // all accumulators of the row are requested before the first wait, so that the round trips to
+        // tensor memory overlap: 64 -> two loads of 32, 48 -> 32 + 16, 32 -> one load
+        uint32_t low[16], high[16];
+        TmemLoadPacked16(ctx.tmemLane, low);
+        if (kN == 64)
+            TmemLoadPacked16(ctx.tmemLane + 32, high);
+        else if (kN == 48)
         {
-            if (part * 32 + 32 <= kN)
-            {
-                uint32_t acc[16];
-                TmemLoadPacked16(ctx.tmemLane + part * 32, acc);
-                TmemLoadWait();
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    rowChunk[(part * 4 + c) * 128] =
-                        make_uint4(ActivateRef<kNextFp8>(acc[4 * c]), ActivateRef<kNextFp8>(acc[4 * c + 1]),
-                                   ActivateRef<kNextFp8>(acc[4 * c + 2]), ActivateRef<kNextFp8>(acc[4 * c + 3]));
-            }
-            else
-            {
-                uint32_t acc[8];
-                TmemLoadPacked8(ctx.tmemLane + part * 32, acc);
-                TmemLoadWait();
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                    rowChunk[(part * 4 + c) * 128] =
-                        make_uint4(ActivateRef<kNextFp8>(acc[4 * c]), ActivateRef<kNextFp8>(acc[4 * c + 1]),
-                                   ActivateRef<kNextFp8>(acc[4 * c + 2]), ActivateRef<kNextFp8>(acc[4 * c + 3]));
-            }
+            uint32_t (&tail)[8] = reinterpret_cast<uint32_t (&)[8]>(high);
+            TmemLoadPacked8(ctx.tmemLane + 32, tail);
         }
+        TmemLoadWait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            rowChunk[c * 128] = make_uint4(ActivateRef<kNextFp8>(low[4 * c]), ActivateRef<kNextFp8>(low[4 * c + 1]),
+                                           ActivateRef<kNextFp8>(low[4 * c + 2]), ActivateRef<kNextFp8>(low[4 * c + 3]));
+#pragma unroll
+        for (int c = 0; c < (kN - 32) / 8; ++c)
+            rowChunk[(4 + c) * 128] = make_uint4(ActivateRef<kNextFp8>(high[4 * c]), ActivateRef<kNextFp8>(high[4 * c + 1]),
+                                                 ActivateRef<kNextFp8>(high[4 * c + 2]), ActivateRef<kNextFp8>(high[4 * c + 3]));
     }
     else
     {
