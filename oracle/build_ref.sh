@@ -14,7 +14,7 @@
 #   * src/GDeflate.cpp is replaced by oracle/gdeflate_stub.cpp (libdeflate sources are absent);
 #   * src/Shaders.cpp is left out, exactly as the stock build does without prebuilt shaders.
 #
-# Usage: oracle/build_ref.sh [reference-source-dir]   (default: $NTC_REFERENCE_DIR or /root/reference)
+# Usage: oracle/build_ref.sh [reference-source-dir]   (default: $NTC_REFERENCE_DIR, else the REF default below)
 set -euo pipefail
 
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"

@@ -36,6 +36,7 @@
 
 #include "decode_kernel.h"
 #include "kernel_parts.cuh"
+#include "input_stage.cuh"
 #include "output_convert.cuh"
 #include "epilogue_convert.cuh"
 
@@ -89,41 +90,6 @@ __host__ __device__ constexpr uint32_t MakeInstrDescriptor(bool fp8, int n)
 // Small arithmetic helpers
 // ---------------------------------------------------------------------------------------------
 
-// Quantises a pair of network inputs.  Int8: floor(x * 127.5 - 0.5) clamped to +-127
-// (src/tin/tin_mlp.h:25-31), returned as the low bytes of the two 16-bit lanes.  FP8: round to
-// nearest even e4m3, saturating (src/tin/tin_activation.h:44-48), returned as two packed bytes.
-template <bool kFp8>
-__device__ __forceinline__ uint32_t QuantizeInputPair(__half2 x)
-{
-    if (kFp8)
-    {
-        return uint32_t(__nv_cvt_halfraw2_to_fp8x2(static_cast<__half2_raw>(x), __NV_SATFINITE, __NV_E4M3));
-    }
-    else
-    {
-        __half2 y = __hfma2(x, __float2half2_rn(127.5f), __float2half2_rn(-0.5f));
-        y = h2floor(y);
-        y = __hmax2(__hmin2(y, __float2half2_rn(127.f)), __float2half2_rn(-127.f));
-        // integer-valued: adding 1536 puts the two's-complement code in the low byte of each lane
-        return AsU32(__hadd2_rn(y, __float2half2_rn(1536.f)));
-    }
-}
-
-// Two quantised pairs -> four operand bytes.
-template <bool kFp8>
-__device__ __forceinline__ uint32_t PackCodes(uint32_t pair0, uint32_t pair1)
-{
-    if (kFp8)
-    {
-        // pair0 | pair1 << 16 (both are 16-bit values) as an integer multiply-add: it runs on the FMA
-        // pipe, leaving the busier ALU pipe to the conversions and min/max
-        uint32_t packed;
-        asm("mad.lo.u32 %0, %1, 65536, %2;" : "=r"(packed) : "r"(pair1), "r"(pair0));
-        return packed;
-    }
-    return __byte_perm(pair0, pair1, 0x6420);
-}
-
 // Clamped HGELU in binary16 (src/tin/tin_activation.h:88-92) followed by re-quantisation:
 // e4m3 when `toFp8`, otherwise the int8 code rint(y * 80) - 113 (src/tin/tin_activation.h:94-99,
 // the -113 offset is folded into the next layer's stored bias, src/Quantizer.cu:176-181).
@@ -149,50 +115,9 @@ __device__ __forceinline__ uint32_t ActivatePair(__half2 x)
     }
 }
 
-// One latent pixel layer (four 4-bit features) of one grid -> four quantised inputs.
-// Blend order as the reference build evaluates it: fma(l11,w3, fma(l10,w2, fma(l00,w0, l01*w1))).
-template <bool kFp8>
-__device__ __forceinline__ uint32_t SampleLayer(const uint16_t* __restrict__ plane, const GridTaps& taps,
-    const uint32_t* __restrict__ lut)
-{
-    uint32_t p00 = __ldg(plane + taps.o00), p01 = __ldg(plane + taps.o01);
-    uint32_t p10 = __ldg(plane + taps.o10), p11 = __ldg(plane + taps.o11);
-    uint32_t pairs[2];
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-    {
-        __half2 l00 = AsHalf2(lut[(p00 >> (8 * j)) & 0xFF]), l01 = AsHalf2(lut[(p01 >> (8 * j)) & 0xFF]);
-        __half2 l10 = AsHalf2(lut[(p10 >> (8 * j)) & 0xFF]), l11 = AsHalf2(lut[(p11 >> (8 * j)) & 0xFF]);
-        __half2 d = __hmul2_rn(l01, taps.w01);
-        d = __hfma2(l00, taps.w00, d);
-        d = __hfma2(l10, taps.w10, d);
-        d = __hfma2(l11, taps.w11, d);
-        d = __hfma2(d, __float2half2_rn(2.f), __float2half2_rn(-1.f));
-        pairs[j] = QuantizeInputPair<kFp8>(d);
-    }
-    return PackCodes<kFp8>(pairs[0], pairs[1]);
-}
-
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-
-// Per-tile lookup tables: the bilinear tap position and weights are separable in x and y, and so
-// is the positional encoding, so they are computed once per tile column / row instead of once per
-// texel.
-struct __align__(16) TileTables
-{
-    // per grid (0 = high-res, 1 = low-res) and tile column: footprint x index, dx, 1 - dx
-    int4 colTap[2][kTileWidth];
-    // per grid and tile row: footprint y index, dy, 1 - dy
-    int4 rowTap[2][kTileHeight];
-    // positional-encoding operand bytes: x = {X0 w0, X1 w0, X0 w1, X1 w1}, y = {X0 w2, X1 w2, 0, 0}
-    uint2 colEnc[kTileWidth];
-    uint2 rowEnc[kTileHeight];
-    int footWidth[2];  // footprint width in latent pixels, per grid
-    uint32_t lodWord;  // operand bytes of inputs 44..47: lod, lod, 0, 0
-    uint32_t pad;
-};
 
 struct __align__(128) SharedStorage
 {
@@ -209,146 +134,6 @@ struct __align__(128) SharedStorage
     uint32_t tmemBase;
 };
 
-
-// Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory
-// (nibbles unpacked to binary16 once per latent pixel instead of once per texel and tap).
-// Even warps work on the high-res grid, odd warps on the low-res grid.
-template <bool kFp8>
-__device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, SharedStorage& shared,
-    int tileX0, int tileY0, int lane, int warp)
-{
-    const int grid = warp & 1;
-    const int gw = grid ? mip.loWidth : mip.hiWidth;
-    const int gh = grid ? mip.loHeight : mip.hiHeight;
-
-    int xb, yb;
-    float dx, dy;
-    AxisTap(min(tileX0 + lane, mip.width - 1), mip.invWidth, gw, xb, dx);
-    AxisTap(min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
-    const int fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
-    const int fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
-    const int footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
-    const int footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
-
-    if (warp < 2)
-    {
-        shared.tables.colTap[grid][lane] = make_int4(xb - fx0, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
-        if (lane < kTileHeight)
-            shared.tables.rowTap[grid][lane] = make_int4(yb - fy0, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
-        if (lane == 0)
-            shared.tables.footWidth[grid] = footW;
-    }
-    else if (warp < 4)
-    {
-        // positional encoding (src/RegressionKernels.h:59-85): warp 2 the x part per column, warp 3
-        // the y part per row, quantised exactly as the per-texel inputs would be
-        const bool rows = warp == 3;
-        const int coordinate = rows ? min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1) : min(tileX0 + lane, mip.width - 1);
-        float f = __fmul_rn(float(coordinate), mip.positionScale);
-        uint32_t q[3];
-#pragma unroll
-        for (int wave = 0; wave < 3; ++wave)
-        {
-            const float e0 = __fmaf_rn(Frac(f), 2.f, -1.f);
-            const float e1 = __fmaf_rn(Frac(__fadd_rn(f, 0.25f)), 2.f, -1.f);
-            q[wave] = QuantizeInputPair<kFp8>(__floats2half2_rn(e0, e1));
-            f = __fmul_rn(f, 2.f);
-        }
-        const uint2 enc = make_uint2(PackCodes<kFp8>(q[0], q[1]), PackCodes<kFp8>(q[2], 0));
-        if (!rows)
-            shared.tables.colEnc[lane] = enc;
-        else if (lane < kTileHeight)
-            shared.tables.rowEnc[lane] = enc;
-        if (rows && lane == kTileHeight)
-            shared.tables.lodWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(mip.positionLod)),
-                                                   QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
-    }
-
-    if (mip.staged)
-    {
-        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
-        const int count = footW * footH;
-        // p / footW == (p * magic) >> 20 for p < 2048; the IEEE quotient of 2^20 / footW floors exactly
-        const uint32_t magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
-        const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
-        const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
-        uint8_t* foot = grid ? shared.footprintLo : shared.footprintHi;
-        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
-        {
-            const int fy = int((uint32_t(p) * magic) >> 20);
-            const int fx = p - fy * footW;
-            // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
-            int gx = fx0 + fx, gy = fy0 + fy;
-            gx += gx < 0 ? gw : 0;
-            gx -= gx >= gw ? gw : 0;
-            gy += gy < 0 ? gh : 0;
-            gy -= gy >= gh ? gh : 0;
-            const uint16_t* src = plane0 + size_t(gy) * gw + gx;
-            uint2* dst = reinterpret_cast<uint2*>(foot + (size_t(p) << mip.strideShift));
-#pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
-            {
-                if (layer < params.numLayers)
-                {
-                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
-                    dst[layer] = make_uint2(shared.latentTable[pixel & 0xFF], shared.latentTable[pixel >> 8]);
-                }
-            }
-        }
-    }
-}
-
-// Four quantised inputs of one latent layer from the four staged taps.
-// Blend order as the reference build evaluates it: fma(l11,w3, fma(l10,w2, fma(l00,w0, l01*w1))).
-template <bool kFp8>
-__device__ __forceinline__ uint32_t BlendLayer(uint2 l00, uint2 l01, uint2 l10, uint2 l11, __half2 w00, __half2 w01,
-    __half2 w10, __half2 w11)
-{
-    const __half2 two = __float2half2_rn(2.f), minusOne = __float2half2_rn(-1.f);
-    __half2 a = __hmul2_rn(AsHalf2(l01.x), w01);
-    __half2 b = __hmul2_rn(AsHalf2(l01.y), w01);
-    a = __hfma2(AsHalf2(l00.x), w00, a);
-    b = __hfma2(AsHalf2(l00.y), w00, b);
-    a = __hfma2(AsHalf2(l10.x), w10, a);
-    b = __hfma2(AsHalf2(l10.y), w10, b);
-    a = __hfma2(AsHalf2(l11.x), w11, a);
-    b = __hfma2(AsHalf2(l11.y), w11, b);
-    a = __hfma2(a, two, minusOne);
-    b = __hfma2(b, two, minusOne);
-    return PackCodes<kFp8>(QuantizeInputPair<kFp8>(a), QuantizeInputPair<kFp8>(b));
-}
-
-// Inputs 0..15 or 16..31 of one texel from the staged footprint of one grid.
-template <bool kFp8>
-__device__ __forceinline__ void GatherGrid(const KernelParams& params, const KernelMip& mip, const SharedStorage& shared,
-    int grid, int lane, int tileRow, uint32_t* words)
-{
-    const int4 col = shared.tables.colTap[grid][lane];
-    const int4 row = shared.tables.rowTap[grid][tileRow];
-    const int footW = shared.tables.footWidth[grid];
-    const float dx = __int_as_float(col.y), dxn = __int_as_float(col.z);
-    const float dy = __int_as_float(row.y), dyn = __int_as_float(row.z);
-    // src/FeatureGridDevice.h:46-49
-    const float f00 = __fmul_rn(dxn, dyn), f01 = __fmul_rn(dx, dyn), f10 = __fmul_rn(dxn, dy), f11 = __fmul_rn(dx, dy);
-    const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
-    const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
-
-    const int stride = 1 << mip.strideShift;
-    const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (size_t(row.x * footW + col.x) << mip.strideShift);
-    const uint8_t* tap10 = tap00 + (size_t(footW) << mip.strideShift);
-#pragma unroll
-    for (int layer = 0; layer < 4; ++layer)
-    {
-        if (layer < params.numLayers)
-        {
-            const uint2 l00 = *reinterpret_cast<const uint2*>(tap00 + layer * 8);
-            const uint2 l01 = *reinterpret_cast<const uint2*>(tap00 + stride + layer * 8);
-            const uint2 l10 = *reinterpret_cast<const uint2*>(tap10 + layer * 8);
-            const uint2 l11 = *reinterpret_cast<const uint2*>(tap10 + stride + layer * 8);
-            words[layer] = BlendLayer<kFp8>(l00, l01, l10, l11, w00, w01, w10, w11);
-        }
-    }
-}
 
 struct TileContext
 {
@@ -566,72 +351,6 @@ __device__ __forceinline__ int RunLayer(const Params& params, const SharedStorag
         return 1;
     ConsumeLayer<kFp8, kLayer, kConvert>(params, shared, ctx, phase, failed);
     return 0;
-}
-
-// Inputs 0..31 of one texel with the taps read straight from global memory.
-template <bool kFp8>
-__device__ __forceinline__ void SampleGridsDirect(const uint16_t* __restrict__ latents, int numLayers, const KernelMip& mip,
-    int x, int y, const uint32_t* __restrict__ latentTable, uint32_t* words)
-{
-    // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
-    const float u = __fmul_rn(__fadd_rn(float(x), 0.5f), mip.invWidth);
-    const float v = __fmul_rn(__fadd_rn(float(y), 0.5f), mip.invHeight);
-    GridTaps taps;
-    SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
-    const uint16_t* hi = latents + mip.hiOffset;
-#pragma unroll
-    for (int layer = 0; layer < 4; ++layer)
-        if (layer < numLayers)
-            words[layer] = SampleLayer<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, latentTable);
-    SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
-    const uint16_t* lo = latents + mip.loOffset;
-#pragma unroll
-    for (int layer = 0; layer < 4; ++layer)
-        if (layer < numLayers)
-            words[4 + layer] = SampleLayer<kFp8>(lo + size_t(layer) * mip.loPlane, taps, latentTable);
-}
-
-// The 48 network inputs of one texel -> its 64-byte row of the A operand (K-major core matrices:
-// 16-byte chunk j of row r lives at j * 2048 + r * 16).
-template <bool kFp8>
-__device__ __forceinline__ void BuildInputs(const KernelParams& params, const KernelMip& mip, const SharedStorage& shared,
-    const TileContext& ctx, int lane, int tileRow)
-{
-    uint32_t words[16];
-    const uint32_t zeroWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(0.f)),
-                                              QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        words[i] = zeroWord; // unused feature slots hold quantised zeros (src/Inference.cu:49)
-    // K padding: zeros for e4m3 operands; for int8 operands the constant inputs of the bias slots
-    const uint32_t slotFill = kFp8 ? 0u : kBiasSlotValue * 0x01010101u;
-    words[12] = words[13] = words[14] = slotFill;
-    words[15] = kFp8 ? 0u : ((slotFill & 0x00FFFFFFu) | 0x01000000u);
-
-    if (mip.staged)
-    {
-        GatherGrid<kFp8>(params, mip, shared, 0, lane, tileRow, words);
-        GatherGrid<kFp8>(params, mip, shared, 1, lane, tileRow, words + 4);
-    }
-    else
-    {
-        // footprint too large to stage (strong minification): read the taps from global memory;
-        // threads past the right / bottom edge compute a clamped texel and store nothing
-        SampleGridsDirect<kFp8>(params.latents, params.numLayers, mip, min(ctx.x, mip.width - 1), min(ctx.y, mip.rowEnd - 1),
-            shared.latentTable, words);
-    }
-
-    // positional encoding: interleave the column's x bytes with the row's y bytes
-    const uint2 cx = shared.tables.colEnc[lane];
-    const uint2 ry = shared.tables.rowEnc[tileRow];
-    words[8] = __byte_perm(cx.x, ry.x, 0x5140);
-    words[9] = __byte_perm(cx.x, ry.x, 0x7362);
-    words[10] = __byte_perm(cx.y, ry.y, 0x5140);
-    words[11] = shared.tables.lodWord;
-
-#pragma unroll
-    for (int chunk = 0; chunk < 4; ++chunk)
-        ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
 }
 
 // One-time setup of a CTA: the network image arrives by one TMA bulk copy while the threads fill

@@ -49,13 +49,17 @@ constexpr uint32_t kFlagBiasTable = 1; // int8 layers add their bias from the ta
 constexpr int kBiasSlotValue = 127;
 constexpr int kBiasRegionBytes = 128 * 32; // constant A operand of the extra K step: 128 rows x 32 slots
 
-// Image of the network for the reference-numerics kernel (produced by ntcb_stage_network_reference):
-// binary16 weights as the reference's CUDA path rebuilds them from the file
+// Image of the network for the reference-numerics kernels (produced by ntcb_stage_network_reference).
+// Int8 networks, and layer 3 of FP8 networks: binary16 weights as the reference's CUDA path rebuilds
+// them from the file
 // (src/Quantizer.cu:325-408), K-major core matrices of 8 halves (element (n, k) of layer l at
 // (k / 8) * (N_l * 16) + n * 16 + (k % 8) * 2), followed per layer by the operand of the "bias
 // step": an N_l x 16 matrix whose column 0 is the binary16 bias.  Multiplied by a constant A operand
 // whose rows are (1, 0, ..., 0), it sets the accumulators to the bias exactly, as the reference
-// initialises its accumulator fragments (src/tin/tin_mlp.h:71-89).
+// initialises its accumulator fragments (src/tin/tin_mlp.h:71-89).  Layers 0-2 of FP8 networks keep
+// their e4m3 bytes: one N_l x 32 byte matrix per 16-wide K step, the step's 16 weights at their place
+// inside the 32-wide chunk and zeros in the other half (same offsets and sizes as the binary16
+// matrices they replace).
 constexpr int kRefWeightOffset0 = 0;       // 64 x 48 halves
 constexpr int kRefWeightOffset1 = 6144;    // 48 x 64
 constexpr int kRefWeightOffset2 = 12288;   // 32 x 48
@@ -76,6 +80,7 @@ constexpr int kRefTmemColumns = kRefChains * kTmemColumnsPerHalf;
 constexpr int kRefFootprintHiBytes = 8192;  // the binary16 operands leave less room for the high-res footprint
 constexpr int kRefFootprintLoBytes = 4096;
 constexpr int kCtasPerSmRef = 3;
+constexpr int kCtasPerSmRefFp8 = 4; // FP8 networks: 8-bit operands halve the A buffers
 
 constexpr uint32_t kStatusBarrierTimeout = 1;
 

@@ -31,6 +31,7 @@
 
 #include "decode_kernel.h"
 #include "kernel_parts.cuh"
+#include "input_stage.cuh"
 #include "output_convert.cuh"
 #include "epilogue_convert.cuh"
 
@@ -809,6 +810,465 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernel
     TeardownCtaRef(shared, ctx, phase, failed, tid, warp);
 }
 
+// =============================================================================================
+// FP8 networks: the same arithmetic with 8-bit operands
+// =============================================================================================
+//
+// In an FP8 network the inputs of layers 0-2 and their weights are e4m3 numbers, which binary16
+// holds exactly, so the products the reference forms are the same whether the operands are stored
+// as binary16 or as e4m3 bytes.  What has to be preserved is the rounding rhythm: one rounding of
+// the binary16 accumulator per 16 products.  tcgen05.mma kind::f8f6f4 takes 32 products per
+// instruction, so every 32-wide K chunk is issued twice, against two copies of the weights of
+// which one has columns 16-31 zeroed and the other columns 0-15: each instruction adds 16 real
+// products (and 16 exact zeros) to the accumulator and rounds once - bit for bit what the binary16
+// path does (checked on the GPU against wmma on 1.2 M accumulators before this kernel was written).
+// The A operand shrinks to 64 bytes per row, which lets four CTAs share an SM.  Layer 3 (int8-grid
+// activations, weights rebuilt from int8) stays on the binary16 path; its 32 inputs fit the same
+// 64-byte rows.
+
+struct __align__(128) RefFp8SharedStorage
+{
+    uint8_t network[kRefNetworkBytes];                  // layers 0-2: split e4m3 weight copies; layer 3 and bias steps: binary16
+    alignas(128) uint8_t operandA[2 * kOperandBytes];   // A operands (top half, bottom half): 128 rows x 64 bytes each
+    alignas(128) uint8_t biasRegion[128 * 32];          // constant binary16 A operand of the bias step: rows (1, 0 x 15)
+    uint8_t footprintHi[kRefFootprintHiBytes];
+    uint8_t footprintLo[kRefFootprintLoBytes];
+    uint32_t latentTable[256];
+    TileTables tables;
+    uint64_t barrier[kRefChains]; // MMA completion, per chain
+    uint64_t loadBarrier;         // arrival of the network image
+    uint32_t tmemBase;
+};
+
+// D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 32 e4m3 operands, binary16 accumulators.
+__device__ __forceinline__ void UmmaE4m3F16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(tmemD),
+        "l"(descA), "l"(descB), "r"(instr), "r"(accumulate)
+        : "memory");
+}
+
+template <int kLayer>
+__device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int failed)
+{
+    constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
+    constexpr int kK = kLayer == 0 ? 48 : kLayer == 1 ? 64 : kLayer == 2 ? 48 : 32;
+    constexpr int kWeightOffset =
+        kLayer == 0 ? kRefWeightOffset0 : kLayer == 1 ? kRefWeightOffset1 : kLayer == 2 ? kRefWeightOffset2 : kRefWeightOffset3;
+    constexpr int kBiasOffset =
+        kLayer == 0 ? kRefBiasOffset0 : kLayer == 1 ? kRefBiasOffset1 : kLayer == 2 ? kRefBiasOffset2 : kRefBiasOffset3;
+
+    FenceProxyAsyncShared();
+    TcgenFenceBeforeSync();
+    if (__syncthreads_or(failed))
+        return 1;
+
+    if (ctx.tid == 0)
+    {
+        TcgenFenceAfterSync();
+        // both descriptors: binary16 accumulators, operand formats 0 (binary16 for kind::f16, e4m3 for kind::f8f6f4)
+        constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
+#pragma unroll
+        for (int half = 0; half < kRefChains; ++half)
+        {
+            const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
+            // accumulators := bias (binary16 step: rows (1, 0, ...) times the bias column: exact)
+            UmmaF16(accumulators, MakeSmemDescriptor(ctx.biasRegion, 2048, 128),
+                MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128), instr, 0);
+#pragma unroll
+            for (int step = 0; step < kK / 16; ++step)
+            {
+                if (kLayer < 3)
+                {
+                    // 16 products of the 32-wide chunk step / 2: weight copy `step` has the other 16 columns zeroed
+                    const uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes + (step / 2) * 2 * 2048, 2048, 128);
+                    const uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + step * kN * 32, kN * 16, 128);
+                    UmmaE4m3F16(accumulators, descA, descB, instr, 1);
+                }
+                else
+                {
+                    // binary16 operands: one K step = two core matrices of 8 halves
+                    const uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes + step * 2 * 2048, 2048, 128);
+                    const uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + step * 2 * kN * 16, kN * 16, 128);
+                    UmmaF16(accumulators, descA, descB, instr, 1);
+                }
+            }
+            UmmaCommit(ctx.barrierBase + half * 8);
+        }
+    }
+    return 0;
+}
+
+// Clamped HGELU in binary16 and the e4m3 code of the result: two codes in the low 16 bits.
+__device__ __forceinline__ uint32_t ActivateToE4m3(uint32_t bits)
+{
+    const __half2 x = AsHalf2(bits);
+    const __half2 third = __float2half2_rn(1 / 3.f);
+    const __half2 t = __hfma2_sat(third, x, __float2half2_rn(0.5f));
+    const __half2 m = __hmin2(x, __float2half2_rn(3.f));
+    const __half2 y = __hmul2_rn(m, t);
+    return uint32_t(__nv_cvt_halfraw2_to_fp8x2(static_cast<__half2_raw>(y), __NV_SATFINITE, __NV_E4M3));
+}
+
+template <int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+{
+    constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
+
+    if (!MbarrierWaitBounded(ctx.barrier, phase))
+    {
+        failed = 1;
+        params.status[0] = kStatusBarrierTimeout;
+        params.status[1] = uint32_t(ctx.tile);
+        params.status[2] = uint32_t(kLayer);
+    }
+    phase ^= 1;
+    TcgenFenceAfterSync();
+
+    if (kLayer < 2)
+    {
+        // e4m3 codes for the next layer: 16 per 16-byte chunk
+        uint4* rowChunk = ctx.rowChunk;
+        uint32_t low[16], high[16];
+        TmemLoadPacked16(ctx.tmemLane, low);
+        if (kN == 64)
+            TmemLoadPacked16(ctx.tmemLane + 32, high);
+        else
+        {
+            uint32_t (&tail)[8] = reinterpret_cast<uint32_t (&)[8]>(high);
+            TmemLoadPacked8(ctx.tmemLane + 32, tail);
+        }
+        TmemLoadWait();
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+            rowChunk[c * 128] = make_uint4(
+                PackCodes<true>(ActivateToE4m3(low[8 * c]), ActivateToE4m3(low[8 * c + 1])),
+                PackCodes<true>(ActivateToE4m3(low[8 * c + 2]), ActivateToE4m3(low[8 * c + 3])),
+                PackCodes<true>(ActivateToE4m3(low[8 * c + 4]), ActivateToE4m3(low[8 * c + 5])),
+                PackCodes<true>(ActivateToE4m3(low[8 * c + 6]), ActivateToE4m3(low[8 * c + 7])));
+#pragma unroll
+        for (int c = 0; c < (kN - 32) / 16; ++c)
+            rowChunk[(2 + c) * 128] = make_uint4(
+                PackCodes<true>(ActivateToE4m3(high[8 * c]), ActivateToE4m3(high[8 * c + 1])),
+                PackCodes<true>(ActivateToE4m3(high[8 * c + 2]), ActivateToE4m3(high[8 * c + 3])),
+                PackCodes<true>(ActivateToE4m3(high[8 * c + 4]), ActivateToE4m3(high[8 * c + 5])),
+                PackCodes<true>(ActivateToE4m3(high[8 * c + 6]), ActivateToE4m3(high[8 * c + 7])));
+        if (kLayer == 1)
+            rowChunk[3 * 128] = make_uint4(0, 0, 0, 0); // layer 2 has 48 inputs: the rest of its second chunk must be zeros
+    }
+    else if (kLayer == 2)
+    {
+        // layer 3 runs on the binary16 path: its inputs are the int8 grid values rint(y * 80) * 0.0125
+        uint4* rowChunk = ctx.rowChunk;
+        uint32_t acc[16];
+        TmemLoadPacked16(ctx.tmemLane, acc);
+        TmemLoadWait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            rowChunk[c * 128] = make_uint4(ActivateRef<false>(acc[4 * c]), ActivateRef<false>(acc[4 * c + 1]),
+                                           ActivateRef<false>(acc[4 * c + 2]), ActivateRef<false>(acc[4 * c + 3]));
+    }
+    else
+    {
+        // output (src/Inference.cu:121-135): the accumulators are the channels
+        uint32_t bits[8];
+        TmemLoadPacked8(ctx.tmemLane, bits);
+        TmemLoadWait();
+        const int channelPairs = params.channels >> 1;
+        uint32_t special = 0; // bit 15 / 31 set when a value has an all-ones exponent
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < channelPairs)
+                special |= (bits[j] & 0x7C007C00u) + 0x04000400u;
+        if (special & 0x80008000u)
+        {
+            // Inf / NaN -> 0 (src/CudaUtils.h:30-35); rare, so kept off the common path
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+            {
+                if (j < channelPairs)
+                {
+                    if ((bits[j] & 0x7C00u) == 0x7C00u) bits[j] &= 0xFFFF0000u;
+                    if ((bits[j] & 0x7C000000u) == 0x7C000000u) bits[j] &= 0x0000FFFFu;
+                }
+            }
+        }
+        if constexpr (kConvert)
+        {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j >= channelPairs)
+                    bits[j] = 0;
+            if (ctx.out)
+                StoreConverted(params.conversion, params.firstChannel, params.numChannels, ctx, bits);
+        }
+        else if (ctx.out)
+        {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (j < channelPairs)
+                    ctx.out[j * ctx.outStepWords] = bits[j];
+        }
+    }
+}
+
+template <int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+{
+    if (IssueLayerRefFp8<kLayer>(ctx, failed))
+        return 1;
+    ConsumeLayerRefFp8<kLayer, kConvert>(params, ctx, phase, failed);
+    return 0;
+}
+
+// Setup and teardown as for the binary16 kernel, on the FP8 kernel's shared-memory structure.
+__device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const uint8_t* network, uint32_t* status, int tid, int warp)
+{
+    for (int i = tid; i < 256; i += kThreadsPerCta)
+    {
+        __half lo = __float2half_rn(__fmul_rn(float(i & 15), 1.f / 15.f));
+        __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
+        shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
+    }
+    for (int i = tid; i < 128 * 32 / 16; i += kThreadsPerCta)
+        reinterpret_cast<uint4*>(shared.biasRegion)[i] = make_uint4(i < 128 ? 0x00003C00u : 0u, 0u, 0u, 0u);
+    const uint32_t loadBarrier = SharedAddress(&shared.loadBarrier);
+    if (tid == 0)
+    {
+        for (int chain = 0; chain < kRefChains; ++chain)
+            MbarrierInit(SharedAddress(&shared.barrier[chain]), 1);
+        MbarrierInit(loadBarrier, 1);
+        FenceBarrierInit();
+        MbarrierArriveExpectTx(loadBarrier, kRefNetworkBytes);
+        BulkCopyToShared(SharedAddress(shared.network), network, kRefNetworkBytes, loadBarrier);
+    }
+    if (warp == 0)
+        TmemAlloc(SharedAddress(&shared.tmemBase), kTmemColumns);
+    FenceProxyAsyncShared();
+    TcgenFenceBeforeSync();
+    __syncthreads();
+    TcgenFenceAfterSync();
+    int failed = 0;
+    if (!MbarrierWaitBounded(loadBarrier, 0))
+    {
+        failed = 1;
+        status[0] = kStatusBarrierTimeout;
+        status[1] = 0xFFFFFFFFu;
+        status[2] = 0xFFFFFFFFu;
+    }
+    return failed;
+}
+
+__device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, const RefTileContext& ctx, uint32_t phase, int failed,
+    int tid, int warp)
+{
+    TcgenFenceBeforeSync();
+    const int aborted = __syncthreads_or(failed);
+    if (aborted && tid == 0)
+    {
+        for (int chain = 0; chain < kRefChains; ++chain)
+            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phase ^ 1);
+        (void)MbarrierWaitBounded(SharedAddress(&shared.loadBarrier), 0);
+    }
+    __syncthreads();
+    if (warp == 0)
+        TmemFree(ctx.tmemBase, kTmemColumns);
+}
+
+template <bool kConvert>
+__global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernelRefFp8(const __grid_constant__ KernelParams params)
+{
+    extern __shared__ __align__(128) unsigned char dynamicShared[];
+    RefFp8SharedStorage& shared = *reinterpret_cast<RefFp8SharedStorage*>(dynamicShared);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;      // = the thread's row of the tile
+    const int half = warp >> 2;     // the 128-row chain of this thread
+
+    int failed = SetupCtaRefFp8(shared, params.network, params.status, tid, warp);
+    uint32_t phase = 0;
+    int aborted = 0;
+
+    RefTileContext ctx;
+    ctx.tid = tid;
+    ctx.tmemBase = shared.tmemBase;
+    ctx.tmemLane = ctx.tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
+    ctx.barrierBase = SharedAddress(&shared.barrier[0]);
+    ctx.barrier = ctx.barrierBase + half * 8;
+    ctx.operandA = SharedAddress(shared.operandA);
+    ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
+    ctx.networkBase = SharedAddress(shared.network);
+    ctx.biasRegion = SharedAddress(shared.biasRegion);
+
+    struct TilePlace
+    {
+        int mipIndex, tileX0, tileY0;
+    };
+    auto locate = [&](int tile, int fromMip) {
+        TilePlace place;
+        place.mipIndex = fromMip;
+        while (place.mipIndex + 1 < params.numMips && tile >= params.mips[place.mipIndex + 1].firstTile)
+            ++place.mipIndex;
+        const KernelMip& mip = params.mips[place.mipIndex];
+        const int local = tile - mip.firstTile;
+        const int tileY = mip.tilesX == 1 ? local : int(__umulhi(uint32_t(local), mip.tilesXMagic));
+        place.tileX0 = (local - tileY * mip.tilesX) * kTileWidth;
+        place.tileY0 = mip.rowBegin + tileY * kTileHeight;
+        return place;
+    };
+
+    int tile = blockIdx.x;
+    TilePlace place{0, 0, 0};
+    if (tile < params.totalTiles)
+    {
+        place = locate(tile, 0);
+        PrepareTile<true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        __syncthreads();
+    }
+    while (tile < params.totalTiles)
+    {
+        const KernelMip& mip = params.mips[place.mipIndex];
+        ctx.tile = tile;
+        ctx.x = place.tileX0 + lane;
+        ctx.y = place.tileY0 + warp;
+        {
+            const bool planar = params.outputLayout == kLayoutPlanarPairs;
+            const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
+                                          : (uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x)) * uint32_t(params.channels);
+            const bool inside = ctx.x < mip.width && ctx.y < mip.rowEnd;
+            if constexpr (kConvert)
+            {
+                const uint32_t pixelIndex = uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x);
+                const size_t component = size_t(mip.outOffset) + size_t(pixelIndex) * size_t(params.conversion.dstChannels);
+                unsigned char* bytes = reinterpret_cast<unsigned char*>(params.out) + component * BytesPerComponent(params.conversion.format);
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(bytes) : nullptr;
+                ctx.outStepWords = pixelIndex;
+            }
+            else
+            {
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
+                ctx.outStepWords = planar ? uint32_t(mip.width) : 1u;
+            }
+        }
+
+        // the e4m3 input stage is the one of the exact-accumulation kernel (64-byte rows of codes)
+        BuildInputs<true>(params, mip, shared, ctx, lane, warp);
+
+        aborted = IssueLayerRefFp8<0>(ctx, failed);
+        if (aborted)
+            break;
+        const int nextTile = tile + int(gridDim.x);
+        if (nextTile < params.totalTiles)
+        {
+            place = locate(nextTile, place.mipIndex);
+            PrepareTile<true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        }
+        ConsumeLayerRefFp8<0, false>(params, ctx, phase, failed);
+
+        aborted = RunLayerRefFp8<1, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<2, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<3, kConvert>(params, ctx, phase, failed);
+        if (aborted)
+            break;
+        tile = nextTile;
+    }
+    TeardownCtaRefFp8(shared, ctx, phase, failed, tid, warp);
+}
+
+// Inference on sample for FP8 networks (8-bit operands): one thread per query, taps read straight
+// from global memory.
+__global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernelRefFp8(const __grid_constant__ SampleParams params)
+{
+    extern __shared__ __align__(128) unsigned char dynamicShared[];
+    RefFp8SharedStorage& shared = *reinterpret_cast<RefFp8SharedStorage*>(dynamicShared);
+    __shared__ KernelMip mipTable[16];
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int half = warp >> 2;
+
+    if (tid < params.numMips)
+        mipTable[tid] = params.mips[tid];
+    int failed = SetupCtaRefFp8(shared, params.network, params.status, tid, warp);
+    int aborted = 0;
+    uint32_t phase = 0;
+
+    RefTileContext ctx;
+    ctx.tid = tid;
+    ctx.tmemBase = shared.tmemBase;
+    ctx.tmemLane = ctx.tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
+    ctx.barrierBase = SharedAddress(&shared.barrier[0]);
+    ctx.barrier = ctx.barrierBase + half * 8;
+    ctx.operandA = SharedAddress(shared.operandA);
+    ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
+    ctx.networkBase = SharedAddress(shared.network);
+    ctx.biasRegion = SharedAddress(shared.biasRegion);
+    ctx.outStepWords = 1;
+
+    const unsigned long long tiles = (params.numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
+    for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x)
+    {
+        const unsigned long long query = tile * kThreadsPerCta + tid;
+        const bool valid = query < params.numQueries;
+        const unsigned long long q = valid ? query : params.numQueries - 1;
+        const float u = __ldg(params.queries + 3 * q), v = __ldg(params.queries + 3 * q + 1), lod = __ldg(params.queries + 3 * q + 2);
+        const int mipIndex = max(0, min(params.numMips - 1, int(floorf(lod))));
+        const KernelMip& mip = mipTable[mipIndex];
+        const int x = max(0, min(mip.width - 1, int(floorf(__fmul_rn(u, float(mip.width))))));
+        const int y = max(0, min(mip.height - 1, int(floorf(__fmul_rn(v, float(mip.height))))));
+        ctx.tile = int(tile);
+        ctx.x = x;
+        ctx.y = y;
+        ctx.out = valid ? reinterpret_cast<uint32_t*>(params.out + query * params.channels) : nullptr;
+
+        {
+            uint32_t words[16];
+            const uint32_t zeroWord = PackCodes<true>(QuantizeInputPair<true>(__float2half2_rn(0.f)),
+                                                      QuantizeInputPair<true>(__float2half2_rn(0.f)));
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                words[i] = zeroWord; // unused feature slots hold quantised zeros (src/Inference.cu:49)
+#pragma unroll
+            for (int i = 12; i < 16; ++i)
+                words[i] = 0;        // K padding
+            SampleGridsDirect<true>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
+            // src/RegressionKernels.h:59-85
+            float xf = __fmul_rn(float(x), mip.positionScale);
+            float yf = __fmul_rn(float(y), mip.positionScale);
+#pragma unroll
+            for (int wave = 0; wave < 3; ++wave)
+            {
+                const float ex = __fmaf_rn(Frac(xf), 2.f, -1.f), ey = __fmaf_rn(Frac(yf), 2.f, -1.f);
+                const float ez = __fmaf_rn(Frac(__fadd_rn(xf, 0.25f)), 2.f, -1.f);
+                const float ew = __fmaf_rn(Frac(__fadd_rn(yf, 0.25f)), 2.f, -1.f);
+                words[8 + wave] = PackCodes<true>(QuantizeInputPair<true>(__floats2half2_rn(ex, ey)),
+                                                  QuantizeInputPair<true>(__floats2half2_rn(ez, ew)));
+                xf = __fmul_rn(xf, 2.f);
+                yf = __fmul_rn(yf, 2.f);
+            }
+            words[11] = PackCodes<true>(QuantizeInputPair<true>(__float2half2_rn(mip.positionLod)),
+                                        QuantizeInputPair<true>(__float2half2_rn(0.f)));
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk)
+                ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
+        }
+
+        aborted = RunLayerRefFp8<0, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<1, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<2, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<3, false>(params, ctx, phase, failed);
+        if (aborted)
+            break;
+    }
+    TeardownCtaRefFp8(shared, ctx, phase, failed, tid, warp);
+}
+
 } // namespace
 
 cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
@@ -830,9 +1290,28 @@ cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cuda
         kernel<<<ctas, kRefThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
         return cudaGetLastError();
     };
-    if (params.convert)
-        return fp8 ? launch(DecodeKernelRef<true, true>, done[3]) : launch(DecodeKernelRef<false, true>, done[2]);
-    return fp8 ? launch(DecodeKernelRef<true, false>, done[1]) : launch(DecodeKernelRef<false, false>, done[0]);
+    if (fp8)
+    {
+        // FP8 networks take the kernel with 8-bit operands (same bits, four CTAs per SM)
+        auto launchFp8 = [&](auto kernel, std::atomic<unsigned long long>& doneMask) -> cudaError_t {
+            int device = 0;
+            cudaError_t err = cudaGetDevice(&device);
+            if (err != cudaSuccess)
+                return err;
+            const unsigned long long bit = 1ull << (device & 63);
+            if (!(doneMask.load(std::memory_order_acquire) & bit))
+            {
+                err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefFp8SharedStorage)));
+                if (err != cudaSuccess)
+                    return err;
+                doneMask.fetch_or(bit, std::memory_order_release);
+            }
+            kernel<<<ctas, kThreadsPerCta, sizeof(RefFp8SharedStorage), stream>>>(params);
+            return cudaGetLastError();
+        };
+        return params.convert ? launchFp8(DecodeKernelRefFp8<true>, done[3]) : launchFp8(DecodeKernelRefFp8<false>, done[1]);
+    }
+    return params.convert ? launch(DecodeKernelRef<false, true>, done[2]) : launch(DecodeKernelRef<false, false>, done[0]);
 }
 
 cudaError_t LaunchSampleRef(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream)
@@ -854,7 +1333,24 @@ cudaError_t LaunchSampleRef(const SampleParams& params, bool fp8, int ctas, cuda
         kernel<<<ctas, kRefThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
         return cudaGetLastError();
     };
-    return fp8 ? launch(SampleKernelRef<true>, done[1]) : launch(SampleKernelRef<false>, done[0]);
+    if (fp8)
+    {
+        int device = 0;
+        cudaError_t err = cudaGetDevice(&device);
+        if (err != cudaSuccess)
+            return err;
+        const unsigned long long bit = 1ull << (device & 63);
+        if (!(done[1].load(std::memory_order_acquire) & bit))
+        {
+            err = cudaFuncSetAttribute(SampleKernelRefFp8, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefFp8SharedStorage)));
+            if (err != cudaSuccess)
+                return err;
+            done[1].fetch_or(bit, std::memory_order_release);
+        }
+        SampleKernelRefFp8<<<ctas, kThreadsPerCta, sizeof(RefFp8SharedStorage), stream>>>(params);
+        return cudaGetLastError();
+    }
+    return launch(SampleKernelRef<false>, done[0]);
 }
 
 } // namespace ntcb

@@ -150,8 +150,8 @@ namespace
 // Number of CTAs that fill the current device, cached per device.
 int ResidentCtas(bool fp8, bool converting, int* outCtas, bool reference = false)
 {
-    static std::atomic<int> cache[64][4];
-    const int variant = reference ? 3 : converting ? 2 : fp8 ? 1 : 0;
+    static std::atomic<int> cache[64][5];
+    const int variant = reference ? (fp8 ? 4 : 3) : converting ? 2 : fp8 ? 1 : 0;
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess)
@@ -182,9 +182,10 @@ int ResidentCtas(bool fp8, bool converting, int* outCtas, bool reference = false
     // occupancy query reports one CTA per SM for kernels that allocate tensor memory, so it is not
     // used here.)
     static_assert(kCtasPerSmInt8 * kTmemColumns <= 512 && kCtasPerSmFp8 * kTmemColumns <= 512 &&
-                      kCtasPerSmConverting * kTmemColumns <= 512 && kCtasPerSmRef * kRefTmemColumns <= 512,
+                      kCtasPerSmConverting * kTmemColumns <= 512 && kCtasPerSmRef * kRefTmemColumns <= 512 &&
+                      kCtasPerSmRefFp8 * kTmemColumns <= 512,
         "resident CTAs must fit into tensor memory");
-    const int perSm = reference ? kCtasPerSmRef : converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
+    const int perSm = reference ? (fp8 ? kCtasPerSmRefFp8 : kCtasPerSmRef) : converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
     *outCtas = sms * perSm;
     if (device >= 0 && device < 64)
         cache[device][variant].store(*outCtas, std::memory_order_relaxed);
@@ -443,11 +444,17 @@ int ntcb_stage_network_reference(const void* blob, size_t blobBytes, int weightM
             uint16_t bias;
             if (layerFp8)
             {
-                // UnquantizeColumnFP8 (src/Quantizer.cu:384-408): e4m3 -> binary16 is exact; the bias is copied
+                // UnquantizeColumnFP8 (src/Quantizer.cu:384-408) turns the e4m3 weights into the same numbers
+                // in binary16, so the kernel multiplies the e4m3 bytes themselves.  Each 16-wide K step s gets
+                // its own N x 32 byte matrix (K-major core matrices: byte (n, j) at (j / 16) * (N * 16) + n * 16
+                // + j % 16) that holds the 16 weights of the step at their place inside the 32-wide chunk
+                // s / 2 and zeros in the other half: 16 real products per 32-product instruction.
+                uint8_t* bytes = dst + kRefWeightOffsets[layer];
                 for (int k = 0; k < nin; ++k)
                 {
-                    const __half_raw w = __nv_cvt_fp8_to_halfraw(src[weightStart[layer] + size_t(n) * nin + k], __NV_E4M3);
-                    weights[(k / 8) * (nout * 8) + n * 8 + (k % 8)] = w.x;
+                    const int step = k / 16, j = k % 32;
+                    bytes[size_t(step) * nout * 32 + (j / 16) * (nout * 16) + n * 16 + (j % 16)] =
+                        src[weightStart[layer] + size_t(n) * nin + k];
                 }
                 memcpy(&bias, biasStart[layer] + 2u * n, 2);
             }
