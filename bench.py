@@ -57,7 +57,7 @@ WORKLOAD = ("PBR texture set 4096x4096, 12 channels, 13 mips, latent shape {grid
 
 # DRAM bytes per launch of the decode kernel on this workload (dram__bytes_read.sum +
 # dram__bytes_write.sum from the ncu capture summarised in profiles/).
-MEASURED_TRAFFIC_BYTES = 492.3e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
+MEASURED_TRAFFIC_BYTES = 491.2e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
 
 
 def measured_peak_gbs():
@@ -352,7 +352,9 @@ def run_ours(args) -> dict:
                 "launches_per_step": len(step_ms) and launch_count // max(1, args.steps)}
     if numerics == binding.NUMERICS_REFERENCE:
         dtype = ("f16 x f16 -> f16 (tcgen05 kind::f16, binary16 accumulators rounded per 16 products: the reference's own "
-                 "arithmetic on %s weights, reproduced bit for bit)" % ("int8" if use_int8 else "e4m3 / int8"))
+                 "arithmetic on int8 weights, reproduced bit for bit)" if use_int8 else
+                 "e4m3 x e4m3 -> f16 (tcgen05 kind::f8f6f4, binary16 accumulators, 16 non-zero products per rounding; last layer "
+                 "f16 x f16 -> f16): the reference's own arithmetic, reproduced bit for bit")
     else:
         dtype = ("fp8_e4m3 x fp8_e4m3 -> f32 (layers 0-2), s8 x s8 -> s32 (layer 3), f16 activations" if not use_int8
                  else "s8 x s8 -> s32 (all layers), f16 activations")
