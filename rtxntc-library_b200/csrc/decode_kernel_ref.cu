@@ -419,19 +419,24 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
     {
         TcgenFenceAfterSync();
         constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
+        // The issuing thread is the critical path of the layer: the four base descriptors are built
+        // once, every operand is then a constant offset (in 16-byte units) added to the address field.
+        const uint64_t operandBase = MakeSmemDescriptor(ctx.operandA, 2048, 128);
+        const uint64_t onesBase = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
+        const uint64_t weightBase = MakeSmemDescriptor(ctx.networkBase + kWeightOffset, kN * 16, 128);
+        const uint64_t biasBase = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
 #pragma unroll
         for (int half = 0; half < kRefChains; ++half)
         {
             const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
             // accumulators := bias (rows (1, 0, ...) times the bias column: exact)
-            UmmaF16(accumulators, MakeSmemDescriptor(ctx.biasRegion, 2048, 128),
-                MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128), instr, 0);
+            UmmaF16(accumulators, onesBase, biasBase, instr, 0);
 #pragma unroll
             for (int kStep = 0; kStep < kK / 16; ++kStep)
             {
                 // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
-                const uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kRefOperandBytes + kStep * 2 * 2048, 2048, 128);
-                const uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
+                const uint64_t descA = operandBase + uint64_t((half * kRefOperandBytes + kStep * 2 * 2048) >> 4);
+                const uint64_t descB = weightBase + uint64_t((kStep * 2 * kN * 16) >> 4);
                 UmmaF16(accumulators, descA, descB, instr, 1);
             }
             // arrives once everything issued so far has completed: this chain's accumulators are ready
@@ -873,28 +878,33 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
         TcgenFenceAfterSync();
         // both descriptors: binary16 accumulators, operand formats 0 (binary16 for kind::f16, e4m3 for kind::f8f6f4)
         constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
+        // The issuing thread is the critical path of the layer: the four base descriptors are built
+        // once, every operand is then a constant offset (in 16-byte units) added to the address field.
+        const uint64_t operandBase = MakeSmemDescriptor(ctx.operandA, 2048, 128);
+        const uint64_t onesBase = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
+        const uint64_t weightBase = MakeSmemDescriptor(ctx.networkBase + kWeightOffset, kN * 16, 128);
+        const uint64_t biasBase = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
 #pragma unroll
         for (int half = 0; half < kRefChains; ++half)
         {
             const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
             // accumulators := bias (binary16 step: rows (1, 0, ...) times the bias column: exact)
-            UmmaF16(accumulators, MakeSmemDescriptor(ctx.biasRegion, 2048, 128),
-                MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128), instr, 0);
+            UmmaF16(accumulators, onesBase, biasBase, instr, 0);
 #pragma unroll
             for (int step = 0; step < kK / 16; ++step)
             {
                 if (kLayer < 3)
                 {
                     // 16 products of the 32-wide chunk step / 2: weight copy `step` has the other 16 columns zeroed
-                    const uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes + (step / 2) * 2 * 2048, 2048, 128);
-                    const uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + step * kN * 32, kN * 16, 128);
+                    const uint64_t descA = operandBase + uint64_t((half * kOperandBytes + (step / 2) * 2 * 2048) >> 4);
+                    const uint64_t descB = weightBase + uint64_t((step * kN * 32) >> 4);
                     UmmaE4m3F16(accumulators, descA, descB, instr, 1);
                 }
                 else
                 {
                     // binary16 operands: one K step = two core matrices of 8 halves
-                    const uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes + step * 2 * 2048, 2048, 128);
-                    const uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + step * 2 * kN * 16, kN * 16, 128);
+                    const uint64_t descA = operandBase + uint64_t((half * kOperandBytes + step * 2 * 2048) >> 4);
+                    const uint64_t descB = weightBase + uint64_t((step * 2 * kN * 16) >> 4);
                     UmmaF16(accumulators, descA, descB, instr, 1);
                 }
             }
