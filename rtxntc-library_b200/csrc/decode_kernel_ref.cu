@@ -21,6 +21,12 @@
 //     as the reference does (src/tin/tin_activation.h:44-48, 94-99).
 //
 // Every wait on an mbarrier is bounded, as in decode_kernel.cu.
+//
+// Two kernels live here.  DecodeKernelRef (first part of the file) keeps every operand in binary16
+// and serves Int8 networks.  DecodeKernelRefFp8 (second part) serves FP8 networks with 8-bit operands
+// for layers 0-2 and produces the same bits; since ntcb_stage_network_reference lays an FP8
+// network out for it, the binary16 kernel's templates are only instantiated with kFp8 = false
+// (their kFp8 = true paths describe what the FP8 kernel replaces: e4m3 round trips in binary16).
 
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
