@@ -168,6 +168,7 @@ public:
 private:
     Status CheckKernelStatus();
     Status GrowStaging(size_t bytes);
+    Status CopyBands(const uint8_t* deviceMip0, uint8_t* host, size_t rowBytes);
     Status DecodeInto(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights,
         const NtcbOutputConversion* conversion, void* deviceOut);
 
@@ -195,6 +196,16 @@ private:
     size_t m_stagingBytes = 0;
     cudaEvent_t m_eventStart = nullptr, m_eventStop = nullptr;
     bool m_decoded = false;
+
+    // A whole-set decode of a large set is issued as kBands launches over row bands of mip 0 plus one
+    // for the other mips, so that a host read of mip 0 can start copying the first band while the
+    // rest is still being decoded (the read-back, not the decode, bounds Decompress + ReadChannels).
+    static constexpr int kBands = 4;
+    static constexpr int kBandMinRows = 512;
+    cudaStream_t m_copyStream = nullptr;
+    cudaEvent_t m_bandEvents[kBands + 1] = {}; // [b]: band b of mip 0 decoded; [kBands]: everything decoded
+    int m_bandEnd[kBands] = {};                // last row + 1 of each band
+    int m_bandCount = 0;                       // 0: the last decode was a single launch
 };
 
 class Context final : public IContext
@@ -397,8 +408,13 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
     err = cudaEventCreate(&m_eventStart);
     if (err == cudaSuccess)
         err = cudaEventCreate(&m_eventStop);
+    for (int b = 0; b <= kBands && err == cudaSuccess; ++b)
+        err = cudaEventCreateWithFlags(&m_bandEvents[b], cudaEventDisableTiming);
     if (err != cudaSuccess)
         return CudaFailure("cudaEventCreate", err);
+    err = cudaStreamCreateWithFlags(&m_copyStream, cudaStreamNonBlocking);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamCreateWithFlags", err);
     return NTCB_OK;
 }
 
@@ -406,6 +422,17 @@ void TextureSet::Release()
 {
     if (m_stream)
         cudaStreamSynchronize(m_stream);
+    if (m_copyStream)
+    {
+        cudaStreamSynchronize(m_copyStream);
+        cudaStreamDestroy(m_copyStream);
+        m_copyStream = nullptr;
+    }
+    for (cudaEvent_t& event : m_bandEvents)
+    {
+        if (event) cudaEventDestroy(event);
+        event = nullptr;
+    }
     if (m_eventStart) cudaEventDestroy(m_eventStart);
     if (m_eventStop) cudaEventDestroy(m_eventStop);
     if (m_staging) cudaFree(m_staging);
@@ -491,7 +518,23 @@ Status TextureSet::DecompressConverted(DecompressionStats* pOutStats, bool useIn
     if (status != NTCB_OK)
         return status;
     cudaError_t err;
-    if (toHost)
+    if (toHost && m_bandCount > 0)
+    {
+        // mip 0 band by band while the rest is decoded, then the other mips
+        const size_t rowBytes = size_t(m_geometry.mipWidth[0]) * pixelBytes;
+        const size_t mip0Bytes = rowBytes * size_t(m_geometry.mipHeight[0]);
+        status = CopyBands(m_staging, static_cast<uint8_t*>(destination), rowBytes);
+        if (status != NTCB_OK)
+            return status;
+        if (bytes > mip0Bytes)
+        {
+            err = cudaMemcpyAsync(static_cast<uint8_t*>(destination) + mip0Bytes, m_staging + mip0Bytes, bytes - mip0Bytes,
+                cudaMemcpyDeviceToHost, m_stream);
+            if (err != cudaSuccess)
+                return CudaFailure("cudaMemcpyAsync (converted texels)", err);
+        }
+    }
+    else if (toHost)
     {
         err = cudaMemcpyAsync(destination, m_staging, bytes, cudaMemcpyDeviceToHost, m_stream);
         if (err != cudaSuccess)
@@ -504,6 +547,31 @@ Status TextureSet::DecompressConverted(DecompressionStats* pOutStats, bool useIn
     if (status != NTCB_OK)
         return status;
     ClearError();
+    return NTCB_OK;
+}
+
+// Device-to-host copy of mip 0 (rows of `rowBytes` bytes, no padding) band by band as the bands of
+// the last decode complete; returns when the copy stream has drained.
+Status TextureSet::CopyBands(const uint8_t* deviceMip0, uint8_t* host, size_t rowBytes)
+{
+    int begin = 0;
+    for (int b = 0; b < m_bandCount; ++b)
+    {
+        const int end = m_bandEnd[b];
+        if (end > begin)
+        {
+            cudaError_t err = cudaStreamWaitEvent(m_copyStream, m_bandEvents[b], 0);
+            if (err == cudaSuccess)
+                err = cudaMemcpyAsync(host + size_t(begin) * rowBytes, deviceMip0 + size_t(begin) * rowBytes,
+                    size_t(end - begin) * rowBytes, cudaMemcpyDeviceToHost, m_copyStream);
+            if (err != cudaSuccess)
+                return CudaFailure("cudaMemcpyAsync (band)", err);
+        }
+        begin = end;
+    }
+    cudaError_t err = cudaStreamSynchronize(m_copyStream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamSynchronize (copy stream)", err);
     return NTCB_OK;
 }
 
@@ -597,7 +665,38 @@ Status TextureSet::DecodeInto(const int32_t* rowRanges, DecompressionStats* pOut
         if (err != cudaSuccess)
             return CudaFailure("cudaEventRecord (1)", err);
     }
-    Status status = ntcb_decode(&params, m_stream);
+    Status status = NTCB_OK;
+    m_bandCount = 0;
+    const int height0 = m_geometry.mipHeight[0];
+    if (!rowRanges && height0 >= kBandMinRows)
+    {
+        // row bands of mip 0 (whole tile rows), then the other mips
+        const int bandRows = ((height0 + kBands - 1) / kBands + 15) & ~15;
+        NtcbDecodeParams part = params;
+        for (int mip = 1; mip < m_geometry.mips; ++mip)
+            part.mips[mip].rowBegin = part.mips[mip].rowEnd = 0;
+        for (int b = 0; b < kBands && status == NTCB_OK; ++b)
+        {
+            part.mips[0].rowBegin = std::min(height0, b * bandRows);
+            part.mips[0].rowEnd = std::min(height0, (b + 1) * bandRows);
+            m_bandEnd[b] = part.mips[0].rowEnd;
+            status = ntcb_decode(&part, m_stream);
+            if (status == NTCB_OK && cudaEventRecord(m_bandEvents[b], m_stream) != cudaSuccess)
+                status = CudaFailure("cudaEventRecord (band)", cudaGetLastError());
+        }
+        if (status == NTCB_OK)
+        {
+            part = params;
+            part.mips[0].rowBegin = part.mips[0].rowEnd = 0;
+            status = ntcb_decode(&part, m_stream);
+            if (status == NTCB_OK && cudaEventRecord(m_bandEvents[kBands], m_stream) != cudaSuccess)
+                status = CudaFailure("cudaEventRecord (band)", cudaGetLastError());
+        }
+        if (status == NTCB_OK)
+            m_bandCount = kBands;
+    }
+    else
+        status = ntcb_decode(&params, m_stream);
     if (status != NTCB_OK)
         return status;
     if (pOutStats)
@@ -706,7 +805,15 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
                         params.numChannels == m_geometry.channels && params.pixelStride == size_t(m_geometry.channels) * 2 &&
                         params.rowPitch == params.pixelStride * size_t(width);
     cudaError_t err;
-    if (direct)
+    if (direct && toHost && params.mipLevel == 0 && m_bandCount > 0)
+    {
+        // the request is the internal layout and the decode ran in row bands: every band is copied as
+        // soon as it is decoded, on a stream of its own
+        Status copied = CopyBands(reinterpret_cast<const uint8_t*>(mipData), static_cast<uint8_t*>(params.pOutData), params.rowPitch);
+        if (copied != NTCB_OK)
+            return copied;
+    }
+    else if (direct)
     {
         // the request is the internal layout: one copy, no conversion pass
         err = cudaMemcpyAsync(params.pOutData, mipData, bytes, toHost ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice,

@@ -289,6 +289,34 @@ def test_texture_set_api_decompress_and_read_channels(oracle):
         context.close()
 
 
+def test_large_sets_decode_in_row_bands_with_pipelined_readback():
+    """A set whose mip 0 has 512 rows or more is decoded by the texture-set API in four row-band
+    launches plus one for the other mips, and a host read of mip 0 copies band by band: same bits
+    as the single launch, for fp16 and for converted pixels, in both numerics."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(200, 530, 6, 0, 2, 8, seed=12, network="unit"))
+    geo = data.geometry
+    with binding.Context(0) as context:
+        for numerics in (REFERENCE, EXACT):
+            resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
+            texture_set = context.create_texture_set(data.container, numerics=numerics)
+            for use_int8 in (True, False):
+                resident.decode(use_int8)
+                _sync()
+                resident.check_status()
+                texture_set.decompress(use_int8)
+                for mip in range(geo.mips):
+                    assert np.array_equal(texture_set.read_mip(mip).view(np.uint16), resident.mip_numpy(mip).view(np.uint16)), mip
+                # a second read, a sub-range read and a converted decode see the same texels
+                assert np.array_equal(texture_set.read_mip(0, 1, 3).view(np.uint16), resident.mip_numpy(0)[:, :, 1:4].view(np.uint16))
+                conversion = binding.make_conversion(binding.CHANNEL_FORMAT_UNORM8, 6)
+                fused, _ = texture_set.decompress_converted(conversion, use_int8)
+                texture_set.decompress(use_int8)
+                for mip in (0, 1, geo.mips - 1):
+                    two_pass = texture_set.read_mip(mip, 0, 6, binding.CHANNEL_FORMAT_UNORM8)
+                    assert np.array_equal(fused[mip], two_pass), mip
+            texture_set.close()
+
+
 def test_live_reference_comparison(oracle):
     """Runs the unmodified reference decoder (oracle/_ref) on this GPU next to ours on a set the
     fixtures do not contain."""
