@@ -494,6 +494,51 @@ def run_profile_case(case: str) -> int:
     return 0
 
 
+def run_producers_case(side: int) -> int:
+    """Times the two encoder-side producers on their own: latent packing on a SIDE x SIDE grid of four
+    layers (algorithmic bytes per latent word: 8 read + 2 written; the arrays are larger than L2 from
+    SIDE = 4096 up) against the HBM copy peak, and one network quantisation (a single CTA: latency).
+    With the reference library present, its own kernels are timed beside them through the harness's
+    host-to-host calls (copies included, so only an upper bound on their kernel time).  Prints a
+    plain line per producer, not the benchmark's JSON line."""
+    import numpy as np
+    import torch
+
+    entry.load_package()
+    from rtxntc_library_b200 import binding
+
+    layers, texels = 4, side * side
+    stride = texels * 2
+    latents = (torch.randint(0, 16, (layers * stride * 2,), device="cuda", dtype=torch.int32).to(torch.float16) / 15.0).contiguous()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(13):
+        start.record()
+        packed = binding.pack_latents(latents, side, side, layers, stride)
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    ms = float(np.median(times[3:]))
+    peak, source = measured_peak_gbs()
+    gbs = 10.0 * texels * layers / ms / 1e6
+    print("pack latents %dx%dx%d: %.3f ms, %.0f GB/s algorithmic = %.2f of %s HBM peak %.0f GB/s (%d words)"
+          % (side, side, layers, ms, gbs, gbs / peak, source, peak, packed.numel()))
+
+    rng = np.random.default_rng(1)
+    weights = torch.from_numpy(rng.normal(0, 0.3, binding.NETWORK_WEIGHT_COUNT).astype(np.float16)).cuda()
+    biases = torch.from_numpy(rng.normal(0, 0.5, binding.NETWORK_COLUMN_COUNT).astype(np.float16)).cuda()
+    for mode, name in ((binding.WEIGHTS_INT8, "int8"), (binding.WEIGHTS_FP8, "fp8")):
+        times = []
+        for _ in range(13):
+            start.record()
+            binding.quantize_network(weights, biases, mode)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop))
+        print("quantize network %s: %.1f us per call (blob allocation included)" % (name, 1000 * float(np.median(times[3:]))))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -507,9 +552,13 @@ def main() -> int:
                         help="reference (default): binary16 accumulation, the reference decoder's bits; exact: exact accumulation")
     parser.add_argument("--profile-case", metavar="SIZE:MODE:LAUNCHES[:NUMERICS]",
                         help="only launch the decode kernel LAUNCHES times on a small SIZE^2 set (fp8 or int8) and exit")
+    parser.add_argument("--producers-case", metavar="SIDE", type=int,
+                        help="only time latent packing on a SIDE x SIDE x 4 grid and one network quantisation, and exit")
     args = parser.parse_args()
     if args.profile_case:
         return run_profile_case(args.profile_case)
+    if args.producers_case:
+        return run_producers_case(args.producers_case)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:

@@ -335,6 +335,40 @@ typedef struct NtcbConvertParams
 } NtcbConvertParams;
 int ntcb_convert_channels(const NtcbConvertParams* params, void* stream);
 
+/* ---- Encoder-side producers of what the decoder consumes -------------------------------------- */
+
+/* Packs quantised fp16 latents into the 16-bit words the decode kernels read (four 4-bit codes per
+   word, the first feature in the low bits; one width x height plane of words per layer, the layers
+   one after another).  Replaces cuda::PackLatents (src/Quantizer.cu:497-541; called from
+   TextureSet::FinalizeCompression, src/TextureSet.cpp:1589-1602) with the same input layout:
+   `latents` holds, for layer z and texel t = y * width + x, features 0 and 1 at element
+   z * latentStride * 2 + t * 2 and features 2 and 3 `latentStride` elements further on.  Each code
+   is round(15 * clamp(value, 0, 1)).  Both pointers are device memory; queued on `stream`. */
+int ntcb_pack_latents(const void* latents, int width, int height, int numLayers, size_t latentStride,
+    void* packed, void* stream);
+
+/* Quantises the decoder network from fp16 to a GenericInt8 or GenericFP8 blob, the form containers
+   store and ntcb_stage_network* read.  Replaces cuda::QuantizeNetwork (src/Quantizer.cu:90-325;
+   called from src/TextureSet.cpp:1610-1633).  Int8: per output column, codes round(w * 127.5 /
+   max|w|), a float scale that folds the input or activation step (and, for the output layer, the
+   channel's optimal-to-linear scale), and the bias as an integer multiple of that scale.  FP8:
+   layers 0-2 rounded to e4m3 with their fp16 biases kept; the output layer as in Int8.
+   All pointers but outputScale / outputBias are device memory. */
+typedef struct NtcbQuantizeNetworkParams
+{
+    const void* weights;     /* fp16; per layer outputs x inputs values, the inputs of one output together
+                                (the order of the blob's weight section): 3072 + 3072 + 1536 + 512 values */
+    const void* biases;      /* fp16; 64 + 48 + 32 + 16 values */
+    const float* outputScale; /* host, 16 values: optimal-to-linear scale per output channel; NULL = 1 */
+    const float* outputBias;  /* host, 16 values: optimal-to-linear bias per output channel; NULL = 0 */
+    int32_t weightMode;      /* NTCB_WEIGHTS_INT8 or NTCB_WEIGHTS_FP8 */
+    int32_t reserved;
+    void* blob;              /* NTCB_INT8_BLOB_BYTES or NTCB_FP8_BLOB_BYTES */
+    void* roundedWeights;    /* optional, fp16, same order as `weights`: the weights as the decoder will apply
+                                them (the reference overwrites its fp16 copy with these) */
+} NtcbQuantizeNetworkParams;
+int ntcb_quantize_network(const NtcbQuantizeNetworkParams* params, void* stream);
+
 /* Size of the staging area built into the library for ntcb_read_channels_to_host_noalloc. */
 #define NTCB_NOALLOC_STAGING_BYTES (4u << 20)
 

@@ -2,7 +2,8 @@
 # TEST INFRASTRUCTURE ONLY.
 #
 # Builds the UNMODIFIED reference library (LibNTC) from its own sources, where they lie, into
-# oracle/_ref/libntc_ref.so together with the plain-C driver oracle/ref_harness.cpp.  The result is
+# oracle/_ref/libntc_ref.so together with the plain-C drivers oracle/ref_harness.cpp and
+# oracle/ref_harness_producers.cu.  The result is
 # the parity checker and the benchmark's reference arm; it is never linked into the product.
 #
 # The reference's own CMake build needs network access (FetchContent) and the libdeflate submodule,
@@ -56,22 +57,29 @@ compile_cu() {
         -rdc=true -Xcompiler -fPIC -Xcompiler -fno-strict-aliasing $DEFS $INCS \
         -c "$REF/src/$1.cu" -o "$OBJ/$1.cu.o"
 }
+compile_harness_cu() {
+    "$NVCC" -arch=sm_100 -std=c++17 -O3 --expt-relaxed-constexpr --extended-lambda --use_fast_math \
+        -rdc=true -Xcompiler -fPIC -Xcompiler -fno-strict-aliasing $DEFS $INCS \
+        -c "$HERE/$1.cu" -o "$OBJ/$1.cu.o"
+}
 compile_cpp() {
     "$CXX" -std=c++17 -O2 -fPIC -fno-strict-aliasing $DEFS $INCS -c "$2" -o "$OBJ/$1.o"
 }
-export -f compile_cu compile_cpp
-export NVCC CXX DEFS INCS OBJ REF
+export -f compile_cu compile_harness_cu compile_cpp
+export NVCC CXX DEFS INCS OBJ REF HERE
 
 {
     for s in $CU_SOURCES; do echo "compile_cu $s"; done
     for s in $CPP_SOURCES; do echo "compile_cpp $s $REF/src/$s.cpp"; done
     echo "compile_cpp gdeflate_stub $HERE/gdeflate_stub.cpp"
     echo "compile_cpp ref_harness $HERE/ref_harness.cpp"
+    echo "compile_harness_cu ref_harness_producers"
 } | xargs -P "$JOBS" -I{} bash -c '{}'
 
 OBJECTS=""
 for s in $CU_SOURCES; do OBJECTS="$OBJECTS $OBJ/$s.cu.o"; done
 for s in $CPP_SOURCES gdeflate_stub ref_harness; do OBJECTS="$OBJECTS $OBJ/$s.o"; done
+OBJECTS="$OBJECTS $OBJ/ref_harness_producers.cu.o"
 
 "$NVCC" -arch=sm_100 -shared -o "$OUT/libntc_ref.so" $OBJECTS -lcudart_static -lpthread -ldl -lrt
 echo "built $OUT/libntc_ref.so"

@@ -6,6 +6,7 @@
  */
 #include "ntc_oracle.h"
 
+#include <float.h>
 #include <immintrin.h>
 #include <math.h>
 #include <stdlib.h>
@@ -891,6 +892,157 @@ int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* p, uint8_
                 write_component(dst, ch, p->channelFormat, dstSpace, value, dither);
             }
         }
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------- */
+/* Encoder-side producers (src/Quantizer.cu)                                                    */
+/* ------------------------------------------------------------------------------------------- */
+
+static float flush_denormal(float x)
+{
+    return fabsf(x) < 1.17549435e-38f ? copysignf(0.f, x) : x;
+}
+
+/* QuantizeValue(value, 4), src/Quantizer.cu:481-487.  std::min(1.f, NaN) is 1. */
+static uint32_t latent_code(uint16_t bits)
+{
+    float value = h2f(bits);
+    value = (value < 1.f) ? value : 1.f;
+    value = (0.f < value) ? value : 0.f;
+    const float step = 1.f / 15.f;
+    return (uint32_t)roundf(value / step);
+}
+
+/* PackLatentsKernel, src/Quantizer.cu:497-527. */
+int ntco_pack_latents(const uint16_t* latents, int width, int height, int numLayers, size_t latentStride, uint16_t* packed)
+{
+    if (!latents || !packed || width <= 0 || height <= 0 || numLayers <= 0)
+        return -1;
+    const size_t texels = (size_t)width * (size_t)height;
+    for (int z = 0; z < numLayers; ++z)
+        for (size_t t = 0; t < texels; ++t)
+        {
+            const uint16_t* src = latents + (size_t)z * latentStride * 2 + t * 2;
+            packed[(size_t)z * texels + t] = (uint16_t)(latent_code(src[0]) | (latent_code(src[1]) << 4)
+                | (latent_code(src[latentStride]) << 8) | (latent_code(src[latentStride + 1]) << 12));
+        }
+    return 0;
+}
+
+static const int kProducerInputs[4] = {48, 64, 48, 32};
+static const int kProducerOutputs[4] = {64, 48, 32, 16};
+
+/* QuantizeColumnInt8, src/Quantizer.cu:90-208.  The reference's divisions are the GPU's approximate
+   ones (it is built with --use_fast_math); exact divisions stand in for them here, so a code or an
+   integer bias whose unrounded value lies within a few units in the last place of a tie, and the
+   last bits of the first layer's scales, can differ from what the GPU produces. */
+static void quantize_column_int8(int layer, const uint16_t* weights, uint16_t bias, int8_t* codes, uint16_t* rounded,
+    float* scaleOut, int32_t* biasOut, float outputScale, float outputBias)
+{
+    const int rows = kProducerInputs[layer];
+    float low = FLT_MAX, high = FLT_MIN;
+    for (int r = 0; r < rows; ++r)
+    {
+        const float w = h2f(weights[r]);
+        low = (w < low) ? w : low;
+        high = (high < w) ? w : high;
+    }
+    const float limit = fmaxf(fabsf(high), fabsf(low));
+    const float inverseLimit = flush_denormal(1.f / limit);
+    const float scale = 127.5f, inverseScale = 1.f / 127.5f;
+    const float ratio = flush_denormal(scale / limit);
+    int sum = 0;
+    for (int r = 0; r < rows; ++r)
+    {
+        const float w = h2f(weights[r]);
+        float q = (r & 1) ? roundf(flush_denormal(w * ratio)) : roundf(flush_denormal(flush_denormal(w * scale) * inverseLimit));
+        q = (127.f < q) ? 127.f : q;   /* std::min / std::max keep a NaN first operand */
+        q = (q < -127.f) ? -127.f : q;
+        codes[r] = isnan(q) ? 0 : (int8_t)q;
+        sum += codes[r];
+        if (rounded)
+            rounded[r] = f2h(flush_denormal(flush_denormal(q * limit) * inverseScale));
+    }
+
+    float layerScale = flush_denormal(limit * inverseScale);
+    float layerBias = h2f(bias);
+    if (layer == 0)
+        layerScale = flush_denormal(layerScale / 127.5f);
+    else
+    {
+        const float activationStep = 3.1875f / 255.f;
+        const int activationBias = -113;
+        layerScale = flush_denormal(layerScale * activationStep);
+        layerBias = flush_denormal(fmaf(-(float)(sum * activationBias), layerScale, layerBias));
+        if (layer == 3)
+        {
+            layerScale = flush_denormal(layerScale * outputScale);
+            layerBias = flush_denormal(fmaf(layerBias, outputScale, outputBias));
+        }
+    }
+    int32_t integerBias;
+    if (layerScale == 0.f)
+    {
+        layerScale = 1.f / 65536.f;
+        integerBias = (int32_t)roundf(layerBias * 65536.f);
+        for (int r = 0; r < rows; ++r)
+            codes[r] = 0;
+    }
+    else
+        integerBias = (int32_t)roundf(layerBias / layerScale);
+    *scaleOut = layerScale;
+    *biasOut = integerBias;
+}
+
+/* QuantizeNetworkInt8Kernel / QuantizeNetworkFP8Kernel, src/Quantizer.cu:254-303; the blob's layout
+   is the one of src/WeightLayout.cpp:142-268. */
+int ntco_quantize_network(const uint16_t* weights, const uint16_t* biases, const float* outputScale, const float* outputBias,
+    int useFP8, uint8_t* blob, uint16_t* roundedWeights)
+{
+    if (!weights || !biases || !blob)
+        return -1;
+    const size_t weightBytes = 48 * 64 + 64 * 48 + 48 * 32 + 32 * 16;
+    size_t weightOffset = 0, columnOffset = 0;
+    for (int layer = 0; layer < 4; ++layer)
+    {
+        const int rows = kProducerInputs[layer], cols = kProducerOutputs[layer];
+        for (int col = 0; col < cols; ++col)
+        {
+            const uint16_t* w = weights + weightOffset + (size_t)col * rows;
+            uint16_t* rounded = roundedWeights ? roundedWeights + weightOffset + (size_t)col * rows : NULL;
+            uint8_t* codes = blob + weightOffset + (size_t)col * rows;
+            const uint16_t bias = biases[columnOffset + col];
+            const float os = outputScale ? outputScale[col & 15] : 1.f, ob = outputBias ? outputBias[col & 15] : 0.f;
+            float scaleValue;
+            int32_t biasValue;
+            if (!useFP8)
+            {
+                quantize_column_int8(layer, w, bias, (int8_t*)codes, rounded, &scaleValue, &biasValue, os, ob);
+                memcpy(blob + weightBytes + 4 * (columnOffset + col), &scaleValue, 4);
+                memcpy(blob + weightBytes + 4 * 160 + 4 * (columnOffset + col), &biasValue, 4);
+            }
+            else if (layer < 3)
+            {
+                for (int r = 0; r < rows; ++r) /* QuantizeColumnFP8, src/Quantizer.cu:210-252 */
+                {
+                    codes[r] = ntco_half_to_e4m3(w[r]);
+                    if (rounded)
+                        rounded[r] = f2h(ntco_e4m3_to_float(codes[r]));
+                }
+                memcpy(blob + weightBytes + 2 * (columnOffset + col), &bias, 2);
+            }
+            else
+            {
+                quantize_column_int8(layer, w, bias, (int8_t*)codes, rounded, &scaleValue, &biasValue, os, ob);
+                uint8_t* tail = blob + weightBytes + 2 * 144;
+                memcpy(tail + 4 * col, &scaleValue, 4);
+                memcpy(tail + 64 + 4 * col, &biasValue, 4);
+            }
+        }
+        weightOffset += (size_t)rows * cols;
+        columnOffset += (size_t)cols;
     }
     return 0;
 }

@@ -126,6 +126,17 @@ typedef struct NtcoReadChannels
 } NtcoReadChannels;
 int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* params, uint8_t* out);
 
+/* PackLatentsKernel (src/Quantizer.cu:497-527): quantised fp16 latents (bit patterns) to 4-bit
+   words; `packed` receives width * height * numLayers words.  Returns 0, or -1 on invalid arguments. */
+int ntco_pack_latents(const uint16_t* latents, int width, int height, int numLayers, size_t latentStride, uint16_t* packed);
+
+/* QuantizeNetwork (src/Quantizer.cu:90-325): fp16 weights (per layer outputs x inputs, the inputs
+   of one output together) and 160 fp16 biases to a GenericInt8 (9472 bytes) or GenericFP8 (8608
+   bytes) blob; `roundedWeights` (optional) receives the fp16 weights after quantisation.  Exact
+   divisions stand in for the GPU's approximate ones: see the note in the source. */
+int ntco_quantize_network(const uint16_t* weights, const uint16_t* biases, const float* outputScale, const float* outputBias,
+    int useFP8, uint8_t* blob, uint16_t* roundedWeights);
+
 /* Element helpers exposed for unit tests. */
 uint16_t ntco_float_to_half(float value);
 float ntco_half_to_float(uint16_t bits);

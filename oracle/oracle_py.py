@@ -85,6 +85,30 @@ def read_channels(texels: np.ndarray, channel_format: int, first_channel: int = 
     return out
 
 
+def pack_latents(latents: np.ndarray, width: int, height: int, num_layers: int, latent_stride: int) -> np.ndarray:
+    """PackLatents restated on the CPU: a flat float16 array in the reference's latent layout to
+    uint16 words [num_layers][height][width]."""
+    latents = np.ascontiguousarray(latents, dtype=np.float16)
+    out = np.empty((num_layers, height, width), dtype=np.uint16)
+    if oracle_lib().ntco_pack_latents(latents.ctypes.data, width, height, num_layers, latent_stride, out.ctypes.data) != 0:
+        raise ValueError("ntco_pack_latents rejected its arguments")
+    return out
+
+
+def quantize_network(weights: np.ndarray, biases: np.ndarray, use_fp8: bool, output_scale=None, output_bias=None):
+    """QuantizeNetwork restated on the CPU; returns (blob bytes, rounded fp16 weights)."""
+    weights = np.ascontiguousarray(weights, dtype=np.float16)
+    biases = np.ascontiguousarray(biases, dtype=np.float16)
+    scale = np.ascontiguousarray(np.ones(16) if output_scale is None else output_scale, dtype=np.float32)
+    bias = np.ascontiguousarray(np.zeros(16) if output_bias is None else output_bias, dtype=np.float32)
+    blob = np.zeros(8608 if use_fp8 else 9472, dtype=np.uint8)
+    rounded = np.empty_like(weights)
+    if oracle_lib().ntco_quantize_network(weights.ctypes.data, biases.ctypes.data, scale.ctypes.data, bias.ctypes.data,
+                                          int(use_fp8), blob.ctypes.data, rounded.ctypes.data) != 0:
+        raise ValueError("ntco_quantize_network rejected its arguments")
+    return blob.tobytes(), rounded
+
+
 def build_oracle() -> None:
     subprocess.run(["make", "-s", "-C", HERE, "libntc_oracle.so"], check=True)
 
@@ -101,6 +125,10 @@ def oracle_lib():
         lib.ntco_sample.argtypes = [ctypes.POINTER(_TextureSet), ctypes.POINTER(Options), ctypes.c_void_p,
                                     ctypes.c_size_t, ctypes.c_void_p]
         lib.ntco_read_channels.argtypes = [ctypes.c_void_p, ctypes.POINTER(ReadChannels), ctypes.c_void_p]
+        lib.ntco_pack_latents.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t,
+                                          ctypes.c_void_p]
+        lib.ntco_quantize_network.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
         lib.ntco_float_to_half.restype = ctypes.c_uint16
         lib.ntco_float_to_half.argtypes = [ctypes.c_float]
         lib.ntco_half_to_float.restype = ctypes.c_float
@@ -201,6 +229,11 @@ def reference_lib():
                                              ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t,
                                              ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_void_p]
         lib.ntcref_close.argtypes = [ctypes.c_void_p]
+        lib.ntcref_producers_last_error.restype = ctypes.c_char_p
+        lib.ntcref_pack_latents.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p,
+                                            ctypes.c_size_t, ctypes.c_void_p]
+        lib.ntcref_quantize_network.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
         _ref = lib
     return _ref
 
@@ -212,6 +245,34 @@ def reference_probe(container: bytes) -> List[int]:
     if rc != 0:
         raise RuntimeError("reference loader rejected the container: %s" % lib.ntcref_last_error().decode())
     return list(out)
+
+
+def reference_pack_latents(latents: np.ndarray, width: int, height: int, num_layers: int, latent_stride: int) -> np.ndarray:
+    """The reference's own PackLatents kernel on a flat float16 array; uint16 [layers][height][width]."""
+    latents = np.ascontiguousarray(latents, dtype=np.float16)
+    out = np.empty((num_layers, height, width), dtype=np.uint16)
+    lib = reference_lib()
+    rc = lib.ntcref_pack_latents(width, height, num_layers, latent_stride, latents.ctypes.data, latents.size, out.ctypes.data)
+    if rc != 0:
+        raise RuntimeError("reference PackLatents failed: %s" % lib.ntcref_producers_last_error().decode())
+    return out
+
+
+def reference_quantize_network(weights: np.ndarray, biases: np.ndarray, use_fp8: bool, output_scale=None, output_bias=None):
+    """The reference's own QuantizeNetwork kernel.  `weights` / `biases`: float16, the blob's order.
+    Returns (blob bytes, rounded fp16 weights)."""
+    weights = np.ascontiguousarray(weights, dtype=np.float16)
+    biases = np.ascontiguousarray(biases, dtype=np.float16)
+    scale = np.ascontiguousarray(np.ones(16) if output_scale is None else output_scale, dtype=np.float32)
+    bias = np.ascontiguousarray(np.zeros(16) if output_bias is None else output_bias, dtype=np.float32)
+    blob = np.zeros(8608 if use_fp8 else 9472, dtype=np.uint8)
+    rounded = np.empty_like(weights)
+    lib = reference_lib()
+    rc = lib.ntcref_quantize_network(weights.ctypes.data, biases.ctypes.data, scale.ctypes.data, bias.ctypes.data,
+                                     int(use_fp8), blob.ctypes.data, blob.size, rounded.ctypes.data)
+    if rc != 0:
+        raise RuntimeError("reference QuantizeNetwork failed: %s" % lib.ntcref_producers_last_error().decode())
+    return blob.tobytes(), rounded
 
 
 class ReferenceDecoder:

@@ -13,7 +13,7 @@ from typing import Optional, Sequence, Tuple
 
 import numpy as np
 
-from .geometry import Geometry
+from .geometry import FP8_BLOB_BYTES, INT8_BLOB_BYTES, Geometry
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.path.join(_HERE, "libntcb200.so")
@@ -160,6 +160,9 @@ def lib():
             ctypes.c_void_p, ctypes.POINTER(DecompressionStats), ctypes.c_int, ctypes.POINTER(OutputConversion), ctypes.c_int,
             ctypes.c_void_p, ctypes.c_size_t]
         handle.ntcb_convert_channels.argtypes = [ctypes.POINTER(ConvertParams), ctypes.c_void_p]
+        handle.ntcb_pack_latents.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t,
+                                             ctypes.c_void_p, ctypes.c_void_p]
+        handle.ntcb_quantize_network.argtypes = [ctypes.POINTER(QuantizeNetworkParams), ctypes.c_void_p]
         handle.ntcb_texture_set_device_mip.argtypes = [
             ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t)]
         handle.ntcb_texture_set_synchronize.argtypes = [ctypes.c_void_p]
@@ -262,6 +265,65 @@ def convert_channels(texels, conversion: OutputConversion, layout: int = LAYOUT_
         stream = torch.cuda.current_stream(texels.device).cuda_stream
         check(lib().ntcb_convert_channels(ctypes.byref(params), ctypes.c_void_p(stream)))
     return out
+
+
+class QuantizeNetworkParams(ctypes.Structure):
+    _fields_ = [("weights", ctypes.c_void_p), ("biases", ctypes.c_void_p),
+                ("outputScale", ctypes.POINTER(ctypes.c_float)), ("outputBias", ctypes.POINTER(ctypes.c_float)),
+                ("weightMode", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("blob", ctypes.c_void_p), ("roundedWeights", ctypes.c_void_p)]
+
+
+NETWORK_WEIGHT_COUNT = 48 * 64 + 64 * 48 + 48 * 32 + 32 * 16
+NETWORK_COLUMN_COUNT = 64 + 48 + 32 + 16
+
+
+def pack_latents(latents, width: int, height: int, num_layers: int, latent_stride: int):
+    """Packs quantised fp16 latents (a flat CUDA float16 tensor in the reference's layout: layer z,
+    texel t has features 0-1 at z * latent_stride * 2 + t * 2 and features 2-3 latent_stride
+    elements later) into 16-bit words; returns a CUDA int16 tensor [num_layers][height][width]."""
+    import torch
+
+    needed = (num_layers - 1) * latent_stride * 2 + latent_stride + width * height * 2
+    if latents.dtype != torch.float16 or latents.numel() < needed:
+        raise ValueError(f"latents must be float16 with at least {needed} elements")
+    out = torch.empty((num_layers, height, width), dtype=torch.int16, device=latents.device)
+    with torch.cuda.device(latents.device):
+        stream = torch.cuda.current_stream(latents.device).cuda_stream
+        check(lib().ntcb_pack_latents(ctypes.c_void_p(latents.data_ptr()), width, height, num_layers, latent_stride,
+                                      ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(stream)))
+    return out
+
+
+def quantize_network(weights, biases, weight_mode: int, output_scale=None, output_bias=None, want_rounded: bool = False):
+    """Quantises fp16 network weights (CUDA float16 tensors: NETWORK_WEIGHT_COUNT weights, per layer
+    outputs x inputs with one output's inputs together, and NETWORK_COLUMN_COUNT biases) to a
+    GenericInt8 / GenericFP8 blob.  Returns the blob as a CUDA uint8 tensor, and with `want_rounded`
+    also the fp16 weights as the decoder will apply them."""
+    import torch
+
+    if weights.dtype != torch.float16 or weights.numel() != NETWORK_WEIGHT_COUNT:
+        raise ValueError("weights must be float16 with NETWORK_WEIGHT_COUNT elements")
+    if biases.dtype != torch.float16 or biases.numel() != NETWORK_COLUMN_COUNT:
+        raise ValueError("biases must be float16 with NETWORK_COLUMN_COUNT elements")
+    blob_bytes = INT8_BLOB_BYTES if weight_mode == WEIGHTS_INT8 else FP8_BLOB_BYTES
+    blob = torch.zeros(blob_bytes, dtype=torch.uint8, device=weights.device)
+    rounded = torch.empty_like(weights) if want_rounded else None
+    params = QuantizeNetworkParams()
+    params.weights, params.biases = weights.data_ptr(), biases.data_ptr()
+    keep = []
+    for name, values in (("outputScale", output_scale), ("outputBias", output_bias)):
+        if values is not None:
+            array = (ctypes.c_float * 16)(*[float(v) for v in values])
+            keep.append(array)
+            setattr(params, name, array)
+    params.weightMode = weight_mode
+    params.blob = blob.data_ptr()
+    params.roundedWeights = rounded.data_ptr() if want_rounded else None
+    with torch.cuda.device(weights.device):
+        stream = torch.cuda.current_stream(weights.device).cuda_stream
+        check(lib().ntcb_quantize_network(ctypes.byref(params), ctypes.c_void_p(stream)))
+    return (blob, rounded) if want_rounded else blob
 
 
 class ResidentTextureSet:

@@ -1,0 +1,327 @@
+// The two small encoder-side producers of the data the decode kernels consume: 4-bit latent words
+// from quantised fp16 latents, and the GenericInt8 / GenericFP8 network blobs from fp16 weights.
+// They replace cuda::PackLatents (src/Quantizer.cu:497-541) and cuda::QuantizeNetwork
+// (src/Quantizer.cu:90-325), which the reference runs at the end of a compression session
+// (src/TextureSet.cpp:1589-1633).
+//
+// The reference is built with --use_fast_math (src/CMakeLists.txt:33): its float divisions are the
+// approximate hardware form and everything flushes denormals.  The same forms are spelled out here
+// so that the results do not depend on this library's compiler flags.
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "error.h"
+#include "ntcb.h"
+#include "output_convert.cuh"
+
+namespace ntcb
+{
+namespace
+{
+
+// ---------------------------------------------------------------------------------------------
+// Latent packing
+
+// QuantizeValue(value, 4) of src/Quantizer.cu:481-487: clamp to [0, 1], divide by the step 1/15
+// (as a float), round half away from zero.  The quotient of an fp16 value and that step lies at
+// least 2^-16 away from every tie except at 0.5, where every form of the division lands just below
+// 7.5; so the approximate division and the exact one give the same code for every input.  The
+// reference's std::min(1.f, NaN) is 1, so NaN packs as 15; it is tested on the bits here because a
+// min / max clamp to [0, 1] may be compiled to a saturating operation, which turns NaN into 0.
+__device__ __forceinline__ uint32_t LatentCode(__half value)
+{
+    const float step = 1.f / 15.f;
+    if ((__half_as_ushort(value) & 0x7fffu) > 0x7c00u)
+        return 15u;
+    const float v = fmaxf(0.f, fminf(1.f, __half2float(value)));
+    return uint32_t(roundf(ApproxDivide(v, step)));
+}
+
+__device__ __forceinline__ __half2 AsHalf2Bits(uint32_t bits)
+{
+    return *reinterpret_cast<const __half2*>(&bits);
+}
+
+__device__ __forceinline__ uint32_t LatentWord(__half2 first, __half2 second)
+{
+    return LatentCode(__low2half(first)) | (LatentCode(__high2half(first)) << 4)
+         | (LatentCode(__low2half(second)) << 8) | (LatentCode(__high2half(second)) << 12);
+}
+
+// One thread per latent texel and layer; any width, stride and alignment.
+__global__ void PackLatentsKernel(const __half* __restrict__ latents, uint64_t texels, int layers, uint64_t latentStride,
+    uint16_t* __restrict__ packed)
+{
+    const uint64_t total = texels * uint64_t(layers);
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x)
+    {
+        const uint64_t layer = i / texels, texel = i - layer * texels;
+        const __half* src = latents + layer * latentStride * 2 + texel * 2;
+        const __half2 first = __halves2half2(src[0], src[1]);
+        const __half2 second = __halves2half2(src[latentStride], src[latentStride + 1]);
+        packed[i] = uint16_t(LatentWord(first, second));
+    }
+}
+
+// Eight texels per thread: two 32-byte reads, one 16-byte store.  Needs texels and latentStride to
+// be multiples of 8 and both pointers 16-byte aligned.
+__global__ void PackLatentsWideKernel(const uint4* __restrict__ latents, uint64_t texelGroups, int layers,
+    uint64_t strideVectors, uint4* __restrict__ packed)
+{
+    const uint64_t total = texelGroups * uint64_t(layers);
+    for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < total; i += uint64_t(gridDim.x) * blockDim.x)
+    {
+        const uint64_t layer = i / texelGroups, group = i - layer * texelGroups;
+        const uint4* src = latents + layer * strideVectors * 2 + group * 2; // 8 texels x 2 halves = 2 vectors
+        const uint4 a0 = __ldcs(src), a1 = __ldcs(src + 1);
+        const uint4 b0 = __ldcs(src + strideVectors), b1 = __ldcs(src + strideVectors + 1);
+        const uint32_t a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const uint32_t b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        uint32_t words[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+        {
+            const uint32_t lo = LatentWord(AsHalf2Bits(a[2 * k]), AsHalf2Bits(b[2 * k]));
+            const uint32_t hi = LatentWord(AsHalf2Bits(a[2 * k + 1]), AsHalf2Bits(b[2 * k + 1]));
+            words[k] = lo | (hi << 16);
+        }
+        __stcs(packed + i, make_uint4(words[0], words[1], words[2], words[3]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Network quantisation
+
+constexpr int kLayers = 4;
+__host__ __device__ constexpr int LayerInputs(int layer) { return layer == 0 ? 48 : layer == 1 ? 64 : layer == 2 ? 48 : 32; }
+__host__ __device__ constexpr int LayerOutputs(int layer) { return layer == 0 ? 64 : layer == 1 ? 48 : layer == 2 ? 32 : 16; }
+constexpr int kColumns = 64 + 48 + 32 + 16;
+constexpr int kWeights = 48 * 64 + 64 * 48 + 48 * 32 + 32 * 16;
+
+struct QuantizeArguments
+{
+    const __half* weights; // per layer: outputs x inputs, one output's inputs together (the blob's order)
+    const __half* biases;  // kColumns values, the layers one after another
+    uint8_t* blob;
+    __half* rounded;       // optional: the weights as the decoder will see them, same order as `weights`
+    float outputScale[16], outputBias[16];
+    int fp8;
+};
+
+// roundf: half away from zero, exact.
+__device__ __forceinline__ float RoundAway(float x)
+{
+    return roundf(x);
+}
+
+// One output column quantised to int8 with a per-column scale and an integer bias
+// (QuantizeColumnInt8, src/Quantizer.cu:90-208).
+__device__ void QuantizeColumnInt8(int layer, int column, const __half* weights, float bias, int8_t* codes, __half* rounded,
+    float* scaleOut, int32_t* biasOut, float outputScale, float outputBias)
+{
+    const int rows = LayerInputs(layer);
+    float low = 3.402823466e+38f, high = 1.175494351e-38f; // the reference's starting values
+    for (int r = 0; r < rows; ++r)
+    {
+        const float w = __half2float(weights[r]);
+        low = fminf(low, w);
+        high = fmaxf(high, w);
+    }
+    const float limit = fmaxf(fabsf(high), fabsf(low));
+    float inverseLimit;
+    asm("rcp.rn.ftz.f32 %0, %1;" : "=f"(inverseLimit) : "f"(limit));
+
+    const float scale = 127.5f, inverseScale = 1.f / 127.5f;
+    const float ratio = ApproxDivide(scale, limit); // the odd rows use scale / limit, the even ones scale * (1 / limit)
+    int sum = 0;
+    for (int r = 0; r < rows; ++r)
+    {
+        const float w = __half2float(weights[r]);
+        float q = (r & 1) ? RoundAway(MulFtz(w, ratio)) : RoundAway(MulFtz(MulFtz(w, scale), inverseLimit));
+        q = fmaxf(fminf(q, 127.f), -127.f);
+        codes[r] = int8_t(q);
+        sum += int(q);
+        if (rounded)
+            rounded[r] = __float2half_rn(MulFtz(MulFtz(q, limit), inverseScale));
+    }
+
+    float layerScale = MulFtz(limit, inverseScale);
+    float layerBias = bias;
+    if (layer == 0)
+        layerScale = ApproxDivide(layerScale, 127.5f); // tin::InputQuant::scale
+    else
+    {
+        const float activationStep = 3.1875f / 255.f; // tin::ActHGELUClamp::step
+        const int activationBias = -113;             // tin::ActHGELUClamp::bias
+        layerScale = MulFtz(layerScale, activationStep);
+        layerBias = FmaFtz(-float(sum * activationBias), layerScale, layerBias);
+        if (layer == kLayers - 1)
+        {
+            layerScale = MulFtz(layerScale, outputScale);
+            layerBias = FmaFtz(layerBias, outputScale, outputBias);
+        }
+    }
+
+    // (output * scale + bias) becomes ((output + integer bias) * scale); a zero scale (a constant
+    // image channel) is replaced by 2^-16 with zero weights.
+    int integerBias;
+    if (layerScale == 0.f)
+    {
+        layerScale = 1.f / 65536.f;
+        integerBias = int(RoundAway(MulFtz(layerBias, 65536.f)));
+        for (int r = 0; r < rows; ++r)
+            codes[r] = 0;
+    }
+    else
+        integerBias = int(RoundAway(ApproxDivide(layerBias, layerScale)));
+    *scaleOut = layerScale;
+    *biasOut = integerBias;
+}
+
+// One output column rounded to e4m3; the bias stays fp16 (QuantizeColumnFP8, src/Quantizer.cu:210-252).
+__device__ void QuantizeColumnFp8(int rows, const __half* weights, uint8_t* codes, __half* rounded)
+{
+    for (int r = 0; r < rows; r += 2)
+    {
+        const __half2 pair = __halves2half2(weights[r], weights[r + 1]);
+        const __nv_fp8x2_e4m3 q(pair);
+        codes[r] = uint8_t(q.__x & 0xff);
+        codes[r + 1] = uint8_t(q.__x >> 8);
+        if (rounded)
+        {
+            const __half2 back = __half2(q);
+            rounded[r] = __low2half(back);
+            rounded[r + 1] = __high2half(back);
+        }
+    }
+}
+
+// One thread per output column, the columns of all layers one after another: a single CTA.
+__global__ void __launch_bounds__(kColumns) QuantizeNetworkKernel(const QuantizeArguments args)
+{
+    int column = threadIdx.x, layer = 0, weightOffset = 0, columnOffset = 0;
+    while (column >= LayerOutputs(layer))
+    {
+        column -= LayerOutputs(layer);
+        columnOffset += LayerOutputs(layer);
+        weightOffset += LayerInputs(layer) * LayerOutputs(layer);
+        ++layer;
+    }
+    const int rows = LayerInputs(layer);
+    const __half* weights = args.weights + weightOffset + column * rows;
+    __half* rounded = args.rounded ? args.rounded + weightOffset + column * rows : nullptr;
+    uint8_t* codes = args.blob + weightOffset + column * rows;
+    const __half bias = args.biases[columnOffset + column];
+
+    if (!args.fp8)
+    {
+        // weights, then the scales of all layers, then the integer biases (src/WeightLayout.cpp:184-255)
+        float* scales = reinterpret_cast<float*>(args.blob + kWeights) + columnOffset + column;
+        int32_t* biases = reinterpret_cast<int32_t*>(args.blob + kWeights + 4 * kColumns) + columnOffset + column;
+        QuantizeColumnInt8(layer, column, weights, __half2float(bias), reinterpret_cast<int8_t*>(codes), rounded, scales, biases,
+            args.outputScale[column & 15], args.outputBias[column & 15]);
+    }
+    else if (layer < kLayers - 1)
+    {
+        // weights, then the fp16 biases of layers 0-2, then the output layer's scales and integer biases
+        QuantizeColumnFp8(rows, weights, codes, rounded);
+        reinterpret_cast<__half*>(args.blob + kWeights)[columnOffset + column] = bias;
+    }
+    else
+    {
+        uint8_t* tail = args.blob + kWeights + 2 * (kColumns - 16);
+        QuantizeColumnInt8(layer, column, weights, __half2float(bias), reinterpret_cast<int8_t*>(codes), rounded,
+            reinterpret_cast<float*>(tail) + column, reinterpret_cast<int32_t*>(tail + 64) + column,
+            args.outputScale[column], args.outputBias[column]);
+    }
+}
+
+} // namespace
+} // namespace ntcb
+
+using namespace ntcb;
+
+extern "C" int ntcb_pack_latents(const void* latents, int width, int height, int numLayers, size_t latentStride,
+    void* packed, void* stream)
+{
+    if (!latents || !packed)
+    {
+        SetError("ntcb_pack_latents: latents and packed must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (width <= 0 || height <= 0 || numLayers <= 0)
+    {
+        SetError("ntcb_pack_latents: width (%d), height (%d) and numLayers (%d) must be positive.", width, height, numLayers);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    const uint64_t texels = uint64_t(width) * uint64_t(height);
+    if (latentStride < texels * 2)
+    {
+        SetError("ntcb_pack_latents: latentStride (%zu) must be at least 2 * width * height (%llu).", latentStride,
+            static_cast<unsigned long long>(texels * 2));
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    int device = 0, sms = 0;
+    cudaError_t error = cudaGetDevice(&device);
+    if (error == cudaSuccess)
+        error = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (error != cudaSuccess)
+        return CudaFailure("cudaDeviceGetAttribute", error);
+
+    const cudaStream_t cudaStream = static_cast<cudaStream_t>(stream);
+    const int threads = 256;
+    const bool wide = texels % 8 == 0 && latentStride % 8 == 0 && reinterpret_cast<uintptr_t>(latents) % 16 == 0
+                   && reinterpret_cast<uintptr_t>(packed) % 16 == 0;
+    const uint64_t items = (wide ? texels / 8 : texels) * uint64_t(numLayers);
+    const uint64_t wanted = (items + threads - 1) / threads;
+    // Whole waves of 8 CTAs of 256 threads per SM; eight waves, each CTA striding over the items,
+    // measured 6 % faster than a single resident wave (the tail of a wave overlaps the next one).
+    const uint64_t resident = uint64_t(sms) * 8 * 8;
+    const unsigned grid = unsigned(wanted < resident ? wanted : resident);
+    if (wide)
+        PackLatentsWideKernel<<<grid, threads, 0, cudaStream>>>(static_cast<const uint4*>(latents), texels / 8, numLayers,
+            latentStride / 8, static_cast<uint4*>(packed));
+    else
+        PackLatentsKernel<<<grid, threads, 0, cudaStream>>>(static_cast<const __half*>(latents), texels, numLayers, latentStride,
+            static_cast<uint16_t*>(packed));
+    CountLaunch();
+    error = cudaGetLastError();
+    if (error != cudaSuccess)
+        return CudaFailure("PackLatentsKernel", error);
+    ClearError();
+    return NTCB_OK;
+}
+
+extern "C" int ntcb_quantize_network(const NtcbQuantizeNetworkParams* params, void* stream)
+{
+    if (!params || !params->weights || !params->biases || !params->blob)
+    {
+        SetError("ntcb_quantize_network: params, weights, biases and blob must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (params->weightMode != NTCB_WEIGHTS_INT8 && params->weightMode != NTCB_WEIGHTS_FP8)
+    {
+        SetError("ntcb_quantize_network: unknown weight mode %d.", params->weightMode);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    QuantizeArguments args;
+    args.weights = static_cast<const __half*>(params->weights);
+    args.biases = static_cast<const __half*>(params->biases);
+    args.blob = static_cast<uint8_t*>(params->blob);
+    args.rounded = static_cast<__half*>(params->roundedWeights);
+    args.fp8 = params->weightMode == NTCB_WEIGHTS_FP8;
+    for (int c = 0; c < 16; ++c)
+    {
+        args.outputScale[c] = params->outputScale ? params->outputScale[c] : 1.f;
+        args.outputBias[c] = params->outputBias ? params->outputBias[c] : 0.f;
+    }
+    QuantizeNetworkKernel<<<1, kColumns, 0, static_cast<cudaStream_t>(stream)>>>(args);
+    CountLaunch();
+    const cudaError_t error = cudaGetLastError();
+    if (error != cudaSuccess)
+        return CudaFailure("QuantizeNetworkKernel", error);
+    ClearError();
+    return NTCB_OK;
+}
