@@ -539,6 +539,37 @@ def run_producers_case(side: int) -> int:
     return 0
 
 
+def run_block_compress_case(side: int) -> int:
+    """Times BC4 and BC5 encoding of a SIDE x SIDE mip of 12 interleaved fp16 channels (random texels
+    with smooth and noisy regions; larger than L2 from SIDE = 4096 up).  Prints a plain line per
+    format, not the benchmark's JSON line."""
+    import numpy as np
+    import torch
+
+    entry.load_package()
+    from rtxntc_library_b200 import binding
+
+    generator = torch.Generator(device="cuda").manual_seed(3)
+    base = torch.rand((side // 16, side // 16, 12), device="cuda", generator=generator)
+    texels = torch.nn.functional.interpolate(base.permute(2, 0, 1)[None], size=(side, side), mode="bilinear")[0].permute(1, 2, 0)
+    texels = (texels + 0.05 * torch.rand((side, side, 12), device="cuda", generator=generator)).clamp(0, 1).to(torch.float16).contiguous()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    peak, source = measured_peak_gbs()
+    for block_format, name, channels in ((binding.BLOCK_FORMAT_BC4, "BC4", 1), (binding.BLOCK_FORMAT_BC5, "BC5", 2)):
+        times = []
+        for _ in range(13):
+            start.record()
+            binding.block_compress(texels, block_format, 2)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop))
+        ms = float(np.median(times[3:]))
+        touched = side * side * (24 + 0.5 * channels)  # every 32-byte sector of the interleaved mip is read
+        print("%s of %dx%d (12 interleaved channels): %.3f ms, %.1f Gtexel/s, %.0f GB/s of sectors touched = %.2f of %s HBM peak"
+              % (name, side, side, ms, side * side / ms / 1e6, touched / ms / 1e6, touched / ms / 1e6 / peak, source))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -554,11 +585,15 @@ def main() -> int:
                         help="only launch the decode kernel LAUNCHES times on a small SIZE^2 set (fp8 or int8) and exit")
     parser.add_argument("--producers-case", metavar="SIDE", type=int,
                         help="only time latent packing on a SIDE x SIDE x 4 grid and one network quantisation, and exit")
+    parser.add_argument("--block-compress-case", metavar="SIDE", type=int,
+                        help="only time BC4 / BC5 encoding of a SIDE x SIDE 12-channel mip, and exit")
     args = parser.parse_args()
     if args.profile_case:
         return run_profile_case(args.profile_case)
     if args.producers_case:
         return run_producers_case(args.producers_case)
+    if args.block_compress_case:
+        return run_block_compress_case(args.block_compress_case)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:

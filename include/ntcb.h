@@ -369,6 +369,35 @@ typedef struct NtcbQuantizeNetworkParams
 } NtcbQuantizeNetworkParams;
 int ntcb_quantize_network(const NtcbQuantizeNetworkParams* params, void* stream);
 
+/* ---- Block compression of decoded texels ------------------------------------------------------ */
+
+/* ntc::BlockCompressedFormat (include/libntc/ntc.h:238-249) */
+#define NTCB_BLOCK_FORMAT_BC4 4
+#define NTCB_BLOCK_FORMAT_BC5 5
+
+/* Encodes one or two channels of a decoded mip (fp16, device memory) as BC4 or BC5 blocks in device
+   memory.  The CUDA counterpart of the compute pass that IContext::MakeBlockCompressionComputePass
+   describes (include/libntc/ntc.h:1050-1100, src/Context.cpp:630-779) and that the reference runs
+   as src/shaders/CompressBC4.hlsl / CompressBC5.hlsl through a graphics API; the encoder is
+   BC4_CompressFast (src/shaders/BlockCompressCommon.hlsli:710-796).  srcLeft / srcTop and
+   widthInBlocks / heightInBlocks mean what srcRect means there (texels outside the mip read as 0);
+   the destination offset is folded into `deviceBlocks`.  Other formats: NTCB_ERR_UNSUPPORTED.
+   Queued on `stream`; returns without waiting. */
+typedef struct NtcbBlockCompressParams
+{
+    const void* deviceMip;   /* decoded texels of one mip */
+    int32_t layout;          /* NtcbOutputLayout of deviceMip */
+    int32_t width, height, channels; /* of deviceMip */
+    int32_t firstChannel;    /* the channel BC4 encodes; BC5 encodes it and the next one */
+    int32_t format;          /* NTCB_BLOCK_FORMAT_* */
+    int32_t srcLeft, srcTop; /* texel position of the first block */
+    int32_t widthInBlocks, heightInBlocks;
+    int32_t reserved;
+    void* deviceBlocks;      /* 8 (BC4) or 16 (BC5) bytes per block */
+    size_t rowPitch;         /* bytes between rows of blocks */
+} NtcbBlockCompressParams;
+int ntcb_block_compress(const NtcbBlockCompressParams* params, void* stream);
+
 /* Size of the staging area built into the library for ntcb_read_channels_to_host_noalloc. */
 #define NTCB_NOALLOC_STAGING_BYTES (4u << 20)
 

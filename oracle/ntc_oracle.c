@@ -1046,3 +1046,230 @@ int ntco_quantize_network(const uint16_t* weights, const uint16_t* biases, const
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------------- */
+/* BC4 / BC5 block compression (src/shaders/BlockCompressCommon.hlsli:510-796,                  */
+/* CompressBC4.hlsl, CompressBC5.hlsl)                                                          */
+/*                                                                                             */
+/* PARITY UNPINNED: the reference runs these encoders as compute shaders through a graphics    */
+/* API, which cannot run here; this is a restatement of the shader's arithmetic in C (binary32 */
+/* operations in the shader's order, nothing fused; HLSL round = half to even; clamp and       */
+/* saturate treat NaN as the shader's min / max do).                                            */
+/* ------------------------------------------------------------------------------------------- */
+
+typedef struct { uint32_t x, y; } bc_uint2;
+
+static void bc4_palette(uint32_t a0, uint32_t a1, uint32_t alphas[8])
+{
+    alphas[0] = a0;
+    alphas[1] = a1;
+    if (a0 > a1)
+    {
+        alphas[2] = (6 * a0 + 1 * a1 + 3) / 7;
+        alphas[3] = (5 * a0 + 2 * a1 + 3) / 7;
+        alphas[4] = (4 * a0 + 3 * a1 + 3) / 7;
+        alphas[5] = (3 * a0 + 4 * a1 + 3) / 7;
+        alphas[6] = (2 * a0 + 5 * a1 + 3) / 7;
+        alphas[7] = (1 * a0 + 6 * a1 + 3) / 7;
+    }
+    else
+    {
+        alphas[2] = (4 * a0 + 1 * a1 + 2) / 5;
+        alphas[3] = (3 * a0 + 2 * a1 + 2) / 5;
+        alphas[4] = (2 * a0 + 3 * a1 + 2) / 5;
+        alphas[5] = (1 * a0 + 4 * a1 + 2) / 5;
+        alphas[6] = 0;
+        alphas[7] = 255;
+    }
+}
+
+static uint32_t bc4_get_index(bc_uint2 block, int pixel)
+{
+    const uint64_t bits = (uint64_t)block.x | ((uint64_t)block.y << 32);
+    return (uint32_t)(bits >> (16 + 3 * pixel)) & 7u;
+}
+
+static float bc4_compute_indices(const uint32_t values[16], bc_uint2* block) /* :605-632 */
+{
+    uint32_t alphas[8];
+    bc4_palette(block->x & 0xff, (block->x >> 8) & 0xff, alphas);
+    uint64_t bits = block->x & 0xffffu;
+    float total = 0.f;
+    for (int i = 0; i < 16; ++i)
+    {
+        int best = 0x7fffffff;
+        uint32_t bestIndex = 8;
+        for (uint32_t p = 0; p < 8; ++p)
+        {
+            int d = (int)values[i] - (int)alphas[p];
+            d *= d;
+            if (d < best)
+            {
+                best = d;
+                bestIndex = p;
+            }
+        }
+        total += (float)best;
+        bits |= (uint64_t)(bestIndex & 7u) << (16 + 3 * i);
+    }
+    block->x = (uint32_t)bits;
+    block->y = (uint32_t)(bits >> 32);
+    return total;
+}
+
+static float bc_clamp_byte(float x) /* clamp(x, 0, 255): min(max(x, 0), 255), NaN -> 0 */
+{
+    x = fmaxf(x, 0.f);
+    return fminf(x, 255.f);
+}
+
+static void bc4_optimize8(const uint32_t values[16], bc_uint2* block, int zeroAlpha1, int oneAlpha0) /* :634-670 */
+{
+    float alpha2 = 0, beta2 = 0, alphabeta = 0, alphax = 0, betax = 0;
+    for (int i = 0; i < 16; ++i)
+    {
+        const uint32_t index = bc4_get_index(*block, i);
+        const float alpha = index < 2 ? 1.0f - (float)index : (8.0f - (float)index) / 7.0f;
+        const float beta = 1 - alpha;
+        alpha2 += alpha * alpha;
+        beta2 += beta * beta;
+        alphabeta += alpha * beta;
+        alphax += alpha * (float)values[i];
+        betax += beta * (float)values[i];
+    }
+    const float factor = 1.0f / (alpha2 * beta2 - alphabeta * alphabeta);
+    const float a = (alphax * beta2 - betax * alphabeta) * factor;
+    const float b = (betax * alpha2 - alphax * alphabeta) * factor;
+    uint32_t alpha0 = oneAlpha0 ? 255u : (uint32_t)rintf(bc_clamp_byte(a));
+    uint32_t alpha1 = zeroAlpha1 ? 0u : (uint32_t)rintf(bc_clamp_byte(b));
+    if (alpha0 < alpha1)
+    {
+        const uint32_t t = alpha0;
+        alpha0 = alpha1;
+        alpha1 = t;
+    }
+    block->x = (block->x & 0xffff0000u) | (alpha0 & 0xff) | ((alpha1 & 0xff) << 8);
+}
+
+static void bc4_optimize6(const uint32_t values[16], bc_uint2* block) /* :672-708 */
+{
+    float alpha2 = 0, beta2 = 0, alphabeta = 0, alphax = 0, betax = 0;
+    for (int i = 0; i < 16; ++i)
+    {
+        const uint32_t index = bc4_get_index(*block, i);
+        float alpha;
+        if (index < 2)
+            alpha = 1.0f - (float)index;
+        else if (index < 6)
+            alpha = (6.0f - (float)index) / 5.0f;
+        else
+            continue;
+        const float beta = 1.0f - alpha;
+        alpha2 += alpha * alpha;
+        beta2 += beta * beta;
+        alphabeta += alpha * beta;
+        alphax += alpha * (float)values[i];
+        betax += beta * (float)values[i];
+    }
+    const float factor = alpha2 * beta2 - alphabeta * alphabeta;
+    if (factor == 0.0f)
+        return;
+    const float a = (alphax * beta2 - betax * alphabeta) / factor;
+    const float b = (betax * alpha2 - alphax * alphabeta) / factor;
+    const uint32_t alpha0 = (uint32_t)rintf(bc_clamp_byte(a)), alpha1 = (uint32_t)rintf(bc_clamp_byte(b));
+    block->x = (block->x & 0xffff0000u) | (alpha0 & 0xff) | ((alpha1 & 0xff) << 8);
+}
+
+static int bc4_same_indices(bc_uint2 a, bc_uint2 b)
+{
+    return (a.x & 0xffff0000u) == (b.x & 0xffff0000u) && a.y == b.y;
+}
+
+static bc_uint2 bc4_compress_fast(const float pixels[16]) /* :710-796 */
+{
+    uint32_t values[16];
+    uint32_t mina = 255, maxa = 0, mina_no01 = 255, maxa_no01 = 0;
+    for (int i = 0; i < 16; ++i)
+    {
+        float s = pixels[i];
+        s = isnan(s) ? 0.f : fminf(fmaxf(s, 0.f), 1.f);
+        values[i] = (uint32_t)rintf(s * 255.0f);
+        if (values[i] < mina) mina = values[i];
+        if (values[i] > maxa) maxa = values[i];
+        if (values[i] != 0 && values[i] < mina_no01) mina_no01 = values[i];
+        if (values[i] != 255 && values[i] > maxa_no01) maxa_no01 = values[i];
+    }
+    const int zeroAlpha1 = mina == 0, oneAlpha0 = maxa == 255;
+
+    bc_uint2 block = {0, 0};
+    const uint32_t start0 = oneAlpha0 ? 255u : maxa - (maxa - mina) / 34u;
+    const uint32_t start1 = zeroAlpha1 ? 0u : mina + (maxa - mina) / 34u;
+    block.x = (start0 & 0xff) | ((start1 & 0xff) << 8);
+    float besterror = bc4_compute_indices(values, &block);
+    bc_uint2 bestblock = block;
+    for (int i = 0; i < 8; ++i)
+    {
+        bc4_optimize8(values, &block, zeroAlpha1, oneAlpha0);
+        const float error = bc4_compute_indices(values, &block);
+        if (error >= besterror)
+            break;
+        if (bc4_same_indices(block, bestblock))
+        {
+            bestblock = block;
+            break;
+        }
+        bestblock = block;
+        besterror = error;
+    }
+
+    const uint32_t six0 = mina_no01 + (maxa_no01 - mina_no01) / 34u; /* unsigned wrap-around as in the shader */
+    const uint32_t six1 = maxa_no01 - (maxa_no01 - mina_no01) / 34u;
+    block.x = (block.x & 0xffff0000u) | (six0 & 0xff) | ((six1 & 0xff) << 8);
+    float besterror2 = bc4_compute_indices(values, &block);
+    bc_uint2 bestblock2 = block;
+    for (int i = 0; i < 8; ++i)
+    {
+        bc4_optimize6(values, &block);
+        const float error = bc4_compute_indices(values, &block);
+        if (error >= besterror2)
+            break;
+        if (bc4_same_indices(block, bestblock2))
+        {
+            bestblock2 = block;
+            break;
+        }
+        bestblock2 = block;
+        besterror2 = error;
+    }
+    if (besterror2 < besterror)
+        bestblock = bestblock2;
+    return bestblock;
+}
+
+/* CompressBC4.hlsl / CompressBC5.hlsl main(): one block per 4x4 texels starting at (srcLeft, srcTop);
+   texels outside the image read as 0.  `texels` is interleaved fp16 [height][width][channels];
+   `formatChannels` 1 = BC4, 2 = BC5; `blocks` receives 8 * formatChannels bytes per block, row-major. */
+int ntco_block_compress(const uint16_t* texels, int width, int height, int channels, int firstChannel, int formatChannels,
+    int srcLeft, int srcTop, int widthInBlocks, int heightInBlocks, uint8_t* blocks)
+{
+    if (!texels || !blocks || (formatChannels != 1 && formatChannels != 2) || firstChannel < 0
+        || firstChannel + formatChannels > channels || widthInBlocks <= 0 || heightInBlocks <= 0)
+        return -1;
+    for (int by = 0; by < heightInBlocks; ++by)
+        for (int bx = 0; bx < widthInBlocks; ++bx)
+            for (int c = 0; c < formatChannels; ++c)
+            {
+                float pixels[16];
+                for (int i = 0; i < 16; ++i)
+                {
+                    const int x = srcLeft + bx * 4 + (i & 3), y = srcTop + by * 4 + (i >> 2);
+                    pixels[i] = (x < width && y < height)
+                        ? h2f(texels[((size_t)y * width + x) * channels + firstChannel + c]) : 0.f;
+                }
+                const bc_uint2 block = bc4_compress_fast(pixels);
+                uint8_t* dst = blocks + (((size_t)by * widthInBlocks + bx) * formatChannels + c) * 8;
+                memcpy(dst, &block.x, 4);
+                memcpy(dst + 4, &block.y, 4);
+            }
+    return 0;
+}

@@ -137,6 +137,13 @@ int ntco_pack_latents(const uint16_t* latents, int width, int height, int numLay
 int ntco_quantize_network(const uint16_t* weights, const uint16_t* biases, const float* outputScale, const float* outputBias,
     int useFP8, uint8_t* blob, uint16_t* roundedWeights);
 
+/* BC4 (formatChannels 1) or BC5 (2) encoding of interleaved fp16 texels, following the reference's
+   compute shaders (src/shaders/CompressBC4.hlsl, CompressBC5.hlsl, BlockCompressCommon.hlsli:510-796).
+   PARITY UNPINNED: those shaders need a graphics API to run, which is unavailable here.  Texels
+   outside the image read as 0.  `blocks` receives 8 * formatChannels bytes per block, row-major. */
+int ntco_block_compress(const uint16_t* texels, int width, int height, int channels, int firstChannel, int formatChannels,
+    int srcLeft, int srcTop, int widthInBlocks, int heightInBlocks, uint8_t* blocks);
+
 /* Element helpers exposed for unit tests. */
 uint16_t ntco_float_to_half(float value);
 float ntco_half_to_float(uint16_t bits);

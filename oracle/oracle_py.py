@@ -109,6 +109,22 @@ def quantize_network(weights: np.ndarray, biases: np.ndarray, use_fp8: bool, out
     return blob.tobytes(), rounded
 
 
+def block_compress(texels: np.ndarray, first_channel: int, format_channels: int, src_left: int = 0, src_top: int = 0,
+                   width_in_blocks: Optional[int] = None, height_in_blocks: Optional[int] = None) -> np.ndarray:
+    """BC4 (format_channels 1) / BC5 (2) encoding restated on the CPU (parity unpinned: the
+    reference's encoders are compute shaders).  `texels`: [h][w][channels] float16.  Returns uint8
+    [blocks_y][blocks_x][8 * format_channels]."""
+    texels = np.ascontiguousarray(texels, dtype=np.float16)
+    h, w, channels = texels.shape
+    bw = (w - src_left + 3) // 4 if width_in_blocks is None else width_in_blocks
+    bh = (h - src_top + 3) // 4 if height_in_blocks is None else height_in_blocks
+    out = np.zeros((bh, bw, 8 * format_channels), dtype=np.uint8)
+    if oracle_lib().ntco_block_compress(texels.ctypes.data, w, h, channels, first_channel, format_channels, src_left, src_top,
+                                        bw, bh, out.ctypes.data) != 0:
+        raise ValueError("ntco_block_compress rejected its arguments")
+    return out
+
+
 def build_oracle() -> None:
     subprocess.run(["make", "-s", "-C", HERE, "libntc_oracle.so"], check=True)
 
@@ -129,6 +145,7 @@ def oracle_lib():
                                           ctypes.c_void_p]
         lib.ntco_quantize_network.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        lib.ntco_block_compress.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 9 + [ctypes.c_void_p]
         lib.ntco_float_to_half.restype = ctypes.c_uint16
         lib.ntco_float_to_half.argtypes = [ctypes.c_float]
         lib.ntco_half_to_float.restype = ctypes.c_float

