@@ -540,7 +540,7 @@ def run_producers_case(side: int) -> int:
 
 
 def run_block_compress_case(side: int) -> int:
-    """Times BC4 and BC5 encoding of a SIDE x SIDE mip of 12 interleaved fp16 channels (random texels
+    """Times BC4, BC5, BC1 and BC3 encoding of a SIDE x SIDE mip of 12 interleaved fp16 channels (random texels
     with smooth and noisy regions; larger than L2 from SIDE = 4096 up).  Prints a plain line per
     format, not the benchmark's JSON line."""
     import numpy as np
@@ -555,7 +555,8 @@ def run_block_compress_case(side: int) -> int:
     texels = (texels + 0.05 * torch.rand((side, side, 12), device="cuda", generator=generator)).clamp(0, 1).to(torch.float16).contiguous()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     peak, source = measured_peak_gbs()
-    for block_format, name, channels in ((binding.BLOCK_FORMAT_BC4, "BC4", 1), (binding.BLOCK_FORMAT_BC5, "BC5", 2)):
+    for block_format, name, channels in ((binding.BLOCK_FORMAT_BC4, "BC4", 1), (binding.BLOCK_FORMAT_BC5, "BC5", 2),
+                                         (binding.BLOCK_FORMAT_BC1, "BC1", 3), (binding.BLOCK_FORMAT_BC3, "BC3", 4)):
         times = []
         for _ in range(13):
             start.record()
@@ -564,7 +565,7 @@ def run_block_compress_case(side: int) -> int:
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop))
         ms = float(np.median(times[3:]))
-        touched = side * side * (24 + 0.5 * channels)  # every 32-byte sector of the interleaved mip is read
+        touched = side * side * (24 + (0.5 if block_format in (1, 4) else 1.0))  # every 32-byte sector of the interleaved mip is read
         print("%s of %dx%d (12 interleaved channels): %.3f ms, %.1f Gtexel/s, %.0f GB/s of sectors touched = %.2f of %s HBM peak"
               % (name, side, side, ms, side * side / ms / 1e6, touched / ms / 1e6, touched / ms / 1e6 / peak, source))
     return 0
@@ -586,7 +587,7 @@ def main() -> int:
     parser.add_argument("--producers-case", metavar="SIDE", type=int,
                         help="only time latent packing on a SIDE x SIDE x 4 grid and one network quantisation, and exit")
     parser.add_argument("--block-compress-case", metavar="SIDE", type=int,
-                        help="only time BC4 / BC5 encoding of a SIDE x SIDE 12-channel mip, and exit")
+                        help="only time BC4 / BC5 / BC1 / BC3 encoding of a SIDE x SIDE 12-channel mip, and exit")
     args = parser.parse_args()
     if args.profile_case:
         return run_profile_case(args.profile_case)

@@ -372,29 +372,37 @@ int ntcb_quantize_network(const NtcbQuantizeNetworkParams* params, void* stream)
 /* ---- Block compression of decoded texels ------------------------------------------------------ */
 
 /* ntc::BlockCompressedFormat (include/libntc/ntc.h:238-249) */
+#define NTCB_BLOCK_FORMAT_BC1 1
+#define NTCB_BLOCK_FORMAT_BC2 2
+#define NTCB_BLOCK_FORMAT_BC3 3
 #define NTCB_BLOCK_FORMAT_BC4 4
 #define NTCB_BLOCK_FORMAT_BC5 5
 
-/* Encodes one or two channels of a decoded mip (fp16, device memory) as BC4 or BC5 blocks in device
-   memory.  The CUDA counterpart of the compute pass that IContext::MakeBlockCompressionComputePass
-   describes (include/libntc/ntc.h:1050-1100, src/Context.cpp:630-779) and that the reference runs
-   as src/shaders/CompressBC4.hlsl / CompressBC5.hlsl through a graphics API; the encoder is
-   BC4_CompressFast (src/shaders/BlockCompressCommon.hlsli:710-796).  srcLeft / srcTop and
-   widthInBlocks / heightInBlocks mean what srcRect means there (texels outside the mip read as 0);
-   the destination offset is folded into `deviceBlocks`.  Other formats: NTCB_ERR_UNSUPPORTED.
+/* Encodes channels of a decoded mip (fp16, device memory) as BC1 - BC5 blocks in device memory.
+   The CUDA counterpart of the compute pass that IContext::MakeBlockCompressionComputePass describes
+   (include/libntc/ntc.h:1050-1100, src/Context.cpp:630-779) and that the reference runs as
+   src/shaders/CompressBC1-5.hlsl through a graphics API; the encoders follow
+   src/shaders/BlockCompressCommon.hlsli (BC1_EncodeSingleColor, BC1_CompressFast, BC1a_CompressFast,
+   BC2_EncodeAlpha, BC4_CompressFast).  srcLeft / srcTop and widthInBlocks / heightInBlocks mean what
+   srcRect means there (texels outside the mip read as 0 in every component); the destination offset
+   is folded into `deviceBlocks`.  BC6 and BC7: NTCB_ERR_UNSUPPORTED.  The first call of a colour
+   format on a device uploads two 512-byte tables (make it before any stream capture).
    Queued on `stream`; returns without waiting. */
 typedef struct NtcbBlockCompressParams
 {
     const void* deviceMip;   /* decoded texels of one mip */
     int32_t layout;          /* NtcbOutputLayout of deviceMip */
     int32_t width, height, channels; /* of deviceMip */
-    int32_t firstChannel;    /* the channel BC4 encodes; BC5 encodes it and the next one */
+    int32_t firstChannel;    /* BC4: the channel; BC5: it and the next; BC1-3: red, then green, blue, alpha */
     int32_t format;          /* NTCB_BLOCK_FORMAT_* */
     int32_t srcLeft, srcTop; /* texel position of the first block */
     int32_t widthInBlocks, heightInBlocks;
-    int32_t reserved;
-    void* deviceBlocks;      /* 8 (BC4) or 16 (BC5) bytes per block */
+    int32_t numChannels;     /* BC1-3: channels that feed the block, 1..4 (green and blue then read 0, alpha 1);
+                                0 = 3 for BC1, 4 for BC2 / BC3.  BC4 / BC5: 0 */
+    void* deviceBlocks;      /* 8 (BC1, BC4) or 16 (BC2, BC3, BC5) bytes per block */
     size_t rowPitch;         /* bytes between rows of blocks */
+    float alphaThreshold;    /* BC1: texels with alpha <= this are transparent (the reference's default: 1/255) */
+    int32_t reserved;
 } NtcbBlockCompressParams;
 int ntcb_block_compress(const NtcbBlockCompressParams* params, void* stream);
 

@@ -1273,3 +1273,444 @@ int ntco_block_compress(const uint16_t* texels, int width, int height, int chann
             }
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------------- */
+/* BC1 / BC2 / BC3 (src/shaders/BlockCompressCommon.hlsli:82-508, CompressBC1-3.hlsl).          */
+/* PARITY UNPINNED, as for BC4 / BC5 above.                                                     */
+/* ------------------------------------------------------------------------------------------- */
+
+typedef struct { float x, y, z; } bc_float3;
+typedef struct { float x, y, z, w; } bc_float4;
+
+static uint16_t g_match5[256], g_match6[256];
+static int g_matchReady = 0;
+
+/* Single-colour match tables; see the note at ntco_color_match_table in the header. */
+static void bc_fill_match_table(int bits, uint16_t* table)
+{
+    const int size = 1 << bits;
+    int expanded[64];
+    for (int c = 0; c < size; ++c)
+        expanded[c] = (c << (8 - bits)) | (c >> (2 * bits - 8));
+    for (int i = 0; i < 256; ++i)
+    {
+        int best = 1 << 30;
+        for (int mn = 0; mn < size; ++mn)
+            for (int mx = 0; mx < size; ++mx)
+            {
+                const int cost = 1000 * abs((2 * expanded[mx] + expanded[mn]) / 3 - i) + 14 * abs(expanded[mx] - expanded[mn]);
+                if (cost < best)
+                {
+                    best = cost;
+                    table[i] = (uint16_t)(mx | (mn << 8));
+                }
+            }
+    }
+}
+
+static void bc_ensure_tables(void)
+{
+    if (!g_matchReady)
+    {
+        bc_fill_match_table(5, g_match5);
+        bc_fill_match_table(6, g_match6);
+        g_matchReady = 1;
+    }
+}
+
+int ntco_color_match_table(int bits, uint16_t* table)
+{
+    if ((bits != 5 && bits != 6) || !table)
+        return -1;
+    bc_fill_match_table(bits, table);
+    return 0;
+}
+
+static float bc_saturate(float x) { return isnan(x) ? 0.f : fminf(fmaxf(x, 0.f), 1.f); }
+static bc_float3 f3(float x, float y, float z) { bc_float3 v = {x, y, z}; return v; }
+static bc_float3 f3_sub(bc_float3 a, bc_float3 b) { return f3(a.x - b.x, a.y - b.y, a.z - b.z); }
+static bc_float3 f3_add(bc_float3 a, bc_float3 b) { return f3(a.x + b.x, a.y + b.y, a.z + b.z); }
+static bc_float3 f3_mul(bc_float3 a, float s) { return f3(a.x * s, a.y * s, a.z * s); }
+static bc_float3 f3_saturate(bc_float3 a) { return f3(bc_saturate(a.x), bc_saturate(a.y), bc_saturate(a.z)); }
+static float f3_dot(bc_float3 a, bc_float3 b) { return a.x * b.x + a.y * b.y + a.z * b.z; }
+static bc_float3 f3_lerp(bc_float3 x, bc_float3 y, float s) { return f3_add(x, f3_mul(f3_sub(y, x), s)); }
+static bc_float3 rgb_of(bc_float4 p) { return f3(p.x, p.y, p.z); }
+static float f4_dot(bc_float4 a) { return a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w; }
+static float color_distance(bc_float3 c0, bc_float3 c1) { const bc_float3 d = f3_sub(c0, c1); return f3_dot(d, d); }
+
+static uint32_t bc1_select_best_index(const float d[4], float* error) /* :116-144 */
+{
+    if (fminf(d[0], d[1]) < fminf(d[2], d[3]))
+    {
+        if (d[0] < d[1]) { *error = d[0]; return 0; }
+        *error = d[1];
+        return 1;
+    }
+    if (d[2] < d[3]) { *error = d[2]; return 2; }
+    *error = d[3];
+    return 3;
+}
+
+static uint32_t bc1_compute_index4(bc_float4 color, bc_float3 maxColor, bc_float3 minColor, float* error) /* :146-159 */
+{
+    const bc_float3 color2 = f3_lerp(maxColor, minColor, 1.0f / 3.0f);
+    const bc_float3 color3 = f3_lerp(maxColor, minColor, 2.0f / 3.0f);
+    const float alphaDistance = (1.0f - color.w) * (1.0f - color.w);
+    float d[4];
+    d[0] = color_distance(maxColor, rgb_of(color)) + alphaDistance;
+    d[1] = color_distance(minColor, rgb_of(color)) + alphaDistance;
+    d[2] = color_distance(color2, rgb_of(color)) + alphaDistance;
+    d[3] = color_distance(color3, rgb_of(color)) + alphaDistance;
+    return bc1_select_best_index(d, error);
+}
+
+static uint32_t bc1_compute_index3(bc_float4 color, bc_float3 maxColor, bc_float3 minColor, float threshold, float* error) /* :161-179 */
+{
+    if (color.w <= threshold)
+    {
+        *error = 0;
+        return 3;
+    }
+    const bc_float3 color2 = f3_lerp(maxColor, minColor, 0.5f);
+    const float alphaDistance = (1.0f - color.w) * (1.0f - color.w);
+    float d[4];
+    d[0] = color_distance(maxColor, rgb_of(color)) + alphaDistance;
+    d[1] = color_distance(minColor, rgb_of(color)) + alphaDistance;
+    d[2] = color_distance(color2, rgb_of(color)) + alphaDistance;
+    d[3] = f4_dot(color);
+    return bc1_select_best_index(d, error);
+}
+
+static bc_float3 expand565(uint32_t w)
+{
+    return f3((float)((w >> 11) & 0x1f) * 1.0f / 31.0f, (float)((w >> 5) & 0x3f) * 1.0f / 63.0f, (float)(w & 0x1f) * 1.0f / 31.0f);
+}
+
+static bc_float3 round_and_expand565(bc_float3 v, uint32_t* w)
+{
+    const uint32_t x = (uint32_t)rintf(bc_saturate(v.x) * 31.0f);
+    const uint32_t y = (uint32_t)rintf(bc_saturate(v.y) * 63.0f);
+    const uint32_t z = (uint32_t)rintf(bc_saturate(v.z) * 31.0f);
+    *w = (x << 11) | (y << 5) | z;
+    return expand565(*w);
+}
+
+static int clamp_byte_index(float v)
+{
+    const int i = (int)rintf(v);
+    return i < 0 ? 0 : i > 255 ? 255 : i; /* the shader indexes unclamped; both implementations here clamp */
+}
+
+static bc_uint2 bc1_encode_single_color(const bc_float4 pixels[16], float* blockError) /* :205-247 */
+{
+    bc_float3 average = f3(0, 0, 0);
+    for (int i = 0; i < 16; ++i)
+        average = f3_add(average, rgb_of(pixels[i]));
+    average = f3(average.x / 16.0f, average.y / 16.0f, average.z / 16.0f);
+    const uint32_t mr = g_match5[clamp_byte_index(average.x * 255.f)], mg = g_match6[clamp_byte_index(average.y * 255.f)],
+                   mb = g_match5[clamp_byte_index(average.z * 255.f)];
+    const uint32_t color0 = ((mr & 0x1f) << 11) | ((mg & 0x3f) << 5) | (mb & 0x1f);
+    const uint32_t color1 = (((mr >> 8) & 0x1f) << 11) | (((mg >> 8) & 0x3f) << 5) | ((mb >> 8) & 0x1f);
+    bc_uint2 result;
+    if (color0 < color1)
+    {
+        result.x = (color0 << 16) | color1;
+        result.y = 0xffffffffu;
+    }
+    else
+    {
+        result.x = (color1 << 16) | color0;
+        result.y = 0xaaaaaaaau;
+    }
+    const bc_float3 encoded = f3_lerp(expand565(color0), expand565(color1), 1.0f / 3.0f);
+    *blockError = 0;
+    for (int i = 0; i < 16; ++i)
+    {
+        const bc_float4 diff = {pixels[i].x - encoded.x, pixels[i].y - encoded.y, pixels[i].z - encoded.z, pixels[i].w - 1.0f};
+        *blockError += f4_dot(diff);
+    }
+    return result;
+}
+
+static void bc_swapf(float* a, float* b) { const float t = *a; *a = *b; *b = t; }
+
+static void bc_orient(bc_float3* minColor, bc_float3* maxColor, float cov_rg, float cov_rb, float cov_gb)
+{
+    if (minColor->x != maxColor->x)
+    {
+        if (cov_rg < 0) bc_swapf(&minColor->y, &maxColor->y);
+        if (cov_rb < 0) bc_swapf(&minColor->z, &maxColor->z);
+    }
+    else if (minColor->y != maxColor->y)
+    {
+        if (cov_gb < 0) bc_swapf(&minColor->z, &maxColor->z);
+    }
+}
+
+static float keep_extreme(float current, float refitted)
+{
+    return (current == 0.0f || current == 1.0f) ? current : bc_saturate(refitted);
+}
+
+static bc_uint2 bc1_compress_fast(const bc_float4 pixels[16], float* blockError) /* :249-376 */
+{
+    bc_float3 sums = f3(0, 0, 0), minColor = f3(1, 1, 1), maxColor = f3(0, 0, 0);
+    for (int i = 0; i < 16; ++i)
+    {
+        const bc_float3 c = rgb_of(pixels[i]);
+        sums = f3_add(sums, c);
+        minColor = f3(fminf(minColor.x, c.x), fminf(minColor.y, c.y), fminf(minColor.z, c.z));
+        maxColor = f3(fmaxf(maxColor.x, c.x), fmaxf(maxColor.y, c.y), fmaxf(maxColor.z, c.z));
+    }
+    const bc_float3 center = f3(sums.x / 16.0f, sums.y / 16.0f, sums.z / 16.0f);
+    float cov_rg = 0, cov_rb = 0, cov_gb = 0;
+    for (int i = 0; i < 16; ++i)
+    {
+        const bc_float3 pix = f3_sub(rgb_of(pixels[i]), center);
+        cov_rg += pix.x * pix.y;
+        cov_rb += pix.x * pix.z;
+        cov_gb += pix.y * pix.z;
+    }
+    bc_orient(&minColor, &maxColor, cov_rg, cov_rb, cov_gb);
+    const bc_float3 extent = f3_sub(maxColor, minColor);
+    const bc_float3 inset = f3(extent.x / 16.0f, extent.y / 16.0f, extent.z / 16.0f);
+    maxColor = f3_saturate(f3_sub(maxColor, inset));
+    minColor = f3_saturate(f3_add(minColor, inset));
+
+    uint32_t color0 = 0, color1 = 0;
+    for (int pass = 0; pass < 4; ++pass)
+    {
+        float alpha2 = 0, beta2 = 0, alphabeta = 0;
+        bc_float3 alphax = f3(0, 0, 0), betax = f3(0, 0, 0);
+        for (int i = 0; i < 16; ++i)
+        {
+            float pixelError;
+            const uint32_t index = bc1_compute_index4(pixels[i], maxColor, minColor, &pixelError);
+            float beta = (float)(index & 1);
+            if (index & 2)
+                beta = (1 + beta) / 3.0f;
+            const float alpha = 1.0f - beta;
+            alpha2 += alpha * alpha;
+            beta2 += beta * beta;
+            alphabeta += alpha * beta;
+            alphax = f3_add(alphax, f3_mul(rgb_of(pixels[i]), alpha));
+            betax = f3_add(betax, f3_mul(rgb_of(pixels[i]), beta));
+        }
+        const float denom = alpha2 * beta2 - alphabeta * alphabeta;
+        if (fabsf(denom) > 0.0001f)
+        {
+            const float factor = 1.0f / denom;
+            const bc_float3 a = f3_mul(f3_sub(f3_mul(alphax, beta2), f3_mul(betax, alphabeta)), factor);
+            const bc_float3 b = f3_mul(f3_sub(f3_mul(betax, alpha2), f3_mul(alphax, alphabeta)), factor);
+            minColor = f3(keep_extreme(minColor.x, b.x), keep_extreme(minColor.y, b.y), keep_extreme(minColor.z, b.z));
+            maxColor = f3(keep_extreme(maxColor.x, a.x), keep_extreme(maxColor.y, a.y), keep_extreme(maxColor.z, a.z));
+        }
+        uint32_t newColor0, newColor1;
+        maxColor = round_and_expand565(maxColor, &newColor0);
+        minColor = round_and_expand565(minColor, &newColor1);
+        if (newColor0 == color0 && newColor1 == color1)
+            break;
+        color0 = newColor0;
+        color1 = newColor1;
+    }
+    if (color0 == color1)
+    {
+        if (color0 == 0)
+        {
+            color0 = 1;
+            maxColor = expand565(color0);
+        }
+        else
+        {
+            color1 = color0 - 1;
+            minColor = expand565(color1);
+        }
+    }
+    else if (color0 < color1)
+    {
+        const bc_float3 t = maxColor;
+        maxColor = minColor;
+        minColor = t;
+        const uint32_t c = color0;
+        color0 = color1;
+        color1 = c;
+    }
+    uint32_t indices = 0;
+    *blockError = 0;
+    for (int i = 0; i < 16; ++i)
+    {
+        float pixelError;
+        const uint32_t index = bc1_compute_index4(pixels[i], maxColor, minColor, &pixelError);
+        indices |= index << (2 * i);
+        *blockError += pixelError;
+    }
+    bc_uint2 result = {(color1 << 16) | color0, indices};
+    return result;
+}
+
+static bc_uint2 bc1a_compress_fast(const bc_float4 pixels[16], float threshold, float* blockError) /* :378-493 */
+{
+    bc_float3 sums = f3(0, 0, 0), minColor = f3(1, 1, 1), maxColor = f3(0, 0, 0);
+    int opaqueCount = 0;
+    for (int i = 0; i < 16; ++i)
+        if (!(pixels[i].w <= threshold))
+        {
+            const bc_float3 c = rgb_of(pixels[i]);
+            sums = f3_add(sums, c);
+            minColor = f3(fminf(minColor.x, c.x), fminf(minColor.y, c.y), fminf(minColor.z, c.z));
+            maxColor = f3(fmaxf(maxColor.x, c.x), fmaxf(maxColor.y, c.y), fmaxf(maxColor.z, c.z));
+            opaqueCount += 1;
+        }
+    const float count = (float)opaqueCount;
+    const bc_float3 center = opaqueCount > 0 ? f3(sums.x / count, sums.y / count, sums.z / count) : f3(0, 0, 0);
+    float cov_rg = 0, cov_rb = 0, cov_gb = 0;
+    for (int i = 0; i < 16; ++i)
+        if (!(pixels[i].w <= threshold))
+        {
+            const bc_float3 pix = f3_sub(rgb_of(pixels[i]), center);
+            cov_rg += pix.x * pix.y;
+            cov_rb += pix.x * pix.z;
+            cov_gb += pix.y * pix.z;
+        }
+    bc_orient(&minColor, &maxColor, cov_rg, cov_rb, cov_gb);
+    const bc_float3 extent = f3_sub(maxColor, minColor);
+    const bc_float3 inset = f3(extent.x / count, extent.y / count, extent.z / count);
+    maxColor = f3_saturate(f3_sub(maxColor, inset));
+    minColor = f3_saturate(f3_add(minColor, inset));
+
+    float alpha2 = 0, beta2 = 0, alphabeta = 0;
+    bc_float3 alphax = f3(0, 0, 0), betax = f3(0, 0, 0);
+    for (int i = 0; i < 16; ++i)
+    {
+        float pixelError;
+        const uint32_t index = bc1_compute_index3(pixels[i], maxColor, minColor, threshold, &pixelError);
+        if (index != 3)
+        {
+            float beta = (float)(index & 1);
+            if (index & 2)
+                beta = 0.5f;
+            const float alpha = 1.0f - beta;
+            alpha2 += alpha * alpha;
+            beta2 += beta * beta;
+            alphabeta += alpha * beta;
+            alphax = f3_add(alphax, f3_mul(rgb_of(pixels[i]), alpha));
+            betax = f3_add(betax, f3_mul(rgb_of(pixels[i]), beta));
+        }
+    }
+    const float denom = alpha2 * beta2 - alphabeta * alphabeta;
+    if (fabsf(denom) > 0.0001f)
+    {
+        const float factor = 1.0f / denom;
+        const bc_float3 a = f3_mul(f3_sub(f3_mul(alphax, beta2), f3_mul(betax, alphabeta)), factor);
+        const bc_float3 b = f3_mul(f3_sub(f3_mul(betax, alpha2), f3_mul(alphax, alphabeta)), factor);
+        minColor = f3(keep_extreme(minColor.x, a.x), keep_extreme(minColor.y, a.y), keep_extreme(minColor.z, a.z));
+        maxColor = f3(keep_extreme(maxColor.x, b.x), keep_extreme(maxColor.y, b.y), keep_extreme(maxColor.z, b.z));
+    }
+    uint32_t color0, color1;
+    maxColor = round_and_expand565(maxColor, &color0);
+    minColor = round_and_expand565(minColor, &color1);
+    if (color0 > color1)
+    {
+        const bc_float3 t = maxColor;
+        maxColor = minColor;
+        minColor = t;
+        const uint32_t c = color0;
+        color0 = color1;
+        color1 = c;
+    }
+    uint32_t indices = 0;
+    *blockError = 0;
+    for (int i = 0; i < 16; ++i)
+    {
+        float pixelError;
+        const uint32_t index = bc1_compute_index3(pixels[i], maxColor, minColor, threshold, &pixelError);
+        indices |= index << (2 * i);
+        if (index != 3 || !(pixels[i].w <= threshold))
+            *blockError += pixelError;
+    }
+    bc_uint2 result = {(color1 << 16) | color0, indices};
+    return result;
+}
+
+static bc_uint2 bc2_encode_alpha(const float alphas[16]) /* :495-508 */
+{
+    bc_uint2 block = {0, 0};
+    for (int i = 0; i < 16; ++i)
+    {
+        const uint32_t value = (uint32_t)rintf(bc_saturate(alphas[i]) * 15.0f);
+        if (i < 8)
+            block.x |= value << (i * 4);
+        else
+            block.y |= value << ((i - 8) * 4);
+    }
+    return block;
+}
+
+/* CompressBC1.hlsl / CompressBC2.hlsl / CompressBC3.hlsl main().  `format` 1, 2 or 3; `numChannels`
+   (1..4) consecutive channels from `firstChannel` are red, green, blue, alpha (missing: 0, alpha 1);
+   texels outside the image read as 0 in all four.  8 (BC1) or 16 bytes per block, row-major. */
+int ntco_block_compress_color(const uint16_t* texels, int width, int height, int channels, int firstChannel, int numChannels,
+    int format, float alphaThreshold, int srcLeft, int srcTop, int widthInBlocks, int heightInBlocks, uint8_t* blocks)
+{
+    if (!texels || !blocks || format < 1 || format > 3 || numChannels < 1 || numChannels > 4 || firstChannel < 0
+        || firstChannel + numChannels > channels || widthInBlocks <= 0 || heightInBlocks <= 0)
+        return -1;
+    bc_ensure_tables();
+    const size_t blockBytes = format == 1 ? 8 : 16;
+    for (int by = 0; by < heightInBlocks; ++by)
+        for (int bx = 0; bx < widthInBlocks; ++bx)
+        {
+            bc_float4 colors[16];
+            float alphas[16];
+            for (int i = 0; i < 16; ++i)
+            {
+                const int x = srcLeft + bx * 4 + (i & 3), y = srcTop + by * 4 + (i >> 2);
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                if (x < width && y < height)
+                {
+                    c[3] = 1.f;
+                    for (int k = 0; k < numChannels; ++k)
+                        c[k] = h2f(texels[((size_t)y * width + x) * channels + firstChannel + k]);
+                }
+                colors[i].x = c[0];
+                colors[i].y = c[1];
+                colors[i].z = c[2];
+                colors[i].w = format == 1 ? c[3] : 1.0f;
+                alphas[i] = c[3];
+            }
+            float bestError, error;
+            bc_uint2 best, candidate;
+            if (format == 1)
+            {
+                bestError = 0; /* BC1a_TransparentBlock, :99-109 */
+                for (int i = 0; i < 16; ++i)
+                    if (!(colors[i].w <= alphaThreshold))
+                        bestError += f4_dot(colors[i]);
+                best.x = 0;
+                best.y = 0xffffffffu;
+                candidate = bc1_encode_single_color(colors, &error);
+                if (error < bestError) { bestError = error; best = candidate; }
+            }
+            else
+                best = bc1_encode_single_color(colors, &bestError);
+            candidate = bc1_compress_fast(colors, &error);
+            if (error < bestError) { bestError = error; best = candidate; }
+            uint8_t* dst = blocks + ((size_t)by * widthInBlocks + bx) * blockBytes;
+            if (format == 1)
+            {
+                candidate = bc1a_compress_fast(colors, alphaThreshold, &error);
+                if (error < bestError) { bestError = error; best = candidate; }
+                memcpy(dst, &best.x, 4);
+                memcpy(dst + 4, &best.y, 4);
+            }
+            else
+            {
+                const bc_uint2 alpha = format == 2 ? bc2_encode_alpha(alphas) : bc4_compress_fast(alphas);
+                memcpy(dst, &alpha.x, 4);
+                memcpy(dst + 4, &alpha.y, 4);
+                memcpy(dst + 8, &best.x, 4);
+                memcpy(dst + 12, &best.y, 4);
+            }
+        }
+    return 0;
+}

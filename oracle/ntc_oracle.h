@@ -144,6 +144,19 @@ int ntco_quantize_network(const uint16_t* weights, const uint16_t* biases, const
 int ntco_block_compress(const uint16_t* texels, int width, int height, int channels, int firstChannel, int formatChannels,
     int srcLeft, int srcTop, int widthInBlocks, int heightInBlocks, uint8_t* blocks);
 
+/* BC1 (format 1), BC2 (2) or BC3 (3) encoding, following src/shaders/CompressBC1-3.hlsl and
+   BlockCompressCommon.hlsli:82-508.  PARITY UNPINNED, as above.  `numChannels` (1..4) channels from
+   `firstChannel` are red, green, blue, alpha (missing ones 0, alpha 1); texels outside the image
+   read as 0 in all four.  8 (BC1) or 16 bytes per block. */
+int ntco_block_compress_color(const uint16_t* texels, int width, int height, int channels, int firstChannel, int numChannels,
+    int format, float alphaThreshold, int srcLeft, int srcTop, int widthInBlocks, int heightInBlocks, uint8_t* blocks);
+
+/* The single-colour match table for 5- or 6-bit endpoints (256 entries: mx | mn << 8), generated:
+   the pair minimising 1000 * |(2 e(mx) + e(mn)) / 3 - i| + 14 * |e(mx) - e(mn)|, mn in the outer
+   loop, first minimum kept.  Reproduces c_ColorMatch5bit / c_ColorMatch6bit of
+   BlockCompressCommon.hlsli:40-80 (checked by digest in tests/test_block_compress.py). */
+int ntco_color_match_table(int bits, uint16_t* table);
+
 /* Element helpers exposed for unit tests. */
 uint16_t ntco_float_to_half(float value);
 float ntco_half_to_float(uint16_t bits);

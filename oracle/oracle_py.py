@@ -125,6 +125,30 @@ def block_compress(texels: np.ndarray, first_channel: int, format_channels: int,
     return out
 
 
+def block_compress_color(texels: np.ndarray, block_format: int, first_channel: int = 0, num_channels: Optional[int] = None,
+                         alpha_threshold: float = 1.0 / 255.0, src_left: int = 0, src_top: int = 0,
+                         width_in_blocks: Optional[int] = None, height_in_blocks: Optional[int] = None) -> np.ndarray:
+    """BC1 / BC2 / BC3 (block_format 1 / 2 / 3) restated on the CPU (parity unpinned).  Returns uint8
+    [blocks_y][blocks_x][8 or 16]."""
+    texels = np.ascontiguousarray(texels, dtype=np.float16)
+    h, w, channels = texels.shape
+    n = (3 if block_format == 1 else 4) if num_channels is None else num_channels
+    bw = (w - src_left + 3) // 4 if width_in_blocks is None else width_in_blocks
+    bh = (h - src_top + 3) // 4 if height_in_blocks is None else height_in_blocks
+    out = np.zeros((bh, bw, 8 if block_format == 1 else 16), dtype=np.uint8)
+    if oracle_lib().ntco_block_compress_color(texels.ctypes.data, w, h, channels, first_channel, n, block_format,
+                                              alpha_threshold, src_left, src_top, bw, bh, out.ctypes.data) != 0:
+        raise ValueError("ntco_block_compress_color rejected its arguments")
+    return out
+
+
+def color_match_table(bits: int) -> np.ndarray:
+    table = np.zeros(256, dtype=np.uint16)
+    if oracle_lib().ntco_color_match_table(bits, table.ctypes.data) != 0:
+        raise ValueError("bits must be 5 or 6")
+    return table
+
+
 def build_oracle() -> None:
     subprocess.run(["make", "-s", "-C", HERE, "libntc_oracle.so"], check=True)
 
@@ -146,6 +170,9 @@ def oracle_lib():
         lib.ntco_quantize_network.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
         lib.ntco_block_compress.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 9 + [ctypes.c_void_p]
+        lib.ntco_block_compress_color.argtypes = ([ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_float] + [ctypes.c_int] * 4
+                                                  + [ctypes.c_void_p])
+        lib.ntco_color_match_table.argtypes = [ctypes.c_int, ctypes.c_void_p]
         lib.ntco_float_to_half.restype = ctypes.c_uint16
         lib.ntco_float_to_half.argtypes = [ctypes.c_float]
         lib.ntco_half_to_float.restype = ctypes.c_float

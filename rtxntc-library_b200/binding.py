@@ -327,22 +327,23 @@ def quantize_network(weights, biases, weight_mode: int, output_scale=None, outpu
     return (blob, rounded) if want_rounded else blob
 
 
-BLOCK_FORMAT_BC4, BLOCK_FORMAT_BC5 = 4, 5
+BLOCK_FORMAT_BC1, BLOCK_FORMAT_BC2, BLOCK_FORMAT_BC3, BLOCK_FORMAT_BC4, BLOCK_FORMAT_BC5 = 1, 2, 3, 4, 5
 
 
 class BlockCompressParams(ctypes.Structure):
     _fields_ = [("deviceMip", ctypes.c_void_p), ("layout", ctypes.c_int32), ("width", ctypes.c_int32),
                 ("height", ctypes.c_int32), ("channels", ctypes.c_int32), ("firstChannel", ctypes.c_int32),
                 ("format", ctypes.c_int32), ("srcLeft", ctypes.c_int32), ("srcTop", ctypes.c_int32),
-                ("widthInBlocks", ctypes.c_int32), ("heightInBlocks", ctypes.c_int32), ("reserved", ctypes.c_int32),
-                ("deviceBlocks", ctypes.c_void_p), ("rowPitch", ctypes.c_size_t)]
+                ("widthInBlocks", ctypes.c_int32), ("heightInBlocks", ctypes.c_int32), ("numChannels", ctypes.c_int32),
+                ("deviceBlocks", ctypes.c_void_p), ("rowPitch", ctypes.c_size_t), ("alphaThreshold", ctypes.c_float),
+                ("reserved", ctypes.c_int32)]
 
 
 def block_compress(texels, block_format: int, first_channel: int = 0, layout: int = LAYOUT_INTERLEAVED,
                    width: Optional[int] = None, height: Optional[int] = None, channels: Optional[int] = None,
                    src_left: int = 0, src_top: int = 0, width_in_blocks: Optional[int] = None,
-                   height_in_blocks: Optional[int] = None):
-    """BC4 / BC5 encoding of decoded texels the caller holds: `texels` is a CUDA float16 tensor,
+                   height_in_blocks: Optional[int] = None, num_channels: int = 0, alpha_threshold: float = 1.0 / 255.0):
+    """BC1 - BC5 encoding of decoded texels the caller holds: `texels` is a CUDA float16 tensor,
     [height][width][channels] for the interleaved layout (sizes then come from its shape).  Returns a
     CUDA uint8 tensor [blocks_y][blocks_x][8 or 16]."""
     import torch
@@ -351,7 +352,7 @@ def block_compress(texels, block_format: int, first_channel: int = 0, layout: in
         height, width, channels = texels.shape
     bw = (width - src_left + 3) // 4 if width_in_blocks is None else width_in_blocks
     bh = (height - src_top + 3) // 4 if height_in_blocks is None else height_in_blocks
-    block_bytes = 8 if block_format == BLOCK_FORMAT_BC4 else 16
+    block_bytes = 8 if block_format in (BLOCK_FORMAT_BC1, BLOCK_FORMAT_BC4) else 16
     out = torch.zeros((bh, bw, block_bytes), dtype=torch.uint8, device=texels.device)
     params = BlockCompressParams()
     params.deviceMip = texels.data_ptr()
@@ -360,6 +361,7 @@ def block_compress(texels, block_format: int, first_channel: int = 0, layout: in
     params.srcLeft, params.srcTop, params.widthInBlocks, params.heightInBlocks = src_left, src_top, bw, bh
     params.deviceBlocks = out.data_ptr()
     params.rowPitch = bw * block_bytes
+    params.numChannels, params.alphaThreshold = num_channels, alpha_threshold
     with torch.cuda.device(texels.device):
         stream = torch.cuda.current_stream(texels.device).cuda_stream
         check(lib().ntcb_block_compress(ctypes.byref(params), ctypes.c_void_p(stream)))

@@ -1,8 +1,8 @@
-"""BC4 / BC5 encoding of decoded texels (`ntcb_block_compress`).
+"""BC1 - BC5 encoding of decoded texels (`ntcb_block_compress`).
 
-PARITY UNPINNED against the reference: its encoders are compute shaders (src/shaders/CompressBC4.hlsl,
-CompressBC5.hlsl, BC4_CompressFast in BlockCompressCommon.hlsli) that only run through a graphics
-API, which is unavailable here.  What is tested instead:
+PARITY UNPINNED against the reference: its encoders are compute shaders (src/shaders/CompressBC1-5.hlsl,
+BlockCompressCommon.hlsli) that only run through a graphics API, which is unavailable here.  What
+is tested instead:
   * the CUDA kernel against the CPU restatement of the shader's arithmetic (two separately written
     implementations of the same algorithm): IDENTICAL BYTES, both layouts, offsets, ragged edges;
   * the format itself, through a BC4 decoder written from the format's definition: constant blocks
@@ -34,6 +34,51 @@ def decode_bc4(blocks: np.ndarray) -> np.ndarray:
             for i in range(16):
                 out[y * 4 + (i >> 2), x * 4 + (i & 3)] = palette[(bits >> (3 * i)) & 7]
     return out
+
+
+def decode_bc1(blocks: np.ndarray):
+    """[by][bx][8] bytes -> ([by*4][bx*4][3] colours in 0..1, [by*4][bx*4] alpha), per the format's definition."""
+    by, bx, _ = blocks.shape
+    rgb, alpha = np.zeros((by * 4, bx * 4, 3)), np.ones((by * 4, bx * 4))
+
+    def expand(w):
+        return np.array([((w >> 11) & 31) / 31.0, ((w >> 5) & 63) / 63.0, (w & 31) / 31.0])
+
+    for y in range(by):
+        for x in range(bx):
+            block = blocks[y, x]
+            c0, c1 = int(block[0]) | int(block[1]) << 8, int(block[2]) | int(block[3]) << 8
+            bits = int.from_bytes(bytes(block[4:8]), "little")
+            e0, e1 = expand(c0), expand(c1)
+            if c0 > c1:
+                palette = [(e0, 1), (e1, 1), ((2 * e0 + e1) / 3, 1), ((e0 + 2 * e1) / 3, 1)]
+            else:
+                palette = [(e0, 1), (e1, 1), ((e0 + e1) / 2, 1), (np.zeros(3), 0)]
+            for i in range(16):
+                colour, a = palette[(bits >> (2 * i)) & 3]
+                rgb[y * 4 + (i >> 2), x * 4 + (i & 3)] = colour
+                alpha[y * 4 + (i >> 2), x * 4 + (i & 3)] = a
+    return rgb, alpha
+
+
+def color_images():
+    rng = np.random.default_rng(31)
+    h, w = 24, 40
+    smooth = np.zeros((h, w, 4))
+    smooth[..., 0] = np.linspace(0.1, 0.9, w)[None, :]
+    smooth[..., 1] = np.linspace(0.8, 0.2, h)[:, None]
+    smooth[..., 2] = 0.5 + 0.3 * np.sin(np.arange(w) / 5.0)[None, :]
+    smooth[..., 3] = 1.0
+    noise = rng.uniform(-0.05, 1.05, (h, w, 4))
+    cutout = smooth + rng.normal(0, 0.02, (h, w, 4))
+    cutout[..., 3] = (rng.uniform(size=(h, w)) < 0.6).astype(np.float64)
+    cutout[:8, :8, 3] = 0
+    flat = np.zeros((h, w, 4))
+    flat[...] = rng.integers(0, 256, (h // 4, w // 4, 4)).repeat(4, axis=0).repeat(4, axis=1) / 255.0
+    flat[..., 3] = 1.0
+    extremes = rng.integers(0, 2, (h, w, 4)).astype(np.float64)
+    return {name: image.astype(np.float16) for name, image in
+            (("smooth", smooth), ("noise", noise), ("cutout", cutout), ("flat", flat), ("extremes", extremes))}
 
 
 def quantised(texels: np.ndarray) -> np.ndarray:
@@ -116,6 +161,78 @@ def test_source_window(oracle):
     assert np.array_equal(window, oracle.block_compress(texels, 0, 1)[1:3, 2:5])
 
 
+def test_match_tables_are_the_reference_ones(oracle):
+    """The single-colour match tables are generated, not stored; their digests are those of the
+    tables in BlockCompressCommon.hlsli:40-80 (taken where the reference's sources are at hand)."""
+    import hashlib
+
+    assert hashlib.sha256(oracle.color_match_table(5).astype("<u2").tobytes()).hexdigest() == \
+        "51207020db025e90c3a7b985b0b78d4eff317eb74b68e21329fff7db3f22d196"
+    assert hashlib.sha256(oracle.color_match_table(6).astype("<u2").tobytes()).hexdigest() == \
+        "db2ca3aa978ed0f5b3aa05a2e4efb53f44d6741014dd578498f4e50a05a0576c"
+
+
+def test_bc1_flat_blocks_and_error_bounds(oracle):
+    images = color_images()
+    flat = images["flat"]
+    rgb, alpha = decode_bc1(oracle.block_compress_color(flat, 1, 0, 4))
+    assert (alpha == 1).all()
+    # one colour per block: the match tables land within 2/255 per component (3 % rule included)
+    assert np.abs(rgb - flat[..., :3].astype(np.float64)).max() <= 2.5 / 255
+    for name, bound in (("smooth", 33.0), ("noise", 12.0)):
+        source = np.clip(images[name][..., :3].astype(np.float64), 0, 1)
+        rgb, alpha = decode_bc1(oracle.block_compress_color(images[name], 1, 0, 3))
+        assert (alpha == 1).all(), name
+        psnr = -10 * np.log10(np.mean((rgb - source) ** 2))
+        assert psnr >= bound, (name, psnr)
+
+
+def test_bc1_transparency(oracle):
+    image = color_images()["cutout"]
+    blocks = oracle.block_compress_color(image, 1, 0, 4)
+    rgb, alpha = decode_bc1(blocks)
+    source_alpha = image[..., 3].astype(np.float64)
+    # a fully transparent block is the reference's fixed pattern
+    assert (blocks[0, 0] == np.array([0, 0, 0, 0, 255, 255, 255, 255], np.uint8)).all()
+    # where the encoder chose the transparent mode, exactly the transparent texels carry index 3
+    by, bx = blocks.shape[:2]
+    chosen = 0
+    for y in range(by):
+        for x in range(bx):
+            c0 = int(blocks[y, x, 0]) | int(blocks[y, x, 1]) << 8
+            c1 = int(blocks[y, x, 2]) | int(blocks[y, x, 3]) << 8
+            tile = source_alpha[y * 4:y * 4 + 4, x * 4:x * 4 + 4]
+            if c0 <= c1 and 0 < (tile == 0).sum() < 16:
+                chosen += 1
+                assert np.array_equal(alpha[y * 4:y * 4 + 4, x * 4:x * 4 + 4] == 0, tile == 0), (y, x)
+    assert chosen >= 10
+    opaque = source_alpha == 1
+    error = np.abs(rgb - np.clip(image[..., :3].astype(np.float64), 0, 1))[opaque & (alpha == 1)]
+    assert np.sqrt(np.mean(error ** 2)) <= 0.05
+
+
+def test_bc2_and_bc3_share_the_colour_block(oracle):
+    image = color_images()["cutout"]
+    bc2, bc3 = oracle.block_compress_color(image, 2, 0, 4), oracle.block_compress_color(image, 3, 0, 4)
+    assert np.array_equal(bc2[..., 8:], bc3[..., 8:])
+    # BC2 alpha: 4 bits per texel, round(15 a); BC3 alpha: the BC4 block of the alpha channel
+    nibbles = np.rint(np.clip(image[..., 3].astype(np.float32), 0, 1) * np.float32(15)).astype(np.uint8)
+    for y in range(bc2.shape[0]):
+        for x in range(bc2.shape[1]):
+            bits = int.from_bytes(bytes(bc2[y, x, :8]), "little")
+            got = np.array([(bits >> (4 * i)) & 15 for i in range(16)]).reshape(4, 4)
+            assert np.array_equal(got, nibbles[y * 4:y * 4 + 4, x * 4:x * 4 + 4])
+    assert np.array_equal(bc3[..., :8], oracle.block_compress(image, 3, 1))
+    # the colour block ignores alpha: the same as BC1 of the opaque image whenever that is a four-colour block
+    opaque = image.copy()
+    opaque[..., 3] = 1
+    bc1 = oracle.block_compress_color(opaque, 1, 0, 4)
+    c0 = bc1[..., 0].astype(np.int32) | bc1[..., 1].astype(np.int32) << 8
+    c1 = bc1[..., 2].astype(np.int32) | bc1[..., 3].astype(np.int32) << 8
+    four = c0 > c1
+    assert four.sum() > 30 and np.array_equal(bc1[four], bc3[..., 8:][four])
+
+
 def test_arguments_are_checked():
     lib = binding.lib()
     assert lib.ntcb_block_compress(None, None) == -1
@@ -125,6 +242,9 @@ def test_arguments_are_checked():
     params.widthInBlocks, params.heightInBlocks, params.rowPitch = 2, 2, 16
     params.format = 7
     assert lib.ntcb_block_compress(params, None) == -5  # BC7: a valid format of the reference, not built here
+    params.format, params.numChannels = binding.BLOCK_FORMAT_BC1, 5
+    assert lib.ntcb_block_compress(params, None) == -9 and b"numChannels" in lib.ntcb_last_error()
+    params.numChannels = 0
     params.format = 9
     assert lib.ntcb_block_compress(params, None) == -9
     params.format, params.firstChannel = binding.BLOCK_FORMAT_BC5, 1
@@ -151,6 +271,24 @@ def test_kernel_matches_the_restated_encoder(oracle, name):
         assert np.array_equal(got, oracle.block_compress(texels, channel, 1)), (name, channel)
     got = binding.block_compress(device, binding.BLOCK_FORMAT_BC5, 1).cpu().numpy()
     assert np.array_equal(got, oracle.block_compress(texels, 1, 2)), name
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["smooth", "noise", "cutout", "flat", "extremes"])
+def test_colour_kernels_match_the_restated_encoders(oracle, name):
+    import torch
+
+    image = color_images()[name]
+    device = torch.from_numpy(image).cuda()
+    for block_format in (binding.BLOCK_FORMAT_BC1, binding.BLOCK_FORMAT_BC2, binding.BLOCK_FORMAT_BC3):
+        for channels in (3, 4):
+            got = binding.block_compress(device, block_format, 0, num_channels=channels).cpu().numpy()
+            expected = oracle.block_compress_color(image, block_format, 0, channels)
+            assert np.array_equal(got, expected), (name, block_format, channels, int((got != expected).any(axis=-1).sum()))
+    ragged = image[:22, :37]
+    got = binding.block_compress(torch.from_numpy(np.ascontiguousarray(ragged)).cuda(), binding.BLOCK_FORMAT_BC1, 0, num_channels=4,
+                                 alpha_threshold=0.5).cpu().numpy()
+    assert np.array_equal(got, oracle.block_compress_color(ragged, 1, 0, 4, alpha_threshold=0.5))
 
 
 @pytest.mark.gpu
