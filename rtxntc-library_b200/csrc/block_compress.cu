@@ -62,21 +62,43 @@ __device__ __forceinline__ void Palette(uint32_t a0, uint32_t a1, uint32_t (&pal
 
 // Nearest palette entry per pixel, the first one on ties; returns the block's squared error
 // (BC4_ComputeAlphaIndices, :605-632).
-__device__ uint32_t AssignIndices(const uint32_t (&values)[16], Bc4Block& block)
+// The sixteen 8-bit values of a block, packed: the loops over the texels stay rolled (a dynamic
+// shift instead of a register array), which keeps the encoder's code a few hundred instructions.
+// Fully unrolled, the kernel spent most of its issue slots waiting for instructions (ncu: stall
+// "no_instruction" 3.7 per issue).
+struct BlockValues
+{
+    uint64_t low = 0, high = 0; // texels 0-7 and 8-15, one byte each
+
+    __device__ __forceinline__ void Set(int pixel, uint32_t value)
+    {
+        if (pixel < 8)
+            low |= uint64_t(value) << (8 * pixel);
+        else
+            high |= uint64_t(value) << (8 * (pixel - 8));
+    }
+    __device__ __forceinline__ uint32_t operator[](int pixel) const
+    {
+        return uint32_t((pixel < 8 ? low : high) >> (8 * (pixel & 7))) & 0xffu;
+    }
+};
+
+__device__ uint32_t AssignIndices(const BlockValues& values, Bc4Block& block)
 {
     uint32_t palette[8];
     Palette(block.alpha0, block.alpha1, palette);
     uint64_t indices = 0;
     uint32_t total = 0;
-#pragma unroll
+#pragma unroll 1
     for (int pixel = 0; pixel < 16; ++pixel)
     {
         int best = 0x7fffffff;
         uint32_t bestIndex = 0;
+        const uint32_t value = values[pixel];
 #pragma unroll
         for (uint32_t p = 0; p < 8; ++p)
         {
-            const int difference = int(values[pixel]) - int(palette[p]);
+            const int difference = int(value) - int(palette[p]);
             const int distance = difference * difference;
             if (distance < best)
             {
@@ -130,10 +152,10 @@ __device__ __forceinline__ uint32_t RoundToByte(float x)
 }
 
 // Least-squares endpoints for the current indices, eight-interpolant mode (BC4_OptimizeAlpha8, :634-670).
-__device__ void RefitEight(const uint32_t (&values)[16], Bc4Block& block, bool zeroAlpha1, bool oneAlpha0)
+__device__ void RefitEight(const BlockValues& values, Bc4Block& block, bool zeroAlpha1, bool oneAlpha0)
 {
     RefitSums sums;
-#pragma unroll
+#pragma unroll 1
     for (int pixel = 0; pixel < 16; ++pixel)
     {
         const uint32_t index = IndexOf(block, pixel);
@@ -154,10 +176,10 @@ __device__ void RefitEight(const uint32_t (&values)[16], Bc4Block& block, bool z
 
 // The same for the six-interpolant mode; pixels on the explicit 0 / 255 entries do not take part
 // (BC4_OptimizeAlpha6, :672-708).
-__device__ void RefitSix(const uint32_t (&values)[16], Bc4Block& block)
+__device__ void RefitSix(const BlockValues& values, Bc4Block& block)
 {
     RefitSums sums;
-#pragma unroll
+#pragma unroll 1
     for (int pixel = 0; pixel < 16; ++pixel)
     {
         const uint32_t index = IndexOf(block, pixel);
@@ -174,7 +196,7 @@ __device__ void RefitSix(const uint32_t (&values)[16], Bc4Block& block)
 
 // Alternates refit and index assignment while the error falls (the two loops of BC4_CompressFast, :741-794).
 template <bool kSix>
-__device__ void Refine(const uint32_t (&values)[16], Bc4Block& block, Bc4Block& best, uint32_t& bestError, bool zeroAlpha1,
+__device__ void Refine(const BlockValues& values, Bc4Block& block, Bc4Block& best, uint32_t& bestError, bool zeroAlpha1,
     bool oneAlpha0)
 {
     for (int pass = 0; pass < 8; ++pass)
@@ -196,7 +218,7 @@ __device__ void Refine(const uint32_t (&values)[16], Bc4Block& block, Bc4Block& 
 
 __device__ uint2 EncodeBc4(const float (&pixels)[16])
 {
-    uint32_t values[16];
+    BlockValues values;
     uint32_t low = 255, high = 0, lowInside = 255, highInside = 0;
 #pragma unroll
     for (int pixel = 0; pixel < 16; ++pixel)
@@ -204,7 +226,7 @@ __device__ uint2 EncodeBc4(const float (&pixels)[16])
         // saturate() sends NaN to 0
         const float saturated = pixels[pixel] != pixels[pixel] ? 0.f : fminf(fmaxf(pixels[pixel], 0.f), 1.f);
         const uint32_t v = uint32_t(rintf(__fmul_rn(saturated, 255.f)));
-        values[pixel] = v;
+        values.Set(pixel, v);
         low = min(low, v);
         high = max(high, v);
         if (v != 0)

@@ -24,19 +24,23 @@ namespace
 // ---------------------------------------------------------------------------------------------
 // Latent packing
 
-// QuantizeValue(value, 4) of src/Quantizer.cu:481-487: clamp to [0, 1], divide by the step 1/15
-// (as a float), round half away from zero.  The quotient of an fp16 value and that step lies at
-// least 2^-16 away from every tie except at 0.5, where every form of the division lands just below
-// 7.5; so the approximate division and the exact one give the same code for every input.  The
-// reference's std::min(1.f, NaN) is 1, so NaN packs as 15; it is tested on the bits here because a
-// min / max clamp to [0, 1] may be compiled to a saturating operation, which turns NaN into 0.
-__device__ __forceinline__ uint32_t LatentCode(__half value)
+// QuantizeValue(value, 4) of src/Quantizer.cu:481-487: clamp to [0, 1] (std::min(1.f, NaN) is 1, so NaN
+// packs as 15), divide by the step fl(1/15), round half away from zero.
+//
+// For an fp16 value v the product 15 v is exact in binary32 and lies at least 2^-16 away from every
+// rounding tie, except v = 0.5 (15 v = 7.5), where the reference's quotient 0.5 / fl(1/15) falls
+// just below the tie and rounds to 7.  Hence code = floor(v * m + 0.5) with m = 15 - 2^-20: the
+// shortfall (at most 1e-6) moves nothing across an integer but sends 7.5 to 7.  The floor and the
+// conversion to an integer are folded into the same fused multiply-add: adding 2^22 + 0.5 with
+// rounding towards minus infinity leaves floor-to-halves of v * m + 0.5 in the low mantissa bits
+// (units of 0.5 in [2^22, 2^23)), so bits 1-4 of the result are the code.  Two half-precision
+// min / max clamp a pair (they return the other operand for NaN), then one conversion, one
+// multiply-add, one shift and one logic operation per code - the first version (approximate
+// division, roundf, a float-to-integer conversion: 14 instructions per code) was bound by
+// instruction issue, not by memory.
+__device__ __forceinline__ uint32_t CodeBits(float clamped)
 {
-    const float step = 1.f / 15.f;
-    if ((__half_as_ushort(value) & 0x7fffu) > 0x7c00u)
-        return 15u;
-    const float v = fmaxf(0.f, fminf(1.f, __half2float(value)));
-    return uint32_t(roundf(ApproxDivide(v, step)));
+    return __float_as_uint(__fmaf_rd(clamped, 14.99999905f, 4194304.5f));
 }
 
 __device__ __forceinline__ __half2 AsHalf2Bits(uint32_t bits)
@@ -46,8 +50,11 @@ __device__ __forceinline__ __half2 AsHalf2Bits(uint32_t bits)
 
 __device__ __forceinline__ uint32_t LatentWord(__half2 first, __half2 second)
 {
-    return LatentCode(__low2half(first)) | (LatentCode(__high2half(first)) << 4)
-         | (LatentCode(__low2half(second)) << 8) | (LatentCode(__high2half(second)) << 12);
+    const __half2 zero = __float2half2_rn(0.f), one = __float2half2_rn(1.f);
+    const float2 a = __half22float2(__hmax2(__hmin2(first, one), zero));
+    const float2 b = __half22float2(__hmax2(__hmin2(second, one), zero));
+    return ((CodeBits(a.x) >> 1) & 0xfu) | ((CodeBits(a.y) << 3) & 0xf0u) | ((CodeBits(b.x) << 7) & 0xf00u)
+         | ((CodeBits(b.y) << 11) & 0xf000u);
 }
 
 // One thread per latent texel and layer; any width, stride and alignment.
