@@ -406,6 +406,13 @@ typedef struct NtcbBlockCompressParams
 } NtcbBlockCompressParams;
 int ntcb_block_compress(const NtcbBlockCompressParams* params, void* stream);
 
+/* The same for one whole mip of a decompressed texture set (NTCB_ERR_INVALID_STATE before
+   ntcb_texture_set_decompress): (width + 3) / 4 by (height + 3) / 4 blocks into device memory,
+   `rowPitch` bytes between rows of blocks, queued on the texture set's stream
+   (ntcb_texture_set_synchronize waits for it). */
+int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, int firstChannel, int numChannels, int format,
+    float alphaThreshold, void* deviceBlocks, size_t rowPitch);
+
 /* Size of the staging area built into the library for ntcb_read_channels_to_host_noalloc. */
 #define NTCB_NOALLOC_STAGING_BYTES (4u << 20)
 

@@ -58,6 +58,10 @@ public:
         NtcbOutputConversion const& conversion, int addressSpace, void* destination, size_t destinationBytes) = 0;
     virtual Status ReadChannels(ReadChannelsParameters const& params) = 0;
     virtual Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) = 0;
+    // One decoded mip to BC1 - BC5 blocks in device memory (see ntcb_block_compress), queued on the
+    // set's stream: the whole mip, (width + 3) / 4 blocks per row, rowPitch bytes between rows of blocks.
+    virtual Status BlockCompress(int mipLevel, int firstChannel, int numChannels, int format, float alphaThreshold,
+        void* deviceBlocks, size_t rowPitch) = 0;
     virtual Status Synchronize() = 0;
     virtual ~ITextureSet() = default;
 };

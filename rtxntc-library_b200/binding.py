@@ -164,6 +164,8 @@ def lib():
                                              ctypes.c_void_p, ctypes.c_void_p]
         handle.ntcb_quantize_network.argtypes = [ctypes.POINTER(QuantizeNetworkParams), ctypes.c_void_p]
         handle.ntcb_block_compress.argtypes = [ctypes.POINTER(BlockCompressParams), ctypes.c_void_p]
+        handle.ntcb_texture_set_block_compress.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                           ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t]
         handle.ntcb_texture_set_device_mip.argtypes = [
             ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t)]
         handle.ntcb_texture_set_synchronize.argtypes = [ctypes.c_void_p]
@@ -583,6 +585,22 @@ class TextureSet:
             mips.append(flat[offset:offset + count].reshape(h, w, conversion.components))
             offset += count
         return mips, (stats.gpuTimeMilliseconds if want_stats else None)
+
+    def block_compress(self, mip: int, block_format: int, first_channel: int = 0, num_channels: int = 0,
+                       alpha_threshold: float = 1.0 / 255.0):
+        """One decoded mip as BC1 - BC5 blocks: a CUDA uint8 tensor [blocks_y][blocks_x][8 or 16]
+        (waits for the texture set's stream)."""
+        import torch
+
+        width, height = self.mip_size(mip)
+        bw, bh = (width + 3) // 4, (height + 3) // 4
+        block_bytes = 8 if block_format in (BLOCK_FORMAT_BC1, BLOCK_FORMAT_BC4) else 16
+        out = torch.zeros((bh, bw, block_bytes), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        check(lib().ntcb_texture_set_block_compress(self.handle, mip, first_channel, num_channels, block_format,
+                                                    alpha_threshold, ctypes.c_void_p(out.data_ptr()), bw * block_bytes))
+        self.synchronize()
+        return out
 
     def device_mip(self, mip: int) -> Tuple[int, int]:
         """Device address and size in bytes of one decoded mip in the internal layout."""

@@ -161,6 +161,8 @@ public:
         int addressSpace, void* destination, size_t destinationBytes) override;
     Status ReadChannels(ReadChannelsParameters const& params) override;
     Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) override;
+    Status BlockCompress(int mipLevel, int firstChannel, int numChannels, int format, float alphaThreshold,
+        void* deviceBlocks, size_t rowPitch) override;
     Status Synchronize() override;
 
     const SetGeometry& Geometry() const { return m_geometry; }
@@ -878,6 +880,39 @@ Status TextureSet::GetDeviceMip(int mipLevel, void** outPointer, size_t* outByte
     return NTCB_OK;
 }
 
+Status TextureSet::BlockCompress(int mipLevel, int firstChannel, int numChannels, int format, float alphaThreshold,
+    void* deviceBlocks, size_t rowPitch)
+{
+    if (!m_decoded)
+    {
+        SetError("BlockCompress needs decoded texels: call Decompress first.");
+        return NTCB_ERR_INVALID_STATE;
+    }
+    if (mipLevel < 0 || mipLevel >= m_geometry.mips)
+    {
+        SetError("mipLevel (%d) must be between 0 and %d.", mipLevel, m_geometry.mips - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+    NtcbBlockCompressParams params = {};
+    params.deviceMip = m_texels + m_geometry.mipTexelOffset[mipLevel] * m_geometry.channels;
+    params.layout = m_layout;
+    params.width = m_geometry.mipWidth[mipLevel];
+    params.height = m_geometry.mipHeight[mipLevel];
+    params.channels = m_geometry.channels;
+    params.firstChannel = firstChannel;
+    params.numChannels = numChannels;
+    params.format = format;
+    params.alphaThreshold = alphaThreshold;
+    params.widthInBlocks = (params.width + 3) / 4;
+    params.heightInBlocks = (params.height + 3) / 4;
+    params.deviceBlocks = deviceBlocks;
+    params.rowPitch = rowPitch;
+    return ntcb_block_compress(&params, m_stream);
+}
+
 Status TextureSet::Synchronize()
 {
     DeviceGuard guard(m_device);
@@ -1111,6 +1146,17 @@ int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void**
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     return textureSet->impl->GetDeviceMip(mipLevel, outPointer, outBytes);
+}
+
+int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, int firstChannel, int numChannels, int format,
+    float alphaThreshold, void* deviceBlocks, size_t rowPitch)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->BlockCompress(mipLevel, firstChannel, numChannels, format, alphaThreshold, deviceBlocks, rowPitch);
 }
 
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet)

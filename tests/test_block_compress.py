@@ -337,3 +337,23 @@ def test_decoded_texture_set_to_bc5(oracle):
             decoded = decode_bc4(np.ascontiguousarray(blocks[..., 8 * k:8 * k + 8]))[:h, :w]
             mse = np.mean((decoded - source) ** 2)
             assert mse <= 40.0, (mip, k, mse)  # > 32 dB on noise-like synthetic texels
+
+
+@pytest.mark.gpu
+def test_texture_set_block_compress(oracle):
+    """The texture-set level call: NTCB_ERR_INVALID_STATE before Decompress, then the same blocks as
+    the restated encoder makes of the texels ReadChannels hands back."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(72, 40, 6, 0, 2, 8, seed=4, network="unit"))
+    with binding.Context() as context:
+        texture_set = context.create_texture_set(data.container)
+        with pytest.raises(binding.NtcbError) as error:
+            texture_set.block_compress(0, binding.BLOCK_FORMAT_BC4, 1)
+        assert error.value.code == -8
+        texture_set.decompress(False)
+        for mip in (0, 2):
+            texels = texture_set.read_mip(mip)
+            assert np.array_equal(texture_set.block_compress(mip, binding.BLOCK_FORMAT_BC4, 1).cpu().numpy(),
+                                  oracle.block_compress(texels, 1, 1))
+            assert np.array_equal(texture_set.block_compress(mip, binding.BLOCK_FORMAT_BC3, 0, 4).cpu().numpy(),
+                                  oracle.block_compress_color(texels, 3, 0, 4))
+        texture_set.close()
