@@ -540,7 +540,7 @@ def run_producers_case(side: int) -> int:
 
 
 def run_block_compress_case(side: int) -> int:
-    """Times BC4, BC5, BC1 and BC3 encoding of a SIDE x SIDE mip of 12 interleaved fp16 channels (random texels
+    """Times BC4, BC5, BC1, BC2 and BC3 encoding of a SIDE x SIDE mip of 12 interleaved fp16 channels (random texels
     with smooth and noisy regions; larger than L2 from SIDE = 4096 up).  Prints a plain line per
     format, not the benchmark's JSON line."""
     import numpy as np
@@ -556,7 +556,8 @@ def run_block_compress_case(side: int) -> int:
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     peak, source = measured_peak_gbs()
     for block_format, name, channels in ((binding.BLOCK_FORMAT_BC4, "BC4", 1), (binding.BLOCK_FORMAT_BC5, "BC5", 2),
-                                         (binding.BLOCK_FORMAT_BC1, "BC1", 3), (binding.BLOCK_FORMAT_BC3, "BC3", 4)):
+                                         (binding.BLOCK_FORMAT_BC1, "BC1", 3), (binding.BLOCK_FORMAT_BC2, "BC2", 4),
+                                         (binding.BLOCK_FORMAT_BC3, "BC3", 4)):
         times = []
         for _ in range(13):
             start.record()

@@ -279,6 +279,24 @@ __device__ __forceinline__ float LoadChannel(const BlockCompressArguments& args,
     return __half2float(args.texels[index]);
 }
 
+__device__ __forceinline__ __half LoadHalf(const BlockCompressArguments& args, int x, int y, int channel)
+{
+    const size_t w = size_t(args.width), c = size_t(args.channels);
+    const size_t index = args.layout == NTCB_LAYOUT_INTERLEAVED
+        ? (size_t(y) * w + size_t(x)) * c + size_t(channel)
+        : size_t(y) * w * c + size_t(channel & ~1) * w + 2 * size_t(x) + size_t(channel & 1);
+    return args.texels[index];
+}
+
+// Channels `channel` (even) and `channel + 1` of one texel as one word; needs an even channel count.
+__device__ __forceinline__ uint32_t LoadPair(const BlockCompressArguments& args, int x, int y, int channel)
+{
+    const size_t w = size_t(args.width), c = size_t(args.channels);
+    const size_t index = args.layout == NTCB_LAYOUT_INTERLEAVED ? (size_t(y) * w + size_t(x)) * c + size_t(channel)
+                                                                 : size_t(y) * w * c + size_t(channel) * w + 2 * size_t(x);
+    return *reinterpret_cast<const uint32_t*>(args.texels + index);
+}
+
 // One thread per 4x4 block and channel: BC5 is two BC4 blocks side by side, encoded by two threads
 // (blockIdx.z = the channel), which keeps one copy of the encoder's code and its register count.
 __global__ void __launch_bounds__(128) BlockCompressKernel(const BlockCompressArguments args)
@@ -491,11 +509,33 @@ __device__ __forceinline__ Rgb KeepExtremes(Rgb current, Rgb refitted)
     return {KeepExtreme(current.r, refitted.r), KeepExtreme(current.g, refitted.g), KeepExtreme(current.b, refitted.b)};
 }
 
+// The sixteen texels of a block, staged in shared memory as four halves each (the input is fp16, so
+// nothing is lost), texel i of thread t at word i * 128 + t: conflict-free to read, and indexable, so
+// the loops over the texels stay rolled.  Held in registers (64 of them) with every loop unrolled, the
+// BC1 kernel needed 158 registers and waited for instructions.
+struct BlockTexels
+{
+    const uint2* base;
+    bool opaque; // alpha reads as 1
+
+    __device__ __forceinline__ Texel operator[](int i) const
+    {
+        const uint2 raw = base[i * 128];
+        const float2 rg = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 ba = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        return {{rg.x, rg.y, ba.x}, opaque ? 1.f : ba.y};
+    }
+    __device__ __forceinline__ float Alpha(int i) const
+    {
+        return __high2float(*reinterpret_cast<const __half2*>(&base[i * 128].y));
+    }
+};
+
 // The whole block as one colour, through the match tables (BC1_EncodeSingleColor, :205-247).
-__device__ uint2 EncodeSingleColor(const Texel (&texels)[16], float& blockError)
+__device__ uint2 EncodeSingleColor(const BlockTexels& texels, float& blockError)
 {
     Rgb sum{0.f, 0.f, 0.f};
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
         sum = Add(sum, texels[i].rgb);
     const Rgb average = {__fdiv_rn(sum.r, 16.f), __fdiv_rn(sum.g, 16.f), __fdiv_rn(sum.b, 16.f)};
@@ -513,25 +553,26 @@ __device__ uint2 EncodeSingleColor(const Texel (&texels)[16], float& blockError)
         result = make_uint2((color1 << 16) | color0, 0xaaaaaaaau);
     const Rgb encoded = Lerp(Expand565(color0), Expand565(color1), 1.0f / 3.0f);
     blockError = 0.f;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
     {
-        const Texel difference = {Sub(texels[i].rgb, encoded), Sub(texels[i].a, 1.f)};
+        const Texel texel = texels[i];
+        const Texel difference = {Sub(texel.rgb, encoded), Sub(texel.a, 1.f)};
         blockError = Add(blockError, Dot4(difference));
     }
     return result;
 }
 
 // Four-colour mode: endpoints from the extremes, refined by least squares (BC1_CompressFast, :249-376).
-__device__ uint2 EncodeFourColors(const Texel (&texels)[16], float& blockError)
+__device__ uint2 EncodeFourColors(const BlockTexels& texels, float& blockError)
 {
     Extremes extremes;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
         extremes.Include(texels[i].rgb);
     const Rgb center = {__fdiv_rn(extremes.sums.r, 16.f), __fdiv_rn(extremes.sums.g, 16.f), __fdiv_rn(extremes.sums.b, 16.f)};
     Covariance covariance;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
         covariance.Include(texels[i].rgb, center);
     OrientAndInset(extremes, covariance, 16.f);
@@ -542,15 +583,16 @@ __device__ uint2 EncodeFourColors(const Texel (&texels)[16], float& blockError)
     {
         const Palette4 palette(maxColor, minColor);
         ColorRefit refit;
-#pragma unroll
+#pragma unroll 1
         for (int i = 0; i < 16; ++i)
         {
             float ignored;
-            const uint32_t index = palette.Index(texels[i], ignored);
+            const Texel texel = texels[i];
+            const uint32_t index = palette.Index(texel, ignored);
             float beta = float(index & 1u);
             if (index & 2u)
                 beta = __fdiv_rn(Add(1.f, beta), 3.0f);
-            refit.Include(beta, texels[i].rgb);
+            refit.Include(beta, texel.rgb);
         }
         Rgb a, b;
         if (refit.Solve(a, b))
@@ -594,7 +636,7 @@ __device__ uint2 EncodeFourColors(const Texel (&texels)[16], float& blockError)
     const Palette4 palette(maxColor, minColor);
     uint32_t indices = 0;
     blockError = 0.f;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
     {
         float pixelError;
@@ -605,38 +647,45 @@ __device__ uint2 EncodeFourColors(const Texel (&texels)[16], float& blockError)
 }
 
 // Three colours and transparent black: one refit, transparent texels left out (BC1a_CompressFast, :378-493).
-__device__ uint2 EncodeThreeColors(const Texel (&texels)[16], float alphaThreshold, float& blockError)
+__device__ uint2 EncodeThreeColors(const BlockTexels& texels, float alphaThreshold, float& blockError)
 {
     Extremes extremes;
     int opaque = 0;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
-        if (!(texels[i].a <= alphaThreshold))
+    {
+        const Texel texel = texels[i];
+        if (!(texel.a <= alphaThreshold))
         {
-            extremes.Include(texels[i].rgb);
+            extremes.Include(texel.rgb);
             ++opaque;
         }
+    }
     const float count = float(opaque);
     const Rgb center = opaque > 0 ? Rgb{__fdiv_rn(extremes.sums.r, count), __fdiv_rn(extremes.sums.g, count), __fdiv_rn(extremes.sums.b, count)}
                                   : Rgb{0.f, 0.f, 0.f};
     Covariance covariance;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
-        if (!(texels[i].a <= alphaThreshold))
-            covariance.Include(texels[i].rgb, center);
+    {
+        const Texel texel = texels[i];
+        if (!(texel.a <= alphaThreshold))
+            covariance.Include(texel.rgb, center);
+    }
     OrientAndInset(extremes, covariance, count);
     Rgb maxColor = extremes.high, minColor = extremes.low;
 
     ColorRefit refit;
     {
         const Palette3 palette(maxColor, minColor, alphaThreshold);
-#pragma unroll
+#pragma unroll 1
         for (int i = 0; i < 16; ++i)
         {
             float ignored;
-            const uint32_t index = palette.Index(texels[i], ignored);
+            const Texel texel = texels[i];
+            const uint32_t index = palette.Index(texel, ignored);
             if (index != 3u)
-                refit.Include((index & 2u) ? 0.5f : float(index & 1u), texels[i].rgb);
+                refit.Include((index & 2u) ? 0.5f : float(index & 1u), texel.rgb);
         }
     }
     Rgb a, b;
@@ -661,26 +710,27 @@ __device__ uint2 EncodeThreeColors(const Texel (&texels)[16], float alphaThresho
     const Palette3 palette(maxColor, minColor, alphaThreshold);
     uint32_t indices = 0;
     blockError = 0.f;
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
     {
         float pixelError;
-        const uint32_t index = palette.Index(texels[i], pixelError);
+        const Texel texel = texels[i];
+        const uint32_t index = palette.Index(texel, pixelError);
         indices |= index << (2 * i);
-        if (index != 3u || !(texels[i].a <= alphaThreshold))
+        if (index != 3u || !(texel.a <= alphaThreshold))
             blockError = Add(blockError, pixelError);
     }
     return make_uint2((color1 << 16) | color0, indices);
 }
 
 // BC2's alpha: 4 bits per texel (BC2_EncodeAlpha, :495-508).
-__device__ uint2 EncodeAlpha4(const float (&alphas)[16])
+__device__ uint2 EncodeAlpha4(const BlockTexels& texels)
 {
     uint2 block = make_uint2(0u, 0u);
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 16; ++i)
     {
-        const uint32_t value = uint32_t(rintf(Mul(Saturate(alphas[i]), 15.f)));
+        const uint32_t value = uint32_t(rintf(Mul(Saturate(texels.Alpha(i)), 15.f)));
         if (i < 8)
             block.x |= value << (4 * i);
         else
@@ -700,25 +750,51 @@ struct ColorCompressArguments
 template <int kFormat>
 __global__ void __launch_bounds__(128) ColorBlockCompressKernel(const ColorCompressArguments args)
 {
+    __shared__ uint2 staged[16 * 128];
+    // The CTA's 64 x 32 texels are loaded with neighbouring threads on neighbouring texels of a row
+    // (coalesced) and handed to the thread that owns their block through shared memory.
+    // an even first channel of an even channel count: channel pairs are aligned 32-bit words in both layouts
+    const bool pairs = !(args.base.firstChannel & 1) && !(args.base.channels & 1);
+#pragma unroll 1
+    for (int k = 0; k < 16; ++k)
+    {
+        const int p = k * 128 + threadIdx.x;
+        const int localX = p & 63, localY = p >> 6;
+        const int x = args.base.srcLeft + blockIdx.x * 64 + localX, y = args.base.srcTop + blockIdx.y * 32 + localY;
+        const bool inside = x < args.base.width && y < args.base.height;
+        // red-green and blue-alpha as two 32-bit words; missing channels read 0, alpha 1 (0x3c00)
+        uint32_t redGreen = 0u, blueAlpha = 0u;
+        if (inside)
+        {
+            const int first = args.base.firstChannel, count = args.numChannels;
+            if (pairs)
+            {
+                redGreen = count >= 2 ? LoadPair(args.base, x, y, first) : uint32_t(__half_as_ushort(LoadHalf(args.base, x, y, first)));
+                blueAlpha = count == 4 ? LoadPair(args.base, x, y, first + 2)
+                          : (count == 3 ? uint32_t(__half_as_ushort(LoadHalf(args.base, x, y, first + 2))) : 0u) | 0x3c000000u;
+            }
+            else
+            {
+                uint32_t c[4] = {0u, 0u, 0u, 0x3c00u};
+#pragma unroll
+                for (int channel = 0; channel < 4; ++channel)
+                    if (channel < count)
+                        c[channel] = __half_as_ushort(LoadHalf(args.base, x, y, first + channel));
+                redGreen = c[0] | (c[1] << 16);
+                blueAlpha = c[2] | (c[3] << 16);
+            }
+        }
+        const int owner = (localY >> 2) * 16 + (localX >> 2), texel = (localY & 3) * 4 + (localX & 3);
+        staged[texel * 128 + owner] = make_uint2(redGreen, blueAlpha);
+    }
+    __syncthreads();
     const int blockX = blockIdx.x * 16 + (threadIdx.x & 15);
     const int blockY = blockIdx.y * 8 + (threadIdx.x >> 4);
     if (blockX >= args.base.widthInBlocks || blockY >= args.base.heightInBlocks)
         return;
-    Texel texels[16];
-    float alphas[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-    {
-        const int x = args.base.srcLeft + blockX * 4 + (i & 3), y = args.base.srcTop + blockY * 4 + (i >> 2);
-        const bool inside = x < args.base.width && y < args.base.height;
-        float c[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-            c[k] = !inside ? 0.f : k < args.numChannels ? LoadChannel(args.base, x, y, args.base.firstChannel + k) : (k == 3 ? 1.f : 0.f);
-        texels[i].rgb = {c[0], c[1], c[2]};
-        texels[i].a = kFormat == NTCB_BLOCK_FORMAT_BC1 ? c[3] : 1.f;
-        alphas[i] = c[3];
-    }
+    BlockTexels texels;
+    texels.base = staged + threadIdx.x;
+    texels.opaque = kFormat != NTCB_BLOCK_FORMAT_BC1; // BC2 / BC3 colour blocks ignore alpha
 
     float bestError;
     uint2 best;
@@ -726,10 +802,13 @@ __global__ void __launch_bounds__(128) ColorBlockCompressKernel(const ColorCompr
     {
         // BC1a_TransparentBlock: everything transparent; the error is what the opaque texels lose
         bestError = 0.f;
-#pragma unroll
+#pragma unroll 1
         for (int i = 0; i < 16; ++i)
-            if (!(texels[i].a <= args.alphaThreshold))
-                bestError = Add(bestError, Dot4(texels[i]));
+        {
+            const Texel texel = texels[i];
+            if (!(texel.a <= args.alphaThreshold))
+                bestError = Add(bestError, Dot4(texel));
+        }
         best = make_uint2(0u, 0xffffffffu);
         float error;
         const uint2 single = EncodeSingleColor(texels, error);
@@ -761,11 +840,11 @@ __global__ void __launch_bounds__(128) ColorBlockCompressKernel(const ColorCompr
     }
     else if (kFormat == NTCB_BLOCK_FORMAT_BC2)
     {
-        const uint2 alpha = EncodeAlpha4(alphas);
+        const uint2 alpha = EncodeAlpha4(texels);
         reinterpret_cast<uint4*>(destination)[blockX] = make_uint4(alpha.x, alpha.y, best.x, best.y);
     }
-    else // BC3: the alpha half is a BC4 block, written by BlockCompressKernel in a launch of its own
-        reinterpret_cast<uint2*>(destination)[2 * blockX + 1] = best;
+    else // BC3: the alpha half is a BC4 block, written afterwards by BlockCompressKernel in a launch of its own
+        reinterpret_cast<uint4*>(destination)[blockX] = make_uint4(0u, 0u, best.x, best.y);
 }
 
 // Entry i: the endpoint pair (mx | mn << 8) that minimises 1000 * |(2 * e(mx) + e(mn)) / 3 - i| +

@@ -292,6 +292,35 @@ def test_colour_kernels_match_the_restated_encoders(oracle, name):
 
 
 @pytest.mark.gpu
+def test_colour_kernels_with_odd_channel_offsets_and_the_planar_layout(oracle):
+    """Channel pairs are read as 32-bit words when the first channel and the channel count are even;
+    every other combination takes single-channel reads."""
+    import torch
+
+    rng = np.random.default_rng(8)
+    for channels in (5, 6):
+        image = rng.uniform(0, 1, (26, 45, channels)).astype(np.float16)
+        image[..., -1] = (rng.uniform(size=(26, 45)) < 0.7)
+        device = torch.from_numpy(image).cuda()
+        for first, count in ((0, 4), (1, 4), (2, 3), (1, 3), (channels - 1, 1), (2, 2)):
+            if first + count > channels:
+                continue
+            for block_format in (binding.BLOCK_FORMAT_BC1, binding.BLOCK_FORMAT_BC3):
+                got = binding.block_compress(device, block_format, first, num_channels=count).cpu().numpy()
+                assert np.array_equal(got, oracle.block_compress_color(image, block_format, first, count)), (channels, first, count)
+    image = rng.uniform(0, 1, (26, 45, 6)).astype(np.float16)
+    h, w, c = image.shape
+    planar = np.zeros(h * w * c, np.float16)
+    for ch in range(c):
+        for y in range(h):
+            planar[y * w * c + (ch & ~1) * w + (ch & 1):y * w * c + (ch & ~1) * w + 2 * w:2] = image[y, :, ch]
+    for first, count in ((0, 4), (2, 4), (1, 3)):
+        got = binding.block_compress(torch.from_numpy(planar).cuda(), binding.BLOCK_FORMAT_BC1, first, layout=binding.LAYOUT_PLANAR_PAIRS,
+                                     width=w, height=h, channels=c, num_channels=count).cpu().numpy()
+        assert np.array_equal(got, oracle.block_compress_color(image, 1, first, count)), (first, count)
+
+
+@pytest.mark.gpu
 def test_kernel_on_ragged_images_windows_and_the_planar_layout(oracle):
     import torch
 
