@@ -7,6 +7,7 @@
 
 #include "error.h"
 #include "json_mini.h"
+#include "network_shape.h"
 #include "ntcb.h"
 
 namespace ntcb
@@ -162,9 +163,6 @@ const std::vector<json::Value>* GetArray(const json::Value& object, const char* 
         return nullptr;
     return &v->items;
 }
-
-constexpr int kLayerInputs[4] = {48, 64, 48, 32};
-constexpr int kLayerOutputs[4] = {64, 48, 32, 16};
 
 struct Reader
 {

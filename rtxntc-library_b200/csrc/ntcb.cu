@@ -15,6 +15,7 @@
 
 #include "decode_kernel.h"
 #include "error.h"
+#include "network_shape.h"
 
 namespace ntcb
 {
@@ -50,8 +51,6 @@ void CountLaunch()
 namespace
 {
 
-constexpr int kLayerInputs[4] = {48, 64, 48, 32};
-constexpr int kLayerOutputs[4] = {64, 48, 32, 16};
 constexpr int kBiasSlots[4] = {16, 32, 48, 32};    // K slots that carry the bias of an int8 layer
 constexpr int kWeightOffsets[4] = {kWeightOffset0, kWeightOffset1, kWeightOffset2, kWeightOffset3};
 constexpr int kRefWeightOffsets[4] = {kRefWeightOffset0, kRefWeightOffset1, kRefWeightOffset2, kRefWeightOffset3};

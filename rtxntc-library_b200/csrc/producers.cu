@@ -13,6 +13,7 @@
 #include <stdint.h>
 
 #include "error.h"
+#include "network_shape.h"
 #include "ntcb.h"
 #include "output_convert.cuh"
 
@@ -101,11 +102,9 @@ __global__ void PackLatentsWideKernel(const uint4* __restrict__ latents, uint64_
 // ---------------------------------------------------------------------------------------------
 // Network quantisation
 
-constexpr int kLayers = 4;
-__host__ __device__ constexpr int LayerInputs(int layer) { return layer == 0 ? 48 : layer == 1 ? 64 : layer == 2 ? 48 : 32; }
-__host__ __device__ constexpr int LayerOutputs(int layer) { return layer == 0 ? 64 : layer == 1 ? 48 : layer == 2 ? 32 : 16; }
-constexpr int kColumns = 64 + 48 + 32 + 16;
-constexpr int kWeights = 48 * 64 + 64 * 48 + 48 * 32 + 32 * 16;
+constexpr int kLayers = kMlpLayers;
+constexpr int kColumns = kNetworkColumns;
+constexpr int kWeights = kNetworkWeights;
 
 struct QuantizeArguments
 {
