@@ -10,7 +10,9 @@
 //   IContext::DestroyTextureSet                         -> same name
 //   ITextureSet::GetDesc / GetLatentShape               -> same names
 //   ITextureSet::Decompress(stats, useInt8Weights)      -> same name, same default (FP8 weights)
-//   ITextureSet::ReadChannels(params)                   -> same name (ChannelFormat::FLOAT16)
+//   ITextureSet::ReadChannels(params)                   -> same name (every ChannelFormat, colour spaces, dithering)
+//   IContext::MakeBlockCompressionComputePass + dispatch -> ITextureSet::BlockCompress (BC1 - BC5, CUDA)
+// tests/cpp/host_example.cpp is a complete client.
 //
 // Status values are the NtcbStatus codes of ntcb.h; ntcb::GetLastErrorMessage() returns the
 // thread-local message of the last failing call, like ntc::GetLastErrorMessage().

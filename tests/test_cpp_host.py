@@ -1,0 +1,69 @@
+"""The C++ host interface (include/ntcb_host.h) used from a C++ program, as a client of the
+reference's ntc::IContext / ITextureSet would use it: tests/cpp/host_example.cpp is compiled against
+the header, linked with the library and run.  Without a GPU it must fail loudly at CreateContext;
+on a GPU its texels and BC4 blocks must be the ones the Python binding gets through the C ABI."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+
+entry.load_package()
+from rtxntc_library_b200 import binding, synthetic  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PACKAGE = os.path.join(ROOT, "rtxntc-library_b200")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+
+
+def _build(tmp_path) -> str:
+    binary = str(tmp_path / "host_example")
+    subprocess.run([NVCC, "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp", "host_example.cpp"),
+                    "-o", binary, "-L", PACKAGE, "-lntcb200", "-Xlinker", "-rpath", "-Xlinker", PACKAGE], check=True)
+    return binary
+
+
+def _fnv1a(data: bytes) -> int:
+    value = 1469598103934665603
+    for chunk in np.frombuffer(data, dtype=np.uint8):
+        value = ((value ^ int(chunk)) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return value
+
+
+def _container(tmp_path):
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(48, 24, 4, 0, 2, 8, seed=17, network="unit", weights="fp8"))
+    path = tmp_path / "set.ntc"
+    path.write_bytes(data.container)
+    return data, str(path)
+
+
+def test_cpp_client_builds_and_fails_loudly_without_a_gpu(tmp_path):
+    import torch
+
+    binary = _build(tmp_path)
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: covered by the GPU test")
+    _, path = _container(tmp_path)
+    result = subprocess.run([binary, path], capture_output=True, text=True)
+    assert result.returncode == 2, result.stderr
+    assert "CreateContext" in result.stderr and "cuda" in result.stderr.lower()
+
+
+@pytest.mark.gpu
+def test_cpp_client_matches_the_c_abi(tmp_path):
+    binary = _build(tmp_path)
+    data, path = _container(tmp_path)
+    result = subprocess.run([binary, path], capture_output=True, text=True)
+    assert result.returncode == 0, result.stderr
+    fields = result.stdout.split()
+    with binding.Context() as context:
+        texture_set = context.create_texture_set(data.container)
+        texture_set.decompress(False)
+        texels = texture_set.read_mip(0)
+        blocks = texture_set.block_compress(0, binding.BLOCK_FORMAT_BC4, 0).cpu().numpy()
+        texture_set.close()
+    assert int(fields[1], 16) == _fnv1a(np.ascontiguousarray(texels).tobytes())
+    assert int(fields[3], 16) == _fnv1a(blocks.tobytes())
+    assert fields[5] == "48x24x4"
