@@ -443,7 +443,8 @@ def run_reference(args) -> dict:
     value = texels * args.steps / seconds / 1e9
     kernel_value = texels / (statistics.mean(kernel_ms) / 1e3) / 1e9
     return {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "gpus_used": 1,
+        "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": seconds * 1e3 / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 x f16 -> f16 (wmma), as the reference's CUDA decoder computes",
         "data": "synthetic (seeded latents and weights of the configuration's shape)",
