@@ -241,7 +241,8 @@ typedef struct NtcbReadChannelsParams
     int32_t mipLevel, firstChannel, numChannels;
     int32_t addressSpace;  /* NTCB_ADDRESS_SPACE_* */
     void* pOutData;
-    int32_t width, height; /* must equal the mip's size (the reference's bilinear resize is not offered) */
+    int32_t width, height; /* the mip's size; any other positive size resizes bilinearly, as the reference does
+                              (SetupBilinearFilter, src/ImageProcessing.cu:24-71) */
     int32_t channelFormat; /* NTCB_CHANNEL_FORMAT_* */
     int32_t useDithering;  /* nonzero: hash-based dither before rounding to UNORM8 / UNORM16 */
     size_t pixelStride, rowPitch; /* bytes; pixelStride / bytes-per-component components are written per

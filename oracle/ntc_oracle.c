@@ -858,22 +858,52 @@ static void write_component(uint8_t* dst, int ch, int format, int space, float v
     }
 }
 
-int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* p, uint8_t* out)
+/* SetupBilinearFilter, src/ImageProcessing.cu:24-71 (the reference's division here is the GPU's
+   approximate one; an exact one stands in, so a tap position on an exact texel boundary or a
+   weight's last bit can differ). */
+static void bilinear_filter(int srcWidth, int srcHeight, int dstWidth, int dstHeight, int x, int y, int* sx, int* sy, float w[4])
+{
+    if (srcWidth == dstWidth && srcHeight == dstHeight)
+    {
+        *sx = x;
+        *sy = y;
+        w[0] = 1.f;
+        w[1] = w[2] = w[3] = 0.f;
+        return;
+    }
+    const float u = ((float)x + 0.5f) / (float)dstWidth, v = ((float)y + 0.5f) / (float)dstHeight;
+    float px = fmaf(u, (float)srcWidth, -0.5f), py = fmaf(v, (float)srcHeight, -0.5f);
+    px = fmaxf(0.f, fminf((float)srcWidth - 1.f, px));
+    py = fmaxf(0.f, fminf((float)srcHeight - 1.f, py));
+    *sx = (int)floorf(px);
+    *sy = (int)floorf(py);
+    const float fx = px - floorf(px), fy = py - floorf(py);
+    w[0] = (1.f - fx) * (1.f - fy);
+    w[1] = fx * (1.f - fy);
+    w[2] = (1.f - fx) * fy;
+    w[3] = fx * fy;
+}
+
+/* CopyImageKernel, src/ImageProcessing.cu:220-266: `p` describes the source mip and the request,
+   (dstWidth, dstHeight) the size handed back (the mip's size: a 1:1 copy; any other: bilinear). */
+int ntco_read_channels_resized(const uint16_t* texels, const NtcoReadChannels* p, int dstWidth, int dstHeight, uint8_t* out)
 {
     if (!texels || !p || !out)
         return -1;
     const int componentBytes = bytes_per_component(p->channelFormat);
-    if (!componentBytes || p->width <= 0 || p->height <= 0 || p->firstChannel < 0 || p->numChannels < 1 ||
-        p->firstChannel + p->numChannels > p->channels || p->pixelStride < 1 || p->rowPitch < p->pixelStride)
+    if (!componentBytes || p->width <= 0 || p->height <= 0 || dstWidth <= 0 || dstHeight <= 0 || p->firstChannel < 0 ||
+        p->numChannels < 1 || p->firstChannel + p->numChannels > p->channels || p->pixelStride < 1 || p->rowPitch < p->pixelStride)
         return -1;
     const int dstChannels = (int)(p->pixelStride / (size_t)componentBytes); /* src/TextureSet.cpp:957 */
-    for (int y = 0; y < p->height; ++y)
+    for (int y = 0; y < dstHeight; ++y)
     {
-        for (int x = 0; x < p->width; ++x)
+        for (int x = 0; x < dstWidth; ++x)
         {
-            const uint16_t* src = texels + ((size_t)y * p->width + x) * p->channels + p->firstChannel;
+            int sx, sy;
+            float w[4];
+            bilinear_filter(p->width, p->height, dstWidth, dstHeight, x, y, &sx, &sy, w);
             uint8_t* dst = out + (size_t)y * p->rowPitch + (size_t)x * p->pixelStride;
-            const uint32_t seed = jenkins_hash((uint32_t)x + (uint32_t)y * (uint32_t)p->width);
+            const uint32_t seed = jenkins_hash((uint32_t)x + (uint32_t)y * (uint32_t)dstWidth);
             uint32_t draw = 1;
             for (int ch = 0; ch < dstChannels; ++ch)
             {
@@ -881,7 +911,15 @@ int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* p, uint8_
                 if (ch < p->numChannels)
                 {
                     const int srcSpace = p->srcColorSpaces ? p->srcColorSpaces[p->firstChannel + ch] : 0;
-                    value = colorspace_decode(srcSpace, h2f(src[ch]));
+                    float taps[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int t = 0; t < 4; ++t)
+                        if (w[t] > 0.f)
+                        {
+                            const size_t index = ((size_t)(sy + (t >> 1)) * p->width + (size_t)(sx + (t & 1))) * p->channels;
+                            taps[t] = colorspace_decode(srcSpace, h2f(texels[index + p->firstChannel + ch]));
+                        }
+                    /* the reference build's contraction: the second product stays a multiplication */
+                    value = fmaf(taps[3], w[3], fmaf(taps[2], w[2], fmaf(taps[0], w[0], taps[1] * w[1])));
                 }
                 else
                     value = ch == 3 ? 1.f : 0.f; /* src/ImageProcessing.cu:166-170 */
@@ -894,6 +932,11 @@ int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* p, uint8_
         }
     }
     return 0;
+}
+
+int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* p, uint8_t* out)
+{
+    return p ? ntco_read_channels_resized(texels, p, p->width, p->height, out) : -1;
 }
 
 /* ------------------------------------------------------------------------------------------- */

@@ -125,6 +125,9 @@ typedef struct NtcoReadChannels
     int useDithering;
 } NtcoReadChannels;
 int ntco_read_channels(const uint16_t* texels, const NtcoReadChannels* params, uint8_t* out);
+/* The same with a destination of another size: the reference's bilinear resize (SetupBilinearFilter,
+   src/ImageProcessing.cu:24-71); `params` keeps describing the source mip, rowPitch the destination. */
+int ntco_read_channels_resized(const uint16_t* texels, const NtcoReadChannels* params, int dstWidth, int dstHeight, uint8_t* out);
 
 /* PackLatentsKernel (src/Quantizer.cu:497-527): quantised fp16 latents (bit patterns) to 4-bit
    words; `packed` receives width * height * numLayers words.  Returns 0, or -1 on invalid arguments. */

@@ -60,18 +60,20 @@ FORMAT_DTYPES = {1: np.uint8, 2: np.uint16, 3: np.float16, 4: np.float32, 5: np.
 
 def read_channels(texels: np.ndarray, channel_format: int, first_channel: int = 0, num_channels: Optional[int] = None,
                   components: Optional[int] = None, src_color_spaces=None, dst_color_spaces=None,
-                  use_dithering: bool = False) -> np.ndarray:
+                  use_dithering: bool = False, size=None) -> np.ndarray:
     """ReadChannels restated on the CPU: `texels` is a decoded mip [h][w][channels] (float16);
-    returns [h][w][components] in the channel format's dtype."""
+    returns [h][w][components] in the channel format's dtype; `size` = (width, height) other than
+    the mip's resizes bilinearly."""
     texels = np.ascontiguousarray(texels, dtype=np.float16)
     h, w, channels = texels.shape
     n = channels - first_channel if num_channels is None else num_channels
     count = n if components is None else components
     dtype = np.dtype(FORMAT_DTYPES[channel_format])
-    out = np.zeros((h, w, count), dtype=dtype)
+    dw, dh = (w, h) if size is None else size
+    out = np.zeros((dh, dw, count), dtype=dtype)
     p = ReadChannels()
     p.width, p.height, p.channels, p.firstChannel, p.numChannels, p.channelFormat = w, h, channels, first_channel, n, channel_format
-    p.pixelStride, p.rowPitch = count * dtype.itemsize, count * dtype.itemsize * w
+    p.pixelStride, p.rowPitch = count * dtype.itemsize, count * dtype.itemsize * dw
     keep = []
     if src_color_spaces is not None:
         keep.append((ctypes.c_int * channels)(*src_color_spaces))
@@ -80,7 +82,7 @@ def read_channels(texels: np.ndarray, channel_format: int, first_channel: int = 
         keep.append((ctypes.c_int * n)(*dst_color_spaces))
         p.dstColorSpaces = ctypes.cast(keep[-1], ctypes.POINTER(ctypes.c_int))
     p.useDithering = 1 if use_dithering else 0
-    if oracle_lib().ntco_read_channels(texels.ctypes.data, ctypes.byref(p), out.ctypes.data) != 0:
+    if oracle_lib().ntco_read_channels_resized(texels.ctypes.data, ctypes.byref(p), dw, dh, out.ctypes.data) != 0:
         raise ValueError("ntco_read_channels rejected its arguments")
     return out
 
@@ -165,6 +167,8 @@ def oracle_lib():
         lib.ntco_sample.argtypes = [ctypes.POINTER(_TextureSet), ctypes.POINTER(Options), ctypes.c_void_p,
                                     ctypes.c_size_t, ctypes.c_void_p]
         lib.ntco_read_channels.argtypes = [ctypes.c_void_p, ctypes.POINTER(ReadChannels), ctypes.c_void_p]
+        lib.ntco_read_channels_resized.argtypes = [ctypes.c_void_p, ctypes.POINTER(ReadChannels), ctypes.c_int, ctypes.c_int,
+                                                   ctypes.c_void_p]
         lib.ntco_pack_latents.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t,
                                           ctypes.c_void_p]
         lib.ntco_quantize_network.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,

@@ -528,8 +528,8 @@ class TextureSet:
     def read_channels_into(self, mip: int, address: int, to_device: bool = False, first_channel: int = 0,
                            num_channels: Optional[int] = None, pixel_stride: Optional[int] = None,
                            row_pitch: Optional[int] = None, channel_format: int = CHANNEL_FORMAT_FLOAT16,
-                           dst_color_spaces=None, use_dithering: bool = False) -> None:
-        w, h = self.mip_size(mip)
+                           dst_color_spaces=None, use_dithering: bool = False, size: Optional[Tuple[int, int]] = None) -> None:
+        w, h = self.mip_size(mip) if size is None else size
         n = self.desc.channels - first_channel if num_channels is None else num_channels
         component = np.dtype(CHANNEL_FORMAT_DTYPES.get(channel_format, np.float16)).itemsize
         params = ReadChannelsParams()
@@ -549,16 +549,17 @@ class TextureSet:
 
     def read_mip(self, mip: int, first_channel: int = 0, num_channels: Optional[int] = None,
                  channel_format: int = CHANNEL_FORMAT_FLOAT16, dst_color_spaces=None, use_dithering: bool = False,
-                 components: Optional[int] = None) -> np.ndarray:
+                 components: Optional[int] = None, size: Optional[Tuple[int, int]] = None) -> np.ndarray:
         """One decoded mip as [height][width][components] in the given channel format; `components`
-        (default: the number of channels read) above that number adds the default components."""
-        w, h = self.mip_size(mip)
+        (default: the number of channels read) above that number adds the default components;
+        `size` = (width, height) other than the mip's resizes bilinearly, as the reference does."""
+        w, h = self.mip_size(mip) if size is None else size
         n = self.desc.channels - first_channel if num_channels is None else num_channels
         dtype = np.dtype(CHANNEL_FORMAT_DTYPES[channel_format])
         count = n if components is None else components
         out = np.empty((h, w, count), dtype=dtype)
         self.read_channels_into(mip, out.ctypes.data, False, first_channel, n, count * dtype.itemsize, None, channel_format,
-                                dst_color_spaces, use_dithering)
+                                dst_color_spaces, use_dithering, size)
         return out
 
     def decompress_converted(self, conversion: OutputConversion, use_int8: bool = False, want_stats: bool = False,

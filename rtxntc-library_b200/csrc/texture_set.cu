@@ -99,6 +99,69 @@ __global__ void ReadChannelsKernel(const __half* __restrict__ src, int layout, i
     }
 }
 
+// The resizing case of CopyImageKernel (src/ImageProcessing.cu:24-71, 220-266): each output pixel is a
+// bilinear blend of up to four source texels, each taken out of its stored colour space first; taps
+// of zero weight are not read.  The reference is built with --use_fast_math, so its division is the
+// approximate one and its multiply-adds are fused; both are spelled out here.
+__global__ void ResizeChannelsKernel(const __half* __restrict__ src, int layout, int srcWidth, int srcHeight, int channels,
+    int firstChannel, int numChannels, OutputConversion conversion, uint8_t* __restrict__ dst, int dstWidth, int dstHeight,
+    size_t pixelStride, size_t rowPitch)
+{
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    const int y = blockIdx.y * blockDim.y + threadIdx.y;
+    if (x >= dstWidth || y >= dstHeight)
+        return;
+    const float u = ApproxDivide(AddFtz(float(x), 0.5f), float(dstWidth));
+    const float v = ApproxDivide(AddFtz(float(y), 0.5f), float(dstHeight));
+    const float px = fmaxf(0.f, fminf(AddFtz(float(srcWidth), -1.f), FmaFtz(u, float(srcWidth), -0.5f)));
+    const float py = fmaxf(0.f, fminf(AddFtz(float(srcHeight), -1.f), FmaFtz(v, float(srcHeight), -0.5f)));
+    const int sx = int(__float2uint_rd(px)), sy = int(__float2uint_rd(py));
+    const float fx = AddFtz(px, -floorf(px)), fy = AddFtz(py, -floorf(py));
+    const float gx = AddFtz(1.f, -fx), gy = AddFtz(1.f, -fy);
+    const float weights[4] = {MulFtz(gx, gy), MulFtz(fx, gy), MulFtz(gx, fy), MulFtz(fx, fy)};
+
+    uint8_t* out = dst + size_t(y) * rowPitch + size_t(x) * pixelStride;
+    const uint32_t seed = conversion.dither ? DitherSeed(uint32_t(x) + uint32_t(y) * uint32_t(dstWidth)) : 0u;
+    const int componentBytes = BytesPerComponent(conversion.format);
+    for (int c = 0; c < conversion.dstChannels; ++c)
+    {
+        const float dither = conversion.dither ? DitherDraw(seed, uint32_t(c) + 1u) : 0.f;
+        float value;
+        if (c < numChannels)
+        {
+            const int channel = firstChannel + c;
+            const int srcSpace = (conversion.srcSpaces >> (2 * c)) & 3;
+            float taps[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+            {
+                taps[t] = 0.f;
+                if (weights[t] > 0.f)
+                {
+                    const int tx = sx + (t & 1), ty = sy + (t >> 1);
+                    const size_t index = layout == kLayoutPlanarPairs
+                        ? size_t(ty) * srcWidth * channels + size_t(channel & ~1) * srcWidth + size_t(tx) * 2 + (channel & 1)
+                        : (size_t(ty) * srcWidth + tx) * channels + channel;
+                    taps[t] = DecodeColorSpace(srcSpace, __half2float(src[index]));
+                }
+            }
+            // a*w0 + b*w1 + c*w2 + d*w3 as the reference build contracts it: the second product is the
+            // one that stays a plain multiplication
+            value = FmaFtz(taps[3], weights[3], FmaFtz(taps[2], weights[2], FmaFtz(taps[0], weights[0], MulFtz(taps[1], weights[1]))));
+            value = EncodeColorSpace((conversion.dstSpaces >> (2 * c)) & 3, value);
+        }
+        else
+            value = c == 3 ? 1.f : 0.f;
+        const uint32_t bits = QuantizeComponent(conversion.format, value, dither);
+        if (componentBytes == 1)
+            out[c] = uint8_t(bits);
+        else if (componentBytes == 2)
+            reinterpret_cast<uint16_t*>(out)[c] = uint16_t(bits);
+        else
+            reinterpret_cast<uint32_t*>(out)[c] = bits;
+    }
+}
+
 // Plain FLOAT16 read-out: linear to linear, no dithering.
 OutputConversion Float16Conversion(size_t pixelStride)
 {
@@ -748,13 +811,15 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
             params.numChannels, m_geometry.channels - params.firstChannel);
         return NTCB_ERR_OUT_OF_RANGE;
     }
-    const int width = m_geometry.mipWidth[params.mipLevel], height = m_geometry.mipHeight[params.mipLevel];
-    if (params.width != width || params.height != height)
+    // the mip's own size, and the size asked for: a different one means a bilinear resize, as in the reference
+    const int mipWidth = m_geometry.mipWidth[params.mipLevel], mipHeight = m_geometry.mipHeight[params.mipLevel];
+    if (params.width <= 0 || params.height <= 0)
     {
-        SetError("width (%d) and height (%d) must match the mip's dimensions (%dx%d).", params.width, params.height, width,
-            height);
+        SetError("width (%d) and height (%d) must be positive.", params.width, params.height);
         return NTCB_ERR_OUT_OF_RANGE;
     }
+    const int width = params.width, height = params.height;
+    const bool resized = width != mipWidth || height != mipHeight;
     const size_t componentBytes = size_t(BytesPerComponent(params.channelFormat));
     if (componentBytes == 0)
     {
@@ -803,7 +868,7 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
     const __half* mipData = m_texels + m_geometry.mipTexelOffset[params.mipLevel] * m_geometry.channels;
     const size_t bytes = size_t(height) * params.rowPitch;
     const bool toHost = params.addressSpace == NTCB_ADDRESS_SPACE_HOST;
-    const bool direct = plainCopy && m_layout == NTCB_LAYOUT_INTERLEAVED && params.firstChannel == 0 &&
+    const bool direct = !resized && plainCopy && m_layout == NTCB_LAYOUT_INTERLEAVED && params.firstChannel == 0 &&
                         params.numChannels == m_geometry.channels && params.pixelStride == size_t(m_geometry.channels) * 2 &&
                         params.rowPitch == params.pixelStride * size_t(width);
     cudaError_t err;
@@ -843,8 +908,12 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
         }
         dim3 block(32, 8);
         dim3 grid((width + block.x - 1) / block.x, (height + block.y - 1) / block.y);
-        ReadChannelsKernel<<<grid, block, 0, m_stream>>>(mipData, m_layout, width, height, m_geometry.channels,
-            params.firstChannel, params.numChannels, conversion, target, params.pixelStride, params.rowPitch);
+        if (resized)
+            ResizeChannelsKernel<<<grid, block, 0, m_stream>>>(mipData, m_layout, mipWidth, mipHeight, m_geometry.channels,
+                params.firstChannel, params.numChannels, conversion, target, width, height, params.pixelStride, params.rowPitch);
+        else
+            ReadChannelsKernel<<<grid, block, 0, m_stream>>>(mipData, m_layout, width, height, m_geometry.channels,
+                params.firstChannel, params.numChannels, conversion, target, params.pixelStride, params.rowPitch);
         err = cudaGetLastError();
         if (err != cudaSuccess)
             return CudaFailure("ReadChannelsKernel launch", err);

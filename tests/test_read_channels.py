@@ -288,3 +288,82 @@ def test_conversion_against_a_live_reference_run(oracle):
             assert np.array_equal(_bytes(got), _bytes(expected)), (mip, channel_format, first)
     raw.close()
     reference.close()
+
+
+# ---------------------------------------------------------------------------------------------
+# ReadChannels with a size other than the mip's: the reference's bilinear resize
+# (fixture: tests/golden/readchannels_resize.npz, generator tests/golden/make_golden_resize.py)
+# ---------------------------------------------------------------------------------------------
+
+RESIZE_SPACES = [SRGB, SRGB, SRGB, LINEAR, HLG, LINEAR]
+RESIZE_SIZES = [(0, (32, 24)), (0, (100, 70)), (0, (65, 47)), (0, (1, 1)), (1, (9, 40)), (1, (32, 25))]
+RESIZE_REQUESTS = {
+    "f16_all_linear": (FLOAT16, 0, 6, 6, None, False),
+    "u8_rgba_srgb_dither": (UNORM8, 0, 4, 4, [SRGB, SRGB, SRGB, LINEAR], True),
+    "f32_mixed": (FLOAT32, 2, 4, 4, [LINEAR, SRGB, HLG, LINEAR], False),
+    "u16_pair_plus_default": (UNORM16, 4, 2, 4, None, True),
+}
+
+
+def test_restated_resize_against_reference_outputs(oracle):
+    """The CPU restatement divides exactly where the reference's GPU code divides approximately and
+    uses the C library's transfer functions: UNORM8 within 1 code, UNORM16 within 8, floating point
+    within 1 % (of the value, or of 0.001 for smaller ones), at most 1 % of UNORM values differing."""
+    golden = load_golden("readchannels_resize")
+    for mip, (width, height) in RESIZE_SIZES:
+        texels = golden["texels_mip%d" % mip].view(np.float16)
+        for name, (channel_format, first, count, components, dst, dither) in RESIZE_REQUESTS.items():
+            expected = golden["%s_mip%d_%dx%d" % (name, mip, width, height)]
+            got = oracle.read_channels(texels, channel_format, first, count, components, RESIZE_SPACES, dst, dither, size=(width, height))
+            assert got.shape == expected.shape == (height, width, components)
+            if channel_format in (UNORM8, UNORM16):
+                distance = np.abs(got.astype(np.int64) - expected.astype(np.int64))
+                assert distance.max() <= (1 if channel_format == UNORM8 else 8), (name, mip, width, height)
+                assert (distance > 0).mean() <= 0.01, (name, mip, width, height)
+            else:
+                a, b = got.astype(np.float64), expected.astype(np.float64)
+                assert (np.abs(a - b) <= 0.01 * np.maximum(np.abs(b), 1e-3)).all(), (name, mip, width, height)
+
+
+@pytest.mark.gpu
+def test_resized_read_matches_reference_outputs():
+    """The library on the fixture's container: identical bytes for every size and request."""
+    golden = load_golden("readchannels_resize")
+    with binding.Context() as context:
+        texture_set = context.create_texture_set(golden["container"].tobytes())
+        texture_set.decompress(False)
+        for mip, size in RESIZE_SIZES:
+            for name, (channel_format, first, count, components, dst, dither) in RESIZE_REQUESTS.items():
+                expected = golden["%s_mip%d_%dx%d" % (name, mip, size[0], size[1])]
+                got = texture_set.read_mip(mip, first, count, channel_format, dst, dither, components, size=size)
+                assert np.array_equal(_bytes(got), _bytes(expected)), (name, mip, size)
+        # the mip's own size is the 1:1 path; a non-positive size is refused as in the reference
+        width, height = texture_set.mip_size(1)
+        assert np.array_equal(texture_set.read_mip(1, size=(width, height)), texture_set.read_mip(1))
+        with pytest.raises(binding.NtcbError) as error:
+            texture_set.read_mip(0, size=(0, 8))
+        assert error.value.code == -9 and "must be positive" in str(error.value)
+        texture_set.close()
+
+
+@pytest.mark.gpu
+def test_resized_read_against_a_live_reference_run(oracle):
+    if not oracle.reference_available():
+        pytest.skip("oracle/_ref/libntc_ref.so is not built")
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(160, 96, 8, 0, 2, 8, seed=45, network="unit"))
+    spaces = [SRGB, SRGB, SRGB, LINEAR, HLG, HLG, LINEAR, SRGB]
+    data.channel_color_spaces = spaces
+    reference = oracle.ReferenceDecoder(data.container, data.geometry.channels, staging_bytes_per_pixel=256)
+    reference.decompress(True)
+    requests = [(FLOAT16, 0, 8, 8, None, False), (UNORM8, 0, 4, 4, [SRGB, SRGB, SRGB, LINEAR], True),
+                (FLOAT32, 3, 5, 6, [SRGB] * 5, False), (UNORM16, 4, 2, 2, [HLG, LINEAR], True), (UINT32, 6, 2, 2, None, False)]
+    with binding.Context() as context:
+        texture_set = context.create_texture_set(data.container)
+        texture_set.decompress(True)
+        for mip, size in ((0, (80, 48)), (0, (213, 131)), (0, (161, 95)), (2, (7, 5)), (3, (33, 64)), (0, (160, 97)), (1, (1, 1))):
+            for channel_format, first, count, components, dst, dither in requests:
+                expected = reference.read_channels(mip, size[0], size[1], channel_format, first, count, components, dst, dither)
+                got = texture_set.read_mip(mip, first, count, channel_format, dst, dither, components, size=size)
+                assert np.array_equal(_bytes(got), _bytes(expected)), (mip, size, channel_format)
+        texture_set.close()
+    reference.close()
