@@ -1,9 +1,10 @@
-// BC4 / BC5 encoding of decoded texels: the "decompress on load, then block-compress" step that the
+// BC1 - BC5 encoding of decoded texels: the "decompress on load, then block-compress" step that the
 // reference runs as compute shaders through a graphics API (IContext::MakeBlockCompressionComputePass,
-// src/Context.cpp:630-779; src/shaders/CompressBC4.hlsl, CompressBC5.hlsl and BC4_CompressFast in
-// src/shaders/BlockCompressCommon.hlsli:510-796), here as a CUDA kernel on the decode output.
+// src/Context.cpp:630-779; src/shaders/CompressBC1-5.hlsl, src/shaders/BlockCompressCommon.hlsli),
+// here as CUDA kernels on the decode output.  First part: BC4 / BC5 (BC4_CompressFast, :510-796);
+// second part: the BC1 colour block and the formats built on it.
 //
-// The encoder follows the shader's algorithm: quantise the 16 values to 8 bits; start from endpoints
+// The BC4 encoder follows the shader's algorithm: quantise the 16 values to 8 bits; start from endpoints
 // pulled 1/34 of the range inwards (pinned to 0 / 255 when the block touches them); alternate
 // nearest-palette index assignment with a least-squares refit of the endpoints, at most eight times,
 // while the squared error falls; do the same for the six-interpolant mode (explicit 0 and 255);
@@ -60,8 +61,6 @@ __device__ __forceinline__ void Palette(uint32_t a0, uint32_t a1, uint32_t (&pal
     }
 }
 
-// Nearest palette entry per pixel, the first one on ties; returns the block's squared error
-// (BC4_ComputeAlphaIndices, :605-632).
 // The sixteen 8-bit values of a block, packed: the loops over the texels stay rolled (a dynamic
 // shift instead of a register array), which keeps the encoder's code a few hundred instructions.
 // Fully unrolled, the kernel spent most of its issue slots waiting for instructions (ncu: stall
@@ -83,6 +82,8 @@ struct BlockValues
     }
 };
 
+// Nearest palette entry per pixel, the first one on ties; returns the block's squared error
+// (BC4_ComputeAlphaIndices, :605-632).
 __device__ uint32_t AssignIndices(const BlockValues& values, Bc4Block& block)
 {
     uint32_t palette[8];
