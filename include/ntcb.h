@@ -216,6 +216,18 @@ typedef struct NtcbTextureSetDesc
     uint64_t totalTexels;
 } NtcbTextureSetDesc;
 
+/* One texture of a set: a named range of channels and the formats its author intended for it.
+   ITextureMetadata::GetName / GetChannels / GetChannelFormat / GetBlockCompressedFormat /
+   GetRgbColorSpace / GetAlphaColorSpace (include/libntc/ntc.h:390-436). */
+typedef struct NtcbTextureDesc
+{
+    char name[128];                /* truncated if longer */
+    int32_t firstChannel, numChannels;
+    int32_t channelFormat;         /* NTCB_CHANNEL_FORMAT_*; UNORM8 when the file says nothing */
+    int32_t blockCompressedFormat; /* 0 = None, else NTCB_BLOCK_FORMAT_* (6 = BC6, 7 = BC7) */
+    int32_t rgbColorSpace, alphaColorSpace; /* NTCB_COLOR_SPACE_* */
+} NtcbTextureDesc;
+
 /* Creation options; the reference's TextureSetFeatures (include/libntc/ntc.h:179-199) sizes staging
    and training buffers that this decoder does not have. */
 typedef struct NtcbTextureSetFeatures
@@ -254,6 +266,12 @@ typedef struct NtcbReadChannelsParams
    Replaces IContext::CreateTextureSetMetadataFromStream + ITextureSetMetadata::GetDesc /
    GetLatentShape (include/libntc/ntc.h:1161, 546-552; src/Context.cpp:236-283). */
 int ntcb_probe_container(const void* data, size_t size, NtcbTextureSetDesc* outDesc);
+
+/* Host only, no GPU needed.  Texture `index` of a container; *outCount (optional) receives the
+   number of textures.  An index outside [0, count) returns NTCB_ERR_OUT_OF_RANGE after *outCount is
+   written, so index -1 asks for the count alone.  Replaces ITextureSetMetadata::GetTextureCount /
+   GetTexture (include/libntc/ntc.h:500-520) on a set opened with CreateTextureSetMetadataFromStream. */
+int ntcb_probe_container_texture(const void* data, size_t size, int index, NtcbTextureDesc* outTexture, int* outCount);
 
 /* Creates a decoder context on a CUDA device.  Replaces ntc::CreateContext
    (include/libntc/ntc.h:1330, src/PublicFunctions.cpp:62-162).  Fails with NTCB_ERR_CUDA when the
@@ -315,6 +333,9 @@ int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadCha
    TextureSet::GetTextureDataSlice (src/TextureSet.cpp:1958-1983) for callers that consume the
    texels on the GPU. */
 int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void** outPointer, size_t* outBytes);
+
+/* The textures of a loaded set: see ntcb_probe_container_texture. */
+int ntcb_texture_set_get_texture(NtcbTextureSet* textureSet, int index, NtcbTextureDesc* outTexture, int* outCount);
 
 /* Waits for everything queued on the texture set's stream. */
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet);

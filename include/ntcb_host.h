@@ -49,6 +49,9 @@ class ITextureSet
 public:
     virtual TextureSetDesc const& GetDesc() const = 0;
     virtual LatentShape const& GetLatentShape() const = 0;
+    // ITextureSetMetadata::GetTextureCount / GetTexture: a named channel range with its intended formats
+    virtual int GetTextureCount() const = 0;
+    virtual Status GetTexture(int index, NtcbTextureDesc& outTexture) const = 0;
     virtual Status Decompress(DecompressionStats* pOutStats, bool useInt8Weights = false) = 0;
     // rowRanges: [mips][2] = {rowBegin, rowEnd} per mip (tile-row sharding); NULL = whole mips
     virtual Status DecompressRows(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights = false) = 0;

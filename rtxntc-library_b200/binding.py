@@ -90,6 +90,17 @@ class TextureSetDesc(ctypes.Structure):
                 ("numNeuralMips", ctypes.c_int32), ("numLayers", ctypes.c_int32), ("totalTexels", ctypes.c_uint64)]
 
 
+class TextureDesc(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char * 128), ("firstChannel", ctypes.c_int32), ("numChannels", ctypes.c_int32),
+                ("channelFormat", ctypes.c_int32), ("blockCompressedFormat", ctypes.c_int32),
+                ("rgbColorSpace", ctypes.c_int32), ("alphaColorSpace", ctypes.c_int32)]
+
+    def as_dict(self) -> dict:
+        return {"name": self.name.decode(), "firstChannel": self.firstChannel, "numChannels": self.numChannels,
+                "channelFormat": self.channelFormat, "blockCompressedFormat": self.blockCompressedFormat,
+                "rgbColorSpace": self.rgbColorSpace, "alphaColorSpace": self.alphaColorSpace}
+
+
 class TextureSetFeatures(ctypes.Structure):
     _fields_ = [("outputLayout", ctypes.c_int32), ("numerics", ctypes.c_int32)]
 
@@ -141,6 +152,10 @@ def lib():
         handle.ntcb_sample.argtypes = [ctypes.POINTER(SampleParams), ctypes.c_void_p]
         handle.ntcb_decode_resident_ctas.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         handle.ntcb_probe_container.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetDesc)]
+        handle.ntcb_probe_container_texture.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.POINTER(TextureDesc),
+                                                        ctypes.POINTER(ctypes.c_int)]
+        handle.ntcb_texture_set_get_texture.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(TextureDesc),
+                                                        ctypes.POINTER(ctypes.c_int)]
         handle.ntcb_context_create.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]
         handle.ntcb_context_destroy.argtypes = [ctypes.c_void_p]
         handle.ntcb_context_destroy.restype = None
@@ -200,6 +215,21 @@ def probe_container(container: bytes) -> TextureSetDesc:
     buffer = np.frombuffer(container, dtype=np.uint8)
     check(lib().ntcb_probe_container(buffer.ctypes.data, len(container), ctypes.byref(desc)))
     return desc
+
+
+def probe_textures(container: bytes) -> list:
+    """The texture headers of a container (host only): a list of dictionaries."""
+    buffer = np.frombuffer(container, dtype=np.uint8)
+    count = ctypes.c_int()
+    code = lib().ntcb_probe_container_texture(buffer.ctypes.data, len(container), -1, None, ctypes.byref(count))
+    if code != -9:  # index -1 is out of range by design once the container has loaded
+        check(code)
+    textures = []
+    for index in range(count.value):
+        desc = TextureDesc()
+        check(lib().ntcb_probe_container_texture(buffer.ctypes.data, len(container), index, ctypes.byref(desc), None))
+        textures.append(desc.as_dict())
+    return textures
 
 
 def out_elements(geo: Geometry) -> int:
@@ -602,6 +632,17 @@ class TextureSet:
                                                     alpha_threshold, ctypes.c_void_p(out.data_ptr()), bw * block_bytes))
         self.synchronize()
         return out
+
+    def textures(self) -> list:
+        """The texture headers of the set: a list of dictionaries (see TextureDesc)."""
+        count = ctypes.c_int()
+        lib().ntcb_texture_set_get_texture(self.handle, -1, None, ctypes.byref(count))
+        result = []
+        for index in range(count.value):
+            desc = TextureDesc()
+            check(lib().ntcb_texture_set_get_texture(self.handle, index, ctypes.byref(desc), None))
+            result.append(desc.as_dict())
+        return result
 
     def device_mip(self, mip: int) -> Tuple[int, int]:
         """Device address and size in bytes of one decoded mip in the internal layout."""

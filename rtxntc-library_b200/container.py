@@ -88,11 +88,14 @@ COLOR_SPACE_NAMES = ("Linear", "sRGB", "HLG")  # ntc::ColorSpace values 0, 1, 2
 
 
 def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: bytes, fp8_blob: bytes,
-                    channel_color_spaces: Optional[Sequence[int]] = None) -> bytes:
+                    channel_color_spaces: Optional[Sequence[int]] = None, textures: Optional[Sequence[dict]] = None) -> bytes:
     """Serialises one compressed texture set.
 
     latents[m] is the u16 array [layers][height][width] of neural mip m.  channel_color_spaces, when
     given, holds one ntc::ColorSpace value per channel (the colour space the channel was stored in).
+    textures, when given, holds the documents of the texture headers (the schema's own field names:
+    name, firstChannel, numChannels and optionally channelFormat, rgbColorSpace, alphaColorSpace,
+    bcFormat as the schema's strings).
     """
     chunk = _BinaryChunk()
     latent_entries = []
@@ -130,7 +133,7 @@ def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: byt
         "numColorMips": geo.mips,
         "latentShape": {"numFeatures": geo.num_features},
         "mlpVersions": mlp_versions,
-        "textures": [],
+        "textures": list(textures) if textures else [],
         "channels": channel_entries,
         "latents": latent_entries,
         "colorMips": color_mips,

@@ -577,6 +577,64 @@ int LoadContainer(const void* data, size_t size, LoadedSet& out)
         }
     }
 
+    // texture headers (src/JsonFileFormat.cpp:118-127, src/TextureSetMetadata.cpp:460-468)
+    out.textures.clear();
+    const std::vector<json::Value>* textureHeaders = GetArray(document, "textures");
+    if (!textureHeaders)
+    {
+        SetError("Document: 'textures' must be an array.");
+        return NTCB_ERR_FILE_UNRECOGNIZED;
+    }
+    for (size_t t = 0; t < textureHeaders->size(); ++t)
+    {
+        const json::Value& entry = (*textureHeaders)[t];
+        if (entry.kind != json::Kind::Object)
+        {
+            SetError("Document: 'textures' must hold objects.");
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        }
+        LoadedTexture texture;
+        uint64_t first = 0, count = 0;
+        if (!GetString(entry, "name", texture.name))
+        {
+            SetError("Texture %zu: required field 'name' is missing.", t);
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        }
+        if (!GetUnsigned(entry, "firstChannel", true, first, "Texture") || !GetUnsigned(entry, "numChannels", true, count, "Texture"))
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        texture.firstChannel = int(first);
+        texture.numChannels = int(count);
+        struct EnumField
+        {
+            const char* name;
+            int* target;
+            std::vector<const char*> values; // the index is the enum's value
+        };
+        const EnumField enums[] = {
+            {"channelFormat", &texture.channelFormat, {"UNKNOWN", "UNORM8", "UNORM16", "FLOAT16", "FLOAT32", "UINT32"}},
+            {"rgbColorSpace", &texture.rgbColorSpace, {"Linear", "sRGB", "HLG"}},
+            {"alphaColorSpace", &texture.alphaColorSpace, {"Linear", "sRGB", "HLG"}},
+            {"bcFormat", &texture.blockCompressedFormat, {"None", "BC1", "BC2", "BC3", "BC4", "BC5", "BC6", "BC7"}},
+        };
+        for (const EnumField& field : enums)
+        {
+            std::string text;
+            if (!GetString(entry, field.name, text))
+                continue; // optional: the default stays
+            int value = -1;
+            for (size_t v = 0; v < field.values.size(); ++v)
+                if (text == field.values[v])
+                    value = int(v);
+            if (value < 0)
+            {
+                SetError("Texture %zu: field '%s' has an unknown value '%s'.", t, field.name, text.c_str());
+                return NTCB_ERR_FILE_UNRECOGNIZED;
+            }
+            *field.target = value;
+        }
+        out.textures.push_back(texture);
+    }
+
     // latent planes -> device order
     out.latents.resize(size_t(geo.TotalLatentPixels()) * geo.numLayers);
     for (int m = 0; m < geo.numNeuralMips; ++m)

@@ -4,6 +4,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <string>
 #include <vector>
 
 namespace ntcb
@@ -39,6 +40,18 @@ int GridDimension(int imageDimension, int neuralLod, int gridSizeScale);
 // with the reference's messages).
 int MakeGeometry(int width, int height, int channels, int mips, int gridSizeScale, int numFeatures, SetGeometry& out);
 
+// One texture of the set: a named range of channels with the formats its author intended for it
+// (json::Texture, src/JsonFileFormat.h:124-139; defaults as TextureSetMetadata::LoadMetadataFromStream
+// applies them, src/TextureSetMetadata.cpp:460-468).
+struct LoadedTexture
+{
+    std::string name;
+    int firstChannel = 0, numChannels = 0;
+    int channelFormat = 1;         // ntc::ChannelFormat, default UNORM8
+    int blockCompressedFormat = 0; // ntc::BlockCompressedFormat, default None
+    int rgbColorSpace = 0, alphaColorSpace = 0; // ntc::ColorSpace, default Linear
+};
+
 struct LoadedSet
 {
     SetGeometry geometry;
@@ -47,6 +60,7 @@ struct LoadedSet
     std::vector<uint8_t> int8Blob; // GenericInt8, empty when the file has no Int8 network
     std::vector<uint8_t> fp8Blob;  // GenericFP8, empty when the file has no FloatE4M3 network
     int channelColorSpaces[kMaxChannels] = {}; // ntc::ColorSpace each channel is stored in (0 Linear, 1 sRGB, 2 HLG)
+    std::vector<LoadedTexture> textures;
 };
 
 // Parses a container held in memory.  Returns an NtcbStatus and sets the thread-local error

@@ -223,6 +223,8 @@ public:
     Status DecompressConverted(DecompressionStats* pOutStats, bool useInt8Weights, NtcbOutputConversion const& conversion,
         int addressSpace, void* destination, size_t destinationBytes) override;
     Status ReadChannels(ReadChannelsParameters const& params) override;
+    int GetTextureCount() const override { return int(m_textures.size()); }
+    Status GetTexture(int index, NtcbTextureDesc& outTexture) const override;
     Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) override;
     Status BlockCompress(int mipLevel, int firstChannel, int numChannels, int format, float alphaThreshold,
         void* deviceBlocks, size_t rowPitch) override;
@@ -257,6 +259,7 @@ private:
     uint32_t* m_status = nullptr;
     uint32_t* m_hostStatus = nullptr; // pinned
     int m_channelColorSpaces[kMaxChannels] = {}; // ntc::ColorSpace each channel is stored in (from the container)
+    std::vector<LoadedTexture> m_textures;
     uint8_t* m_staging = nullptr;     // grown on demand by ReadChannels to host with padded strides
     size_t m_stagingBytes = 0;
     cudaEvent_t m_eventStart = nullptr, m_eventStop = nullptr;
@@ -419,6 +422,7 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
     m_networkBytes = m_numerics == NTCB_NUMERICS_REFERENCE ? size_t(kRefNetworkBytes) : size_t(kStagedNetworkBytes);
     for (int c = 0; c < kMaxChannels; ++c)
         m_channelColorSpaces[c] = loaded.channelColorSpaces[c];
+    m_textures = loaded.textures;
     m_hasInt8 = !loaded.int8Blob.empty();
     m_hasFp8 = !loaded.fp8Blob.empty();
 
@@ -935,6 +939,32 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
     return NTCB_OK;
 }
 
+// Texture `index` of `textures` as the C structure; OutOfRange past the end.
+Status FillTextureDesc(const std::vector<LoadedTexture>& textures, int index, NtcbTextureDesc* out)
+{
+    if (index < 0 || index >= int(textures.size()) || !out)
+    {
+        SetError("Texture index (%d) must be between 0 and %d and the output must not be NULL.", index, int(textures.size()) - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    const LoadedTexture& texture = textures[size_t(index)];
+    memset(out, 0, sizeof *out);
+    snprintf(out->name, sizeof out->name, "%s", texture.name.c_str());
+    out->firstChannel = texture.firstChannel;
+    out->numChannels = texture.numChannels;
+    out->channelFormat = texture.channelFormat;
+    out->blockCompressedFormat = texture.blockCompressedFormat;
+    out->rgbColorSpace = texture.rgbColorSpace;
+    out->alphaColorSpace = texture.alphaColorSpace;
+    ClearError();
+    return NTCB_OK;
+}
+
+Status TextureSet::GetTexture(int index, NtcbTextureDesc& outTexture) const
+{
+    return FillTextureDesc(m_textures, index, &outTexture);
+}
+
 Status TextureSet::GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes)
 {
     if (mipLevel < 0 || mipLevel >= m_geometry.mips || !outPointer || !outBytes)
@@ -1077,6 +1107,17 @@ int ntcb_probe_container(const void* data, size_t size, NtcbTextureSetDesc* outD
         return status;
     FillDesc(loaded.geometry, outDesc);
     return NTCB_OK;
+}
+
+int ntcb_probe_container_texture(const void* data, size_t size, int index, NtcbTextureDesc* outTexture, int* outCount)
+{
+    ntcb::LoadedSet loaded;
+    int status = ntcb::LoadContainer(data, size, loaded);
+    if (status != NTCB_OK)
+        return status;
+    if (outCount)
+        *outCount = int(loaded.textures.size());
+    return ntcb::FillTextureDesc(loaded.textures, index, outTexture);
 }
 
 int ntcb_context_create(int cudaDevice, NtcbContext** outContext)
@@ -1226,6 +1267,19 @@ int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, in
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     return textureSet->impl->BlockCompress(mipLevel, firstChannel, numChannels, format, alphaThreshold, deviceBlocks, rowPitch);
+}
+
+int ntcb_texture_set_get_texture(NtcbTextureSet* textureSet, int index, NtcbTextureDesc* outTexture, int* outCount)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (outCount)
+        *outCount = textureSet->impl->GetTextureCount();
+    NtcbTextureDesc scratch;
+    return textureSet->impl->GetTexture(index, outTexture ? *outTexture : scratch);
 }
 
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet)

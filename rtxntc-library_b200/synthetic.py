@@ -85,12 +85,13 @@ class SyntheticSet:
     fp8_blob: bytes
     _container: Optional[bytes] = None
     channel_color_spaces: Optional[List[int]] = None  # ntc::ColorSpace per channel; None = all Linear
+    textures: Optional[List[dict]] = None             # texture headers as the container's JSON holds them
 
     @property
     def container(self) -> bytes:
         if self._container is None:
             self._container = write_container(self.geometry, self.latents, self.int8_blob, self.fp8_blob,
-                                              self.channel_color_spaces)
+                                              self.channel_color_spaces, self.textures)
         return self._container
 
     @property

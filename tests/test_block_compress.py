@@ -386,3 +386,30 @@ def test_texture_set_block_compress(oracle):
             assert np.array_equal(texture_set.block_compress(mip, binding.BLOCK_FORMAT_BC3, 0, 4).cpu().numpy(),
                                   oracle.block_compress_color(texels, 3, 0, 4))
         texture_set.close()
+
+
+@pytest.mark.gpu
+def test_transcode_every_texture_by_its_header(oracle):
+    """The SDK's "decompress on load, then BCn" flow driven by the container's own texture headers:
+    each texture's channel range is encoded in the block format its header names."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 32, 6, 0, 2, 8, seed=6, network="unit"))
+    data.textures = [
+        {"name": "Albedo", "firstChannel": 0, "numChannels": 3, "rgbColorSpace": "sRGB", "bcFormat": "BC1"},
+        {"name": "Normal", "firstChannel": 3, "numChannels": 2, "bcFormat": "BC5"},
+        {"name": "Roughness", "firstChannel": 5, "numChannels": 1, "bcFormat": "BC4"},
+    ]
+    with binding.Context() as context:
+        texture_set = context.create_texture_set(data.container)
+        headers = texture_set.textures()
+        assert [h["name"] for h in headers] == ["Albedo", "Normal", "Roughness"]
+        texture_set.decompress(False)
+        texels = texture_set.read_mip(0)
+        for header in headers:
+            block_format, first, count = header["blockCompressedFormat"], header["firstChannel"], header["numChannels"]
+            blocks = texture_set.block_compress(0, block_format, first, count if block_format <= 3 else 0).cpu().numpy()
+            if block_format <= 3:
+                expected = oracle.block_compress_color(texels, block_format, first, count)
+            else:
+                expected = oracle.block_compress(texels, first, count)
+            assert np.array_equal(blocks, expected), header["name"]
+        texture_set.close()

@@ -319,3 +319,53 @@ def test_no_cpu_fallback():
     geo = synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=0).geometry()
     params = binding.fill_params(geo, 0x1000, 0x2000, 0x3000, 0x4000, binding.WEIGHTS_INT8)
     assert lib.ntcb_decode(ctypes.byref(params), None) == -2
+
+
+TEXTURES = [
+    {"name": "Albedo", "firstChannel": 0, "numChannels": 3, "channelFormat": "UNORM8", "rgbColorSpace": "sRGB", "bcFormat": "BC1"},
+    {"name": "Normal", "firstChannel": 3, "numChannels": 2, "bcFormat": "BC5"},
+    {"name": "Emissive HDR with a rather long name " + "x" * 120, "firstChannel": 5, "numChannels": 1,
+     "channelFormat": "FLOAT16", "rgbColorSpace": "HLG", "alphaColorSpace": "Linear", "bcFormat": "BC6"},
+]
+
+
+def _set_with_textures(textures=TEXTURES):
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 6, 0, 2, 8, seed=3))
+    data.textures = textures
+    return data
+
+
+def test_texture_headers_are_read_with_the_reference_defaults():
+    """ITextureSetMetadata::GetTexture: name, channel range and intended formats; a field the file
+    leaves out takes the default the reference's loader gives it (UNORM8, Linear, no block format)."""
+    textures = binding.probe_textures(_set_with_textures().container)
+    assert [t["name"] for t in textures[:2]] == ["Albedo", "Normal"]
+    assert textures[2]["name"] == TEXTURES[2]["name"][:127]  # the C structure holds 127 characters
+    assert [(t["firstChannel"], t["numChannels"]) for t in textures] == [(0, 3), (3, 2), (5, 1)]
+    assert [t["channelFormat"] for t in textures] == [1, 1, 3]
+    assert [t["blockCompressedFormat"] for t in textures] == [1, 5, 6]
+    assert [(t["rgbColorSpace"], t["alphaColorSpace"]) for t in textures] == [(1, 0), (0, 0), (2, 0)]
+    assert binding.probe_textures(synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 0, 2, 8, seed=3)).container) == []
+
+
+def test_texture_header_errors():
+    lib = binding.lib()
+    for bad in ([{"name": "A", "firstChannel": 0, "numChannels": 3, "bcFormat": "BC9"}],
+                [{"firstChannel": 0, "numChannels": 3}],
+                [{"name": "A", "numChannels": 3}],
+                ["Albedo"]):
+        container = _set_with_textures(bad).container
+        buffer = np.frombuffer(container, dtype=np.uint8)
+        assert lib.ntcb_probe_container_texture(buffer.ctypes.data, len(container), 0, None, None) == -3, bad
+    container = _set_with_textures().container
+    buffer = np.frombuffer(container, dtype=np.uint8)
+    desc = binding.TextureDesc()
+    assert lib.ntcb_probe_container_texture(buffer.ctypes.data, len(container), 3, ctypes.byref(desc), None) == -9
+
+
+def test_reference_loader_accepts_the_texture_headers(oracle):
+    if not oracle.reference_available():
+        pytest.skip("oracle/_ref/libntc_ref.so is not built")
+    probed = oracle.reference_probe(_set_with_textures().container)
+    assert probed[:6] == [64, 64, 6, 7, 2, 8]
+    assert probed[7] == 0b111111  # the reference's valid-channel mask: the channels the textures cover
