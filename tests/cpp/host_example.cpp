@@ -58,6 +58,15 @@ int main(int argc, char** argv)
     CHECK(context->CreateCompressedTextureSetFromFile(argv[1], features, &textureSet));
     const ntcb::TextureSetDesc& desc = textureSet->GetDesc();
 
+    // the texture headers: which channels form which texture, and the formats their author intended
+    for (int i = 0; i < textureSet->GetTextureCount(); ++i)
+    {
+        NtcbTextureDesc texture;
+        CHECK(textureSet->GetTexture(i, texture));
+        std::printf("texture %d: %s channels %d+%d bc %d\n", i, texture.name, texture.firstChannel, texture.numChannels,
+            texture.blockCompressedFormat);
+    }
+
     ntcb::DecompressionStats stats = {};
     CHECK(textureSet->Decompress(&stats, /*useInt8Weights*/ false));
 

@@ -34,6 +34,8 @@ def _fnv1a(data: bytes) -> int:
 
 def _container(tmp_path):
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(48, 24, 4, 0, 2, 8, seed=17, network="unit", weights="fp8"))
+    data.textures = [{"name": "Height", "firstChannel": 0, "numChannels": 1, "bcFormat": "BC4"},
+                     {"name": "Mask", "firstChannel": 1, "numChannels": 3}]
     path = tmp_path / "set.ntc"
     path.write_bytes(data.container)
     return data, str(path)
@@ -57,7 +59,9 @@ def test_cpp_client_matches_the_c_abi(tmp_path):
     data, path = _container(tmp_path)
     result = subprocess.run([binary, path], capture_output=True, text=True)
     assert result.returncode == 0, result.stderr
-    fields = result.stdout.split()
+    lines = result.stdout.splitlines()
+    assert lines[0] == "texture 0: Height channels 0+1 bc 4" and lines[1] == "texture 1: Mask channels 1+3 bc 0"
+    fields = lines[2].split()
     with binding.Context() as context:
         texture_set = context.create_texture_set(data.container)
         texture_set.decompress(False)
