@@ -63,40 +63,128 @@ private:
 // Converts `numChannels` channels of one decoded mip into a pixel-interleaved destination with
 // arbitrary strides: the 1:1 case of the reference's CopyImageKernel (src/ImageProcessing.cu:220-266)
 // with the decoded fp16 texels as source.  One thread per texel.
-__global__ void ReadChannelsKernel(const __half* __restrict__ src, int layout, int width, int height, int channels,
+template <int kFormat, bool kLinear>
+__global__ void ReadChannelsKernelT(const __half* __restrict__ src, int layout, int width, int height, int channels,
     int firstChannel, int numChannels, OutputConversion conversion, uint8_t* __restrict__ dst, size_t pixelStride,
     size_t rowPitch)
 {
+    // the format and "every colour space is Linear" are compile-time here: the per-component work of
+    // the common requests is a multiply and a rounding, not a chain of run-time switches
+    conversion.format = kFormat;
+    if (kLinear)
+        conversion.srcSpaces = conversion.dstSpaces = 0u;
     const int x = blockIdx.x * blockDim.x + threadIdx.x;
     const int y = blockIdx.y * blockDim.y + threadIdx.y;
     if (x >= width || y >= height)
         return;
     uint8_t* out = dst + size_t(y) * rowPitch + size_t(x) * pixelStride;
     const uint32_t seed = conversion.dither ? DitherSeed(uint32_t(x) + uint32_t(y) * uint32_t(width)) : 0u;
-    const int componentBytes = BytesPerComponent(conversion.format);
-    for (int c = 0; c < conversion.dstChannels; ++c)
+    constexpr int componentBytes = kFormat == kFormatUnorm8 ? 1 : (kFormat == kFormatUnorm16 || kFormat == kFormatFloat16) ? 2 : 4;
+    // Channel pairs (even channel, even channel count) are aligned 32-bit words in both layouts.
+    const bool pairs = !(firstChannel & 1) && !(channels & 1);
+    const size_t texel = layout == kLayoutPlanarPairs ? size_t(y) * width * channels + size_t(x) * 2
+                                                       : (size_t(y) * width + x) * channels;
+    // The pixel is assembled in registers and stored as whole words when everything is 4-byte
+    // aligned (one- and two-byte stores per component otherwise): the kernel moves bytes, nothing else.
+    const int pixelBytes = conversion.dstChannels * componentBytes;
+    const bool wordStores = !(pixelBytes & 3) && !(pixelStride & 3) && !(rowPitch & 3) && !(reinterpret_cast<uintptr_t>(dst) & 3);
+    uint32_t words[kMaxChannels] = {};
+    uint32_t pairBits = 0;
+#pragma unroll
+    for (int c = 0; c < kMaxChannels; ++c)
     {
+        if (c >= conversion.dstChannels)
+            break;
         const float dither = conversion.dither ? DitherDraw(seed, uint32_t(c) + 1u) : 0.f;
         uint32_t bits;
         if (c < numChannels)
         {
             const int channel = firstChannel + c;
-            size_t index;
-            if (layout == kLayoutPlanarPairs)
-                index = size_t(y) * width * channels + size_t(channel & ~1) * width + size_t(x) * 2 + (channel & 1);
+            uint32_t halfBits;
+            if (pairs)
+            {
+                if (!(c & 1))
+                {
+                    const size_t index = layout == kLayoutPlanarPairs ? texel + size_t(channel) * width : texel + size_t(channel);
+                    pairBits = c + 1 < numChannels ? *reinterpret_cast<const uint32_t*>(src + index)
+                                                   : uint32_t(__half_as_ushort(src[index]));
+                }
+                halfBits = (c & 1) ? pairBits >> 16 : pairBits & 0xffffu;
+            }
             else
-                index = (size_t(y) * width + x) * channels + channel;
-            bits = ConvertComponent(conversion, c, src[index], dither);
+            {
+                const size_t index = layout == kLayoutPlanarPairs ? texel + size_t(channel & ~1) * width + (channel & 1)
+                                                                   : texel + size_t(channel);
+                halfBits = __half_as_ushort(src[index]);
+            }
+            bits = ConvertComponent(conversion, c, __ushort_as_half(static_cast<unsigned short>(halfBits)), dither);
         }
         else
             bits = DefaultComponent(conversion, c, dither);
-        if (componentBytes == 1)
-            out[c] = uint8_t(bits);
+        if (!wordStores)
+        {
+            if (componentBytes == 1)
+                out[c] = uint8_t(bits);
+            else if (componentBytes == 2)
+                reinterpret_cast<uint16_t*>(out)[c] = uint16_t(bits);
+            else
+                reinterpret_cast<uint32_t*>(out)[c] = bits;
+        }
+        else if (componentBytes == 1)
+            words[c >> 2] |= (bits & 0xffu) << (8 * (c & 3));
         else if (componentBytes == 2)
-            reinterpret_cast<uint16_t*>(out)[c] = uint16_t(bits);
+            words[c >> 1] |= (bits & 0xffffu) << (16 * (c & 1));
         else
-            reinterpret_cast<uint32_t*>(out)[c] = bits;
+            words[c] = bits;
     }
+    if (wordStores)
+    {
+        const int count = pixelBytes >> 2;
+        uint32_t* out32 = reinterpret_cast<uint32_t*>(out);
+        if (!(count & 3) && !(pixelStride & 15) && !(rowPitch & 15) && !(reinterpret_cast<uintptr_t>(dst) & 15))
+        {
+#pragma unroll
+            for (int w = 0; w < kMaxChannels; w += 4)
+                if (w < count)
+                    reinterpret_cast<uint4*>(out32)[w >> 2] = make_uint4(words[w], words[w + 1], words[w + 2], words[w + 3]);
+        }
+        else
+        {
+#pragma unroll
+            for (int w = 0; w < kMaxChannels; ++w)
+                if (w < count)
+                    out32[w] = words[w];
+        }
+    }
+}
+
+// Launches the instantiation for the request's format.
+cudaError_t LaunchReadChannels(dim3 grid, dim3 block, cudaStream_t stream, const __half* src, int layout, int width, int height,
+    int channels, int firstChannel, int numChannels, const OutputConversion& conversion, uint8_t* dst, size_t pixelStride,
+    size_t rowPitch)
+{
+    const bool linear = conversion.srcSpaces == 0u && conversion.dstSpaces == 0u;
+#define NTCB_READ_CHANNELS_CASE(format)                                                                                  \
+    case format:                                                                                                         \
+        if (linear)                                                                                                      \
+            ReadChannelsKernelT<format, true><<<grid, block, 0, stream>>>(src, layout, width, height, channels, firstChannel, \
+                numChannels, conversion, dst, pixelStride, rowPitch);                                                    \
+        else                                                                                                             \
+            ReadChannelsKernelT<format, false><<<grid, block, 0, stream>>>(src, layout, width, height, channels, firstChannel, \
+                numChannels, conversion, dst, pixelStride, rowPitch);                                                    \
+        break;
+    switch (conversion.format)
+    {
+        NTCB_READ_CHANNELS_CASE(kFormatUnorm8)
+        NTCB_READ_CHANNELS_CASE(kFormatUnorm16)
+        NTCB_READ_CHANNELS_CASE(kFormatFloat16)
+        NTCB_READ_CHANNELS_CASE(kFormatFloat32)
+        NTCB_READ_CHANNELS_CASE(kFormatUint32)
+    default:
+        return cudaErrorInvalidValue;
+    }
+#undef NTCB_READ_CHANNELS_CASE
+    return cudaGetLastError();
 }
 
 // The resizing case of CopyImageKernel (src/ImageProcessing.cu:24-71, 220-266): each output pixel is a
@@ -916,9 +1004,10 @@ Status TextureSet::ReadChannels(ReadChannelsParameters const& params)
             ResizeChannelsKernel<<<grid, block, 0, m_stream>>>(mipData, m_layout, mipWidth, mipHeight, m_geometry.channels,
                 params.firstChannel, params.numChannels, conversion, target, width, height, params.pixelStride, params.rowPitch);
         else
-            ReadChannelsKernel<<<grid, block, 0, m_stream>>>(mipData, m_layout, width, height, m_geometry.channels,
+            err = LaunchReadChannels(grid, block, m_stream, mipData, m_layout, width, height, m_geometry.channels,
                 params.firstChannel, params.numChannels, conversion, target, params.pixelStride, params.rowPitch);
-        err = cudaGetLastError();
+        if (resized)
+            err = cudaGetLastError();
         if (err != cudaSuccess)
             return CudaFailure("ReadChannelsKernel launch", err);
         CountLaunch();
@@ -1343,9 +1432,8 @@ int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int wi
     }
     dim3 block(32, 8);
     dim3 grid((width + block.x - 1) / block.x, (height + block.y - 1) / block.y);
-    ReadChannelsKernel<<<grid, block, 0, cudaStream>>>(static_cast<const __half*>(deviceMip), layout, width, height, channels,
+    err = LaunchReadChannels(grid, block, cudaStream, static_cast<const __half*>(deviceMip), layout, width, height, channels,
         firstChannel, numChannels, Float16Conversion(pixelStride), staging, pixelStride, rowPitch);
-    err = cudaGetLastError();
     if (err != cudaSuccess)
         return CudaFailure("ReadChannelsKernel launch", err);
     CountLaunch();
@@ -1391,11 +1479,10 @@ int ntcb_convert_channels(const NtcbConvertParams* params, void* stream)
     }
     dim3 block(32, 8);
     dim3 grid((params->width + block.x - 1) / block.x, (params->height + block.y - 1) / block.y);
-    ReadChannelsKernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(params->deviceMip),
+    cudaError_t err = LaunchReadChannels(grid, block, static_cast<cudaStream_t>(stream), static_cast<const __half*>(params->deviceMip),
         params->layout, params->width, params->height, params->channels, params->conversion.firstChannel,
         params->conversion.numChannels, conversion, static_cast<uint8_t*>(params->deviceDestination), params->pixelStride,
         params->rowPitch);
-    cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess)
         return CudaFailure("ReadChannelsKernel launch", err);
     CountLaunch();
