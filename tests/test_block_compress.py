@@ -413,3 +413,42 @@ def test_transcode_every_texture_by_its_header(oracle):
                 expected = oracle.block_compress(texels, first, count)
             assert np.array_equal(blocks, expected), header["name"]
         texture_set.close()
+
+
+@pytest.mark.gpu
+def test_flat_and_binary_blocks_decode_exactly_at_full_size():
+    """Size-independent property on a 4096 x 4096 channel (1 M blocks): blocks of one value and blocks
+    holding only 0 and 1 decode, through the format's definition, to exactly the encoder's 8-bit values."""
+    import torch
+
+    side = 4096
+    blocks_per_side = side // 4
+    generator = torch.Generator(device="cuda").manual_seed(5)
+    flat = torch.randint(0, 256, (blocks_per_side, blocks_per_side), device="cuda", generator=generator)
+    flat = flat.repeat_interleave(4, 0).repeat_interleave(4, 1).to(torch.float32) / 255.0
+    binary = torch.randint(0, 2, (side, side), device="cuda", generator=generator).to(torch.float32)
+    chooser = torch.randint(0, 2, (blocks_per_side, blocks_per_side), device="cuda", generator=generator)
+    chooser = chooser.repeat_interleave(4, 0).repeat_interleave(4, 1).bool()
+    image = torch.where(chooser, flat, binary).to(torch.float16)
+    texels = torch.stack([image, image.flip(0)], dim=-1).contiguous()
+    blocks = binding.block_compress(texels, binding.BLOCK_FORMAT_BC5, 0)
+
+    def decode(block_bytes):
+        wide = block_bytes.to(torch.int64)
+        a0, a1 = wide[..., 0], wide[..., 1]
+        bits = sum(wide[..., 2 + k] << (8 * k) for k in range(6))
+        eight = a0 > a1
+        palette = [a0.double(), a1.double()]
+        for k in range(1, 7):
+            interpolant8 = ((7 - k) * a0 + k * a1).double() / 7
+            interpolant6 = ((5 - k) * a0 + k * a1).double() / 5 if k <= 4 else torch.full_like(interpolant8, 0.0 if k == 5 else 255.0)
+            palette.append(torch.where(eight, interpolant8, interpolant6))
+        palette = torch.stack(palette, dim=-1)                                    # [by][bx][8]
+        indices = torch.stack([(bits >> (3 * i)) & 7 for i in range(16)], dim=-1)  # [by][bx][16]
+        values = torch.gather(palette, -1, indices)                               # [by][bx][16]
+        by, bx = values.shape[:2]
+        return values.view(by, bx, 4, 4).permute(0, 2, 1, 3).reshape(by * 4, bx * 4)
+
+    for channel in range(2):
+        expected = torch.round(texels[..., channel].to(torch.float32).clamp(0, 1) * 255.0).double()
+        assert torch.equal(decode(blocks[..., 8 * channel:8 * channel + 8]), expected), channel
