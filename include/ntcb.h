@@ -354,6 +354,8 @@ typedef struct NtcbConvertParams
     void* deviceDestination;
     size_t pixelStride, rowPitch; /* bytes */
     NtcbOutputConversion conversion; /* components * bytes-per-component must not exceed pixelStride */
+    int32_t dstWidth, dstHeight; /* size of the destination; 0, 0 = the mip's own size.  Another size resizes
+                                    bilinearly as the reference's ReadChannels does; rowPitch then counts dstWidth pixels */
 } NtcbConvertParams;
 int ntcb_convert_channels(const NtcbConvertParams* params, void* stream);
 

@@ -73,7 +73,7 @@ class ConvertParams(ctypes.Structure):
     _fields_ = [("deviceMip", ctypes.c_void_p), ("layout", ctypes.c_int32), ("width", ctypes.c_int32),
                 ("height", ctypes.c_int32), ("channels", ctypes.c_int32), ("reserved", ctypes.c_int32),
                 ("deviceDestination", ctypes.c_void_p), ("pixelStride", ctypes.c_size_t), ("rowPitch", ctypes.c_size_t),
-                ("conversion", OutputConversion)]
+                ("conversion", OutputConversion), ("dstWidth", ctypes.c_int32), ("dstHeight", ctypes.c_int32)]
 
 
 class SampleParams(ctypes.Structure):
@@ -275,7 +275,7 @@ def fill_params(geo: Geometry, latents_ptr: int, network_ptr: int, out_ptr: int,
 
 
 def convert_channels(texels, conversion: OutputConversion, layout: int = LAYOUT_INTERLEAVED, width: Optional[int] = None,
-                     height: Optional[int] = None, channels: Optional[int] = None):
+                     height: Optional[int] = None, channels: Optional[int] = None, size: Optional[Tuple[int, int]] = None):
     """Runs the ReadChannels conversion kernel on decoded texels that the caller holds: `texels` is
     a CUDA float16 tensor, [height][width][channels] for the interleaved layout (the sizes are then
     taken from its shape).  Returns a CUDA tensor [height][width][components] of the channel
@@ -286,14 +286,17 @@ def convert_channels(texels, conversion: OutputConversion, layout: int = LAYOUT_
         height, width, channels = texels.shape
     dtype = {CHANNEL_FORMAT_UNORM8: torch.uint8, CHANNEL_FORMAT_UNORM16: torch.int16, CHANNEL_FORMAT_FLOAT16: torch.float16,
              CHANNEL_FORMAT_FLOAT32: torch.float32, CHANNEL_FORMAT_UINT32: torch.int32}[conversion.channelFormat]
-    out = torch.zeros((height, width, conversion.components), dtype=dtype, device=texels.device)
+    out_width, out_height = (width, height) if size is None else size  # another size: bilinear resize
+    out = torch.zeros((out_height, out_width, conversion.components), dtype=dtype, device=texels.device)
     params = ConvertParams()
     params.deviceMip = texels.data_ptr()
     params.layout, params.width, params.height, params.channels = layout, width, height, channels
     params.deviceDestination = out.data_ptr()
     params.pixelStride = conversion.components * out.element_size()
-    params.rowPitch = params.pixelStride * width
+    params.rowPitch = params.pixelStride * out_width
     params.conversion = conversion
+    if size is not None:
+        params.dstWidth, params.dstHeight = size
     with torch.cuda.device(texels.device):
         stream = torch.cuda.current_stream(texels.device).cuda_stream
         check(lib().ntcb_convert_channels(ctypes.byref(params), ctypes.c_void_p(stream)))

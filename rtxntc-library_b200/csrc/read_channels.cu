@@ -358,9 +358,17 @@ int ntcb_convert_channels(const NtcbConvertParams* params, void* stream)
     int status = MakeOutputConversion(params->conversion, params->channels, conversion);
     if (status != NTCB_OK)
         return status;
+    if (params->dstWidth < 0 || params->dstHeight < 0 || (params->dstWidth == 0) != (params->dstHeight == 0))
+    {
+        SetError("dstWidth (%d) and dstHeight (%d) must both be positive, or both 0 for the mip's size.", params->dstWidth,
+            params->dstHeight);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    const int dstWidth = params->dstWidth ? params->dstWidth : params->width;
+    const int dstHeight = params->dstHeight ? params->dstHeight : params->height;
     const size_t componentBytes = size_t(BytesPerComponent(conversion.format));
     if (params->pixelStride < size_t(conversion.dstChannels) * componentBytes ||
-        params->rowPitch < params->pixelStride * size_t(params->width) || params->pixelStride % componentBytes ||
+        params->rowPitch < params->pixelStride * size_t(dstWidth) || params->pixelStride % componentBytes ||
         params->rowPitch % componentBytes || reinterpret_cast<uintptr_t>(params->deviceDestination) % componentBytes ||
         (reinterpret_cast<uintptr_t>(params->deviceMip) & 1))
     {
@@ -370,11 +378,18 @@ int ntcb_convert_channels(const NtcbConvertParams* params, void* stream)
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     dim3 block(32, 8);
-    dim3 grid((params->width + block.x - 1) / block.x, (params->height + block.y - 1) / block.y);
-    cudaError_t err = LaunchReadChannels(grid, block, static_cast<cudaStream_t>(stream), static_cast<const __half*>(params->deviceMip),
-        params->layout, params->width, params->height, params->channels, params->conversion.firstChannel,
-        params->conversion.numChannels, conversion, static_cast<uint8_t*>(params->deviceDestination), params->pixelStride,
-        params->rowPitch);
+    dim3 grid((dstWidth + block.x - 1) / block.x, (dstHeight + block.y - 1) / block.y);
+    const __half* source = static_cast<const __half*>(params->deviceMip);
+    uint8_t* destination = static_cast<uint8_t*>(params->deviceDestination);
+    const cudaStream_t cudaStream = static_cast<cudaStream_t>(stream);
+    const bool resized = dstWidth != params->width || dstHeight != params->height;
+    cudaError_t err = resized
+        ? LaunchResizeChannels(grid, block, cudaStream, source, params->layout, params->width, params->height, params->channels,
+              params->conversion.firstChannel, params->conversion.numChannels, conversion, destination, dstWidth, dstHeight,
+              params->pixelStride, params->rowPitch)
+        : LaunchReadChannels(grid, block, cudaStream, source, params->layout, params->width, params->height, params->channels,
+              params->conversion.firstChannel, params->conversion.numChannels, conversion, destination, params->pixelStride,
+              params->rowPitch);
     if (err != cudaSuccess)
         return CudaFailure("ReadChannelsKernel launch", err);
     CountLaunch();

@@ -337,6 +337,14 @@ def test_resized_read_matches_reference_outputs():
                 expected = golden["%s_mip%d_%dx%d" % (name, mip, size[0], size[1])]
                 got = texture_set.read_mip(mip, first, count, channel_format, dst, dither, components, size=size)
                 assert np.array_equal(_bytes(got), _bytes(expected)), (name, mip, size)
+        # the same kernel on texels the caller holds (ntcb_convert_channels with a destination size)
+        import torch
+
+        texels = torch.from_numpy(golden["texels_mip0"].view(np.float16).copy()).cuda()
+        name, (channel_format, first, count, components, dst, dither) = "u8_rgba_srgb_dither", RESIZE_REQUESTS["u8_rgba_srgb_dither"]
+        conversion = binding.make_conversion(channel_format, count, first, components, RESIZE_SPACES[first:first + count], dst, dither)
+        got = binding.convert_channels(texels, conversion, size=(100, 70)).cpu().numpy()
+        assert np.array_equal(_bytes(got), _bytes(golden["%s_mip0_100x70" % name]))
         # the mip's own size is the 1:1 path; a non-positive size is refused as in the reference
         width, height = texture_set.mip_size(1)
         assert np.array_equal(texture_set.read_mip(1, size=(width, height)), texture_set.read_mip(1))
