@@ -129,7 +129,10 @@ typedef struct NtcbDecodeParams
     const void* network;     /* device: NTCB_STAGED_REFERENCE_NETWORK_BYTES produced by
                                 ntcb_stage_network_reference (NTCB_NUMERICS_REFERENCE), or NTCB_STAGED_NETWORK_BYTES
                                 produced by ntcb_stage_network (NTCB_NUMERICS_EXACT) */
-    void* out;               /* device: fp16 texels, or converted pixels when `conversion` is set */
+    void* out;               /* device, 4-byte aligned: fp16 texels, or converted pixels when `conversion` is set.
+                                A mip may hold at most 2^32 - 1 values (width x height x channels: the
+                                kernels index a mip with 32 bits); a larger one is refused with
+                                NTCB_ERR_OUT_OF_RANGE */
     uint32_t* status;        /* device: NTCB_STATUS_WORDS words, zeroed by the caller before the launch;
                                 word 0 != 0 after the kernel means a bounded wait expired */
     int32_t numMips;
@@ -144,7 +147,10 @@ typedef struct NtcbDecodeParams
        pixel-interleaved rows without padding: the fp16 copy of the texels is never stored.  In this
        mode mips[i].outOffset counts components of the channel format (bytes / bytes-per-component)
        and must be a multiple of `components`; the dither pattern of a mip is seeded per pixel with
-       x + y * width, as a full-mip ReadChannels does. */
+       x + y * width, as a full-mip ReadChannels does.  A pixel is stored with the widest vector its
+       size (components x bytes per component) is a multiple of - 16, 8, 4, 2 or 1 bytes - so the
+       first pixel of every mip (`out` plus its outOffset) must be aligned to that width; a request
+       that is not is refused with NTCB_ERR_INVALID_ARGUMENT before anything is launched. */
     const NtcbOutputConversion* conversion;
 } NtcbDecodeParams;
 
@@ -298,8 +304,9 @@ void ntcb_texture_set_destroy(NtcbTextureSet* textureSet);
 int ntcb_texture_set_get_desc(const NtcbTextureSet* textureSet, NtcbTextureSetDesc* outDesc);
 
 /* Uploads the compressed data (as the reference does on every call for a set loaded from a file,
-   src/TextureSet.cpp:1691-1757) and decodes every mip into the internal texel buffer with ONE
-   kernel launch.  With `stats` the call waits for the GPU and reports the device time; without it
+   src/TextureSet.cpp:1691-1757) and decodes every mip into the internal texel buffer: one kernel
+   launch, or - when mip 0 has 512 rows or more - four launches for row bands of mip 0 and one for
+   the other mips, so that a host read can copy a band while the next is decoded.  With `stats` the call waits for the GPU and reports the device time; without it
    the work is only queued.  Replaces ITextureSet::Decompress (include/libntc/ntc.h:933,
    src/TextureSet.cpp:1664-1897). */
 int ntcb_texture_set_decompress(NtcbTextureSet* textureSet, NtcbDecompressionStats* stats, int useInt8Weights);
@@ -347,7 +354,7 @@ int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet);
    Queued on `stream`; returns without waiting. */
 typedef struct NtcbConvertParams
 {
-    const void* deviceMip;
+    const void* deviceMip;   /* 4-byte aligned (channel pairs are read as 32-bit words) */
     int32_t layout;          /* NtcbOutputLayout of deviceMip */
     int32_t width, height, channels;
     int32_t reserved;
@@ -457,11 +464,13 @@ int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, in
    buffer given to ntcb_decode plus the mip's offset) in `layout` with `channels` channels;
    firstChannel / numChannels / pixelStride / rowPitch mean what they mean in NtcbReadChannelsParams.
    height * rowPitch must not exceed NTCB_NOALLOC_STAGING_BYTES, otherwise NTCB_ERR_OUT_OF_RANGE is
-   returned and nothing is done: read a large mip in row bands (offset `deviceMip` by whole rows
-   for the interleaved layout) or channel groups.
+   returned and nothing is done: read a large mip in row bands (offset `deviceMip` by whole rows;
+   a row of either layout is width x channels values, so with an even channel count the address
+   stays 4-byte aligned, which the gather kernel needs and the call checks) or channel groups.
 
-   The first call on a device looks up the array's device address; make that call before any
-   stream capture begins.  Every call uses the same array, which keeps the previous call's
+   The first call on a device looks up the array's device address.  Every call waits for `stream`
+   before it returns, so it must not be made on a stream that is being captured.  Every call uses
+   the same array, which keeps the previous call's
    contents (gaps are cleared when a request has gaps): two calls whose GPU work overlaps - on
    different streams or from different threads - race on it, so serialise them. */
 int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int width, int height, int channels,

@@ -15,11 +15,12 @@
 #   * src/GDeflate.cpp is replaced by oracle/gdeflate_stub.cpp (libdeflate sources are absent);
 #   * src/Shaders.cpp is left out, exactly as the stock build does without prebuilt shaders.
 #
-# Usage: oracle/build_ref.sh [reference-source-dir]   (default: $NTC_REFERENCE_DIR, else the REF default below)
+# Usage: oracle/build_ref.sh [reference-source-dir]
+#   (default: $NTC_REFERENCE_DIR, else a checkout named `reference` beside this repository)
 set -euo pipefail
 
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-${NTC_REFERENCE_DIR:-/root/reference}}"
+REF="${1:-${NTC_REFERENCE_DIR:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 OBJ="$OUT/obj"
 NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"

@@ -134,6 +134,14 @@ struct SampleParams
     KernelMip mips[16];
 };
 
+// Alignment the converting epilogue needs for the first pixel of a mip: it stores a pixel of
+// `pixelBytes` bytes with the widest vector store that divides its size (16, 8, 4, 2 or 1 bytes),
+// and consecutive pixels are `pixelBytes` apart.
+inline size_t ConvertedPixelAlignment(size_t pixelBytes)
+{
+    return !(pixelBytes & 15) ? 16 : !(pixelBytes & 7) ? 8 : !(pixelBytes & 3) ? 4 : !(pixelBytes & 1) ? 2 : 1;
+}
+
 // Checks a client's conversion request (NtcbOutputConversion of the C ABI) against a texture set of
 // `channels` channels and packs it for the kernels; returns an NtcbStatus.
 int MakeOutputConversion(const ::NtcbOutputConversion& request, int channels, OutputConversion& out);

@@ -562,6 +562,30 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
                 k.conversion.dstChannels);
             return NTCB_ERR_INVALID_ARGUMENT;
         }
+        if (k.convert)
+        {
+            // the converting epilogue stores a pixel with the widest vector its size allows
+            const size_t componentBytes = size_t(BytesPerComponent(k.conversion.format));
+            const size_t alignment = ConvertedPixelAlignment(size_t(k.conversion.dstChannels) * componentBytes);
+            if ((reinterpret_cast<uintptr_t>(p->out) + size_t(m.outOffset) * componentBytes) % alignment)
+            {
+                SetError("ntcb_decode: converted pixels of %zu bytes need mip %d to start at a multiple of %zu bytes.",
+                    size_t(k.conversion.dstChannels) * componentBytes, i, alignment);
+                return NTCB_ERR_INVALID_ARGUMENT;
+            }
+        }
+        else if (uint64_t(m.width) * uint64_t(m.height) * uint64_t(p->channels) > 0xFFFFFFFFull)
+        {
+            // the kernels index the elements of a mip with 32 bits
+            SetError("ntcb_decode: mip %d has %llu x %d values; a mip may hold at most 2^32 - 1.", i,
+                (unsigned long long)m.width * (unsigned long long)m.height, p->channels);
+            return NTCB_ERR_OUT_OF_RANGE;
+        }
+        if (k.convert && uint64_t(m.width) * uint64_t(m.height) > 0xFFFFFFFFull)
+        {
+            SetError("ntcb_decode: mip %d has more than 2^32 - 1 pixels.", i);
+            return NTCB_ERR_OUT_OF_RANGE;
+        }
         if (m.rowBegin == m.rowEnd)
             continue; // nothing of this mip belongs to this launch
         KernelMip& km = k.mips[used++];

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "container.h"
 #include "decode_kernel.h"
@@ -245,7 +246,9 @@ static __device__ __align__(256) unsigned char g_noAllocStaging[NTCB_NOALLOC_STA
 // once per device, with that device current.
 int NoAllocStagingAddress(unsigned char** outPointer)
 {
-    static unsigned char* cache[64] = {};
+    // one slot per device; relaxed atomics: two threads that make their first call together both ask
+    // the runtime and store the same address
+    static std::atomic<unsigned char*> cache[64];
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess)
@@ -255,15 +258,17 @@ int NoAllocStagingAddress(unsigned char** outPointer)
         SetError("CUDA device index %d is out of the supported range.", device);
         return NTCB_ERR_CUDA;
     }
-    if (!cache[device])
+    unsigned char* pointer = cache[device].load(std::memory_order_relaxed);
+    if (!pointer)
     {
         void* address = nullptr;
         err = cudaGetSymbolAddress(&address, g_noAllocStaging);
         if (err != cudaSuccess)
             return CudaFailure("cudaGetSymbolAddress", err);
-        cache[device] = static_cast<unsigned char*>(address);
+        pointer = static_cast<unsigned char*>(address);
+        cache[device].store(pointer, std::memory_order_relaxed);
     }
-    *outPointer = cache[device];
+    *outPointer = pointer;
     return NTCB_OK;
 }
 
@@ -280,6 +285,12 @@ int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int wi
     if (!deviceMip || !hostDestination)
     {
         SetError("deviceMip and hostDestination must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (reinterpret_cast<uintptr_t>(deviceMip) & 3)
+    {
+        // the gather kernel reads channel pairs as 32-bit words
+        SetError("deviceMip must be 4-byte aligned.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     if ((layout != NTCB_LAYOUT_PLANAR_PAIRS && layout != NTCB_LAYOUT_INTERLEAVED) || width < 1 || height < 1 ||
@@ -370,10 +381,10 @@ int ntcb_convert_channels(const NtcbConvertParams* params, void* stream)
     if (params->pixelStride < size_t(conversion.dstChannels) * componentBytes ||
         params->rowPitch < params->pixelStride * size_t(dstWidth) || params->pixelStride % componentBytes ||
         params->rowPitch % componentBytes || reinterpret_cast<uintptr_t>(params->deviceDestination) % componentBytes ||
-        (reinterpret_cast<uintptr_t>(params->deviceMip) & 1))
+        (reinterpret_cast<uintptr_t>(params->deviceMip) & 3))
     {
         SetError("pixelStride (%zu) must hold %d components of %zu bytes and rowPitch (%zu) a row of pixels; strides and "
-                 "addresses must be multiples of the component size.",
+                 "the destination must be multiples of the component size, deviceMip 4-byte aligned.",
             params->pixelStride, conversion.dstChannels, componentBytes, params->rowPitch);
         return NTCB_ERR_INVALID_ARGUMENT;
     }

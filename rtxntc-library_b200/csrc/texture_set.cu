@@ -426,9 +426,12 @@ Status TextureSet::DecompressConverted(DecompressionStats* pOutStats, bool useIn
         return NTCB_ERR_OUT_OF_RANGE;
     }
     const bool toHost = addressSpace == NTCB_ADDRESS_SPACE_HOST;
-    if (!toHost && (reinterpret_cast<uintptr_t>(destination) & 3))
+    // every mip starts a whole number of pixels into the destination, so the pixel stores are as
+    // aligned as the destination itself
+    const size_t alignment = std::max<size_t>(4, ConvertedPixelAlignment(pixelBytes));
+    if (!toHost && (reinterpret_cast<uintptr_t>(destination) % alignment))
     {
-        SetError("A device destination must be 4-byte aligned.");
+        SetError("A device destination for pixels of %zu bytes must be %zu-byte aligned.", pixelBytes, alignment);
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     DeviceGuard guard(m_device);

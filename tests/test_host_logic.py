@@ -306,6 +306,41 @@ def test_decode_validates_arguments_before_touching_the_gpu():
     assert lib.ntcb_decode(ctypes.byref(good), None) == -1
 
 
+def test_misaligned_and_oversized_requests_are_refused_on_the_host():
+    """Requests that would make a kernel issue a misaligned vector access, or overflow its 32-bit
+    element index, are refused before anything is launched (the addresses here are never touched)."""
+    import torch
+
+    gpu_present = torch.cuda.is_available()
+    lib = binding.lib()
+    geo = synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=0).geometry()
+    # converting epilogue: a pixel of 16 (8) bytes is stored as one 16-byte (8-byte) vector
+    for channel_format, components, misaligned, aligned in (
+            (binding.CHANNEL_FORMAT_FLOAT32, 4, 0x3004, 0x3010), (binding.CHANNEL_FORMAT_FLOAT16, 8, 0x3008, 0x3020),
+            (binding.CHANNEL_FORMAT_FLOAT16, 4, 0x3004, 0x3008), (binding.CHANNEL_FORMAT_UNORM8, 16, 0x3004, 0x3030)):
+        conversion = binding.make_conversion(channel_format, 4, components=components)
+        params = binding.fill_params(geo, 0x1000, 0x2000, misaligned, 0x4000, binding.WEIGHTS_INT8, conversion=conversion)
+        assert lib.ntcb_decode(ctypes.byref(params), None) == -1
+        assert b"multiple of" in lib.ntcb_last_error()
+        if not gpu_present:
+            # the aligned request passes the argument checks and fails only for want of a GPU (never tried
+            # where a GPU is present: the addresses are made up)
+            params = binding.fill_params(geo, 0x1000, 0x2000, aligned, 0x4000, binding.WEIGHTS_INT8, conversion=conversion)
+            assert lib.ntcb_decode(ctypes.byref(params), None) == -2
+    # a mip of 2^32 values or more
+    params = binding.fill_params(geo, 0x1000, 0x2000, 0x3000, 0x4000, binding.WEIGHTS_INT8)
+    params.mips[0].width, params.mips[0].height, params.mips[0].rowEnd = 65536, 16384, 16384
+    assert lib.ntcb_decode(ctypes.byref(params), None) == -9
+    # ntcb_convert_channels and the allocation-free read take channel pairs as 32-bit words
+    convert = binding.ConvertParams()
+    convert.deviceMip, convert.layout, convert.width, convert.height, convert.channels = 0x5002, binding.LAYOUT_INTERLEAVED, 8, 8, 4
+    convert.deviceDestination, convert.pixelStride, convert.rowPitch = 0x6000, 8, 64
+    convert.conversion = binding.make_conversion(binding.CHANNEL_FORMAT_FLOAT16, 4)
+    assert lib.ntcb_convert_channels(ctypes.byref(convert), None) == -1
+    host = np.zeros(8 * 8 * 4, dtype=np.float16)
+    assert lib.ntcb_read_channels_to_host_noalloc(0x5002, binding.LAYOUT_INTERLEAVED, 8, 8, 4, 0, 4, host.ctypes.data, 8, 64, None) == -1
+
+
 def test_no_cpu_fallback():
     """Without a usable GPU the compute entry points fail with a CUDA error instead of computing
     on the host."""

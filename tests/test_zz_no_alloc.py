@@ -57,6 +57,26 @@ def test_noalloc_read_matches_read_channels(layout):
             got = _read_noalloc(pointer, layout, width, height, channels, 0, channels, pixel_stride, row_pitch, 7.0)
             assert np.array_equal(got.view(np.uint16), expected.view(np.uint16))
 
+        # the property the entry point exists for: once the first call on the device has looked up the
+        # array's address, a call takes no device memory - not even for a padded channel subset, the
+        # request that makes ntcb_texture_set_read_channels grow its staging buffer
+        import torch
+
+        width, height = texture_set.mip_size(1)
+        pointer, _ = texture_set.device_mip(1)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        for first, count, pixel_stride in ((1, 4, 12), (0, channels, channels * 2), (3, 2, 4)):
+            _read_noalloc(pointer, layout, width, height, channels, first, count, pixel_stride, (width + 3) * pixel_stride, 1.0)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, "the allocation-free read took %d bytes of device memory" % (free_before - free_after)
+
+        # a mip address that is not 4-byte aligned is refused on the host (nothing is launched)
+        code = binding.lib().ntcb_read_channels_to_host_noalloc(
+            pointer + 2, layout, width, height, channels, 0, channels, got.ctypes.data, channels * 2, width * channels * 2, None)
+        assert code == -1
+
         # requests beyond the built-in staging area are refused, not truncated
         width, height = texture_set.mip_size(0)
         pointer, _ = texture_set.device_mip(0)
