@@ -23,13 +23,15 @@ The JSON line reports
             converting epilogue writes them, so the read-back is half as large (informational; the
             reference arm reports Decompress + ReadChannels(UNORM8) beside it).
 
-`--config 0|2|3` time the other benchmark configurations (1024^2 single mip; 64 sets of 2048^2
-sharded by set; 8192^2 sharded by tile rows - the last two split a fixed job over the ranks, strong
-scaling); they report the device-resident figure only.
+`--config 0|2|3|4` time the other benchmark configurations on their own (1024^2 single mip; 64 sets
+of 2048^2 sharded by set; 8192^2 sharded by tile rows; 16.7 M inference-on-sample queries split
+over the ranks - the last three split a fixed job over the ranks, strong scaling); they report the
+device-resident figure only.  The default run carries them as `other_configs` sub-records.
 
 The reference arm runs the reference's own CUDA decoder (LibNTC has no CPU decoder) through its
-public API on the same GPU and reports the end-to-end figure as its value, so that the two arms'
-`e2e` values compare like with like; its kernel-only figure is given beside it.
+public API on the same GPU.  Like this library's arm, its `value` is the device figure (the
+reference's own DecompressionStats::gpuTimeMilliseconds, which brackets its mip loop) and its `e2e`
+the wall clock of Decompress + ReadChannels(FLOAT16, Host) of every mip, with the bytes it copies.
 """
 from __future__ import annotations
 
@@ -55,9 +57,34 @@ L2_FLUSH_BYTES = 256 << 20
 WORKLOAD = ("PBR texture set 4096x4096, 12 channels, 13 mips, latent shape {gridSizeScale 4, 12 features}, "
             "FP8 e4m3 hidden layers + int8 output layer")
 
-# DRAM bytes per launch of the decode kernel on this workload (dram__bytes_read.sum +
-# dram__bytes_write.sum from the ncu capture summarised in profiles/).
-MEASURED_TRAFFIC_BYTES = 491.2e6  # profiles/decode_kernel_fp8_4096sq_launch_list.md
+# DRAM bytes per launch of the decode kernel on the benchmark workload come from the ncu capture
+# summarised in this file (its line "traffic_bytes_per_launch: N").
+TRAFFIC_CAPTURE = "profiles/decode_kernel_fp8_4096sq_launch_list.md"
+# Thread instructions per texel of the decode kernel (smsp__inst_executed.sum x 32 / texels) come from
+# this capture (its line "thread_instructions_per_texel: N"): the third bound, SIMT instruction issue.
+INSTRUCTION_CAPTURE = "profiles/decode_kernel_ref_fp8_2048sq_ncu_full.md"
+
+
+def captured_figure(path: str, key: str):
+    """A `key: number` line of a capture summary under profiles/, or None."""
+    try:
+        with open(os.path.join(ROOT, path)) as f:
+            for line in f:
+                if line.strip().startswith(key + ":"):
+                    return float(line.split(":", 1)[1].split()[0])
+    except Exception:
+        pass
+    return None
+
+
+def measured_tensor_peak_tflops():
+    """Dense 8-bit tensor peak used for the MMA bound: no 8-bit GEMM peak is measured on this pool,
+    so twice the measured bf16 burst figure stands in (8-bit operands run at twice the 16-bit rate)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return 2.0 * float(json.load(f)["bf16_tflops"]), "2 x measured bf16 burst (no 8-bit peak is measured)"
+    except Exception:
+        return 2.0 * 1590.0, "2 x fallback bf16 burst"
 
 
 def measured_peak_gbs():
@@ -185,7 +212,18 @@ WORKLOADS = {
     1: WORKLOAD,
     2: "64 texture sets 2048x2048, 8 channels, 12 mips each, latent shape {4, 8 features}, int8 weights, sharded by set",
     3: "texture set 8192x8192, 16 channels, 14 mips, latent shape {4, 16 features}, int8 weights, sharded by tile rows",
+    4: "inference on sample: 16,777,216 random (u, v, lod) queries on the 4096x4096 12-channel FP8 set, split over the ranks",
 }
+SAMPLE_QUERIES = 1 << 24
+
+
+def config_block(config: int, numerics_name: str, job_texels: int, rank_texels: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same keys and, for the same workload
+    and rank count, the same values."""
+    return {"workload": WORKLOADS[config], "numerics": numerics_name,
+            "texels_per_step": job_texels, "texels_per_step_this_rank": rank_texels,
+            "parallelism": "sharded by texture set / tile rows, no collective",
+            "l2": "256 MiB written between steps, outside the per-step events; each step's output also exceeds L2"}
 
 
 def build_launches(config: int, rank: int, world: int, device, binding, synthetic, sharding, numerics: int):
@@ -232,6 +270,88 @@ def build_launches(config: int, rank: int, world: int, device, binding, syntheti
     raise ValueError("unknown configuration")
 
 
+class SampleJob:
+    """Configuration 4 on one rank: this rank's slice of the query array against its resident copy
+    of the 4096x4096 FP8 set (the set is replicated, the queries are split)."""
+
+    def __init__(self, rank: int, world: int, device, binding, synthetic, numerics: int):
+        import torch
+
+        self.data = synthetic.make_texture_set(synthetic.config_spec(4))
+        self.resident = binding.ResidentTextureSet.from_synthetic(self.data, device=str(device), numerics=numerics,
+                                                                  allocate_output=False)
+        begin, end = SAMPLE_QUERIES * rank // world, SAMPLE_QUERIES * (rank + 1) // world
+        queries = synthetic.make_queries(SAMPLE_QUERIES, max_lod=12.0, seed=9)[begin:end]
+        self.queries = torch.from_numpy(np.ascontiguousarray(queries)).to(device)
+        self.count = end - begin
+        geo = self.data.geometry
+        # per query: 12 B in, 2 B x channels out, plus the set once
+        self.algorithmic_bytes = self.count * (12 + 2 * geo.channels) + geo.encoded_latent_bytes + binding.STAGED_NETWORK_BYTES
+
+    def step(self):
+        self.out = self.resident.sample(self.queries, False)
+
+    def check_status(self):
+        self.resident.check_status()
+
+
+def time_steps(torch, dist, device, step, checks, steps: int, warmup: int, flush):
+    """W untimed steps, then K steps each bracketed by CUDA events on the launching stream (the L2
+    flush sits between the events of consecutive steps), barrier + synchronize on both sides.
+    Returns (seconds summed over the K steps, max over ranks; per-step milliseconds of this rank;
+    wall seconds of the timed region)."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    for check in checks:
+        check()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    barrier_sync(dist, torch)
+    wall_start = time.perf_counter()
+    for index in range(steps):
+        flush.fill_(index & 0xFF)  # evict L2 between steps (not inside the per-step events)
+        starts[index].record()
+        step()
+        stops[index].record()
+    barrier_sync(dist, torch)
+    wall = time.perf_counter() - wall_start
+    for check in checks:
+        check()
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    return reduce_max(dist, torch, sum(step_ms) / 1e3, device), step_ms, wall
+
+
+def measure_other_config(config: int, rank: int, world: int, dist, device, binding, synthetic, sharding, numerics: int,
+                         steps: int, flush) -> dict:
+    """Device-resident throughput of one of the other benchmark configurations at this launch's rank
+    count (a sub-record of the default line; the same figure `--config N` reports on its own)."""
+    import torch
+
+    if config == 4:
+        job = SampleJob(rank, world, device, binding, synthetic, numerics)
+        seconds, step_ms, _ = time_steps(torch, dist, device, job.step, [job.check_status], steps, 3, flush)
+        record = {"workload": WORKLOADS[4], "value": SAMPLE_QUERIES * steps / seconds / 1e9, "unit": "Gquery/s",
+                  "ms_per_step": seconds * 1e3 / steps, "scaling": "strong", "queries_this_rank": job.count}
+        del job
+    else:
+        launches, texels, job_texels, _, _, scaling = build_launches(config, rank, world, device, binding, synthetic,
+                                                                     sharding, numerics)
+
+        def step():
+            for resident, params in launches:
+                resident.launch(params)
+
+        seconds, step_ms, _ = time_steps(torch, dist, device, step, [r.check_status for r, _ in launches], steps, 3, flush)
+        record = {"workload": WORKLOADS[config], "value": job_texels * steps / seconds / 1e9, "unit": UNIT,
+                  "ms_per_step": seconds * 1e3 / steps, "scaling": scaling, "texels_per_step": job_texels,
+                  "texels_per_step_this_rank": texels, "launches_per_step_this_rank": len(launches)}
+        launches.clear()
+    record["steps"] = steps
+    torch.cuda.empty_cache()
+    return record
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -243,54 +363,56 @@ def run_ours(args) -> dict:
     torch.cuda.set_device(device)
 
     numerics = binding.NUMERICS_EXACT if args.numerics == "exact" else binding.NUMERICS_REFERENCE
-    launches, texels, job_texels, algorithmic_bytes, data, scaling = build_launches(
-        args.config, rank, world, device, binding, synthetic, sharding, numerics)
+    numerics_name = "reference" if numerics == binding.NUMERICS_REFERENCE else "exact"
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+
+    if args.config == 4:
+        job = SampleJob(rank, world, device, binding, synthetic, numerics)
+        launches, texels, job_texels, algorithmic_bytes, data, scaling = [], job.count, SAMPLE_QUERIES, job.algorithmic_bytes, job.data, "strong"
+        step, checks = job.step, [job.check_status]
+    else:
+        launches, texels, job_texels, algorithmic_bytes, data, scaling = build_launches(
+            args.config, rank, world, device, binding, synthetic, sharding, numerics)
+
+        def step():
+            for resident, params in launches:
+                resident.launch(params)
+
+        checks = [resident.check_status for resident, _ in launches]
     geo = data.geometry
     use_int8 = data.use_int8
 
     # ---- device-resident throughput -------------------------------------------------------
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
-
-    def step():
-        for resident, params in launches:
-            resident.launch(params)
-
     # nvidia-smi needs a moment before its first sample: start it ahead of the warm-up so that the
     # (short) timed region is covered
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.5)
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
-    for resident, _ in launches:
-        resident.check_status()
-
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     launches_before = binding.lib().ntcb_launch_count()
-    barrier_sync(dist, torch)
-    wall_start = time.perf_counter()
-    for index in range(args.steps):
-        flush.fill_(index & 0xFF)  # evict L2 between steps (not inside the per-step events)
-        starts[index].record()
-        step()
-        stops[index].record()
-    barrier_sync(dist, torch)
-    wall = time.perf_counter() - wall_start
+    device_seconds, step_ms, wall = time_steps(torch, dist, device, step, checks, args.steps, args.warmup, flush)
     clocks = sampler.stop() if rank == 0 else None
-    launch_count = binding.lib().ntcb_launch_count() - launches_before
-    for resident, _ in launches:
-        resident.check_status()
-    step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
-    device_seconds = reduce_max(dist, torch, sum(step_ms) / 1e3, device)
+    # launches inside the timed region (the warm-up steps are the same launches, untimed)
+    launch_count = (binding.lib().ntcb_launch_count() - launches_before) * args.steps // (args.steps + args.warmup)
     total_launches = int(reduce_sum(dist, torch, float(launch_count), device))
     value = job_texels * args.steps / device_seconds / 1e9
+
+    # ---- the other configurations, device-resident, at this rank count ------------------------
+    other_configs = None
+    if args.config == 1 and not args.no_other_configs:
+        launches.clear()
+        torch.cuda.empty_cache()
+        other_steps = max(3, min(args.steps, 10))
+        other_configs = {}
+        for other in (0, 2, 3, 4):
+            record = measure_other_config(other, rank, world, dist, device, binding, synthetic, sharding, numerics,
+                                          other_steps, flush)
+            other_configs["config_%d" % other] = record
 
     # ---- end to end through the texture-set API with host buffers ---------------------------
     e2e = None
     e2e_unorm8 = None
+    e2e_ceiling = None
     if args.config in (0, 1):
         launches.clear()
         del flush
@@ -317,6 +439,26 @@ def run_ours(args) -> dict:
         e2e = {"value": world * texels * args.steps / e2e_seconds / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": geo.encoded_latent_bytes + 2 * binding.STAGED_NETWORK_BYTES,
                "d2h_bytes_per_step": texels * geo.channels * 2}
+
+        # The ceiling of that job on this machine: the same device-to-host bytes as one plain
+        # cudaMemcpyAsync per step into the same pinned buffer, every rank at once, no decode.
+        device_texels = torch.empty(texels * geo.channels, dtype=torch.float16, device=device)
+        for _ in range(2):
+            host_out.copy_(device_texels, non_blocking=True)
+        barrier_sync(dist, torch)
+        copy_start = time.perf_counter()
+        for _ in range(args.steps):
+            host_out.copy_(device_texels, non_blocking=True)
+        torch.cuda.synchronize()
+        copy_seconds = reduce_max(dist, torch, time.perf_counter() - copy_start, device)
+        barrier_sync(dist, torch)
+        del device_texels
+        ceiling = world * texels * args.steps / copy_seconds / 1e9
+        e2e_ceiling = {"value": ceiling, "unit": UNIT, "gb_per_s": world * texels * geo.channels * 2 * args.steps / copy_seconds / 1e9,
+                       "e2e_fraction_of_ceiling": e2e["value"] / ceiling,
+                       "what": "plain device-to-host copies of one step's texels into pinned host memory on all %d ranks at "
+                               "once (no decode, no upload): what the host link sustains" % world}
+
         if args.config == 1:
             # the same job with UNORM8 pixels as the client's format: one fused launch writes them, the
             # read-back is half the size (the reference arm runs Decompress + ReadChannels(UNORM8))
@@ -346,10 +488,29 @@ def run_ours(args) -> dict:
     peak, peak_kind = measured_peak_gbs()
     step_seconds = statistics.mean(step_ms) / 1e3
     achieved = algorithmic_bytes / step_seconds / 1e9
+    traffic = captured_figure(TRAFFIC_CAPTURE, "traffic_bytes_per_launch") if args.config == 1 else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": MEASURED_TRAFFIC_BYTES if args.config == 1 else None,
+                "traffic": traffic, "traffic_source": TRAFFIC_CAPTURE if traffic is not None else None,
                 "peak_source": "%s copy bandwidth" % peak_kind, "algorithmic_bytes_per_step": algorithmic_bytes,
-                "launches_per_step": len(step_ms) and launch_count // max(1, args.steps)}
+                "launches_per_step": launch_count // max(1, args.steps)}
+    if args.config != 4:
+        # the other two bounds of a tile: the matrix products at the 8-bit tensor peak, and SIMT
+        # instruction issue (every SM sub-partition issues one warp instruction per clock)
+        tensor_peak, tensor_source = measured_tensor_peak_tflops()
+        flops = 16384.0 * texels
+        roofline["mma"] = {"achieved": flops / step_seconds / 1e12, "peak": tensor_peak, "unit": "TFLOP/s",
+                           "frac": flops / step_seconds / 1e12 / tensor_peak, "flops_per_texel": 16384, "peak_source": tensor_source}
+        t_hbm, t_mma = algorithmic_bytes / (peak * 1e9), flops / (tensor_peak * 1e12)
+        roofline["tile"] = {"t_hbm_ms": t_hbm * 1e3, "t_mma_ms": t_mma * 1e3, "frac": max(t_hbm, t_mma) / step_seconds,
+                            "what": "the slower of the bytes at the HBM peak and the matrix products at the 8-bit tensor peak, over the measured time"}
+        instructions = captured_figure(INSTRUCTION_CAPTURE, "thread_instructions_per_texel") if args.config == 1 else None
+        if instructions:
+            properties = torch.cuda.get_device_properties(device)
+            sm_hz = (clocks or {}).get("sm_mhz") or 1965.0
+            issue_peak = properties.multi_processor_count * 4 * 32 * sm_hz * 1e6 / instructions / 1e9
+            roofline["simt"] = {"thread_instructions_per_texel": instructions, "source": INSTRUCTION_CAPTURE,
+                                "peak": issue_peak, "unit": UNIT, "frac": (texels / step_seconds / 1e9) / issue_peak,
+                                "what": "SMs x 4 sub-partitions x 32 lanes x SM clock / thread instructions per texel"}
     if numerics == binding.NUMERICS_REFERENCE:
         dtype = ("f16 x f16 -> f16 (tcgen05 kind::f16, binary16 accumulators rounded per 16 products: the reference's own "
                  "arithmetic on int8 weights, reproduced bit for bit)" if use_int8 else
@@ -359,19 +520,21 @@ def run_ours(args) -> dict:
         dtype = ("fp8_e4m3 x fp8_e4m3 -> f32 (layers 0-2), s8 x s8 -> s32 (layer 3), f16 activations" if not use_int8
                  else "s8 x s8 -> s32 (all layers), f16 activations")
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if args.config != 4 else "inference-on-sample Gquery/s", "value": value,
+        "unit": UNIT if args.config != 4 else "Gquery/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": device_seconds * 1e3 / args.steps, "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": dtype,
         "data": "synthetic (seeded latents and weights of the configuration's shape)",
-        "config": {"workload": WORKLOADS[args.config], "numerics": "reference" if numerics == binding.NUMERICS_REFERENCE else "exact",
-                   "texels_per_step": job_texels, "texels_per_step_this_rank": texels,
-                   "parallelism": "sharded by texture set / tile rows, no collective",
-                   "l2": "256 MiB written between steps, outside the per-step events; each step's output also exceeds L2"},
+        "config": config_block(args.config, numerics_name, job_texels, texels),
         "clocks": clocks, "e2e": e2e, "gpu_launches": total_launches, "roofline": roofline,
         "wall_seconds_timed_region": wall,
     }
+    if e2e_ceiling is not None:
+        line["e2e_ceiling"] = e2e_ceiling
     if e2e_unorm8 is not None:
         line["e2e_unorm8"] = e2e_unorm8
+    if other_configs is not None:
+        line["other_configs"] = other_configs
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(data)
     if dist is not None:
@@ -401,27 +564,38 @@ def run_reference(args) -> dict:
     decoder = oracle_py.ReferenceDecoder(data.container, geo.channels, device=0)
     host_out = torch.empty(texels * geo.channels, dtype=torch.float16).pin_memory()
     base = host_out.data_ptr()
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda:0")
 
-    kernel_ms = []
-
-    def step():
-        kernel_ms.append(decoder.decompress(data.use_int8))
-        for mip, cm in enumerate(geo.color_mips):
-            decoder.read_mip_into(mip, cm.width, cm.height, base + cm.texel_offset * geo.channels * 2, False)
-
+    # ---- device figure: the reference's own timing of its mip loop, L2 flushed between steps ----
     for _ in range(args.warmup):
-        step()
-    kernel_ms.clear()
+        decoder.decompress(data.use_int8)
     sampler = ClockSampler(0)
     torch.cuda.synchronize()
     sampler.start()
     time.sleep(0.5)
+    kernel_ms = []
+    for index in range(args.steps):
+        flush.fill_(index & 0xFF)
+        torch.cuda.synchronize()
+        kernel_ms.append(decoder.decompress(data.use_int8))
+    clocks = sampler.stop()
+    kernel_seconds = sum(kernel_ms) / 1e3
+    value = texels * args.steps / kernel_seconds / 1e9
+
+    # ---- end to end: Decompress + ReadChannels(FLOAT16, Host) of every mip, wall clock ----------
+    def step():
+        decoder.decompress(data.use_int8)
+        for mip, cm in enumerate(geo.color_mips):
+            decoder.read_mip_into(mip, cm.width, cm.height, base + cm.texel_offset * geo.channels * 2, False)
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    torch.cuda.synchronize()
     start = time.perf_counter()
     for _ in range(args.steps):
         step()
     torch.cuda.synchronize()
     seconds = time.perf_counter() - start
-    clocks = sampler.stop()
 
     # the same job with UNORM8 pixels as the client's format
     host_bytes = torch.empty(texels * geo.channels, dtype=torch.uint8).pin_memory()
@@ -440,24 +614,29 @@ def run_reference(args) -> dict:
     torch.cuda.synchronize()
     unorm8_seconds = time.perf_counter() - unorm8_start
     decoder.close()
-    value = texels * args.steps / seconds / 1e9
-    kernel_value = texels / (statistics.mean(kernel_ms) / 1e3) / 1e9
+    e2e_value = texels * args.steps / seconds / 1e9
+    # every Decompress of a set loaded from a file uploads the encoded latents and both weight blobs
+    # again (src/TextureSet.cpp:1695-1719); ReadChannels(Host) copies every mip back
+    h2d = geo.encoded_latent_bytes + 9472 + 8608
     return {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "gpus_used": 1,
         "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": seconds * 1e3 / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": kernel_seconds * 1e3 / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 x f16 -> f16 (wmma), as the reference's CUDA decoder computes",
         "data": "synthetic (seeded latents and weights of the configuration's shape)",
-        "config": {"workload": WORKLOAD, "texels_per_step_per_gpu": texels,
-                   "path": "CreateCompressedTextureSetFromMemory once; per step Decompress + ReadChannels(FLOAT16, Host) of every mip",
-                   "note": "the reference has no CPU decoder and no multi-GPU path: one rank runs its CUDA decoder on GPU 0"
-                           + ("; the other %d ranks idle" % (world - 1) if world > 1 else "")},
+        "config": config_block(1, "reference", texels * world, texels),
+        "reference_path": "CreateCompressedTextureSetFromMemory once; value: DecompressionStats::gpuTimeMilliseconds of "
+                          "Decompress (its mip loop; upload, latent unpacking and weight conversion excluded); e2e: wall clock "
+                          "of Decompress + ReadChannels(FLOAT16, Host) of every mip.  The reference has no CPU decoder and no "
+                          "multi-GPU path: one rank runs its CUDA decoder on GPU 0"
+                          + ("; the other %d ranks idle" % (world - 1) if world > 1 else ""),
         "clocks": clocks,
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": texels * geo.channels * 2,
+                "ms_per_step": seconds * 1e3 / args.steps},
         "e2e_unorm8": {"value": texels * args.steps / unorm8_seconds / 1e9, "unit": UNIT,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": texels * geo.channels,
                        "path": "per step Decompress + ReadChannels(UNORM8, Host) of every mip"},
-        "kernel_only": {"value": kernel_value, "unit": UNIT, "ms": statistics.mean(kernel_ms),
-                        "source": "DecompressionStats::gpuTimeMilliseconds (mip loop only; upload, unpack and weight conversion excluded)"},
+        "gpu_launches": args.steps * geo.mips,  # the reference launches its kernel once per mip
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 0, "kind": "reference",
                          "sample": "whole workload; the reference's only decoder is its CUDA kernel, run on the GPU of this box"},
     }
@@ -580,7 +759,9 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3],
+    parser.add_argument("--no-other-configs", action="store_true",
+                        help="skip the sub-records of configurations 0, 2, 3 and 4 in the default line")
+    parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4],
                         help="benchmark configuration; 1 (the default) is the one the metric is quoted on")
     parser.add_argument("--numerics", default="reference", choices=["reference", "exact"],
                         help="reference (default): binary16 accumulation, the reference decoder's bits; exact: exact accumulation")

@@ -11,7 +11,7 @@ Two plans:
                    (set, mips >= 1) - mip 0 is 75 % of a set - assigned longest-first to the least
                    loaded rank;
   * `plan_rows`    one large set: every mip tall enough is cut into one band of tile rows per rank,
-                   the small mips all go to rank 0.
+                   the small mips go whole, largest first, to the least loaded rank.
 Row bands are multiples of the kernel's tile height so that no tile straddles two ranks.
 """
 from __future__ import annotations
@@ -58,15 +58,24 @@ def plan_rows(geo: Geometry, world: int) -> List[List[Tuple[int, int]]]:
     if world < 1:
         raise ValueError("world must be positive")
     plan = [[(0, 0)] * geo.mips for _ in range(world)]
+    load = [0] * world
+    whole = []
     for mip, cm in enumerate(geo.color_mips):
         if cm.height < world * MIN_ROWS_PER_RANK:
-            plan[0][mip] = (0, cm.height)
+            whole.append(mip)
             continue
         tiles = (cm.height + TILE_ROWS - 1) // TILE_ROWS
         for rank in range(world):
             begin = (tiles * rank // world) * TILE_ROWS
             end = min(cm.height, (tiles * (rank + 1) // world) * TILE_ROWS)
             plan[rank][mip] = (begin, end)
+            load[rank] += (end - begin) * cm.width
+    # the mips too short to split go whole, largest first, to the rank with the least work so far
+    for mip in sorted(whole, key=lambda m: -geo.color_mips[m].width * geo.color_mips[m].height):
+        cm = geo.color_mips[mip]
+        rank = min(range(world), key=lambda r: (load[r], r))
+        plan[rank][mip] = (0, cm.height)
+        load[rank] += cm.width * cm.height
     return plan
 
 

@@ -68,3 +68,22 @@ def psnr_db(test: np.ndarray, reference: np.ndarray) -> float:
     if mse == 0.0:
         return float("inf")
     return 10.0 * np.log10(peak * peak / mse)
+
+
+def reference_chain(oracle, data, use_int8):
+    """The unmodified reference's decode of every mip of a synthetic set (oracle/_ref, through its
+    public API: Decompress, then ReadChannels(FLOAT16, AddressSpace::Device) per mip), as one flat
+    CUDA tensor in the interleaved order [mip][y][x][c]."""
+    import torch
+
+    geo = data.geometry
+    decoder = oracle.ReferenceDecoder(data.container, geo.channels)
+    try:
+        decoder.decompress(use_int8)
+        chain = torch.empty(geo.total_texels * geo.channels, dtype=torch.float16, device="cuda:0")
+        for mip, cm in enumerate(geo.color_mips):
+            decoder.read_mip_into(mip, cm.width, cm.height, chain.data_ptr() + cm.texel_offset * geo.channels * 2, True)
+        torch.cuda.synchronize()
+    finally:
+        decoder.close()
+    return chain

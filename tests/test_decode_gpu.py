@@ -25,7 +25,7 @@ import ctypes
 import numpy as np
 import pytest
 
-from conftest import load_golden, psnr_db
+from conftest import load_golden, psnr_db, reference_chain
 
 import __graft_entry__ as entry
 
@@ -143,15 +143,27 @@ def test_kernel_matches_contract_on_ragged_shapes(oracle, shape, network, numeri
     geo = data.geometry
     checker = oracle.OracleSet.from_synthetic(data)
     resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
+    # the default numerics are held to the reference itself wherever it can answer: identical bits to a
+    # live run of the unmodified reference on this GPU; the CPU model of its rounding (2 differences in
+    # 10,000 allowed, because the model is 99.998 % exact) is only the fallback
+    live = numerics == REFERENCE and oracle.reference_available()
     tally = _Tally(numerics)
     for use_int8 in (True, False):
         resident.out.fill_(float("nan"))
         resident.decode(use_int8)
         _sync()
         resident.check_status()
+        if live:
+            chain = reference_chain(oracle, data, use_int8).cpu().numpy()
         for mip in range(geo.mips):
-            tally.add(resident.mip_numpy(mip), _restated(oracle, checker, mip, use_int8, numerics), use_int8,
-                      "%s mip %d" % (shape, mip))
+            if live:
+                cm = geo.color_mips[mip]
+                theirs = chain[cm.texel_offset * geo.channels:(cm.texel_offset + cm.width * cm.height) * geo.channels]
+                assert np.array_equal(resident.mip_numpy(mip).reshape(-1).view(np.uint16), theirs.view(np.uint16)), \
+                    "%s mip %d differs from the live reference" % (shape, mip)
+            else:
+                tally.add(resident.mip_numpy(mip), _restated(oracle, checker, mip, use_int8, numerics), use_int8,
+                          "%s mip %d" % (shape, mip))
     tally.check()
 
 
@@ -421,6 +433,15 @@ def test_inference_on_sample_matches_contract(oracle, shape, numerics):
         if numerics == EXACT:
             expected = checker.sample(queries, use_int8, oracle.NUMERICS_SPEC)
             assert np.array_equal(got.view(np.uint16), expected.view(np.uint16))
+        elif oracle.reference_available():
+            # identical bits to a gather from the live reference's decoded mip chain
+            chain = reference_chain(oracle, data, use_int8).cpu().numpy().reshape(-1, geo.channels)
+            for q in range(queries.shape[0]):
+                mip = int(max(0, min(geo.mips - 1, np.floor(queries[q, 2]))))
+                cm = geo.color_mips[mip]
+                x = int(max(0, min(cm.width - 1, np.floor(np.float32(queries[q, 0]) * np.float32(cm.width)))))
+                y = int(max(0, min(cm.height - 1, np.floor(np.float32(queries[q, 1]) * np.float32(cm.height)))))
+                assert np.array_equal(got[q].view(np.uint16), chain[cm.texel_offset + y * cm.width + x].view(np.uint16)), (q, mip, x, y)
         else:
             expected = checker.sample(queries, use_int8, oracle.NUMERICS_REF)
             different = int((got.view(np.uint16) != expected.view(np.uint16)).sum())

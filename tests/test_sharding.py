@@ -51,7 +51,7 @@ def test_row_plan_partitions_every_mip(shape, world):
     assert sum(sharding.texels_of_rows(geo, plan[r]) for r in range(world)) == geo.total_texels
     if geo.color_mips[0].height >= world * sharding.MIN_ROWS_PER_RANK:
         loads = [sharding.texels_of_rows(geo, plan[r]) for r in range(world)]
-        assert max(loads) <= 1.4 * geo.total_texels / world  # small mips all sit on rank 0
+        assert max(loads) <= 1.4 * geo.total_texels / world  # the small mips go whole to single ranks
 
 
 WORKER = r'''
