@@ -663,14 +663,16 @@ def run_profile_case(case: str) -> int:
     resident = binding.ResidentTextureSet.from_synthetic(
         data, numerics=binding.NUMERICS_EXACT if numerics == "exact" else binding.NUMERICS_REFERENCE)
     params = resident.params(mode == "int8")
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for _ in range(int(launches)):
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(int(launches))]
+    for start, stop in events:
         start.record()
         resident.launch(params)
         stop.record()
     torch.cuda.synchronize()
     resident.check_status()
-    print("profile case %s: %d texels, last launch %.3f ms" % (case, data.geometry.total_texels, start.elapsed_time(stop)))
+    times = sorted(start.elapsed_time(stop) for start, stop in events[1:] or events)
+    print("profile case %s (%s): %d texels, launches after the first: median %.4f ms, fastest %.4f ms"
+          % (case, os.path.basename(binding.LIBRARY_PATH), data.geometry.total_texels, times[len(times) // 2], times[0]))
     return 0
 
 

@@ -16,7 +16,8 @@ import numpy as np
 from .geometry import FP8_BLOB_BYTES, INT8_BLOB_BYTES, Geometry
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIBRARY_PATH = os.path.join(_HERE, "libntcb200.so")
+# NTCB_LIBRARY selects another build of the library (the profiling variants `make ablations` produces)
+LIBRARY_PATH = os.environ.get("NTCB_LIBRARY") or os.path.join(_HERE, "libntcb200.so")
 
 MAX_MIPS = 16
 STAGED_NETWORK_BYTES = 14864

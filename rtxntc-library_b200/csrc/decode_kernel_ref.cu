@@ -41,10 +41,23 @@
 #include "output_convert.cuh"
 #include "epilogue_convert.cuh"
 
+// Profiling aid: NTCB_ABLATE (a bit mask, 0 in the product build) removes one phase of
+// DecodeKernelRefFp8 at a time so that its share of the kernel's instructions and time can be
+// measured as a difference (`make ablations` builds one library per mask; their output is wrong by
+// construction).  1: the per-tile tables and footprint staging after the first tile; 2: the latent
+// gather and blend (constants are stored instead); 4: the activation arithmetic of layers 0-2 (the
+// raw accumulator words are stored); 8: the global stores of the epilogue; 16: the tensor-core work
+// (no MMA issue, no wait for it); 32: the tensor-memory loads.
+#ifndef NTCB_ABLATE
+#define NTCB_ABLATE 0
+#endif
+
 namespace ntcb
 {
 namespace
 {
+
+constexpr int kAblate = NTCB_ABLATE;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
 __device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
@@ -879,7 +892,7 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     if (__syncthreads_or(failed))
         return 1;
 
-    if (ctx.tid == 0)
+    if (ctx.tid == 0 && !(kAblate & 16))
     {
         TcgenFenceAfterSync();
         // both descriptors: binary16 accumulators, operand formats 0 (binary16 for kind::f16, e4m3 for kind::f8f6f4)
@@ -936,7 +949,7 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
-    if (!MbarrierWaitBounded(ctx.barrier, phase))
+    if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phase))
     {
         failed = 1;
         params.status[0] = kStatusBarrierTimeout;
@@ -946,20 +959,51 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
     phase ^= 1;
     TcgenFenceAfterSync();
 
+    if ((kAblate & 4) && kLayer < 3)
+    {
+        // profiling variant: the accumulator words go to the operand as they are
+        uint4* rowChunk = ctx.rowChunk;
+        uint32_t low[16];
+        if (!(kAblate & 32))
+        {
+            TmemLoadPacked16(ctx.tmemLane, low);
+            TmemLoadWait();
+        }
+        else
+        {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                low[i] = uint32_t(ctx.tile + i);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            rowChunk[c * 128] = make_uint4(low[4 * c], low[4 * c + 1], low[4 * c + 2], low[4 * c + 3]);
+        return;
+    }
+
     if (kLayer < 2)
     {
         // e4m3 codes for the next layer: 16 per 16-byte chunk
         uint4* rowChunk = ctx.rowChunk;
         uint32_t low[16], high[16];
-        TmemLoadPacked16(ctx.tmemLane, low);
-        if (kN == 64)
-            TmemLoadPacked16(ctx.tmemLane + 32, high);
+        if (!(kAblate & 32))
+        {
+            TmemLoadPacked16(ctx.tmemLane, low);
+            if (kN == 64)
+                TmemLoadPacked16(ctx.tmemLane + 32, high);
+            else
+            {
+                uint32_t (&tail)[8] = reinterpret_cast<uint32_t (&)[8]>(high);
+                TmemLoadPacked8(ctx.tmemLane + 32, tail);
+            }
+            TmemLoadWait();
+        }
         else
         {
-            uint32_t (&tail)[8] = reinterpret_cast<uint32_t (&)[8]>(high);
-            TmemLoadPacked8(ctx.tmemLane + 32, tail);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                low[i] = high[i] = uint32_t(ctx.tile * 3 + i) & 0x3FFF3FFFu;
         }
-        TmemLoadWait();
 #pragma unroll
         for (int c = 0; c < 2; ++c)
             rowChunk[c * 128] = make_uint4(
@@ -982,8 +1026,17 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
         // layer 3 runs on the binary16 path: its inputs are the int8 grid values rint(y * 80) * 0.0125
         uint4* rowChunk = ctx.rowChunk;
         uint32_t acc[16];
-        TmemLoadPacked16(ctx.tmemLane, acc);
-        TmemLoadWait();
+        if (!(kAblate & 32))
+        {
+            TmemLoadPacked16(ctx.tmemLane, acc);
+            TmemLoadWait();
+        }
+        else
+        {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                acc[i] = uint32_t(ctx.tile * 5 + i) & 0x3FFF3FFFu;
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c)
             rowChunk[c * 128] = make_uint4(ActivateRef<false>(acc[4 * c]), ActivateRef<false>(acc[4 * c + 1]),
@@ -993,8 +1046,17 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
     {
         // output (src/Inference.cu:121-135): the accumulators are the channels
         uint32_t bits[8];
-        TmemLoadPacked8(ctx.tmemLane, bits);
-        TmemLoadWait();
+        if (!(kAblate & 32))
+        {
+            TmemLoadPacked8(ctx.tmemLane, bits);
+            TmemLoadWait();
+        }
+        else
+        {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                bits[i] = uint32_t(ctx.tile * 7 + i) & 0x3FFF3FFFu;
+        }
         const int channelPairs = params.channels >> 1;
         uint32_t special = 0; // bit 15 / 31 set when a value has an all-ones exponent
 #pragma unroll
@@ -1025,10 +1087,23 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
         }
         else if (ctx.out)
         {
+            if (kAblate & 8)
+            {
+                // profiling variant: keep the values alive without storing them (the condition never holds)
+                uint32_t all = 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (j < channelPairs)
-                    ctx.out[j * ctx.outStepWords] = bits[j];
+                for (int j = 0; j < 8; ++j)
+                    all ^= bits[j];
+                if (all == 0x12345679u && ctx.tile < 0)
+                    ctx.out[0] = all;
+            }
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j < channelPairs)
+                        ctx.out[j * ctx.outStepWords] = bits[j];
+            }
         }
     }
 }
@@ -1174,7 +1249,15 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         }
 
         // the e4m3 input stage is the one of the exact-accumulation kernel (64-byte rows of codes)
-        BuildInputs<true>(params, mip, shared, ctx, lane, warp);
+        if (kAblate & 2)
+        {
+            const uint32_t filler = uint32_t(tile) & 0x3F3F3F3Fu;
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk)
+                ctx.rowChunk[chunk * 128] = make_uint4(filler, filler + chunk, filler, filler);
+        }
+        else
+            BuildInputs<true>(params, mip, shared, ctx, lane, warp);
 
         aborted = IssueLayerRefFp8<0>(ctx, failed);
         if (aborted)
@@ -1183,7 +1266,8 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         if (nextTile < params.totalTiles)
         {
             place = locate(nextTile, place.mipIndex);
-            PrepareTile<true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+            if (!(kAblate & 1))
+                PrepareTile<true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
         }
         ConsumeLayerRefFp8<0, false>(params, ctx, phase, failed);
 
