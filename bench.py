@@ -615,6 +615,38 @@ def run_reference(args) -> dict:
     unorm8_seconds = time.perf_counter() - unorm8_start
     decoder.close()
     e2e_value = texels * args.steps / seconds / 1e9
+
+    # The same calls on the same reference build with ONE translation unit changed: TextureSet::Decompress
+    # routed to libntcb200.so (oracle/_ref/libntc_ref_ntcb.so).  What an application linked against
+    # ntc.h gets from the integration, measured through ntc.h.
+    via_ntc_h = None
+    if oracle_py.reference_ntcb_available():
+        routed = oracle_py.ReferenceDecoder(data.container, geo.channels, device=0, library=oracle_py.REF_NTCB_LIB)
+
+        def routed_step():
+            routed.decompress(data.use_int8)
+            for mip, cm in enumerate(geo.color_mips):
+                routed.read_mip_into(mip, cm.width, cm.height, base + cm.texel_offset * geo.channels * 2, False)
+
+        for _ in range(max(1, min(args.warmup, 3))):
+            routed_step()
+        routed_ms = []
+        for index in range(args.steps):
+            flush.fill_(index & 0xFF)
+            torch.cuda.synchronize()
+            routed_ms.append(routed.decompress(data.use_int8))
+        torch.cuda.synchronize()
+        routed_start = time.perf_counter()
+        for _ in range(args.steps):
+            routed_step()
+        torch.cuda.synchronize()
+        routed_seconds = time.perf_counter() - routed_start
+        routed.close()
+        via_ntc_h = {"value": texels * args.steps / (sum(routed_ms) / 1e3) / 1e9, "unit": UNIT,
+                     "e2e": texels * args.steps / routed_seconds / 1e9,
+                     "what": "the reference library with TextureSet::Decompress routed to libntcb200.so, driven through "
+                             "ntc::CreateContext / ITextureSet::Decompress / ITextureSet::ReadChannels like the stock arm: "
+                             "value from DecompressionStats::gpuTimeMilliseconds, e2e wall clock with ReadChannels(FLOAT16, Host)"}
     # every Decompress of a set loaded from a file uploads the encoded latents and both weight blobs
     # again (src/TextureSet.cpp:1695-1719); ReadChannels(Host) copies every mip back
     h2d = geo.encoded_latent_bytes + 9472 + 8608
@@ -636,6 +668,7 @@ def run_reference(args) -> dict:
         "e2e_unorm8": {"value": texels * args.steps / unorm8_seconds / 1e9, "unit": UNIT,
                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": texels * geo.channels,
                        "path": "per step Decompress + ReadChannels(UNORM8, Host) of every mip"},
+        "e2e_via_ntc_h": via_ntc_h,
         "gpu_launches": args.steps * geo.mips,  # the reference launches its kernel once per mip
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": 0, "kind": "reference",
                          "sample": "whole workload; the reference's only decoder is its CUDA kernel, run on the GPU of this box"},

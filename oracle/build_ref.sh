@@ -15,11 +15,22 @@
 #   * src/GDeflate.cpp is replaced by oracle/gdeflate_stub.cpp (libdeflate sources are absent);
 #   * src/Shaders.cpp is left out, exactly as the stock build does without prebuilt shaders.
 #
-# Usage: oracle/build_ref.sh [reference-source-dir]
+# With --with-ntcb a second library, oracle/_ref/libntc_ref_ntcb.so, is built from the same objects
+# except TextureSet.cpp, which is compiled from a patched copy (oracle/patch_texture_set.py +
+# oracle/texture_set_ntcb.inl) whose Decompress calls libntcb200.so: the reference's public API
+# (ntc::CreateContext, IContext, ITextureSet) with this repository's decoder behind it.  It proves the
+# integration described in INTEGRATION.md and is test infrastructure like the rest of oracle/.
+#
+# Usage: oracle/build_ref.sh [--with-ntcb] [reference-source-dir]
 #   (default: $NTC_REFERENCE_DIR, else a checkout named `reference` beside this repository)
 set -euo pipefail
 
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+WITH_NTCB=0
+if [ "${1:-}" = "--with-ntcb" ]; then
+    WITH_NTCB=1
+    shift
+fi
 REF="${1:-${NTC_REFERENCE_DIR:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 OBJ="$OUT/obj"
@@ -84,3 +95,20 @@ OBJECTS="$OBJECTS $OBJ/ref_harness_producers.cu.o"
 
 "$NVCC" -arch=sm_100 -shared -o "$OUT/libntc_ref.so" $OBJECTS -lcudart_static -lpthread -ldl -lrt
 echo "built $OUT/libntc_ref.so"
+
+if [ "$WITH_NTCB" = 1 ]; then
+    PRODUCT="$HERE/../rtxntc-library_b200"
+    if [ ! -f "$PRODUCT/libntcb200.so" ]; then
+        echo "build_ref.sh: $PRODUCT/libntcb200.so is not built (make -C rtxntc-library_b200/csrc)" >&2
+        exit 4
+    fi
+    PATCHED="$OUT/obj_ntcb"
+    python3 "$HERE/patch_texture_set.py" "$REF" "$PATCHED"
+    # the patched copy finds its own TextureSet.h first (same directory), everything else in the reference
+    "$CXX" -std=c++17 -O2 -fPIC -fno-strict-aliasing $DEFS -I"$PATCHED" $INCS -I"$HERE/../include" \
+        -c "$PATCHED/TextureSet.cpp" -o "$PATCHED/TextureSet.o"
+    OBJECTS_NTCB="${OBJECTS/$OBJ\/TextureSet.o/$PATCHED/TextureSet.o}"
+    "$NVCC" -arch=sm_100 -shared -o "$OUT/libntc_ref_ntcb.so" $OBJECTS_NTCB -L"$PRODUCT" -lntcb200 \
+        -Xlinker -rpath -Xlinker '$ORIGIN/../../rtxntc-library_b200' -lcudart_static -lpthread -ldl -lrt
+    echo "built $OUT/libntc_ref_ntcb.so"
+fi

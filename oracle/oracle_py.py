@@ -255,17 +255,24 @@ def make_options(use_int8: bool, numerics: int, threads: int = 0, **ref_switches
 # The unmodified reference library (needs a GPU to decode)
 # ---------------------------------------------------------------------------------------------
 
-_ref = None
+# The reference with its CUDA decompression routed through libntcb200.so (build_ref.sh --with-ntcb):
+# the same public API, the same harness, this repository's decoder behind ITextureSet::Decompress.
+REF_NTCB_LIB = os.path.join(HERE, "_ref", "libntc_ref_ntcb.so")
+
+_ref = {}
 
 
 def reference_available() -> bool:
     return os.path.exists(REF_LIB)
 
 
-def reference_lib():
-    global _ref
-    if _ref is None:
-        lib = ctypes.CDLL(REF_LIB)
+def reference_ntcb_available() -> bool:
+    return os.path.exists(REF_NTCB_LIB)
+
+
+def reference_lib(path: str = REF_LIB):
+    if path not in _ref:
+        lib = ctypes.CDLL(path)
         lib.ntcref_last_error.restype = ctypes.c_char_p
         lib.ntcref_open.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int,
                                     ctypes.POINTER(ctypes.c_void_p)]
@@ -282,8 +289,8 @@ def reference_lib():
                                             ctypes.c_size_t, ctypes.c_void_p]
         lib.ntcref_quantize_network.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                 ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
-        _ref = lib
-    return _ref
+        _ref[path] = lib
+    return _ref[path]
 
 
 def reference_probe(container: bytes) -> List[int]:
@@ -326,8 +333,9 @@ def reference_quantize_network(weights: np.ndarray, biases: np.ndarray, use_fp8:
 class ReferenceDecoder:
     """The reference's CUDA decompression of one container, through its public API."""
 
-    def __init__(self, container: bytes, channels: int, device: int = 0, staging_bytes_per_pixel: Optional[int] = None):
-        self._lib = reference_lib()
+    def __init__(self, container: bytes, channels: int, device: int = 0, staging_bytes_per_pixel: Optional[int] = None,
+                 library: str = REF_LIB):
+        self._lib = reference_lib(library)
         self._container = container
         self._handle = ctypes.c_void_p()
         # the reference sizes its ReadChannels staging buffer from TextureSetFeatures::stagingBytesPerPixel
