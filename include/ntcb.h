@@ -481,6 +481,18 @@ int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int wi
    shared memory and tensor-memory columns.  For benchmarks and tests. */
 int ntcb_decode_resident_ctas(int weightMode, int* outCtas);
 
+/* Test hook for the kernels' timeout path (no counterpart in the reference).  Every wait inside the
+   kernels is bounded; a CTA whose wait runs out records it in the status words (word 0 =
+   1, word 1 = tile, word 2 = layer; 0xFFFFFFFF in both for the wait described here), lets the work it has in
+   flight finish, releases its tensor memory and exits, and the host reports NTCB_ERR_DEVICE_TIMEOUT.
+   This call sets, for every later launch of the process, how many polls a CTA spends on its FIRST
+   wait - for the network image its bulk copy brings into shared memory, before any tile is touched
+   and with no tensor-core work in flight - and returns the previous value.  0 makes that wait run
+   out at once, which lets a test walk the whole error path without hanging or faulting anything;
+   NTCB_DEFAULT_WAIT_POLLS restores normal operation.  No other wait is affected. */
+#define NTCB_DEFAULT_WAIT_POLLS (1u << 22)
+uint32_t ntcb_debug_set_network_wait_polls(uint32_t polls);
+
 /* Number of kernel launches this library has issued from the calling process so far
    (bookkeeping for benchmarks). */
 uint64_t ntcb_launch_count(void);

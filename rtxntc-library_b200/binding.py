@@ -20,6 +20,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.environ.get("NTCB_LIBRARY") or os.path.join(_HERE, "libntcb200.so")
 
 MAX_MIPS = 16
+DEFAULT_WAIT_POLLS = 1 << 22  # NTCB_DEFAULT_WAIT_POLLS
 STAGED_NETWORK_BYTES = 14864
 STAGED_REFERENCE_NETWORK_BYTES = 21504
 NUMERICS_REFERENCE, NUMERICS_EXACT = 0, 1  # NtcbNumerics: the reference's binary16 accumulation (default) / exact accumulation
@@ -147,6 +148,8 @@ def lib():
         handle.ntcb_status_string.restype = ctypes.c_char_p
         handle.ntcb_status_string.argtypes = [ctypes.c_int]
         handle.ntcb_launch_count.restype = ctypes.c_uint64
+        handle.ntcb_debug_set_network_wait_polls.restype = ctypes.c_uint32
+        handle.ntcb_debug_set_network_wait_polls.argtypes = [ctypes.c_uint32]
         handle.ntcb_stage_network.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_stage_network_reference.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]

@@ -213,9 +213,7 @@ __device__ __forceinline__ void ConsumeLayerImpl(const Params& params, const Sha
     if (!MbarrierWaitBounded(ctx.barrier, phase))
     {
         failed = 1;
-        status[0] = kStatusBarrierTimeout;
-        status[1] = uint32_t(ctx.tile);
-        status[2] = uint32_t(kLayer);
+        ReportTimeout(status, uint32_t(ctx.tile), uint32_t(kLayer));
     }
     phase ^= 1;
     TcgenFenceAfterSync();
@@ -357,7 +355,7 @@ __device__ __forceinline__ int RunLayer(const Params& params, const SharedStorag
 // the constant tables, set up the barriers and allocate tensor memory.  Returns nonzero, uniformly
 // over the CTA, when some thread gave up waiting for the image (status words written, one more
 // bounded wait for the copy done, tensor memory released): the caller returns at once.
-__device__ __forceinline__ int SetupCta(SharedStorage& shared, const uint8_t* network, uint32_t* status, int tid, int warp)
+__device__ __forceinline__ int SetupCta(SharedStorage& shared, const uint8_t* network, uint32_t* status, uint32_t loadWaitPolls, int tid, int warp)
 {
     // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
     for (int i = tid; i < 256; i += kThreadsPerCta)
@@ -389,12 +387,10 @@ __device__ __forceinline__ int SetupCta(SharedStorage& shared, const uint8_t* ne
     __syncthreads();         // also publishes the barriers' initialisation
     TcgenFenceAfterSync();
     int failed = 0;
-    if (!MbarrierWaitBounded(loadBarrier, 0))
+    if (!MbarrierWaitBounded(loadBarrier, 0, loadWaitPolls))
     {
         failed = 1;
-        status[0] = kStatusBarrierTimeout;
-        status[1] = 0xFFFFFFFFu; // no tile: the network image did not arrive
-        status[2] = 0xFFFFFFFFu;
+        ReportTimeout(status, 0xFFFFFFFFu, 0xFFFFFFFFu); // no tile: the network image did not arrive
     }
     if (__syncthreads_or(failed))
     {
@@ -421,7 +417,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
     const int warp = tid >> 5;      // = the thread's row of the tile
     const int half = warp >> 2;     // 0: rows 0-3 of the tile, 1: rows 4-7
 
-    if (SetupCta(shared, params.network, params.status, tid, warp))
+    if (SetupCta(shared, params.network, params.status, params.loadWaitPolls, tid, warp))
         return;
     int failed = 0;   // this thread gave up on a wait
     const uint32_t tmemBase = shared.tmemBase;
@@ -553,7 +549,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
     // the mip descriptions are indexed per thread: a copy in shared memory (visible after the barrier inside SetupCta)
     if (tid < params.numMips)
         mipTable[tid] = params.mips[tid];
-    if (SetupCta(shared, params.network, params.status, tid, warp))
+    if (SetupCta(shared, params.network, params.status, params.loadWaitPolls, tid, warp))
         return;
     int failed = 0, aborted = 0;
     const uint32_t tmemBase = shared.tmemBase;

@@ -113,6 +113,7 @@ struct KernelParams
     int channels;
     int outputLayout;
     int totalTiles;
+    uint32_t loadWaitPolls; // polls a CTA spends waiting for the network image before it gives up (kSpinLimit by default)
     // converting epilogue (convert != 0): `out` receives pixels in the client's format instead of fp16 texels
     int convert;
     int firstChannel, numChannels; // channels the converted pixel starts with
@@ -131,6 +132,7 @@ struct SampleParams
     int numMips;
     int numLayers;
     int channels;
+    uint32_t loadWaitPolls; // as in KernelParams
     KernelMip mips[16];
 };
 

@@ -476,9 +476,7 @@ __device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefT
     if (!MbarrierWaitBounded(ctx.barrier, phase))
     {
         failed = 1;
-        params.status[0] = kStatusBarrierTimeout;
-        params.status[1] = uint32_t(ctx.tile);
-        params.status[2] = uint32_t(kLayer);
+        ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(kLayer));
     }
     phase ^= 1;
     TcgenFenceAfterSync();
@@ -564,7 +562,7 @@ __device__ __forceinline__ int RunLayerRef(const Params& params, const RefTileCo
 // One-time setup of a CTA: the network image arrives by one TMA bulk copy while the threads fill
 // the constant tables, set up the barriers and allocate tensor memory.  Returns nonzero in every
 // thread that gave up waiting for the image (status words written).
-__device__ __forceinline__ int SetupCtaRef(RefSharedStorage& shared, const uint8_t* network, uint32_t* status, int tid, int warp)
+__device__ __forceinline__ int SetupCtaRef(RefSharedStorage& shared, const uint8_t* network, uint32_t* status, uint32_t loadWaitPolls, int tid, int warp)
 {
     // src/Quantizer.cu:490-495: value = float(nibble) * (1.f / 15.f), stored as binary16
     for (int i = tid; i < 256; i += kRefThreadsPerCta)
@@ -593,12 +591,10 @@ __device__ __forceinline__ int SetupCtaRef(RefSharedStorage& shared, const uint8
     __syncthreads();
     TcgenFenceAfterSync();
     int failed = 0;
-    if (!MbarrierWaitBounded(loadBarrier, 0))
+    if (!MbarrierWaitBounded(loadBarrier, 0, loadWaitPolls))
     {
         failed = 1;
-        status[0] = kStatusBarrierTimeout;
-        status[1] = 0xFFFFFFFFu; // no tile: the network image did not arrive
-        status[2] = 0xFFFFFFFFu;
+        ReportTimeout(status, 0xFFFFFFFFu, 0xFFFFFFFFu); // no tile: the network image did not arrive
     }
     return failed;
 }
@@ -636,7 +632,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
     const int warp = tid >> 5;      // = the thread's row of the tile
     const int half = warp >> 2;     // the 128-row chain of this thread: rows 4 * half .. + 3 of the tile
 
-    int failed = SetupCtaRef(shared, params.network, params.status, tid, warp); // this thread gave up on a wait
+    int failed = SetupCtaRef(shared, params.network, params.status, params.loadWaitPolls, tid, warp); // this thread gave up on a wait
     const uint32_t tmemBase = shared.tmemBase;
     uint32_t phase = 0;
     int aborted = 0;  // some thread of the CTA gave up (uniform: comes out of a barrier)
@@ -749,7 +745,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernel
     // the mip descriptions are indexed per thread: a copy in shared memory (visible after the barrier inside SetupCtaRef)
     if (tid < params.numMips)
         mipTable[tid] = params.mips[tid];
-    int failed = SetupCtaRef(shared, params.network, params.status, tid, warp);
+    int failed = SetupCtaRef(shared, params.network, params.status, params.loadWaitPolls, tid, warp);
     int aborted = 0;
     uint32_t phase = 0;
 
@@ -952,9 +948,7 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
     if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phase))
     {
         failed = 1;
-        params.status[0] = kStatusBarrierTimeout;
-        params.status[1] = uint32_t(ctx.tile);
-        params.status[2] = uint32_t(kLayer);
+        ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(kLayer));
     }
     phase ^= 1;
     TcgenFenceAfterSync();
@@ -1118,7 +1112,7 @@ __device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTil
 }
 
 // Setup and teardown as for the binary16 kernel, on the FP8 kernel's shared-memory structure.
-__device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const uint8_t* network, uint32_t* status, int tid, int warp)
+__device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const uint8_t* network, uint32_t* status, uint32_t loadWaitPolls, int tid, int warp)
 {
     for (int i = tid; i < 256; i += kThreadsPerCta)
     {
@@ -1145,12 +1139,10 @@ __device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const
     __syncthreads();
     TcgenFenceAfterSync();
     int failed = 0;
-    if (!MbarrierWaitBounded(loadBarrier, 0))
+    if (!MbarrierWaitBounded(loadBarrier, 0, loadWaitPolls))
     {
         failed = 1;
-        status[0] = kStatusBarrierTimeout;
-        status[1] = 0xFFFFFFFFu;
-        status[2] = 0xFFFFFFFFu;
+        ReportTimeout(status, 0xFFFFFFFFu, 0xFFFFFFFFu); // no tile: the network image did not arrive
     }
     return failed;
 }
@@ -1182,7 +1174,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
     const int warp = tid >> 5;      // = the thread's row of the tile
     const int half = warp >> 2;     // the 128-row chain of this thread
 
-    int failed = SetupCtaRefFp8(shared, params.network, params.status, tid, warp);
+    int failed = SetupCtaRefFp8(shared, params.network, params.status, params.loadWaitPolls, tid, warp);
     uint32_t phase = 0;
     int aborted = 0;
 
@@ -1295,7 +1287,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
 
     if (tid < params.numMips)
         mipTable[tid] = params.mips[tid];
-    int failed = SetupCtaRefFp8(shared, params.network, params.status, tid, warp);
+    int failed = SetupCtaRefFp8(shared, params.network, params.status, params.loadWaitPolls, tid, warp);
     int aborted = 0;
     uint32_t phase = 0;
 

@@ -59,15 +59,26 @@ __device__ __forceinline__ void BulkCopyToShared(uint32_t dstShared, const void*
                  : "memory");
 }
 
-// Bounded wait: returns false when the barrier did not complete within the spin budget.
-__device__ __forceinline__ bool MbarrierWaitBounded(uint32_t bar, uint32_t parity)
+// Bounded wait: returns false when the barrier did not complete within `limit` polls.
+__device__ __forceinline__ bool MbarrierWaitBounded(uint32_t bar, uint32_t parity, uint32_t limit = kSpinLimit)
 {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    for (uint32_t spin = 0; spin < limit; ++spin)
     {
         if (MbarrierTryWait(bar, parity))
             return true;
     }
     return false;
+}
+
+// Records an expired wait in the status words.  The first thread of the grid to report claims word 0
+// and alone writes the tile and layer, so the three words always describe one and the same wait.
+__device__ __noinline__ void ReportTimeout(uint32_t* status, uint32_t tile, uint32_t layer)
+{
+    if (atomicCAS(&status[0], 0u, kStatusBarrierTimeout) == 0u)
+    {
+        status[1] = tile;
+        status[2] = layer;
+    }
 }
 
 __device__ __forceinline__ void FenceProxyAsyncShared()

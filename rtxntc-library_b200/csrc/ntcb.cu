@@ -22,6 +22,7 @@ namespace ntcb
 
 thread_local char g_lastError[1024] = "";
 std::atomic<uint64_t> g_launchCount{0};
+std::atomic<uint32_t> g_networkWaitPolls{kSpinLimit}; // see ntcb_debug_set_network_wait_polls
 
 void SetError(const char* format, ...)
 {
@@ -484,6 +485,11 @@ int ntcb_stage_network_reference(const void* blob, size_t blobBytes, int weightM
     return NTCB_OK;
 }
 
+uint32_t ntcb_debug_set_network_wait_polls(uint32_t polls)
+{
+    return g_networkWaitPolls.exchange(polls, std::memory_order_relaxed);
+}
+
 int ntcb_decode(const NtcbDecodeParams* p, void* stream)
 {
     if (!p || !p->latents || !p->network || !p->out || !p->status)
@@ -613,6 +619,7 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         return NTCB_OK;
     k.numMips = used;
     k.totalTiles = int(tiles);
+    k.loadWaitPolls = g_networkWaitPolls.load(std::memory_order_relaxed);
 
     const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
     int resident = 0;
@@ -676,6 +683,7 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
         }
         FillKernelMip(m, k.numLayers, k.mips[i]);
     }
+    k.loadWaitPolls = g_networkWaitPolls.load(std::memory_order_relaxed);
     ClearError();
     if (p->numQueries == 0)
         return NTCB_OK;

@@ -456,3 +456,60 @@ def test_inference_on_sample_matches_contract(oracle, shape, numerics):
             assert np.array_equal(resident.mip_numpy(mip)[y, x].view(np.uint16), got[q].view(np.uint16))
     # zero queries is a no-op
     assert resident.sample(device_queries[:0], True).shape[0] == 0
+
+
+def test_an_expired_wait_is_reported_and_leaves_the_gpu_usable():
+    """The kernels' timeout path, walked without hanging or faulting anything: the test hook makes
+    the FIRST wait of every CTA - for the network image, before any tile is touched and with no
+    tensor-core work in flight - run out at once.  Every kernel must then report the wait in the
+    status words ({1, no tile, no layer}), the host must turn it into NTCB_ERR_DEVICE_TIMEOUT, and
+    the next ordinary decode on the same objects must be bit-correct again."""
+    import torch
+
+    lib = binding.lib()
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(200, 72, 6, 0, 2, 8, seed=31, network="unit"))
+    geo = data.geometry
+    queries = torch.from_numpy(synthetic.make_queries(3000, max_lod=geo.mips - 0.001, seed=5)).cuda()
+    with binding.Context(0) as context:
+        for numerics in (REFERENCE, EXACT):
+            resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
+            texture_set = context.create_texture_set(data.container, numerics=numerics)
+            for use_int8 in (True, False):
+                resident.decode(use_int8)
+                good_samples = resident.sample(queries, use_int8)
+                _sync()
+                resident.check_status()
+                good = resident.out.clone()
+
+                assert lib.ntcb_debug_set_network_wait_polls(0) == binding.DEFAULT_WAIT_POLLS
+                try:
+                    resident.out.fill_(float("nan"))
+                    resident.decode(use_int8)
+                    _sync()
+                    assert resident.status.cpu().numpy().view(np.uint32).tolist()[:3] == [1, 0xFFFFFFFF, 0xFFFFFFFF]
+                    with pytest.raises(binding.NtcbError) as error:
+                        resident.check_status()
+                    assert error.value.code == -7
+                    assert bool(torch.isnan(resident.out).all())  # the CTAs left before touching a tile
+                    resident.status.zero_()
+                    resident.sample(queries, use_int8)
+                    _sync()
+                    assert resident.status.cpu().numpy().view(np.uint32).tolist()[:3] == [1, 0xFFFFFFFF, 0xFFFFFFFF]
+                    resident.status.zero_()
+                    # the texture-set level reports it as a status code with a message
+                    with pytest.raises(binding.NtcbError) as error:
+                        texture_set.decompress(use_int8, with_stats=True)
+                    assert error.value.code == -7 and "wait" in str(error.value)
+                finally:
+                    assert lib.ntcb_debug_set_network_wait_polls(binding.DEFAULT_WAIT_POLLS) == 0
+
+                resident.decode(use_int8)
+                again = resident.sample(queries, use_int8)
+                _sync()
+                resident.check_status()
+                assert torch.equal(resident.out.view(torch.int16), good.view(torch.int16))
+                assert torch.equal(again.view(torch.int16), good_samples.view(torch.int16))
+                texture_set.decompress(use_int8, with_stats=True)
+                for mip in range(geo.mips):
+                    assert np.array_equal(texture_set.read_mip(mip).view(np.uint16), resident.mip_numpy(mip).view(np.uint16))
+            texture_set.close()
