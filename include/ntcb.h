@@ -490,7 +490,7 @@ int ntcb_decode_resident_ctas(int weightMode, int* outCtas);
    and with no tensor-core work in flight - and returns the previous value.  0 makes that wait run
    out at once, which lets a test walk the whole error path without hanging or faulting anything;
    NTCB_DEFAULT_WAIT_POLLS restores normal operation.  No other wait is affected. */
-#define NTCB_DEFAULT_WAIT_POLLS (1u << 22)
+#define NTCB_DEFAULT_WAIT_POLLS (1u << 20)
 uint32_t ntcb_debug_set_network_wait_polls(uint32_t polls);
 
 /* Number of kernel launches this library has issued from the calling process so far

@@ -20,7 +20,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.environ.get("NTCB_LIBRARY") or os.path.join(_HERE, "libntcb200.so")
 
 MAX_MIPS = 16
-DEFAULT_WAIT_POLLS = 1 << 22  # NTCB_DEFAULT_WAIT_POLLS
+DEFAULT_WAIT_POLLS = 1 << 20  # NTCB_DEFAULT_WAIT_POLLS
 STAGED_NETWORK_BYTES = 14864
 STAGED_REFERENCE_NETWORK_BYTES = 21504
 NUMERICS_REFERENCE, NUMERICS_EXACT = 0, 1  # NtcbNumerics: the reference's binary16 accumulation (default) / exact accumulation

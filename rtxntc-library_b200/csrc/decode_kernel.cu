@@ -457,11 +457,13 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
 
     int tile = blockIdx.x;
     TilePlace place{0, 0, 0};
+    int tablesMip = -1; // mip whose tap / encoding tables are in shared memory and valid for every inner tile of it
     if (tile < params.totalTiles)
     {
         // ---- tables and latent footprints of the first tile -----------------------------------
         place = locate(tile, 0);
-        PrepareTile<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        PrepareTile<kFp8, false>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
+        tablesMip = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0) ? place.mipIndex : -1;
         __syncthreads();
     }
     while (tile < params.totalTiles)
@@ -494,7 +496,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
 
         // ---- 1. this tile's network inputs -> A operand (the last MMA that read the A operand has
         //         completed: every thread waited for it) -------------------------------------------
-        BuildInputs<kFp8>(params, mip, shared, ctx, lane, warp);
+        BuildInputs<kFp8, false>(params, mip, shared, ctx, lane, warp);
 
         // ---- 2. layer 0; while the tensor core works on it, prepare the NEXT tile: its tables and
         //         footprints replace this tile's, which nobody reads after the barrier inside
@@ -506,7 +508,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, kConvert ? kCtasPerSmConvertin
         if (nextTile < params.totalTiles)
         {
             place = locate(nextTile, place.mipIndex);
-            PrepareTile<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+            // the tables of the previous tile serve this one too when both lie inside the same mip with invariant tables
+            const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
+            PrepareTile<kFp8, false>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, keepsTables && place.mipIndex == tablesMip);
+            tablesMip = keepsTables ? place.mipIndex : -1;
         }
         ConsumeLayer<kFp8, 0, false>(params, shared, ctx, phase, failed);
 
@@ -593,7 +598,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
             const uint32_t slotFill = kFp8 ? 0u : kBiasSlotValue * 0x01010101u;
             words[12] = words[13] = words[14] = slotFill;
             words[15] = kFp8 ? 0u : ((slotFill & 0x00FFFFFFu) | 0x01000000u);
-            SampleGridsDirect<kFp8>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
+            SampleGridsDirect<kFp8, false>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
             // src/RegressionKernels.h:59-85
             float xf = __fmul_rn(float(x), mip.positionScale);
             float yf = __fmul_rn(float(y), mip.positionScale);

@@ -21,7 +21,8 @@ constexpr int kCtasPerSmFp8 = 4;
 constexpr int kCtasPerSmConverting = 4; // ... and the variants with a converting epilogue (either weight mode)
 constexpr int kTmemColumnsPerHalf = 64;    // widest accumulator (layer 0: 64 outputs)
 constexpr int kTmemColumns = 2 * kTmemColumnsPerHalf;
-constexpr uint32_t kSpinLimit = 1u << 22;  // mbarrier polls before a wait is declared expired
+constexpr uint32_t kSpinLimit = 1u << 20;  // mbarrier polls before a wait is declared expired (about two seconds)
+constexpr uint32_t kWaitHintNanoseconds = 2000; // how long one poll may suspend the thread
 constexpr int kFootprintHiBytes = 11264;   // shared memory for a tile's unpacked footprint in the high-res grid
 constexpr int kFootprintLoBytes = 4096;    // ... and in the low-res grid (half the resolution)
 
@@ -99,7 +100,12 @@ struct KernelMip
     int firstTile, tilesX;
     unsigned tilesXMagic; // ceil(2^32 / tilesX) for tilesX > 1: local / tilesX == umulhi(local, magic) while local * tilesX < 2^32
     int staged;      // the tile footprints of both grids fit into shared memory
-    int strideShift; // log2 of the bytes per staged latent pixel (8 bytes per layer, rounded up to a power of two)
+    int strideBytes; // bytes per staged latent pixel: 8 per layer, padded to an odd multiple of 8 (8, 24, 24, 40) so that
+                     // the 8-byte reads of neighbouring pixels fall into different shared-memory banks
+    int storeBytes;  // widest store (4, 8 or 16 bytes) the fp16 texels of this mip may go out with: the interleaved
+                     // layout with a texel size and a mip address that are multiples of it; 4 otherwise
+    int invariant;   // every size involved is a power of two: the tap and positional-encoding tables of a tile do not
+                     // depend on which tile of the mip it is (see PrepareTaps)
 };
 
 struct KernelParams

@@ -52,12 +52,22 @@
 #define NTCB_ABLATE 0
 #endif
 
+// NTCB_DECOUPLE = 1: the two 128-row chains of a tile of DecodeKernelRefFp8 synchronise with each
+// other once per tile (before layer 0) instead of once per layer: each chain has its own issuing
+// thread, which waits on an mbarrier that the chain's 128 threads arrive on when their rows of the A
+// operand are written, so a chain whose matrix product has finished goes on without waiting for the
+// other one.
+#ifndef NTCB_DECOUPLE
+#define NTCB_DECOUPLE 0
+#endif
+
 namespace ntcb
 {
 namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
+constexpr bool kDecouple = NTCB_DECOUPLE != 0;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
 __device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
@@ -150,17 +160,17 @@ __device__ __forceinline__ uint32_t ActivateRef(uint32_t bits)
 // Shared memory
 // ---------------------------------------------------------------------------------------------
 
-// Per-tile lookup tables (separable in x and y, computed once per tile column / row).
+// Per-tile lookup tables: the taps (shared with the other kernels) and the positional encoding as
+// quantised binary16 pairs.
 struct __align__(16) RefTileTables
 {
-    int4 colTap[2][kTileWidth];   // per grid and column: footprint x index, dx, 1 - dx
-    int4 rowTap[2][kRefTileHeight];  // per grid and row: footprint y index, dy, 1 - dy
-    // positional encoding as quantised binary16 pairs: word w = (wave w phase 0, wave w phase 0.25)
+    TapTables taps;
+    // positional encoding: word w = (wave w phase 0, wave w phase 0.25)
     uint4 colEnc[kTileWidth];
     uint4 rowEnc[kRefTileHeight];
-    int footWidth[2];
     uint32_t lodPair;   // (lod, lod)
     uint32_t zeroPair;  // (quantised 0, quantised 0)
+    uint32_t pad[2];
 };
 
 struct __align__(128) RefSharedStorage
@@ -187,40 +197,22 @@ struct RefTileContext
     int tile, x, y;
     uint32_t* out;
     uint32_t outStepWords;
+    int storeBytes; // widest store the texel may go out with (KernelMip::storeBytes)
+    uint32_t ready; // decoupled chains: shared address of this chain's operand-ready mbarrier
 };
 
 // ---------------------------------------------------------------------------------------------
 // Inputs
 // ---------------------------------------------------------------------------------------------
 
-// Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory.
-// Even warps work on the high-res grid, odd warps on the low-res grid.
+// Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory
+// (`tablesValid`: the tables already hold this tile's values, see PrepareTaps).
 template <bool kFp8>
 __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const KernelMip& mip, RefSharedStorage& shared,
-    int tileX0, int tileY0, int lane, int warp)
+    int tileX0, int tileY0, int lane, int warp, bool tablesValid)
 {
-    const int grid = warp & 1;
-    const int gw = grid ? mip.loWidth : mip.hiWidth;
-    const int gh = grid ? mip.loHeight : mip.hiHeight;
-
-    int xb, yb;
-    float dx, dy;
-    AxisTap(min(tileX0 + lane, mip.width - 1), mip.invWidth, gw, xb, dx);
-    AxisTap(min(tileY0 + (lane & (kRefTileHeight - 1)), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
-    const int fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
-    const int fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
-    const int footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
-    const int footH = __shfl_sync(0xFFFFFFFFu, yb, kRefTileHeight - 1) - fy0 + 2;
-
-    if (warp < 2)
-    {
-        shared.tables.colTap[grid][lane] = make_int4(xb - fx0, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
-        if (lane < kRefTileHeight)
-            shared.tables.rowTap[grid][lane] = make_int4(yb - fy0, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
-        if (lane == 0)
-            shared.tables.footWidth[grid] = footW;
-    }
-    else if (warp < 4)
+    static_assert(kRefTileHeight == kTileHeight && kRefThreadsPerCta == kThreadsPerCta, "the tap tables assume the common tile");
+    if (!tablesValid && warp >= 2 && warp < 4)
     {
         // positional encoding (src/RegressionKernels.h:59-85): warp 2 the x part per column, warp 3
         // the y part per row, quantised exactly as the per-texel inputs would be
@@ -246,39 +238,8 @@ __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const
             shared.tables.zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
         }
     }
-
-    if (mip.staged)
-    {
-        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
-        const int count = footW * footH;
-        // p / footW == (p * magic) >> 20 for p < 2048; the IEEE quotient of 2^20 / footW floors exactly
-        const uint32_t magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
-        const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
-        const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
-        uint8_t* foot = grid ? shared.footprintLo : shared.footprintHi;
-        for (int p = lane + 32 * (warp >> 1); p < count; p += kRefThreadsPerCta / 2)
-        {
-            const int fy = int((uint32_t(p) * magic) >> 20);
-            const int fx = p - fy * footW;
-            // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
-            int gx = fx0 + fx, gy = fy0 + fy;
-            gx += gx < 0 ? gw : 0;
-            gx -= gx >= gw ? gw : 0;
-            gy += gy < 0 ? gh : 0;
-            gy -= gy >= gh ? gh : 0;
-            const uint16_t* src = plane0 + size_t(gy) * gw + gx;
-            uint2* dst = reinterpret_cast<uint2*>(foot + (size_t(p) << mip.strideShift));
-#pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
-            {
-                if (layer < params.numLayers)
-                {
-                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
-                    dst[layer] = make_uint2(shared.latentTable[pixel & 0xFF], shared.latentTable[pixel >> 8]);
-                }
-            }
-        }
-    }
+    PrepareTaps<true>(params, mip, shared.tables.taps, shared.footprintHi, shared.footprintLo, shared.latentTable, tileX0, tileY0,
+        lane, warp, tablesValid);
 }
 
 // Four inputs of one latent layer from the four taps, as two binary16 pairs.
@@ -307,9 +268,8 @@ template <bool kFp8>
 __device__ __forceinline__ void GatherGridRef(const KernelParams& params, const KernelMip& mip, const RefSharedStorage& shared,
     int grid, int lane, int tileRow, uint32_t* words)
 {
-    const int4 col = shared.tables.colTap[grid][lane];
-    const int4 row = shared.tables.rowTap[grid][tileRow];
-    const int footW = shared.tables.footWidth[grid];
+    const int4 col = shared.tables.taps.colTap[grid][lane];
+    const int4 row = shared.tables.taps.rowTap[grid][tileRow];
     const float dx = __int_as_float(col.y), dxn = __int_as_float(col.z);
     const float dy = __int_as_float(row.y), dyn = __int_as_float(row.z);
     // src/FeatureGridDevice.h:46-49
@@ -317,9 +277,9 @@ __device__ __forceinline__ void GatherGridRef(const KernelParams& params, const 
     const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
     const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
 
-    const int stride = 1 << mip.strideShift;
-    const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (size_t(row.x * footW + col.x) << mip.strideShift);
-    const uint8_t* tap10 = tap00 + (size_t(footW) << mip.strideShift);
+    const int stride = mip.strideBytes;
+    const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (col.x + row.x);
+    const uint8_t* tap10 = tap00 + shared.tables.taps.rowBytes[grid];
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
     {
@@ -376,8 +336,8 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
         // footprint too large to stage: read the taps from global memory; threads past the right /
         // bottom edge compute a clamped texel and store nothing
         const int x = min(ctx.x, mip.width - 1), y = min(ctx.y, mip.rowEnd - 1);
-        const float u = __fmul_rn(__fadd_rn(float(x), 0.5f), mip.invWidth);
-        const float v = __fmul_rn(__fadd_rn(float(y), 0.5f), mip.invHeight);
+        const float u = TexelCoordinate<true>(x, mip.width, mip.invWidth);
+        const float v = TexelCoordinate<true>(y, mip.height, mip.invHeight);
         GridTaps taps;
         SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
         const uint16_t* hi = params.latents + mip.hiOffset;
@@ -668,10 +628,12 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
 
     int tile = blockIdx.x;
     TilePlace place{0, 0, 0};
+    int tablesMip = -1; // mip whose tap / encoding tables are in shared memory and valid for every inner tile of it
     if (tile < params.totalTiles)
     {
         place = locate(tile, 0);
-        PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
+        tablesMip = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0) ? place.mipIndex : -1;
         __syncthreads();
     }
     while (tile < params.totalTiles)
@@ -713,7 +675,10 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
         if (nextTile < params.totalTiles)
         {
             place = locate(nextTile, place.mipIndex);
-            PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+            // the tables of the previous tile serve this one too when both lie inside the same mip with invariant tables
+            const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
+            PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, keepsTables && place.mipIndex == tablesMip);
+            tablesMip = keepsTables ? place.mipIndex : -1;
         }
         ConsumeLayerRef<kFp8, 0, false>(params, ctx, phase, failed);
 
@@ -760,6 +725,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernel
     ctx.networkBase = SharedAddress(shared.network);
     ctx.biasRegion = SharedAddress(shared.biasRegion);
     ctx.outStepWords = 1;
+    ctx.storeBytes = 4;
 
     const uint32_t zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
     const unsigned long long tiles = (params.numQueries + kRefThreadsPerCta - 1) / kRefThreadsPerCta;
@@ -783,9 +749,9 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernel
 #pragma unroll
             for (int i = 0; i < 16; ++i)
                 words[i] = zeroPair; // unused feature slots hold quantised zeros (src/Inference.cu:49)
-            // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
-            const float su = __fmul_rn(__fadd_rn(float(x), 0.5f), mip.invWidth);
-            const float sv = __fmul_rn(__fadd_rn(float(y), 0.5f), mip.invHeight);
+            // src/Inference.cu:52-53
+            const float su = TexelCoordinate<true>(x, mip.width, mip.invWidth);
+            const float sv = TexelCoordinate<true>(y, mip.height, mip.invHeight);
             GridTaps taps;
             SetupTaps(su, sv, mip.hiWidth, mip.hiHeight, taps);
             const uint16_t* hi = params.latents + mip.hiOffset;
@@ -857,6 +823,8 @@ struct __align__(128) RefFp8SharedStorage
     TileTables tables;
     uint64_t barrier[kRefChains]; // MMA completion, per chain
     uint64_t loadBarrier;         // arrival of the network image
+    uint64_t ready[kRefChains];   // decoupled chains: the chain's 128 rows of the A operand are written
+    uint64_t prepared;            // decoupled chains: all 256 threads have finished preparing the next tile
     uint32_t tmemBase;
 };
 
@@ -873,8 +841,9 @@ __device__ __forceinline__ void UmmaE4m3F16(uint32_t tmemD, uint64_t descA, uint
         : "memory");
 }
 
+// The matrix products of one layer for one chain of the tile, issued by the calling thread.
 template <int kLayer>
-__device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int failed)
+__device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int half)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
     constexpr int kK = kLayer == 0 ? 48 : kLayer == 1 ? 64 : kLayer == 2 ? 48 : 32;
@@ -882,49 +851,93 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
         kLayer == 0 ? kRefWeightOffset0 : kLayer == 1 ? kRefWeightOffset1 : kLayer == 2 ? kRefWeightOffset2 : kRefWeightOffset3;
     constexpr int kBiasOffset =
         kLayer == 0 ? kRefBiasOffset0 : kLayer == 1 ? kRefBiasOffset1 : kLayer == 2 ? kRefBiasOffset2 : kRefBiasOffset3;
+    // both descriptors: binary16 accumulators, operand formats 0 (binary16 for kind::f16, e4m3 for kind::f8f6f4)
+    constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
+    // The issuing thread is the critical path of the layer: the four base descriptors are built
+    // once, every operand is then a constant offset (in 16-byte units) added to the address field.
+    const uint64_t operandBase = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes, 2048, 128);
+    const uint64_t onesBase = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
+    const uint64_t weightBase = MakeSmemDescriptor(ctx.networkBase + kWeightOffset, kN * 16, 128);
+    const uint64_t biasBase = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
+    const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
+    // accumulators := bias (binary16 step: rows (1, 0, ...) times the bias column: exact)
+    UmmaF16(accumulators, onesBase, biasBase, instr, 0);
+#pragma unroll
+    for (int step = 0; step < kK / 16; ++step)
+    {
+        if (kLayer < 3)
+        {
+            // 16 products of the 32-wide chunk step / 2: weight copy `step` has the other 16 columns zeroed
+            const uint64_t descA = operandBase + uint64_t(((step / 2) * 2 * 2048) >> 4);
+            const uint64_t descB = weightBase + uint64_t((step * kN * 32) >> 4);
+            UmmaE4m3F16(accumulators, descA, descB, instr, 1);
+        }
+        else
+        {
+            // binary16 operands: one K step = two core matrices of 8 halves
+            const uint64_t descA = operandBase + uint64_t((step * 2 * 2048) >> 4);
+            const uint64_t descB = weightBase + uint64_t((step * 2 * kN * 16) >> 4);
+            UmmaF16(accumulators, descA, descB, instr, 1);
+        }
+    }
+    // arrives once everything issued so far has completed: this chain's accumulators are ready
+    UmmaCommit(ctx.barrierBase + half * 8);
+}
 
+// Bits of the per-thread word that tracks the parity of the barriers a thread waits on.
+constexpr uint32_t kPhaseMma = 1, kPhaseReady = 2, kPhasePrepared = 4;
+
+// First half of a layer: hands the A operand written before this call to the tensor core.  Returns
+// nonzero (uniformly over the CTA) when the CTA agreed that some thread gave up on a wait.
+template <int kLayer>
+__device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int& failed, uint32_t& phases, uint32_t* status)
+{
+    // Makes the A operand visible to the tensor core (async proxy) and orders this thread's reads of
+    // the previous layer's accumulators before they are overwritten.
     FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
-    if (__syncthreads_or(failed))
-        return 1;
-
-    if (ctx.tid == 0 && !(kAblate & 16))
+    if (!kDecouple || kLayer == 0)
     {
-        TcgenFenceAfterSync();
-        // both descriptors: binary16 accumulators, operand formats 0 (binary16 for kind::f16, e4m3 for kind::f8f6f4)
-        constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
-        // The issuing thread is the critical path of the layer: the four base descriptors are built
-        // once, every operand is then a constant offset (in 16-byte units) added to the address field.
-        const uint64_t operandBase = MakeSmemDescriptor(ctx.operandA, 2048, 128);
-        const uint64_t onesBase = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
-        const uint64_t weightBase = MakeSmemDescriptor(ctx.networkBase + kWeightOffset, kN * 16, 128);
-        const uint64_t biasBase = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
-#pragma unroll
-        for (int half = 0; half < kRefChains; ++half)
+        // the whole CTA meets: also the point where it agrees on giving up
+        if (__syncthreads_or(failed))
+            return 1;
+        if (kAblate & 16)
+            return 0;
+        if (kDecouple)
         {
-            const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
-            // accumulators := bias (binary16 step: rows (1, 0, ...) times the bias column: exact)
-            UmmaF16(accumulators, onesBase, biasBase, instr, 0);
-#pragma unroll
-            for (int step = 0; step < kK / 16; ++step)
+            if ((ctx.tid & 127) == 0)
             {
-                if (kLayer < 3)
-                {
-                    // 16 products of the 32-wide chunk step / 2: weight copy `step` has the other 16 columns zeroed
-                    const uint64_t descA = operandBase + uint64_t((half * kOperandBytes + (step / 2) * 2 * 2048) >> 4);
-                    const uint64_t descB = weightBase + uint64_t((step * kN * 32) >> 4);
-                    UmmaE4m3F16(accumulators, descA, descB, instr, 1);
-                }
-                else
-                {
-                    // binary16 operands: one K step = two core matrices of 8 halves
-                    const uint64_t descA = operandBase + uint64_t((half * kOperandBytes + step * 2 * 2048) >> 4);
-                    const uint64_t descB = weightBase + uint64_t((step * 2 * kN * 16) >> 4);
-                    UmmaF16(accumulators, descA, descB, instr, 1);
-                }
+                TcgenFenceAfterSync();
+                IssueChainRefFp8<kLayer>(ctx, ctx.tid >> 7);
             }
-            UmmaCommit(ctx.barrierBase + half * 8);
         }
+        else if (ctx.tid == 0)
+        {
+            TcgenFenceAfterSync();
+            // (one issuing thread for both chains measured faster than one per chain with this barrier)
+#pragma unroll
+            for (int half = 0; half < kRefChains; ++half)
+                IssueChainRefFp8<kLayer>(ctx, half);
+        }
+    }
+    else
+    {
+        // the chain's 128 threads arrive; its first thread waits for all of them and issues
+        MbarrierArrive(ctx.ready);
+        if ((ctx.tid & 127) == 0)
+        {
+            if (MbarrierWaitBounded(ctx.ready, (phases & kPhaseReady) ? 1u : 0u))
+            {
+                TcgenFenceAfterSync();
+                IssueChainRefFp8<kLayer>(ctx, ctx.tid >> 7);
+            }
+            else
+            {
+                failed = 1;
+                ReportTimeout(status, uint32_t(ctx.tile), uint32_t(16 + kLayer));
+            }
+        }
+        phases ^= kPhaseReady;
     }
     return 0;
 }
@@ -941,16 +954,16 @@ __device__ __forceinline__ uint32_t ActivateToE4m3(uint32_t bits)
 }
 
 template <int kLayer, bool kConvert, typename Params>
-__device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+__device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phases, int& failed)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
-    if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phase))
+    if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phases & kPhaseMma))
     {
         failed = 1;
         ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(kLayer));
     }
-    phase ^= 1;
+    phases ^= kPhaseMma;
     TcgenFenceAfterSync();
 
     if ((kAblate & 4) && kLayer < 3)
@@ -1052,24 +1065,7 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
                 bits[i] = uint32_t(ctx.tile * 7 + i) & 0x3FFF3FFFu;
         }
         const int channelPairs = params.channels >> 1;
-        uint32_t special = 0; // bit 15 / 31 set when a value has an all-ones exponent
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (j < channelPairs)
-                special |= (bits[j] & 0x7C007C00u) + 0x04000400u;
-        if (special & 0x80008000u)
-        {
-            // Inf / NaN -> 0 (src/CudaUtils.h:30-35); rare, so kept off the common path
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-            {
-                if (j < channelPairs)
-                {
-                    if ((bits[j] & 0x7C00u) == 0x7C00u) bits[j] &= 0xFFFF0000u;
-                    if ((bits[j] & 0x7C000000u) == 0x7C000000u) bits[j] &= 0x0000FFFFu;
-                }
-            }
-        }
+        ScrubSpecials(bits, channelPairs);
         if constexpr (kConvert)
         {
 #pragma unroll
@@ -1092,22 +1088,17 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
                     ctx.out[0] = all;
             }
             else
-            {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (j < channelPairs)
-                        ctx.out[j * ctx.outStepWords] = bits[j];
-            }
+                StoreTexel(ctx.out, ctx.outStepWords, ctx.storeBytes, bits, channelPairs);
         }
     }
 }
 
 template <int kLayer, bool kConvert, typename Params>
-__device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
+__device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phases, int& failed)
 {
-    if (IssueLayerRefFp8<kLayer>(ctx, failed))
+    if (IssueLayerRefFp8<kLayer>(ctx, failed, phases, params.status))
         return 1;
-    ConsumeLayerRefFp8<kLayer, kConvert>(params, ctx, phase, failed);
+    ConsumeLayerRefFp8<kLayer, kConvert>(params, ctx, phases, failed);
     return 0;
 }
 
@@ -1126,7 +1117,11 @@ __device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const
     if (tid == 0)
     {
         for (int chain = 0; chain < kRefChains; ++chain)
+        {
             MbarrierInit(SharedAddress(&shared.barrier[chain]), 1);
+            MbarrierInit(SharedAddress(&shared.ready[chain]), 128);
+        }
+        MbarrierInit(SharedAddress(&shared.prepared), kThreadsPerCta);
         MbarrierInit(loadBarrier, 1);
         FenceBarrierInit();
         MbarrierArriveExpectTx(loadBarrier, kRefNetworkBytes);
@@ -1147,7 +1142,7 @@ __device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const
     return failed;
 }
 
-__device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, const RefTileContext& ctx, uint32_t phase, int failed,
+__device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, const RefTileContext& ctx, uint32_t phases, int failed,
     int tid, int warp)
 {
     TcgenFenceBeforeSync();
@@ -1155,7 +1150,7 @@ __device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, c
     if (aborted && tid == 0)
     {
         for (int chain = 0; chain < kRefChains; ++chain)
-            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phase ^ 1);
+            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, (phases & kPhaseMma) ^ 1);
         (void)MbarrierWaitBounded(SharedAddress(&shared.loadBarrier), 0);
     }
     __syncthreads();
@@ -1184,6 +1179,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
     ctx.tmemLane = ctx.tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
     ctx.barrierBase = SharedAddress(&shared.barrier[0]);
     ctx.barrier = ctx.barrierBase + half * 8;
+    ctx.ready = SharedAddress(&shared.ready[half]);
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
@@ -1208,10 +1204,14 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
 
     int tile = blockIdx.x;
     TilePlace place{0, 0, 0};
+    int tablesMip = -1; // mip whose tap / encoding tables are in shared memory and valid for every inner tile of it
     if (tile < params.totalTiles)
     {
         place = locate(tile, 0);
-        PrepareTile<true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
+        PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
+        tablesMip = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0) ? place.mipIndex : -1;
+        if (kDecouple)
+            MbarrierArrive(SharedAddress(&shared.prepared));
         __syncthreads();
     }
     while (tile < params.totalTiles)
@@ -1220,7 +1220,51 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         ctx.tile = tile;
         ctx.x = place.tileX0 + lane;
         ctx.y = place.tileY0 + warp;
+        if (kDecouple)
         {
+            // the tables and footprints of this tile, written by all 256 threads while the previous tile's
+            // first layer ran, are complete (the chains no longer meet between that point and this one)
+            if (!MbarrierWaitBounded(SharedAddress(&shared.prepared), (phase & kPhasePrepared) ? 1u : 0u))
+            {
+                failed = 1;
+                ReportTimeout(params.status, uint32_t(tile), 32u);
+            }
+            phase ^= kPhasePrepared;
+        }
+        // the e4m3 input stage is the one of the exact-accumulation kernel (64-byte rows of codes)
+        if (kAblate & 2)
+        {
+            const uint32_t filler = uint32_t(tile) & 0x3F3F3F3Fu;
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk)
+                ctx.rowChunk[chunk * 128] = make_uint4(filler, filler + chunk, filler, filler);
+        }
+        else
+            BuildInputs<true, true>(params, mip, shared, ctx, lane, warp);
+
+        aborted = IssueLayerRefFp8<0>(ctx, failed, phase, params.status);
+        if (aborted)
+            break;
+        const int nextTile = tile + int(gridDim.x);
+        if (nextTile < params.totalTiles)
+        {
+            place = locate(nextTile, place.mipIndex);
+            // the tables of the previous tile serve this one too when both lie inside the same mip with invariant tables
+            const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
+            if (!(kAblate & 1))
+                PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, keepsTables && place.mipIndex == tablesMip);
+            tablesMip = keepsTables ? place.mipIndex : -1;
+        }
+        if (kDecouple)
+            MbarrierArrive(SharedAddress(&shared.prepared));
+        ConsumeLayerRefFp8<0, false>(params, ctx, phase, failed);
+
+        aborted = RunLayerRefFp8<1, false>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<2, false>(params, ctx, phase, failed);
+        if (aborted)
+            break;
+        {
+            // where the texel goes (worked out only now: nothing of it has to stay in registers through the layers)
             const bool planar = params.outputLayout == kLayoutPlanarPairs;
             const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
                                           : (uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x)) * uint32_t(params.channels);
@@ -1237,35 +1281,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
             {
                 ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
                 ctx.outStepWords = planar ? uint32_t(mip.width) : 1u;
+                ctx.storeBytes = mip.storeBytes;
             }
         }
-
-        // the e4m3 input stage is the one of the exact-accumulation kernel (64-byte rows of codes)
-        if (kAblate & 2)
-        {
-            const uint32_t filler = uint32_t(tile) & 0x3F3F3F3Fu;
-#pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk)
-                ctx.rowChunk[chunk * 128] = make_uint4(filler, filler + chunk, filler, filler);
-        }
-        else
-            BuildInputs<true>(params, mip, shared, ctx, lane, warp);
-
-        aborted = IssueLayerRefFp8<0>(ctx, failed);
-        if (aborted)
-            break;
-        const int nextTile = tile + int(gridDim.x);
-        if (nextTile < params.totalTiles)
-        {
-            place = locate(nextTile, place.mipIndex);
-            if (!(kAblate & 1))
-                PrepareTile<true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp);
-        }
-        ConsumeLayerRefFp8<0, false>(params, ctx, phase, failed);
-
-        aborted = RunLayerRefFp8<1, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRefFp8<2, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRefFp8<3, kConvert>(params, ctx, phase, failed);
+        aborted = RunLayerRefFp8<3, kConvert>(params, ctx, phase, failed);
         if (aborted)
             break;
         tile = nextTile;
@@ -1297,11 +1316,13 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
     ctx.tmemLane = ctx.tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
     ctx.barrierBase = SharedAddress(&shared.barrier[0]);
     ctx.barrier = ctx.barrierBase + half * 8;
+    ctx.ready = SharedAddress(&shared.ready[half]);
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
     ctx.biasRegion = SharedAddress(shared.biasRegion);
     ctx.outStepWords = 1;
+    ctx.storeBytes = 4;
 
     const unsigned long long tiles = (params.numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
     for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x)
@@ -1329,7 +1350,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
 #pragma unroll
             for (int i = 12; i < 16; ++i)
                 words[i] = 0;        // K padding
-            SampleGridsDirect<true>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
+            SampleGridsDirect<true, true>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
             // src/RegressionKernels.h:59-85
             float xf = __fmul_rn(float(x), mip.positionScale);
             float yf = __fmul_rn(float(y), mip.positionScale);

@@ -76,52 +76,124 @@ __device__ __forceinline__ uint32_t SampleLayer(const uint16_t* __restrict__ pla
     return PackCodes<kFp8>(pairs[0], pairs[1]);
 }
 
-// Per-tile lookup tables: the bilinear tap position and weights are separable in x and y, and so
-// is the positional encoding, so they are computed once per tile column / row instead of once per
-// texel.
+// Per-tile lookup tables of the bilinear taps: tap position and weights are separable in x and y, so
+// they are computed once per tile column / row instead of once per texel.  Shared by every decode
+// kernel.
+struct __align__(16) TapTables
+{
+    // per grid (0 = high-res, 1 = low-res) and tile column: byte offset of the left tap inside a footprint row, dx, 1 - dx
+    int4 colTap[2][kTileWidth];
+    // per grid and tile row: byte offset of the upper tap's footprint row, dy, 1 - dy
+    int4 rowTap[2][kTileHeight];
+    int footWidth[2], footHeight[2]; // footprint size in latent pixels, per grid
+    int rowBytes[2];                 // bytes per footprint row, per grid
+    int pad[2];
+};
+
+// Tap tables plus the positional encoding as operand bytes (kernels whose A operand holds 8-bit codes).
 struct __align__(16) TileTables
 {
-    // per grid (0 = high-res, 1 = low-res) and tile column: footprint x index, dx, 1 - dx
-    int4 colTap[2][kTileWidth];
-    // per grid and tile row: footprint y index, dy, 1 - dy
-    int4 rowTap[2][kTileHeight];
+    TapTables taps;
     // positional-encoding operand bytes: x = {X0 w0, X1 w0, X0 w1, X1 w1}, y = {X0 w2, X1 w2, 0, 0}
     uint2 colEnc[kTileWidth];
     uint2 rowEnc[kTileHeight];
-    int footWidth[2];  // footprint width in latent pixels, per grid
     uint32_t lodWord;  // operand bytes of inputs 44..47: lod, lod, 0, 0
-    uint32_t pad;
+    uint32_t pad[3];
 };
 
-// Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory
+// Builds the tile's tap tables and stages the latent footprint of both grids in shared memory
 // (nibbles unpacked to binary16 once per latent pixel instead of once per texel and tap).
 // Even warps work on the high-res grid, odd warps on the low-res grid.
-template <bool kFp8, typename Shared>
-__device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, Shared& shared,
-    int tileX0, int tileY0, int lane, int warp)
+//
+// `tablesValid`: the tables already hold this tile's values.  In a mip whose sizes and grid sizes
+// are powers of two (KernelMip::invariant) every tile that lies wholly inside the mip has the same
+// tap offsets and fractions relative to its own footprint - all the arithmetic is exact - so the
+// tables are built for the first such tile and only the footprint is staged for the others.
+template <bool kReferenceDivision>
+__device__ __forceinline__ void PrepareTaps(const KernelParams& params, const KernelMip& mip, TapTables& taps,
+    uint8_t* footprintHi, uint8_t* footprintLo, const uint32_t* latentTable, int tileX0, int tileY0, int lane, int warp,
+    bool tablesValid)
 {
     const int grid = warp & 1;
     const int gw = grid ? mip.loWidth : mip.hiWidth;
     const int gh = grid ? mip.loHeight : mip.hiHeight;
+    const int stride = mip.strideBytes;
 
-    int xb, yb;
-    float dx, dy;
-    AxisTap(min(tileX0 + lane, mip.width - 1), mip.invWidth, gw, xb, dx);
-    AxisTap(min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1), mip.invHeight, gh, yb, dy);
-    const int fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
-    const int fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
-    const int footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
-    const int footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
-
-    if (warp < 2)
+    int fx0, fy0, footW, footH;
+    if (tablesValid)
     {
-        shared.tables.colTap[grid][lane] = make_int4(xb - fx0, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
-        if (lane < kTileHeight)
-            shared.tables.rowTap[grid][lane] = make_int4(yb - fy0, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
-        if (lane == 0)
-            shared.tables.footWidth[grid] = footW;
+        // only the footprint's origin depends on the tile: the taps of its first column and row
+        float unused;
+        AxisTap<kReferenceDivision>(tileX0, mip.width, mip.invWidth, gw, fx0, unused);
+        AxisTap<kReferenceDivision>(tileY0, mip.height, mip.invHeight, gh, fy0, unused);
+        footW = taps.footWidth[grid];
+        footH = taps.footHeight[grid];
     }
-    else if (warp < 4)
+    else
+    {
+        int xb, yb;
+        float dx, dy;
+        AxisTap<kReferenceDivision>(min(tileX0 + lane, mip.width - 1), mip.width, mip.invWidth, gw, xb, dx);
+        AxisTap<kReferenceDivision>(min(tileY0 + (lane & (kTileHeight - 1)), mip.rowEnd - 1), mip.height, mip.invHeight, gh, yb, dy);
+        fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
+        fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
+        footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
+        footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
+        if (warp < 2)
+        {
+            taps.colTap[grid][lane] = make_int4((xb - fx0) * stride, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
+            if (lane < kTileHeight)
+                taps.rowTap[grid][lane] =
+                    make_int4((yb - fy0) * footW * stride, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
+            if (lane == 0)
+            {
+                taps.footWidth[grid] = footW;
+                taps.footHeight[grid] = footH;
+                taps.rowBytes[grid] = footW * stride;
+            }
+        }
+    }
+
+    if (mip.staged)
+    {
+        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
+        const int count = footW * footH;
+        // p / footW == (p * magic) >> 20 for p < 2048; the IEEE quotient of 2^20 / footW floors exactly
+        const uint32_t magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
+        const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
+        const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
+        uint8_t* foot = grid ? footprintLo : footprintHi;
+        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
+        {
+            const int fy = int((uint32_t(p) * magic) >> 20);
+            const int fx = p - fy * footW;
+            // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
+            int gx = fx0 + fx, gy = fy0 + fy;
+            gx += gx < 0 ? gw : 0;
+            gx -= gx >= gw ? gw : 0;
+            gy += gy < 0 ? gh : 0;
+            gy -= gy >= gh ? gh : 0;
+            const uint16_t* src = plane0 + size_t(gy) * gw + gx;
+            uint2* dst = reinterpret_cast<uint2*>(foot + p * stride);
+#pragma unroll
+            for (int layer = 0; layer < 4; ++layer)
+            {
+                if (layer < params.numLayers)
+                {
+                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
+                    dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
+                }
+            }
+        }
+    }
+}
+
+// The tile's tables (taps and positional encoding as operand bytes) and its staged footprints.
+template <bool kFp8, bool kReferenceDivision, typename Shared>
+__device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, Shared& shared,
+    int tileX0, int tileY0, int lane, int warp, bool tablesValid)
+{
+    if (!tablesValid && warp >= 2 && warp < 4)
     {
         // positional encoding (src/RegressionKernels.h:59-85): warp 2 the x part per column, warp 3
         // the y part per row, quantised exactly as the per-texel inputs would be
@@ -146,39 +218,16 @@ __device__ __forceinline__ void PrepareTile(const KernelParams& params, const Ke
             shared.tables.lodWord = PackCodes<kFp8>(QuantizeInputPair<kFp8>(__float2half2_rn(mip.positionLod)),
                                                    QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
     }
+    PrepareTaps<kReferenceDivision>(params, mip, shared.tables.taps, shared.footprintHi, shared.footprintLo, shared.latentTable,
+        tileX0, tileY0, lane, warp, tablesValid);
+}
 
-    if (mip.staged)
-    {
-        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
-        const int count = footW * footH;
-        // p / footW == (p * magic) >> 20 for p < 2048; the IEEE quotient of 2^20 / footW floors exactly
-        const uint32_t magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
-        const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
-        const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
-        uint8_t* foot = grid ? shared.footprintLo : shared.footprintHi;
-        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
-        {
-            const int fy = int((uint32_t(p) * magic) >> 20);
-            const int fx = p - fy * footW;
-            // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
-            int gx = fx0 + fx, gy = fy0 + fy;
-            gx += gx < 0 ? gw : 0;
-            gx -= gx >= gw ? gw : 0;
-            gy += gy < 0 ? gh : 0;
-            gy -= gy >= gh ? gh : 0;
-            const uint16_t* src = plane0 + size_t(gy) * gw + gx;
-            uint2* dst = reinterpret_cast<uint2*>(foot + (size_t(p) << mip.strideShift));
-#pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
-            {
-                if (layer < params.numLayers)
-                {
-                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
-                    dst[layer] = make_uint2(shared.latentTable[pixel & 0xFF], shared.latentTable[pixel >> 8]);
-                }
-            }
-        }
-    }
+// Whether the tables built for one tile of `mip` serve the tile at (tileX0, tileY0) too, and whether
+// tables built for that tile may be kept for later ones: the tile lies wholly inside the decoded rows
+// of a mip with invariant tables.
+__device__ __forceinline__ bool TileKeepsTables(const KernelMip& mip, int tileX0, int tileY0)
+{
+    return mip.invariant && tileX0 + kTileWidth <= mip.width && tileY0 + kTileHeight <= mip.rowEnd;
 }
 
 // Four quantised inputs of one latent layer from the four staged taps.
@@ -206,9 +255,8 @@ template <bool kFp8, typename Shared>
 __device__ __forceinline__ void GatherGrid(const KernelParams& params, const KernelMip& mip, const Shared& shared,
     int grid, int lane, int tileRow, uint32_t* words)
 {
-    const int4 col = shared.tables.colTap[grid][lane];
-    const int4 row = shared.tables.rowTap[grid][tileRow];
-    const int footW = shared.tables.footWidth[grid];
+    const int4 col = shared.tables.taps.colTap[grid][lane];
+    const int4 row = shared.tables.taps.rowTap[grid][tileRow];
     const float dx = __int_as_float(col.y), dxn = __int_as_float(col.z);
     const float dy = __int_as_float(row.y), dyn = __int_as_float(row.z);
     // src/FeatureGridDevice.h:46-49
@@ -216,9 +264,9 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
     const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
     const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
 
-    const int stride = 1 << mip.strideShift;
-    const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (size_t(row.x * footW + col.x) << mip.strideShift);
-    const uint8_t* tap10 = tap00 + (size_t(footW) << mip.strideShift);
+    const int stride = mip.strideBytes;
+    const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (col.x + row.x);
+    const uint8_t* tap10 = tap00 + shared.tables.taps.rowBytes[grid];
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
     {
@@ -234,13 +282,13 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
 }
 
 // Inputs 0..31 of one texel with the taps read straight from global memory.
-template <bool kFp8>
+template <bool kFp8, bool kReferenceDivision>
 __device__ __forceinline__ void SampleGridsDirect(const uint16_t* __restrict__ latents, int numLayers, const KernelMip& mip,
     int x, int y, const uint32_t* __restrict__ latentTable, uint32_t* words)
 {
-    // src/Inference.cu:52-53 with the division replaced by a precomputed reciprocal
-    const float u = __fmul_rn(__fadd_rn(float(x), 0.5f), mip.invWidth);
-    const float v = __fmul_rn(__fadd_rn(float(y), 0.5f), mip.invHeight);
+    // src/Inference.cu:52-53
+    const float u = TexelCoordinate<kReferenceDivision>(x, mip.width, mip.invWidth);
+    const float v = TexelCoordinate<kReferenceDivision>(y, mip.height, mip.invHeight);
     GridTaps taps;
     SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
     const uint16_t* hi = latents + mip.hiOffset;
@@ -258,7 +306,7 @@ __device__ __forceinline__ void SampleGridsDirect(const uint16_t* __restrict__ l
 
 // The 48 network inputs of one texel -> its 64-byte row of the A operand (K-major core matrices:
 // 16-byte chunk j of row r lives at j * 2048 + r * 16).
-template <bool kFp8, typename Shared, typename Context>
+template <bool kFp8, bool kReferenceDivision, typename Shared, typename Context>
 __device__ __forceinline__ void BuildInputs(const KernelParams& params, const KernelMip& mip, const Shared& shared,
     const Context& ctx, int lane, int tileRow)
 {
@@ -282,7 +330,7 @@ __device__ __forceinline__ void BuildInputs(const KernelParams& params, const Ke
     {
         // footprint too large to stage (strong minification): read the taps from global memory;
         // threads past the right / bottom edge compute a clamped texel and store nothing
-        SampleGridsDirect<kFp8>(params.latents, params.numLayers, mip, min(ctx.x, mip.width - 1), min(ctx.y, mip.rowEnd - 1),
+        SampleGridsDirect<kFp8, kReferenceDivision>(params.latents, params.numLayers, mip, min(ctx.x, mip.width - 1), min(ctx.y, mip.rowEnd - 1),
             shared.latentTable, words);
     }
 

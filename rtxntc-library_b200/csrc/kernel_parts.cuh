@@ -29,19 +29,30 @@ __device__ __forceinline__ void FenceBarrierInit()
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
+// One poll of a barrier phase.  The instruction may suspend the thread until the phase completes
+// or `kWaitHintNanoseconds` have passed, whichever comes first; without the hint the suspension is a
+// fraction of a microsecond and the polling loops of the waiting warps take a tenth of the kernel's
+// issue slots.
 __device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
 {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNanoseconds)
         : "memory");
     return done != 0;
+}
+
+// One arrival on a barrier (release semantics at CTA scope: what the thread wrote before is visible
+// to whoever observes the phase complete).
+__device__ __forceinline__ void MbarrierArrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // Announces `bytes` of asynchronous copies that will complete on the barrier, and arrives on it.
@@ -152,6 +163,60 @@ __device__ __forceinline__ __half2 AsHalf2(uint32_t v)
     return *reinterpret_cast<__half2*>(&v);
 }
 
+// Inf / NaN -> 0 in the channel pairs of one texel (src/Inference.cu:125-126, src/CudaUtils.h:30-35).
+// A binary16 value times zero is a zero unless the value is an infinity or a NaN, so one fused
+// multiply-add per pair into a common sum detects whether anything has to be done at all.
+__device__ __forceinline__ void ScrubSpecials(uint32_t (&bits)[8], int channelPairs)
+{
+    __half2 sum = __float2half2_rn(0.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < channelPairs)
+            sum = __hfma2(AsHalf2(bits[j]), __float2half2_rn(0.f), sum);
+    if (AsU32(sum) & 0x7FFF7FFFu)
+    {
+        // rare, so kept off the common path
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            if (j < channelPairs)
+            {
+                if ((bits[j] & 0x7C00u) == 0x7C00u) bits[j] &= 0xFFFF0000u;
+                if ((bits[j] & 0x7C000000u) == 0x7C000000u) bits[j] &= 0x0000FFFFu;
+            }
+        }
+    }
+}
+
+// Stores the channel pairs of one texel.  Pixel-interleaved layout: the pairs are consecutive words
+// and go out as 16-, 8- or 4-byte stores, whatever `vectorBytes` (the alignment every texel of the
+// mip has) allows; planar-pair layout: `stepWords` words apart, one word each.
+__device__ __forceinline__ void StoreTexel(uint32_t* out, uint32_t stepWords, int vectorBytes, const uint32_t (&bits)[8],
+    int channelPairs)
+{
+    if (vectorBytes == 16)
+    {
+#pragma unroll
+        for (int j = 0; j < 8; j += 4)
+            if (j < channelPairs)
+                *reinterpret_cast<uint4*>(out + j) = make_uint4(bits[j], bits[j + 1], bits[j + 2], bits[j + 3]);
+    }
+    else if (vectorBytes == 8)
+    {
+#pragma unroll
+        for (int j = 0; j < 8; j += 2)
+            if (j < channelPairs)
+                *reinterpret_cast<uint2*>(out + j) = make_uint2(bits[j], bits[j + 1]);
+    }
+    else
+    {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (j < channelPairs)
+                out[j * stepWords] = bits[j];
+    }
+}
+
 struct GridTaps
 {
     int o00, o01, o10, o11;
@@ -187,11 +252,32 @@ __device__ __forceinline__ float Frac(float t)
     return __fsub_rn(t, floorf(t));
 }
 
+// Normalised sample coordinate of a texel, (texel + 0.5) / extent (src/Inference.cu:52-53).  The
+// reference is built with --use_fast_math, so its division is the approximate one
+// (div.approx.ftz.f32: the operand times the hardware's reciprocal approximation, which for extents
+// that are not powers of two can differ from the correctly rounded reciprocal in the last bit, and
+// with it - rarely - a bilinear weight).  The reference-numerics kernels issue the same instruction;
+// the exact-accumulation kernels keep the multiplication by the correctly rounded reciprocal that
+// their CPU restatement uses.
+template <bool kReferenceDivision>
+__device__ __forceinline__ float TexelCoordinate(int texel, int extent, float invExtent)
+{
+    const float centre = __fadd_rn(float(texel), 0.5f);
+    if (kReferenceDivision)
+    {
+        float u;
+        asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(u) : "f"(centre), "f"(float(extent)));
+        return u;
+    }
+    return __fmul_rn(centre, invExtent);
+}
+
 // One axis of the bilinear footprint (src/FeatureGridDevice.h:35-45): base tap index (before
 // wrapping) and the fractional offset of a texel coordinate in a latent grid of `size` pixels.
-__device__ __forceinline__ void AxisTap(int texel, float invExtent, int size, int& base, float& frac)
+template <bool kReferenceDivision>
+__device__ __forceinline__ void AxisTap(int texel, int extent, float invExtent, int size, int& base, float& frac)
 {
-    const float u = __fmul_rn(__fadd_rn(float(texel), 0.5f), invExtent);
+    const float u = TexelCoordinate<kReferenceDivision>(texel, extent, invExtent);
     const float p = __fmaf_rn(u, float(size), -0.5f);
     const float b = floorf(p);
     base = int(b);

@@ -88,12 +88,26 @@ void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km, int footprin
     km.positionLod = m.positionLod;
     // Largest footprint a tile can have in each grid: the tap index of the last column (row) minus
     // that of the first is at most floor(31 (7) * grid / mip) + 1, plus the second tap.
-    km.strideShift = layers == 1 ? 3 : layers == 2 ? 4 : 5;
-    const long long hiCapacity = footprintHiBytes >> km.strideShift, loCapacity = footprintLoBytes >> km.strideShift;
+    km.strideBytes = layers == 1 ? 8 : layers <= 3 ? 24 : 40;
+    const long long hiCapacity = footprintHiBytes / km.strideBytes, loCapacity = footprintLoBytes / km.strideBytes;
     auto footprint = [](int grid, int mip, int span) { return (long long)((long long)span * grid / mip) + 3; };
     const long long hiPixels = footprint(m.hiWidth, m.width, kTileWidth - 1) * footprint(m.hiHeight, m.height, tileHeight - 1);
     const long long loPixels = footprint(m.loWidth, m.width, kTileWidth - 1) * footprint(m.loHeight, m.height, tileHeight - 1);
     km.staged = (hiPixels <= hiCapacity && loPixels <= loCapacity) ? 1 : 0;
+    // Tables that do not depend on the tile: with power-of-two sizes all the tap arithmetic is exact in
+    // binary32, and when a tile's width and height map to whole latent pixels of both grids (and to whole
+    // periods of the positional encoding) moving from tile to tile shifts every tap by an integer.
+    auto powerOfTwo = [](long long v) { return v > 0 && (v & (v - 1)) == 0; };
+    const float scaledColumns = m.positionScale * float(kTileWidth), scaledRows = m.positionScale * float(tileHeight);
+    int exponent = 0;
+    const bool scaleIsPowerOfTwo = m.positionScale > 0.f && frexpf(m.positionScale, &exponent) == 0.5f && exponent > -20 && exponent < 20;
+    km.invariant = powerOfTwo(m.width) && powerOfTwo(m.height) && powerOfTwo(m.hiWidth) && powerOfTwo(m.hiHeight) &&
+                   powerOfTwo(m.loWidth) && powerOfTwo(m.loHeight) && m.width >= kTileWidth && m.height >= tileHeight &&
+                   (m.rowBegin % tileHeight) == 0 &&
+                   ((long long)kTileWidth * m.hiWidth) % m.width == 0 && ((long long)kTileWidth * m.loWidth) % m.width == 0 &&
+                   ((long long)tileHeight * m.hiHeight) % m.height == 0 && ((long long)tileHeight * m.loHeight) % m.height == 0 &&
+                   scaledColumns == floorf(scaledColumns) && scaledRows == floorf(scaledRows) && scaleIsPowerOfTwo
+        ? 1 : 0;
     km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
     km.tilesXMagic = km.tilesX == 1 ? 0u : unsigned((0x100000000ull + km.tilesX - 1) / km.tilesX);
     km.firstTile = 0;
@@ -601,6 +615,13 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         else
             FillKernelMip(m, p->numFeatures / 4, km);
         km.firstTile = int(tiles);
+        km.storeBytes = 4;
+        if (!k.convert && p->outputLayout == NTCB_LAYOUT_INTERLEAVED)
+        {
+            const uintptr_t address = reinterpret_cast<uintptr_t>(p->out) + size_t(m.outOffset) * 2;
+            const size_t texelBytes = size_t(p->channels) * 2;
+            km.storeBytes = !(address & 15) && !(texelBytes & 15) ? 16 : !(address & 7) && !(texelBytes & 7) ? 8 : 4;
+        }
         const long long mipTiles = (long long)km.tilesX * ((m.rowEnd - m.rowBegin + tileHeight - 1) / tileHeight);
         if (mipTiles * km.tilesX >= 0x100000000ll)
         {
