@@ -52,22 +52,12 @@
 #define NTCB_ABLATE 0
 #endif
 
-// NTCB_DECOUPLE = 1: the two 128-row chains of a tile of DecodeKernelRefFp8 synchronise with each
-// other once per tile (before layer 0) instead of once per layer: each chain has its own issuing
-// thread, which waits on an mbarrier that the chain's 128 threads arrive on when their rows of the A
-// operand are written, so a chain whose matrix product has finished goes on without waiting for the
-// other one.
-#ifndef NTCB_DECOUPLE
-#define NTCB_DECOUPLE 0
-#endif
-
 namespace ntcb
 {
 namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
-constexpr bool kDecouple = NTCB_DECOUPLE != 0;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
 __device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
@@ -198,7 +188,6 @@ struct RefTileContext
     uint32_t* out;
     uint32_t outStepWords;
     int storeBytes; // widest store the texel may go out with (KernelMip::storeBytes)
-    uint32_t ready; // decoupled chains: shared address of this chain's operand-ready mbarrier
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -279,7 +268,7 @@ __device__ __forceinline__ void GatherGridRef(const KernelParams& params, const 
 
     const int stride = mip.strideBytes;
     const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (col.x + row.x);
-    const uint8_t* tap10 = tap00 + shared.tables.taps.rowBytes[grid];
+    const uint8_t* tap10 = tap00 + row.w;
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
     {
@@ -823,8 +812,6 @@ struct __align__(128) RefFp8SharedStorage
     TileTables tables;
     uint64_t barrier[kRefChains]; // MMA completion, per chain
     uint64_t loadBarrier;         // arrival of the network image
-    uint64_t ready[kRefChains];   // decoupled chains: the chain's 128 rows of the A operand are written
-    uint64_t prepared;            // decoupled chains: all 256 threads have finished preparing the next tile
     uint32_t tmemBase;
 };
 
@@ -884,60 +871,26 @@ __device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int 
     UmmaCommit(ctx.barrierBase + half * 8);
 }
 
-// Bits of the per-thread word that tracks the parity of the barriers a thread waits on.
-constexpr uint32_t kPhaseMma = 1, kPhaseReady = 2, kPhasePrepared = 4;
-
 // First half of a layer: hands the A operand written before this call to the tensor core.  Returns
-// nonzero (uniformly over the CTA) when the CTA agreed that some thread gave up on a wait.
+// nonzero (uniformly over the CTA) when some thread gave up on a wait.
+// (Tried and dropped: letting the two chains run apart between tiles - each chain with its own
+// issuing thread waiting on an mbarrier its 128 threads arrive on - was 4 % slower than this
+// CTA-wide barrier with one issuing thread.)
 template <int kLayer>
-__device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int& failed, uint32_t& phases, uint32_t* status)
+__device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int failed)
 {
-    // Makes the A operand visible to the tensor core (async proxy) and orders this thread's reads of
-    // the previous layer's accumulators before they are overwritten.
+    // Makes the A operand visible to the tensor core (async proxy), orders this thread's reads of the
+    // previous layer's accumulators before they are overwritten, and agrees on giving up.
     FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
-    if (!kDecouple || kLayer == 0)
+    if (__syncthreads_or(failed))
+        return 1;
+    if (ctx.tid == 0 && !(kAblate & 16))
     {
-        // the whole CTA meets: also the point where it agrees on giving up
-        if (__syncthreads_or(failed))
-            return 1;
-        if (kAblate & 16)
-            return 0;
-        if (kDecouple)
-        {
-            if ((ctx.tid & 127) == 0)
-            {
-                TcgenFenceAfterSync();
-                IssueChainRefFp8<kLayer>(ctx, ctx.tid >> 7);
-            }
-        }
-        else if (ctx.tid == 0)
-        {
-            TcgenFenceAfterSync();
-            // (one issuing thread for both chains measured faster than one per chain with this barrier)
+        TcgenFenceAfterSync();
 #pragma unroll
-            for (int half = 0; half < kRefChains; ++half)
-                IssueChainRefFp8<kLayer>(ctx, half);
-        }
-    }
-    else
-    {
-        // the chain's 128 threads arrive; its first thread waits for all of them and issues
-        MbarrierArrive(ctx.ready);
-        if ((ctx.tid & 127) == 0)
-        {
-            if (MbarrierWaitBounded(ctx.ready, (phases & kPhaseReady) ? 1u : 0u))
-            {
-                TcgenFenceAfterSync();
-                IssueChainRefFp8<kLayer>(ctx, ctx.tid >> 7);
-            }
-            else
-            {
-                failed = 1;
-                ReportTimeout(status, uint32_t(ctx.tile), uint32_t(16 + kLayer));
-            }
-        }
-        phases ^= kPhaseReady;
+        for (int half = 0; half < kRefChains; ++half)
+            IssueChainRefFp8<kLayer>(ctx, half);
     }
     return 0;
 }
@@ -958,12 +911,12 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
-    if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phases & kPhaseMma))
+    if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phases))
     {
         failed = 1;
         ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(kLayer));
     }
-    phases ^= kPhaseMma;
+    phases ^= 1;
     TcgenFenceAfterSync();
 
     if ((kAblate & 4) && kLayer < 3)
@@ -1096,7 +1049,7 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
 template <int kLayer, bool kConvert, typename Params>
 __device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phases, int& failed)
 {
-    if (IssueLayerRefFp8<kLayer>(ctx, failed, phases, params.status))
+    if (IssueLayerRefFp8<kLayer>(ctx, failed))
         return 1;
     ConsumeLayerRefFp8<kLayer, kConvert>(params, ctx, phases, failed);
     return 0;
@@ -1117,11 +1070,7 @@ __device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const
     if (tid == 0)
     {
         for (int chain = 0; chain < kRefChains; ++chain)
-        {
             MbarrierInit(SharedAddress(&shared.barrier[chain]), 1);
-            MbarrierInit(SharedAddress(&shared.ready[chain]), 128);
-        }
-        MbarrierInit(SharedAddress(&shared.prepared), kThreadsPerCta);
         MbarrierInit(loadBarrier, 1);
         FenceBarrierInit();
         MbarrierArriveExpectTx(loadBarrier, kRefNetworkBytes);
@@ -1150,7 +1099,7 @@ __device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, c
     if (aborted && tid == 0)
     {
         for (int chain = 0; chain < kRefChains; ++chain)
-            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, (phases & kPhaseMma) ^ 1);
+            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phases ^ 1);
         (void)MbarrierWaitBounded(SharedAddress(&shared.loadBarrier), 0);
     }
     __syncthreads();
@@ -1179,7 +1128,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
     ctx.tmemLane = ctx.tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
     ctx.barrierBase = SharedAddress(&shared.barrier[0]);
     ctx.barrier = ctx.barrierBase + half * 8;
-    ctx.ready = SharedAddress(&shared.ready[half]);
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
@@ -1210,8 +1158,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         place = locate(tile, 0);
         PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
         tablesMip = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0) ? place.mipIndex : -1;
-        if (kDecouple)
-            MbarrierArrive(SharedAddress(&shared.prepared));
         __syncthreads();
     }
     while (tile < params.totalTiles)
@@ -1220,17 +1166,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         ctx.tile = tile;
         ctx.x = place.tileX0 + lane;
         ctx.y = place.tileY0 + warp;
-        if (kDecouple)
-        {
-            // the tables and footprints of this tile, written by all 256 threads while the previous tile's
-            // first layer ran, are complete (the chains no longer meet between that point and this one)
-            if (!MbarrierWaitBounded(SharedAddress(&shared.prepared), (phase & kPhasePrepared) ? 1u : 0u))
-            {
-                failed = 1;
-                ReportTimeout(params.status, uint32_t(tile), 32u);
-            }
-            phase ^= kPhasePrepared;
-        }
         // the e4m3 input stage is the one of the exact-accumulation kernel (64-byte rows of codes)
         if (kAblate & 2)
         {
@@ -1242,7 +1177,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         else
             BuildInputs<true, true>(params, mip, shared, ctx, lane, warp);
 
-        aborted = IssueLayerRefFp8<0>(ctx, failed, phase, params.status);
+        aborted = IssueLayerRefFp8<0>(ctx, failed);
         if (aborted)
             break;
         const int nextTile = tile + int(gridDim.x);
@@ -1255,8 +1190,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
                 PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, keepsTables && place.mipIndex == tablesMip);
             tablesMip = keepsTables ? place.mipIndex : -1;
         }
-        if (kDecouple)
-            MbarrierArrive(SharedAddress(&shared.prepared));
         ConsumeLayerRefFp8<0, false>(params, ctx, phase, failed);
 
         aborted = RunLayerRefFp8<1, false>(params, ctx, phase, failed);
@@ -1316,7 +1249,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
     ctx.tmemLane = ctx.tmemBase + half * kTmemColumnsPerHalf + (uint32_t((warp & 3) * 32) << 16);
     ctx.barrierBase = SharedAddress(&shared.barrier[0]);
     ctx.barrier = ctx.barrierBase + half * 8;
-    ctx.ready = SharedAddress(&shared.ready[half]);
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);

@@ -83,12 +83,15 @@ struct __align__(16) TapTables
 {
     // per grid (0 = high-res, 1 = low-res) and tile column: byte offset of the left tap inside a footprint row, dx, 1 - dx
     int4 colTap[2][kTileWidth];
-    // per grid and tile row: byte offset of the upper tap's footprint row, dy, 1 - dy
+    // per grid and tile row: byte offset of the upper tap's footprint row, dy, 1 - dy, bytes per footprint row
     int4 rowTap[2][kTileHeight];
-    int footWidth[2], footHeight[2]; // footprint size in latent pixels, per grid
-    int rowBytes[2];                 // bytes per footprint row, per grid
-    int pad[2];
+    // per grid: footprint width and height in latent pixels, bytes per footprint row, and the multiplier
+    // that divides a pixel index by the width (p / width == (p * magic) >> 20 for p < 2048)
+    int4 footprint[2];
 };
+
+// The warps that stage the footprints: one per grid, in different chains and scheduler partitions.
+constexpr int kStagingWarpHi = 0, kStagingWarpLo = 5;
 
 // Tap tables plus the positional encoding as operand bytes (kernels whose A operand holds 8-bit codes).
 struct __align__(16) TileTables
@@ -114,20 +117,27 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
     uint8_t* footprintHi, uint8_t* footprintLo, const uint32_t* latentTable, int tileX0, int tileY0, int lane, int warp,
     bool tablesValid)
 {
-    const int grid = warp & 1;
+    const bool stagesHi = warp == kStagingWarpHi, stagesLo = warp == kStagingWarpLo;
+    if (tablesValid && !(stagesHi || stagesLo))
+        return; // nothing to build; two warps stage the footprints
+    // while the tables are built, even warps work on the high-res grid and odd warps on the low-res one
+    const int grid = tablesValid ? (stagesLo ? 1 : 0) : (warp & 1);
     const int gw = grid ? mip.loWidth : mip.hiWidth;
     const int gh = grid ? mip.loHeight : mip.hiHeight;
     const int stride = mip.strideBytes;
 
     int fx0, fy0, footW, footH;
+    uint32_t magic;
     if (tablesValid)
     {
         // only the footprint's origin depends on the tile: the taps of its first column and row
         float unused;
         AxisTap<kReferenceDivision>(tileX0, mip.width, mip.invWidth, gw, fx0, unused);
         AxisTap<kReferenceDivision>(tileY0, mip.height, mip.invHeight, gh, fy0, unused);
-        footW = taps.footWidth[grid];
-        footH = taps.footHeight[grid];
+        const int4 footprint = taps.footprint[grid];
+        footW = footprint.x;
+        footH = footprint.y;
+        magic = uint32_t(footprint.w);
     }
     else
     {
@@ -139,31 +149,29 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
         fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
         footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
         footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
+        // the IEEE quotient of 2^20 / footW floors exactly
+        magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
         if (warp < 2)
         {
             taps.colTap[grid][lane] = make_int4((xb - fx0) * stride, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
             if (lane < kTileHeight)
                 taps.rowTap[grid][lane] =
-                    make_int4((yb - fy0) * footW * stride, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), 0);
+                    make_int4((yb - fy0) * footW * stride, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), footW * stride);
             if (lane == 0)
-            {
-                taps.footWidth[grid] = footW;
-                taps.footHeight[grid] = footH;
-                taps.rowBytes[grid] = footW * stride;
-            }
+                taps.footprint[grid] = make_int4(footW, footH, footW * stride, int(magic));
         }
+        if (!(stagesHi || stagesLo) || grid != (stagesLo ? 1 : 0))
+            return;
     }
 
     if (mip.staged)
     {
-        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
+        // footprint pixel p = fy * footW + fx, handed out over the lanes of this warp
         const int count = footW * footH;
-        // p / footW == (p * magic) >> 20 for p < 2048; the IEEE quotient of 2^20 / footW floors exactly
-        const uint32_t magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
         uint8_t* foot = grid ? footprintLo : footprintHi;
-        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
+        for (int p = lane; p < count; p += 32)
         {
             const int fy = int((uint32_t(p) * magic) >> 20);
             const int fx = p - fy * footW;
@@ -266,7 +274,7 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
 
     const int stride = mip.strideBytes;
     const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (col.x + row.x);
-    const uint8_t* tap10 = tap00 + shared.tables.taps.rowBytes[grid];
+    const uint8_t* tap10 = tap00 + row.w;
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
     {

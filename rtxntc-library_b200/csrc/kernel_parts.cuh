@@ -48,13 +48,6 @@ __device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
     return done != 0;
 }
 
-// One arrival on a barrier (release semantics at CTA scope: what the thread wrote before is visible
-// to whoever observes the phase complete).
-__device__ __forceinline__ void MbarrierArrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
 // Announces `bytes` of asynchronous copies that will complete on the barrier, and arrives on it.
 __device__ __forceinline__ void MbarrierArriveExpectTx(uint32_t bar, uint32_t bytes)
 {
