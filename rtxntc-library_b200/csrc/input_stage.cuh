@@ -90,9 +90,6 @@ struct __align__(16) TapTables
     int4 footprint[2];
 };
 
-// The warps that stage the footprints: one per grid, in different chains and scheduler partitions.
-constexpr int kStagingWarpHi = 0, kStagingWarpLo = 5;
-
 // Tap tables plus the positional encoding as operand bytes (kernels whose A operand holds 8-bit codes).
 struct __align__(16) TileTables
 {
@@ -104,9 +101,32 @@ struct __align__(16) TileTables
     uint32_t pad[3];
 };
 
-// Builds the tile's tap tables and stages the latent footprint of both grids in shared memory
+// A footprint pixel whose latents a thread has requested from global memory but not yet unpacked:
+// the request goes out while the tensor core works on the current tile's first layer, the data is
+// used after the wait for that layer, so the round trip to memory is off the critical path.
+struct PendingFootprint
+{
+    uint32_t pixel[4]; // one 16-bit latent pixel per layer
+    int offset;        // byte offset of the pixel in its grid's footprint; -1: nothing pending
+    int grid;
+};
+
+// Unpacks one latent pixel (four 4-bit features per layer) into its footprint slot.
+__device__ __forceinline__ void UnpackFootprintPixel(const uint32_t (&pixel)[4], int numLayers, uint8_t* slot,
+    const uint32_t* latentTable)
+{
+    uint2* dst = reinterpret_cast<uint2*>(slot);
+#pragma unroll
+    for (int layer = 0; layer < 4; ++layer)
+        if (layer < numLayers)
+            dst[layer] = make_uint2(latentTable[pixel[layer] & 0xFF], latentTable[pixel[layer] >> 8]);
+}
+
+// Builds the tile's tap tables and starts staging the latent footprint of both grids in shared memory
 // (nibbles unpacked to binary16 once per latent pixel instead of once per texel and tap).
-// Even warps work on the high-res grid, odd warps on the low-res grid.
+// Even warps work on the high-res grid, odd warps on the low-res grid; the 128 threads of a grid take
+// one footprint pixel each and leave it in `pending` (FinishFootprint completes it); what a larger
+// footprint has beyond 128 pixels is staged here, synchronously.
 //
 // `tablesValid`: the tables already hold this tile's values.  In a mip whose sizes and grid sizes
 // are powers of two (KernelMip::invariant) every tile that lies wholly inside the mip has the same
@@ -115,13 +135,9 @@ struct __align__(16) TileTables
 template <bool kReferenceDivision>
 __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const KernelMip& mip, TapTables& taps,
     uint8_t* footprintHi, uint8_t* footprintLo, const uint32_t* latentTable, int tileX0, int tileY0, int lane, int warp,
-    bool tablesValid)
+    bool tablesValid, PendingFootprint& pending)
 {
-    const bool stagesHi = warp == kStagingWarpHi, stagesLo = warp == kStagingWarpLo;
-    if (tablesValid && !(stagesHi || stagesLo))
-        return; // nothing to build; two warps stage the footprints
-    // while the tables are built, even warps work on the high-res grid and odd warps on the low-res one
-    const int grid = tablesValid ? (stagesLo ? 1 : 0) : (warp & 1);
+    const int grid = warp & 1;
     const int gw = grid ? mip.loWidth : mip.hiWidth;
     const int gh = grid ? mip.loHeight : mip.hiHeight;
     const int stride = mip.strideBytes;
@@ -149,7 +165,7 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
         fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
         footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
         footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
-        // the IEEE quotient of 2^20 / footW floors exactly
+        // p / footW == (p * magic) >> 20 for p < 2048: the IEEE quotient of 2^20 / footW floors exactly
         magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
         if (warp < 2)
         {
@@ -160,18 +176,19 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
             if (lane == 0)
                 taps.footprint[grid] = make_int4(footW, footH, footW * stride, int(magic));
         }
-        if (!(stagesHi || stagesLo) || grid != (stagesLo ? 1 : 0))
-            return;
     }
 
+    pending.offset = -1;
+    pending.grid = grid;
     if (mip.staged)
     {
-        // footprint pixel p = fy * footW + fx, handed out over the lanes of this warp
+        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
         const int count = footW * footH;
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
         uint8_t* foot = grid ? footprintLo : footprintHi;
-        for (int p = lane; p < count; p += 32)
+        bool first = true;
+        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
         {
             const int fy = int((uint32_t(p) * magic) >> 20);
             const int fx = p - fy * footW;
@@ -182,24 +199,37 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
             gy += gy < 0 ? gh : 0;
             gy -= gy >= gh ? gh : 0;
             const uint16_t* src = plane0 + size_t(gy) * gw + gx;
-            uint2* dst = reinterpret_cast<uint2*>(foot + p * stride);
+            uint32_t pixel[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int layer = 0; layer < 4; ++layer)
-            {
                 if (layer < params.numLayers)
-                {
-                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
-                    dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
-                }
+                    pixel[layer] = __ldg(src + size_t(layer) * planePixels);
+            if (first)
+            {
+#pragma unroll
+                for (int layer = 0; layer < 4; ++layer)
+                    pending.pixel[layer] = pixel[layer];
+                pending.offset = p * stride;
+                first = false;
             }
+            else
+                UnpackFootprintPixel(pixel, params.numLayers, foot + p * stride, latentTable);
         }
     }
+}
+
+// Completes the footprint pixel PrepareTaps left pending.
+__device__ __forceinline__ void FinishFootprint(const KernelParams& params, const PendingFootprint& pending,
+    uint8_t* footprintHi, uint8_t* footprintLo, const uint32_t* latentTable)
+{
+    if (pending.offset >= 0)
+        UnpackFootprintPixel(pending.pixel, params.numLayers, (pending.grid ? footprintLo : footprintHi) + pending.offset, latentTable);
 }
 
 // The tile's tables (taps and positional encoding as operand bytes) and its staged footprints.
 template <bool kFp8, bool kReferenceDivision, typename Shared>
 __device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, Shared& shared,
-    int tileX0, int tileY0, int lane, int warp, bool tablesValid)
+    int tileX0, int tileY0, int lane, int warp, bool tablesValid, PendingFootprint& pending)
 {
     if (!tablesValid && warp >= 2 && warp < 4)
     {
@@ -227,7 +257,17 @@ __device__ __forceinline__ void PrepareTile(const KernelParams& params, const Ke
                                                    QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
     }
     PrepareTaps<kReferenceDivision>(params, mip, shared.tables.taps, shared.footprintHi, shared.footprintLo, shared.latentTable,
-        tileX0, tileY0, lane, warp, tablesValid);
+        tileX0, tileY0, lane, warp, tablesValid, pending);
+}
+
+// The same with the footprint completed at once (nothing left pending).
+template <bool kFp8, bool kReferenceDivision, typename Shared>
+__device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, Shared& shared,
+    int tileX0, int tileY0, int lane, int warp, bool tablesValid)
+{
+    PendingFootprint pending;
+    PrepareTile<kFp8, kReferenceDivision>(params, mip, shared, tileX0, tileY0, lane, warp, tablesValid, pending);
+    FinishFootprint(params, pending, shared.footprintHi, shared.footprintLo, shared.latentTable);
 }
 
 // Whether the tables built for one tile of `mip` serve the tile at (tileX0, tileY0) too, and whether
