@@ -444,6 +444,67 @@ int ntcb_block_compress(const NtcbBlockCompressParams* params, void* stream);
 int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, int firstChannel, int numChannels, int format,
     float alphaThreshold, void* deviceBlocks, size_t rowPitch);
 
+/* ---- Several GPUs of one machine ------------------------------------------------------------ */
+
+/* One texture set of a batch: its container, and the host image that receives the decoded chain. */
+typedef struct NtcbBatchItem
+{
+    const void* container;   /* NTC container in host memory */
+    size_t containerBytes;
+    void* hostTexels;        /* host memory (pinned memory copies fastest): every mip one after the other as
+                                fp16 [y][x][c] - what ReadChannels(FLOAT16) of each mip hands back; the devices
+                                write disjoint rows of it: the final host gather */
+    size_t hostTexelsBytes;  /* at least totalTexels x channels x 2 */
+    int32_t useInt8Weights;
+    int32_t status;          /* out: NTCB_OK, or the error that kept one of this item's units from being decoded */
+} NtcbBatchItem;
+
+/* One unit of work: rows [rowBegin[m], rowEnd[m]) of each mip m of one item. */
+typedef struct NtcbBatchUnit
+{
+    int32_t item;
+    int32_t device;          /* out: the device of the last attempt (-1: never tried) */
+    int32_t attempts;        /* out */
+    int32_t status;          /* out: result of the last attempt */
+    int32_t rowBegin[NTCB_MAX_MIPS], rowEnd[NTCB_MAX_MIPS];
+    uint64_t texels;
+} NtcbBatchUnit;
+
+typedef struct NtcbBatchOptions
+{
+    int32_t numerics;         /* NtcbNumerics */
+    int32_t maxAttempts;      /* tries per unit, each on another device; 0 = 3 */
+    int32_t unitsPerDevice;   /* the job is cut into about devices x this many units; 0 = 4 */
+    int32_t workersPerDevice; /* host threads (each with its own context) per device, so that one's copy to the
+                                 host overlaps the other's decode; 0 = 2 */
+    /* Test hook: when set, it is called in place of the GPU work of a unit (no CUDA call is made at
+       all) and its return value is the unit's result - a stand-in for a device that fails, or is slow. */
+    int (*worker)(void* user, int device, const NtcbBatchUnit* unit);
+    void* workerUser;
+} NtcbBatchOptions;
+
+/* Cuts a job into work units, largest first (host only).  An item of at most ~1.5 times the target
+   size (all texels / (numDevices x unitsPerDevice)) becomes two units - mip 0, and the other mips;
+   a larger one becomes bands of tile rows (multiples of 8 rows, at least 64) of its tall mips, the
+   short mips going whole to the lightest band.  `units` may be NULL to ask for the count. */
+int ntcb_plan_batch(const NtcbTextureSetDesc* descs, int numItems, int numDevices, int unitsPerDevice, NtcbBatchUnit* units,
+    int maxUnits, int* outNumUnits);
+
+/* Decodes a batch of texture sets (or one large set) on several devices and gathers the texels in
+   host memory.  No counterpart in the reference, which drives one device per context
+   (include/libntc/ntc.h:1289-1290) and leaves this layer to the client: the units of ntcb_plan_batch
+   are handed out, largest first, to one or more host threads per listed device, each with its own
+   context; a thread decodes a unit's rows (ntcb_texture_set_decompress_rows on its copy of the set)
+   and copies them to their place in the item's host image.  The devices share nothing: no peer
+   access, no collective.  A device may be listed more than once.
+   A unit that fails on a device (context creation, a CUDA error, NTCB_ERR_DEVICE_TIMEOUT) is tried
+   again on another one, up to maxAttempts; a device that fails two units in a row takes no more
+   work.  Returns NTCB_OK when every unit was decoded; otherwise an error, with the items' `status`
+   and - when `outUnits` is given - the per-unit record telling what failed where.  Blocks until
+   all work is done. */
+int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, int numDevices, const NtcbBatchOptions* options,
+    NtcbBatchUnit* outUnits, int maxUnits, int* outNumUnits);
+
 /* Size of the staging area built into the library for ntcb_read_channels_to_host_noalloc. */
 #define NTCB_NOALLOC_STAGING_BYTES (4u << 20)
 

@@ -259,7 +259,36 @@ def make_options(use_int8: bool, numerics: int, threads: int = 0, **ref_switches
 # the same public API, the same harness, this repository's decoder behind ITextureSet::Decompress.
 REF_NTCB_LIB = os.path.join(HERE, "_ref", "libntc_ref_ntcb.so")
 
+# The reference's BC1 - BC5 compute shaders compiled for the CPU (build_ref.sh; no graphics API).
+REF_BC_LIB = os.path.join(HERE, "_ref", "libntc_ref_bc.so")
+
 _ref = {}
+_ref_bc = None
+
+
+def reference_bc_available() -> bool:
+    return os.path.exists(REF_BC_LIB)
+
+
+def reference_block_compress(block_format: int, rgba: np.ndarray, alpha_threshold: float = 1.0 / 255.0, src_left: int = 0,
+                             src_top: int = 0, width_in_blocks: Optional[int] = None,
+                             height_in_blocks: Optional[int] = None) -> np.ndarray:
+    """Runs the reference's own CompressBC<n>.hlsl (n = block_format, 1..5) on the CPU over an RGBA binary32
+    image [h][w][4] - what the shader's input texture holds - and returns uint8 [blocks_y][blocks_x][8 or 16]."""
+    global _ref_bc
+    if _ref_bc is None:
+        _ref_bc = ctypes.CDLL(REF_BC_LIB)
+    rgba = np.ascontiguousarray(rgba, dtype=np.float32)
+    h, w, four = rgba.shape
+    assert four == 4
+    bw = (w - src_left + 3) // 4 if width_in_blocks is None else width_in_blocks
+    bh = (h - src_top + 3) // 4 if height_in_blocks is None else height_in_blocks
+    out = np.zeros((bh, bw, 8 if block_format in (1, 4) else 16), dtype=np.uint8)
+    function = getattr(_ref_bc, "ntcref_block_compress_bc%d" % block_format)
+    function.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_float, ctypes.c_void_p]
+    function(rgba.ctypes.data, w, h, src_left, src_top, bw, bh, alpha_threshold, out.ctypes.data)
+    return out
+
 
 
 def reference_available() -> bool:

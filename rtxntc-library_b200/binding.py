@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -126,6 +126,27 @@ CHANNEL_FORMAT_UNORM8, CHANNEL_FORMAT_UNORM16, CHANNEL_FORMAT_FLOAT16, CHANNEL_F
 COLOR_SPACE_LINEAR, COLOR_SPACE_SRGB, COLOR_SPACE_HLG = 0, 1, 2
 CHANNEL_FORMAT_DTYPES = {CHANNEL_FORMAT_UNORM8: np.uint8, CHANNEL_FORMAT_UNORM16: np.uint16, CHANNEL_FORMAT_FLOAT16: np.float16,
                          CHANNEL_FORMAT_FLOAT32: np.float32, CHANNEL_FORMAT_UINT32: np.uint32}
+
+
+class BatchItem(ctypes.Structure):
+    """NtcbBatchItem: one texture set of a multi-device batch."""
+    _fields_ = [("container", ctypes.c_void_p), ("containerBytes", ctypes.c_size_t), ("hostTexels", ctypes.c_void_p),
+                ("hostTexelsBytes", ctypes.c_size_t), ("useInt8Weights", ctypes.c_int32), ("status", ctypes.c_int32)]
+
+
+class BatchUnit(ctypes.Structure):
+    """NtcbBatchUnit: rows [rowBegin[m], rowEnd[m]) of every mip m of one item."""
+    _fields_ = [("item", ctypes.c_int32), ("device", ctypes.c_int32), ("attempts", ctypes.c_int32), ("status", ctypes.c_int32),
+                ("rowBegin", ctypes.c_int32 * MAX_MIPS), ("rowEnd", ctypes.c_int32 * MAX_MIPS), ("texels", ctypes.c_uint64)]
+
+
+BATCH_WORKER = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(BatchUnit))
+
+
+class BatchOptions(ctypes.Structure):
+    """NtcbBatchOptions."""
+    _fields_ = [("numerics", ctypes.c_int32), ("maxAttempts", ctypes.c_int32), ("unitsPerDevice", ctypes.c_int32),
+                ("workersPerDevice", ctypes.c_int32), ("worker", BATCH_WORKER), ("workerUser", ctypes.c_void_p)]
 
 
 class NtcbError(RuntimeError):
@@ -664,3 +685,54 @@ class TextureSet:
         if self.handle:
             lib().ntcb_texture_set_destroy(self.handle)
             self.handle = ctypes.c_void_p()
+
+
+# ---------------------------------------------------------------------------------------------
+# Several GPUs of one machine
+# ---------------------------------------------------------------------------------------------
+
+def plan_batch(shapes: Sequence[Tuple[int, int, int]], num_devices: int, units_per_device: int = 0) -> List[BatchUnit]:
+    """ntcb_plan_batch for items given as (width, height, mips): the work units, largest first."""
+    descs = (TextureSetDesc * len(shapes))()
+    for desc, (width, height, mips) in zip(descs, shapes):
+        desc.width, desc.height, desc.mips = width, height, mips
+        desc.totalTexels = sum(max(width >> m, 1) * max(height >> m, 1) for m in range(mips))
+    count = ctypes.c_int()
+    check(lib().ntcb_plan_batch(descs, len(shapes), num_devices, units_per_device, None, 0, ctypes.byref(count)))
+    units = (BatchUnit * count.value)()
+    check(lib().ntcb_plan_batch(descs, len(shapes), num_devices, units_per_device, units, count.value, ctypes.byref(count)))
+    return list(units)
+
+
+def decode_batch(containers: Sequence[bytes], devices: Sequence[int], use_int8, host_images=None, numerics: int = NUMERICS_REFERENCE,
+                 worker=None, max_attempts: int = 0, units_per_device: int = 0, workers_per_device: int = 0):
+    """ntcb_decode_batch: decodes the sets on the listed devices and gathers every set's mip chain in
+    `host_images[i]` (a writable buffer object exposing its address as .data_ptr() or .ctypes.data;
+    None with a fake `worker`).  `use_int8`: one flag, or one per set.  `worker(device, unit) -> status`
+    replaces the GPU work (tests).  Returns (status code, item statuses, units as BatchUnit list)."""
+    items = (BatchItem * len(containers))()
+    keep = []
+    flags = [use_int8] * len(containers) if isinstance(use_int8, (bool, int)) else list(use_int8)
+    for index, (item, container) in enumerate(zip(items, containers)):
+        buffer = ctypes.create_string_buffer(container, len(container))
+        keep.append(buffer)
+        item.container = ctypes.cast(buffer, ctypes.c_void_p)
+        item.containerBytes = len(container)
+        item.useInt8Weights = 1 if flags[index] else 0
+        if host_images is not None:
+            image = host_images[index]
+            item.hostTexels = image.data_ptr() if hasattr(image, "data_ptr") else image.ctypes.data
+            item.hostTexelsBytes = image.numel() * image.element_size() if hasattr(image, "numel") else image.nbytes
+    options = BatchOptions()
+    options.numerics, options.maxAttempts = numerics, max_attempts
+    options.unitsPerDevice, options.workersPerDevice = units_per_device, workers_per_device
+    if worker is not None:
+        callback = BATCH_WORKER(lambda user, device, unit: int(worker(device, unit.contents)))
+        keep.append(callback)
+        options.worker = callback
+    device_list = (ctypes.c_int * len(devices))(*devices)
+    units = (BatchUnit * 8192)()
+    count = ctypes.c_int()
+    code = lib().ntcb_decode_batch(items, len(containers), device_list, len(devices), ctypes.byref(options), units, 8192,
+                                   ctypes.byref(count))
+    return code, [item.status for item in items], list(units)[:count.value]

@@ -52,12 +52,6 @@
 #define NTCB_ABLATE 0
 #endif
 
-// Experiment: NTCB_SKEW = n delays the start of the CTAs that share an SM by multiples of n
-// nanoseconds, so that they do not all wait for the tensor core at the same moment.
-#ifndef NTCB_SKEW
-#define NTCB_SKEW 0
-#endif
-
 namespace ntcb
 {
 namespace
@@ -233,10 +227,8 @@ __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const
             shared.tables.zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
         }
     }
-    PendingFootprint pending;
     PrepareTaps<true>(params, mip, shared.tables.taps, shared.footprintHi, shared.footprintLo, shared.latentTable, tileX0, tileY0,
-        lane, warp, tablesValid, pending);
-    FinishFootprint(params, pending, shared.footprintHi, shared.footprintLo, shared.latentTable);
+        lane, warp, tablesValid);
 }
 
 // Four inputs of one latent layer from the four taps, as two binary16 pairs.
@@ -914,28 +906,19 @@ __device__ __forceinline__ uint32_t ActivateToE4m3(uint32_t bits)
     return uint32_t(__nv_cvt_halfraw2_to_fp8x2(static_cast<__half2_raw>(y), __NV_SATFINITE, __NV_E4M3));
 }
 
-// Waits for the matrix products of a layer of this thread's chain.
-template <typename Params>
-__device__ __forceinline__ void WaitLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed, int layer)
-{
-    if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phase))
-    {
-        failed = 1;
-        ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(layer));
-    }
-    phase ^= 1;
-    TcgenFenceAfterSync();
-}
-
-// Second half of a layer: waits for the MMA (unless the caller has: kWait = false), then applies the
-// activation and writes the next layer's A operand (layers 0-2) or stores the texel (layer 3).
-template <int kLayer, bool kConvert, bool kWait = true, typename Params>
-__device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phases, int& failed)
+template <int kLayer, bool kConvert, typename Params>
+__device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
-    if (kWait)
-        WaitLayerRefFp8(params, ctx, phases, failed, kLayer);
+    // one warp of the chain polls for the chain's matrix products, the other three wait for it in a named barrier
+    if (!(kAblate & 16) && !MbarrierWaitGroup(ctx.barrier, phase, (ctx.tid & 96) == 0, 1 + (ctx.tid >> 7), 128))
+    {
+        failed = 1;
+        ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(kLayer));
+    }
+    phase ^= 1;
+    TcgenFenceAfterSync();
 
     if ((kAblate & 4) && kLayer < 3)
     {
@@ -1065,11 +1048,11 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
 }
 
 template <int kLayer, bool kConvert, typename Params>
-__device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phases, int& failed)
+__device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
 {
     if (IssueLayerRefFp8<kLayer>(ctx, failed))
         return 1;
-    ConsumeLayerRefFp8<kLayer, kConvert>(params, ctx, phases, failed);
+    ConsumeLayerRefFp8<kLayer, kConvert>(params, ctx, phase, failed);
     return 0;
 }
 
@@ -1109,7 +1092,7 @@ __device__ __forceinline__ int SetupCtaRefFp8(RefFp8SharedStorage& shared, const
     return failed;
 }
 
-__device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, const RefTileContext& ctx, uint32_t phases, int failed,
+__device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, const RefTileContext& ctx, uint32_t phase, int failed,
     int tid, int warp)
 {
     TcgenFenceBeforeSync();
@@ -1117,7 +1100,7 @@ __device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, c
     if (aborted && tid == 0)
     {
         for (int chain = 0; chain < kRefChains; ++chain)
-            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phases ^ 1);
+            (void)MbarrierWaitBounded(ctx.barrierBase + chain * 8, phase ^ 1);
         (void)MbarrierWaitBounded(SharedAddress(&shared.loadBarrier), 0);
     }
     __syncthreads();
@@ -1139,8 +1122,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
     int failed = SetupCtaRefFp8(shared, params.network, params.status, params.loadWaitPolls, tid, warp);
     uint32_t phase = 0;
     int aborted = 0;
-    if (NTCB_SKEW)
-        __nanosleep((blockIdx.x / 148u) * unsigned(NTCB_SKEW));
 
     RefTileContext ctx;
     ctx.tid = tid;
@@ -1201,8 +1182,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         if (aborted)
             break;
         const int nextTile = tile + int(gridDim.x);
-        PendingFootprint pending;
-        pending.offset = -1;
         if (nextTile < params.totalTiles)
         {
             place = locate(nextTile, place.mipIndex);
@@ -1210,13 +1189,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
             const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
             if (!(kAblate & 1))
                 PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp,
-                    keepsTables && place.mipIndex == tablesMip, pending);
+                    keepsTables && place.mipIndex == tablesMip);
             tablesMip = keepsTables ? place.mipIndex : -1;
         }
-        // the latents requested for the next tile's footprint have had the layer's time to arrive
-        WaitLayerRefFp8(params, ctx, phase, failed, 0);
-        FinishFootprint(params, pending, shared.footprintHi, shared.footprintLo, shared.latentTable);
-        ConsumeLayerRefFp8<0, false, false>(params, ctx, phase, failed);
+        ConsumeLayerRefFp8<0, false>(params, ctx, phase, failed);
 
         aborted = RunLayerRefFp8<1, false>(params, ctx, phase, failed);
         if (!aborted) aborted = RunLayerRefFp8<2, false>(params, ctx, phase, failed);

@@ -101,32 +101,13 @@ struct __align__(16) TileTables
     uint32_t pad[3];
 };
 
-// A footprint pixel whose latents a thread has requested from global memory but not yet unpacked:
-// the request goes out while the tensor core works on the current tile's first layer, the data is
-// used after the wait for that layer, so the round trip to memory is off the critical path.
-struct PendingFootprint
-{
-    uint32_t pixel[4]; // one 16-bit latent pixel per layer
-    int offset;        // byte offset of the pixel in its grid's footprint; -1: nothing pending
-    int grid;
-};
-
-// Unpacks one latent pixel (four 4-bit features per layer) into its footprint slot.
-__device__ __forceinline__ void UnpackFootprintPixel(const uint32_t (&pixel)[4], int numLayers, uint8_t* slot,
-    const uint32_t* latentTable)
-{
-    uint2* dst = reinterpret_cast<uint2*>(slot);
-#pragma unroll
-    for (int layer = 0; layer < 4; ++layer)
-        if (layer < numLayers)
-            dst[layer] = make_uint2(latentTable[pixel[layer] & 0xFF], latentTable[pixel[layer] >> 8]);
-}
-
-// Builds the tile's tap tables and starts staging the latent footprint of both grids in shared memory
+// Builds the tile's tap tables and stages the latent footprint of both grids in shared memory
 // (nibbles unpacked to binary16 once per latent pixel instead of once per texel and tap).
-// Even warps work on the high-res grid, odd warps on the low-res grid; the 128 threads of a grid take
-// one footprint pixel each and leave it in `pending` (FinishFootprint completes it); what a larger
-// footprint has beyond 128 pixels is staged here, synchronously.
+// Even warps work on the high-res grid, odd warps on the low-res grid; the 128 threads of a grid
+// share its footprint pixels.
+// (Tried and dropped, both slower although they execute fewer instructions: two warps staging the
+// footprints while the others go on - the tile then waits for those two; and requesting the latents
+// before the wait for layer 0 and unpacking them after it.)
 //
 // `tablesValid`: the tables already hold this tile's values.  In a mip whose sizes and grid sizes
 // are powers of two (KernelMip::invariant) every tile that lies wholly inside the mip has the same
@@ -135,7 +116,7 @@ __device__ __forceinline__ void UnpackFootprintPixel(const uint32_t (&pixel)[4],
 template <bool kReferenceDivision>
 __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const KernelMip& mip, TapTables& taps,
     uint8_t* footprintHi, uint8_t* footprintLo, const uint32_t* latentTable, int tileX0, int tileY0, int lane, int warp,
-    bool tablesValid, PendingFootprint& pending)
+    bool tablesValid)
 {
     const int grid = warp & 1;
     const int gw = grid ? mip.loWidth : mip.hiWidth;
@@ -178,8 +159,6 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
         }
     }
 
-    pending.offset = -1;
-    pending.grid = grid;
     if (mip.staged)
     {
         // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
@@ -187,7 +166,6 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
         uint8_t* foot = grid ? footprintLo : footprintHi;
-        bool first = true;
         for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
         {
             const int fy = int((uint32_t(p) * magic) >> 20);
@@ -199,37 +177,24 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
             gy += gy < 0 ? gh : 0;
             gy -= gy >= gh ? gh : 0;
             const uint16_t* src = plane0 + size_t(gy) * gw + gx;
-            uint32_t pixel[4] = {0, 0, 0, 0};
+            uint2* dst = reinterpret_cast<uint2*>(foot + p * stride);
 #pragma unroll
             for (int layer = 0; layer < 4; ++layer)
-                if (layer < params.numLayers)
-                    pixel[layer] = __ldg(src + size_t(layer) * planePixels);
-            if (first)
             {
-#pragma unroll
-                for (int layer = 0; layer < 4; ++layer)
-                    pending.pixel[layer] = pixel[layer];
-                pending.offset = p * stride;
-                first = false;
+                if (layer < params.numLayers)
+                {
+                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
+                    dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
+                }
             }
-            else
-                UnpackFootprintPixel(pixel, params.numLayers, foot + p * stride, latentTable);
         }
     }
-}
-
-// Completes the footprint pixel PrepareTaps left pending.
-__device__ __forceinline__ void FinishFootprint(const KernelParams& params, const PendingFootprint& pending,
-    uint8_t* footprintHi, uint8_t* footprintLo, const uint32_t* latentTable)
-{
-    if (pending.offset >= 0)
-        UnpackFootprintPixel(pending.pixel, params.numLayers, (pending.grid ? footprintLo : footprintHi) + pending.offset, latentTable);
 }
 
 // The tile's tables (taps and positional encoding as operand bytes) and its staged footprints.
 template <bool kFp8, bool kReferenceDivision, typename Shared>
 __device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, Shared& shared,
-    int tileX0, int tileY0, int lane, int warp, bool tablesValid, PendingFootprint& pending)
+    int tileX0, int tileY0, int lane, int warp, bool tablesValid)
 {
     if (!tablesValid && warp >= 2 && warp < 4)
     {
@@ -257,17 +222,7 @@ __device__ __forceinline__ void PrepareTile(const KernelParams& params, const Ke
                                                    QuantizeInputPair<kFp8>(__float2half2_rn(0.f)));
     }
     PrepareTaps<kReferenceDivision>(params, mip, shared.tables.taps, shared.footprintHi, shared.footprintLo, shared.latentTable,
-        tileX0, tileY0, lane, warp, tablesValid, pending);
-}
-
-// The same with the footprint completed at once (nothing left pending).
-template <bool kFp8, bool kReferenceDivision, typename Shared>
-__device__ __forceinline__ void PrepareTile(const KernelParams& params, const KernelMip& mip, Shared& shared,
-    int tileX0, int tileY0, int lane, int warp, bool tablesValid)
-{
-    PendingFootprint pending;
-    PrepareTile<kFp8, kReferenceDivision>(params, mip, shared, tileX0, tileY0, lane, warp, tablesValid, pending);
-    FinishFootprint(params, pending, shared.footprintHi, shared.footprintLo, shared.latentTable);
+        tileX0, tileY0, lane, warp, tablesValid);
 }
 
 // Whether the tables built for one tile of `mip` serve the tile at (tileX0, tileY0) too, and whether

@@ -85,6 +85,21 @@ __device__ __noinline__ void ReportTimeout(uint32_t* status, uint32_t tile, uint
     }
 }
 
+// Waits for a barrier phase on behalf of a group of `threads` threads (a multiple of 32) that all
+// call this with the same named barrier `id` (1..15): the first warp of the group polls the
+// mbarrier, the others block in the hardware barrier until it joins them.  A warp that polls spends
+// issue slots on it - several polls per wait even with a suspend hint - a warp blocked in bar.sync
+// spends none.  `leader`: this thread belongs to the polling warp.  Returns false (in the polling
+// warp only) when the wait ran out; the group is released all the same.
+__device__ __forceinline__ bool MbarrierWaitGroup(uint32_t bar, uint32_t parity, bool leader, int id, int threads)
+{
+    bool completed = true;
+    if (leader)
+        completed = MbarrierWaitBounded(bar, parity);
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+    return completed;
+}
+
 __device__ __forceinline__ void FenceProxyAsyncShared()
 {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

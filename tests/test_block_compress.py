@@ -1,14 +1,26 @@
 """BC1 - BC5 encoding of decoded texels (`ntcb_block_compress`).
 
-PARITY UNPINNED against the reference: its encoders are compute shaders (src/shaders/CompressBC1-5.hlsl,
-BlockCompressCommon.hlsli) that only run through a graphics API, which is unavailable here.  What
-is tested instead:
-  * the CUDA kernel against the CPU restatement of the shader's arithmetic (two separately written
-    implementations of the same algorithm): IDENTICAL BYTES, both layouts, offsets, ragged edges;
-  * the format itself, through a BC4 decoder written from the format's definition: constant blocks
-    and blocks of 0 / 255 decode exactly, ramps and noise within the bounds the palette allows, and
-    the encoder never does worse than its own starting endpoints.
+PARITY PINNED to the reference's own shader source.  The reference's encoders are compute shaders
+(src/shaders/CompressBC1-5.hlsl, BlockCompressCommon.hlsli) that it only runs through a graphics
+API, which is unavailable here - but the shader source itself compiles as C++ once HLSL's vector
+types are supplied (oracle/hlsl_shim.h; oracle/transform_hlsl.py changes parameter qualifiers,
+literal suffixes and attributes, nothing of the arithmetic), and oracle/build_ref.sh builds it that
+way, without floating-point contraction, into oracle/_ref/libntc_ref_bc.so.  Its output on seeded
+images is committed as tests/golden/block_compress_ref.npz (generator:
+tests/golden/make_golden_block_compress.py).  What is tested:
+  * the CPU restatement of the encoders (oracle/ntc_oracle.c) against that fixture, and against a
+    live run of the compiled shader source where it is built: IDENTICAL BYTES;
+  * the CUDA kernels against the fixture: IDENTICAL BYTES; and against the CPU restatement on
+    more images, both layouts, offsets, ragged edges, NaN / infinity: IDENTICAL BYTES;
+  * the format itself, through BC1 / BC4 decoders written from the formats' definitions: constant
+    blocks and blocks of 0 / 255 decode exactly, ramps and noise within the bounds the palette
+    allows, and the encoder never does worse than its own starting endpoints.
+One deviation, outside what the reference defines: the shader indexes its single-colour tables
+with the unclamped 8-bit average of a block, so a block whose average lies outside [0, 1] reads
+beyond them; both implementations here clamp the index.  The pinned images stay inside [0, 1].
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -100,6 +112,79 @@ def images():
     special[1::5, ::3, 0] = np.inf
     special[2::5, ::3, 0] = -np.inf
     return {"noise": noise, "ramp": ramp.astype(np.float16), "binary": binary, "special": special}
+
+
+# ---------------------------------------------------------------------------------------------
+# The pin: blocks produced by the reference's own shader source compiled for the CPU
+# ---------------------------------------------------------------------------------------------
+
+PIN_IMAGES = ["smooth", "noise", "cutout", "flat", "extremes", "gentle", "two_tone"]
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "block_compress_ref.npz")
+
+
+@pytest.fixture(scope="module")
+def pinned():
+    return np.load(GOLDEN)
+
+
+def _restated(oracle, block_format, texels, **window):
+    """The CPU restatement on the channels the shader of `block_format` reads."""
+    if block_format in (4, 5):
+        window = {k: v for k, v in window.items() if k != "alpha_threshold"}
+        return oracle.block_compress(texels, 0, block_format - 3, **window)
+    return oracle.block_compress_color(texels, block_format, 0, 4, **window)
+
+
+@pytest.mark.parametrize("name", PIN_IMAGES)
+def test_restatement_reproduces_the_reference_shader_source(oracle, pinned, name):
+    """oracle/ntc_oracle.c against what src/shaders/CompressBC1-5.hlsl computed on the same texels."""
+    texels = pinned["image_" + name]
+    for block_format in (1, 2, 3, 4, 5):
+        assert np.array_equal(_restated(oracle, block_format, texels), pinned["bc%d_%s" % (block_format, name)]), block_format
+    window = dict(src_left=3, src_top=5, width_in_blocks=13, height_in_blocks=8)
+    assert np.array_equal(_restated(oracle, 1, texels, **window), pinned["bc1_window_" + name])
+    assert np.array_equal(_restated(oracle, 4, texels, **window), pinned["bc4_window_" + name])
+    assert np.array_equal(_restated(oracle, 1, texels, alpha_threshold=-1.0), pinned["bc1_opaque_" + name])
+
+
+def test_live_reference_shader_source_on_more_images(oracle):
+    """Where the compiled shader source is present: it and the restatement on fresh random images
+    (inside [0, 1], the range the reference defines), every format."""
+    if not oracle.reference_bc_available():
+        pytest.skip("oracle/_ref/libntc_ref_bc.so is not built")
+    rng = np.random.default_rng(77)
+    for trial in range(6):
+        h, w = int(rng.integers(4, 40)), int(rng.integers(4, 60))
+        base = rng.random((h, w, 4))
+        if trial % 2:
+            base = np.clip(rng.random((1, 1, 4)) + 0.1 * rng.standard_normal((h, w, 4)), 0, 1)
+        if trial % 3 == 0:
+            base[..., 3] = rng.random((h, w)) < 0.5
+        texels = base.astype(np.float16)
+        for block_format in (1, 2, 3, 4, 5):
+            rgba = np.zeros((h, w, 4), dtype=np.float32)
+            count = {4: 1, 5: 2}.get(block_format, 4)
+            rgba[..., :count] = texels[..., :count].astype(np.float32)
+            assert np.array_equal(_restated(oracle, block_format, texels), oracle.reference_block_compress(block_format, rgba)), \
+                (trial, block_format)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", PIN_IMAGES)
+def test_kernels_reproduce_the_reference_shader_source(pinned, name):
+    """The CUDA kernels against what src/shaders/CompressBC1-5.hlsl computed on the same texels."""
+    import torch
+
+    texels = torch.from_numpy(pinned["image_" + name]).cuda()
+    for block_format in (1, 2, 3, 4, 5):
+        channels = 0 if block_format in (4, 5) else 4
+        blocks = binding.block_compress(texels, block_format, 0, num_channels=channels)
+        assert np.array_equal(blocks.cpu().numpy(), pinned["bc%d_%s" % (block_format, name)]), block_format
+    window = dict(src_left=3, src_top=5, width_in_blocks=13, height_in_blocks=8)
+    assert np.array_equal(binding.block_compress(texels, 1, 0, num_channels=4, **window).cpu().numpy(), pinned["bc1_window_" + name])
+    assert np.array_equal(binding.block_compress(texels, 4, 0, **window).cpu().numpy(), pinned["bc4_window_" + name])
+    assert np.array_equal(binding.block_compress(texels, 1, 0, num_channels=4, alpha_threshold=-1.0).cpu().numpy(),
+                          pinned["bc1_opaque_" + name])
 
 
 # ---------------------------------------------------------------------------------------------
