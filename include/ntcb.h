@@ -529,9 +529,9 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
    a row of either layout is width x channels values, so with an even channel count the address
    stays 4-byte aligned, which the gather kernel needs and the call checks) or channel groups.
 
-   The first call on a device looks up the array's device address.  Every call waits for `stream`
-   before it returns, so it must not be made on a stream that is being captured.  Every call uses
-   the same array, which keeps the previous call's
+   The first call on a device looks up the array's device address: make that call before any
+   stream capture begins.  Every call waits for `stream` before it returns, so it must never be
+   made on a stream that is being captured.  Every call uses the same array, which keeps the previous call's
    contents (gaps are cleared when a request has gaps): two calls whose GPU work overlaps - on
    different streams or from different threads - race on it, so serialise them. */
 int ntcb_read_channels_to_host_noalloc(const void* deviceMip, int layout, int width, int height, int channels,

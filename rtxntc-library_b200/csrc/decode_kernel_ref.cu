@@ -52,12 +52,20 @@
 #define NTCB_ABLATE 0
 #endif
 
+// Experiments (bit mask, 0 in the product build): 1 = one issuing thread per chain instead of one for
+// both; 2 = one polling warp per chain, the others blocked in a named barrier, instead of every warp
+// polling the MMA-completion barrier itself; 4 = barrier polls without a suspend-time hint.
+#ifndef NTCB_VARIANT
+#define NTCB_VARIANT 0
+#endif
+
 namespace ntcb
 {
 namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
+constexpr int kVariant = NTCB_VARIANT;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
 __device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
@@ -462,24 +470,7 @@ __device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefT
         TmemLoadPacked8(ctx.tmemLane, bits);
         TmemLoadWait();
         const int channelPairs = params.channels >> 1;
-        uint32_t special = 0; // bit 15 / 31 set when a value has an all-ones exponent
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (j < channelPairs)
-                special |= (bits[j] & 0x7C007C00u) + 0x04000400u;
-        if (special & 0x80008000u)
-        {
-            // Inf / NaN -> 0 (src/CudaUtils.h:30-35); rare, so kept off the common path
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-            {
-                if (j < channelPairs)
-                {
-                    if ((bits[j] & 0x7C00u) == 0x7C00u) bits[j] &= 0xFFFF0000u;
-                    if ((bits[j] & 0x7C000000u) == 0x7C000000u) bits[j] &= 0x0000FFFFu;
-                }
-            }
-        }
+        ScrubSpecials(bits, channelPairs);
         if constexpr (kConvert)
         {
 #pragma unroll
@@ -490,12 +481,7 @@ __device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefT
                 StoreConverted(params.conversion, params.firstChannel, params.numChannels, ctx, bits);
         }
         else if (ctx.out)
-        {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (j < channelPairs)
-                    ctx.out[j * ctx.outStepWords] = bits[j];
-        }
+            StoreTexel(ctx.out, ctx.outStepWords, ctx.storeBytes, bits, channelPairs);
     }
 }
 
@@ -631,28 +617,6 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
         ctx.tile = tile;
         ctx.x = place.tileX0 + lane;
         ctx.y = place.tileY0 + warp;
-        {
-            // element index inside the mip fits 32 bits (8192^2 texels x 16 channels is 2^30)
-            const bool planar = params.outputLayout == kLayoutPlanarPairs;
-            const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
-                                          : (uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x)) * uint32_t(params.channels);
-            const bool inside = ctx.x < mip.width && ctx.y < mip.rowEnd;
-            if constexpr (kConvert)
-            {
-                // pixels of dstChannels components, rows without padding; outOffset counts components
-                const uint32_t pixelIndex = uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x);
-                const size_t component = size_t(mip.outOffset) + size_t(pixelIndex) * size_t(params.conversion.dstChannels);
-                unsigned char* bytes = reinterpret_cast<unsigned char*>(params.out) + component * BytesPerComponent(params.conversion.format);
-                ctx.out = inside ? reinterpret_cast<uint32_t*>(bytes) : nullptr;
-                ctx.outStepWords = pixelIndex;
-            }
-            else
-            {
-                ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
-                ctx.outStepWords = planar ? uint32_t(mip.width) : 1u;
-            }
-        }
-
         BuildInputsRef<kFp8>(params, mip, shared, ctx, lane, warp);
 
         // layer 0; while the tensor core works on it, prepare the NEXT tile (its tables and
@@ -673,7 +637,32 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
 
         aborted = RunLayerRef<kFp8, 1, false>(params, ctx, phase, failed);
         if (!aborted) aborted = RunLayerRef<kFp8, 2, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRef<kFp8, 3, kConvert>(params, ctx, phase, failed);
+        if (aborted)
+            break;
+        {
+            // where the texel goes (worked out only now: nothing of it has to stay in registers through the
+            // layers); the element index inside a mip fits 32 bits (checked on the host)
+            const bool planar = params.outputLayout == kLayoutPlanarPairs;
+            const uint32_t first = planar ? uint32_t(ctx.y) * uint32_t(mip.width) * uint32_t(params.channels) + 2u * uint32_t(ctx.x)
+                                          : (uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x)) * uint32_t(params.channels);
+            const bool inside = ctx.x < mip.width && ctx.y < mip.rowEnd;
+            if constexpr (kConvert)
+            {
+                // pixels of dstChannels components, rows without padding; outOffset counts components
+                const uint32_t pixelIndex = uint32_t(ctx.y) * uint32_t(mip.width) + uint32_t(ctx.x);
+                const size_t component = size_t(mip.outOffset) + size_t(pixelIndex) * size_t(params.conversion.dstChannels);
+                unsigned char* bytes = reinterpret_cast<unsigned char*>(params.out) + component * BytesPerComponent(params.conversion.format);
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(bytes) : nullptr;
+                ctx.outStepWords = pixelIndex;
+            }
+            else
+            {
+                ctx.out = inside ? reinterpret_cast<uint32_t*>(params.out + mip.outOffset + first) : nullptr;
+                ctx.outStepWords = planar ? uint32_t(mip.width) : 1u;
+                ctx.storeBytes = mip.storeBytes;
+            }
+        }
+        aborted = RunLayerRef<kFp8, 3, kConvert>(params, ctx, phase, failed);
         if (aborted)
             break;
         tile = nextTile;
@@ -885,6 +874,16 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     TcgenFenceBeforeSync();
     if (__syncthreads_or(failed))
         return 1;
+    if (kVariant & 1)
+    {
+        // thread 0 issues chain 0, thread 160 (another scheduler partition) chain 1
+        if ((ctx.tid == 0 || ctx.tid == 160) && !(kAblate & 16))
+        {
+            TcgenFenceAfterSync();
+            IssueChainRefFp8<kLayer>(ctx, ctx.tid ? 1 : 0);
+        }
+        return 0;
+    }
     if (ctx.tid == 0 && !(kAblate & 16))
     {
         TcgenFenceAfterSync();
@@ -912,7 +911,10 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
     // one warp of the chain polls for the chain's matrix products, the other three wait for it in a named barrier
-    if (!(kAblate & 16) && !MbarrierWaitGroup(ctx.barrier, phase, (ctx.tid & 96) == 0, 1 + (ctx.tid >> 7), 128))
+    // (every warp polls the barrier itself: one polling warp per chain with the others blocked in a named
+    // barrier executes 1.5 % fewer instructions but wakes the chain later - 4.5 % slower)
+    if (!(kAblate & 16) && !((kVariant & 2) ? MbarrierWaitGroup(ctx.barrier, phase, (ctx.tid & 96) == 0, 1 + (ctx.tid >> 7), 128)
+                                             : MbarrierWaitBounded(ctx.barrier, phase)))
     {
         failed = 1;
         ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(kLayer));

@@ -36,6 +36,17 @@ __device__ __forceinline__ void FenceBarrierInit()
 __device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
 {
     uint32_t done;
+#if defined(NTCB_VARIANT) && (NTCB_VARIANT & 4)
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+#else
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -45,6 +56,7 @@ __device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
         : "=r"(done)
         : "r"(bar), "r"(parity), "r"(kWaitHintNanoseconds)
         : "memory");
+#endif
     return done != 0;
 }
 
