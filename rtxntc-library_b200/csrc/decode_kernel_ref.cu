@@ -45,18 +45,11 @@
 // DecodeKernelRefFp8 at a time so that its share of the kernel's instructions and time can be
 // measured as a difference (`make ablations` builds one library per mask; their output is wrong by
 // construction).  1: the per-tile tables and footprint staging after the first tile; 2: the latent
-// gather and blend (constants are stored instead); 4: the activation arithmetic of layers 0-2 (the
+// gather and blend (constants are stored instead); 64: the tap tables are rebuilt for every tile; 4: the activation arithmetic of layers 0-2 (the
 // raw accumulator words are stored); 8: the global stores of the epilogue; 16: the tensor-core work
 // (no MMA issue, no wait for it); 32: the tensor-memory loads.
 #ifndef NTCB_ABLATE
 #define NTCB_ABLATE 0
-#endif
-
-// Experiments (bit mask, 0 in the product build): 1 = one issuing thread per chain instead of one for
-// both; 2 = one polling warp per chain, the others blocked in a named barrier, instead of every warp
-// polling the MMA-completion barrier itself; 4 = barrier polls without a suspend-time hint.
-#ifndef NTCB_VARIANT
-#define NTCB_VARIANT 0
 #endif
 
 namespace ntcb
@@ -65,7 +58,11 @@ namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
-constexpr int kVariant = NTCB_VARIANT;
+
+// The thread that issues the matrix products of both chains of a tile, chain 0 first: the first
+// thread of chain 1.  Its warp then waits for chain 1, whose products finish last anyway; a warp of
+// chain 0 would start on its own chain's results late by the time it takes to issue chain 1's.
+constexpr int kIssuingThread = 128;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
 __device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
@@ -391,7 +388,7 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
     if (__syncthreads_or(failed))
         return 1;
 
-    if (ctx.tid == 0)
+    if (ctx.tid == kIssuingThread)
     {
         TcgenFenceAfterSync();
         constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
@@ -874,17 +871,7 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     TcgenFenceBeforeSync();
     if (__syncthreads_or(failed))
         return 1;
-    if (kVariant & 1)
-    {
-        // thread 0 issues chain 0, thread 160 (another scheduler partition) chain 1
-        if ((ctx.tid == 0 || ctx.tid == 160) && !(kAblate & 16))
-        {
-            TcgenFenceAfterSync();
-            IssueChainRefFp8<kLayer>(ctx, ctx.tid ? 1 : 0);
-        }
-        return 0;
-    }
-    if (ctx.tid == 0 && !(kAblate & 16))
+    if (ctx.tid == kIssuingThread && !(kAblate & 16))
     {
         TcgenFenceAfterSync();
 #pragma unroll
@@ -911,10 +898,11 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
     // one warp of the chain polls for the chain's matrix products, the other three wait for it in a named barrier
-    // (every warp polls the barrier itself: one polling warp per chain with the others blocked in a named
-    // barrier executes 1.5 % fewer instructions but wakes the chain later - 4.5 % slower)
-    if (!(kAblate & 16) && !((kVariant & 2) ? MbarrierWaitGroup(ctx.barrier, phase, (ctx.tid & 96) == 0, 1 + (ctx.tid >> 7), 128)
-                                             : MbarrierWaitBounded(ctx.barrier, phase)))
+    // (Every warp polls the barrier itself.  Tried and dropped: one polling warp per chain with the other
+    // three blocked in a named barrier executes 1.5 % fewer instructions but wakes the chain later, 4.5 %
+    // slower; an issuing thread per chain instead of one for both, 7 % slower; polls without a suspend-time
+    // hint, the same speed.)
+    if (!(kAblate & 16) && !MbarrierWaitBounded(ctx.barrier, phase))
     {
         failed = 1;
         ReportTimeout(params.status, uint32_t(ctx.tile), uint32_t(kLayer));
@@ -1191,7 +1179,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
             const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
             if (!(kAblate & 1))
                 PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp,
-                    keepsTables && place.mipIndex == tablesMip);
+                    keepsTables && place.mipIndex == tablesMip && !(kAblate & 64));
             tablesMip = keepsTables ? place.mipIndex : -1;
         }
         ConsumeLayerRefFp8<0, false>(params, ctx, phase, failed);

@@ -30,23 +30,11 @@ __device__ __forceinline__ void FenceBarrierInit()
 }
 
 // One poll of a barrier phase.  The instruction may suspend the thread until the phase completes
-// or `kWaitHintNanoseconds` have passed, whichever comes first; without the hint the suspension is a
-// fraction of a microsecond and the polling loops of the waiting warps take a tenth of the kernel's
-// issue slots.
+// or `kWaitHintNanoseconds` have passed, whichever comes first (measured: the same speed as polls
+// without the hint).
 __device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
 {
     uint32_t done;
-#if defined(NTCB_VARIANT) && (NTCB_VARIANT & 4)
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-#else
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -56,7 +44,6 @@ __device__ __forceinline__ bool MbarrierTryWait(uint32_t bar, uint32_t parity)
         : "=r"(done)
         : "r"(bar), "r"(parity), "r"(kWaitHintNanoseconds)
         : "memory");
-#endif
     return done != 0;
 }
 
@@ -95,21 +82,6 @@ __device__ __noinline__ void ReportTimeout(uint32_t* status, uint32_t tile, uint
         status[1] = tile;
         status[2] = layer;
     }
-}
-
-// Waits for a barrier phase on behalf of a group of `threads` threads (a multiple of 32) that all
-// call this with the same named barrier `id` (1..15): the first warp of the group polls the
-// mbarrier, the others block in the hardware barrier until it joins them.  A warp that polls spends
-// issue slots on it - several polls per wait even with a suspend hint - a warp blocked in bar.sync
-// spends none.  `leader`: this thread belongs to the polling warp.  Returns false (in the polling
-// warp only) when the wait ran out; the group is released all the same.
-__device__ __forceinline__ bool MbarrierWaitGroup(uint32_t bar, uint32_t parity, bool leader, int id, int threads)
-{
-    bool completed = true;
-    if (leader)
-        completed = MbarrierWaitBounded(bar, parity);
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-    return completed;
 }
 
 __device__ __forceinline__ void FenceProxyAsyncShared()
