@@ -106,6 +106,7 @@ struct KernelMip
                      // layout with a texel size and a mip address that are multiples of it; 4 otherwise
     int invariant;   // every size involved is a power of two: the tap and positional-encoding tables of a tile do not
                      // depend on which tile of the mip it is (see PrepareTaps)
+    int hiStepX, hiStepY, loStepX, loStepY; // invariant mips: latent pixels of each grid per tile step in x and y
 };
 
 struct KernelParams

@@ -85,9 +85,10 @@ struct __align__(16) TapTables
     int4 colTap[2][kTileWidth];
     // per grid and tile row: byte offset of the upper tap's footprint row, dy, 1 - dy, bytes per footprint row
     int4 rowTap[2][kTileHeight];
-    // per grid: footprint width and height in latent pixels, bytes per footprint row, and the multiplier
-    // that divides a pixel index by the width (p / width == (p * magic) >> 20 for p < 2048)
-    int4 footprint[2];
+    // per grid: footprint width and height in latent pixels
+    int2 footprint[2];
+    // per grid: the footprint origin (tap of the first column / row) of the tile the tables were built for, and that tile's origin
+    int4 origin[2];
 };
 
 // Tap tables plus the positional encoding as operand bytes (kernels whose A operand holds 8-bit codes).
@@ -124,17 +125,15 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
     const int stride = mip.strideBytes;
 
     int fx0, fy0, footW, footH;
-    uint32_t magic;
     if (tablesValid)
     {
-        // only the footprint's origin depends on the tile: the taps of its first column and row
-        float unused;
-        AxisTap<kReferenceDivision>(tileX0, mip.width, mip.invWidth, gw, fx0, unused);
-        AxisTap<kReferenceDivision>(tileY0, mip.height, mip.invHeight, gh, fy0, unused);
-        const int4 footprint = taps.footprint[grid];
+        // only the footprint's origin depends on the tile, and it moves by whole latent pixels per tile step
+        const int4 origin = taps.origin[grid];
+        const int2 footprint = taps.footprint[grid];
+        fx0 = origin.x + ((tileX0 - origin.z) >> 5) * (grid ? mip.loStepX : mip.hiStepX);
+        fy0 = origin.y + ((tileY0 - origin.w) >> 3) * (grid ? mip.loStepY : mip.hiStepY);
         footW = footprint.x;
         footH = footprint.y;
-        magic = uint32_t(footprint.w);
     }
     else
     {
@@ -146,8 +145,6 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
         fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
         footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
         footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
-        // p / footW == (p * magic) >> 20 for p < 2048: the IEEE quotient of 2^20 / footW floors exactly
-        magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
         if (warp < 2)
         {
             taps.colTap[grid][lane] = make_int4((xb - fx0) * stride, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
@@ -155,36 +152,42 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
                 taps.rowTap[grid][lane] =
                     make_int4((yb - fy0) * footW * stride, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), footW * stride);
             if (lane == 0)
-                taps.footprint[grid] = make_int4(footW, footH, footW * stride, int(magic));
+            {
+                taps.footprint[grid] = make_int2(footW, footH);
+                taps.origin[grid] = make_int4(fx0, fy0, tileX0, tileY0);
+            }
         }
     }
 
     if (mip.staged)
     {
-        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
-        const int count = footW * footH;
+        // Footprint rows go to the four warps that share this grid, the pixels of a row to the lanes:
+        // the row's wrap and address are uniform over the warp and nothing has to be divided.
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
-        const size_t planePixels = grid ? mip.loPlane : mip.hiPlane;
+        const uint32_t planePixels = uint32_t(grid ? mip.loPlane : mip.hiPlane);
         uint8_t* foot = grid ? footprintLo : footprintHi;
-        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
+        for (int fy = warp >> 1; fy < footH; fy += kThreadsPerCta / 64)
         {
-            const int fy = int((uint32_t(p) * magic) >> 20);
-            const int fx = p - fy * footW;
             // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
-            int gx = fx0 + fx, gy = fy0 + fy;
-            gx += gx < 0 ? gw : 0;
-            gx -= gx >= gw ? gw : 0;
+            int gy = fy0 + fy;
             gy += gy < 0 ? gh : 0;
             gy -= gy >= gh ? gh : 0;
-            const uint16_t* src = plane0 + size_t(gy) * gw + gx;
-            uint2* dst = reinterpret_cast<uint2*>(foot + p * stride);
-#pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
+            const uint32_t rowFirst = uint32_t(gy) * uint32_t(gw);
+            uint8_t* rowSlots = foot + fy * footW * stride;
+            for (int fx = lane; fx < footW; fx += 32)
             {
-                if (layer < params.numLayers)
+                int gx = fx0 + fx;
+                gx += gx < 0 ? gw : 0;
+                gx -= gx >= gw ? gw : 0;
+                uint2* dst = reinterpret_cast<uint2*>(rowSlots + fx * stride);
+#pragma unroll
+                for (int layer = 0; layer < 4; ++layer)
                 {
-                    const uint32_t pixel = __ldg(src + size_t(layer) * planePixels);
-                    dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
+                    if (layer < params.numLayers)
+                    {
+                        const uint32_t pixel = __ldg(plane0 + (rowFirst + uint32_t(gx) + uint32_t(layer) * planePixels));
+                        dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
+                    }
                 }
             }
         }

@@ -62,7 +62,9 @@ bool ValidMip(const NtcbMipDesc& m, bool pairedOutput)
 {
     return !(m.width < 1 || m.height < 1 || m.hiWidth < 1 || m.hiHeight < 1 || m.loWidth < 1 || m.loHeight < 1 ||
              m.rowBegin < 0 || m.rowEnd > m.height || m.rowBegin > m.rowEnd || (pairedOutput && (m.outOffset & 1)) ||
-             m.hiPlane < uint64_t(m.hiWidth) * m.hiHeight || m.loPlane < uint64_t(m.loWidth) * m.loHeight);
+             m.hiPlane < uint64_t(m.hiWidth) * m.hiHeight || m.loPlane < uint64_t(m.loWidth) * m.loHeight ||
+             // the kernels index the pixels of a grid's layers with 32 bits
+             m.hiPlane > 0x3FFFFFFFull || m.loPlane > 0x3FFFFFFFull);
 }
 
 // The kernel's view of one mip (everything but its place in the tile list).
@@ -108,6 +110,14 @@ void FillKernelMip(const NtcbMipDesc& m, int layers, KernelMip& km, int footprin
                    ((long long)tileHeight * m.hiHeight) % m.height == 0 && ((long long)tileHeight * m.loHeight) % m.height == 0 &&
                    scaledColumns == floorf(scaledColumns) && scaledRows == floorf(scaledRows) && scaleIsPowerOfTwo
         ? 1 : 0;
+    km.hiStepX = km.hiStepY = km.loStepX = km.loStepY = 0;
+    if (km.invariant)
+    {
+        km.hiStepX = int((long long)kTileWidth * m.hiWidth / m.width);
+        km.loStepX = int((long long)kTileWidth * m.loWidth / m.width);
+        km.hiStepY = int((long long)tileHeight * m.hiHeight / m.height);
+        km.loStepY = int((long long)tileHeight * m.loHeight / m.height);
+    }
     km.tilesX = (m.width + kTileWidth - 1) / kTileWidth;
     km.tilesXMagic = km.tilesX == 1 ? 0u : unsigned((0x100000000ull + km.tilesX - 1) / km.tilesX);
     km.firstTile = 0;
