@@ -52,12 +52,39 @@
 #define NTCB_ABLATE 0
 #endif
 
+// Experiment: NTCB_PREFETCH = 1 asks for the next tile's latents in the L1 cache before this tile's inputs are built.
+#ifndef NTCB_PREFETCH
+#define NTCB_PREFETCH 0
+#endif
+
+// Experiment: NTCB_UNIFORM_ISSUE = 1 lets the whole issuing warp run the descriptor arithmetic, on values
+// the compiler can see are the same in every lane, and elects one lane only for the instructions
+// that hand work to the tensor core.
+#ifndef NTCB_UNIFORM_ISSUE
+#define NTCB_UNIFORM_ISSUE 0
+#endif
+
 namespace ntcb
 {
 namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
+constexpr bool kUniformIssue = NTCB_UNIFORM_ISSUE != 0;
+
+// Nonzero in exactly one lane of the (converged) warp.
+__device__ __forceinline__ uint32_t ElectOne()
+{
+    uint32_t elected;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(elected));
+    return elected;
+}
 
 // The thread that issues the matrix products of both chains of a tile, chain 0 first: the first
 // thread of chain 1.  Its warp then waits for chain 1, whose products finish last anyway; a warp of
@@ -65,15 +92,17 @@ constexpr int kAblate = NTCB_ABLATE;
 constexpr int kIssuingThread = 128;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
-__device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
+__device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate,
+    uint32_t enabled = 1)
 {
     asm volatile(
         "{\n\t"
-        ".reg .pred p;\n\t"
+        ".reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
         "}" ::"r"(tmemD),
-        "l"(descA), "l"(descB), "r"(instr), "r"(accumulate)
+        "l"(descA), "l"(descB), "r"(instr), "r"(accumulate), "r"(enabled)
         : "memory");
 }
 
@@ -802,21 +831,23 @@ struct __align__(128) RefFp8SharedStorage
 };
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 32 e4m3 operands, binary16 accumulators.
-__device__ __forceinline__ void UmmaE4m3F16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate)
+__device__ __forceinline__ void UmmaE4m3F16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate,
+    uint32_t enabled = 1)
 {
     asm volatile(
         "{\n\t"
-        ".reg .pred p;\n\t"
+        ".reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
         "}" ::"r"(tmemD),
-        "l"(descA), "l"(descB), "r"(instr), "r"(accumulate)
+        "l"(descA), "l"(descB), "r"(instr), "r"(accumulate), "r"(enabled)
         : "memory");
 }
 
 // The matrix products of one layer for one chain of the tile, issued by the calling thread.
 template <int kLayer>
-__device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int half)
+__device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int half, uint32_t enabled = 1)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
     constexpr int kK = kLayer == 0 ? 48 : kLayer == 1 ? 64 : kLayer == 2 ? 48 : 32;
@@ -834,7 +865,7 @@ __device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int 
     const uint64_t biasBase = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
     const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
     // accumulators := bias (binary16 step: rows (1, 0, ...) times the bias column: exact)
-    UmmaF16(accumulators, onesBase, biasBase, instr, 0);
+    UmmaF16(accumulators, onesBase, biasBase, instr, 0, enabled);
 #pragma unroll
     for (int step = 0; step < kK / 16; ++step)
     {
@@ -843,18 +874,19 @@ __device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int 
             // 16 products of the 32-wide chunk step / 2: weight copy `step` has the other 16 columns zeroed
             const uint64_t descA = operandBase + uint64_t(((step / 2) * 2 * 2048) >> 4);
             const uint64_t descB = weightBase + uint64_t((step * kN * 32) >> 4);
-            UmmaE4m3F16(accumulators, descA, descB, instr, 1);
+            UmmaE4m3F16(accumulators, descA, descB, instr, 1, enabled);
         }
         else
         {
             // binary16 operands: one K step = two core matrices of 8 halves
             const uint64_t descA = operandBase + uint64_t((step * 2 * 2048) >> 4);
             const uint64_t descB = weightBase + uint64_t((step * 2 * kN * 16) >> 4);
-            UmmaF16(accumulators, descA, descB, instr, 1);
+            UmmaF16(accumulators, descA, descB, instr, 1, enabled);
         }
     }
     // arrives once everything issued so far has completed: this chain's accumulators are ready
-    UmmaCommit(ctx.barrierBase + half * 8);
+    if (enabled)
+        UmmaCommit(ctx.barrierBase + half * 8);
 }
 
 // First half of a layer: hands the A operand written before this call to the tensor core.  Returns
@@ -871,6 +903,25 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     TcgenFenceBeforeSync();
     if (__syncthreads_or(failed))
         return 1;
+    if (kUniformIssue)
+    {
+        if ((ctx.tid >> 5) == kIssuingThread / 32 && !(kAblate & 16))
+        {
+            TcgenFenceAfterSync();
+            // the same values in every lane, in a form that shows it
+            RefTileContext uniform = ctx;
+            uniform.operandA = __shfl_sync(0xFFFFFFFFu, ctx.operandA, 0);
+            uniform.biasRegion = __shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0);
+            uniform.networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
+            uniform.tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
+            uniform.barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
+            const uint32_t elected = ElectOne();
+#pragma unroll
+            for (int half = 0; half < kRefChains; ++half)
+                IssueChainRefFp8<kLayer>(uniform, half, elected);
+        }
+        return 0;
+    }
     if (ctx.tid == kIssuingThread && !(kAblate & 16))
     {
         TcgenFenceAfterSync();
@@ -1157,6 +1208,16 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         ctx.tile = tile;
         ctx.x = place.tileX0 + lane;
         ctx.y = place.tileY0 + warp;
+        if (NTCB_PREFETCH)
+        {
+            const int ahead = tile + int(gridDim.x);
+            if (ahead < params.totalTiles)
+            {
+                const TilePlace next = locate(ahead, place.mipIndex);
+                if (next.mipIndex == tablesMip && TileKeepsTables(params.mips[next.mipIndex], next.tileX0, next.tileY0))
+                    PrefetchFootprint(params, params.mips[next.mipIndex], shared.tables.taps, next.tileX0, next.tileY0, lane, warp);
+            }
+        }
         // the e4m3 input stage is the one of the exact-accumulation kernel (64-byte rows of codes)
         if (kAblate & 2)
         {

@@ -85,8 +85,9 @@ struct __align__(16) TapTables
     int4 colTap[2][kTileWidth];
     // per grid and tile row: byte offset of the upper tap's footprint row, dy, 1 - dy, bytes per footprint row
     int4 rowTap[2][kTileHeight];
-    // per grid: footprint width and height in latent pixels
-    int2 footprint[2];
+    // per grid: footprint width and height in latent pixels, pixel count, and the multiplier that divides a
+    // pixel index by the width (p / width == (p * magic) >> 20 for p < 2048)
+    int4 footprint[2];
     // per grid: the footprint origin (tap of the first column / row) of the tile the tables were built for, and that tile's origin
     int4 origin[2];
 };
@@ -124,16 +125,18 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
     const int gh = grid ? mip.loHeight : mip.hiHeight;
     const int stride = mip.strideBytes;
 
-    int fx0, fy0, footW, footH;
+    int fx0, fy0, footW, count;
+    uint32_t magic;
     if (tablesValid)
     {
         // only the footprint's origin depends on the tile, and it moves by whole latent pixels per tile step
         const int4 origin = taps.origin[grid];
-        const int2 footprint = taps.footprint[grid];
+        const int4 footprint = taps.footprint[grid];
         fx0 = origin.x + ((tileX0 - origin.z) >> 5) * (grid ? mip.loStepX : mip.hiStepX);
         fy0 = origin.y + ((tileY0 - origin.w) >> 3) * (grid ? mip.loStepY : mip.hiStepY);
         footW = footprint.x;
-        footH = footprint.y;
+        count = footprint.z;
+        magic = uint32_t(footprint.w);
     }
     else
     {
@@ -144,7 +147,10 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
         fx0 = __shfl_sync(0xFFFFFFFFu, xb, 0);
         fy0 = __shfl_sync(0xFFFFFFFFu, yb, 0);
         footW = __shfl_sync(0xFFFFFFFFu, xb, 31) - fx0 + 2;
-        footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
+        const int footH = __shfl_sync(0xFFFFFFFFu, yb, kTileHeight - 1) - fy0 + 2;
+        count = footW * footH;
+        // the IEEE quotient of 2^20 / footW floors exactly
+        magic = uint32_t(__float2int_rd(__fdiv_rn(1048576.f, float(footW)))) + 1;
         if (warp < 2)
         {
             taps.colTap[grid][lane] = make_int4((xb - fx0) * stride, __float_as_int(dx), __float_as_int(__fsub_rn(1.f, dx)), 0);
@@ -153,7 +159,7 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
                     make_int4((yb - fy0) * footW * stride, __float_as_int(dy), __float_as_int(__fsub_rn(1.f, dy)), footW * stride);
             if (lane == 0)
             {
-                taps.footprint[grid] = make_int2(footW, footH);
+                taps.footprint[grid] = make_int4(footW, footH, count, int(magic));
                 taps.origin[grid] = make_int4(fx0, fy0, tileX0, tileY0);
             }
         }
@@ -161,37 +167,69 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
 
     if (mip.staged)
     {
-        // Footprint rows go to the four warps that share this grid, the pixels of a row to the lanes:
-        // the row's wrap and address are uniform over the warp and nothing has to be divided.
+        // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
+        // (tried: one footprint row per warp - no division, but more warps with a few active lanes each:
+        // 5 % more instructions and 6 % slower)
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const uint32_t planePixels = uint32_t(grid ? mip.loPlane : mip.hiPlane);
         uint8_t* foot = grid ? footprintLo : footprintHi;
-        for (int fy = warp >> 1; fy < footH; fy += kThreadsPerCta / 64)
+        for (int p = lane + 32 * (warp >> 1); p < count; p += kThreadsPerCta / 2)
         {
+            const int fy = int((uint32_t(p) * magic) >> 20);
+            const int fx = p - fy * footW;
             // wrap addressing (src/FeatureGridDevice.h:51-57); the footprint spans [-1, size]
-            int gy = fy0 + fy;
+            int gx = fx0 + fx, gy = fy0 + fy;
+            gx += gx < 0 ? gw : 0;
+            gx -= gx >= gw ? gw : 0;
             gy += gy < 0 ? gh : 0;
             gy -= gy >= gh ? gh : 0;
-            const uint32_t rowFirst = uint32_t(gy) * uint32_t(gw);
-            uint8_t* rowSlots = foot + fy * footW * stride;
-            for (int fx = lane; fx < footW; fx += 32)
-            {
-                int gx = fx0 + fx;
-                gx += gx < 0 ? gw : 0;
-                gx -= gx >= gw ? gw : 0;
-                uint2* dst = reinterpret_cast<uint2*>(rowSlots + fx * stride);
+            const uint32_t first = uint32_t(gy) * uint32_t(gw) + uint32_t(gx);
+            uint2* dst = reinterpret_cast<uint2*>(foot + p * stride);
 #pragma unroll
-                for (int layer = 0; layer < 4; ++layer)
+            for (int layer = 0; layer < 4; ++layer)
+            {
+                if (layer < params.numLayers)
                 {
-                    if (layer < params.numLayers)
-                    {
-                        const uint32_t pixel = __ldg(plane0 + (rowFirst + uint32_t(gx) + uint32_t(layer) * planePixels));
-                        dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
-                    }
+                    const uint32_t pixel = __ldg(plane0 + (first + uint32_t(layer) * planePixels));
+                    dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
                 }
             }
         }
     }
+}
+
+// Asks for the latents of the NEXT tile's footprint to be brought into the L1 cache, one tile ahead
+// of PrepareTaps, which then finds them close: only in mips with invariant tables (the footprint's
+// place follows from the tables in shared memory), and nothing has to be held in registers meanwhile.
+__device__ __forceinline__ void PrefetchFootprint(const KernelParams& params, const KernelMip& mip, const TapTables& taps,
+    int tileX0, int tileY0, int lane, int warp)
+{
+    if (!mip.staged)
+        return;
+    const int grid = warp & 1;
+    const int gw = grid ? mip.loWidth : mip.hiWidth;
+    const int gh = grid ? mip.loHeight : mip.hiHeight;
+    const int4 origin = taps.origin[grid];
+    const int4 footprint = taps.footprint[grid];
+    const int p = lane + 32 * (warp >> 1);
+    if (p >= footprint.z)
+        return;
+    const int fx0 = origin.x + ((tileX0 - origin.z) >> 5) * (grid ? mip.loStepX : mip.hiStepX);
+    const int fy0 = origin.y + ((tileY0 - origin.w) >> 3) * (grid ? mip.loStepY : mip.hiStepY);
+    const int fy = int((uint32_t(p) * uint32_t(footprint.w)) >> 20);
+    const int fx = p - fy * footprint.x;
+    int gx = fx0 + fx, gy = fy0 + fy;
+    gx += gx < 0 ? gw : 0;
+    gx -= gx >= gw ? gw : 0;
+    gy += gy < 0 ? gh : 0;
+    gy -= gy >= gh ? gh : 0;
+    const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
+    const uint32_t planePixels = uint32_t(grid ? mip.loPlane : mip.hiPlane);
+    const uint32_t first = uint32_t(gy) * uint32_t(gw) + uint32_t(gx);
+#pragma unroll
+    for (int layer = 0; layer < 4; ++layer)
+        if (layer < params.numLayers)
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(plane0 + (first + uint32_t(layer) * planePixels)));
 }
 
 // The tile's tables (taps and positional encoding as operand bytes) and its staged footprints.
