@@ -52,25 +52,12 @@
 #define NTCB_ABLATE 0
 #endif
 
-// Experiment: NTCB_PREFETCH = 1 asks for the next tile's latents in the L1 cache before this tile's inputs are built.
-#ifndef NTCB_PREFETCH
-#define NTCB_PREFETCH 0
-#endif
-
-// Experiment: NTCB_UNIFORM_ISSUE = 1 lets the whole issuing warp run the descriptor arithmetic, on values
-// the compiler can see are the same in every lane, and elects one lane only for the instructions
-// that hand work to the tensor core.
-#ifndef NTCB_UNIFORM_ISSUE
-#define NTCB_UNIFORM_ISSUE 0
-#endif
-
 namespace ntcb
 {
 namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
-constexpr bool kUniformIssue = NTCB_UNIFORM_ISSUE != 0;
 
 // Nonzero in exactly one lane of the (converged) warp.
 __device__ __forceinline__ uint32_t ElectOne()
@@ -86,10 +73,10 @@ __device__ __forceinline__ uint32_t ElectOne()
     return elected;
 }
 
-// The thread that issues the matrix products of both chains of a tile, chain 0 first: the first
-// thread of chain 1.  Its warp then waits for chain 1, whose products finish last anyway; a warp of
-// chain 0 would start on its own chain's results late by the time it takes to issue chain 1's.
-constexpr int kIssuingThread = 128;
+// The warp that issues the matrix products of both chains of a tile, chain 0 first: the first
+// warp of chain 1.  It then waits for chain 1, whose products finish last anyway; a warp of chain 0
+// would start on its own chain's results late by the time it takes to issue chain 1's (2 %).
+constexpr int kIssuingWarp = 4;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
 __device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate,
@@ -300,7 +287,7 @@ __device__ __forceinline__ void GatherGridRef(const KernelParams& params, const 
     const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
     const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
 
-    const int stride = mip.strideBytes;
+    const int stride = StrideBytes(mip);
     const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (col.x + row.x);
     const uint8_t* tap10 = tap00 + row.w;
 #pragma unroll
@@ -417,33 +404,39 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
     if (__syncthreads_or(failed))
         return 1;
 
-    if (ctx.tid == kIssuingThread)
+    // The whole issuing warp runs the descriptor arithmetic on values that are visibly the same in every
+    // lane; one elected lane hands the work to the tensor core (see IssueLayerRefFp8).
+    if ((ctx.tid >> 5) == kIssuingWarp)
     {
         TcgenFenceAfterSync();
         constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
-        // The issuing thread is the critical path of the layer: the four base descriptors are built
-        // once, every operand is then a constant offset (in 16-byte units) added to the address field.
-        const uint64_t operandBase = MakeSmemDescriptor(ctx.operandA, 2048, 128);
-        const uint64_t onesBase = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
-        const uint64_t weightBase = MakeSmemDescriptor(ctx.networkBase + kWeightOffset, kN * 16, 128);
-        const uint64_t biasBase = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
+        const uint32_t networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
+        const uint32_t tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
+        const uint32_t barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
+        // the four base descriptors are built once, every operand is then a constant offset (in 16-byte
+        // units) added to the address field
+        const uint64_t operandBase = MakeSmemDescriptor(__shfl_sync(0xFFFFFFFFu, ctx.operandA, 0), 2048, 128);
+        const uint64_t onesBase = MakeSmemDescriptor(__shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0), 2048, 128);
+        const uint64_t weightBase = MakeSmemDescriptor(networkBase + kWeightOffset, kN * 16, 128);
+        const uint64_t biasBase = MakeSmemDescriptor(networkBase + kBiasOffset, kN * 16, 128);
+        const uint32_t elected = ElectOne();
 #pragma unroll
         for (int half = 0; half < kRefChains; ++half)
         {
-            const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
+            const uint32_t accumulators = tmemBase + half * kTmemColumnsPerHalf;
             // accumulators := bias (rows (1, 0, ...) times the bias column: exact)
-            UmmaF16(accumulators, onesBase, biasBase, instr, 0);
+            UmmaF16(accumulators, onesBase, biasBase, instr, 0, elected);
 #pragma unroll
             for (int kStep = 0; kStep < kK / 16; ++kStep)
             {
                 // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
                 const uint64_t descA = operandBase + uint64_t((half * kRefOperandBytes + kStep * 2 * 2048) >> 4);
                 const uint64_t descB = weightBase + uint64_t((kStep * 2 * kN * 16) >> 4);
-                UmmaF16(accumulators, descA, descB, instr, 1);
+                UmmaF16(accumulators, descA, descB, instr, 1, elected);
             }
             // arrives once everything issued so far has completed: this chain's accumulators are ready
-            // (one issuing thread for both chains measured faster than one per chain)
-            UmmaCommit(ctx.barrierBase + half * 8);
+            if (elected)
+                UmmaCommit(barrierBase + half * 8);
         }
     }
     return 0;
@@ -903,31 +896,22 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     TcgenFenceBeforeSync();
     if (__syncthreads_or(failed))
         return 1;
-    if (kUniformIssue)
-    {
-        if ((ctx.tid >> 5) == kIssuingThread / 32 && !(kAblate & 16))
-        {
-            TcgenFenceAfterSync();
-            // the same values in every lane, in a form that shows it
-            RefTileContext uniform = ctx;
-            uniform.operandA = __shfl_sync(0xFFFFFFFFu, ctx.operandA, 0);
-            uniform.biasRegion = __shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0);
-            uniform.networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
-            uniform.tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
-            uniform.barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
-            const uint32_t elected = ElectOne();
-#pragma unroll
-            for (int half = 0; half < kRefChains; ++half)
-                IssueChainRefFp8<kLayer>(uniform, half, elected);
-        }
-        return 0;
-    }
-    if (ctx.tid == kIssuingThread && !(kAblate & 16))
+    // The whole issuing warp runs the descriptor arithmetic, on values the compiler can see are the same
+    // in every lane (hence the shuffles), and one elected lane hands the work to the tensor core: issued
+    // from a single thread inside a divergent branch the same code cost 85 instructions per texel more.
+    if ((ctx.tid >> 5) == kIssuingWarp && !(kAblate & 16))
     {
         TcgenFenceAfterSync();
+        RefTileContext uniform = ctx;
+        uniform.operandA = __shfl_sync(0xFFFFFFFFu, ctx.operandA, 0);
+        uniform.biasRegion = __shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0);
+        uniform.networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
+        uniform.tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
+        uniform.barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
+        const uint32_t elected = ElectOne();
 #pragma unroll
         for (int half = 0; half < kRefChains; ++half)
-            IssueChainRefFp8<kLayer>(ctx, half);
+            IssueChainRefFp8<kLayer>(uniform, half, elected);
     }
     return 0;
 }
@@ -1157,7 +1141,12 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
+#if defined(NTCB_UNIFORM_WARP) && NTCB_UNIFORM_WARP
+    // experiment: the warp index in a form the compiler can see is the same in every lane
+    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
+#else
     const int warp = tid >> 5;      // = the thread's row of the tile
+#endif
     const int half = warp >> 2;     // the 128-row chain of this thread
 
     int failed = SetupCtaRefFp8(shared, params.network, params.status, params.loadWaitPolls, tid, warp);
@@ -1208,16 +1197,6 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         ctx.tile = tile;
         ctx.x = place.tileX0 + lane;
         ctx.y = place.tileY0 + warp;
-        if (NTCB_PREFETCH)
-        {
-            const int ahead = tile + int(gridDim.x);
-            if (ahead < params.totalTiles)
-            {
-                const TilePlace next = locate(ahead, place.mipIndex);
-                if (next.mipIndex == tablesMip && TileKeepsTables(params.mips[next.mipIndex], next.tileX0, next.tileY0))
-                    PrefetchFootprint(params, params.mips[next.mipIndex], shared.tables.taps, next.tileX0, next.tileY0, lane, warp);
-            }
-        }
         // the e4m3 input stage is the one of the exact-accumulation kernel (64-byte rows of codes)
         if (kAblate & 2)
         {

@@ -12,10 +12,25 @@
 #include "decode_kernel.h"
 #include "kernel_parts.cuh"
 
+// Experiment: NTCB_FIXED_LAYERS = n compiles the input stage for n latent layers (4 n features) only.
+#ifndef NTCB_FIXED_LAYERS
+#define NTCB_FIXED_LAYERS 0
+#endif
+
 namespace ntcb
 {
 namespace
 {
+
+__device__ __forceinline__ int NumLayers(const KernelParams& params)
+{
+    return NTCB_FIXED_LAYERS ? NTCB_FIXED_LAYERS : params.numLayers;
+}
+
+__device__ __forceinline__ int StrideBytes(const KernelMip& mip)
+{
+    return NTCB_FIXED_LAYERS ? (NTCB_FIXED_LAYERS == 1 ? 8 : NTCB_FIXED_LAYERS <= 3 ? 24 : 40) : mip.strideBytes;
+}
 
 // Quantises a pair of network inputs.  Int8: floor(x * 127.5 - 0.5) clamped to +-127
 // (src/tin/tin_mlp.h:25-31), returned as the low bytes of the two 16-bit lanes.  FP8: round to
@@ -123,7 +138,7 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
     const int grid = warp & 1;
     const int gw = grid ? mip.loWidth : mip.hiWidth;
     const int gh = grid ? mip.loHeight : mip.hiHeight;
-    const int stride = mip.strideBytes;
+    const int stride = StrideBytes(mip);
 
     int fx0, fy0, footW, count;
     uint32_t magic;
@@ -169,7 +184,7 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
     {
         // footprint pixel p = fy * footW + fx, handed out over the 128 threads that share this grid
         // (tried: one footprint row per warp - no division, but more warps with a few active lanes each:
-        // 5 % more instructions and 6 % slower)
+        // 5 % more instructions and 6 % slower; prefetching the next tile's latents into L1 a tile ahead: 5 % slower)
         const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
         const uint32_t planePixels = uint32_t(grid ? mip.loPlane : mip.hiPlane);
         uint8_t* foot = grid ? footprintLo : footprintHi;
@@ -188,7 +203,7 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
 #pragma unroll
             for (int layer = 0; layer < 4; ++layer)
             {
-                if (layer < params.numLayers)
+                if (layer < NumLayers(params))
                 {
                     const uint32_t pixel = __ldg(plane0 + (first + uint32_t(layer) * planePixels));
                     dst[layer] = make_uint2(latentTable[pixel & 0xFF], latentTable[pixel >> 8]);
@@ -196,40 +211,6 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
             }
         }
     }
-}
-
-// Asks for the latents of the NEXT tile's footprint to be brought into the L1 cache, one tile ahead
-// of PrepareTaps, which then finds them close: only in mips with invariant tables (the footprint's
-// place follows from the tables in shared memory), and nothing has to be held in registers meanwhile.
-__device__ __forceinline__ void PrefetchFootprint(const KernelParams& params, const KernelMip& mip, const TapTables& taps,
-    int tileX0, int tileY0, int lane, int warp)
-{
-    if (!mip.staged)
-        return;
-    const int grid = warp & 1;
-    const int gw = grid ? mip.loWidth : mip.hiWidth;
-    const int gh = grid ? mip.loHeight : mip.hiHeight;
-    const int4 origin = taps.origin[grid];
-    const int4 footprint = taps.footprint[grid];
-    const int p = lane + 32 * (warp >> 1);
-    if (p >= footprint.z)
-        return;
-    const int fx0 = origin.x + ((tileX0 - origin.z) >> 5) * (grid ? mip.loStepX : mip.hiStepX);
-    const int fy0 = origin.y + ((tileY0 - origin.w) >> 3) * (grid ? mip.loStepY : mip.hiStepY);
-    const int fy = int((uint32_t(p) * uint32_t(footprint.w)) >> 20);
-    const int fx = p - fy * footprint.x;
-    int gx = fx0 + fx, gy = fy0 + fy;
-    gx += gx < 0 ? gw : 0;
-    gx -= gx >= gw ? gw : 0;
-    gy += gy < 0 ? gh : 0;
-    gy -= gy >= gh ? gh : 0;
-    const uint16_t* plane0 = params.latents + (grid ? mip.loOffset : mip.hiOffset);
-    const uint32_t planePixels = uint32_t(grid ? mip.loPlane : mip.hiPlane);
-    const uint32_t first = uint32_t(gy) * uint32_t(gw) + uint32_t(gx);
-#pragma unroll
-    for (int layer = 0; layer < 4; ++layer)
-        if (layer < params.numLayers)
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(plane0 + (first + uint32_t(layer) * planePixels)));
 }
 
 // The tile's tables (taps and positional encoding as operand bytes) and its staged footprints.
@@ -308,13 +289,13 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
     const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
     const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
 
-    const int stride = mip.strideBytes;
+    const int stride = StrideBytes(mip);
     const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (col.x + row.x);
     const uint8_t* tap10 = tap00 + row.w;
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
     {
-        if (layer < params.numLayers)
+        if (layer < NumLayers(params))
         {
             const uint2 l00 = *reinterpret_cast<const uint2*>(tap00 + layer * 8);
             const uint2 l01 = *reinterpret_cast<const uint2*>(tap00 + stride + layer * 8);
