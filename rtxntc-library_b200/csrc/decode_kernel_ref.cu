@@ -217,7 +217,7 @@ struct RefTileContext
 
 // Builds the tile's lookup tables and stages the latent footprint of both grids in shared memory
 // (`tablesValid`: the tables already hold this tile's values, see PrepareTaps).
-template <bool kFp8>
+template <bool kFp8, int kLayers = 0>
 __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const KernelMip& mip, RefSharedStorage& shared,
     int tileX0, int tileY0, int lane, int warp, bool tablesValid)
 {
@@ -248,8 +248,8 @@ __device__ __forceinline__ void PrepareTileRef(const KernelParams& params, const
             shared.tables.zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
         }
     }
-    PrepareTaps<true>(params, mip, shared.tables.taps, shared.footprintHi, shared.footprintLo, shared.latentTable, tileX0, tileY0,
-        lane, warp, tablesValid);
+    PrepareTaps<true, kLayers>(params, mip, shared.tables.taps, shared.footprintHi, shared.footprintLo, shared.latentTable, tileX0,
+        tileY0, lane, warp, tablesValid);
 }
 
 // Four inputs of one latent layer from the four taps, as two binary16 pairs.
@@ -274,7 +274,7 @@ __device__ __forceinline__ void BlendLayerRef(uint2 l00, uint2 l01, uint2 l10, u
 }
 
 // Inputs 0..15 or 16..31 of one texel (eight binary16 pairs) from the staged footprint of one grid.
-template <bool kFp8>
+template <bool kFp8, int kLayers = 0>
 __device__ __forceinline__ void GatherGridRef(const KernelParams& params, const KernelMip& mip, const RefSharedStorage& shared,
     int grid, int lane, int tileRow, uint32_t* words)
 {
@@ -287,13 +287,13 @@ __device__ __forceinline__ void GatherGridRef(const KernelParams& params, const 
     const __half2 w00 = __floats2half2_rn(f00, f00), w01 = __floats2half2_rn(f01, f01);
     const __half2 w10 = __floats2half2_rn(f10, f10), w11 = __floats2half2_rn(f11, f11);
 
-    const int stride = StrideBytes(mip);
+    const int stride = StrideBytes<kLayers>(mip);
     const uint8_t* tap00 = (grid ? shared.footprintLo : shared.footprintHi) + (col.x + row.x);
     const uint8_t* tap10 = tap00 + row.w;
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
     {
-        if (layer < params.numLayers)
+        if (layer < NumLayers<kLayers>(params))
         {
             const uint2 l00 = *reinterpret_cast<const uint2*>(tap00 + layer * 8);
             const uint2 l01 = *reinterpret_cast<const uint2*>(tap00 + stride + layer * 8);
@@ -326,7 +326,7 @@ __device__ __forceinline__ void SampleLayerRef(const uint16_t* __restrict__ plan
 }
 
 // The 48 network inputs of one texel as 24 binary16 pairs -> its 96-byte row of the A operand.
-template <bool kFp8>
+template <bool kFp8, int kLayers = 0>
 __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const KernelMip& mip, const RefSharedStorage& shared,
     const RefTileContext& ctx, int lane, int tileRow)
 {
@@ -338,8 +338,8 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
 
     if (mip.staged)
     {
-        GatherGridRef<kFp8>(params, mip, shared, 0, lane, tileRow, words);
-        GatherGridRef<kFp8>(params, mip, shared, 1, lane, tileRow, words + 8);
+        GatherGridRef<kFp8, kLayers>(params, mip, shared, 0, lane, tileRow, words);
+        GatherGridRef<kFp8, kLayers>(params, mip, shared, 1, lane, tileRow, words + 8);
     }
     else
     {
@@ -353,13 +353,13 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
         const uint16_t* hi = params.latents + mip.hiOffset;
 #pragma unroll
         for (int layer = 0; layer < 4; ++layer)
-            if (layer < params.numLayers)
+            if (layer < NumLayers<kLayers>(params))
                 SampleLayerRef<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable, words + 2 * layer);
         SetupTaps(u, v, mip.loWidth, mip.loHeight, taps);
         const uint16_t* lo = params.latents + mip.loOffset;
 #pragma unroll
         for (int layer = 0; layer < 4; ++layer)
-            if (layer < params.numLayers)
+            if (layer < NumLayers<kLayers>(params))
                 SampleLayerRef<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable, words + 8 + 2 * layer);
     }
 
@@ -575,7 +575,7 @@ __device__ __forceinline__ void TeardownCtaRef(RefSharedStorage& shared, const R
 // The kernels
 // ---------------------------------------------------------------------------------------------
 
-template <bool kFp8, bool kConvert>
+template <bool kFp8, bool kConvert, int kLayers>
 __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernelRef(const __grid_constant__ KernelParams params)
 {
     extern __shared__ __align__(128) unsigned char dynamicShared[];
@@ -626,7 +626,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
     if (tile < params.totalTiles)
     {
         place = locate(tile, 0);
-        PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
+        PrepareTileRef<kFp8, kLayers>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
         tablesMip = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0) ? place.mipIndex : -1;
         __syncthreads();
     }
@@ -636,7 +636,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
         ctx.tile = tile;
         ctx.x = place.tileX0 + lane;
         ctx.y = place.tileY0 + warp;
-        BuildInputsRef<kFp8>(params, mip, shared, ctx, lane, warp);
+        BuildInputsRef<kFp8, kLayers>(params, mip, shared, ctx, lane, warp);
 
         // layer 0; while the tensor core works on it, prepare the NEXT tile (its tables and
         // footprints replace this tile's, which nobody reads after the barrier inside IssueLayerRef)
@@ -649,7 +649,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
             place = locate(nextTile, place.mipIndex);
             // the tables of the previous tile serve this one too when both lie inside the same mip with invariant tables
             const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
-            PrepareTileRef<kFp8>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, keepsTables && place.mipIndex == tablesMip);
+            PrepareTileRef<kFp8, kLayers>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, keepsTables && place.mipIndex == tablesMip);
             tablesMip = keepsTables ? place.mipIndex : -1;
         }
         ConsumeLayerRef<kFp8, 0, false>(params, ctx, phase, failed);
@@ -1133,7 +1133,7 @@ __device__ __forceinline__ void TeardownCtaRefFp8(RefFp8SharedStorage& shared, c
         TmemFree(ctx.tmemBase, kTmemColumns);
 }
 
-template <bool kConvert>
+template <bool kConvert, int kLayers>
 __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernelRefFp8(const __grid_constant__ KernelParams params)
 {
     extern __shared__ __align__(128) unsigned char dynamicShared[];
@@ -1187,7 +1187,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
     if (tile < params.totalTiles)
     {
         place = locate(tile, 0);
-        PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
+        PrepareTile<true, true, kLayers>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp, false);
         tablesMip = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0) ? place.mipIndex : -1;
         __syncthreads();
     }
@@ -1206,7 +1206,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
                 ctx.rowChunk[chunk * 128] = make_uint4(filler, filler + chunk, filler, filler);
         }
         else
-            BuildInputs<true, true>(params, mip, shared, ctx, lane, warp);
+            BuildInputs<true, true, kLayers>(params, mip, shared, ctx, lane, warp);
 
         aborted = IssueLayerRefFp8<0>(ctx, failed);
         if (aborted)
@@ -1218,7 +1218,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
             // the tables of the previous tile serve this one too when both lie inside the same mip with invariant tables
             const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
             if (!(kAblate & 1))
-                PrepareTile<true, true>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp,
+                PrepareTile<true, true, kLayers>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp,
                     keepsTables && place.mipIndex == tablesMip && !(kAblate & 64));
             tablesMip = keepsTables ? place.mipIndex : -1;
         }
@@ -1348,47 +1348,57 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
 
 } // namespace
 
-cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
+// One kernel, set up for its dynamic shared memory on first use per device (`done`: one bit per device).
+template <typename Kernel>
+cudaError_t LaunchRefKernel(Kernel kernel, std::atomic<unsigned long long>& done, size_t sharedBytes, int threads,
+    const KernelParams& params, int ctas, cudaStream_t stream)
 {
-    static std::atomic<unsigned long long> done[4];
-    auto launch = [&](auto kernel, std::atomic<unsigned long long>& doneMask) -> cudaError_t {
-        int device = 0;
-        cudaError_t err = cudaGetDevice(&device);
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess)
+        return err;
+    const unsigned long long bit = 1ull << (device & 63);
+    if (!(done.load(std::memory_order_acquire) & bit))
+    {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sharedBytes));
         if (err != cudaSuccess)
             return err;
-        const unsigned long long bit = 1ull << (device & 63);
-        if (!(doneMask.load(std::memory_order_acquire) & bit))
-        {
-            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefSharedStorage)));
-            if (err != cudaSuccess)
-                return err;
-            doneMask.fetch_or(bit, std::memory_order_release);
-        }
-        kernel<<<ctas, kRefThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
-        return cudaGetLastError();
-    };
+        done.fetch_or(bit, std::memory_order_release);
+    }
+    kernel<<<ctas, threads, sharedBytes, stream>>>(params);
+    return cudaGetLastError();
+}
+
+cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
+{
+    // fp16 output: kernels compiled for 2, 3 or 4 latent layers and one for any number; the converting
+    // epilogue comes with the general one only
+    static std::atomic<unsigned long long> done[2][5];
+    const int layers = params.convert || params.numLayers < 2 || params.numLayers > 4 ? 0 : params.numLayers;
     if (fp8)
     {
         // FP8 networks take the kernel with 8-bit operands (same bits, four CTAs per SM)
-        auto launchFp8 = [&](auto kernel, std::atomic<unsigned long long>& doneMask) -> cudaError_t {
-            int device = 0;
-            cudaError_t err = cudaGetDevice(&device);
-            if (err != cudaSuccess)
-                return err;
-            const unsigned long long bit = 1ull << (device & 63);
-            if (!(doneMask.load(std::memory_order_acquire) & bit))
-            {
-                err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefFp8SharedStorage)));
-                if (err != cudaSuccess)
-                    return err;
-                doneMask.fetch_or(bit, std::memory_order_release);
-            }
-            kernel<<<ctas, kThreadsPerCta, sizeof(RefFp8SharedStorage), stream>>>(params);
-            return cudaGetLastError();
-        };
-        return params.convert ? launchFp8(DecodeKernelRefFp8<true>, done[3]) : launchFp8(DecodeKernelRefFp8<false>, done[1]);
+        const size_t bytes = sizeof(RefFp8SharedStorage);
+        if (params.convert)
+            return LaunchRefKernel(DecodeKernelRefFp8<true, 0>, done[1][4], bytes, kThreadsPerCta, params, ctas, stream);
+        switch (layers)
+        {
+        case 2: return LaunchRefKernel(DecodeKernelRefFp8<false, 2>, done[1][2], bytes, kThreadsPerCta, params, ctas, stream);
+        case 3: return LaunchRefKernel(DecodeKernelRefFp8<false, 3>, done[1][3], bytes, kThreadsPerCta, params, ctas, stream);
+        case 4: return LaunchRefKernel(DecodeKernelRefFp8<false, 4>, done[1][1], bytes, kThreadsPerCta, params, ctas, stream);
+        default: return LaunchRefKernel(DecodeKernelRefFp8<false, 0>, done[1][0], bytes, kThreadsPerCta, params, ctas, stream);
+        }
     }
-    return params.convert ? launch(DecodeKernelRef<false, true>, done[2]) : launch(DecodeKernelRef<false, false>, done[0]);
+    const size_t bytes = sizeof(RefSharedStorage);
+    if (params.convert)
+        return LaunchRefKernel(DecodeKernelRef<false, true, 0>, done[0][4], bytes, kRefThreadsPerCta, params, ctas, stream);
+    switch (layers)
+    {
+    case 2: return LaunchRefKernel(DecodeKernelRef<false, false, 2>, done[0][2], bytes, kRefThreadsPerCta, params, ctas, stream);
+    case 3: return LaunchRefKernel(DecodeKernelRef<false, false, 3>, done[0][3], bytes, kRefThreadsPerCta, params, ctas, stream);
+    case 4: return LaunchRefKernel(DecodeKernelRef<false, false, 4>, done[0][1], bytes, kRefThreadsPerCta, params, ctas, stream);
+    default: return LaunchRefKernel(DecodeKernelRef<false, false, 0>, done[0][0], bytes, kRefThreadsPerCta, params, ctas, stream);
+    }
 }
 
 cudaError_t LaunchSampleRef(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream)
