@@ -47,7 +47,8 @@
 // construction).  1: the per-tile tables and footprint staging after the first tile; 2: the latent
 // gather and blend (constants are stored instead); 64: the tap tables are rebuilt for every tile; 4: the activation arithmetic of layers 0-2 (the
 // raw accumulator words are stored); 8: the global stores of the epilogue; 16: the tensor-core work
-// (no MMA issue, no wait for it); 32: the tensor-memory loads.
+// (no MMA issue, no wait for it); 32: the tensor-memory loads; 128: the proxy fence before each layer's
+// barrier; 256: a plain barrier instead of the one that also agrees on giving up.
 #ifndef NTCB_ABLATE
 #define NTCB_ABLATE 0
 #endif
@@ -892,9 +893,12 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
 {
     // Makes the A operand visible to the tensor core (async proxy), orders this thread's reads of the
     // previous layer's accumulators before they are overwritten, and agrees on giving up.
-    FenceProxyAsyncShared();
+    if (!(kAblate & 128))
+        FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
-    if (__syncthreads_or(failed))
+    if (kAblate & 256)
+        __syncthreads();
+    else if (__syncthreads_or(failed))
         return 1;
     // The whole issuing warp runs the descriptor arithmetic, on values the compiler can see are the same
     // in every lane (hence the shuffles), and one elected lane hands the work to the tensor core: issued
@@ -1141,12 +1145,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
-#if defined(NTCB_UNIFORM_WARP) && NTCB_UNIFORM_WARP
-    // experiment: the warp index in a form the compiler can see is the same in every lane
-    const int warp = __shfl_sync(0xFFFFFFFFu, tid >> 5, 0);
-#else
     const int warp = tid >> 5;      // = the thread's row of the tile
-#endif
     const int half = warp >> 2;     // the 128-row chain of this thread
 
     int failed = SetupCtaRefFp8(shared, params.network, params.status, params.loadWaitPolls, tid, warp);
