@@ -784,6 +784,27 @@ def run_block_compress_case(side: int) -> int:
         touched = side * side * (24 + (0.5 if block_format in (1, 4) else 1.0))  # every 32-byte sector of the interleaved mip is read
         print("%s of %dx%d (12 interleaved channels): %.3f ms, %.1f Gtexel/s, %.0f GB/s of sectors touched = %.2f of %s HBM peak"
               % (name, side, side, ms, side * side / ms / 1e6, touched / ms / 1e6, touched / ms / 1e6 / peak, source))
+    # BC7: the full search once (it is the offline path), then with the mode buffer made from its own blocks
+    timings = {}
+    blocks = None
+    for name, repeats in (("BC7, full search", 4), ("BC7, mode buffer", 13)):
+        modes = None
+        if blocks is not None:
+            modes = torch.from_numpy(binding.make_bc7_mode_buffer(blocks.cpu().numpy())).cuda()
+        times = []
+        for _ in range(repeats):
+            start.record()
+            result = binding.block_compress(texels, binding.BLOCK_FORMAT_BC7, 2, mode_buffer=modes)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop))
+        if blocks is None:
+            blocks = result
+        else:
+            timings["same"] = bool(torch.equal(result, blocks))
+        ms = float(np.median(times[1:]))
+        print("%s of %dx%d (12 interleaved channels): %.3f ms, %.2f Gtexel/s" % (name, side, side, ms, side * side / ms / 1e6))
+    print("the mode-buffer path reproduces the full search's blocks: %s" % timings.get("same"))
     return 0
 
 
@@ -805,7 +826,7 @@ def main() -> int:
     parser.add_argument("--producers-case", metavar="SIDE", type=int,
                         help="only time latent packing on a SIDE x SIDE x 4 grid and one network quantisation, and exit")
     parser.add_argument("--block-compress-case", metavar="SIDE", type=int,
-                        help="only time BC4 / BC5 / BC1 / BC3 encoding of a SIDE x SIDE 12-channel mip, and exit")
+                        help="only time BC1 - BC5 and BC7 encoding of a SIDE x SIDE 12-channel mip, and exit")
     args = parser.parse_args()
     if args.profile_case:
         return run_profile_case(args.profile_case)

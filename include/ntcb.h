@@ -408,34 +408,58 @@ int ntcb_quantize_network(const NtcbQuantizeNetworkParams* params, void* stream)
 #define NTCB_BLOCK_FORMAT_BC3 3
 #define NTCB_BLOCK_FORMAT_BC4 4
 #define NTCB_BLOCK_FORMAT_BC5 5
+#define NTCB_BLOCK_FORMAT_BC7 7
 
-/* Encodes channels of a decoded mip (fp16, device memory) as BC1 - BC5 blocks in device memory.
+/* Encodes channels of a decoded mip (fp16, device memory) as BC1 - BC5 or BC7 blocks in device memory.
    The CUDA counterpart of the compute pass that IContext::MakeBlockCompressionComputePass describes
    (include/libntc/ntc.h:1050-1100, src/Context.cpp:630-779) and that the reference runs as
-   src/shaders/CompressBC1-5.hlsl through a graphics API; the encoders follow
+   src/shaders/CompressBC1-5.hlsl, CompressBC7.hlsl through a graphics API; the encoders follow
    src/shaders/BlockCompressCommon.hlsli (BC1_EncodeSingleColor, BC1_CompressFast, BC1a_CompressFast,
-   BC2_EncodeAlpha, BC4_CompressFast).  srcLeft / srcTop and widthInBlocks / heightInBlocks mean what
-   srcRect means there (texels outside the mip read as 0 in every component); the destination offset
-   is folded into `deviceBlocks`.  BC6 and BC7: NTCB_ERR_UNSUPPORTED.  The first call of a colour
-   format on a device uploads two 512-byte tables (make it before any stream capture).
-   Queued on `stream`; returns without waiting. */
+   BC2_EncodeAlpha, BC4_CompressFast) and CompressBC7.hlsl.  srcLeft / srcTop and widthInBlocks /
+   heightInBlocks mean what srcRect means there (texels outside the mip read as 0 in every
+   component); the destination offset is folded into `deviceBlocks`.  BC6: NTCB_ERR_UNSUPPORTED.
+
+   BC7 without a mode buffer searches every mode and partition (the reference's slow path, meant for
+   offline use); with `deviceModeBuffer` it encodes each block in the mode and partition the buffer
+   names (the reference's BlockCompressionModeBufferSource::Custom / TextureSet; 9 bits per block as
+   ntcb_make_bc7_mode_buffer lays them out), and writes a block of four coloured squares where the
+   buffer has no entry.  modeMapOffsetX / Y are added to a block's position before the look-up;
+   modeBufferByteOffset must be a multiple of 4.
+
+   The first call of a colour format (BC1 - BC3) on a device uploads two 512-byte tables (make it
+   before any stream capture).  Queued on `stream`; returns without waiting. */
 typedef struct NtcbBlockCompressParams
 {
     const void* deviceMip;   /* decoded texels of one mip */
     int32_t layout;          /* NtcbOutputLayout of deviceMip */
     int32_t width, height, channels; /* of deviceMip */
-    int32_t firstChannel;    /* BC4: the channel; BC5: it and the next; BC1-3: red, then green, blue, alpha */
+    int32_t firstChannel;    /* BC4: the channel; BC5: it and the next; BC1-3, BC7: red, then green, blue, alpha */
     int32_t format;          /* NTCB_BLOCK_FORMAT_* */
     int32_t srcLeft, srcTop; /* texel position of the first block */
     int32_t widthInBlocks, heightInBlocks;
-    int32_t numChannels;     /* BC1-3: channels that feed the block, 1..4 (green and blue then read 0, alpha 1);
-                                0 = 3 for BC1, 4 for BC2 / BC3.  BC4 / BC5: 0 */
-    void* deviceBlocks;      /* 8 (BC1, BC4) or 16 (BC2, BC3, BC5) bytes per block */
+    int32_t numChannels;     /* BC1-3, BC7: channels that feed the block, 1..4 (green and blue then read 0, alpha 1);
+                                0 = 3 for BC1, 4 for BC2 / BC3 / BC7.  BC4 / BC5: 0 */
+    void* deviceBlocks;      /* 8 (BC1, BC4) or 16 (BC2, BC3, BC5, BC7) bytes per block */
     size_t rowPitch;         /* bytes between rows of blocks */
     float alphaThreshold;    /* BC1: texels with alpha <= this are transparent (the reference's default: 1/255) */
     int32_t reserved;
+    /* BC7 only; all zero = full search */
+    const void* deviceModeBuffer;   /* device memory, 4-byte aligned */
+    uint32_t modeBufferByteOffset;
+    uint32_t modeMapWidthInBlocks, modeMapHeightInBlocks; /* size of the block grid the buffer describes */
+    int32_t modeMapOffsetX, modeMapOffsetY;
+    int32_t reserved2;
 } NtcbBlockCompressParams;
 int ntcb_block_compress(const NtcbBlockCompressParams* params, void* stream);
+
+/* Host side of the BC7 mode buffer: ntc::GetBC7ModeBufferSize and ntc::MakeBC7ModeBuffer
+   (include/libntc/ntc.h:1381-1387, src/PublicFunctions.cpp:470-556).  From BC7 blocks (host memory, rows
+   `rowPitch` bytes apart) to the 9-bit-per-block bitmap of their modes and partitions (3 bits mode, 6 bits
+   partition; for modes 4 and 5 the rotation and index selector); the size is rounded up to 4 bytes.  The
+   mode buffer is cleared before it is filled. */
+size_t ntcb_bc7_mode_buffer_size(int widthInBlocks, int heightInBlocks);
+int ntcb_make_bc7_mode_buffer(int widthInBlocks, int heightInBlocks, const void* blockData, size_t blockDataSize,
+                              size_t rowPitch, void* modeBuffer, size_t modeBufferSize);
 
 /* The same for one whole mip of a decompressed texture set (NTCB_ERR_INVALID_STATE before
    ntcb_texture_set_decompress): (width + 3) / 4 by (height + 3) / 4 blocks into device memory,

@@ -96,20 +96,30 @@ OBJECTS="$OBJECTS $OBJ/ref_harness_producers.cu.o"
 "$NVCC" -arch=sm_100 -shared -o "$OUT/libntc_ref.so" $OBJECTS -lcudart_static -lpthread -ldl -lrt
 echo "built $OUT/libntc_ref.so"
 
-# The reference's BC1 - BC5 encoders (compute shaders) as C++ on the CPU: src/shaders/CompressBC1-5.hlsl and
-# BlockCompressCommon.hlsli, passed through oracle/transform_hlsl.py (parameter qualifiers, literal
-# suffixes, attributes - nothing that changes the arithmetic) and compiled against oracle/hlsl_shim.h
-# without contraction, one translation unit per format (oracle/ref_bc_harness.cpp).  No graphics API.
+# The reference's BC1 - BC5 and BC7 encoders (compute shaders) as C++ on the CPU: src/shaders/CompressBC1-5.hlsl,
+# CompressBC7.hlsl and BlockCompressCommon.hlsli, passed through oracle/transform_hlsl.py (parameter qualifiers,
+# literal suffixes, attributes, swizzle spelling - nothing that changes the arithmetic) and compiled against
+# oracle/hlsl_shim.h without contraction, one translation unit per format (oracle/ref_bc_harness.cpp); BC7 twice,
+# with and without its mode buffer, as the reference builds that shader twice.  No graphics API.
 BCGEN="$OUT/bc_gen"
 mkdir -p "$BCGEN"
 python3 "$HERE/transform_hlsl.py" "$REF/src/shaders/BlockCompressCommon.hlsli" "$BCGEN/BlockCompressCommon.hlsli"
 : > "$BCGEN/BindingHelpers.hlsli"   # the binding macros come from the shim
+BC_FLAGS="-std=c++17 -O2 -fPIC -ffp-contract=off -fno-fast-math -fno-strict-aliasing -w"
 BC_OBJECTS=""
-for n in 1 2 3 4 5; do
+for n in 1 2 3 4 5 7; do
     python3 "$HERE/transform_hlsl.py" "$REF/src/shaders/CompressBC$n.hlsl" "$BCGEN/CompressBC$n.hlsl" shader_main
-    "$CXX" -std=c++17 -O2 -fPIC -ffp-contract=off -fno-fast-math -w -I"$HERE" -I"$BCGEN" -I"$REF/include" \
-        -DNTC_BC_SHADER="\"CompressBC$n.hlsl\"" -DNTC_BC_FORMAT=$n -c "$HERE/ref_bc_harness.cpp" -o "$BCGEN/bc$n.o"
-    BC_OBJECTS="$BC_OBJECTS $BCGEN/bc$n.o"
+    if [ $n = 7 ]; then
+        for modes in 0 1; do
+            "$CXX" $BC_FLAGS -I"$HERE" -I"$BCGEN" -I"$REF/include" -DNTC_BC_SHADER="\"CompressBC$n.hlsl\"" -DNTC_BC_FORMAT=$n \
+                -DUSE_MODE_BUFFER=$modes -c "$HERE/ref_bc_harness.cpp" -o "$BCGEN/bc${n}_$modes.o"
+            BC_OBJECTS="$BC_OBJECTS $BCGEN/bc${n}_$modes.o"
+        done
+    else
+        "$CXX" $BC_FLAGS -I"$HERE" -I"$BCGEN" -I"$REF/include" -DNTC_BC_SHADER="\"CompressBC$n.hlsl\"" -DNTC_BC_FORMAT=$n \
+            -c "$HERE/ref_bc_harness.cpp" -o "$BCGEN/bc$n.o"
+        BC_OBJECTS="$BC_OBJECTS $BCGEN/bc$n.o"
+    fi
 done
 "$CXX" -shared -o "$OUT/libntc_ref_bc.so" $BC_OBJECTS
 echo "built $OUT/libntc_ref_bc.so"

@@ -13,41 +13,65 @@
 
 typedef uint32_t uint;
 
+// HLSL's vector<T, N>; vec2 / vec3 / vec4 are its aliases (so a function template over
+// vector<int, C> accepts an int3).
+template <typename T, int N>
+struct vector;
 template <typename T>
-struct vec2;
+using vec1 = vector<T, 1>;
 template <typename T>
-struct vec3;
+using vec2 = vector<T, 2>;
 template <typename T>
-struct vec4;
+using vec3 = vector<T, 3>;
+template <typename T>
+using vec4 = vector<T, 4>;
+
+// One component: converts to and from its scalar, so scalar arithmetic applies to it.
+template <typename T>
+struct vector<T, 1>
+{
+    T x;
+    vector() : x(T()) {}
+    vector(T s) : x(s) {}
+    template <typename U>
+    explicit vector(const vector<U, 1>& o) : x(T(o.x)) {}
+    operator T() const { return x; }
+    T& operator[](int) { return x; }
+    const T& operator[](int) const { return x; }
+};
 
 template <typename T>
-struct vec2
+struct vector<T, 2>
 {
     union
     {
         struct { T x, y; };
         struct { T r, g; };
     };
-    vec2() : x(T()), y(T()) {}
-    vec2(T s) : x(s), y(s) {}
-    vec2(T a, T b) : x(a), y(b) {}
+    vector() : x(T()), y(T()) {}
+    vector(T s) : x(s), y(s) {}
+    vector(T a, T b) : x(a), y(b) {}
     template <typename U>
-    explicit vec2(const vec2<U>& o) : x(T(o.x)), y(T(o.y)) {}
+    explicit vector(const vector<U, 2>& o) : x(T(o.x)), y(T(o.y)) {}
+    T& operator[](int i) { return (&x)[i]; }
+    const T& operator[](int i) const { return (&x)[i]; }
 };
 
 template <typename T>
-struct vec3
+struct vector<T, 3>
 {
     union
     {
         struct { T x, y, z; };
         struct { T r, g, b; };
     };
-    vec3() : x(T()), y(T()), z(T()) {}
-    vec3(T s) : x(s), y(s), z(s) {}
-    vec3(T a, T b_, T c) : x(a), y(b_), z(c) {}
+    vector() : x(T()), y(T()), z(T()) {}
+    vector(T s) : x(s), y(s), z(s) {}
+    vector(T a, T b_, T c) : x(a), y(b_), z(c) {}
     template <typename U>
-    explicit vec3(const vec3<U>& o) : x(T(o.x)), y(T(o.y)), z(T(o.z)) {}
+    explicit vector(const vector<U, 3>& o) : x(T(o.x)), y(T(o.y)), z(T(o.z)) {}
+    T& operator[](int i) { return (&x)[i]; }
+    const T& operator[](int i) const { return (&x)[i]; }
 };
 
 // The first three components of a four-component vector, as HLSL's .rgb swizzle: reads as a vec3,
@@ -67,7 +91,7 @@ struct swizzle3
 };
 
 template <typename T>
-struct vec4
+struct vector<T, 4>
 {
     union
     {
@@ -76,13 +100,15 @@ struct vec4
         swizzle3<T> rgb;
         swizzle3<T> xyz;
     };
-    vec4() : x(T()), y(T()), z(T()), w(T()) {}
-    vec4(T s) : x(s), y(s), z(s), w(s) {}
-    vec4(T a_, T b_, T c, T d) : x(a_), y(b_), z(c), w(d) {}
-    vec4(const vec3<T>& v, T d) : x(v.x), y(v.y), z(v.z), w(d) {}
-    vec4(const vec2<T>& u, const vec2<T>& v) : x(u.x), y(u.y), z(v.x), w(v.y) {}
-    vec4(const vec4& o) : x(o.x), y(o.y), z(o.z), w(o.w) {}
-    vec4& operator=(const vec4& o)
+    vector() : x(T()), y(T()), z(T()), w(T()) {}
+    vector(T s) : x(s), y(s), z(s), w(s) {}
+    vector(T a_, T b_, T c, T d) : x(a_), y(b_), z(c), w(d) {}
+    vector(const vec3<T>& v, T d) : x(v.x), y(v.y), z(v.z), w(d) {}
+    vector(const vec2<T>& u, const vec2<T>& v) : x(u.x), y(u.y), z(v.x), w(v.y) {}
+    vector(const vector& o) : x(o.x), y(o.y), z(o.z), w(o.w) {}
+    template <typename U>
+    explicit vector(const vector<U, 4>& o) : x(T(o.x)), y(T(o.y)), z(T(o.z)), w(T(o.w)) {}
+    vector& operator=(const vector& o)
     {
         x = o.x;
         y = o.y;
@@ -90,6 +116,10 @@ struct vec4
         w = o.w;
         return *this;
     }
+    T& operator[](int i) { return (&x)[i]; }
+    const T& operator[](int i) const { return (&x)[i]; }
+    // a four-component swizzle such as .agbr, spelled by the transform as .swizzle4(3, 1, 2, 0)
+    vector swizzle4(int i0, int i1, int i2, int i3) const { return vector((&x)[i0], (&x)[i1], (&x)[i2], (&x)[i3]); }
 };
 
 typedef vec2<float> float2;
@@ -102,6 +132,7 @@ typedef vec2<uint> uint2;
 typedef vec3<uint> uint3;
 typedef vec4<uint> uint4;
 typedef vec3<bool> bool3;
+typedef vec4<bool> bool4;
 
 // ---- component-wise arithmetic ----------------------------------------------------------------
 #define HLSL_BINARY(op)                                                                                          \
@@ -185,6 +216,53 @@ inline float3 select(const bool3& c, const float3& a, const float3& b)
 {
     return float3(c.x ? a.x : b.x, c.y ? a.y : b.y, c.z ? a.z : b.z);
 }
+
+// ---- more of the same, for the BC7 encoder (src/shaders/CompressBC7.hlsl) ------------------------------
+inline float4 min(const float4& a, const float4& b) { return float4(min(a.x, b.x), min(a.y, b.y), min(a.z, b.z), min(a.w, b.w)); }
+inline float4 max(const float4& a, const float4& b) { return float4(max(a.x, b.x), max(a.y, b.y), max(a.z, b.z), max(a.w, b.w)); }
+inline float4 saturate(const float4& v) { return float4(saturate(v.x), saturate(v.y), saturate(v.z), saturate(v.w)); }
+inline float dot(float a, float b) { return a * b; }
+inline bool4 operator==(const float4& a, float s) { return bool4(a.x == s, a.y == s, a.z == s, a.w == s); }
+inline bool hlsl_or(bool a, bool b) { return a || b; }
+inline bool4 hlsl_or(const bool4& a, const bool4& b) { return bool4(a.x || b.x, a.y || b.y, a.z || b.z, a.w || b.w); }
+inline float select(bool c, float a, float b) { return c ? a : b; }
+inline float4 select(const bool4& c, const float4& a, const float4& b)
+{
+    return float4(c.x ? a.x : b.x, c.y ? a.y : b.y, c.z ? a.z : b.z, c.w ? a.w : b.w);
+}
+inline float3 operator/(const float3& a, uint s) { return a / float3(float(s)); }
+inline float4 operator/(const float4& a, uint s) { return a / float4(float(s)); }
+inline uint countbits(uint v) { return uint(__builtin_popcount(v)); }
+
+// integer vectors with an integer scalar
+#define HLSL_INT_SCALAR(op)                                                                          \
+    inline int3 operator op(const int3& a, int s) { return int3(a.x op s, a.y op s, a.z op s); }      \
+    inline int4 operator op(const int4& a, int s) { return int4(a.x op s, a.y op s, a.z op s, a.w op s); }
+HLSL_INT_SCALAR(+)
+HLSL_INT_SCALAR(*)
+HLSL_INT_SCALAR(>>)
+HLSL_INT_SCALAR(&)
+HLSL_INT_SCALAR(|)
+#undef HLSL_INT_SCALAR
+
+// Thread-group machinery of the BC7 shader's single-mode path, for ONE thread running alone: the
+// harness clears the group-shared counters before every call, so the thread is the only one of its
+// group and of its wave, and the re-ordering hands it back its own block.
+#define groupshared static
+inline void InterlockedAdd(uint& target, uint value, uint& original)
+{
+    original = target;
+    target += value;
+}
+inline uint WaveActiveCountBits(bool) { return 1; }
+inline bool WaveIsFirstLane() { return true; }
+inline uint WaveReadLaneFirst(uint v) { return v; }
+inline uint WavePrefixCountBits(bool) { return 0; }
+inline void GroupMemoryBarrierWithGroupSync() {}
+
+// a scalar array seen as an array of one-component vectors (same storage)
+template <typename T>
+inline const vector<T, 1>* hlsl_as_vec1(const T* p) { return reinterpret_cast<const vector<T, 1>*>(p); }
 
 // ---- resources ------------------------------------------------------------------------------------
 // A read-only four-component texture: texels outside the image read as zero in every component.

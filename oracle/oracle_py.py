@@ -291,6 +291,38 @@ def reference_block_compress(block_format: int, rgba: np.ndarray, alpha_threshol
 
 
 
+def reference_block_compress_bc7(rgba: np.ndarray, mode_buffer: Optional[np.ndarray] = None, mode_buffer_byte_offset: int = 0,
+                                 mode_map_size=None, mode_map_offset=(0, 0), src_left: int = 0, src_top: int = 0,
+                                 width_in_blocks: Optional[int] = None, height_in_blocks: Optional[int] = None) -> np.ndarray:
+    """Runs the reference's own CompressBC7.hlsl on the CPU over an RGBA binary32 image [h][w][4]: the
+    full search, or with `mode_buffer` (uint8, the layout ntc::MakeBC7ModeBuffer writes) the shader built
+    with USE_MODE_BUFFER.  Returns uint8 [blocks_y][blocks_x][16]."""
+    global _ref_bc
+    if _ref_bc is None:
+        _ref_bc = ctypes.CDLL(REF_BC_LIB)
+    rgba = np.ascontiguousarray(rgba, dtype=np.float32)
+    h, w, four = rgba.shape
+    assert four == 4
+    bw = (w - src_left + 3) // 4 if width_in_blocks is None else width_in_blocks
+    bh = (h - src_top + 3) // 4 if height_in_blocks is None else height_in_blocks
+    out = np.zeros((bh, bw, 16), dtype=np.uint8)
+    if mode_buffer is None:
+        function = _ref_bc.ntcref_block_compress_bc7
+        function.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_float, ctypes.c_void_p]
+        function(rgba.ctypes.data, w, h, src_left, src_top, bw, bh, 0.0, out.ctypes.data)
+        return out
+    # the shader reads whole 32-bit words, the second one of an entry also past the last entry's byte
+    words = np.zeros((mode_buffer.nbytes + 3) // 4 + 2, dtype=np.uint32)
+    words.view(np.uint8)[:mode_buffer.nbytes] = np.ascontiguousarray(mode_buffer, dtype=np.uint8).ravel()
+    map_w, map_h = mode_map_size if mode_map_size is not None else (bw, bh)
+    function = _ref_bc.ntcref_block_compress_bc7_modes
+    function.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32,
+                                                                 ctypes.c_uint32, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    function(rgba.ctypes.data, w, h, src_left, src_top, bw, bh, words.ctypes.data, mode_buffer_byte_offset, map_w, map_h,
+             mode_map_offset[0], mode_map_offset[1], out.ctypes.data)
+    return out
+
+
 def reference_available() -> bool:
     return os.path.exists(REF_LIB)
 
@@ -313,6 +345,11 @@ def reference_lib(path: str = REF_LIB):
                                              ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t,
                                              ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_void_p]
         lib.ntcref_close.argtypes = [ctypes.c_void_p]
+        if hasattr(lib, "ntcref_make_bc7_mode_buffer"):
+            lib.ntcref_bc7_mode_buffer_size.argtypes = [ctypes.c_int, ctypes.c_int]
+            lib.ntcref_bc7_mode_buffer_size.restype = ctypes.c_size_t
+            lib.ntcref_make_bc7_mode_buffer.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                                                        ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t]
         lib.ntcref_producers_last_error.restype = ctypes.c_char_p
         lib.ntcref_pack_latents.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p,
                                             ctypes.c_size_t, ctypes.c_void_p]
@@ -329,6 +366,18 @@ def reference_probe(container: bytes) -> List[int]:
     if rc != 0:
         raise RuntimeError("reference loader rejected the container: %s" % lib.ntcref_last_error().decode())
     return list(out)
+
+
+def reference_make_bc7_mode_buffer(blocks: np.ndarray) -> np.ndarray:
+    """ntc::MakeBC7ModeBuffer of the reference library on uint8 [blocks_y][blocks_x][16]."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    bh, bw = blocks.shape[:2]
+    lib = reference_lib()
+    out = np.zeros(lib.ntcref_bc7_mode_buffer_size(bw, bh), dtype=np.uint8)
+    rc = lib.ntcref_make_bc7_mode_buffer(bw, bh, blocks.ctypes.data, blocks.nbytes, bw * 16, out.ctypes.data, out.nbytes)
+    if rc != 0:
+        raise RuntimeError("MakeBC7ModeBuffer failed: %s" % lib.ntcref_last_error().decode())
+    return out
 
 
 def reference_pack_latents(latents: np.ndarray, width: int, height: int, num_layers: int, latent_stride: int) -> np.ndarray:

@@ -226,4 +226,21 @@ void ntcref_close(void* opaque)
     delete handle;
 }
 
+// ntc::GetBC7ModeBufferSize / ntc::MakeBC7ModeBuffer (host functions; the mode buffer must arrive zeroed, as
+// the reference's own caller hands it over: src/TextureMetadata.cpp:125-129).
+size_t ntcref_bc7_mode_buffer_size(int widthInBlocks, int heightInBlocks)
+{
+    return ntc::GetBC7ModeBufferSize(widthInBlocks, heightInBlocks);
+}
+
+int ntcref_make_bc7_mode_buffer(int widthInBlocks, int heightInBlocks, void const* blockData, size_t blockDataSize,
+    size_t rowPitch, void* modeBuffer, size_t modeBufferSize)
+{
+    ntc::Status const status = ntc::MakeBC7ModeBuffer(widthInBlocks, heightInBlocks, blockData, blockDataSize, rowPitch,
+        modeBuffer, modeBufferSize);
+    if (status != ntc::Status::Ok)
+        SetError("MakeBC7ModeBuffer", status);
+    return int(status);
+}
+
 } // extern "C"

@@ -9,6 +9,8 @@ changing what they compute:
     expression it appears in (binary32 here), in C++ it would turn the whole expression into binary64;
   * loop attributes ([unroll], [loop], ...) and the entry point's [numthreads] / semantics go;
   * the boolean intrinsic `or(` becomes hlsl_or( (`or` is an operator keyword in C++);
+  * four-component swizzles (`.agbr`) become `.swizzle4(3, 1, 2, 0)`, and a scalar array passed where
+    the callee is instantiated for one-component vectors (`<1>(alphaPixels`) is passed as such;
   * the constant buffer, declared `static const` for C++ in the source, becomes an ordinary global
     that the harness fills in.
 Nothing of the output is stored in the repository: it is written under oracle/_ref/.
@@ -29,6 +31,8 @@ def transform(text: str, entry: str) -> str:
     # unsuffixed floating literals -> binary32 (not inside identifiers or hexadecimal numbers)
     text = re.sub(r"(?<![\w.])(\d+\.\d*(?:[eE][+-]?\d+)?|\.\d+(?:[eE][+-]?\d+)?|\d+[eE][+-]?\d+)(?![\w.])", r"\1f", text)
     text = re.sub(r"\bor\(", "hlsl_or(", text)
+    text = re.sub(r"\.([rgba]{4})\b", lambda m: ".swizzle4(%s)" % ", ".join(str("rgba".index(ch)) for ch in m.group(1)), text)
+    text = re.sub(r"<1>\((\w+Pixels)\b", r"<1>(hlsl_as_vec1(\1)", text)
     text = text.replace("static const NtcBlockCompressConstants g_Const;", "NtcBlockCompressConstants g_Const;")
     text = re.sub(r"\bvoid\s+main\s*\(", "void %s(" % entry, text)
     return text

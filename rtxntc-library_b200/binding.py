@@ -204,6 +204,10 @@ def lib():
                                              ctypes.c_void_p, ctypes.c_void_p]
         handle.ntcb_quantize_network.argtypes = [ctypes.POINTER(QuantizeNetworkParams), ctypes.c_void_p]
         handle.ntcb_block_compress.argtypes = [ctypes.POINTER(BlockCompressParams), ctypes.c_void_p]
+        handle.ntcb_bc7_mode_buffer_size.argtypes = [ctypes.c_int, ctypes.c_int]
+        handle.ntcb_bc7_mode_buffer_size.restype = ctypes.c_size_t
+        handle.ntcb_make_bc7_mode_buffer.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t,
+                                                     ctypes.c_void_p, ctypes.c_size_t]
         handle.ntcb_texture_set_block_compress.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                            ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t]
         handle.ntcb_texture_set_device_mip.argtypes = [
@@ -388,6 +392,7 @@ def quantize_network(weights, biases, weight_mode: int, output_scale=None, outpu
 
 
 BLOCK_FORMAT_BC1, BLOCK_FORMAT_BC2, BLOCK_FORMAT_BC3, BLOCK_FORMAT_BC4, BLOCK_FORMAT_BC5 = 1, 2, 3, 4, 5
+BLOCK_FORMAT_BC7 = 7
 
 
 class BlockCompressParams(ctypes.Structure):
@@ -396,16 +401,38 @@ class BlockCompressParams(ctypes.Structure):
                 ("format", ctypes.c_int32), ("srcLeft", ctypes.c_int32), ("srcTop", ctypes.c_int32),
                 ("widthInBlocks", ctypes.c_int32), ("heightInBlocks", ctypes.c_int32), ("numChannels", ctypes.c_int32),
                 ("deviceBlocks", ctypes.c_void_p), ("rowPitch", ctypes.c_size_t), ("alphaThreshold", ctypes.c_float),
-                ("reserved", ctypes.c_int32)]
+                ("reserved", ctypes.c_int32), ("deviceModeBuffer", ctypes.c_void_p),
+                ("modeBufferByteOffset", ctypes.c_uint32), ("modeMapWidthInBlocks", ctypes.c_uint32),
+                ("modeMapHeightInBlocks", ctypes.c_uint32), ("modeMapOffsetX", ctypes.c_int32),
+                ("modeMapOffsetY", ctypes.c_int32), ("reserved2", ctypes.c_int32)]
+
+
+def bc7_mode_buffer_size(width_in_blocks: int, height_in_blocks: int) -> int:
+    return int(lib().ntcb_bc7_mode_buffer_size(width_in_blocks, height_in_blocks))
+
+
+def make_bc7_mode_buffer(blocks: np.ndarray, row_pitch: Optional[int] = None) -> np.ndarray:
+    """The 9-bit-per-block mode bitmap of BC7 blocks (uint8 [blocks_y][blocks_x][16], or rows of `row_pitch`
+    bytes): uint8 of bc7_mode_buffer_size() bytes (ntc::MakeBC7ModeBuffer)."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    bh, bw = blocks.shape[0], blocks.shape[1] if blocks.ndim == 3 else blocks.shape[1] // 16
+    if blocks.ndim == 3:
+        row_pitch = bw * 16
+    out = np.full(bc7_mode_buffer_size(bw, bh), 0xAA, dtype=np.uint8)  # the call clears it
+    check(lib().ntcb_make_bc7_mode_buffer(bw, bh, blocks.ctypes.data, blocks.nbytes, row_pitch, out.ctypes.data, out.nbytes))
+    return out
 
 
 def block_compress(texels, block_format: int, first_channel: int = 0, layout: int = LAYOUT_INTERLEAVED,
                    width: Optional[int] = None, height: Optional[int] = None, channels: Optional[int] = None,
                    src_left: int = 0, src_top: int = 0, width_in_blocks: Optional[int] = None,
-                   height_in_blocks: Optional[int] = None, num_channels: int = 0, alpha_threshold: float = 1.0 / 255.0):
-    """BC1 - BC5 encoding of decoded texels the caller holds: `texels` is a CUDA float16 tensor,
+                   height_in_blocks: Optional[int] = None, num_channels: int = 0, alpha_threshold: float = 1.0 / 255.0,
+                   mode_buffer=None, mode_buffer_byte_offset: int = 0, mode_map_size=None, mode_map_offset=(0, 0)):
+    """BC1 - BC5 and BC7 encoding of decoded texels the caller holds: `texels` is a CUDA float16 tensor,
     [height][width][channels] for the interleaved layout (sizes then come from its shape).  Returns a
-    CUDA uint8 tensor [blocks_y][blocks_x][8 or 16]."""
+    CUDA uint8 tensor [blocks_y][blocks_x][8 or 16].  BC7: `mode_buffer` (a CUDA uint8 tensor laid out as
+    make_bc7_mode_buffer does, for a block grid of `mode_map_size` = (width, height) in blocks, default the
+    destination's) selects the one-mode-per-block path."""
     import torch
 
     if layout == LAYOUT_INTERLEAVED and width is None:
@@ -422,6 +449,11 @@ def block_compress(texels, block_format: int, first_channel: int = 0, layout: in
     params.deviceBlocks = out.data_ptr()
     params.rowPitch = bw * block_bytes
     params.numChannels, params.alphaThreshold = num_channels, alpha_threshold
+    if mode_buffer is not None:
+        params.deviceModeBuffer = mode_buffer.data_ptr()
+        params.modeBufferByteOffset = mode_buffer_byte_offset
+        params.modeMapWidthInBlocks, params.modeMapHeightInBlocks = mode_map_size if mode_map_size is not None else (bw, bh)
+        params.modeMapOffsetX, params.modeMapOffsetY = mode_map_offset
     with torch.cuda.device(texels.device):
         stream = torch.cuda.current_stream(texels.device).cuda_stream
         check(lib().ntcb_block_compress(ctypes.byref(params), ctypes.c_void_p(stream)))

@@ -21,6 +21,7 @@
 
 #include <mutex>
 
+#include "block_compress.h"
 #include "error.h"
 #include "ntcb.h"
 
@@ -257,45 +258,6 @@ __device__ uint2 EncodeBc4(const float (&pixels)[16])
         best = bestSix;
     const uint64_t bits = uint64_t(best.alpha0) | (uint64_t(best.alpha1) << 8) | (best.indices << 16);
     return make_uint2(uint32_t(bits), uint32_t(bits >> 32));
-}
-
-struct BlockCompressArguments
-{
-    const __half* texels;
-    int layout, width, height, channels, firstChannel;
-    int srcLeft, srcTop, widthInBlocks, heightInBlocks, formatChannels;
-    uint8_t* blocks;
-    size_t rowPitch;
-};
-
-// A texel outside the mip reads as 0, as an out-of-range texture load does.
-__device__ __forceinline__ float LoadChannel(const BlockCompressArguments& args, int x, int y, int channel)
-{
-    if (x >= args.width || y >= args.height)
-        return 0.f;
-    const size_t w = size_t(args.width), c = size_t(args.channels);
-    const size_t index = args.layout == NTCB_LAYOUT_INTERLEAVED
-        ? (size_t(y) * w + size_t(x)) * c + size_t(channel)
-        : size_t(y) * w * c + size_t(channel & ~1) * w + 2 * size_t(x) + size_t(channel & 1);
-    return __half2float(args.texels[index]);
-}
-
-__device__ __forceinline__ __half LoadHalf(const BlockCompressArguments& args, int x, int y, int channel)
-{
-    const size_t w = size_t(args.width), c = size_t(args.channels);
-    const size_t index = args.layout == NTCB_LAYOUT_INTERLEAVED
-        ? (size_t(y) * w + size_t(x)) * c + size_t(channel)
-        : size_t(y) * w * c + size_t(channel & ~1) * w + 2 * size_t(x) + size_t(channel & 1);
-    return args.texels[index];
-}
-
-// Channels `channel` (even) and `channel + 1` of one texel as one word; needs an even channel count.
-__device__ __forceinline__ uint32_t LoadPair(const BlockCompressArguments& args, int x, int y, int channel)
-{
-    const size_t w = size_t(args.width), c = size_t(args.channels);
-    const size_t index = args.layout == NTCB_LAYOUT_INTERLEAVED ? (size_t(y) * w + size_t(x)) * c + size_t(channel)
-                                                                 : size_t(y) * w * c + size_t(channel) * w + 2 * size_t(x);
-    return *reinterpret_cast<const uint32_t*>(args.texels + index);
 }
 
 // One thread per 4x4 block and channel: BC5 is two BC4 blocks side by side, encoded by two threads
@@ -920,12 +882,18 @@ extern "C" int ntcb_block_compress(const NtcbBlockCompressParams* params, void* 
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     const int format = params->format;
-    if (format < NTCB_BLOCK_FORMAT_BC1 || format > NTCB_BLOCK_FORMAT_BC5)
+    if (format < NTCB_BLOCK_FORMAT_BC1 || format > NTCB_BLOCK_FORMAT_BC7 || format == 6)
     {
-        SetError("dstFormat (%d) is not supported: BC1 to BC5 (%d to %d) are.", format, NTCB_BLOCK_FORMAT_BC1, NTCB_BLOCK_FORMAT_BC5);
-        return format == 6 || format == 7 ? NTCB_ERR_UNSUPPORTED : NTCB_ERR_OUT_OF_RANGE;
+        SetError("dstFormat (%d) is not supported: BC1 to BC5 (%d to %d) and BC7 (%d) are.", format, NTCB_BLOCK_FORMAT_BC1,
+            NTCB_BLOCK_FORMAT_BC5, NTCB_BLOCK_FORMAT_BC7);
+        return format == 6 ? NTCB_ERR_UNSUPPORTED : NTCB_ERR_OUT_OF_RANGE;
     }
-    const bool color = format <= NTCB_BLOCK_FORMAT_BC3;
+    if (format != NTCB_BLOCK_FORMAT_BC7 && params->deviceModeBuffer)
+    {
+        SetError("Mode buffer can only be used with BC7 compression");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    const bool color = format <= NTCB_BLOCK_FORMAT_BC3 || format == NTCB_BLOCK_FORMAT_BC7;
     // channels that feed a block: fixed for BC4 / BC5; red, green, blue[, alpha] for the colour formats
     const int natural = format == NTCB_BLOCK_FORMAT_BC4 ? 1 : format == NTCB_BLOCK_FORMAT_BC5 ? 2 : format == NTCB_BLOCK_FORMAT_BC1 ? 3 : 4;
     const int formatChannels = params->numChannels == 0 ? natural : params->numChannels;
@@ -983,6 +951,8 @@ extern "C" int ntcb_block_compress(const NtcbBlockCompressParams* params, void* 
     args.rowPitch = params->rowPitch;
 
     const cudaStream_t cudaStream = static_cast<cudaStream_t>(stream);
+    if (format == NTCB_BLOCK_FORMAT_BC7)
+        return LaunchBlockCompressBc7(*params, args, cudaStream);
     const dim3 grid(unsigned(params->widthInBlocks + 15) / 16, unsigned(params->heightInBlocks + 7) / 8, color ? 1u : unsigned(formatChannels));
     if (!color)
         BlockCompressKernel<<<grid, 128, 0, cudaStream>>>(args);

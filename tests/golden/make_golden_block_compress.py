@@ -1,6 +1,6 @@
 #!/usr/bin/env python
-"""Generates tests/golden/block_compress_ref.npz: BC1 - BC5 blocks produced by the REFERENCE'S OWN
-shader source (src/shaders/CompressBC1-5.hlsl, BlockCompressCommon.hlsli) compiled for the CPU by
+"""Generates tests/golden/block_compress_ref.npz: BC1 - BC5 and BC7 blocks produced by the REFERENCE'S OWN
+shader source (src/shaders/CompressBC1-5.hlsl, CompressBC7.hlsl, BlockCompressCommon.hlsli) compiled for the CPU by
 oracle/build_ref.sh (oracle/_ref/libntc_ref_bc.so), over small seeded images.  Run where the
 reference sources are present; the fixture then pins the CPU restatement and the CUDA kernels
 wherever the tests run.
@@ -47,6 +47,32 @@ def rgba_for(block_format: int, texels: np.ndarray) -> np.ndarray:
     return rgba
 
 
+PARTITION_MASK = (15, 63, 63, 63, 7, 3, 0, 63)  # what the partition field of each BC7 mode can hold
+
+
+def bc7_mode_entries(blocks_y: int, blocks_x: int, seed: int) -> np.ndarray:
+    """A mode-buffer entry (mode << 6 | partition) per block: every mode, random partitions (for modes 4
+    and 5: rotation and index selector), a few blocks without an entry (0) and mode 0, partition 0."""
+    rng = np.random.default_rng(seed)
+    mode = rng.integers(0, 8, (blocks_y, blocks_x))
+    partition = np.array([[rng.integers(0, PARTITION_MASK[m] + 1) for m in row] for row in mode])
+    entries = (mode << 6 | partition).astype(np.uint32)
+    entries[0, 0] = 0x1BF         # how mode 0, partition 0 is stored
+    entries[1, 1::5] = 0          # nothing stored: the shader writes its four-squares block
+    return entries
+
+
+def pack_mode_entries(entries: np.ndarray) -> np.ndarray:
+    """9 bits per entry, entry k at bit 9 k, little-endian, rounded up to whole 32-bit words."""
+    flat = entries.ravel()
+    bits = np.zeros(((flat.size * 9 + 31) // 32) * 4, dtype=np.uint8)
+    for k, entry in enumerate(int(e) for e in flat):
+        byte, shift = (k * 9) // 8, (k * 9) % 8
+        bits[byte] |= (entry << shift) & 0xFF
+        bits[byte + 1] |= (entry >> (8 - shift)) & 0xFF
+    return bits
+
+
 def main() -> int:
     if not oracle_py.reference_bc_available():
         print("oracle/_ref/libntc_ref_bc.so is not built (oracle/build_ref.sh)", file=sys.stderr)
@@ -62,6 +88,26 @@ def main() -> int:
         arrays["bc4_window_" + name] = oracle_py.reference_block_compress(4, rgba_for(4, texels), src_left=3, src_top=5,
                                                                           width_in_blocks=13, height_in_blocks=8)
         arrays["bc1_opaque_" + name] = oracle_py.reference_block_compress(1, rgba_for(1, texels), alpha_threshold=-1.0)
+        # BC7: the full search on the image as it is and with alpha 1 (only then the three-channel modes
+        # compete), and the one-mode-per-block path on seeded mode buffers, also through a window of a
+        # larger mode map
+        rgba = rgba_for(7, texels)
+        opaque = rgba.copy()
+        opaque[..., 3] = 1.0
+        arrays["bc7_" + name] = oracle_py.reference_block_compress_bc7(rgba)
+        arrays["bc7_opaque_" + name] = oracle_py.reference_block_compress_bc7(opaque)
+        blocks_y, blocks_x = arrays["bc7_" + name].shape[:2]
+        modes = pack_mode_entries(bc7_mode_entries(blocks_y, blocks_x, seed=len(arrays)))
+        arrays["bc7_modebuffer_" + name] = modes
+        arrays["bc7_modes_" + name] = oracle_py.reference_block_compress_bc7(rgba, mode_buffer=modes)
+        wide = pack_mode_entries(bc7_mode_entries(blocks_y + 3, blocks_x + 5, seed=len(arrays)))
+        arrays["bc7_widemodebuffer_" + name] = wide
+        arrays["bc7_window_" + name] = oracle_py.reference_block_compress_bc7(
+            rgba, mode_buffer=wide, mode_map_size=(blocks_x + 5, blocks_y + 3), mode_map_offset=(4, 2), src_left=3, src_top=5,
+            width_in_blocks=blocks_x, height_in_blocks=blocks_y - 1)
+        # the mode bitmap the reference's host function extracts from its own blocks
+        if oracle_py.reference_available():
+            arrays["bc7_extracted_" + name] = oracle_py.reference_make_bc7_mode_buffer(arrays["bc7_opaque_" + name])
     np.savez_compressed(os.path.join(HERE, "block_compress_ref.npz"), **arrays)
     print("wrote %d arrays" % len(arrays))
     return 0

@@ -325,8 +325,16 @@ def test_arguments_are_checked():
     params.deviceMip, params.deviceBlocks = 4096, 8192  # never dereferenced: the checks come first
     params.layout, params.width, params.height, params.channels = binding.LAYOUT_INTERLEAVED, 8, 8, 2
     params.widthInBlocks, params.heightInBlocks, params.rowPitch = 2, 2, 16
-    params.format = 7
-    assert lib.ntcb_block_compress(params, None) == -5  # BC7: a valid format of the reference, not built here
+    params.format = 6
+    assert lib.ntcb_block_compress(params, None) == -5  # BC6: a valid format of the reference, not built here
+    params.format, params.deviceModeBuffer = binding.BLOCK_FORMAT_BC4, 4096
+    assert lib.ntcb_block_compress(params, None) == -1 and b"Mode buffer" in lib.ntcb_last_error()
+    params.format, params.rowPitch, params.numChannels = binding.BLOCK_FORMAT_BC7, 32, 2
+    assert lib.ntcb_block_compress(params, None) == -1 and b"modeMapWidthInBlocks" in lib.ntcb_last_error()
+    params.modeMapWidthInBlocks = params.modeMapHeightInBlocks = 2
+    params.deviceModeBuffer = 4097
+    assert lib.ntcb_block_compress(params, None) == -1 and b"aligned" in lib.ntcb_last_error()
+    params.deviceModeBuffer, params.rowPitch, params.numChannels = None, 16, 0
     params.format, params.numChannels = binding.BLOCK_FORMAT_BC1, 5
     assert lib.ntcb_block_compress(params, None) == -9 and b"numChannels" in lib.ntcb_last_error()
     params.numChannels = 0
@@ -338,6 +346,110 @@ def test_arguments_are_checked():
     assert lib.ntcb_block_compress(params, None) == -1 and b"rowPitch" in lib.ntcb_last_error()
     params.format, params.rowPitch, params.srcLeft = binding.BLOCK_FORMAT_BC4, 16, -4
     assert lib.ntcb_block_compress(params, None) == -9 and b"srcLeft" in lib.ntcb_last_error()
+
+
+# ---------------------------------------------------------------------------------------------
+# BC7: mode buffers (host), then the kernels against the reference's shader source
+# ---------------------------------------------------------------------------------------------
+
+def _entries_of(mode_buffer: np.ndarray, count: int) -> np.ndarray:
+    """The 9-bit entries of a mode buffer, unpacked in numpy."""
+    bits = np.unpackbits(np.asarray(mode_buffer, dtype=np.uint8), bitorder="little")[:count * 9].reshape(count, 9)
+    return (bits.astype(np.uint32) << np.arange(9, dtype=np.uint32)).sum(axis=1)
+
+
+@pytest.mark.parametrize("name", PIN_IMAGES)
+def test_bc7_mode_buffer_is_what_the_reference_extracts(pinned, name):
+    """ntcb_make_bc7_mode_buffer against ntc::MakeBC7ModeBuffer on the blocks of the reference's full
+    search, and on the blocks its one-mode-per-block path wrote: those carry the mode and partition the
+    mode buffer asked for, so extracting them gives the mode buffer back."""
+    blocks = pinned["bc7_opaque_" + name]
+    assert np.array_equal(binding.make_bc7_mode_buffer(blocks), pinned["bc7_extracted_" + name])
+    assert binding.bc7_mode_buffer_size(blocks.shape[1], blocks.shape[0]) == pinned["bc7_extracted_" + name].nbytes
+    asked = _entries_of(pinned["bc7_modebuffer_" + name], blocks.shape[0] * blocks.shape[1])
+    got = _entries_of(binding.make_bc7_mode_buffer(pinned["bc7_modes_" + name]), asked.size)
+    stored = asked != 0
+    assert stored.sum() > 100 and np.array_equal(got[stored], asked[stored])
+    # blocks without an entry: the shader's four coloured squares
+    missing = pinned["bc7_modes_" + name].reshape(-1, 16)[~stored]
+    assert len(missing) and all(bytes(b) == bytes.fromhex("0400f80000f001001f00f03f00009e1f") for b in missing)
+
+
+def test_bc7_mode_buffer_on_random_blocks_and_its_checks(oracle):
+    rng = np.random.default_rng(3)
+    blocks = rng.integers(0, 256, (9, 13, 16), dtype=np.uint8)
+    blocks[0, 0, :4] = 0            # no mode bit in the first word: read as mode 7
+    blocks[0, 1, :4] = (1, 0, 0, 0)  # mode 0, partition 0: stored as 0x1bf
+    ours = binding.make_bc7_mode_buffer(blocks)
+    entries = _entries_of(ours, 9 * 13)
+    assert entries[0] >> 6 == 7 and entries[1] == 0x1BF and ours.nbytes == ((9 * 13 * 9 + 31) // 32) * 4
+    if oracle.reference_available():
+        assert np.array_equal(ours, oracle.reference_make_bc7_mode_buffer(blocks))
+    lib = binding.lib()
+    out = np.zeros(ours.nbytes, dtype=np.uint8)
+    call = lambda *a: lib.ntcb_make_bc7_mode_buffer(*a)  # noqa: E731
+    assert call(13, 9, None, blocks.nbytes, 13 * 16, out.ctypes.data, out.nbytes) == -1
+    assert call(13, 9, blocks.ctypes.data, blocks.nbytes, 13 * 16, None, out.nbytes) == -1
+    assert call(13, 9, blocks.ctypes.data, blocks.nbytes, 13 * 16 - 8, out.ctypes.data, out.nbytes) == -1 and b"rowPitch" in lib.ntcb_last_error()
+    assert call(13, 9, blocks.ctypes.data, blocks.nbytes - 1, 13 * 16, out.ctypes.data, out.nbytes) == -1 and b"block data" in lib.ntcb_last_error()
+    assert call(13, 9, blocks.ctypes.data, blocks.nbytes, 13 * 16, out.ctypes.data, out.nbytes - 4) == -1 and b"mode buffer" in lib.ntcb_last_error()
+    assert call(0, 9, blocks.ctypes.data, blocks.nbytes, 13 * 16, out.ctypes.data, out.nbytes) == -9
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", PIN_IMAGES)
+def test_bc7_kernels_reproduce_the_reference_shader_source(pinned, name):
+    """Both BC7 kernels against what src/shaders/CompressBC7.hlsl computed on the same texels: the full
+    search (every mode wins somewhere in these images) and the mode-buffer path (every mode, seeded
+    partitions, missing entries, a window into a larger mode map)."""
+    import torch
+
+    texels = torch.from_numpy(pinned["image_" + name]).cuda()
+    assert np.array_equal(binding.block_compress(texels, 7).cpu().numpy(), pinned["bc7_" + name])
+    assert np.array_equal(binding.block_compress(texels, 7, num_channels=3).cpu().numpy(), pinned["bc7_opaque_" + name])
+    modes = torch.from_numpy(pinned["bc7_modebuffer_" + name]).cuda()
+    assert np.array_equal(binding.block_compress(texels, 7, mode_buffer=modes).cpu().numpy(), pinned["bc7_modes_" + name])
+    blocks_y, blocks_x = pinned["bc7_" + name].shape[:2]
+    wide = torch.from_numpy(pinned["bc7_widemodebuffer_" + name]).cuda()
+    window = binding.block_compress(texels, 7, mode_buffer=wide, mode_map_size=(blocks_x + 5, blocks_y + 3), mode_map_offset=(4, 2),
+                                    src_left=3, src_top=5, width_in_blocks=blocks_x, height_in_blocks=blocks_y - 1)
+    assert np.array_equal(window.cpu().numpy(), pinned["bc7_window_" + name])
+
+
+@pytest.mark.gpu
+def test_bc7_kernels_against_the_live_shader_source_on_larger_images(oracle):
+    """Images of several CTAs (a CTA covers 32 x 8 blocks), both layouts, channels taken from the middle of a
+    wider mip, against the reference's shader source run on the CPU on the same texels."""
+    import sys
+
+    import torch
+
+    sys.path.insert(0, os.path.dirname(GOLDEN))
+    from make_golden_block_compress import bc7_mode_entries, pack_mode_entries
+
+    if not oracle.reference_bc_available():
+        pytest.skip("oracle/_ref/libntc_ref_bc.so is not built")
+    rng = np.random.default_rng(11)
+    for trial, (h, w, channels, first) in enumerate([(70, 150, 4, 0), (37, 261, 6, 1), (132, 64, 8, 2)]):
+        base = np.clip(rng.random((1, 1, channels)) + (0.05 + 0.2 * trial) * rng.standard_normal((h, w, channels)), 0, 1)
+        base[..., first + 3] = np.where(rng.random((h, w)) < 0.7, 1.0, rng.random((h, w)))
+        texels = base.astype(np.float16)
+        rgba = np.ascontiguousarray(texels[..., first:first + 4].astype(np.float32))
+        bh, bw = (h + 3) // 4, (w + 3) // 4
+        modes = pack_mode_entries(bc7_mode_entries(bh, bw, seed=trial))
+        want_full = oracle.reference_block_compress_bc7(rgba)
+        want_modes = oracle.reference_block_compress_bc7(rgba, mode_buffer=modes)
+        device_modes = torch.from_numpy(modes).cuda()
+        for layout in (binding.LAYOUT_INTERLEAVED, binding.LAYOUT_PLANAR_PAIRS):
+            if layout == binding.LAYOUT_PLANAR_PAIRS:
+                source = torch.from_numpy(np.ascontiguousarray(
+                    texels.reshape(h, w, channels // 2, 2).transpose(0, 2, 1, 3))).cuda()
+            else:
+                source = torch.from_numpy(texels).cuda()
+            common = dict(first_channel=first, layout=layout, width=w, height=h, channels=channels, num_channels=4)
+            assert np.array_equal(binding.block_compress(source, 7, **common).cpu().numpy(), want_full), (trial, layout)
+            assert np.array_equal(binding.block_compress(source, 7, mode_buffer=device_modes, **common).cpu().numpy(), want_modes), \
+                (trial, layout)
 
 
 # ---------------------------------------------------------------------------------------------
