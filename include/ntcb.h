@@ -279,6 +279,13 @@ int ntcb_probe_container(const void* data, size_t size, NtcbTextureSetDesc* outD
    GetTexture (include/libntc/ntc.h:500-520) on a set opened with CreateTextureSetMetadataFromStream. */
 int ntcb_probe_container_texture(const void* data, size_t size, int index, NtcbTextureDesc* outTexture, int* outCount);
 
+/* Host only, no GPU needed.  Where the container keeps the BC7 mode bitmap of a texture's mip level:
+   offset from the start of the container and stored size, both 0 when it keeps none; *outCompressed
+   (optional) is 1 when the view is GDeflate-compressed.  Replaces ITextureMetadata::GetBC7ModeBufferFootprint
+   (include/libntc/ntc.h:451-453, src/TextureMetadata.cpp:154-165). */
+int ntcb_probe_container_bc7_mode_buffer(const void* data, size_t size, int textureIndex, int mipLevel, uint64_t* outOffset,
+                                         uint64_t* outStoredSize, int* outCompressed);
+
 /* Creates a decoder context on a CUDA device.  Replaces ntc::CreateContext
    (include/libntc/ntc.h:1330, src/PublicFunctions.cpp:62-162).  Fails with NTCB_ERR_CUDA when the
    device is not usable or is not compute capability 10.x. */
@@ -467,6 +474,26 @@ int ntcb_make_bc7_mode_buffer(int widthInBlocks, int heightInBlocks, const void*
    (ntcb_texture_set_synchronize waits for it). */
 int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, int firstChannel, int numChannels, int format,
     float alphaThreshold, void* deviceBlocks, size_t rowPitch);
+
+/* BC7 mode bitmaps of a texture of the set: ITextureMetadata::GetBC7ModeBuffer and
+   ITextureMetadata::MakeAndStoreBC7ModeBuffer (include/libntc/ntc.h:436-449, src/TextureMetadata.cpp:96-152).
+   The first returns the bitmap the file stores for that texture and mip level ("bcModeBuffers" of the
+   texture's header) or one stored by the second call: a pointer into host memory owned by the texture set,
+   NULL and 0 when there is none (NTCB_ERR_UNSUPPORTED when the file stores it GDeflate-compressed).  The
+   second makes the bitmap from BC7 blocks whose size in blocks is exactly that of the mip level. */
+int ntcb_texture_set_get_bc7_mode_buffer(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, const void** outData,
+                                         size_t* outSize);
+int ntcb_texture_set_make_and_store_bc7_mode_buffer(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, int widthInBlocks,
+                                                    int heightInBlocks, const void* blockData, size_t blockDataSize,
+                                                    size_t rowPitch);
+
+/* One whole mip of one texture of a decompressed set to the block format the texture's header names
+   (bcFormat: BC1 - BC5, BC7; NTCB_ERR_INVALID_ARGUMENT for None, NTCB_ERR_UNSUPPORTED for BC6), from the
+   texture's channel range.  BC7 uses the texture's mode bitmap of that mip when it has one - the reference's
+   BlockCompressionModeBufferSource::TextureSet (include/libntc/ntc.h:1042-1091, src/Context.cpp:675-706): the
+   bitmap is uploaded on first use and kept - and searches every mode otherwise.  Queued on the set's stream. */
+int ntcb_texture_set_block_compress_texture(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, float alphaThreshold,
+                                            void* deviceBlocks, size_t rowPitch);
 
 /* ---- Several GPUs of one machine ------------------------------------------------------------ */
 

@@ -11,7 +11,7 @@
 //   ITextureSet::GetDesc / GetLatentShape               -> same names
 //   ITextureSet::Decompress(stats, useInt8Weights)      -> same name, same default (FP8 weights)
 //   ITextureSet::ReadChannels(params)                   -> same name (every ChannelFormat, colour spaces, dithering)
-//   IContext::MakeBlockCompressionComputePass + dispatch -> ITextureSet::BlockCompress (BC1 - BC5, CUDA)
+//   IContext::MakeBlockCompressionComputePass + dispatch -> ITextureSet::BlockCompress / BlockCompressTexture (BC1 - BC5, BC7; CUDA)
 // tests/cpp/host_example.cpp is a complete client.
 //
 // Status values are the NtcbStatus codes of ntcb.h; ntcb::GetLastErrorMessage() returns the
@@ -63,10 +63,21 @@ public:
         NtcbOutputConversion const& conversion, int addressSpace, void* destination, size_t destinationBytes) = 0;
     virtual Status ReadChannels(ReadChannelsParameters const& params) = 0;
     virtual Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) = 0;
-    // One decoded mip to BC1 - BC5 blocks in device memory (see ntcb_block_compress), queued on the
+    // One decoded mip to BC1 - BC5 or BC7 blocks in device memory (see ntcb_block_compress), queued on the
     // set's stream: the whole mip, (width + 3) / 4 blocks per row, rowPitch bytes between rows of blocks.
     virtual Status BlockCompress(int mipLevel, int firstChannel, int numChannels, int format, float alphaThreshold,
         void* deviceBlocks, size_t rowPitch) = 0;
+    // ITextureMetadata::GetBC7ModeBuffer / MakeAndStoreBC7ModeBuffer (include/libntc/ntc.h:436-449) for texture
+    // `textureIndex`: the mode bitmap stored in the file for a mip level (host memory owned by the set; null
+    // and 0 when there is none), or made from BC7 blocks of exactly that mip's size in blocks.
+    virtual Status GetBC7ModeBuffer(int textureIndex, int mipLevel, void const** outData, size_t* outSize) const = 0;
+    virtual Status MakeAndStoreBC7ModeBuffer(int textureIndex, int mipLevel, int widthInBlocks, int heightInBlocks,
+        void const* blockData, size_t blockDataSize, size_t rowPitch) = 0;
+    // One mip of one texture of the set to the block format its header names (BC1 - BC5, BC7), with its
+    // channel range; BC7 takes the texture's stored mode buffer of that mip when it has one
+    // (BlockCompressionModeBufferSource::TextureSet), else searches every mode.
+    virtual Status BlockCompressTexture(int textureIndex, int mipLevel, float alphaThreshold, void* deviceBlocks,
+        size_t rowPitch) = 0;
     virtual Status Synchronize() = 0;
     virtual ~ITextureSet() = default;
 };

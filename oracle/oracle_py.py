@@ -345,6 +345,9 @@ def reference_lib(path: str = REF_LIB):
                                              ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t,
                                              ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_void_p]
         lib.ntcref_close.argtypes = [ctypes.c_void_p]
+        if hasattr(lib, "ntcref_probe_mode_buffer_footprint"):
+            lib.ntcref_probe_mode_buffer_footprint.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int,
+                                                               ctypes.POINTER(ctypes.c_uint64)]
         if hasattr(lib, "ntcref_make_bc7_mode_buffer"):
             lib.ntcref_bc7_mode_buffer_size.argtypes = [ctypes.c_int, ctypes.c_int]
             lib.ntcref_bc7_mode_buffer_size.restype = ctypes.c_size_t
@@ -366,6 +369,17 @@ def reference_probe(container: bytes) -> List[int]:
     if rc != 0:
         raise RuntimeError("reference loader rejected the container: %s" % lib.ntcref_last_error().decode())
     return list(out)
+
+
+def reference_mode_buffer_footprint(container: bytes, texture_index: int, mip_level: int):
+    """(offset in the container, stored size, compression type) of a texture's BC7 mode bitmap as the
+    reference's metadata loader reports it (no GPU needed)."""
+    out = (ctypes.c_uint64 * 3)()
+    lib = reference_lib()
+    rc = lib.ntcref_probe_mode_buffer_footprint(container, len(container), texture_index, mip_level, out)
+    if rc != 0:
+        raise RuntimeError("reference loader: status %d %s" % (rc, lib.ntcref_last_error().decode()))
+    return int(out[0]), int(out[1]), int(out[2])
 
 
 def reference_make_bc7_mode_buffer(blocks: np.ndarray) -> np.ndarray:

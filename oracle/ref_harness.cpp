@@ -131,6 +131,54 @@ int ntcref_probe_metadata(void const* fileData, size_t fileSize, int* out)
     return 0;
 }
 
+// Metadata-only: where the reference's loader finds the BC7 mode bitmap of a texture's mip level
+// (ITextureMetadata::GetBC7ModeBufferFootprint).  out[0..2] = offset in the stream, stored size, compression type.
+int ntcref_probe_mode_buffer_footprint(void const* fileData, size_t fileSize, int textureIndex, int mipLevel, uint64_t* out)
+{
+    g_error[0] = 0;
+    ntc::ContextParameters contextParams;
+    contextParams.cudaDevice = ntc::DisableCudaDevice;
+    contextParams.enableCooperativeVector = false;
+    ntc::IContext* context = nullptr;
+    ntc::Status status = ntc::CreateContext(&context, contextParams);
+    if (!context)
+    {
+        SetError("CreateContext", status);
+        return int(status);
+    }
+    ntc::IStream* stream = nullptr;
+    status = context->OpenReadOnlyMemory(fileData, fileSize, &stream);
+    if (status != ntc::Status::Ok)
+    {
+        SetError("OpenReadOnlyMemory", status);
+        ntc::DestroyContext(context);
+        return int(status);
+    }
+    ntc::ITextureSetMetadata* metadata = nullptr;
+    status = context->CreateTextureSetMetadataFromStream(stream, &metadata);
+    if (status != ntc::Status::Ok)
+    {
+        SetError("CreateTextureSetMetadataFromStream", status);
+        context->CloseMemory(stream);
+        ntc::DestroyContext(context);
+        return int(status);
+    }
+    int result = 0;
+    if (textureIndex < 0 || textureIndex >= metadata->GetTextureCount())
+        result = int(ntc::Status::OutOfRange);
+    else
+    {
+        ntc::BufferFootprint const footprint = metadata->GetTexture(textureIndex)->GetBC7ModeBufferFootprint(mipLevel);
+        out[0] = footprint.rangeInStream.offset;
+        out[1] = footprint.rangeInStream.size;
+        out[2] = uint64_t(footprint.compressionType);
+    }
+    context->DestroyTextureSetMetadata(metadata);
+    context->CloseMemory(stream);
+    ntc::DestroyContext(context);
+    return result;
+}
+
 // Runs the reference's CUDA decompression of every mip.  `gpuMilliseconds` receives the
 // reference's own timing of its mip loop (DecompressionStats::gpuTimeMilliseconds).
 int ntcref_decompress(void* opaque, int useInt8Weights, float* gpuMilliseconds)

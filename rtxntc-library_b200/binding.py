@@ -204,6 +204,15 @@ def lib():
                                              ctypes.c_void_p, ctypes.c_void_p]
         handle.ntcb_quantize_network.argtypes = [ctypes.POINTER(QuantizeNetworkParams), ctypes.c_void_p]
         handle.ntcb_block_compress.argtypes = [ctypes.POINTER(BlockCompressParams), ctypes.c_void_p]
+        handle.ntcb_probe_container_bc7_mode_buffer.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int,
+                                                                ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64),
+                                                                ctypes.POINTER(ctypes.c_int)]
+        handle.ntcb_texture_set_get_bc7_mode_buffer.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                                                ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_size_t)]
+        handle.ntcb_texture_set_make_and_store_bc7_mode_buffer.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                                           ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t]
+        handle.ntcb_texture_set_block_compress_texture.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+                                                                   ctypes.c_void_p, ctypes.c_size_t]
         handle.ntcb_bc7_mode_buffer_size.argtypes = [ctypes.c_int, ctypes.c_int]
         handle.ntcb_bc7_mode_buffer_size.restype = ctypes.c_size_t
         handle.ntcb_make_bc7_mode_buffer.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t,
@@ -244,6 +253,15 @@ def probe_container(container: bytes) -> TextureSetDesc:
     buffer = np.frombuffer(container, dtype=np.uint8)
     check(lib().ntcb_probe_container(buffer.ctypes.data, len(container), ctypes.byref(desc)))
     return desc
+
+
+def probe_bc7_mode_buffer(container: bytes, texture_index: int, mip_level: int):
+    """(offset in the container, stored size, compressed?) of a texture's BC7 mode bitmap; (0, 0, False) when the
+    container keeps none.  No GPU needed."""
+    offset, stored, compressed = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_int()
+    check(lib().ntcb_probe_container_bc7_mode_buffer(container, len(container), texture_index, mip_level, ctypes.byref(offset),
+                                                     ctypes.byref(stored), ctypes.byref(compressed)))
+    return int(offset.value), int(stored.value), bool(compressed.value)
 
 
 def probe_textures(container: bytes) -> list:
@@ -690,6 +708,37 @@ class TextureSet:
         torch.cuda.synchronize()
         check(lib().ntcb_texture_set_block_compress(self.handle, mip, first_channel, num_channels, block_format,
                                                     alpha_threshold, ctypes.c_void_p(out.data_ptr()), bw * block_bytes))
+        self.synchronize()
+        return out
+
+    def bc7_mode_buffer(self, texture_index: int, mip_level: int) -> Optional[np.ndarray]:
+        """The BC7 mode bitmap the set keeps for a texture's mip level (a copy, uint8), or None."""
+        data, size = ctypes.c_void_p(), ctypes.c_size_t()
+        check(lib().ntcb_texture_set_get_bc7_mode_buffer(self.handle, texture_index, mip_level, ctypes.byref(data), ctypes.byref(size)))
+        if not data.value:
+            return None
+        return np.frombuffer(ctypes.string_at(data.value, size.value), dtype=np.uint8).copy()
+
+    def make_and_store_bc7_mode_buffer(self, texture_index: int, mip_level: int, blocks: np.ndarray):
+        """Stores the mode bitmap of BC7 blocks (uint8 [blocks_y][blocks_x][16]) for a texture's mip level."""
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+        check(lib().ntcb_texture_set_make_and_store_bc7_mode_buffer(self.handle, texture_index, mip_level, blocks.shape[1],
+                                                                    blocks.shape[0], blocks.ctypes.data, blocks.nbytes,
+                                                                    blocks.shape[1] * 16))
+
+    def block_compress_texture(self, texture_index: int, mip_level: int, alpha_threshold: float = 1.0 / 255.0):
+        """One mip of one texture in the block format its header names (BC7: from its stored mode bitmap when it
+        has one): a CUDA uint8 tensor [blocks_y][blocks_x][8 or 16] (waits for the texture set's stream)."""
+        import torch
+
+        block_format = self.textures()[texture_index]["blockCompressedFormat"]
+        width, height = self.mip_size(mip_level)
+        bw, bh = (width + 3) // 4, (height + 3) // 4
+        block_bytes = 8 if block_format in (BLOCK_FORMAT_BC1, BLOCK_FORMAT_BC4) else 16
+        out = torch.zeros((bh, bw, block_bytes), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        check(lib().ntcb_texture_set_block_compress_texture(self.handle, texture_index, mip_level, alpha_threshold,
+                                                            ctypes.c_void_p(out.data_ptr()), bw * block_bytes))
         self.synchronize()
         return out
 

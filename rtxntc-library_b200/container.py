@@ -95,7 +95,8 @@ def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: byt
     given, holds one ntc::ColorSpace value per channel (the colour space the channel was stored in).
     textures, when given, holds the documents of the texture headers (the schema's own field names:
     name, firstChannel, numChannels and optionally channelFormat, rgbColorSpace, alphaColorSpace,
-    bcFormat as the schema's strings).
+    bcFormat as the schema's strings).  A header's "bcModeBuffers" may hold {"mipLevel": m, "data": bytes}
+    entries: the bytes go into the binary chunk and the entry becomes the schema's {"mipLevel", "view"}.
     """
     chunk = _BinaryChunk()
     latent_entries = []
@@ -125,6 +126,17 @@ def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: byt
     if channel_color_spaces is not None:
         assert len(channel_color_spaces) == geo.channels
         channel_entries = [{} if space == 0 else {"colorSpace": COLOR_SPACE_NAMES[space]} for space in channel_color_spaces]
+    texture_entries = []
+    for header in (textures or []):
+        if not isinstance(header, dict):  # a malformed entry, written as it is (loader tests)
+            texture_entries.append(header)
+            continue
+        header = dict(header)
+        if isinstance(header.get("bcModeBuffers"), list):
+            header["bcModeBuffers"] = [
+                {"mipLevel": item["mipLevel"], "view": chunk.add(bytes(item["data"]))} if isinstance(item, dict) and "data" in item else item
+                for item in header["bcModeBuffers"]]
+        texture_entries.append(header)
     document = {
         "schemaVersion": 3,
         "width": geo.width,
@@ -133,7 +145,7 @@ def write_container(geo: Geometry, latents: Sequence[np.ndarray], int8_blob: byt
         "numColorMips": geo.mips,
         "latentShape": {"numFeatures": geo.num_features},
         "mlpVersions": mlp_versions,
-        "textures": list(textures) if textures else [],
+        "textures": texture_entries,
         "channels": channel_entries,
         "latents": latent_entries,
         "colorMips": color_mips,

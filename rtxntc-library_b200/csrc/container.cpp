@@ -194,6 +194,26 @@ struct Reader
         memcpy(dst, binary + view.offset, bytes);
         return NTCB_OK;
     }
+
+    // The whole of an optional view; `compressed` is set instead for a GDeflate view.
+    int FetchWhole(uint64_t index, std::vector<uint8_t>& out, bool& compressed, uint64_t& offsetInBinaryChunk, uint64_t& storedSize,
+        const char* what)
+    {
+        if (index >= views.size())
+        {
+            SetError("%s refers to buffer view %llu, but the file has only %zu views.", what, (unsigned long long)index,
+                views.size());
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        }
+        const View& view = views[size_t(index)];
+        compressed = view.compressed;
+        offsetInBinaryChunk = view.offset;
+        storedSize = view.storedSize;
+        out.clear();
+        if (!compressed)
+            out.assign(binary + view.offset, binary + view.offset + view.storedSize);
+        return NTCB_OK;
+    }
 };
 
 // One MLP version of the document -> the row-major blob the reference keeps in memory
@@ -632,6 +652,39 @@ int LoadContainer(const void* data, size_t size, LoadedSet& out)
             }
             *field.target = value;
         }
+        texture.modeBuffers.assign(size_t(geo.mips), std::vector<uint8_t>());
+        texture.modeBufferCompressed.assign(size_t(geo.mips), 0);
+        texture.modeBufferOffset.assign(size_t(geo.mips), 0);
+        texture.modeBufferStoredSize.assign(size_t(geo.mips), 0);
+        const std::vector<json::Value>* modeBuffers = GetArray(entry, "bcModeBuffers");
+        if (!modeBuffers)
+        {
+            SetError("Texture %zu: 'bcModeBuffers' must be an array.", t);
+            return NTCB_ERR_FILE_UNRECOGNIZED;
+        }
+        for (const json::Value& item : *modeBuffers)
+            {
+                uint64_t mipLevel = 0, view = 0;
+                if (item.kind != json::Kind::Object)
+                {
+                    SetError("Texture %zu: 'bcModeBuffers' must hold objects.", t);
+                    return NTCB_ERR_FILE_UNRECOGNIZED;
+                }
+                if (!GetUnsigned(item, "mipLevel", true, mipLevel, "BCModeBuffer") || !GetUnsigned(item, "view", true, view, "BCModeBuffer"))
+                    return NTCB_ERR_FILE_UNRECOGNIZED;
+                std::vector<uint8_t> bytes;
+                bool compressed = false;
+                uint64_t offsetInChunk = 0, storedSize = 0;
+                rc = reader.FetchWhole(view, bytes, compressed, offsetInChunk, storedSize, "BC7 mode buffer");
+                if (rc != NTCB_OK)
+                    return rc;
+                if (mipLevel >= uint64_t(geo.mips))
+                    continue; // as the reference: an entry for a mip the set does not have is dropped
+                texture.modeBuffers[size_t(mipLevel)] = std::move(bytes);
+                texture.modeBufferCompressed[size_t(mipLevel)] = compressed ? 1 : 0;
+                texture.modeBufferOffset[size_t(mipLevel)] = uint64_t(reader.binary - static_cast<const uint8_t*>(data)) + offsetInChunk;
+                texture.modeBufferStoredSize[size_t(mipLevel)] = storedSize;
+            }
         out.textures.push_back(texture);
     }
 

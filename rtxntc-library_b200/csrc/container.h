@@ -50,6 +50,12 @@ struct LoadedTexture
     int channelFormat = 1;         // ntc::ChannelFormat, default UNORM8
     int blockCompressedFormat = 0; // ntc::BlockCompressedFormat, default None
     int rgbColorSpace = 0, alphaColorSpace = 0; // ntc::ColorSpace, default Linear
+    // BC7 mode bitmaps stored with the texture (json::Texture::bcModeBuffers), one per mip level, empty where
+    // the file has none (TextureMetadata::SetBC7ModeBufferFootprint / LoadBC7ModeBuffers,
+    // src/TextureMetadata.cpp:154-224)
+    std::vector<std::vector<uint8_t>> modeBuffers;
+    std::vector<uint8_t> modeBufferCompressed; // per mip: 1 = stored with GDeflate compression, which is not read
+    std::vector<uint64_t> modeBufferOffset, modeBufferStoredSize; // per mip: where the file keeps it (0, 0: nowhere)
 };
 
 struct LoadedSet

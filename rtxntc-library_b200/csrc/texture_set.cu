@@ -87,12 +87,17 @@ public:
     Status GetDeviceMip(int mipLevel, void** outPointer, size_t* outBytes) override;
     Status BlockCompress(int mipLevel, int firstChannel, int numChannels, int format, float alphaThreshold,
         void* deviceBlocks, size_t rowPitch) override;
+    Status GetBC7ModeBuffer(int textureIndex, int mipLevel, void const** outData, size_t* outSize) const override;
+    Status MakeAndStoreBC7ModeBuffer(int textureIndex, int mipLevel, int widthInBlocks, int heightInBlocks,
+        void const* blockData, size_t blockDataSize, size_t rowPitch) override;
+    Status BlockCompressTexture(int textureIndex, int mipLevel, float alphaThreshold, void* deviceBlocks, size_t rowPitch) override;
     Status Synchronize() override;
 
     const SetGeometry& Geometry() const { return m_geometry; }
 
 private:
     Status CheckKernelStatus();
+    Status CheckTextureAndMip(int textureIndex, int mipLevel) const;
     Status GrowStaging(size_t bytes);
     Status CopyBands(const uint8_t* deviceMip0, uint8_t* host, size_t rowBytes);
     Status DecodeInto(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights,
@@ -119,6 +124,7 @@ private:
     uint32_t* m_hostStatus = nullptr; // pinned
     int m_channelColorSpaces[kMaxChannels] = {}; // ntc::ColorSpace each channel is stored in (from the container)
     std::vector<LoadedTexture> m_textures;
+    std::vector<std::vector<void*>> m_deviceModeBuffers; // [texture][mip]: device copies of the BC7 mode bitmaps, made on first use
     uint8_t* m_staging = nullptr;     // grown on demand by ReadChannels to host with padded strides
     size_t m_stagingBytes = 0;
     cudaEvent_t m_eventStart = nullptr, m_eventStop = nullptr;
@@ -282,6 +288,7 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
     for (int c = 0; c < kMaxChannels; ++c)
         m_channelColorSpaces[c] = loaded.channelColorSpaces[c];
     m_textures = loaded.textures;
+    m_deviceModeBuffers.assign(m_textures.size(), std::vector<void*>(size_t(m_geometry.mips), nullptr));
     m_hasInt8 = !loaded.int8Blob.empty();
     m_hasFp8 = !loaded.fp8Blob.empty();
 
@@ -363,6 +370,12 @@ void TextureSet::Release()
     }
     if (m_eventStart) cudaEventDestroy(m_eventStart);
     if (m_eventStop) cudaEventDestroy(m_eventStop);
+    for (std::vector<void*>& perMip : m_deviceModeBuffers)
+        for (void*& copy : perMip)
+        {
+            if (copy) cudaFree(copy);
+            copy = nullptr;
+        }
     if (m_staging) cudaFree(m_staging);
     if (m_status) cudaFree(m_status);
     if (m_hostStatus) cudaFreeHost(m_hostStatus);
@@ -873,6 +886,165 @@ Status TextureSet::BlockCompress(int mipLevel, int firstChannel, int numChannels
     return ntcb_block_compress(&params, m_stream);
 }
 
+Status TextureSet::CheckTextureAndMip(int textureIndex, int mipLevel) const
+{
+    if (textureIndex < 0 || textureIndex >= int(m_textures.size()))
+    {
+        SetError("textureIndex (%d) must be between 0 and %d.", textureIndex, int(m_textures.size()) - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (mipLevel < 0 || mipLevel >= m_geometry.mips)
+    {
+        SetError("mipLevel (%d) must be between 0 and %d.", mipLevel, m_geometry.mips - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    return NTCB_OK;
+}
+
+Status TextureSet::GetBC7ModeBuffer(int textureIndex, int mipLevel, void const** outData, size_t* outSize) const
+{
+    if (outData)
+        *outData = nullptr;
+    if (outSize)
+        *outSize = 0;
+    const Status status = CheckTextureAndMip(textureIndex, mipLevel);
+    if (status != NTCB_OK)
+        return status;
+    const LoadedTexture& texture = m_textures[size_t(textureIndex)];
+    if (texture.modeBufferCompressed[size_t(mipLevel)])
+    {
+        SetError("The BC7 mode buffer of texture %d, mip level %d is stored with GDeflate compression, which this decoder does not read.",
+            textureIndex, mipLevel);
+        return NTCB_ERR_UNSUPPORTED;
+    }
+    const std::vector<uint8_t>& data = texture.modeBuffers[size_t(mipLevel)];
+    if (!data.empty())
+    {
+        if (outData)
+            *outData = data.data();
+        if (outSize)
+            *outSize = data.size();
+    }
+    ClearError();
+    return NTCB_OK;
+}
+
+Status TextureSet::MakeAndStoreBC7ModeBuffer(int textureIndex, int mipLevel, int widthInBlocks, int heightInBlocks,
+    void const* blockData, size_t blockDataSize, size_t rowPitch)
+{
+    const Status status = CheckTextureAndMip(textureIndex, mipLevel);
+    if (status != NTCB_OK)
+        return status;
+    const int mipWidthInBlocks = (m_geometry.mipWidth[mipLevel] + 3) / 4, mipHeightInBlocks = (m_geometry.mipHeight[mipLevel] + 3) / 4;
+    if (widthInBlocks != mipWidthInBlocks || heightInBlocks != mipHeightInBlocks)
+    {
+        SetError("Provided widthInBlocks (%d) and heightInBlocks (%d) do not match the expected dimensions (%d x %d) for mip level %d.",
+            widthInBlocks, heightInBlocks, mipWidthInBlocks, mipHeightInBlocks, mipLevel);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    LoadedTexture& texture = m_textures[size_t(textureIndex)];
+    std::vector<uint8_t> data(ntcb_bc7_mode_buffer_size(widthInBlocks, heightInBlocks));
+    const Status made = ntcb_make_bc7_mode_buffer(widthInBlocks, heightInBlocks, blockData, blockDataSize, rowPitch, data.data(), data.size());
+    if (made != NTCB_OK)
+        return made;
+    // a device copy of the bitmap this one replaces may still be read by work queued on the stream
+    void*& deviceCopy = m_deviceModeBuffers[size_t(textureIndex)][size_t(mipLevel)];
+    if (deviceCopy)
+    {
+        DeviceGuard guard(m_device);
+        if (!guard.Success())
+            return NTCB_ERR_CUDA;
+        cudaError_t err = cudaStreamSynchronize(m_stream);
+        if (err == cudaSuccess)
+            err = cudaFree(deviceCopy);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaFree", err);
+        deviceCopy = nullptr;
+    }
+    texture.modeBuffers[size_t(mipLevel)] = std::move(data);
+    texture.modeBufferCompressed[size_t(mipLevel)] = 0;
+    return NTCB_OK;
+}
+
+Status TextureSet::BlockCompressTexture(int textureIndex, int mipLevel, float alphaThreshold, void* deviceBlocks, size_t rowPitch)
+{
+    if (!m_decoded)
+    {
+        SetError("BlockCompress needs decoded texels: call Decompress first.");
+        return NTCB_ERR_INVALID_STATE;
+    }
+    const Status status = CheckTextureAndMip(textureIndex, mipLevel);
+    if (status != NTCB_OK)
+        return status;
+    const LoadedTexture& texture = m_textures[size_t(textureIndex)];
+    const int format = texture.blockCompressedFormat;
+    if (format == 0)
+    {
+        SetError("Texture %d ('%s') names no block-compressed format.", textureIndex, texture.name.c_str());
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+    NtcbBlockCompressParams params = {};
+    params.deviceMip = m_texels + m_geometry.mipTexelOffset[mipLevel] * m_geometry.channels;
+    params.layout = m_layout;
+    params.width = m_geometry.mipWidth[mipLevel];
+    params.height = m_geometry.mipHeight[mipLevel];
+    params.channels = m_geometry.channels;
+    params.firstChannel = texture.firstChannel;
+    params.format = format;
+    params.alphaThreshold = alphaThreshold;
+    params.widthInBlocks = (params.width + 3) / 4;
+    params.heightInBlocks = (params.height + 3) / 4;
+    params.deviceBlocks = deviceBlocks;
+    params.rowPitch = rowPitch;
+    // BC4 / BC5 take their one or two channels; the colour formats what the texture has, up to four
+    params.numChannels = (format == NTCB_BLOCK_FORMAT_BC4 || format == NTCB_BLOCK_FORMAT_BC5) ? 0 : (texture.numChannels < 4 ? texture.numChannels : 4);
+    if (format == NTCB_BLOCK_FORMAT_BC7)
+    {
+        if (texture.modeBufferCompressed[size_t(mipLevel)])
+        {
+            SetError("The BC7 mode buffer of texture %d, mip level %d is stored with GDeflate compression, which this decoder does not read.",
+                textureIndex, mipLevel);
+            return NTCB_ERR_UNSUPPORTED;
+        }
+        const std::vector<uint8_t>& modes = texture.modeBuffers[size_t(mipLevel)];
+        if (!modes.empty())
+        {
+            const size_t needed = ntcb_bc7_mode_buffer_size(params.widthInBlocks, params.heightInBlocks);
+            if (modes.size() < needed)
+            {
+                SetError("The BC7 mode buffer of texture %d, mip level %d holds %zu bytes, %zu are needed.", textureIndex, mipLevel,
+                    modes.size(), needed);
+                return NTCB_ERR_FILE_UNRECOGNIZED;
+            }
+            void*& deviceCopy = m_deviceModeBuffers[size_t(textureIndex)][size_t(mipLevel)];
+            if (!deviceCopy)
+            {
+                // the kernel reads whole 32-bit words: the copy is padded to a multiple of four bytes
+                const size_t bytes = (modes.size() + 3) & ~size_t(3);
+                cudaError_t err = cudaMalloc(&deviceCopy, bytes);
+                if (err == cudaSuccess)
+                    err = cudaMemsetAsync(deviceCopy, 0, bytes, m_stream);
+                if (err == cudaSuccess)
+                    err = cudaMemcpyAsync(deviceCopy, modes.data(), modes.size(), cudaMemcpyHostToDevice, m_stream);
+                if (err != cudaSuccess)
+                {
+                    if (deviceCopy)
+                        cudaFree(deviceCopy);
+                    deviceCopy = nullptr;
+                    return CudaFailure("BC7 mode buffer upload", err);
+                }
+            }
+            params.deviceModeBuffer = deviceCopy;
+            params.modeMapWidthInBlocks = uint32_t(params.widthInBlocks);
+            params.modeMapHeightInBlocks = uint32_t(params.heightInBlocks);
+        }
+    }
+    return ntcb_block_compress(&params, m_stream);
+}
+
 Status TextureSet::Synchronize()
 {
     DeviceGuard guard(m_device);
@@ -979,6 +1151,40 @@ int ntcb_probe_container_texture(const void* data, size_t size, int index, NtcbT
     if (outCount)
         *outCount = int(loaded.textures.size());
     return ntcb::FillTextureDesc(loaded.textures, index, outTexture);
+}
+
+int ntcb_probe_container_bc7_mode_buffer(const void* data, size_t size, int textureIndex, int mipLevel, uint64_t* outOffset,
+    uint64_t* outStoredSize, int* outCompressed)
+{
+    if (outOffset)
+        *outOffset = 0;
+    if (outStoredSize)
+        *outStoredSize = 0;
+    if (outCompressed)
+        *outCompressed = 0;
+    ntcb::LoadedSet loaded;
+    int status = ntcb::LoadContainer(data, size, loaded);
+    if (status != NTCB_OK)
+        return status;
+    if (textureIndex < 0 || textureIndex >= int(loaded.textures.size()))
+    {
+        ntcb::SetError("textureIndex (%d) must be between 0 and %d.", textureIndex, int(loaded.textures.size()) - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    const ntcb::LoadedTexture& texture = loaded.textures[size_t(textureIndex)];
+    if (mipLevel < 0 || mipLevel >= int(texture.modeBufferOffset.size()))
+    {
+        ntcb::SetError("mipLevel (%d) must be between 0 and %d.", mipLevel, int(texture.modeBufferOffset.size()) - 1);
+        return NTCB_ERR_OUT_OF_RANGE;
+    }
+    if (outOffset)
+        *outOffset = texture.modeBufferOffset[size_t(mipLevel)];
+    if (outStoredSize)
+        *outStoredSize = texture.modeBufferStoredSize[size_t(mipLevel)];
+    if (outCompressed)
+        *outCompressed = texture.modeBufferCompressed[size_t(mipLevel)];
+    ntcb::ClearError();
+    return NTCB_OK;
 }
 
 int ntcb_context_create(int cudaDevice, NtcbContext** outContext)
@@ -1128,6 +1334,40 @@ int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, in
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     return textureSet->impl->BlockCompress(mipLevel, firstChannel, numChannels, format, alphaThreshold, deviceBlocks, rowPitch);
+}
+
+int ntcb_texture_set_get_bc7_mode_buffer(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, const void** outData,
+    size_t* outSize)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->GetBC7ModeBuffer(textureIndex, mipLevel, outData, outSize);
+}
+
+int ntcb_texture_set_make_and_store_bc7_mode_buffer(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, int widthInBlocks,
+    int heightInBlocks, const void* blockData, size_t blockDataSize, size_t rowPitch)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->MakeAndStoreBC7ModeBuffer(textureIndex, mipLevel, widthInBlocks, heightInBlocks, blockData, blockDataSize,
+        rowPitch);
+}
+
+int ntcb_texture_set_block_compress_texture(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, float alphaThreshold,
+    void* deviceBlocks, size_t rowPitch)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->BlockCompressTexture(textureIndex, mipLevel, alphaThreshold, deviceBlocks, rowPitch);
 }
 
 int ntcb_texture_set_get_texture(NtcbTextureSet* textureSet, int index, NtcbTextureDesc* outTexture, int* outCount)

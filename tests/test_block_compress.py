@@ -612,6 +612,95 @@ def test_transcode_every_texture_by_its_header(oracle):
         texture_set.close()
 
 
+def _set_with_bc7_textures(mode_buffers=None):
+    """A 72 x 40, 8-channel set with a full mip chain with an RGBA texture and an RGB texture, both headed for BC7."""
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(72, 40, 8, 0, 2, 8, seed=12, network="unit"))
+    data.textures = [
+        {"name": "Albedo", "firstChannel": 0, "numChannels": 4, "rgbColorSpace": "sRGB", "bcFormat": "BC7"},
+        {"name": "Emissive", "firstChannel": 5, "numChannels": 3, "bcFormat": "BC7"},
+    ]
+    for (texture, mip), bits in (mode_buffers or {}).items():
+        data.textures[texture].setdefault("bcModeBuffers", []).append({"mipLevel": mip, "data": bits.tobytes()})
+    return data
+
+
+def test_stored_bc7_mode_buffers_are_found_where_the_reference_finds_them(oracle):
+    """The container's "bcModeBuffers": the loader reports the byte range the Python writer gave them, and the
+    reference's own metadata loader reports the same range (no GPU needed for either)."""
+    rng = np.random.default_rng(8)
+    buffers = {(0, 0): rng.integers(0, 256, binding.bc7_mode_buffer_size(18, 10), dtype=np.uint8),
+               (0, 2): rng.integers(0, 256, binding.bc7_mode_buffer_size(5, 3), dtype=np.uint8),
+               (1, 1): rng.integers(0, 256, binding.bc7_mode_buffer_size(9, 5), dtype=np.uint8)}
+    container = _set_with_bc7_textures(buffers).container
+    for texture in (0, 1):
+        for mip in range(3):
+            offset, stored, compressed = binding.probe_bc7_mode_buffer(container, texture, mip)
+            bits = buffers.get((texture, mip))
+            if bits is None:
+                assert (offset, stored, compressed) == (0, 0, False)
+            else:
+                assert stored == bits.nbytes and not compressed and container[offset:offset + stored] == bits.tobytes()
+            if oracle.reference_available():
+                assert oracle.reference_mode_buffer_footprint(container, texture, mip) == (offset, stored, 0)
+    lib = binding.lib()
+    assert lib.ntcb_probe_container_bc7_mode_buffer(container, len(container), 2, 0, None, None, None) == -9
+    assert lib.ntcb_probe_container_bc7_mode_buffer(container, len(container), 0, 99, None, None, None) == -9
+    # an entry that names a view the file does not have
+    broken = _set_with_bc7_textures()
+    broken.textures[0]["bcModeBuffers"] = [{"mipLevel": 0, "view": 999}]
+    assert lib.ntcb_probe_container_bc7_mode_buffer(broken.container, len(broken.container), 0, 0, None, None, None) == -3
+    assert b"BC7 mode buffer" in lib.ntcb_last_error()
+
+
+@pytest.mark.gpu
+def test_transcode_to_bc7_from_the_mode_buffers_a_set_carries(oracle):
+    """Decompress on load, then BC7 by the stored mode bitmap (BlockCompressionModeBufferSource::TextureSet):
+    an offline pass (here: this library's full search) chooses the modes, the set carries them, and the
+    run-time pass encodes every block in its mode.  Checked against the explicit-mode-buffer call, against the
+    reference's shader source where it is built, and for the modes the blocks end up with."""
+    import torch
+
+    plain = _set_with_bc7_textures()
+    with binding.Context() as context:
+        offline = context.create_texture_set(plain.container)
+        offline.decompress(False)
+        searched = {(t, m): offline.block_compress_texture(t, m).cpu().numpy() for t in (0, 1) for m in (0, 1)}
+        texels = {m: offline.read_mip(m) for m in (0, 1)}
+        assert offline.bc7_mode_buffer(0, 0) is None
+        # the same through MakeAndStoreBC7ModeBuffer on the loaded set
+        offline.make_and_store_bc7_mode_buffer(0, 0, searched[(0, 0)])
+        stored = offline.bc7_mode_buffer(0, 0)
+        assert np.array_equal(stored, binding.make_bc7_mode_buffer(searched[(0, 0)]))
+        from_stored = offline.block_compress_texture(0, 0).cpu().numpy()
+        with pytest.raises(binding.NtcbError):
+            offline.make_and_store_bc7_mode_buffer(0, 1, searched[(0, 0)])  # blocks of another mip's size
+        offline.close()
+
+        buffers = {key: binding.make_bc7_mode_buffer(blocks) for key, blocks in searched.items()}
+        shipped = context.create_texture_set(_set_with_bc7_textures(buffers).container)
+        shipped.decompress(False)
+        for (texture, mip), bits in buffers.items():
+            assert np.array_equal(shipped.bc7_mode_buffer(texture, mip), bits)
+            blocks = shipped.block_compress_texture(texture, mip).cpu().numpy()
+            header = shipped.textures()[texture]
+            first, count = header["firstChannel"], header["numChannels"]
+            mip_texels = torch.from_numpy(texels[mip]).cuda()
+            explicit = binding.block_compress(mip_texels, 7, first, num_channels=count, mode_buffer=torch.from_numpy(bits).cuda())
+            assert np.array_equal(blocks, explicit.cpu().numpy()), (texture, mip)
+            assert np.array_equal(binding.make_bc7_mode_buffer(blocks), bits), (texture, mip)  # every block in its mode
+            if (texture, mip) == (0, 0):
+                assert np.array_equal(blocks, from_stored)
+            if oracle.reference_bc_available():
+                rgba = np.zeros(texels[mip].shape[:2] + (4,), dtype=np.float32)
+                rgba[..., 3] = 1.0
+                rgba[..., :count] = texels[mip][..., first:first + count].astype(np.float32)
+                assert np.array_equal(blocks, oracle.reference_block_compress_bc7(rgba, mode_buffer=bits)), (texture, mip)
+                assert np.array_equal(searched[(texture, mip)], oracle.reference_block_compress_bc7(rgba)), (texture, mip)
+        assert shipped.bc7_mode_buffer(1, 2) is None  # no bitmap for that mip: the full search runs
+        assert shipped.block_compress_texture(1, 2).shape == (3, 5, 16)
+        shipped.close()
+
+
 @pytest.mark.gpu
 def test_flat_and_binary_blocks_decode_exactly_at_full_size():
     """Size-independent property on a 4096 x 4096 channel (1 M blocks): blocks of one value and blocks
