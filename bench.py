@@ -808,6 +808,66 @@ def run_block_compress_case(side: int) -> int:
     return 0
 
 
+def run_batch_case(count: int) -> int:
+    """Times ntcb_decode_batch - ONE process, every visible GPU - on `count` texture sets of the batch
+    configuration's shape (2048 x 2048, 8 channels, 12 mips, Int8 weights) gathered in pinned host memory,
+    and beside it what plain device-to-host copies of the same bytes sustain on the same GPUs at once (the
+    ceiling of any job with host destinations).  Prints plain lines, not the benchmark's JSON line."""
+    import torch
+
+    entry.load_package()
+    from rtxntc_library_b200 import binding, synthetic
+
+    devices = list(range(torch.cuda.device_count()))
+    spec = synthetic.config_spec(2, 0)
+    sets = [synthetic.make_texture_set(synthetic.config_spec(2, index % 4)) for index in range(min(count, 4))]
+    containers = [sets[index % len(sets)].container for index in range(count)]
+    geometry = sets[0].geometry
+    values = geometry.total_texels * geometry.channels
+    images = [torch.empty(values, dtype=torch.float16).pin_memory() for _ in range(count)]
+    times = []
+    for _ in range(4):
+        begin = time.perf_counter()
+        code, statuses, units = binding.decode_batch(containers, devices, True, images)
+        times.append(time.perf_counter() - begin)
+        if code != 0 or any(statuses):
+            print("ntcb_decode_batch failed: %d %s" % (code, binding.lib().ntcb_last_error()))
+            return 1
+    seconds = min(times[1:])
+    texels = geometry.total_texels * count
+    per_device = {}
+    for unit in units:
+        per_device[unit.device] = per_device.get(unit.device, 0) + unit.texels
+    # the ceiling: every device copies its share of the bytes to pinned host memory, all at once
+    share = values * 2 * count // len(devices)
+    sources = []
+    for device in devices:
+        with torch.cuda.device(device):
+            sources.append(torch.empty(share, dtype=torch.uint8, device="cuda:%d" % device))
+    targets = [torch.empty(share, dtype=torch.uint8).pin_memory() for _ in devices]
+    copy_times = []
+    for _ in range(4):
+        for device in devices:
+            torch.cuda.synchronize(device)
+        begin = time.perf_counter()
+        for device, source, target in zip(devices, sources, targets):
+            with torch.cuda.device(device):
+                target.copy_(source, non_blocking=True)
+        for device in devices:
+            torch.cuda.synchronize(device)
+        copy_times.append(time.perf_counter() - begin)
+    ceiling_seconds = min(copy_times[1:])
+    print("ntcb_decode_batch: %d sets of %dx%d x %d channels on %d GPU(s), %d work units: %.1f ms = %.2f Gtexel/s end to end "
+          "(containers parsed, uploaded, decoded, %.0f MB gathered in pinned host memory; includes context and texture-set "
+          "creation on every device)" % (count, spec.width, spec.height, geometry.channels, len(devices), len(units), seconds * 1e3,
+                                        texels / seconds / 1e9, values * 2 * count / 1e6))
+    print("texels per device: %s" % ", ".join("%d: %.1f M" % (d, t / 1e6) for d, t in sorted(per_device.items())))
+    print("plain D2H copies of the same bytes from %d GPU(s) at once: %.1f ms = %.1f GB/s = %.2f Gtexel/s; the batch call is at %.2f of it"
+          % (len(devices), ceiling_seconds * 1e3, values * 2 * count / ceiling_seconds / 1e9, texels / ceiling_seconds / 1e9,
+             ceiling_seconds / seconds))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -827,7 +887,11 @@ def main() -> int:
                         help="only time latent packing on a SIDE x SIDE x 4 grid and one network quantisation, and exit")
     parser.add_argument("--block-compress-case", metavar="SIDE", type=int,
                         help="only time BC1 - BC5 and BC7 encoding of a SIDE x SIDE 12-channel mip, and exit")
+    parser.add_argument("--batch-case", metavar="SETS", type=int,
+                        help="only time ntcb_decode_batch (one process, every visible GPU) on SETS texture sets, and exit")
     args = parser.parse_args()
+    if args.batch_case:
+        return run_batch_case(args.batch_case)
     if args.profile_case:
         return run_profile_case(args.profile_case)
     if args.producers_case:

@@ -348,6 +348,13 @@ int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadCha
    texels on the GPU. */
 int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void** outPointer, size_t* outBytes);
 
+/* Loads another compressed texture set of the same dimensions, channel count, mip count and latent shape into
+   an existing one, re-using every buffer it holds: ITextureSet::LoadFromMemory (include/libntc/ntc.h:869-881).
+   NTCB_ERR_FILE_INCOMPATIBLE when the shapes differ (nothing changes then).  Waits for the set's stream; the
+   decoded texels of the previous set stay in place until the next decompress, but calls that need decoded
+   texels return NTCB_ERR_INVALID_STATE until then. */
+int ntcb_texture_set_load_from_memory(NtcbTextureSet* textureSet, const void* data, size_t size);
+
 /* The textures of a loaded set: see ntcb_probe_container_texture. */
 int ntcb_texture_set_get_texture(NtcbTextureSet* textureSet, int index, NtcbTextureDesc* outTexture, int* outCount);
 

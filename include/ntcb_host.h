@@ -78,6 +78,9 @@ public:
     // (BlockCompressionModeBufferSource::TextureSet), else searches every mode.
     virtual Status BlockCompressTexture(int textureIndex, int mipLevel, float alphaThreshold, void* deviceBlocks,
         size_t rowPitch) = 0;
+    // ITextureSet::LoadFromMemory: another compressed set of the same dimensions and latent shape into this
+    // one's buffers (FileIncompatible otherwise, and nothing changes); the texels must be decompressed again.
+    virtual Status LoadFromMemory(void const* pData, size_t size) = 0;
     virtual Status Synchronize() = 0;
     virtual ~ITextureSet() = default;
 };

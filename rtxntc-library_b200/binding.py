@@ -184,6 +184,7 @@ def lib():
         handle.ntcb_context_create.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]
         handle.ntcb_context_destroy.argtypes = [ctypes.c_void_p]
         handle.ntcb_context_destroy.restype = None
+        handle.ntcb_texture_set_load_from_memory.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
         handle.ntcb_texture_set_create_from_memory.argtypes = [
             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetFeatures),
             ctypes.POINTER(ctypes.c_void_p)]
@@ -710,6 +711,10 @@ class TextureSet:
                                                     alpha_threshold, ctypes.c_void_p(out.data_ptr()), bw * block_bytes))
         self.synchronize()
         return out
+
+    def load_from_memory(self, container: bytes) -> None:
+        """Another compressed set of the same shape into this one's buffers (ITextureSet::LoadFromMemory)."""
+        check(lib().ntcb_texture_set_load_from_memory(self.handle, container, len(container)))
 
     def bc7_mode_buffer(self, texture_index: int, mip_level: int) -> Optional[np.ndarray]:
         """The BC7 mode bitmap the set keeps for a texture's mip level (a copy, uint8), or None."""

@@ -240,7 +240,16 @@ struct DeviceWorker
     int numerics = NTCB_NUMERICS_REFERENCE;
     NtcbContext* context = nullptr;
     cudaStream_t copyStream = nullptr;
-    std::map<int, NtcbTextureSet*> sets; // item -> its texture set on this device
+    // The worker's texture sets, one per SHAPE it has met: a unit of another item of the same dimensions
+    // and latent shape is loaded into the buffers of the set that is already there (LoadFromMemory), so a
+    // batch of equal sets allocates once per worker instead of once per item.
+    struct Slot
+    {
+        NtcbTextureSet* set;
+        NtcbTextureSetDesc desc;
+        int item; // whose compressed data the set holds now
+    };
+    std::vector<Slot> slots;
 
     int Open()
     {
@@ -257,9 +266,9 @@ struct DeviceWorker
 
     void Close()
     {
-        for (auto& entry : sets)
-            ntcb_texture_set_destroy(entry.second);
-        sets.clear();
+        for (Slot& slot : slots)
+            ntcb_texture_set_destroy(slot.set);
+        slots.clear();
         if (copyStream)
         {
             cudaSetDevice(device);
@@ -271,26 +280,57 @@ struct DeviceWorker
         context = nullptr;
     }
 
-    // Decodes the unit's rows and copies them into the item's host image (interleaved fp16, mip after mip).
-    int Run(const NtcbBatchItem& item, const NtcbBatchUnit& unit)
+    static bool SameShape(const NtcbTextureSetDesc& a, const NtcbTextureSetDesc& b)
     {
-        NtcbTextureSet*& set = sets[unit.item];
-        if (!set)
+        return a.width == b.width && a.height == b.height && a.channels == b.channels && a.mips == b.mips
+            && a.gridSizeScale == b.gridSizeScale && a.numFeatures == b.numFeatures;
+    }
+
+    // The texture set that holds (or now loads) the item's compressed data.
+    int Acquire(const NtcbBatchItem& item, int itemIndex, const NtcbTextureSetDesc& itemDesc, NtcbTextureSet** outSet)
+    {
+        Slot* sameShape = nullptr;
+        for (Slot& slot : slots)
         {
-            NtcbTextureSetFeatures features{};
-            features.outputLayout = NTCB_LAYOUT_INTERLEAVED;
-            features.numerics = numerics;
-            int status = ntcb_texture_set_create_from_memory(context, item.container, item.containerBytes, &features, &set);
-            if (status != NTCB_OK)
+            if (slot.item == itemIndex)
             {
-                sets.erase(unit.item);
-                return status;
+                *outSet = slot.set;
+                return NTCB_OK;
             }
+            if (!sameShape && SameShape(slot.desc, itemDesc))
+                sameShape = &slot;
         }
-        NtcbTextureSetDesc desc{};
-        int status = ntcb_texture_set_get_desc(set, &desc);
+        if (sameShape)
+        {
+            sameShape->item = -1;
+            int status = ntcb_texture_set_load_from_memory(sameShape->set, item.container, item.containerBytes);
+            if (status != NTCB_OK)
+                return status;
+            sameShape->item = itemIndex;
+            *outSet = sameShape->set;
+            return NTCB_OK;
+        }
+        NtcbTextureSetFeatures features{};
+        features.outputLayout = NTCB_LAYOUT_INTERLEAVED;
+        features.numerics = numerics;
+        NtcbTextureSet* set = nullptr;
+        int status = ntcb_texture_set_create_from_memory(context, item.container, item.containerBytes, &features, &set);
         if (status != NTCB_OK)
             return status;
+        slots.push_back({set, itemDesc, itemIndex});
+        *outSet = set;
+        return NTCB_OK;
+    }
+
+    // Decodes the unit's rows and copies them into the item's host image (interleaved fp16, mip after mip).
+    int Run(const NtcbBatchItem& item, const NtcbTextureSetDesc& itemDesc, const NtcbBatchUnit& unit)
+    {
+        NtcbTextureSet* set = nullptr;
+        int acquired = Acquire(item, unit.item, itemDesc, &set);
+        if (acquired != NTCB_OK)
+            return acquired;
+        const NtcbTextureSetDesc& desc = itemDesc;
+        int status = NTCB_OK;
         if (item.hostTexelsBytes < size_t(desc.totalTexels) * size_t(desc.channels) * 2)
         {
             SetError("Item %d: the host image holds %zu bytes, the decoded set needs %zu.", unit.item, item.hostTexelsBytes,
@@ -450,7 +490,7 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
                     }
                     snapshot.device = device;
                     const int result = opt.worker ? opt.worker(opt.workerUser, device, &snapshot)
-                                                  : worker.Run(items[snapshot.item], snapshot);
+                                                  : worker.Run(items[snapshot.item], descs[snapshot.item], snapshot);
                     scheduler.Complete(unit, position, device, result);
                 }
                 worker.Close();

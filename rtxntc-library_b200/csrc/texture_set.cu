@@ -91,6 +91,7 @@ public:
     Status MakeAndStoreBC7ModeBuffer(int textureIndex, int mipLevel, int widthInBlocks, int heightInBlocks,
         void const* blockData, size_t blockDataSize, size_t rowPitch) override;
     Status BlockCompressTexture(int textureIndex, int mipLevel, float alphaThreshold, void* deviceBlocks, size_t rowPitch) override;
+    Status LoadFromMemory(void const* pData, size_t size) override;
     Status Synchronize() override;
 
     const SetGeometry& Geometry() const { return m_geometry; }
@@ -98,6 +99,7 @@ public:
 private:
     Status CheckKernelStatus();
     Status CheckTextureAndMip(int textureIndex, int mipLevel) const;
+    Status FillUpload(const LoadedSet& loaded);
     Status GrowStaging(size_t bytes);
     Status CopyBands(const uint8_t* deviceMip0, uint8_t* host, size_t rowBytes);
     Status DecodeInto(const int32_t* rowRanges, DecompressionStats* pOutStats, bool useInt8Weights,
@@ -285,12 +287,6 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
     }
     m_numerics = features.numerics;
     m_networkBytes = m_numerics == NTCB_NUMERICS_REFERENCE ? size_t(kRefNetworkBytes) : size_t(kStagedNetworkBytes);
-    for (int c = 0; c < kMaxChannels; ++c)
-        m_channelColorSpaces[c] = loaded.channelColorSpaces[c];
-    m_textures = loaded.textures;
-    m_deviceModeBuffers.assign(m_textures.size(), std::vector<void*>(size_t(m_geometry.mips), nullptr));
-    m_hasInt8 = !loaded.int8Blob.empty();
-    m_hasFp8 = !loaded.fp8Blob.empty();
 
     // upload image: latents (padded to 16 bytes), then the Int8 and the FP8 network images
     m_latentBytes = (loaded.latents.size() * 2 + 15) & ~size_t(15);
@@ -301,23 +297,9 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
         SetError("Failed to allocate %zu bytes of pinned host memory for the compressed data.", m_uploadBytes);
         return NTCB_ERR_OUT_OF_MEMORY;
     }
-    memset(m_hostUpload, 0, m_uploadBytes);
-    memcpy(m_hostUpload, loaded.latents.data(), loaded.latents.size() * 2);
-    if (m_hasInt8)
-    {
-        auto stage = m_numerics == NTCB_NUMERICS_REFERENCE ? ntcb_stage_network_reference : ntcb_stage_network;
-        Status status = stage(loaded.int8Blob.data(), loaded.int8Blob.size(), NTCB_WEIGHTS_INT8, m_hostUpload + m_latentBytes);
-        if (status != NTCB_OK)
-            return status;
-    }
-    if (m_hasFp8)
-    {
-        auto stage = m_numerics == NTCB_NUMERICS_REFERENCE ? ntcb_stage_network_reference : ntcb_stage_network;
-        Status status = stage(loaded.fp8Blob.data(), loaded.fp8Blob.size(), NTCB_WEIGHTS_FP8,
-            m_hostUpload + m_latentBytes + m_networkBytes);
-        if (status != NTCB_OK)
-            return status;
-    }
+    Status filled = FillUpload(loaded);
+    if (filled != NTCB_OK)
+        return filled;
 
     err = cudaMalloc(reinterpret_cast<void**>(&m_deviceUpload), m_uploadBytes);
     if (err != cudaSuccess)
@@ -350,6 +332,74 @@ Status TextureSet::Initialize(LoadedSet&& loaded, const TextureSetFeatures& feat
     err = cudaStreamCreateWithFlags(&m_copyStream, cudaStreamNonBlocking);
     if (err != cudaSuccess)
         return CudaFailure("cudaStreamCreateWithFlags", err);
+    return NTCB_OK;
+}
+
+// What a container brings besides its shape: latents and staged networks into the pinned upload image,
+// channel colour spaces, texture headers with their BC7 mode bitmaps.
+Status TextureSet::FillUpload(const LoadedSet& loaded)
+{
+    for (int c = 0; c < kMaxChannels; ++c)
+        m_channelColorSpaces[c] = loaded.channelColorSpaces[c];
+    for (std::vector<void*>& perMip : m_deviceModeBuffers)
+        for (void*& copy : perMip)
+        {
+            if (copy) cudaFree(copy);
+            copy = nullptr;
+        }
+    m_textures = loaded.textures;
+    m_deviceModeBuffers.assign(m_textures.size(), std::vector<void*>(size_t(m_geometry.mips), nullptr));
+    m_hasInt8 = !loaded.int8Blob.empty();
+    m_hasFp8 = !loaded.fp8Blob.empty();
+    memset(m_hostUpload, 0, m_uploadBytes);
+    memcpy(m_hostUpload, loaded.latents.data(), loaded.latents.size() * 2);
+    auto stage = m_numerics == NTCB_NUMERICS_REFERENCE ? ntcb_stage_network_reference : ntcb_stage_network;
+    if (m_hasInt8)
+    {
+        Status status = stage(loaded.int8Blob.data(), loaded.int8Blob.size(), NTCB_WEIGHTS_INT8, m_hostUpload + m_latentBytes);
+        if (status != NTCB_OK)
+            return status;
+    }
+    if (m_hasFp8)
+    {
+        Status status = stage(loaded.fp8Blob.data(), loaded.fp8Blob.size(), NTCB_WEIGHTS_FP8,
+            m_hostUpload + m_latentBytes + m_networkBytes);
+        if (status != NTCB_OK)
+            return status;
+    }
+    return NTCB_OK;
+}
+
+// ITextureSet::LoadFromMemory (include/libntc/ntc.h:869-881): another compressed set of the same dimensions
+// into this one's buffers.
+Status TextureSet::LoadFromMemory(void const* pData, size_t size)
+{
+    LoadedSet loaded;
+    Status status = LoadContainer(pData, size, loaded);
+    if (status != NTCB_OK)
+        return status;
+    const SetGeometry& theirs = loaded.geometry;
+    if (theirs.width != m_geometry.width || theirs.height != m_geometry.height || theirs.channels != m_geometry.channels
+        || theirs.mips != m_geometry.mips || theirs.gridSizeScale != m_geometry.gridSizeScale || theirs.numFeatures != m_geometry.numFeatures)
+    {
+        SetError("The file holds a %dx%d set of %d channels and %d mips with latent shape {%d, %d}; this texture set is %dx%d, %d "
+                 "channels, %d mips, {%d, %d}.", theirs.width, theirs.height, theirs.channels, theirs.mips, theirs.gridSizeScale,
+            theirs.numFeatures, m_geometry.width, m_geometry.height, m_geometry.channels, m_geometry.mips, m_geometry.gridSizeScale,
+            m_geometry.numFeatures);
+        return NTCB_ERR_FILE_INCOMPATIBLE;
+    }
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+    // uploads from the pinned image that are still queued must have read it
+    cudaError_t err = cudaStreamSynchronize(m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamSynchronize", err);
+    m_decoded = false;
+    status = FillUpload(loaded);
+    if (status != NTCB_OK)
+        return status;
+    ClearError();
     return NTCB_OK;
 }
 
@@ -1234,6 +1284,16 @@ int ntcb_texture_set_create_from_memory(NtcbContext* context, const void* data, 
     if (status != NTCB_OK)
         return status;
     return WrapTextureSet(context, impl, outTextureSet);
+}
+
+int ntcb_texture_set_load_from_memory(NtcbTextureSet* textureSet, const void* data, size_t size)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return textureSet->impl->LoadFromMemory(data, size);
 }
 
 int ntcb_texture_set_create_from_file(NtcbContext* context, const char* fileName, const NtcbTextureSetFeatures* features,

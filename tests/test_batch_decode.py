@@ -157,26 +157,63 @@ def test_gathered_host_images_equal_a_plain_decode(numerics):
     host image equals what one ordinary launch decodes."""
     import torch
 
+    # two sets share a shape: a worker that meets both loads the second into the buffers of the first
     specs = [synthetic.TextureSetSpec(200, 136, 6, 0, 2, 8, seed=11, network="unit"),
              synthetic.TextureSetSpec(64, 64, 4, 0, 4, 12, seed=12, network="unit"),
-             synthetic.TextureSetSpec(1024, 768, 8, 0, 4, 8, seed=13, network="unit")]
+             synthetic.TextureSetSpec(1024, 768, 8, 0, 4, 8, seed=13, network="unit"),
+             synthetic.TextureSetSpec(200, 136, 6, 0, 2, 8, seed=14, network="unit")]
     sets = [synthetic.make_texture_set(spec) for spec in specs]
     devices = list(range(min(torch.cuda.device_count(), 4)))
     if len(devices) == 1:
         devices = [0, 0]
     images = [torch.full((data.geometry.total_texels * data.geometry.channels,), -5.0, dtype=torch.float16).pin_memory()
               for data in sets]
-    flags = [True, False, True]
+    flags = [True, False, True, True]
     code, statuses, units = binding.decode_batch([data.container for data in sets], devices, flags, images, numerics=numerics)
     assert code == 0, binding.lib().ntcb_last_error()
-    assert statuses == [0, 0, 0] and all(unit.status == 0 and unit.attempts == 1 for unit in units)
-    assert len({unit.item for unit in units}) == 3 and len(units) > 3
+    assert statuses == [0, 0, 0, 0] and all(unit.status == 0 and unit.attempts == 1 for unit in units)
+    assert len({unit.item for unit in units}) == 4 and len(units) > 4
     for data, image, use_int8 in zip(sets, images, flags):
         resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
         resident.decode(use_int8)
         torch.cuda.synchronize()
         resident.check_status()
         assert torch.equal(resident.out.cpu().view(torch.int16), image.view(torch.int16))
+
+
+@pytest.mark.gpu
+def test_a_texture_set_reloaded_in_place_decodes_like_a_fresh_one():
+    """ITextureSet::LoadFromMemory: a second set of the same shape goes into the buffers of the first (what a
+    batch worker does between items); a set of another shape is refused and nothing changes."""
+    import torch
+
+    first = synthetic.make_texture_set(synthetic.TextureSetSpec(200, 136, 6, 0, 2, 8, seed=21, network="unit"))
+    second = synthetic.make_texture_set(synthetic.TextureSetSpec(200, 136, 6, 0, 2, 8, seed=22, network="unit"))
+    other = synthetic.make_texture_set(synthetic.TextureSetSpec(200, 136, 6, 0, 4, 8, seed=23, network="unit"))
+    with binding.Context() as context:
+        fresh = {}
+        for name, data in (("first", first), ("second", second)):
+            texture_set = context.create_texture_set(data.container)
+            texture_set.decompress(True)
+            fresh[name] = [texture_set.read_mip(m) for m in range(data.geometry.mips)]
+            texture_set.close()
+        assert not np.array_equal(fresh["first"][0], fresh["second"][0])
+        texture_set = context.create_texture_set(first.container)
+        texture_set.decompress(True)
+        texture_set.load_from_memory(second.container)
+        with pytest.raises(binding.NtcbError):
+            texture_set.read_mip(0)  # decoded texels of the previous set are not handed out
+        texture_set.decompress(True)
+        assert all(np.array_equal(texture_set.read_mip(m), fresh["second"][m]) for m in range(second.geometry.mips))
+        with pytest.raises(binding.NtcbError) as refused:
+            texture_set.load_from_memory(other.container)
+        assert refused.value.code == -4
+        texture_set.decompress(True)
+        assert all(np.array_equal(texture_set.read_mip(m), fresh["second"][m]) for m in range(second.geometry.mips))
+        texture_set.load_from_memory(first.container)
+        texture_set.decompress(True)
+        assert all(np.array_equal(texture_set.read_mip(m), fresh["first"][m]) for m in range(first.geometry.mips))
+        texture_set.close()
 
 
 @pytest.mark.gpu
