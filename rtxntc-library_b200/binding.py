@@ -800,9 +800,9 @@ def decode_batch(containers: Sequence[bytes], devices: Sequence[int], use_int8, 
     keep = []
     flags = [use_int8] * len(containers) if isinstance(use_int8, (bool, int)) else list(use_int8)
     for index, (item, container) in enumerate(zip(items, containers)):
-        buffer = ctypes.create_string_buffer(container, len(container))
-        keep.append(buffer)
-        item.container = ctypes.cast(buffer, ctypes.c_void_p)
+        pointer = ctypes.c_char_p(container)  # the bytes object's own storage: nothing is copied
+        keep.append((container, pointer))
+        item.container = ctypes.cast(pointer, ctypes.c_void_p)
         item.containerBytes = len(container)
         item.useInt8Weights = 1 if flags[index] else 0
         if host_images is not None:

@@ -20,6 +20,7 @@
 #include <condition_variable>
 #include <cstring>
 #include <map>
+#include <string>
 #include <mutex>
 #include <thread>
 #include <vector>
@@ -42,7 +43,9 @@ struct MipSize
     int width, height;
 };
 
-// Cuts the items into units.  `target` texels per unit; an item smaller than 1.5 targets becomes
+// Cuts the items into units.  `target` texels per unit; an item of at most three quarters of a target
+// stays whole (there are enough of them to balance the devices, and every unit of an item costs its
+// worker a parse and an upload of the item's compressed data); one up to 1.5 targets becomes
 // (mip 0) and (the other mips) - mip 0 is three quarters of a full chain - a larger one becomes
 // `bands` units, each holding one band of tile rows of every mip tall enough to split; the mips too
 // short to split go whole, largest first, to the unit with the least texels.
@@ -70,6 +73,13 @@ void PlanItem(int item, const NtcbTextureSetDesc& desc, uint64_t target, std::ve
     {
         NtcbBatchUnit first = emptyUnit();
         addRows(first, 0, 0, mips[0].height);
+        if (total * 4 <= target * 3)
+        {
+            for (int m = 1; m < desc.mips; ++m)
+                addRows(first, m, 0, mips[m].height);
+            units.push_back(first);
+            return;
+        }
         units.push_back(first);
         if (desc.mips > 1)
         {
@@ -434,7 +444,8 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
         return NTCB_ERR_INVALID_ARGUMENT;
     }
 
-    // what each container holds (host only)
+    // what each container holds (host only; every container is parsed and validated, on as many threads as
+    // there are cores to spare: 64 containers of a megabyte each would otherwise cost the call 20 ms up front)
     std::vector<NtcbTextureSetDesc> descs(numItems);
     for (int i = 0; i < numItems; ++i)
     {
@@ -444,9 +455,29 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
             SetError("ntcb_decode_batch: item %d has no container or no host image.", i);
             return NTCB_ERR_INVALID_ARGUMENT;
         }
-        int status = ntcb_probe_container(items[i].container, items[i].containerBytes, &descs[i]);
-        if (status != NTCB_OK)
-            return status;
+    }
+    {
+        const int probers = std::max(1, std::min<int>(numItems, std::min<unsigned>(std::thread::hardware_concurrency(), 16u)));
+        std::vector<int> probeStatus(numItems, NTCB_OK);
+        std::vector<std::string> probeMessage(numItems);
+        std::vector<std::thread> pool;
+        for (int t = 0; t < probers; ++t)
+            pool.emplace_back([&, t]() {
+                for (int i = t; i < numItems; i += probers)
+                {
+                    probeStatus[i] = ntcb_probe_container(items[i].container, items[i].containerBytes, &descs[i]);
+                    if (probeStatus[i] != NTCB_OK)
+                        probeMessage[i] = ntcb_last_error(); // the message is the probing thread's
+                }
+            });
+        for (std::thread& thread : pool)
+            thread.join();
+        for (int i = 0; i < numItems; ++i)
+            if (probeStatus[i] != NTCB_OK)
+            {
+                SetError("ntcb_decode_batch: item %d: %s", i, probeMessage[i].c_str());
+                return probeStatus[i];
+            }
     }
 
     Scheduler scheduler;

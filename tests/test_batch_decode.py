@@ -55,9 +55,14 @@ def test_plan_balances_the_benchmark_jobs():
     units = binding.plan_batch([(8192, 8192, 14)], 8)
     assert len(units) == 32
     assert units[0].texels <= 1.4 * units[-1].texels
-    # 64 sets on 8 devices: (mip 0) and (the rest) of every set
+    # 64 sets on 8 devices: enough items to balance, every set stays whole (one parse and upload per set)
     units = binding.plan_batch([(2048, 2048, 12)] * 64, 8)
-    assert len(units) == 128 and units[0].texels == 2048 * 2048
+    assert len(units) == 64 and units[0].texels == 5592405
+    # 24 sets on 8 devices: (mip 0) and (the rest) of every set
+    units = binding.plan_batch([(2048, 2048, 12)] * 24, 8)
+    assert len(units) == 48 and units[0].texels == 2048 * 2048
+    # 8 sets on 8 devices: four bands of tile rows each
+    assert len(binding.plan_batch([(2048, 2048, 12)] * 8, 8)) == 32
 
 
 @pytest.fixture(scope="module")
@@ -105,11 +110,9 @@ def test_a_transient_failure_is_retried_on_another_device(containers):
 
     code, statuses, units, log = _run(containers, flaky)
     assert code == 0 and statuses == [0] * 6
-    retried = [unit for unit in units if unit.attempts == 2]
-    assert len(retried) == 2
-    for unit in retried:
-        attempts = [device for device, item, result in log if item == unit.item]
-        assert unit.status == 0
+    # two extra attempts in all (the second failure may hit the unit that failed first, when it comes back)
+    assert sum(unit.attempts - 1 for unit in units) == 2 and len(log) == len(units) + 2
+    assert all(unit.status == 0 for unit in units)
 
 
 def test_failure_on_every_device_is_reported_not_waited_for(containers):
