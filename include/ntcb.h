@@ -541,8 +541,10 @@ typedef struct NtcbBatchOptions
     void* workerUser;
 } NtcbBatchOptions;
 
-/* Cuts a job into work units, largest first (host only).  An item of at most ~1.5 times the target
-   size (all texels / (numDevices x unitsPerDevice)) becomes two units - mip 0, and the other mips;
+/* Cuts a job into work units, largest first (host only).  With the target size = all texels /
+   (numDevices x unitsPerDevice): an item of at most three quarters of it stays whole (there are enough
+   items to balance the devices); one of at most ~1.5 times the target becomes two units - mip 0, and the
+   other mips;
    a larger one becomes bands of tile rows (multiples of 8 rows, at least 64) of its tall mips, the
    short mips going whole to the lightest band.  `units` may be NULL to ask for the count. */
 int ntcb_plan_batch(const NtcbTextureSetDesc* descs, int numItems, int numDevices, int unitsPerDevice, NtcbBatchUnit* units,
@@ -562,6 +564,16 @@ int ntcb_plan_batch(const NtcbTextureSetDesc* descs, int numItems, int numDevice
    all work is done. */
 int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, int numDevices, const NtcbBatchOptions* options,
     NtcbBatchUnit* outUnits, int maxUnits, int* outNumUnits);
+
+/* The same with the worker threads, their contexts and the texture sets they have allocated kept between
+   calls: for a client that decodes batch after batch.  Workers open their device when the first run
+   reaches them; a device that cannot be opened takes no work in that run and is tried again in the next.
+   One run at a time per decoder (a second caller waits).  ntcb_decode_batch is create + run + destroy. */
+typedef struct NtcbBatchDecoder NtcbBatchDecoder;
+int ntcb_batch_decoder_create(const int* devices, int numDevices, const NtcbBatchOptions* options, NtcbBatchDecoder** outDecoder);
+int ntcb_batch_decoder_run(NtcbBatchDecoder* decoder, NtcbBatchItem* items, int numItems, NtcbBatchUnit* outUnits, int maxUnits,
+    int* outNumUnits);
+void ntcb_batch_decoder_destroy(NtcbBatchDecoder* decoder);
 
 /* Size of the staging area built into the library for ntcb_read_channels_to_host_noalloc. */
 #define NTCB_NOALLOC_STAGING_BYTES (4u << 20)

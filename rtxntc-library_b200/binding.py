@@ -184,6 +184,12 @@ def lib():
         handle.ntcb_context_create.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p)]
         handle.ntcb_context_destroy.argtypes = [ctypes.c_void_p]
         handle.ntcb_context_destroy.restype = None
+        handle.ntcb_batch_decoder_create.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.POINTER(BatchOptions),
+                                                     ctypes.POINTER(ctypes.c_void_p)]
+        handle.ntcb_batch_decoder_run.argtypes = [ctypes.c_void_p, ctypes.POINTER(BatchItem), ctypes.c_int, ctypes.POINTER(BatchUnit),
+                                                  ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        handle.ntcb_batch_decoder_destroy.argtypes = [ctypes.c_void_p]
+        handle.ntcb_batch_decoder_destroy.restype = None
         handle.ntcb_texture_set_load_from_memory.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
         handle.ntcb_texture_set_create_from_memory.argtypes = [
             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetFeatures),
@@ -790,12 +796,7 @@ def plan_batch(shapes: Sequence[Tuple[int, int, int]], num_devices: int, units_p
     return list(units)
 
 
-def decode_batch(containers: Sequence[bytes], devices: Sequence[int], use_int8, host_images=None, numerics: int = NUMERICS_REFERENCE,
-                 worker=None, max_attempts: int = 0, units_per_device: int = 0, workers_per_device: int = 0):
-    """ntcb_decode_batch: decodes the sets on the listed devices and gathers every set's mip chain in
-    `host_images[i]` (a writable buffer object exposing its address as .data_ptr() or .ctypes.data;
-    None with a fake `worker`).  `use_int8`: one flag, or one per set.  `worker(device, unit) -> status`
-    replaces the GPU work (tests).  Returns (status code, item statuses, units as BatchUnit list)."""
+def _batch_items(containers: Sequence[bytes], use_int8, host_images):
     items = (BatchItem * len(containers))()
     keep = []
     flags = [use_int8] * len(containers) if isinstance(use_int8, (bool, int)) else list(use_int8)
@@ -809,16 +810,61 @@ def decode_batch(containers: Sequence[bytes], devices: Sequence[int], use_int8, 
             image = host_images[index]
             item.hostTexels = image.data_ptr() if hasattr(image, "data_ptr") else image.ctypes.data
             item.hostTexelsBytes = image.numel() * image.element_size() if hasattr(image, "numel") else image.nbytes
+    return items, keep
+
+
+def _batch_options(numerics, worker, max_attempts, units_per_device, workers_per_device):
     options = BatchOptions()
     options.numerics, options.maxAttempts = numerics, max_attempts
     options.unitsPerDevice, options.workersPerDevice = units_per_device, workers_per_device
+    callback = None
     if worker is not None:
         callback = BATCH_WORKER(lambda user, device, unit: int(worker(device, unit.contents)))
-        keep.append(callback)
         options.worker = callback
+    return options, callback
+
+
+def decode_batch(containers: Sequence[bytes], devices: Sequence[int], use_int8, host_images=None, numerics: int = NUMERICS_REFERENCE,
+                 worker=None, max_attempts: int = 0, units_per_device: int = 0, workers_per_device: int = 0):
+    """ntcb_decode_batch: decodes the sets on the listed devices and gathers every set's mip chain in
+    `host_images[i]` (a writable buffer object exposing its address as .data_ptr() or .ctypes.data;
+    None with a fake `worker`).  `use_int8`: one flag, or one per set.  `worker(device, unit) -> status`
+    replaces the GPU work (tests).  Returns (status code, item statuses, units as BatchUnit list)."""
+    items, keep = _batch_items(containers, use_int8, host_images)
+    options, callback = _batch_options(numerics, worker, max_attempts, units_per_device, workers_per_device)
     device_list = (ctypes.c_int * len(devices))(*devices)
     units = (BatchUnit * 8192)()
     count = ctypes.c_int()
     code = lib().ntcb_decode_batch(items, len(containers), device_list, len(devices), ctypes.byref(options), units, 8192,
                                    ctypes.byref(count))
     return code, [item.status for item in items], list(units)[:count.value]
+
+
+class BatchDecoder:
+    """ntcb_batch_decoder_*: the worker threads of decode_batch, their contexts and texture sets kept between runs."""
+
+    def __init__(self, devices: Sequence[int], numerics: int = NUMERICS_REFERENCE, worker=None, max_attempts: int = 0,
+                 units_per_device: int = 0, workers_per_device: int = 0):
+        options, self._callback = _batch_options(numerics, worker, max_attempts, units_per_device, workers_per_device)
+        device_list = (ctypes.c_int * len(devices))(*devices)
+        self.handle = ctypes.c_void_p()
+        check(lib().ntcb_batch_decoder_create(device_list, len(devices), ctypes.byref(options), ctypes.byref(self.handle)))
+
+    def run(self, containers: Sequence[bytes], use_int8, host_images=None):
+        """One batch; returns (status code, item statuses, units) like decode_batch."""
+        items, keep = _batch_items(containers, use_int8, host_images)
+        units = (BatchUnit * 8192)()
+        count = ctypes.c_int()
+        code = lib().ntcb_batch_decoder_run(self.handle, items, len(containers), units, 8192, ctypes.byref(count))
+        return code, [item.status for item in items], list(units)[:count.value]
+
+    def close(self) -> None:
+        if self.handle:
+            lib().ntcb_batch_decoder_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()

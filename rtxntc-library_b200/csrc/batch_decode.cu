@@ -387,8 +387,87 @@ struct DeviceWorker
     }
 };
 
+// One run of a decoder: what the workers share while it lasts.
+struct BatchJob
+{
+    NtcbBatchItem* items = nullptr;
+    const NtcbTextureSetDesc* descs = nullptr;
+    Scheduler scheduler;
+};
+
 } // namespace
 } // namespace ntcb
+
+// The threads of a batch decoder outlive its runs: a worker opens its context when the first run reaches it
+// and keeps it, with the texture sets it has allocated, until the decoder is destroyed.
+struct NtcbBatchDecoder
+{
+    std::vector<int> devices;
+    NtcbBatchOptions options{};
+    std::vector<std::thread> threads;
+    std::mutex runMutex;  // one run at a time
+    std::mutex mutex;     // guards what follows
+    std::condition_variable wake, done;
+    ntcb::BatchJob* job = nullptr;
+    uint64_t generation = 0;
+    int running = 0;
+    bool closing = false;
+
+    void WorkerLoop(int position)
+    {
+        using namespace ntcb;
+        const int device = devices[size_t(position)];
+        DeviceWorker worker;
+        worker.device = device;
+        worker.numerics = options.numerics;
+        bool opened = false;
+        uint64_t seen = 0;
+        for (;;)
+        {
+            BatchJob* current = nullptr;
+            {
+                std::unique_lock<std::mutex> lock(mutex);
+                wake.wait(lock, [&]() { return closing || generation != seen; });
+                if (closing)
+                    break;
+                seen = generation;
+                current = job;
+            }
+            if (!options.worker && !opened)
+            {
+                opened = worker.Open() == NTCB_OK; // tried again at the next run if it fails now
+                if (!opened)
+                    worker.Close();
+            }
+            Scheduler& scheduler = current->scheduler;
+            if (!options.worker && !opened)
+                scheduler.Retire(position);
+            else
+                for (;;)
+                {
+                    bool finished = false;
+                    const int unit = scheduler.Take(position, finished);
+                    if (finished)
+                        break;
+                    NtcbBatchUnit snapshot;
+                    {
+                        std::lock_guard<std::mutex> lock(scheduler.mutex);
+                        snapshot = scheduler.units[size_t(unit)];
+                    }
+                    snapshot.device = device;
+                    const int result = options.worker ? options.worker(options.workerUser, device, &snapshot)
+                                                      : worker.Run(current->items[snapshot.item], current->descs[snapshot.item], snapshot);
+                    scheduler.Complete(unit, position, device, result);
+                }
+            {
+                std::lock_guard<std::mutex> lock(mutex);
+                if (--running == 0)
+                    done.notify_all();
+            }
+        }
+        worker.Close();
+    }
+};
 
 extern "C"
 {
@@ -420,13 +499,18 @@ int ntcb_plan_batch(const NtcbTextureSetDesc* descs, int numItems, int numDevice
     return NTCB_OK;
 }
 
-int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, int numDevices, const NtcbBatchOptions* options,
-    NtcbBatchUnit* outUnits, int maxUnits, int* outNumUnits)
+int ntcb_batch_decoder_create(const int* devices, int numDevices, const NtcbBatchOptions* options, NtcbBatchDecoder** outDecoder)
 {
     using namespace ntcb;
-    if (!items || numItems < 1 || !devices || numDevices < 1 || numDevices > 64)
+    if (!outDecoder)
     {
-        SetError("ntcb_decode_batch: needs items and 1..64 devices.");
+        SetError("outDecoder is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    *outDecoder = nullptr;
+    if (!devices || numDevices < 1 || numDevices > 64)
+    {
+        SetError("ntcb_batch_decoder_create: needs 1..64 devices.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     NtcbBatchOptions opt{};
@@ -440,9 +524,46 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
         opt.workersPerDevice = opt.worker ? 1 : 2;
     if (opt.numerics != NTCB_NUMERICS_REFERENCE && opt.numerics != NTCB_NUMERICS_EXACT)
     {
-        SetError("ntcb_decode_batch: unknown numerics %d.", opt.numerics);
+        SetError("ntcb_batch_decoder_create: unknown numerics %d.", opt.numerics);
         return NTCB_ERR_INVALID_ARGUMENT;
     }
+    NtcbBatchDecoder* decoder = new NtcbBatchDecoder;
+    decoder->devices.assign(devices, devices + numDevices);
+    decoder->options = opt;
+    for (int position = 0; position < numDevices; ++position)
+        for (int w = 0; w < opt.workersPerDevice; ++w)
+            decoder->threads.emplace_back([decoder, position]() { decoder->WorkerLoop(position); });
+    *outDecoder = decoder;
+    ClearError();
+    return NTCB_OK;
+}
+
+void ntcb_batch_decoder_destroy(NtcbBatchDecoder* decoder)
+{
+    if (!decoder)
+        return;
+    {
+        std::lock_guard<std::mutex> lock(decoder->mutex);
+        decoder->closing = true;
+    }
+    decoder->wake.notify_all();
+    for (std::thread& thread : decoder->threads)
+        thread.join();
+    delete decoder;
+}
+
+int ntcb_batch_decoder_run(NtcbBatchDecoder* decoder, NtcbBatchItem* items, int numItems, NtcbBatchUnit* outUnits, int maxUnits,
+    int* outNumUnits)
+{
+    using namespace ntcb;
+    if (!decoder || !items || numItems < 1)
+    {
+        SetError("ntcb_batch_decoder_run: needs a decoder and items.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    std::lock_guard<std::mutex> oneRunAtATime(decoder->runMutex);
+    const NtcbBatchOptions& opt = decoder->options;
+    const int numDevices = int(decoder->devices.size());
 
     // what each container holds (host only; every container is parsed and validated, on as many threads as
     // there are cores to spare: 64 containers of a megabyte each would otherwise cost the call 20 ms up front)
@@ -480,7 +601,10 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
             }
     }
 
-    Scheduler scheduler;
+    BatchJob job;
+    job.items = items;
+    job.descs = descs.data();
+    Scheduler& scheduler = job.scheduler;
     int status = PlanUnits(descs.data(), numItems, numDevices, opt.unitsPerDevice, scheduler.units);
     if (status != NTCB_OK)
         return status;
@@ -492,44 +616,15 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
     scheduler.numDevices = numDevices;
     scheduler.maxAttempts = opt.maxAttempts;
 
-    std::vector<std::thread> threads;
-    for (int position = 0; position < numDevices; ++position)
     {
-        for (int w = 0; w < opt.workersPerDevice; ++w)
-        {
-            threads.emplace_back([&, position]() {
-                const int device = devices[position];
-                DeviceWorker worker;
-                worker.device = device;
-                worker.numerics = opt.numerics;
-                if (!opt.worker && worker.Open() != NTCB_OK)
-                {
-                    worker.Close();
-                    scheduler.Retire(position);
-                    return;
-                }
-                for (;;)
-                {
-                    bool finished = false;
-                    const int unit = scheduler.Take(position, finished);
-                    if (finished)
-                        break;
-                    NtcbBatchUnit snapshot;
-                    {
-                        std::lock_guard<std::mutex> lock(scheduler.mutex);
-                        snapshot = scheduler.units[unit];
-                    }
-                    snapshot.device = device;
-                    const int result = opt.worker ? opt.worker(opt.workerUser, device, &snapshot)
-                                                  : worker.Run(items[snapshot.item], descs[snapshot.item], snapshot);
-                    scheduler.Complete(unit, position, device, result);
-                }
-                worker.Close();
-            });
-        }
+        std::unique_lock<std::mutex> lock(decoder->mutex);
+        decoder->job = &job;
+        decoder->running = int(decoder->threads.size());
+        ++decoder->generation;
+        decoder->wake.notify_all();
+        decoder->done.wait(lock, [&]() { return decoder->running == 0; });
+        decoder->job = nullptr;
     }
-    for (std::thread& thread : threads)
-        thread.join();
 
     int failedUnits = 0;
     for (size_t u = 0; u < count; ++u)
@@ -553,6 +648,30 @@ int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, in
     }
     ClearError();
     return NTCB_OK;
+}
+
+int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, int numDevices, const NtcbBatchOptions* options,
+    NtcbBatchUnit* outUnits, int maxUnits, int* outNumUnits)
+{
+    using namespace ntcb;
+    if (!items || numItems < 1 || !devices || numDevices < 1 || numDevices > 64)
+    {
+        SetError("ntcb_decode_batch: needs items and 1..64 devices.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (options && options->numerics != NTCB_NUMERICS_REFERENCE && options->numerics != NTCB_NUMERICS_EXACT)
+    {
+        SetError("ntcb_decode_batch: unknown numerics %d.", options->numerics);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    NtcbBatchDecoder* decoder = nullptr;
+    int status = ntcb_batch_decoder_create(devices, numDevices, options, &decoder);
+    if (status != NTCB_OK)
+        return status;
+    status = ntcb_batch_decoder_run(decoder, items, numItems, outUnits, maxUnits, outNumUnits);
+    // the message of a failed run must survive the teardown (ClearError is not called there)
+    ntcb_batch_decoder_destroy(decoder);
+    return status;
 }
 
 } // extern "C"

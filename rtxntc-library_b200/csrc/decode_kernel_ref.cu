@@ -59,6 +59,10 @@ namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
+#ifndef NTCB_VARIANT
+#define NTCB_VARIANT 0
+#endif
+constexpr int kVariant = NTCB_VARIANT; // experiments: 1 chain-local barriers in layers 1 and 2; 2 split accumulator loads
 
 // Nonzero in exactly one lane of the (converged) warp.
 __device__ __forceinline__ uint32_t ElectOne()
@@ -839,27 +843,46 @@ __device__ __forceinline__ void UmmaE4m3F16(uint32_t tmemD, uint64_t descA, uint
         : "memory");
 }
 
-// The matrix products of one layer for one chain of the tile, issued by the calling thread.
+// What the matrix products of a layer address, the same for every tile: descriptors of the operand regions
+// (those of chain 1 lie kOperandBytes further) and the accumulator columns.
+struct ChainBases
+{
+    uint64_t operand, ones, weight, bias;
+    uint32_t accumulators, barrierBase;
+};
+
 template <int kLayer>
-__device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int half, uint32_t enabled = 1)
+__device__ __forceinline__ ChainBases MakeChainBases(const RefTileContext& ctx)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
-    constexpr int kK = kLayer == 0 ? 48 : kLayer == 1 ? 64 : kLayer == 2 ? 48 : 32;
     constexpr int kWeightOffset =
         kLayer == 0 ? kRefWeightOffset0 : kLayer == 1 ? kRefWeightOffset1 : kLayer == 2 ? kRefWeightOffset2 : kRefWeightOffset3;
     constexpr int kBiasOffset =
         kLayer == 0 ? kRefBiasOffset0 : kLayer == 1 ? kRefBiasOffset1 : kLayer == 2 ? kRefBiasOffset2 : kRefBiasOffset3;
-    // both descriptors: binary16 accumulators, operand formats 0 (binary16 for kind::f16, e4m3 for kind::f8f6f4)
-    constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
+    ChainBases bases;
     // The issuing thread is the critical path of the layer: the four base descriptors are built
     // once, every operand is then a constant offset (in 16-byte units) added to the address field.
-    const uint64_t operandBase = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes, 2048, 128);
-    const uint64_t onesBase = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
-    const uint64_t weightBase = MakeSmemDescriptor(ctx.networkBase + kWeightOffset, kN * 16, 128);
-    const uint64_t biasBase = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
-    const uint32_t accumulators = ctx.tmemBase + half * kTmemColumnsPerHalf;
+    bases.operand = MakeSmemDescriptor(ctx.operandA, 2048, 128);
+    bases.ones = MakeSmemDescriptor(ctx.biasRegion, 2048, 128);
+    bases.weight = MakeSmemDescriptor(ctx.networkBase + kWeightOffset, kN * 16, 128);
+    bases.bias = MakeSmemDescriptor(ctx.networkBase + kBiasOffset, kN * 16, 128);
+    bases.accumulators = ctx.tmemBase;
+    bases.barrierBase = ctx.barrierBase;
+    return bases;
+}
+
+// The matrix products of one layer for one chain of the tile, issued by the calling thread.
+template <int kLayer>
+__device__ __forceinline__ void IssueChainRefFp8(const ChainBases& bases, int half, uint32_t enabled)
+{
+    constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
+    constexpr int kK = kLayer == 0 ? 48 : kLayer == 1 ? 64 : kLayer == 2 ? 48 : 32;
+    // both descriptors: binary16 accumulators, operand formats 0 (binary16 for kind::f16, e4m3 for kind::f8f6f4)
+    constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
+    const uint64_t operandBase = bases.operand + uint64_t(uint32_t(half) * uint32_t(kOperandBytes >> 4));
+    const uint32_t accumulators = bases.accumulators + half * kTmemColumnsPerHalf;
     // accumulators := bias (binary16 step: rows (1, 0, ...) times the bias column: exact)
-    UmmaF16(accumulators, onesBase, biasBase, instr, 0, enabled);
+    UmmaF16(accumulators, bases.ones, bases.bias, instr, 0, enabled);
 #pragma unroll
     for (int step = 0; step < kK / 16; ++step)
     {
@@ -867,20 +890,38 @@ __device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int 
         {
             // 16 products of the 32-wide chunk step / 2: weight copy `step` has the other 16 columns zeroed
             const uint64_t descA = operandBase + uint64_t(((step / 2) * 2 * 2048) >> 4);
-            const uint64_t descB = weightBase + uint64_t((step * kN * 32) >> 4);
+            const uint64_t descB = bases.weight + uint64_t((step * kN * 32) >> 4);
             UmmaE4m3F16(accumulators, descA, descB, instr, 1, enabled);
         }
         else
         {
             // binary16 operands: one K step = two core matrices of 8 halves
             const uint64_t descA = operandBase + uint64_t((step * 2 * 2048) >> 4);
-            const uint64_t descB = weightBase + uint64_t((step * 2 * kN * 16) >> 4);
+            const uint64_t descB = bases.weight + uint64_t((step * 2 * kN * 16) >> 4);
             UmmaF16(accumulators, descA, descB, instr, 1, enabled);
         }
     }
     // arrives once everything issued so far has completed: this chain's accumulators are ready
     if (enabled)
-        UmmaCommit(ctx.barrierBase + half * 8);
+        UmmaCommit(bases.barrierBase + half * 8);
+}
+
+template <int kLayer>
+__device__ __forceinline__ void IssueChainRefFp8(const RefTileContext& ctx, int half, uint32_t enabled)
+{
+    IssueChainRefFp8<kLayer>(MakeChainBases<kLayer>(ctx), half, enabled);
+}
+
+// The issuing warp's view of the context: values the compiler can see are the same in every lane.
+__device__ __forceinline__ RefTileContext UniformContext(const RefTileContext& ctx)
+{
+    RefTileContext uniform = ctx;
+    uniform.operandA = __shfl_sync(0xFFFFFFFFu, ctx.operandA, 0);
+    uniform.biasRegion = __shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0);
+    uniform.networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
+    uniform.tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
+    uniform.barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
+    return uniform;
 }
 
 // First half of a layer: hands the A operand written before this call to the tensor core.  Returns
@@ -900,6 +941,45 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     if (!(kAblate & 128))
         FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
+    if ((kVariant & 1) && (kLayer == 1 || kLayer == 2))
+    {
+        // experiment: the chain's 128 threads meet in a barrier of their own and the chain's first warp issues
+        const int half = ctx.tid >> 7;
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+        if (((ctx.tid >> 5) & 3) == 0 && !(kAblate & 16))
+        {
+            TcgenFenceAfterSync();
+            RefTileContext uniform = ctx;
+            uniform.operandA = __shfl_sync(0xFFFFFFFFu, ctx.operandA, 0);
+            uniform.biasRegion = __shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0);
+            uniform.networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
+            uniform.tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
+            uniform.barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
+            const uint32_t elected = ElectOne();
+            IssueChainRefFp8<kLayer>(uniform, __shfl_sync(0xFFFFFFFFu, half, 0), elected);
+        }
+        return 0;
+    }
+    if (kVariant & 4)
+    {
+        // experiment: the issuing warp builds its descriptors before the barrier, so that after it only the
+        // matrix products remain to be issued
+        const bool issuer = (ctx.tid >> 5) == kIssuingWarp;
+        ChainBases bases = {};
+        if (issuer)
+            bases = MakeChainBases<kLayer>(UniformContext(ctx));
+        if (__syncthreads_or(failed))
+            return 1;
+        if (issuer && !(kAblate & 16))
+        {
+            TcgenFenceAfterSync();
+            const uint32_t elected = ElectOne();
+#pragma unroll
+            for (int half = 0; half < kRefChains; ++half)
+                IssueChainRefFp8<kLayer>(bases, half, elected);
+        }
+        return 0;
+    }
     if (kAblate & 256)
         __syncthreads();
     else if (__syncthreads_or(failed))
@@ -983,6 +1063,8 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
         if (!(kAblate & 32))
         {
             TmemLoadPacked16(ctx.tmemLane, low);
+            if (kVariant & 2)
+                TmemLoadWait(); // experiment: the second load's latency under the first half's arithmetic
             if (kN == 64)
                 TmemLoadPacked16(ctx.tmemLane + 32, high);
             else
@@ -990,7 +1072,8 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
                 uint32_t (&tail)[8] = reinterpret_cast<uint32_t (&)[8]>(high);
                 TmemLoadPacked8(ctx.tmemLane + 32, tail);
             }
-            TmemLoadWait();
+            if (!(kVariant & 2))
+                TmemLoadWait();
         }
         else
         {
@@ -1005,6 +1088,8 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 2]), ActivateToE4m3(low[8 * c + 3])),
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 4]), ActivateToE4m3(low[8 * c + 5])),
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 6]), ActivateToE4m3(low[8 * c + 7])));
+        if ((kVariant & 2) && !(kAblate & 32))
+            TmemLoadWait();
 #pragma unroll
         for (int c = 0; c < (kN - 32) / 16; ++c)
             rowChunk[(2 + c) * 128] = make_uint4(

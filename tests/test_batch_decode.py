@@ -144,6 +144,32 @@ def test_a_slow_device_gets_less_work(containers):
     assert per_device[0] <= 2 and sum(per_device.values()) == 18
 
 
+def test_a_decoder_runs_batch_after_batch_with_the_same_workers(containers):
+    """ntcb_batch_decoder_*: the threads survive the runs; a run in which a device keeps failing retires it for
+    that run only."""
+    seen = collections.Counter()
+    lock = threading.Lock()
+    failing = {"device": None}
+
+    def worker(device, unit):
+        with lock:
+            seen[(threading.get_ident(), device)] += 1
+        return -2 if device == failing["device"] else 0
+
+    with binding.BatchDecoder([0, 1, 2], worker=worker) as decoder:
+        code, statuses, units = decoder.run(containers, True)
+        assert code == 0 and statuses == [0] * 6 and all(unit.attempts == 1 for unit in units)
+        threads_after_first = {ident for ident, _ in seen}
+        failing["device"] = 1
+        code, statuses, units = decoder.run(containers[:3], True)
+        assert code == 0 and statuses == [0] * 3 and all(unit.device != 1 and unit.status == 0 for unit in units)
+        failing["device"] = None
+        code, statuses, units = decoder.run(containers, True)
+        assert code == 0 and any(unit.device == 1 for unit in units)  # back in the next run
+        assert {ident for ident, _ in seen} == threads_after_first and len(threads_after_first) == 3
+        assert decoder.run([b"not a container"], True)[0] == -3 and b"item 0" in binding.lib().ntcb_last_error()
+
+
 def test_arguments_are_checked(containers):
     assert binding.decode_batch([], [0], True, worker=lambda d, u: 0)[0] == -1
     assert binding.decode_batch(containers[:1], [], True, worker=lambda d, u: 0)[0] == -1
