@@ -59,10 +59,6 @@ namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
-#ifndef NTCB_VARIANT
-#define NTCB_VARIANT 0
-#endif
-constexpr int kVariant = NTCB_VARIANT; // experiments: 1 chain-local barriers in layers 1 and 2; 2 split accumulator loads
 
 // Nonzero in exactly one lane of the (converged) warp.
 __device__ __forceinline__ uint32_t ElectOne()
@@ -389,9 +385,65 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
 // Layers
 // ---------------------------------------------------------------------------------------------
 
-// First half of a layer for the CTA's current tile: barrier and MMA issue (all chains of the
-// tile).  Returns nonzero (uniformly over the CTA) when some thread gave up on a wait.
+// The barrier before a layer's matrix products.  The operand rows of a chain are written by the chain's
+// own 128 threads, and only they read the chain's accumulators, so between two layers of the same tile a
+// chain needs nobody else: kChainLocal = 1 makes its threads meet in a named barrier of their own (1 or 2)
+// and go on without the other chain - 3.3 % faster on the benchmark workload than the CTA-wide barrier for
+// every layer.  Giving up is then agreed on at the CTA-wide barriers that remain (kChainLocal = 0: layers 0
+// and 3 of the decode kernels, where all eight warps share the tile's tables), or, with kChainLocal = 2,
+// among the chain's threads (inference on sample, where nothing is shared).  Returns nonzero when the
+// caller is to give up.
+template <int kChainLocal>
+__device__ __forceinline__ int LayerBarrier(int tid, int failed)
+{
+    if (kChainLocal == 0)
+        return __syncthreads_or(failed);
+    const int half = tid >> 7;
+    if (kChainLocal == 1)
+    {
+        if (half)
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+        else
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        return 0;
+    }
+    uint32_t any;
+    if (half)
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "bar.red.or.pred p, 2, 128, q;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(any)
+            : "r"(failed)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "bar.red.or.pred p, 1, 128, q;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(any)
+            : "r"(failed)
+            : "memory");
+    return int(any);
+}
+
+// Which barrier a layer of the tile decoders takes: see LayerBarrier.
 template <int kLayer>
+constexpr int TileLayerBarrier()
+{
+    return (kLayer == 1 || kLayer == 2) ? 1 : 0;
+}
+
+// First half of a layer for the current tile: barrier (LayerBarrier) and MMA issue - of both chains by warp 4
+// after a CTA-wide barrier, of its own chain by the chain's first warp after a chain-local one.  Returns
+// nonzero (uniformly over the threads that met in the barrier) when some thread gave up on a wait.
+template <int kLayer, int kChainLocal = TileLayerBarrier<kLayer>()>
 __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int failed)
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
@@ -406,12 +458,13 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
     // on whether any thread gave up waiting.
     FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
-    if (__syncthreads_or(failed))
+    if (LayerBarrier<kChainLocal>(ctx.tid, failed))
         return 1;
 
     // The whole issuing warp runs the descriptor arithmetic on values that are visibly the same in every
     // lane; one elected lane hands the work to the tensor core (see IssueLayerRefFp8).
-    if ((ctx.tid >> 5) == kIssuingWarp)
+    const int warpIndex = ctx.tid >> 5;
+    if (kChainLocal ? (warpIndex & 3) == 0 : warpIndex == kIssuingWarp)
     {
         TcgenFenceAfterSync();
         constexpr uint32_t instr = MakeInstrDescriptorF16(kN);
@@ -425,9 +478,12 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
         const uint64_t weightBase = MakeSmemDescriptor(networkBase + kWeightOffset, kN * 16, 128);
         const uint64_t biasBase = MakeSmemDescriptor(networkBase + kBiasOffset, kN * 16, 128);
         const uint32_t elected = ElectOne();
+        const int ownChain = __shfl_sync(0xFFFFFFFFu, warpIndex >> 2, 0);
 #pragma unroll
         for (int half = 0; half < kRefChains; ++half)
         {
+            if (kChainLocal && half != ownChain)
+                continue;
             const uint32_t accumulators = tmemBase + half * kTmemColumnsPerHalf;
             // accumulators := bias (rows (1, 0, ...) times the bias column: exact)
             UmmaF16(accumulators, onesBase, biasBase, instr, 0, elected);
@@ -509,10 +565,10 @@ __device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefT
     }
 }
 
-template <bool kFp8, int kLayer, bool kConvert, typename Params>
+template <bool kFp8, int kLayer, bool kConvert, int kChainLocal = TileLayerBarrier<kLayer>(), typename Params>
 __device__ __forceinline__ int RunLayerRef(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
 {
-    if (IssueLayerRef<kLayer>(ctx, failed))
+    if (IssueLayerRef<kLayer, kChainLocal>(ctx, failed))
         return 1;
     ConsumeLayerRef<kFp8, kLayer, kConvert>(params, ctx, phase, failed);
     return 0;
@@ -788,10 +844,11 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernel
                 ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
         }
 
-        aborted = RunLayerRef<kFp8, 0, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRef<kFp8, 1, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRef<kFp8, 2, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRef<kFp8, 3, false>(params, ctx, phase, failed);
+        // nothing is shared between the chains of a query tile: each runs at its own pace
+        aborted = RunLayerRef<kFp8, 0, false, 2>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 1, false, 2>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 2, false, 2>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRef<kFp8, 3, false, 2>(params, ctx, phase, failed);
         if (aborted)
             break;
     }
@@ -929,7 +986,7 @@ __device__ __forceinline__ RefTileContext UniformContext(const RefTileContext& c
 // (Tried and dropped: letting the two chains run apart between tiles - each chain with its own
 // issuing thread waiting on an mbarrier its 128 threads arrive on - was 4 % slower than this
 // CTA-wide barrier with one issuing thread.)
-template <int kLayer>
+template <int kLayer, int kChainLocal = TileLayerBarrier<kLayer>()>
 __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int failed)
 {
     // Makes the A operand visible to the tensor core (async proxy), orders this thread's reads of the
@@ -941,65 +998,28 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     if (!(kAblate & 128))
         FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
-    if ((kVariant & 1) && (kLayer == 1 || kLayer == 2))
-    {
-        // experiment: the chain's 128 threads meet in a barrier of their own and the chain's first warp issues
-        const int half = ctx.tid >> 7;
-        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-        if (((ctx.tid >> 5) & 3) == 0 && !(kAblate & 16))
-        {
-            TcgenFenceAfterSync();
-            RefTileContext uniform = ctx;
-            uniform.operandA = __shfl_sync(0xFFFFFFFFu, ctx.operandA, 0);
-            uniform.biasRegion = __shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0);
-            uniform.networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
-            uniform.tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
-            uniform.barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
-            const uint32_t elected = ElectOne();
-            IssueChainRefFp8<kLayer>(uniform, __shfl_sync(0xFFFFFFFFu, half, 0), elected);
-        }
-        return 0;
-    }
-    if (kVariant & 4)
-    {
-        // experiment: the issuing warp builds its descriptors before the barrier, so that after it only the
-        // matrix products remain to be issued
-        const bool issuer = (ctx.tid >> 5) == kIssuingWarp;
-        ChainBases bases = {};
-        if (issuer)
-            bases = MakeChainBases<kLayer>(UniformContext(ctx));
-        if (__syncthreads_or(failed))
-            return 1;
-        if (issuer && !(kAblate & 16))
-        {
-            TcgenFenceAfterSync();
-            const uint32_t elected = ElectOne();
-#pragma unroll
-            for (int half = 0; half < kRefChains; ++half)
-                IssueChainRefFp8<kLayer>(bases, half, elected);
-        }
-        return 0;
-    }
     if (kAblate & 256)
         __syncthreads();
-    else if (__syncthreads_or(failed))
+    else if (LayerBarrier<kChainLocal>(ctx.tid, failed))
         return 1;
     // The whole issuing warp runs the descriptor arithmetic, on values the compiler can see are the same
     // in every lane (hence the shuffles), and one elected lane hands the work to the tensor core: issued
     // from a single thread inside a divergent branch the same code cost 85 instructions per texel more.
-    if ((ctx.tid >> 5) == kIssuingWarp && !(kAblate & 16))
+    // (Tried: building the descriptors before the barrier - 3 % slower.)
+    const int warpIndex = ctx.tid >> 5;
+    if ((kChainLocal ? (warpIndex & 3) == 0 : warpIndex == kIssuingWarp) && !(kAblate & 16))
     {
         TcgenFenceAfterSync();
-        RefTileContext uniform = ctx;
-        uniform.operandA = __shfl_sync(0xFFFFFFFFu, ctx.operandA, 0);
-        uniform.biasRegion = __shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0);
-        uniform.networkBase = __shfl_sync(0xFFFFFFFFu, ctx.networkBase, 0);
-        uniform.tmemBase = __shfl_sync(0xFFFFFFFFu, ctx.tmemBase, 0);
-        uniform.barrierBase = __shfl_sync(0xFFFFFFFFu, ctx.barrierBase, 0);
+        const ChainBases bases = MakeChainBases<kLayer>(UniformContext(ctx));
         const uint32_t elected = ElectOne();
+        if (kChainLocal)
+            IssueChainRefFp8<kLayer>(bases, __shfl_sync(0xFFFFFFFFu, warpIndex >> 2, 0), elected);
+        else
+        {
 #pragma unroll
-        for (int half = 0; half < kRefChains; ++half)
-            IssueChainRefFp8<kLayer>(uniform, half, elected);
+            for (int half = 0; half < kRefChains; ++half)
+                IssueChainRefFp8<kLayer>(bases, half, elected);
+        }
     }
     return 0;
 }
@@ -1063,8 +1083,6 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
         if (!(kAblate & 32))
         {
             TmemLoadPacked16(ctx.tmemLane, low);
-            if (kVariant & 2)
-                TmemLoadWait(); // experiment: the second load's latency under the first half's arithmetic
             if (kN == 64)
                 TmemLoadPacked16(ctx.tmemLane + 32, high);
             else
@@ -1072,8 +1090,7 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
                 uint32_t (&tail)[8] = reinterpret_cast<uint32_t (&)[8]>(high);
                 TmemLoadPacked8(ctx.tmemLane + 32, tail);
             }
-            if (!(kVariant & 2))
-                TmemLoadWait();
+            TmemLoadWait();
         }
         else
         {
@@ -1088,8 +1105,6 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 2]), ActivateToE4m3(low[8 * c + 3])),
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 4]), ActivateToE4m3(low[8 * c + 5])),
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 6]), ActivateToE4m3(low[8 * c + 7])));
-        if ((kVariant & 2) && !(kAblate & 32))
-            TmemLoadWait();
 #pragma unroll
         for (int c = 0; c < (kN - 32) / 16; ++c)
             rowChunk[(2 + c) * 128] = make_uint4(
@@ -1165,10 +1180,10 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
     }
 }
 
-template <int kLayer, bool kConvert, typename Params>
+template <int kLayer, bool kConvert, int kChainLocal = TileLayerBarrier<kLayer>(), typename Params>
 __device__ __forceinline__ int RunLayerRefFp8(const Params& params, const RefTileContext& ctx, uint32_t& phase, int& failed)
 {
-    if (IssueLayerRefFp8<kLayer>(ctx, failed))
+    if (IssueLayerRefFp8<kLayer, kChainLocal>(ctx, failed))
         return 1;
     ConsumeLayerRefFp8<kLayer, kConvert>(params, ctx, phase, failed);
     return 0;
@@ -1424,10 +1439,11 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
                 ctx.rowChunk[chunk * 128] = make_uint4(words[4 * chunk], words[4 * chunk + 1], words[4 * chunk + 2], words[4 * chunk + 3]);
         }
 
-        aborted = RunLayerRefFp8<0, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRefFp8<1, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRefFp8<2, false>(params, ctx, phase, failed);
-        if (!aborted) aborted = RunLayerRefFp8<3, false>(params, ctx, phase, failed);
+        // nothing is shared between the chains of a query tile: each runs at its own pace
+        aborted = RunLayerRefFp8<0, false, 2>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<1, false, 2>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<2, false, 2>(params, ctx, phase, failed);
+        if (!aborted) aborted = RunLayerRefFp8<3, false, 2>(params, ctx, phase, failed);
         if (aborted)
             break;
     }

@@ -24,6 +24,13 @@ __device__ __forceinline__ void MbarrierInit(uint32_t bar, uint32_t count)
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 
+// One arrival (release at CTA scope: what this thread wrote before, and what it observed, is visible to a
+// thread that sees the phase complete).
+__device__ __forceinline__ void MbarrierArrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 __device__ __forceinline__ void FenceBarrierInit()
 {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
