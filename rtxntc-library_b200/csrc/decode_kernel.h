@@ -80,6 +80,11 @@ constexpr int kRefThreadsPerCta = 128 * kRefChains;
 constexpr int kRefTmemColumns = kRefChains * kTmemColumnsPerHalf;
 constexpr int kRefFootprintHiBytes = 8192;  // the binary16 operands leave less room for the high-res footprint
 constexpr int kRefFootprintLoBytes = 4096;
+// The warp that issues the matrix products of both chains of a tile after a CTA-wide barrier, chain 0 first:
+// the first warp of chain 1.  It then waits for chain 1, whose products finish last anyway; a warp of chain 0
+// would start on its own chain's results late by the time it takes to issue chain 1's (2 %).  (After a
+// chain-local barrier each chain's first warp issues its own.)
+constexpr int kIssuingWarp = 4;
 constexpr int kCtasPerSmRef = 3;
 constexpr int kCtasPerSmRefFp8 = 4; // FP8 networks: 8-bit operands halve the A buffers
 

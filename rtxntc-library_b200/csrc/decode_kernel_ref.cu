@@ -60,24 +60,6 @@ namespace
 
 constexpr int kAblate = NTCB_ABLATE;
 
-// Nonzero in exactly one lane of the (converged) warp.
-__device__ __forceinline__ uint32_t ElectOne()
-{
-    uint32_t elected;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "elect.sync _|p, 0xFFFFFFFF;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(elected));
-    return elected;
-}
-
-// The warp that issues the matrix products of both chains of a tile, chain 0 first: the first
-// warp of chain 1.  It then waits for chain 1, whose products finish last anyway; a warp of chain 0
-// would start on its own chain's results late by the time it takes to issue chain 1's (2 %).
-constexpr int kIssuingWarp = 4;
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
 __device__ __forceinline__ void UmmaF16(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t instr, uint32_t accumulate,
@@ -384,61 +366,6 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
 // ---------------------------------------------------------------------------------------------
 // Layers
 // ---------------------------------------------------------------------------------------------
-
-// The barrier before a layer's matrix products.  The operand rows of a chain are written by the chain's
-// own 128 threads, and only they read the chain's accumulators, so between two layers of the same tile a
-// chain needs nobody else: kChainLocal = 1 makes its threads meet in a named barrier of their own (1 or 2)
-// and go on without the other chain - 3.3 % faster on the benchmark workload than the CTA-wide barrier for
-// every layer.  Giving up is then agreed on at the CTA-wide barriers that remain (kChainLocal = 0: layers 0
-// and 3 of the decode kernels, where all eight warps share the tile's tables), or, with kChainLocal = 2,
-// among the chain's threads (inference on sample, where nothing is shared).  Returns nonzero when the
-// caller is to give up.
-template <int kChainLocal>
-__device__ __forceinline__ int LayerBarrier(int tid, int failed)
-{
-    if (kChainLocal == 0)
-        return __syncthreads_or(failed);
-    const int half = tid >> 7;
-    if (kChainLocal == 1)
-    {
-        if (half)
-            asm volatile("bar.sync 2, 128;" ::: "memory");
-        else
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        return 0;
-    }
-    uint32_t any;
-    if (half)
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p, q;\n\t"
-            "setp.ne.b32 q, %1, 0;\n\t"
-            "bar.red.or.pred p, 2, 128, q;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t"
-            "}"
-            : "=r"(any)
-            : "r"(failed)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p, q;\n\t"
-            "setp.ne.b32 q, %1, 0;\n\t"
-            "bar.red.or.pred p, 1, 128, q;\n\t"
-            "selp.b32 %0, 1, 0, p;\n\t"
-            "}"
-            : "=r"(any)
-            : "r"(failed)
-            : "memory");
-    return int(any);
-}
-
-// Which barrier a layer of the tile decoders takes: see LayerBarrier.
-template <int kLayer>
-constexpr int TileLayerBarrier()
-{
-    return (kLayer == 1 || kLayer == 2) ? 1 : 0;
-}
 
 // First half of a layer for the current tile: barrier (LayerBarrier) and MMA issue - of both chains by warp 4
 // after a CTA-wide barrier, of its own chain by the chain's first warp after a chain-local one.  Returns
