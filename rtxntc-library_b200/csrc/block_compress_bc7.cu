@@ -864,12 +864,18 @@ template <bool kSingleMode>
 __global__ void __launch_bounds__(kThreads) Bc7Kernel(const Bc7Arguments args)
 {
     __shared__ uint2 staged[16 * kThreads];
-    __shared__ uint32_t modeCount[9];
+    __shared__ uint32_t binCount[2 * kThreads + 1]; // blocks per (mode, partition) pair, then where each pair's blocks start
+    __shared__ uint32_t warpTotal[kThreads / 32];
     __shared__ uint32_t order[kThreads];
 
     const int tid = threadIdx.x;
-    if (kSingleMode && tid < 9)
-        modeCount[tid] = 0;
+    if (kSingleMode)
+    {
+        binCount[tid] = 0;
+        binCount[tid + kThreads] = 0;
+        if (tid == 0)
+            binCount[2 * kThreads] = 0;
+    }
     // The CTA's 128 x 32 texels, neighbouring threads on neighbouring texels of a row, handed to the slot of
     // their block through shared memory; red-green and blue-alpha as two 32-bit words.
     const bool pairs = !(args.base.firstChannel & 1) && !(args.base.channels & 1);
@@ -918,16 +924,38 @@ __global__ void __launch_bounds__(kThreads) Bc7Kernel(const Bc7Arguments args)
                 reinterpret_cast<uint4*>(args.base.blocks + size_t(blockY) * args.base.rowPitch)[blockX] = MissingModeBlock();
                 active = false;
             }
-            // Threads trade blocks so that those of one mode sit next to each other: a warp then runs one
-            // encoder instead of up to eight in turn.
+            // Threads trade blocks so that those of one mode AND partition sit next to each other: a warp then
+            // runs one encoder, and its lanes loop over the same subsets (sorted by mode alone, as the shader
+            // does, half of the lanes idle in the pixel loops: 16 active lanes per instruction).  A counting
+            // sort over the 512 (mode, partition) pairs, blocks without work last.
             __syncthreads();
-            const uint32_t key = active ? mode : 8u;
-            const uint32_t rank = atomicAdd(&modeCount[key], 1u);
+            const uint32_t key = active ? (mode << 6 | partition) : 512u;
+            const uint32_t rank = atomicAdd(&binCount[key], 1u);
             __syncthreads();
-            uint32_t start = 0;
-            for (uint32_t m = 0; m < key; ++m)
-                start += modeCount[m];
-            order[start + rank] = uint32_t(tid) | (partition << 16) | (key << 24);
+            {
+                // exclusive prefix sum of the bins: two per thread, scanned within the warp, then over the warps
+                const uint32_t first = binCount[2 * tid], second = binCount[2 * tid + 1], pair = first + second;
+                uint32_t inclusive = pair;
+#pragma unroll
+                for (int delta = 1; delta < 32; delta *= 2)
+                {
+                    const uint32_t below = __shfl_up_sync(0xFFFFFFFFu, inclusive, delta);
+                    if ((tid & 31) >= delta)
+                        inclusive += below;
+                }
+                if ((tid & 31) == 31)
+                    warpTotal[tid >> 5] = inclusive;
+                __syncthreads();
+                uint32_t start = inclusive - pair;
+                for (int w = 0; w < (tid >> 5); ++w)
+                    start += warpTotal[w];
+                binCount[2 * tid] = start;
+                binCount[2 * tid + 1] = start + first;
+                if (tid == kThreads - 1)
+                    binCount[512] = start + pair;
+            }
+            __syncthreads();
+            order[binCount[key] + rank] = uint32_t(tid) | (partition << 16) | ((active ? mode : 8u) << 24);
             __syncthreads();
             const uint32_t task = order[tid];
             slot = int(task & 0xffffu);
