@@ -96,6 +96,39 @@ int main(int argc, char** argv)
         return 1;
     cudaFree(deviceBlocks);
 
+    // the texture whose header names BC7, by its stored mode bitmap when the file carries one
+    // (ITextureMetadata::GetBC7ModeBuffer + BlockCompressionModeBufferSource::TextureSet)
+    std::vector<unsigned char> blocks7(size_t(blocksX) * blocksY * 16);
+    void const* modes = nullptr;
+    size_t modeBytes = 0;
+    CHECK(textureSet->GetBC7ModeBuffer(1, 0, &modes, &modeBytes));
+    void* deviceBlocks7 = nullptr;
+    if (cudaMalloc(&deviceBlocks7, blocks7.size()) != cudaSuccess)
+        return 1;
+    CHECK(textureSet->BlockCompressTexture(1, 0, 1.f / 255.f, deviceBlocks7, size_t(blocksX) * 16));
+    CHECK(textureSet->Synchronize());
+    if (cudaMemcpy(blocks7.data(), deviceBlocks7, blocks7.size(), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return 1;
+    cudaFree(deviceBlocks7);
+
+    // ITextureSet::LoadFromMemory: the same file again into the same buffers; the decode must not change
+    std::vector<unsigned char> file;
+    if (std::FILE* handle = std::fopen(argv[1], "rb"))
+    {
+        unsigned char chunk[4096];
+        size_t got;
+        while ((got = std::fread(chunk, 1, sizeof chunk, handle)) > 0)
+            file.insert(file.end(), chunk, chunk + got);
+        std::fclose(handle);
+    }
+    CHECK(textureSet->LoadFromMemory(file.data(), file.size()));
+    CHECK(textureSet->Decompress(nullptr, /*useInt8Weights*/ false));
+    std::vector<uint16_t> again(texels.size());
+    read.pOutData = again.data();
+    CHECK(textureSet->ReadChannels(read));
+    std::printf("bc7 %016llx mode_bytes %zu reloaded %s\n", static_cast<unsigned long long>(Fnv1a(blocks7.data(), blocks7.size())),
+        modeBytes, again == texels ? "same" : "DIFFERENT");
+
     std::printf("texels %016llx bc4 %016llx size %dx%dx%d mips %d gpu_ms %.4f\n",
         static_cast<unsigned long long>(Fnv1a(texels.data(), texels.size() * 2)),
         static_cast<unsigned long long>(Fnv1a(blocks.data(), blocks.size())), desc.width, desc.height, desc.channels, desc.mips,
