@@ -176,7 +176,10 @@ int ntcb_stage_network(const void* blob, size_t blobBytes, int weightMode, void*
 int ntcb_stage_network_reference(const void* blob, size_t blobBytes, int weightMode, void* staged);
 
 /* Decodes the mips (and row ranges) listed in `params` with one kernel launch on `stream`.
-   Asynchronous; the caller synchronises and may then read `status`.  Allocates nothing. */
+   Asynchronous; the caller synchronises and may then read `status`.  Allocates nothing and waits for
+   nothing, so a sequence of decodes can be captured in a CUDA graph and replayed - after one ordinary
+   call of the same kind (weight mode, numerics, latent layer count, conversion or not) on the device:
+   the first use of a kernel sets a function attribute. */
 int ntcb_decode(const NtcbDecodeParams* params, void* stream);
 
 /* Inference on sample: evaluates individual texels instead of whole mips.  Query q is

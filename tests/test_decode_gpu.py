@@ -458,6 +458,41 @@ def test_inference_on_sample_matches_contract(oracle, shape, numerics):
     assert resident.sample(device_queries[:0], True).shape[0] == 0
 
 
+@pytest.mark.parametrize("numerics", [binding.NUMERICS_REFERENCE, binding.NUMERICS_EXACT], ids=["reference", "exact"])
+def test_decode_launches_replay_from_a_cuda_graph(numerics):
+    """ntcb_decode only queues work on the stream it is given, so a batch of decodes can be captured once
+    in a CUDA graph and replayed (after one eager call per kernel: its first use on a device sets a function
+    attribute).  Three sets, both weight modes, replayed twice: the same bits as the eager launches."""
+    import torch
+
+    specs = [synthetic.TextureSetSpec(200, 136, 6, 0, 2, 8, seed=31, network="unit"),
+             synthetic.TextureSetSpec(96, 40, 12, 0, 4, 12, seed=32, network="unit"),
+             synthetic.TextureSetSpec(64, 64, 4, 0, 3, 16, seed=33, network="unit")]
+    residents = [binding.ResidentTextureSet.from_synthetic(synthetic.make_texture_set(spec), numerics=numerics) for spec in specs]
+    for use_int8 in (True, False):
+        eager = []
+        for resident in residents:
+            resident.decode(use_int8)
+            torch.cuda.synchronize()
+            resident.check_status()
+            eager.append(resident.out.clone())
+        stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for resident in residents:
+                    resident.decode(use_int8)
+        for _ in range(2):
+            for resident in residents:
+                resident.out.fill_(float("nan"))
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            for resident, expected in zip(residents, eager):
+                resident.check_status()
+                assert torch.equal(resident.out.view(torch.int16), expected.view(torch.int16))
+
+
 def test_an_expired_wait_is_reported_and_leaves_the_gpu_usable():
     """The kernels' timeout path, walked without hanging or faulting anything: the test hook makes
     the FIRST wait of every CTA - for the network image, before any tile is touched and with no
