@@ -1404,33 +1404,48 @@ cudaError_t LaunchRefKernel(Kernel kernel, std::atomic<unsigned long long>& done
 
 cudaError_t LaunchDecodeRef(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)
 {
-    // fp16 output: kernels compiled for 2, 3 or 4 latent layers and one for any number; the converting
-    // epilogue comes with the general one only
-    static std::atomic<unsigned long long> done[2][5];
-    const int layers = params.convert || params.numLayers < 2 || params.numLayers > 4 ? 0 : params.numLayers;
+    // kernels compiled for 2, 3 or 4 latent layers and one for any number, each with and without the
+    // converting epilogue
+    static std::atomic<unsigned long long> done[2][2][5];
+    const int layers = params.numLayers < 2 || params.numLayers > 4 ? 0 : params.numLayers;
+    const int convert = params.convert ? 1 : 0;
     if (fp8)
     {
         // FP8 networks take the kernel with 8-bit operands (same bits, four CTAs per SM)
         const size_t bytes = sizeof(RefFp8SharedStorage);
-        if (params.convert)
-            return LaunchRefKernel(DecodeKernelRefFp8<true, 0>, done[1][4], bytes, kThreadsPerCta, params, ctas, stream);
+        std::atomic<unsigned long long>& flag = done[1][convert][layers];
+        if (convert)
+            switch (layers)
+            {
+            case 2: return LaunchRefKernel(DecodeKernelRefFp8<true, 2>, flag, bytes, kThreadsPerCta, params, ctas, stream);
+            case 3: return LaunchRefKernel(DecodeKernelRefFp8<true, 3>, flag, bytes, kThreadsPerCta, params, ctas, stream);
+            case 4: return LaunchRefKernel(DecodeKernelRefFp8<true, 4>, flag, bytes, kThreadsPerCta, params, ctas, stream);
+            default: return LaunchRefKernel(DecodeKernelRefFp8<true, 0>, flag, bytes, kThreadsPerCta, params, ctas, stream);
+            }
         switch (layers)
         {
-        case 2: return LaunchRefKernel(DecodeKernelRefFp8<false, 2>, done[1][2], bytes, kThreadsPerCta, params, ctas, stream);
-        case 3: return LaunchRefKernel(DecodeKernelRefFp8<false, 3>, done[1][3], bytes, kThreadsPerCta, params, ctas, stream);
-        case 4: return LaunchRefKernel(DecodeKernelRefFp8<false, 4>, done[1][1], bytes, kThreadsPerCta, params, ctas, stream);
-        default: return LaunchRefKernel(DecodeKernelRefFp8<false, 0>, done[1][0], bytes, kThreadsPerCta, params, ctas, stream);
+        case 2: return LaunchRefKernel(DecodeKernelRefFp8<false, 2>, flag, bytes, kThreadsPerCta, params, ctas, stream);
+        case 3: return LaunchRefKernel(DecodeKernelRefFp8<false, 3>, flag, bytes, kThreadsPerCta, params, ctas, stream);
+        case 4: return LaunchRefKernel(DecodeKernelRefFp8<false, 4>, flag, bytes, kThreadsPerCta, params, ctas, stream);
+        default: return LaunchRefKernel(DecodeKernelRefFp8<false, 0>, flag, bytes, kThreadsPerCta, params, ctas, stream);
         }
     }
     const size_t bytes = sizeof(RefSharedStorage);
-    if (params.convert)
-        return LaunchRefKernel(DecodeKernelRef<false, true, 0>, done[0][4], bytes, kRefThreadsPerCta, params, ctas, stream);
+    std::atomic<unsigned long long>& flag = done[0][convert][layers];
+    if (convert)
+        switch (layers)
+        {
+        case 2: return LaunchRefKernel(DecodeKernelRef<false, true, 2>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
+        case 3: return LaunchRefKernel(DecodeKernelRef<false, true, 3>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
+        case 4: return LaunchRefKernel(DecodeKernelRef<false, true, 4>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
+        default: return LaunchRefKernel(DecodeKernelRef<false, true, 0>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
+        }
     switch (layers)
     {
-    case 2: return LaunchRefKernel(DecodeKernelRef<false, false, 2>, done[0][2], bytes, kRefThreadsPerCta, params, ctas, stream);
-    case 3: return LaunchRefKernel(DecodeKernelRef<false, false, 3>, done[0][3], bytes, kRefThreadsPerCta, params, ctas, stream);
-    case 4: return LaunchRefKernel(DecodeKernelRef<false, false, 4>, done[0][1], bytes, kRefThreadsPerCta, params, ctas, stream);
-    default: return LaunchRefKernel(DecodeKernelRef<false, false, 0>, done[0][0], bytes, kRefThreadsPerCta, params, ctas, stream);
+    case 2: return LaunchRefKernel(DecodeKernelRef<false, false, 2>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
+    case 3: return LaunchRefKernel(DecodeKernelRef<false, false, 3>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
+    case 4: return LaunchRefKernel(DecodeKernelRef<false, false, 4>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
+    default: return LaunchRefKernel(DecodeKernelRef<false, false, 0>, flag, bytes, kRefThreadsPerCta, params, ctas, stream);
     }
 }
 
