@@ -41,7 +41,8 @@
 #include "output_convert.cuh"
 #include "epilogue_convert.cuh"
 
-// Profiling aid: NTCB_ABLATE (a bit mask, 0 in the product build) removes one phase of
+// Profiling aid: NTCB_ABLATE (a bit mask, 0 in the product build; 512: no tile walk, every tile at the place of the CTA's
+// first; 1024: no barrier before a layer's products - only together with 16) removes one phase of
 // DecodeKernelRefFp8 at a time so that its share of the kernel's instructions and time can be
 // measured as a difference (`make ablations` builds one library per mask; their output is wrong by
 // construction).  1: the per-tile tables and footprint staging after the first tile; 2: the latent
@@ -925,7 +926,9 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     if (!(kAblate & 128))
         FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
-    if (kAblate & 256)
+    if (kAblate & 1024)
+        ;
+    else if (kAblate & 256)
         __syncthreads();
     else if (LayerBarrier<kChainLocal>(ctx.tid, failed))
         return 1;
@@ -1246,9 +1249,10 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) DecodeKernel
         const int nextTile = tile + int(gridDim.x);
         if (nextTile < params.totalTiles)
         {
-            place = locate(nextTile, place.mipIndex);
+            if (!(kAblate & 512))
+                place = locate(nextTile, place.mipIndex);
             // the tables of the previous tile serve this one too when both lie inside the same mip with invariant tables
-            const bool keepsTables = TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
+            const bool keepsTables = (kAblate & 512) ? true : TileKeepsTables(params.mips[place.mipIndex], place.tileX0, place.tileY0);
             if (!(kAblate & 1))
                 PrepareTile<true, true, kLayers>(params, params.mips[place.mipIndex], shared, place.tileX0, place.tileY0, lane, warp,
                     keepsTables && place.mipIndex == tablesMip && !(kAblate & 64));
