@@ -60,6 +60,14 @@ namespace
 {
 
 constexpr int kAblate = NTCB_ABLATE;
+// FP8 networks: the A operand of layers 1-3 lives in tensor memory, not in shared memory.  A layer's 64-byte
+// input row is 16 of the 32-bit columns of its thread's own TMEM lane; layers 1-3 have at most 48 outputs,
+// so their accumulators leave columns 48..63 of the chain's 64 free for it.  (Layer 0 has 64 outputs: its
+// operand, the gathered inputs, stays in shared memory.)  The activations are stored with tcgen05.st, the
+// products read them with the A-in-tensor-memory form of tcgen05.mma: no shared-memory stores, no proxy
+// fence, and no operand reads from shared memory by the tensor core for three of the four layers (3 %).
+constexpr bool kTmemOperand = true;
+constexpr uint32_t kOperandColumn = 48;
 
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 16 binary16 operands, binary16 accumulators.
@@ -368,6 +376,29 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
 // Layers
 // ---------------------------------------------------------------------------------------------
 
+// Int8 networks (binary16 operands, 128-byte rows): the inputs of layers 2 and 3 - 48 and 32 halves, 24 and 16
+// tensor-memory columns - fit beside those layers' 32 and 16 accumulator columns in a chain's 64, from column 32
+// on; layer 1's 64 halves do not fit beside its 48 accumulators and stay in shared memory, like layer 0's.
+constexpr uint32_t kRefOperandColumn = 32;
+template <int kLayer>
+constexpr bool kRefOperandInTmem = kLayer >= 2;
+
+// D[tmem] (+)= A[tmem] * B[smem]^T with binary16 operands: the A operand in tensor memory (lane = row, two K
+// values per column).
+__device__ __forceinline__ void UmmaF16FromTmem(uint32_t tmemD, uint32_t tmemA, uint64_t descB, uint32_t instr, uint32_t accumulate,
+    uint32_t enabled)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}" ::"r"(tmemD),
+        "r"(tmemA), "l"(descB), "r"(instr), "r"(accumulate), "r"(enabled)
+        : "memory");
+}
+
 // First half of a layer for the current tile: barrier (LayerBarrier) and MMA issue - of both chains by warp 4
 // after a CTA-wide barrier, of its own chain by the chain's first warp after a chain-local one.  Returns
 // nonzero (uniformly over the threads that met in the barrier) when some thread gave up on a wait.
@@ -384,7 +415,10 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
     // Makes the A operand written before this call visible to the tensor core, orders every
     // thread's TMEM reads of the previous layer before the accumulators are overwritten, and agrees
     // on whether any thread gave up waiting.
-    FenceProxyAsyncShared();
+    if (kRefOperandInTmem<kLayer>)
+        TmemStoreWait(); // the operand went to tensor memory: nothing the async proxy reads was written
+    else
+        FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
     if (LayerBarrier<kChainLocal>(ctx.tid, failed))
         return 1;
@@ -421,7 +455,10 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
                 // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
                 const uint64_t descA = operandBase + uint64_t((half * kRefOperandBytes + kStep * 2 * 2048) >> 4);
                 const uint64_t descB = weightBase + uint64_t((kStep * 2 * kN * 16) >> 4);
-                UmmaF16(accumulators, descA, descB, instr, 1, elected);
+                if (kRefOperandInTmem<kLayer>)
+                    UmmaF16FromTmem(accumulators, accumulators + kRefOperandColumn + uint32_t(kStep) * 8u, descB, instr, 1, elected);
+                else
+                    UmmaF16(accumulators, descA, descB, instr, 1, elected);
             }
             // arrives once everything issued so far has completed: this chain's accumulators are ready
             if (elected)
@@ -462,14 +499,21 @@ __device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefT
             TmemLoadPacked8(ctx.tmemLane + 32, tail);
         }
         TmemLoadWait();
+        // chunk c (8 halves) of the next layer's operand row: to shared memory, or to tensor-memory columns 32 + 4 c ..
+        auto storeChunk = [&](int c, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+            if (kRefOperandInTmem<kLayer + 1>)
+                TmemStore4(ctx.tmemLane + kRefOperandColumn + 4u * uint32_t(c), w0, w1, w2, w3);
+            else
+                rowChunk[c * 128] = make_uint4(w0, w1, w2, w3);
+        };
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-            rowChunk[c * 128] = make_uint4(ActivateRef<kNextFp8>(low[4 * c]), ActivateRef<kNextFp8>(low[4 * c + 1]),
-                                           ActivateRef<kNextFp8>(low[4 * c + 2]), ActivateRef<kNextFp8>(low[4 * c + 3]));
+            storeChunk(c, ActivateRef<kNextFp8>(low[4 * c]), ActivateRef<kNextFp8>(low[4 * c + 1]),
+                       ActivateRef<kNextFp8>(low[4 * c + 2]), ActivateRef<kNextFp8>(low[4 * c + 3]));
 #pragma unroll
         for (int c = 0; c < (kN - 32) / 8; ++c)
-            rowChunk[(4 + c) * 128] = make_uint4(ActivateRef<kNextFp8>(high[4 * c]), ActivateRef<kNextFp8>(high[4 * c + 1]),
-                                                 ActivateRef<kNextFp8>(high[4 * c + 2]), ActivateRef<kNextFp8>(high[4 * c + 3]));
+            storeChunk(4 + c, ActivateRef<kNextFp8>(high[4 * c]), ActivateRef<kNextFp8>(high[4 * c + 1]),
+                       ActivateRef<kNextFp8>(high[4 * c + 2]), ActivateRef<kNextFp8>(high[4 * c + 3]));
     }
     else
     {
@@ -828,6 +872,21 @@ __device__ __forceinline__ void UmmaE4m3F16(uint32_t tmemD, uint64_t descA, uint
         : "memory");
 }
 
+// The same two products with the A operand in tensor memory (lane = row, four 8-bit or two 16-bit K values per column).
+__device__ __forceinline__ void UmmaE4m3F16FromTmem(uint32_t tmemD, uint32_t tmemA, uint64_t descB, uint32_t instr, uint32_t accumulate,
+    uint32_t enabled)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t"
+        "}" ::"r"(tmemD),
+        "r"(tmemA), "l"(descB), "r"(instr), "r"(accumulate), "r"(enabled)
+        : "memory");
+}
+
 // What the matrix products of a layer address, the same for every tile: descriptors of the operand regions
 // (those of chain 1 lie kOperandBytes further) and the accumulator columns.
 struct ChainBases
@@ -876,14 +935,20 @@ __device__ __forceinline__ void IssueChainRefFp8(const ChainBases& bases, int ha
             // 16 products of the 32-wide chunk step / 2: weight copy `step` has the other 16 columns zeroed
             const uint64_t descA = operandBase + uint64_t(((step / 2) * 2 * 2048) >> 4);
             const uint64_t descB = bases.weight + uint64_t((step * kN * 32) >> 4);
-            UmmaE4m3F16(accumulators, descA, descB, instr, 1, enabled);
+            if (kTmemOperand && kLayer > 0)
+                UmmaE4m3F16FromTmem(accumulators, accumulators + kOperandColumn + uint32_t(step / 2) * 8u, descB, instr, 1, enabled);
+            else
+                UmmaE4m3F16(accumulators, descA, descB, instr, 1, enabled);
         }
         else
         {
             // binary16 operands: one K step = two core matrices of 8 halves
             const uint64_t descA = operandBase + uint64_t((step * 2 * 2048) >> 4);
             const uint64_t descB = bases.weight + uint64_t((step * 2 * kN * 16) >> 4);
-            UmmaF16(accumulators, descA, descB, instr, 1, enabled);
+            if (kTmemOperand)
+                UmmaF16FromTmem(accumulators, accumulators + kOperandColumn + uint32_t(step) * 8u, descB, instr, 1, enabled);
+            else
+                UmmaF16(accumulators, descA, descB, instr, 1, enabled);
         }
     }
     // arrives once everything issued so far has completed: this chain's accumulators are ready
@@ -923,7 +988,9 @@ __device__ __forceinline__ int IssueLayerRefFp8(const RefTileContext& ctx, int f
     // documented pattern.  A single fence in the issuing warp after the barrier passed every parity test
     // and was 2 % faster - the fence costs each thread about 200 cycles - but is not what the
     // programming guide shows, so it was not adopted.)
-    if (!(kAblate & 128))
+    if (kTmemOperand && kLayer > 0)
+        TmemStoreWait(); // the operand went to tensor memory: nothing the async proxy reads was written
+    else if (!(kAblate & 128))
         FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
     if (kAblate & 1024)
@@ -1003,7 +1070,12 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-            rowChunk[c * 128] = make_uint4(low[4 * c], low[4 * c + 1], low[4 * c + 2], low[4 * c + 3]);
+        {
+            if (kTmemOperand)
+                TmemStore4(ctx.tmemLane + kOperandColumn + 4u * uint32_t(c), low[4 * c], low[4 * c + 1], low[4 * c + 2], low[4 * c + 3]);
+            else
+                rowChunk[c * 128] = make_uint4(low[4 * c], low[4 * c + 1], low[4 * c + 2], low[4 * c + 3]);
+        }
         return;
     }
 
@@ -1030,22 +1102,29 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
             for (int i = 0; i < 16; ++i)
                 low[i] = high[i] = uint32_t(ctx.tile * 3 + i) & 0x3FFF3FFFu;
         }
+        // chunk c of the next layer's operand row: to shared memory, or to tensor memory columns 48 + 4 c ..
+        auto storeChunk = [&](int c, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
+            if (kTmemOperand)
+                TmemStore4(ctx.tmemLane + kOperandColumn + 4u * uint32_t(c), w0, w1, w2, w3);
+            else
+                rowChunk[c * 128] = make_uint4(w0, w1, w2, w3);
+        };
 #pragma unroll
         for (int c = 0; c < 2; ++c)
-            rowChunk[c * 128] = make_uint4(
+            storeChunk(c,
                 PackCodes<true>(ActivateToE4m3(low[8 * c]), ActivateToE4m3(low[8 * c + 1])),
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 2]), ActivateToE4m3(low[8 * c + 3])),
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 4]), ActivateToE4m3(low[8 * c + 5])),
                 PackCodes<true>(ActivateToE4m3(low[8 * c + 6]), ActivateToE4m3(low[8 * c + 7])));
 #pragma unroll
         for (int c = 0; c < (kN - 32) / 16; ++c)
-            rowChunk[(2 + c) * 128] = make_uint4(
+            storeChunk(2 + c,
                 PackCodes<true>(ActivateToE4m3(high[8 * c]), ActivateToE4m3(high[8 * c + 1])),
                 PackCodes<true>(ActivateToE4m3(high[8 * c + 2]), ActivateToE4m3(high[8 * c + 3])),
                 PackCodes<true>(ActivateToE4m3(high[8 * c + 4]), ActivateToE4m3(high[8 * c + 5])),
                 PackCodes<true>(ActivateToE4m3(high[8 * c + 6]), ActivateToE4m3(high[8 * c + 7])));
         if (kLayer == 1)
-            rowChunk[3 * 128] = make_uint4(0, 0, 0, 0); // layer 2 has 48 inputs: the rest of its second chunk must be zeros
+            storeChunk(3, 0, 0, 0, 0); // layer 2 has 48 inputs: the rest of its second chunk must be zeros
     }
     else if (kLayer == 2)
     {
@@ -1065,8 +1144,14 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-            rowChunk[c * 128] = make_uint4(ActivateRef<false>(acc[4 * c]), ActivateRef<false>(acc[4 * c + 1]),
-                                           ActivateRef<false>(acc[4 * c + 2]), ActivateRef<false>(acc[4 * c + 3]));
+        {
+            const uint32_t w0 = ActivateRef<false>(acc[4 * c]), w1 = ActivateRef<false>(acc[4 * c + 1]);
+            const uint32_t w2 = ActivateRef<false>(acc[4 * c + 2]), w3 = ActivateRef<false>(acc[4 * c + 3]);
+            if (kTmemOperand)
+                TmemStore4(ctx.tmemLane + kOperandColumn + 4u * uint32_t(c), w0, w1, w2, w3);
+            else
+                rowChunk[c * 128] = make_uint4(w0, w1, w2, w3);
+        }
     }
     else
     {

@@ -135,6 +135,18 @@ __device__ __forceinline__ void TmemLoad16(uint32_t address, uint32_t (&r)[16])
         : "memory");
 }
 
+// Four consecutive 32-bit columns of this thread's TMEM lane, written.
+__device__ __forceinline__ void TmemStore4(uint32_t address, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ void TmemStoreWait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void TmemLoadWait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
