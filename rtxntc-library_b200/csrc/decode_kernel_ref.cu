@@ -10,8 +10,12 @@
 //
 // What differs from decode_kernel.cu:
 //   * the A operand holds binary16 values (the de-quantised network inputs / activations), 128 bytes
-//     per row, written by the threads in K-major core-matrix order: 16-byte chunk j (8 halves) of
-//     row r at j * 2048 + r * 16;
+//     per row.  Layers 0 and 1 read it from shared memory, written by the threads in K-major
+//     core-matrix order (16-byte chunk j, 8 halves, of row r at j * 2048 + r * 16); layers 2 and 3 read
+//     it from tensor memory, where the activation step stores it (columns 32.. of the chain's 64,
+//     beside those layers' accumulators);
+//   * between the layers of a tile the two chains do not wait for each other (LayerBarrier,
+//     kernel_parts.cuh);
 //   * each layer starts with a "bias step": an MMA whose A operand is a constant region with rows
 //     (1, 0, ..., 0) and whose B operand holds the bias in column 0, which sets the accumulators to
 //     the binary16 bias exactly; the K = 16 steps of the layer then accumulate onto it;
@@ -24,7 +28,7 @@
 //
 // Two kernels live here.  DecodeKernelRef (first part of the file) keeps every operand in binary16
 // and serves Int8 networks.  DecodeKernelRefFp8 (second part) serves FP8 networks with 8-bit operands
-// for layers 0-2 and produces the same bits; since ntcb_stage_network_reference lays an FP8
+// for layers 0-2 (those of layers 1-3 in tensor memory) and produces the same bits; since ntcb_stage_network_reference lays an FP8
 // network out for it, the binary16 kernel's templates are only instantiated with kFp8 = false
 // (their kFp8 = true paths describe what the FP8 kernel replaces: e4m3 round trips in binary16).
 
@@ -1039,7 +1043,6 @@ __device__ __forceinline__ void ConsumeLayerRefFp8(const Params& params, const R
 {
     constexpr int kN = kLayer == 0 ? 64 : kLayer == 1 ? 48 : kLayer == 2 ? 32 : 16;
 
-    // one warp of the chain polls for the chain's matrix products, the other three wait for it in a named barrier
     // (Every warp polls the barrier itself.  Tried and dropped: one polling warp per chain with the other
     // three blocked in a named barrier executes 1.5 % fewer instructions but wakes the chain later, 4.5 %
     // slower; an issuing thread per chain instead of one for both, 7 % slower; polls without a suspend-time
