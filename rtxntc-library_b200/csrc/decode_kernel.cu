@@ -16,7 +16,8 @@
 //      instruction) against the weights resident in shared memory; accumulators live in TMEM;
 //   3. after the commit arrives on the mbarrier every thread pulls its row of accumulators with
 //      tcgen05.ld, applies bias/scale and the clamped HGELU in packed binary16, re-quantises and
-//      writes the next layer's A operand over the previous one;
+//      writes the next layer's A operand over the previous one - with FP8 weights into tensor memory
+//      (tcgen05.st; the next product takes A from there), with Int8 weights into shared memory;
 //   4. after the fourth layer the epilogue scales, converts to fp16 and stores.
 //
 // Arithmetic contract (what the CPU checker restates): everything outside the matrix products is
@@ -76,6 +77,45 @@ __device__ __forceinline__ void Umma(uint32_t tmemD, uint64_t descA, uint64_t de
             : "memory");
     }
 }
+
+// The same with the A operand in tensor memory: 8 columns (32 bytes per lane) starting at `tmemA`.
+template <bool kFp8>
+__device__ __forceinline__ void UmmaFromTmem(uint32_t tmemD, uint32_t tmemA, uint64_t descB, uint32_t instr, uint32_t accumulate)
+{
+    if (kFp8)
+    {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t"
+            "}" ::"r"(tmemD),
+            "r"(tmemA), "l"(descB), "r"(instr), "r"(accumulate)
+            : "memory");
+    }
+    else
+    {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t"
+            "}" ::"r"(tmemD),
+            "r"(tmemA), "l"(descB), "r"(instr), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// FP8 networks keep the A operands of layers 1-3 in tensor memory: the activation codes of a row (at most
+// 64 bytes) go to columns [0,16) of the row's lane, and the accumulators of those layers start at column
+// 16 (48 + 16 = 64 columns per chain).  Layer 0 reads its operand from shared memory and accumulates into
+// columns [0,64); its consumer has loaded columns [0,32) before it stores the first codes to [0,8), and
+// [32,64) before it stores to [8,16).  Int8 networks have the bias K step's operand in shared memory
+// and 65 - 80 operand bytes per row: they keep every operand there.
+template <bool kFp8, int kLayer>
+constexpr bool kOperandInTmem = kFp8 && kLayer >= 1;
+template <bool kFp8, int kLayer>
+constexpr uint32_t kAccumulatorColumn = kOperandInTmem<kFp8, kLayer> ? 16u : 0u;
 
 // Instruction descriptor: dense, K-major A and B, M = 128.
 __host__ __device__ constexpr uint32_t MakeInstrDescriptor(bool fp8, int n)
@@ -170,7 +210,10 @@ __device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
     // Makes the A operand written before this call visible to the tensor core, orders every
     // thread's TMEM reads of the previous layer before the accumulators are overwritten, and agrees
     // on whether any thread gave up waiting.
-    FenceProxyAsyncShared();
+    if (kOperandInTmem<kFp8, kLayer>)
+        TmemStoreWait();
+    else
+        FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
     if (__syncthreads_or(failed))
         return 1;
@@ -188,7 +231,11 @@ __device__ __forceinline__ int IssueLayer(const TileContext& ctx, int failed)
                 // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
                 uint64_t descA = MakeSmemDescriptor(ctx.operandA + half * kOperandBytes + kStep * 2 * 2048, 2048, 128);
                 uint64_t descB = MakeSmemDescriptor(ctx.networkBase + kWeightOffset + kStep * 2 * kN * 16, kN * 16, 128);
-                Umma<kLayerFp8>(ctx.tmemBase + half * kTmemColumnsPerHalf, descA, descB, instr, kStep != 0);
+                if (kOperandInTmem<kFp8, kLayer>)
+                    UmmaFromTmem<kLayerFp8>(ctx.tmemBase + half * kTmemColumnsPerHalf + kAccumulatorColumn<kFp8, kLayer>,
+                        ctx.tmemBase + half * kTmemColumnsPerHalf + kStep * 8, descB, instr, kStep != 0);
+                else
+                    Umma<kLayerFp8>(ctx.tmemBase + half * kTmemColumnsPerHalf, descA, descB, instr, kStep != 0);
             }
             if (kBiasStep)
             {
@@ -239,7 +286,7 @@ __device__ __forceinline__ void ConsumeLayerImpl(const Params& params, const Sha
 #pragma unroll
             for (int c = 0; c < 2; ++c)
                 if (firstChunk + c < kChunksTotal)
-                    TmemLoad16(ctx.tmemLane + (firstChunk + c) * 16, acc[c]);
+                    TmemLoad16(ctx.tmemLane + kAccumulatorColumn<kFp8, kLayer> + (firstChunk + c) * 16, acc[c]);
             TmemLoadWait();
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -266,9 +313,13 @@ __device__ __forceinline__ void ConsumeLayerImpl(const Params& params, const Sha
                         }
                         pairs[j] = ActivatePair<kNextFp8>(xh);
                     }
-                    rowChunk[(firstChunk + c) * 128] =
+                    const uint4 codes =
                         make_uint4(PackCodes<kNextFp8>(pairs[0], pairs[1]), PackCodes<kNextFp8>(pairs[2], pairs[3]),
                                    PackCodes<kNextFp8>(pairs[4], pairs[5]), PackCodes<kNextFp8>(pairs[6], pairs[7]));
+                    if (kFp8)
+                        TmemStore4(ctx.tmemLane + (firstChunk + c) * 4, codes.x, codes.y, codes.z, codes.w);
+                    else
+                        rowChunk[(firstChunk + c) * 128] = codes;
                 }
             }
         }
@@ -276,14 +327,17 @@ __device__ __forceinline__ void ConsumeLayerImpl(const Params& params, const Sha
         {
             // layer 2 has 48 inputs, K is padded to 64: zeros (e4m3) or the bias slots' inputs (int8)
             const uint32_t fill = kFp8 ? 0u : kBiasSlotValue * 0x01010101u;
-            rowChunk[3 * 128] = make_uint4(fill, fill, fill, kFp8 ? 0u : ((fill & 0x00FFFFFFu) | 0x01000000u));
+            if (kFp8)
+                TmemStore4(ctx.tmemLane + 12, 0u, 0u, 0u, 0u);
+            else
+                rowChunk[3 * 128] = make_uint4(fill, fill, fill, (fill & 0x00FFFFFFu) | 0x01000000u);
         }
     }
     else
     {
         // output epilogue (src/Inference.cu:121-135)
         uint32_t acc[16];
-        TmemLoad16(ctx.tmemLane, acc);
+        TmemLoad16(ctx.tmemLane + kAccumulatorColumn<kFp8, kLayer>, acc);
         TmemLoadWait();
         const int channelPairs = channels >> 1;
         uint32_t bits[8];
