@@ -455,8 +455,11 @@ struct NtcbBatchDecoder
                         snapshot = scheduler.units[size_t(unit)];
                     }
                     snapshot.device = device;
-                    const int result = options.worker ? options.worker(options.workerUser, device, &snapshot)
-                                                      : worker.Run(current->items[snapshot.item], current->descs[snapshot.item], snapshot);
+                    // (an exception - the host containers running out of memory - fails the unit like any other error)
+                    const int result = Guarded("batch worker", [&]() {
+                        return options.worker ? options.worker(options.workerUser, device, &snapshot)
+                                              : worker.Run(current->items[snapshot.item], current->descs[snapshot.item], snapshot);
+                    });
                     scheduler.Complete(unit, position, device, result);
                 }
             {
@@ -482,7 +485,7 @@ int ntcb_plan_batch(const NtcbTextureSetDesc* descs, int numItems, int numDevice
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     std::vector<NtcbBatchUnit> planned;
-    int status = PlanUnits(descs, numItems, numDevices, unitsPerDevice > 0 ? unitsPerDevice : 4, planned);
+    int status = Guarded(__func__, [&]() { return PlanUnits(descs, numItems, numDevices, unitsPerDevice > 0 ? unitsPerDevice : 4, planned); });
     if (status != NTCB_OK)
         return status;
     *outNumUnits = int(planned.size());
@@ -527,12 +530,23 @@ int ntcb_batch_decoder_create(const int* devices, int numDevices, const NtcbBatc
         SetError("ntcb_batch_decoder_create: unknown numerics %d.", opt.numerics);
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    NtcbBatchDecoder* decoder = new NtcbBatchDecoder;
-    decoder->devices.assign(devices, devices + numDevices);
-    decoder->options = opt;
-    for (int position = 0; position < numDevices; ++position)
-        for (int w = 0; w < opt.workersPerDevice; ++w)
-            decoder->threads.emplace_back([decoder, position]() { decoder->WorkerLoop(position); });
+    NtcbBatchDecoder* decoder = nullptr;
+    int status = Guarded(__func__, [&]() {
+        decoder = new NtcbBatchDecoder;
+        decoder->devices.assign(devices, devices + numDevices);
+        decoder->options = opt;
+        decoder->threads.reserve(size_t(numDevices) * size_t(opt.workersPerDevice));
+        for (int position = 0; position < numDevices; ++position)
+            for (int w = 0; w < opt.workersPerDevice; ++w)
+                decoder->threads.emplace_back([decoder, position]() { decoder->WorkerLoop(position); });
+        return NTCB_OK;
+    });
+    if (status != NTCB_OK)
+    {
+        // the threads that did start are told to leave and joined; the message of the failure stays
+        ntcb_batch_decoder_destroy(decoder);
+        return status;
+    }
     *outDecoder = decoder;
     ClearError();
     return NTCB_OK;
@@ -552,15 +566,10 @@ void ntcb_batch_decoder_destroy(NtcbBatchDecoder* decoder)
     delete decoder;
 }
 
-int ntcb_batch_decoder_run(NtcbBatchDecoder* decoder, NtcbBatchItem* items, int numItems, NtcbBatchUnit* outUnits, int maxUnits,
+static int RunBatch(NtcbBatchDecoder* decoder, NtcbBatchItem* items, int numItems, NtcbBatchUnit* outUnits, int maxUnits,
     int* outNumUnits)
 {
     using namespace ntcb;
-    if (!decoder || !items || numItems < 1)
-    {
-        SetError("ntcb_batch_decoder_run: needs a decoder and items.");
-        return NTCB_ERR_INVALID_ARGUMENT;
-    }
     std::lock_guard<std::mutex> oneRunAtATime(decoder->runMutex);
     const NtcbBatchOptions& opt = decoder->options;
     const int numDevices = int(decoder->devices.size());
@@ -582,17 +591,32 @@ int ntcb_batch_decoder_run(NtcbBatchDecoder* decoder, NtcbBatchItem* items, int 
         std::vector<int> probeStatus(numItems, NTCB_OK);
         std::vector<std::string> probeMessage(numItems);
         std::vector<std::thread> pool;
-        for (int t = 0; t < probers; ++t)
-            pool.emplace_back([&, t]() {
-                for (int i = t; i < numItems; i += probers)
-                {
-                    probeStatus[i] = ntcb_probe_container(items[i].container, items[i].containerBytes, &descs[i]);
-                    if (probeStatus[i] != NTCB_OK)
-                        probeMessage[i] = ntcb_last_error(); // the message is the probing thread's
-                }
-            });
-        for (std::thread& thread : pool)
-            thread.join();
+        struct JoinAll // also when starting one of the threads throws
+        {
+            std::vector<std::thread>& threads;
+            ~JoinAll()
+            {
+                for (std::thread& thread : threads)
+                    if (thread.joinable())
+                        thread.join();
+            }
+        };
+        {
+            JoinAll joinAll{pool};
+            pool.reserve(size_t(probers));
+            for (int t = 0; t < probers; ++t)
+                pool.emplace_back([&, t]() {
+                    for (int i = t; i < numItems; i += probers)
+                    {
+                        probeStatus[i] = ntcb_probe_container(items[i].container, items[i].containerBytes, &descs[i]);
+                        if (probeStatus[i] != NTCB_OK)
+                            (void)Guarded("ntcb_probe_container", [&]() {
+                                probeMessage[i] = ntcb_last_error(); // the message is the probing thread's
+                                return NTCB_OK;
+                            });
+                    }
+                });
+        }
         for (int i = 0; i < numItems; ++i)
             if (probeStatus[i] != NTCB_OK)
             {
@@ -648,6 +672,19 @@ int ntcb_batch_decoder_run(NtcbBatchDecoder* decoder, NtcbBatchItem* items, int 
     }
     ClearError();
     return NTCB_OK;
+}
+
+int ntcb_batch_decoder_run(NtcbBatchDecoder* decoder, NtcbBatchItem* items, int numItems, NtcbBatchUnit* outUnits, int maxUnits,
+    int* outNumUnits)
+{
+    using namespace ntcb;
+    if (!decoder || !items || numItems < 1)
+    {
+        SetError("ntcb_batch_decoder_run: needs a decoder and items.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    // (the workers are handed the job only after everything that can throw here has been allocated)
+    return Guarded(__func__, [&]() { return RunBatch(decoder, items, numItems, outUnits, maxUnits, outNumUnits); });
 }
 
 int ntcb_decode_batch(NtcbBatchItem* items, int numItems, const int* devices, int numDevices, const NtcbBatchOptions* options,

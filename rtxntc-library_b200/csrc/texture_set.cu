@@ -1185,7 +1185,7 @@ int ntcb_probe_container(const void* data, size_t size, NtcbTextureSetDesc* outD
         return NTCB_ERR_INVALID_ARGUMENT;
     }
     ntcb::LoadedSet loaded;
-    int status = ntcb::LoadContainer(data, size, loaded);
+    int status = ntcb::Guarded(__func__, [&]() { return ntcb::LoadContainer(data, size, loaded); });
     if (status != NTCB_OK)
         return status;
     FillDesc(loaded.geometry, outDesc);
@@ -1195,7 +1195,7 @@ int ntcb_probe_container(const void* data, size_t size, NtcbTextureSetDesc* outD
 int ntcb_probe_container_texture(const void* data, size_t size, int index, NtcbTextureDesc* outTexture, int* outCount)
 {
     ntcb::LoadedSet loaded;
-    int status = ntcb::LoadContainer(data, size, loaded);
+    int status = ntcb::Guarded(__func__, [&]() { return ntcb::LoadContainer(data, size, loaded); });
     if (status != NTCB_OK)
         return status;
     if (outCount)
@@ -1213,7 +1213,7 @@ int ntcb_probe_container_bc7_mode_buffer(const void* data, size_t size, int text
     if (outCompressed)
         *outCompressed = 0;
     ntcb::LoadedSet loaded;
-    int status = ntcb::LoadContainer(data, size, loaded);
+    int status = ntcb::Guarded(__func__, [&]() { return ntcb::LoadContainer(data, size, loaded); });
     if (status != NTCB_OK)
         return status;
     if (textureIndex < 0 || textureIndex >= int(loaded.textures.size()))
@@ -1248,10 +1248,16 @@ int ntcb_context_create(int cudaDevice, NtcbContext** outContext)
     ntcb::ContextParameters params;
     params.cudaDevice = cudaDevice;
     ntcb::IContext* impl = nullptr;
-    int status = ntcb::CreateContext(&impl, params);
+    int status = ntcb::Guarded(__func__, [&]() { return ntcb::CreateContext(&impl, params); });
     if (status != NTCB_OK)
         return status;
-    *outContext = new NtcbContext{impl};
+    *outContext = new (std::nothrow) NtcbContext{impl};
+    if (!*outContext)
+    {
+        ntcb::DestroyContext(impl);
+        ntcb::SetError("ntcb_context_create: out of host memory.");
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
     return NTCB_OK;
 }
 
@@ -1265,7 +1271,13 @@ void ntcb_context_destroy(NtcbContext* context)
 
 static int WrapTextureSet(NtcbContext* context, ntcb::ITextureSet* impl, NtcbTextureSet** outTextureSet)
 {
-    *outTextureSet = new NtcbTextureSet{impl, context->impl};
+    *outTextureSet = new (std::nothrow) NtcbTextureSet{impl, context->impl};
+    if (!*outTextureSet)
+    {
+        context->impl->DestroyTextureSet(impl);
+        ntcb::SetError("out of host memory.");
+        return NTCB_ERR_OUT_OF_MEMORY;
+    }
     return NTCB_OK;
 }
 
@@ -1280,7 +1292,7 @@ int ntcb_texture_set_create_from_memory(NtcbContext* context, const void* data, 
     *outTextureSet = nullptr;
     NtcbTextureSetFeatures defaults{NTCB_LAYOUT_INTERLEAVED, 0};
     ntcb::ITextureSet* impl = nullptr;
-    int status = context->impl->CreateCompressedTextureSetFromMemory(data, size, features ? *features : defaults, &impl);
+    int status = ntcb::Guarded(__func__, [&]() { return context->impl->CreateCompressedTextureSetFromMemory(data, size, features ? *features : defaults, &impl); });
     if (status != NTCB_OK)
         return status;
     return WrapTextureSet(context, impl, outTextureSet);
@@ -1293,7 +1305,7 @@ int ntcb_texture_set_load_from_memory(NtcbTextureSet* textureSet, const void* da
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->LoadFromMemory(data, size);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->LoadFromMemory(data, size); });
 }
 
 int ntcb_texture_set_create_from_file(NtcbContext* context, const char* fileName, const NtcbTextureSetFeatures* features,
@@ -1307,7 +1319,7 @@ int ntcb_texture_set_create_from_file(NtcbContext* context, const char* fileName
     *outTextureSet = nullptr;
     NtcbTextureSetFeatures defaults{NTCB_LAYOUT_INTERLEAVED, 0};
     ntcb::ITextureSet* impl = nullptr;
-    int status = context->impl->CreateCompressedTextureSetFromFile(fileName, features ? *features : defaults, &impl);
+    int status = ntcb::Guarded(__func__, [&]() { return context->impl->CreateCompressedTextureSetFromFile(fileName, features ? *features : defaults, &impl); });
     if (status != NTCB_OK)
         return status;
     return WrapTextureSet(context, impl, outTextureSet);
@@ -1339,7 +1351,7 @@ int ntcb_texture_set_decompress(NtcbTextureSet* textureSet, NtcbDecompressionSta
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->Decompress(stats, useInt8Weights != 0);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->Decompress(stats, useInt8Weights != 0); });
 }
 
 int ntcb_texture_set_decompress_rows(NtcbTextureSet* textureSet, const int32_t* rowRanges, NtcbDecompressionStats* stats,
@@ -1350,7 +1362,7 @@ int ntcb_texture_set_decompress_rows(NtcbTextureSet* textureSet, const int32_t* 
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->DecompressRows(rowRanges, stats, useInt8Weights != 0);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->DecompressRows(rowRanges, stats, useInt8Weights != 0); });
 }
 
 int ntcb_texture_set_decompress_converted(NtcbTextureSet* textureSet, NtcbDecompressionStats* stats, int useInt8Weights,
@@ -1361,8 +1373,8 @@ int ntcb_texture_set_decompress_converted(NtcbTextureSet* textureSet, NtcbDecomp
         ntcb::SetError("textureSet and conversion must not be NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->DecompressConverted(stats, useInt8Weights != 0, *conversion, addressSpace, destination,
-        destinationBytes);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->DecompressConverted(stats, useInt8Weights != 0, *conversion, addressSpace, destination,
+        destinationBytes); });
 }
 
 int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadChannelsParams* params)
@@ -1372,7 +1384,7 @@ int ntcb_texture_set_read_channels(NtcbTextureSet* textureSet, const NtcbReadCha
         ntcb::SetError("textureSet and params must not be NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->ReadChannels(*params);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->ReadChannels(*params); });
 }
 
 int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void** outPointer, size_t* outBytes)
@@ -1382,7 +1394,7 @@ int ntcb_texture_set_device_mip(NtcbTextureSet* textureSet, int mipLevel, void**
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->GetDeviceMip(mipLevel, outPointer, outBytes);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->GetDeviceMip(mipLevel, outPointer, outBytes); });
 }
 
 int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, int firstChannel, int numChannels, int format,
@@ -1393,7 +1405,7 @@ int ntcb_texture_set_block_compress(NtcbTextureSet* textureSet, int mipLevel, in
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->BlockCompress(mipLevel, firstChannel, numChannels, format, alphaThreshold, deviceBlocks, rowPitch);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->BlockCompress(mipLevel, firstChannel, numChannels, format, alphaThreshold, deviceBlocks, rowPitch); });
 }
 
 int ntcb_texture_set_get_bc7_mode_buffer(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, const void** outData,
@@ -1404,7 +1416,7 @@ int ntcb_texture_set_get_bc7_mode_buffer(NtcbTextureSet* textureSet, int texture
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->GetBC7ModeBuffer(textureIndex, mipLevel, outData, outSize);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->GetBC7ModeBuffer(textureIndex, mipLevel, outData, outSize); });
 }
 
 int ntcb_texture_set_make_and_store_bc7_mode_buffer(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, int widthInBlocks,
@@ -1415,8 +1427,8 @@ int ntcb_texture_set_make_and_store_bc7_mode_buffer(NtcbTextureSet* textureSet, 
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->MakeAndStoreBC7ModeBuffer(textureIndex, mipLevel, widthInBlocks, heightInBlocks, blockData, blockDataSize,
-        rowPitch);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->MakeAndStoreBC7ModeBuffer(textureIndex, mipLevel, widthInBlocks, heightInBlocks, blockData, blockDataSize,
+        rowPitch); });
 }
 
 int ntcb_texture_set_block_compress_texture(NtcbTextureSet* textureSet, int textureIndex, int mipLevel, float alphaThreshold,
@@ -1427,7 +1439,7 @@ int ntcb_texture_set_block_compress_texture(NtcbTextureSet* textureSet, int text
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->BlockCompressTexture(textureIndex, mipLevel, alphaThreshold, deviceBlocks, rowPitch);
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->BlockCompressTexture(textureIndex, mipLevel, alphaThreshold, deviceBlocks, rowPitch); });
 }
 
 int ntcb_texture_set_get_texture(NtcbTextureSet* textureSet, int index, NtcbTextureDesc* outTexture, int* outCount)
@@ -1450,7 +1462,7 @@ int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet)
         ntcb::SetError("textureSet is NULL.");
         return NTCB_ERR_INVALID_ARGUMENT;
     }
-    return textureSet->impl->Synchronize();
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->Synchronize(); });
 }
 
 } // extern "C"
