@@ -61,6 +61,11 @@ constexpr int kBiasRegionBytes = 128 * 32; // constant A operand of the extra K 
 // their e4m3 bytes: one N_l x 32 byte matrix per 16-wide K step, the step's 16 weights at their place
 // inside the 32-wide chunk and zeros in the other half (same offsets and sizes as the binary16
 // matrices they replace).
+// The image of an INT8 network is shorter: after the four weight matrices it has ONE 64 x 8 matrix of
+// halves, 16 bytes per row n, whose column l is the bias of output n of layer l (kRefInt8BiasOffset).
+// The bias step of layer l multiplies it by rows that are the unit vector e_l, which picks column l;
+// the descriptor's leading offset of 0 makes the step's second 8-wide half read the same matrix, which
+// the zeros in the second half of the e_l rows cancel.
 constexpr int kRefWeightOffset0 = 0;       // 64 x 48 halves
 constexpr int kRefWeightOffset1 = 6144;    // 48 x 64
 constexpr int kRefWeightOffset2 = 12288;   // 32 x 48
@@ -69,8 +74,13 @@ constexpr int kRefBiasOffset0 = 16384;     // 64 x 16 halves
 constexpr int kRefBiasOffset1 = 18432;     // 48 x 16
 constexpr int kRefBiasOffset2 = 19968;     // 32 x 16
 constexpr int kRefBiasOffset3 = 20992;     // 16 x 16
-constexpr int kRefNetworkBytes = 21504;
-constexpr int kRefOperandBytes = 128 * 128; // A operand of one 128-row GEMM chain: 128 rows x 64 halves
+constexpr int kRefNetworkBytes = 21504;     // size of the image, both kinds (an Int8 network's ends early)
+constexpr int kRefInt8BiasOffset = 16384;   // Int8 networks: 64 rows x 8 halves, column l = bias of layer l
+constexpr int kRefInt8NetworkBytes = 17408; // ... what the Int8 kernels copy to shared memory
+// A operand of one 128-row GEMM chain of the Int8 kernels in shared memory: 128 rows x 48 halves.  Layer 0
+// has 48 inputs; of layer 1's 64 the first 32 are here, the other 32 in tensor memory, like all of
+// layers 2 and 3.
+constexpr int kRefOperandBytes = 128 * 96;
 // Tile of the reference-numerics kernel: kRefChains 128-row chains (32 x 4 texels each) per CTA.
 // Two chains (32x8 texels, 256 threads) at three CTAs per SM measured faster than four chains
 // (32x16, 512 threads) at two.
@@ -80,12 +90,17 @@ constexpr int kRefThreadsPerCta = 128 * kRefChains;
 constexpr int kRefTmemColumns = kRefChains * kTmemColumnsPerHalf;
 constexpr int kRefFootprintHiBytes = 8192;  // the binary16 operands leave less room for the high-res footprint
 constexpr int kRefFootprintLoBytes = 4096;
+// The Int8 kernels, whose binary16 operands take more room, have less for the low-res footprint: enough for
+// what fits into the high-res one (the low-res grid has half the resolution: at a grid-to-mip ratio of 1/2
+// a tile's footprint is 18 x 6 pixels of 24 bytes).
+constexpr int kRefInt8FootprintLoBytes = 2816;
 // The warp that issues the matrix products of both chains of a tile after a CTA-wide barrier, chain 0 first:
 // the first warp of chain 1.  It then waits for chain 1, whose products finish last anyway; a warp of chain 0
 // would start on its own chain's results late by the time it takes to issue chain 1's (2 %).  (After a
 // chain-local barrier each chain's first warp issues its own.)
 constexpr int kIssuingWarp = 4;
-constexpr int kCtasPerSmRef = 3;
+constexpr int kCtasPerSmRef = 4;       // Int8 networks: 56 KB of shared memory and 64 registers, like the FP8 kernels
+constexpr int kCtasPerSmRefSample = 3; // inference on sample, Int8 networks: registers to keep the scattered taps in flight
 constexpr int kCtasPerSmRefFp8 = 4; // FP8 networks: 8-bit operands halve the A buffers
 
 constexpr uint32_t kStatusBarrierTimeout = 1;

@@ -182,16 +182,20 @@ struct __align__(16) RefTileTables
 
 struct __align__(128) RefSharedStorage
 {
-    uint8_t network[kRefNetworkBytes];                     // binary16 weights and bias-step operands
-    alignas(128) uint8_t operandA[kRefChains * kRefOperandBytes]; // A operands of the current layer, one per chain
-    alignas(128) uint8_t biasRegion[128 * 32];             // constant A operand of the bias step: rows (1, 0 x 15)
-    uint8_t footprintHi[kRefFootprintHiBytes];
-    uint8_t footprintLo[kRefFootprintLoBytes];
+    uint8_t network[kRefInt8NetworkBytes];                 // binary16 weights and the matrix of biases
+    alignas(128) uint8_t operandA[kRefChains * kRefOperandBytes]; // A operands of layers 0 and 1 (its first half), one per chain
+    // Constant A operands of the bias steps: four core matrices (8 rows x 8 halves) whose rows are the unit
+    // vectors e_0 .. e_3, and one of zeros (the second 8-wide half of every step).  A stride offset of 0 in
+    // the descriptor makes all sixteen 8-row groups of the 128-row operand read the same core matrix.
+    alignas(128) uint8_t onesRegion[5 * 128];
     uint32_t latentTable[256];
-    RefTileTables tables;
     uint64_t barrier[kRefChains]; // MMA completion, per chain: a chain's threads go on as soon as their accumulators are ready
     uint64_t loadBarrier;  // arrival of the network image
     uint32_t tmemBase;
+    // (what inference on sample does not use comes last: its launches leave it out)
+    RefTileTables tables;
+    uint8_t footprintHi[kRefFootprintHiBytes];
+    uint8_t footprintLo[kRefInt8FootprintLoBytes];
 };
 
 struct RefTileContext
@@ -380,15 +384,19 @@ __device__ __forceinline__ void BuildInputsRef(const KernelParams& params, const
 // Layers
 // ---------------------------------------------------------------------------------------------
 
-// Int8 networks (binary16 operands, 128-byte rows): the inputs of layers 2 and 3 - 48 and 32 halves, 24 and 16
-// tensor-memory columns - fit beside those layers' 32 and 16 accumulator columns in a chain's 64, from column 32
-// on; layer 1's 64 halves do not fit beside its 48 accumulators and stay in shared memory, like layer 0's.
+// Int8 networks (binary16 operands): where a layer's inputs live.  A chain has 64 tensor-memory columns; a column
+// holds one accumulator or two operand halves, so K step s (16 halves) of an operand in tensor memory is
+// columns 32 + 8 s .. 32 + 8 s + 7.  Layers 2 and 3 (48 and 32 inputs beside 32 and 16 accumulators) have all
+// their K steps there; layer 1 (64 inputs beside 48 accumulators) its last two, columns 48..63, and the first
+// two in shared memory; layer 0's 48 inputs are all in shared memory (its 64 accumulators fill the chain).
 constexpr uint32_t kRefOperandColumn = 32;
 template <int kLayer>
-constexpr bool kRefOperandInTmem = kLayer >= 2;
+constexpr int kRefFirstTmemStep = kLayer == 0 ? 99 : kLayer == 1 ? 2 : 0;
+template <int kLayer>
+constexpr bool kRefOperandInTmem = kRefFirstTmemStep<kLayer> == 0;      // nothing of it in shared memory
+template <int kLayer>
+constexpr bool kRefOperandInShared = kRefFirstTmemStep<kLayer> != 0;    // some of it in shared memory
 
-// D[tmem] (+)= A[tmem] * B[smem]^T with binary16 operands: the A operand in tensor memory (lane = row, two K
-// values per column).
 __device__ __forceinline__ void UmmaF16FromTmem(uint32_t tmemD, uint32_t tmemA, uint64_t descB, uint32_t instr, uint32_t accumulate,
     uint32_t enabled)
 {
@@ -413,15 +421,13 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
     constexpr int kK = kLayer == 0 ? 48 : kLayer == 1 ? 64 : kLayer == 2 ? 48 : 32;
     constexpr int kWeightOffset =
         kLayer == 0 ? kRefWeightOffset0 : kLayer == 1 ? kRefWeightOffset1 : kLayer == 2 ? kRefWeightOffset2 : kRefWeightOffset3;
-    constexpr int kBiasOffset =
-        kLayer == 0 ? kRefBiasOffset0 : kLayer == 1 ? kRefBiasOffset1 : kLayer == 2 ? kRefBiasOffset2 : kRefBiasOffset3;
 
     // Makes the A operand written before this call visible to the tensor core, orders every
     // thread's TMEM reads of the previous layer before the accumulators are overwritten, and agrees
     // on whether any thread gave up waiting.
-    if (kRefOperandInTmem<kLayer>)
-        TmemStoreWait(); // the operand went to tensor memory: nothing the async proxy reads was written
-    else
+    if (kRefFirstTmemStep<kLayer> < kK / 16)
+        TmemStoreWait(); // (part of) the operand went to tensor memory
+    if (kRefOperandInShared<kLayer>)
         FenceProxyAsyncShared();
     TcgenFenceBeforeSync();
     if (LayerBarrier<kChainLocal>(ctx.tid, failed))
@@ -440,9 +446,11 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
         // the four base descriptors are built once, every operand is then a constant offset (in 16-byte
         // units) added to the address field
         const uint64_t operandBase = MakeSmemDescriptor(__shfl_sync(0xFFFFFFFFu, ctx.operandA, 0), 2048, 128);
-        const uint64_t onesBase = MakeSmemDescriptor(__shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0), 2048, 128);
+        // rows e_kLayer (every 8-row group reads the same core matrix: stride 0), then the core matrix of zeros
+        const uint64_t onesBase = MakeSmemDescriptor(__shfl_sync(0xFFFFFFFFu, ctx.biasRegion, 0) + kLayer * 128, (4 - kLayer) * 128, 0);
         const uint64_t weightBase = MakeSmemDescriptor(networkBase + kWeightOffset, kN * 16, 128);
-        const uint64_t biasBase = MakeSmemDescriptor(networkBase + kBiasOffset, kN * 16, 128);
+        // the matrix of biases, read twice (leading offset 0): its second copy meets the zeros
+        const uint64_t biasBase = MakeSmemDescriptor(networkBase + kRefInt8BiasOffset, 0, 128);
         const uint32_t elected = ElectOne();
         const int ownChain = __shfl_sync(0xFFFFFFFFu, warpIndex >> 2, 0);
 #pragma unroll
@@ -451,7 +459,7 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
             if (kChainLocal && half != ownChain)
                 continue;
             const uint32_t accumulators = tmemBase + half * kTmemColumnsPerHalf;
-            // accumulators := bias (rows (1, 0, ...) times the bias column: exact)
+            // accumulators := bias (rows e_l times the matrix whose column l is the layer's bias: exact)
             UmmaF16(accumulators, onesBase, biasBase, instr, 0, elected);
 #pragma unroll
             for (int kStep = 0; kStep < kK / 16; ++kStep)
@@ -459,7 +467,7 @@ __device__ __forceinline__ int IssueLayerRef(const RefTileContext& ctx, int fail
                 // one K step = two 16-byte core matrices; A: 2048 bytes apart, B: kN*16 bytes apart
                 const uint64_t descA = operandBase + uint64_t((half * kRefOperandBytes + kStep * 2 * 2048) >> 4);
                 const uint64_t descB = weightBase + uint64_t((kStep * 2 * kN * 16) >> 4);
-                if (kRefOperandInTmem<kLayer>)
+                if (kStep >= kRefFirstTmemStep<kLayer>)
                     UmmaF16FromTmem(accumulators, accumulators + kRefOperandColumn + uint32_t(kStep) * 8u, descB, instr, 1, elected);
                 else
                     UmmaF16(accumulators, descA, descB, instr, 1, elected);
@@ -503,9 +511,10 @@ __device__ __forceinline__ void ConsumeLayerRef(const Params& params, const RefT
             TmemLoadPacked8(ctx.tmemLane + 32, tail);
         }
         TmemLoadWait();
-        // chunk c (8 halves) of the next layer's operand row: to shared memory, or to tensor-memory columns 32 + 4 c ..
+        // chunk c (8 halves, half a K step) of the next layer's operand row: to shared memory, or to tensor-memory
+        // columns 32 + 4 c ..
         auto storeChunk = [&](int c, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
-            if (kRefOperandInTmem<kLayer + 1>)
+            if (c >= 2 * kRefFirstTmemStep<kLayer + 1>)
                 TmemStore4(ctx.tmemLane + kRefOperandColumn + 4u * uint32_t(c), w0, w1, w2, w3);
             else
                 rowChunk[c * 128] = make_uint4(w0, w1, w2, w3);
@@ -562,9 +571,14 @@ __device__ __forceinline__ int SetupCtaRef(RefSharedStorage& shared, const uint8
         __half hi = __float2half_rn(__fmul_rn(float(i >> 4), 1.f / 15.f));
         shared.latentTable[i] = AsU32(__halves2half2(lo, hi));
     }
-    // constant A operand of the bias step: every row is (1, 0 x 15); chunk 0 of row r at r * 16
-    for (int i = tid; i < 128 * 32 / 16; i += kRefThreadsPerCta)
-        reinterpret_cast<uint4*>(shared.biasRegion)[i] = make_uint4(i < 128 ? 0x00003C00u : 0u, 0u, 0u, 0u);
+    // constant A operands of the bias steps: core matrix l (8 rows of 16 bytes) has 1.0 as half l of every row,
+    // core matrix 4 is zero
+    for (int i = tid; i < 5 * 8; i += kRefThreadsPerCta)
+    {
+        const int unit = i >> 3;
+        reinterpret_cast<uint4*>(shared.onesRegion)[i] =
+            make_uint4(unit == 0 ? 0x00003C00u : unit == 1 ? 0x3C000000u : 0u, unit == 2 ? 0x00003C00u : unit == 3 ? 0x3C000000u : 0u, 0u, 0u);
+    }
     const uint32_t loadBarrier = SharedAddress(&shared.loadBarrier);
     if (tid == 0)
     {
@@ -572,8 +586,8 @@ __device__ __forceinline__ int SetupCtaRef(RefSharedStorage& shared, const uint8
             MbarrierInit(SharedAddress(&shared.barrier[chain]), 1);
         MbarrierInit(loadBarrier, 1);
         FenceBarrierInit();
-        MbarrierArriveExpectTx(loadBarrier, kRefNetworkBytes);
-        BulkCopyToShared(SharedAddress(shared.network), network, kRefNetworkBytes, loadBarrier);
+        MbarrierArriveExpectTx(loadBarrier, kRefInt8NetworkBytes);
+        BulkCopyToShared(SharedAddress(shared.network), network, kRefInt8NetworkBytes, loadBarrier);
     }
     if (warp == 0)
         TmemAlloc(SharedAddress(&shared.tmemBase), kRefTmemColumns);
@@ -638,7 +652,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kRefOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
-    ctx.biasRegion = SharedAddress(shared.biasRegion);
+    ctx.biasRegion = SharedAddress(shared.onesRegion);
 
     struct TilePlace
     {
@@ -731,7 +745,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) DecodeKernel
 // (mip = clamp(floor(lod)), x = min(floor(u * W), W - 1), y likewise) is evaluated exactly as the
 // decode kernel evaluates it; the taps are read straight from global memory.
 template <bool kFp8>
-__global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernelRef(const __grid_constant__ SampleParams params)
+__global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRefSample) SampleKernelRef(const __grid_constant__ SampleParams params)
 {
     extern __shared__ __align__(128) unsigned char dynamicShared[];
     RefSharedStorage& shared = *reinterpret_cast<RefSharedStorage*>(dynamicShared);
@@ -757,7 +771,7 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRef) SampleKernel
     ctx.operandA = SharedAddress(shared.operandA);
     ctx.rowChunk = reinterpret_cast<uint4*>(shared.operandA + half * kRefOperandBytes) + (tid & 127);
     ctx.networkBase = SharedAddress(shared.network);
-    ctx.biasRegion = SharedAddress(shared.biasRegion);
+    ctx.biasRegion = SharedAddress(shared.onesRegion);
     ctx.outStepWords = 1;
     ctx.storeBytes = 4;
 

@@ -172,10 +172,10 @@ namespace
 {
 
 // Number of CTAs that fill the current device, cached per device.
-int ResidentCtas(bool fp8, bool converting, int* outCtas, bool reference = false)
+int ResidentCtas(bool fp8, bool converting, int* outCtas, bool reference = false, bool sample = false)
 {
-    static std::atomic<int> cache[64][5];
-    const int variant = reference ? (fp8 ? 4 : 3) : converting ? 2 : fp8 ? 1 : 0;
+    static std::atomic<int> cache[64][6];
+    const int variant = reference ? (fp8 ? 4 : sample ? 5 : 3) : converting ? 2 : fp8 ? 1 : 0;
     int device = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err != cudaSuccess)
@@ -207,9 +207,10 @@ int ResidentCtas(bool fp8, bool converting, int* outCtas, bool reference = false
     // used here.)
     static_assert(kCtasPerSmInt8 * kTmemColumns <= 512 && kCtasPerSmFp8 * kTmemColumns <= 512 &&
                       kCtasPerSmConverting * kTmemColumns <= 512 && kCtasPerSmRef * kRefTmemColumns <= 512 &&
+                      kCtasPerSmRefSample * kRefTmemColumns <= 512 &&
                       kCtasPerSmRefFp8 * kTmemColumns <= 512,
         "resident CTAs must fit into tensor memory");
-    const int perSm = reference ? (fp8 ? kCtasPerSmRefFp8 : kCtasPerSmRef) : converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
+    const int perSm = reference ? (fp8 ? kCtasPerSmRefFp8 : sample ? kCtasPerSmRefSample : kCtasPerSmRef) : converting ? kCtasPerSmConverting : fp8 ? kCtasPerSmFp8 : kCtasPerSmInt8;
     *outCtas = sms * perSm;
     if (device >= 0 && device < 64)
         cache[device][variant].store(*outCtas, std::memory_order_relaxed);
@@ -461,7 +462,10 @@ int ntcb_stage_network_reference(const void* blob, size_t blobBytes, int weightM
     {
         const int nin = kLayerInputs[layer], nout = kLayerOutputs[layer];
         uint16_t* weights = reinterpret_cast<uint16_t*>(dst + kRefWeightOffsets[layer]);
-        uint16_t* biasStep = reinterpret_cast<uint16_t*>(dst + kRefBiasOffsets[layer]);
+        // FP8 networks: column 0 of the layer's N x 16 bias-step operand; Int8 networks: column `layer` of the
+        // one 64 x 8 matrix all layers share
+        uint16_t* biasStep = fp8 ? reinterpret_cast<uint16_t*>(dst + kRefBiasOffsets[layer])
+                                 : reinterpret_cast<uint16_t*>(dst + kRefInt8BiasOffset) + layer;
         const bool layerFp8 = fp8 && layer < 3;
         for (int n = 0; n < nout; ++n)
         {
@@ -502,7 +506,7 @@ int ntcb_stage_network_reference(const void* blob, size_t blobBytes, int weightM
                     layerBias = fmaf(float(integerWeightSum * activationBias) * layerScale, activationStep, layerBias);
                 bias = halfBits(layerBias);
             }
-            biasStep[n * 8] = bias; // column 0 of the N x 16 bias-step operand
+            biasStep[n * 8] = bias;
         }
     }
     ClearError();
@@ -621,7 +625,8 @@ int ntcb_decode(const NtcbDecodeParams* p, void* stream)
         KernelMip& km = k.mips[used++];
         const int tileHeight = reference ? kRefTileHeight : kTileHeight;
         if (reference)
-            FillKernelMip(m, p->numFeatures / 4, km, kRefFootprintHiBytes, kRefFootprintLoBytes, kRefTileHeight);
+            FillKernelMip(m, p->numFeatures / 4, km, kRefFootprintHiBytes,
+                p->weightMode == NTCB_WEIGHTS_FP8 ? kRefFootprintLoBytes : kRefInt8FootprintLoBytes, kRefTileHeight);
         else
             FillKernelMip(m, p->numFeatures / 4, km);
         km.firstTile = int(tiles);
@@ -720,7 +725,7 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
         return NTCB_OK;
     const bool fp8 = p->weightMode == NTCB_WEIGHTS_FP8;
     int resident = 0;
-    int rc = ResidentCtas(fp8, false, &resident, reference);
+    int rc = ResidentCtas(fp8, false, &resident, reference, true);
     if (rc != NTCB_OK)
         return rc;
     const unsigned long long perCta = reference ? kRefThreadsPerCta : kThreadsPerCta;

@@ -233,7 +233,8 @@ def test_reference_network_staging():
     """The image of the reference-numerics kernels: binary16 weights rebuilt as the reference's
     ConvertNetworkFromQuantizedToFp16 does, in K-major core matrices of 8 halves (element (n, k) of
     layer l at byte (k / 8) * (N * 16) + n * 16 + (k % 8) * 2), and per layer an N x 16 bias-step operand
-    with the binary16 bias in column 0.  The e4m3 layers of an FP8 network keep their bytes: one
+    with the binary16 bias in column 0 (FP8 networks) or one 64 x 8 matrix whose column l is the bias of
+    layer l (Int8 networks).  The e4m3 layers of an FP8 network keep their bytes: one
     N x 32 byte matrix per 16-wide K step with the step's weights at their place inside the 32-wide
     chunk and zeros in the other half."""
     data = synthetic.make_texture_set(synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=3))
@@ -280,9 +281,15 @@ def test_reference_network_staging():
                     layer_bias = (product.astype(np.float64) * np.float64(step) + layer_bias.astype(np.float64)).astype(np.float32)  # one rounding: fma
                 bias = layer_bias.astype(np.float16)
             assert matrix is None or np.array_equal(matrix, expected), (mode, layer)
-            step_operand = halves[bias_offsets[layer] // 2:bias_offsets[layer] // 2 + nout * 16].reshape(2, nout, 8)
-            assert np.array_equal(step_operand[0, :, 0].view(np.uint16), bias.view(np.uint16)), (mode, layer)
-            assert not step_operand[0, :, 1:].any() and not step_operand[1].any()
+            if mode == binding.WEIGHTS_INT8:
+                bias_matrix = halves[16384 // 2:17408 // 2].reshape(64, 8)
+                assert np.array_equal(bias_matrix[:nout, layer].view(np.uint16), bias.view(np.uint16)), (mode, layer)
+                assert not bias_matrix[nout:, layer].any() and not bias_matrix[:, 4:].any()
+                assert not staged[17408:].any()
+            else:
+                step_operand = halves[bias_offsets[layer] // 2:bias_offsets[layer] // 2 + nout * 16].reshape(2, nout, 8)
+                assert np.array_equal(step_operand[0, :, 0].view(np.uint16), bias.view(np.uint16)), (mode, layer)
+                assert not step_operand[0, :, 1:].any() and not step_operand[1].any()
 
 
 def test_stage_network_rejects_wrong_sizes():
