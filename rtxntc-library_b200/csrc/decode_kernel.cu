@@ -34,6 +34,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <cstddef>
 
 #include "decode_kernel.h"
 #include "kernel_parts.cuh"
@@ -165,13 +166,16 @@ struct __align__(128) SharedStorage
     // the tensor core reads operands as 128-byte core matrices: keep them on 128-byte lines
     alignas(128) uint8_t operandA[2 * kOperandBytes];  // A operands of the current layer (top half, bottom half), core-matrix order
     alignas(128) uint8_t biasRegion[kBiasRegionBytes]; // constant A operand of the bias K step of the int8 layers
-    uint8_t footprintHi[kFootprintHiBytes]; // unpacked latents of the tile's footprint in the high-res grid
-    uint8_t footprintLo[kFootprintLoBytes]; // ... and in the low-res grid
     uint32_t latentTable[256];            // byte (two nibbles) -> two binary16 latent values
-    TileTables tables;
     uint64_t barrier;                     // MMA completion
     uint64_t loadBarrier;                 // arrival of the network image (bulk copy)
     uint32_t tmemBase;
+    // What inference on sample does not use comes last: its launches ask for the bytes before `tables` only.
+    // (With the whole structure, a sample kernel's own static shared memory - its table of mips - puts four CTAs
+    // above an SM's 228 KB: three were resident and the fourth quarter of the grid ran alone afterwards.)
+    alignas(128) TileTables tables;
+    uint8_t footprintHi[kFootprintHiBytes]; // unpacked latents of the tile's footprint in the high-res grid
+    uint8_t footprintLo[kFootprintLoBytes]; // ... and in the low-res grid
 };
 
 
@@ -629,12 +633,24 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
     ctx.outStepWords = 1;
 
     const unsigned long long tiles = (params.numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
+    // a tile's queries are requested one tile ahead: their latency passes under the previous tile's layers
+    float nextU = 0.f, nextV = 0.f, nextLod = 0.f;
+    auto requestQuery = [&](unsigned long long ofTile) {
+        if (ofTile < tiles)
+        {
+            const unsigned long long q = min(ofTile * kThreadsPerCta + tid, params.numQueries - 1);
+            nextU = __ldg(params.queries + 3 * q);
+            nextV = __ldg(params.queries + 3 * q + 1);
+            nextLod = __ldg(params.queries + 3 * q + 2);
+        }
+    };
+    requestQuery(blockIdx.x);
     for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x)
     {
         const unsigned long long query = tile * kThreadsPerCta + tid;
         const bool valid = query < params.numQueries;
-        const unsigned long long q = valid ? query : params.numQueries - 1;
-        const float u = __ldg(params.queries + 3 * q), v = __ldg(params.queries + 3 * q + 1), lod = __ldg(params.queries + 3 * q + 2);
+        const float u = nextU, v = nextV, lod = nextLod;
+        requestQuery(tile + gridDim.x);
         const int mipIndex = max(0, min(params.numMips - 1, int(floorf(lod))));
         const KernelMip& mip = mipTable[mipIndex];
         const int x = max(0, min(mip.width - 1, int(floorf(__fmul_rn(u, float(mip.width))))));
@@ -716,12 +732,12 @@ cudaError_t AllowSharedStorage(Kernel kernel, std::atomic<unsigned long long>& d
 
 template <typename Kernel, typename Params>
 cudaError_t LaunchWithSharedStorage(Kernel kernel, std::atomic<unsigned long long>& doneMask, const Params& params, int ctas,
-    cudaStream_t stream)
+    cudaStream_t stream, size_t bytes = sizeof(SharedStorage))
 {
     cudaError_t err = AllowSharedStorage(kernel, doneMask);
     if (err != cudaSuccess)
         return err;
-    kernel<<<ctas, kThreadsPerCta, sizeof(SharedStorage), stream>>>(params);
+    kernel<<<ctas, kThreadsPerCta, bytes, stream>>>(params);
     return cudaGetLastError();
 }
 
@@ -730,8 +746,9 @@ cudaError_t LaunchWithSharedStorage(Kernel kernel, std::atomic<unsigned long lon
 cudaError_t LaunchSample(const SampleParams& params, bool fp8, int ctas, cudaStream_t stream)
 {
     static std::atomic<unsigned long long> done[2];
-    return fp8 ? LaunchWithSharedStorage(SampleKernel<true>, done[1], params, ctas, stream)
-               : LaunchWithSharedStorage(SampleKernel<false>, done[0], params, ctas, stream);
+    const size_t bytes = offsetof(SharedStorage, tables); // the tables and footprints are not used
+    return fp8 ? LaunchWithSharedStorage(SampleKernel<true>, done[1], params, ctas, stream, bytes)
+               : LaunchWithSharedStorage(SampleKernel<false>, done[0], params, ctas, stream, bytes);
 }
 
 cudaError_t LaunchDecode(const KernelParams& params, bool fp8, int ctas, cudaStream_t stream)

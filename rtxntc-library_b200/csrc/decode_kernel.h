@@ -100,8 +100,8 @@ constexpr int kRefInt8FootprintLoBytes = 2816;
 // chain-local barrier each chain's first warp issues its own.)
 constexpr int kIssuingWarp = 4;
 constexpr int kCtasPerSmRef = 4;       // Int8 networks: 56 KB of shared memory and 64 registers, like the FP8 kernels
-constexpr int kCtasPerSmRefSample = 3; // inference on sample, Int8 networks: registers to keep the scattered taps in flight
 constexpr int kCtasPerSmRefFp8 = 4; // FP8 networks: 8-bit operands halve the A buffers
+constexpr int kCtasPerSmRefSample = 4; // inference on sample, Int8 networks (its launches leave the footprints out)
 
 constexpr uint32_t kStatusBarrierTimeout = 1;
 

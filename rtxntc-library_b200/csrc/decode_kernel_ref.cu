@@ -38,6 +38,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <cstddef>
 
 #include "decode_kernel.h"
 #include "kernel_parts.cuh"
@@ -192,8 +193,8 @@ struct __align__(128) RefSharedStorage
     uint64_t barrier[kRefChains]; // MMA completion, per chain: a chain's threads go on as soon as their accumulators are ready
     uint64_t loadBarrier;  // arrival of the network image
     uint32_t tmemBase;
-    // (what inference on sample does not use comes last: its launches leave it out)
-    RefTileTables tables;
+    // what inference on sample does not use comes last: its launches ask for the bytes before `tables` only
+    alignas(128) RefTileTables tables;
     uint8_t footprintHi[kRefFootprintHiBytes];
     uint8_t footprintLo[kRefInt8FootprintLoBytes];
 };
@@ -777,12 +778,24 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRefSample) Sample
 
     const uint32_t zeroPair = AsU32(QuantizeInputRef<kFp8>(__float2half2_rn(0.f)));
     const unsigned long long tiles = (params.numQueries + kRefThreadsPerCta - 1) / kRefThreadsPerCta;
+    // a tile's queries are requested one tile ahead: their latency passes under the previous tile's layers
+    float nextU = 0.f, nextV = 0.f, nextLod = 0.f;
+    auto requestQuery = [&](unsigned long long ofTile) {
+        if (ofTile < tiles)
+        {
+            const unsigned long long q = min(ofTile * kRefThreadsPerCta + tid, params.numQueries - 1);
+            nextU = __ldg(params.queries + 3 * q);
+            nextV = __ldg(params.queries + 3 * q + 1);
+            nextLod = __ldg(params.queries + 3 * q + 2);
+        }
+    };
+    requestQuery(blockIdx.x);
     for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x)
     {
         const unsigned long long query = tile * kRefThreadsPerCta + tid;
         const bool valid = query < params.numQueries;
-        const unsigned long long q = valid ? query : params.numQueries - 1;
-        const float u = __ldg(params.queries + 3 * q), v = __ldg(params.queries + 3 * q + 1), lod = __ldg(params.queries + 3 * q + 2);
+        const float u = nextU, v = nextV, lod = nextLod;
+        requestQuery(tile + gridDim.x);
         const int mipIndex = max(0, min(params.numMips - 1, int(floorf(lod))));
         const KernelMip& mip = mipTable[mipIndex];
         const int x = max(0, min(mip.width - 1, int(floorf(__fmul_rn(u, float(mip.width))))));
@@ -866,13 +879,15 @@ struct __align__(128) RefFp8SharedStorage
     uint8_t network[kRefNetworkBytes];                  // layers 0-2: split e4m3 weight copies; layer 3 and bias steps: binary16
     alignas(128) uint8_t operandA[2 * kOperandBytes];   // A operands (top half, bottom half): 128 rows x 64 bytes each
     alignas(128) uint8_t biasRegion[128 * 32];          // constant binary16 A operand of the bias step: rows (1, 0 x 15)
-    uint8_t footprintHi[kRefFootprintHiBytes];
-    uint8_t footprintLo[kRefFootprintLoBytes];
     uint32_t latentTable[256];
-    TileTables tables;
     uint64_t barrier[kRefChains]; // MMA completion, per chain
     uint64_t loadBarrier;         // arrival of the network image
     uint32_t tmemBase;
+    // what inference on sample does not use comes last: its launches ask for the bytes before `tables` only
+    // (with the whole structure a sample kernel's static table of mips would cost it the fourth CTA per SM)
+    alignas(128) TileTables tables;
+    uint8_t footprintHi[kRefFootprintHiBytes];
+    uint8_t footprintLo[kRefFootprintLoBytes];
 };
 
 // D[tmem] (+)= A[smem] * B[smem]^T, M = 128, K = 32 e4m3 operands, binary16 accumulators.
@@ -1427,12 +1442,24 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
     ctx.storeBytes = 4;
 
     const unsigned long long tiles = (params.numQueries + kThreadsPerCta - 1) / kThreadsPerCta;
+    // a tile's queries are requested one tile ahead: their latency passes under the previous tile's layers
+    float nextU = 0.f, nextV = 0.f, nextLod = 0.f;
+    auto requestQuery = [&](unsigned long long ofTile) {
+        if (ofTile < tiles)
+        {
+            const unsigned long long q = min(ofTile * kThreadsPerCta + tid, params.numQueries - 1);
+            nextU = __ldg(params.queries + 3 * q);
+            nextV = __ldg(params.queries + 3 * q + 1);
+            nextLod = __ldg(params.queries + 3 * q + 2);
+        }
+    };
+    requestQuery(blockIdx.x);
     for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x)
     {
         const unsigned long long query = tile * kThreadsPerCta + tid;
         const bool valid = query < params.numQueries;
-        const unsigned long long q = valid ? query : params.numQueries - 1;
-        const float u = __ldg(params.queries + 3 * q), v = __ldg(params.queries + 3 * q + 1), lod = __ldg(params.queries + 3 * q + 2);
+        const float u = nextU, v = nextV, lod = nextLod;
+        requestQuery(tile + gridDim.x);
         const int mipIndex = max(0, min(params.numMips - 1, int(floorf(lod))));
         const KernelMip& mip = mipTable[mipIndex];
         const int x = max(0, min(mip.width - 1, int(floorf(__fmul_rn(u, float(mip.width))))));
@@ -1566,12 +1593,12 @@ cudaError_t LaunchSampleRef(const SampleParams& params, bool fp8, int ctas, cuda
         const unsigned long long bit = 1ull << (device & 63);
         if (!(doneMask.load(std::memory_order_acquire) & bit))
         {
-            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefSharedStorage)));
+            err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(offsetof(RefSharedStorage, tables)));
             if (err != cudaSuccess)
                 return err;
             doneMask.fetch_or(bit, std::memory_order_release);
         }
-        kernel<<<ctas, kRefThreadsPerCta, sizeof(RefSharedStorage), stream>>>(params);
+        kernel<<<ctas, kRefThreadsPerCta, offsetof(RefSharedStorage, tables), stream>>>(params);
         return cudaGetLastError();
     };
     if (fp8)
@@ -1583,12 +1610,12 @@ cudaError_t LaunchSampleRef(const SampleParams& params, bool fp8, int ctas, cuda
         const unsigned long long bit = 1ull << (device & 63);
         if (!(done[1].load(std::memory_order_acquire) & bit))
         {
-            err = cudaFuncSetAttribute(SampleKernelRefFp8, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(RefFp8SharedStorage)));
+            err = cudaFuncSetAttribute(SampleKernelRefFp8, cudaFuncAttributeMaxDynamicSharedMemorySize, int(offsetof(RefFp8SharedStorage, tables)));
             if (err != cudaSuccess)
                 return err;
             done[1].fetch_or(bit, std::memory_order_release);
         }
-        SampleKernelRefFp8<<<ctas, kThreadsPerCta, sizeof(RefFp8SharedStorage), stream>>>(params);
+        SampleKernelRefFp8<<<ctas, kThreadsPerCta, offsetof(RefFp8SharedStorage, tables), stream>>>(params);
         return cudaGetLastError();
     }
     return launch(SampleKernelRef<false>, done[0]);
