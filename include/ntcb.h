@@ -189,6 +189,12 @@ int ntcb_decode(const NtcbDecodeParams* params, void* stream);
    The reference exposes this only to shaders, as NtcSampleTextureSet(texel, mipLevel)
    (include/libntc/shaders/Inference.hlsli:282-357) fed by IContext::MakeInferenceData
    (src/Context.cpp:864-922); the (u, v, lod) -> (texel, mip) rule above is this library's. */
+typedef enum NtcbLatentLayout
+{
+    NTCB_LATENTS_PLANAR = 0,     /* the file's order: per grid, layer after layer (NtcbDecodeParams::latents) */
+    NTCB_LATENTS_INTERLEAVED = 1 /* the pixel-major copy made by ntcb_interleave_latents */
+} NtcbLatentLayout;
+
 typedef struct NtcbSampleParams
 {
     const uint16_t* latents; /* device, as in NtcbDecodeParams */
@@ -202,12 +208,27 @@ typedef struct NtcbSampleParams
     int32_t channels;
     int32_t weightMode;
     int32_t numerics;        /* NtcbNumerics; selects the network image as in NtcbDecodeParams */
-    int32_t reserved;
-    NtcbMipDesc mips[NTCB_MAX_MIPS]; /* outOffset, rowBegin and rowEnd are ignored */
+    int32_t latentLayout;    /* NtcbLatentLayout: what `latents` points to (0: the file's order) */
+    NtcbMipDesc mips[NTCB_MAX_MIPS]; /* outOffset, rowBegin and rowEnd are ignored; the grids are described as
+                                        they lie in the file's order, whatever latentLayout says */
 } NtcbSampleParams;
 
 /* One kernel launch on `stream` for all queries.  Asynchronous; allocates nothing. */
 int ntcb_sample(const NtcbSampleParams* params, void* stream);
+
+/* Re-lays packed latents for inference on sample (NTCB_LATENTS_INTERLEAVED).  In the copy a latent pixel is one
+   slot that holds its layers side by side: 1, 2 or 4 elements for 4, 8 and 12 / 16 features (the fourth element
+   of a 12-feature slot is zero), and the grid that starts at element `offset` of `latents` starts at element
+   offset / layers * slot of `interleaved`.  `interleaved` is a device buffer, 8-byte aligned, of as many elements
+   as `latents` - of 4/3 as many with 12 features.  A bilinear tap of a random query is then ONE aligned load of
+   8 (4) bytes instead of one 2-byte load per layer from planes that lie far apart, which is what bounds that
+   kernel (the L1's rate of serving scattered words).  The answers are the same bits.  The
+   grids are taken from `mips` as ntcb_sample reads them (colour mips that share a grid name it twice; it is
+   converted once); every grid's offset must be a multiple of the layer count.  One launch on `stream`;
+   asynchronous; allocates nothing.  No counterpart in the reference, whose sampling path is a shader reading the
+   file's planes. */
+int ntcb_interleave_latents(const uint16_t* latents, uint16_t* interleaved, const NtcbMipDesc* mips, int numMips,
+    int numFeatures, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Texture-set level: the same path as the reference's host objects drive it.

@@ -23,6 +23,7 @@ MAX_MIPS = 16
 DEFAULT_WAIT_POLLS = 1 << 20  # NTCB_DEFAULT_WAIT_POLLS
 STAGED_NETWORK_BYTES = 14864
 STAGED_REFERENCE_NETWORK_BYTES = 21504
+LATENTS_PLANAR, LATENTS_INTERLEAVED = 0, 1
 NUMERICS_REFERENCE, NUMERICS_EXACT = 0, 1  # NtcbNumerics: the reference's binary16 accumulation (default) / exact accumulation
 STATUS_WORDS = 4
 WEIGHTS_INT8, WEIGHTS_FP8 = 0, 1
@@ -82,7 +83,7 @@ class SampleParams(ctypes.Structure):
     _fields_ = [("latents", ctypes.c_void_p), ("network", ctypes.c_void_p), ("queries", ctypes.c_void_p),
                 ("out", ctypes.c_void_p), ("status", ctypes.c_void_p), ("numQueries", ctypes.c_uint64),
                 ("numMips", ctypes.c_int32), ("numFeatures", ctypes.c_int32), ("channels", ctypes.c_int32),
-                ("weightMode", ctypes.c_int32), ("numerics", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("weightMode", ctypes.c_int32), ("numerics", ctypes.c_int32), ("latentLayout", ctypes.c_int32),
                 ("mips", MipDesc * MAX_MIPS)]
 
 
@@ -175,6 +176,8 @@ def lib():
         handle.ntcb_stage_network_reference.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
         handle.ntcb_sample.argtypes = [ctypes.POINTER(SampleParams), ctypes.c_void_p]
+        handle.ntcb_interleave_latents.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(MipDesc), ctypes.c_int,
+                                                   ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode_resident_ctas.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         handle.ntcb_probe_container.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(TextureSetDesc)]
         handle.ntcb_probe_container_texture.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.POINTER(TextureDesc),
@@ -542,17 +545,40 @@ class ResidentTextureSet:
         with self.torch.cuda.device(self.device):
             self.launch(self.params(use_int8, mips=mips, row_ranges=row_ranges))
 
-    def sample(self, queries, use_int8: bool):
+    def interleave_latents(self):
+        """ntcb_interleave_latents: the pixel-major copy of the latents (a slot of 1, 2 or 4 elements per latent
+        pixel; 12 features are padded to 4) for `sample(..., interleaved=True)`.  Made once and kept; queued on
+        torch's current stream."""
+        if getattr(self, "interleaved_latents", None) is None:
+            torch = self.torch
+            layers = self.geometry.num_features // 4
+            slot = 4 if layers == 3 else layers
+            self.interleaved_latents = torch.zeros(self.latents.numel() // layers * slot, dtype=self.latents.dtype,
+                                                   device=self.device)
+            # (only the mip descriptions of these parameters are used)
+            decode = fill_params(self.geometry, self.latents.data_ptr(), self.networks[WEIGHTS_INT8].data_ptr(),
+                                 self.status.data_ptr(), self.status.data_ptr(), WEIGHTS_INT8)
+            with torch.cuda.device(self.device):
+                stream = torch.cuda.current_stream(self.device).cuda_stream
+                check(lib().ntcb_interleave_latents(ctypes.c_void_p(self.latents.data_ptr()),
+                                                    ctypes.c_void_p(self.interleaved_latents.data_ptr()), decode.mips,
+                                                    decode.numMips, decode.numFeatures, ctypes.c_void_p(stream)))
+        return self.interleaved_latents
+
+    def sample(self, queries, use_int8: bool, interleaved: bool = False):
         """Inference on sample: `queries` is a float32 CUDA tensor [n][3] of (u, v, lod); returns a
-        float16 CUDA tensor [n][channels].  Queued on torch's current stream."""
+        float16 CUDA tensor [n][channels].  Queued on torch's current stream.  `interleaved`: read the
+        latents from the copy `interleave_latents()` makes (same answers, fewer memory requests)."""
         torch = self.torch
         mode = WEIGHTS_INT8 if use_int8 else WEIGHTS_FP8
         queries = queries.contiguous()
         out = torch.empty((queries.shape[0], self.geometry.channels), dtype=torch.float16, device=self.device)
         network = self.networks[mode]
-        decode = fill_params(self.geometry, self.latents.data_ptr(), network.data_ptr(), out.data_ptr(),
+        latents = self.interleave_latents() if interleaved else self.latents
+        decode = fill_params(self.geometry, latents.data_ptr(), network.data_ptr(), out.data_ptr(),
                              self.status.data_ptr(), mode)
         params = SampleParams()
+        params.latentLayout = LATENTS_INTERLEAVED if interleaved else LATENTS_PLANAR
         params.latents, params.network, params.queries = decode.latents, decode.network, queries.data_ptr()
         params.out, params.status, params.numQueries = out.data_ptr(), decode.status, queries.shape[0]
         params.numMips, params.numFeatures, params.channels = decode.numMips, decode.numFeatures, decode.channels

@@ -671,7 +671,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kFp8 ? kCtasPerSmFp8 : kCtasPe
             const uint32_t slotFill = kFp8 ? 0u : kBiasSlotValue * 0x01010101u;
             words[12] = words[13] = words[14] = slotFill;
             words[15] = kFp8 ? 0u : ((slotFill & 0x00FFFFFFu) | 0x01000000u);
-            SampleGridsDirect<kFp8, false>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
+            SampleGridsDirect<kFp8, false>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words, params.interleaved != 0);
             // src/RegressionKernels.h:59-85
             float xf = __fmul_rn(float(x), mip.positionScale);
             float yf = __fmul_rn(float(y), mip.positionScale);

@@ -160,6 +160,10 @@ struct SampleParams
     int numLayers;
     int channels;
     uint32_t loadWaitPolls; // as in KernelParams
+    // Nonzero: `latents` is the pixel-major copy ntcb_interleave_latents makes - the layers of a latent pixel side
+    // by side in a slot of 1, 2 or 4 elements (three layers are padded to four) - and hiOffset / loOffset of the
+    // mips are element offsets into THAT buffer.
+    int interleaved;
     KernelMip mips[16];
 };
 

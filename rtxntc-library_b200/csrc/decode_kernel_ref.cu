@@ -305,13 +305,11 @@ __device__ __forceinline__ void GatherGridRef(const KernelParams& params, const 
     }
 }
 
-// One latent layer of one grid with the taps read straight from global memory.
+// One latent layer of one grid (the low 16 bits of each p are the tap's four features) -> two pairs of inputs.
 template <bool kFp8>
-__device__ __forceinline__ void SampleLayerRef(const uint16_t* __restrict__ plane, const GridTaps& taps,
+__device__ __forceinline__ void BlendPixelsRef(uint32_t p00, uint32_t p01, uint32_t p10, uint32_t p11, const GridTaps& taps,
     const uint32_t* __restrict__ lut, uint32_t* words)
 {
-    const uint32_t p00 = __ldg(plane + taps.o00), p01 = __ldg(plane + taps.o01);
-    const uint32_t p10 = __ldg(plane + taps.o10), p11 = __ldg(plane + taps.o11);
 #pragma unroll
     for (int j = 0; j < 2; ++j)
     {
@@ -324,6 +322,16 @@ __device__ __forceinline__ void SampleLayerRef(const uint16_t* __restrict__ plan
         d = __hfma2(d, __float2half2_rn(2.f), __float2half2_rn(-1.f));
         words[j] = AsU32(QuantizeInputRef<kFp8>(d));
     }
+}
+
+// ... with the taps read straight from the layer's plane in global memory.
+template <bool kFp8>
+__device__ __forceinline__ void SampleLayerRef(const uint16_t* __restrict__ plane, const GridTaps& taps,
+    const uint32_t* __restrict__ lut, uint32_t* words)
+{
+    const uint32_t p00 = __ldg(plane + taps.o00), p01 = __ldg(plane + taps.o01);
+    const uint32_t p10 = __ldg(plane + taps.o10), p11 = __ldg(plane + taps.o11);
+    BlendPixelsRef<kFp8>(p00, p01, p10, p11, taps, lut, words);
 }
 
 // The 48 network inputs of one texel as 24 binary16 pairs -> its 96-byte row of the A operand.
@@ -816,16 +824,28 @@ __global__ void __launch_bounds__(kRefThreadsPerCta, kCtasPerSmRefSample) Sample
             GridTaps taps;
             SetupTaps(su, sv, mip.hiWidth, mip.hiHeight, taps);
             const uint16_t* hi = params.latents + mip.hiOffset;
-#pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
-                if (layer < params.numLayers)
-                    SampleLayerRef<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable, words + 2 * layer);
-            SetupTaps(su, sv, mip.loWidth, mip.loHeight, taps);
             const uint16_t* lo = params.latents + mip.loOffset;
+            if (params.interleaved)
+            {
+                GridTaps lowTaps;
+                SetupTaps(su, sv, mip.loWidth, mip.loHeight, lowTaps);
+                SampleInterleaved(hi, lo, params.numLayers, taps, lowTaps,
+                    [&](int grid, int layer, uint32_t p00, uint32_t p01, uint32_t p10, uint32_t p11) {
+                        BlendPixelsRef<kFp8>(p00, p01, p10, p11, grid ? lowTaps : taps, shared.latentTable, words + 8 * grid + 2 * layer);
+                    });
+            }
+            else
+            {
 #pragma unroll
-            for (int layer = 0; layer < 4; ++layer)
-                if (layer < params.numLayers)
-                    SampleLayerRef<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable, words + 8 + 2 * layer);
+                for (int layer = 0; layer < 4; ++layer)
+                    if (layer < params.numLayers)
+                        SampleLayerRef<kFp8>(hi + size_t(layer) * mip.hiPlane, taps, shared.latentTable, words + 2 * layer);
+                SetupTaps(su, sv, mip.loWidth, mip.loHeight, taps);
+#pragma unroll
+                for (int layer = 0; layer < 4; ++layer)
+                    if (layer < params.numLayers)
+                        SampleLayerRef<kFp8>(lo + size_t(layer) * mip.loPlane, taps, shared.latentTable, words + 8 + 2 * layer);
+            }
             // src/RegressionKernels.h:59-85: per wave the inputs (x phase 0, y phase 0, x phase 0.25, y phase 0.25)
             float xf = __fmul_rn(float(x), mip.positionScale);
             float yf = __fmul_rn(float(y), mip.positionScale);
@@ -1479,7 +1499,7 @@ __global__ void __launch_bounds__(kThreadsPerCta, kCtasPerSmRefFp8) SampleKernel
 #pragma unroll
             for (int i = 12; i < 16; ++i)
                 words[i] = 0;        // K padding
-            SampleGridsDirect<true, true>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words);
+            SampleGridsDirect<true, true>(params.latents, params.numLayers, mip, x, y, shared.latentTable, words, params.interleaved != 0);
             // src/RegressionKernels.h:59-85
             float xf = __fmul_rn(float(x), mip.positionScale);
             float yf = __fmul_rn(float(y), mip.positionScale);

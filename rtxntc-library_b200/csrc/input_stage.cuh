@@ -68,14 +68,12 @@ __device__ __forceinline__ uint32_t PackCodes(uint32_t pair0, uint32_t pair1)
     return __byte_perm(pair0, pair1, 0x6420);
 }
 
-// One latent pixel layer (four 4-bit features) of one grid -> four quantised inputs.
+// One latent pixel layer (four 4-bit features, the low 16 bits of each p) of one grid -> four quantised inputs.
 // Blend order as the reference build evaluates it: fma(l11,w3, fma(l10,w2, fma(l00,w0, l01*w1))).
 template <bool kFp8>
-__device__ __forceinline__ uint32_t SampleLayer(const uint16_t* __restrict__ plane, const GridTaps& taps,
+__device__ __forceinline__ uint32_t BlendLayer(uint32_t p00, uint32_t p01, uint32_t p10, uint32_t p11, const GridTaps& taps,
     const uint32_t* __restrict__ lut)
 {
-    uint32_t p00 = __ldg(plane + taps.o00), p01 = __ldg(plane + taps.o01);
-    uint32_t p10 = __ldg(plane + taps.o10), p11 = __ldg(plane + taps.o11);
     uint32_t pairs[2];
 #pragma unroll
     for (int j = 0; j < 2; ++j)
@@ -90,6 +88,65 @@ __device__ __forceinline__ uint32_t SampleLayer(const uint16_t* __restrict__ pla
         pairs[j] = QuantizeInputPair<kFp8>(d);
     }
     return PackCodes<kFp8>(pairs[0], pairs[1]);
+}
+
+// ... with the taps read from one layer's plane in global memory.
+template <bool kFp8>
+__device__ __forceinline__ uint32_t SampleLayer(const uint16_t* __restrict__ plane, const GridTaps& taps,
+    const uint32_t* __restrict__ lut)
+{
+    uint32_t p00 = __ldg(plane + taps.o00), p01 = __ldg(plane + taps.o01);
+    uint32_t p10 = __ldg(plane + taps.o10), p11 = __ldg(plane + taps.o11);
+    return BlendLayer<kFp8>(p00, p01, p10, p11, taps, lut);
+}
+
+// Both grids of a texel from the pixel-major copy of the latents (ntcb_interleave_latents): latent pixel p of a
+// grid is ONE aligned word at grid + p * slot holding its layers side by side - 8 bytes for three or four layers,
+// 4 for two, 2 for one.  `blend(grid, layer, p00, p01, p10, p11)` receives layer l of the four taps in the low 16
+// bits of its arguments.  Inference on sample, whose taps are scattered, is bound by the rate at which the L1
+// serves scattered words: a tap costs it one request instead of one per layer, and the eight requests of a query
+// are all in flight before the first is needed.
+template <typename Blend>
+__device__ __forceinline__ void SampleInterleaved(const uint16_t* __restrict__ hi, const uint16_t* __restrict__ lo, int numLayers,
+    const GridTaps& hiTaps, const GridTaps& loTaps, Blend&& blend)
+{
+    if (numLayers >= 3)
+    {
+        const uint2* wideHi = reinterpret_cast<const uint2*>(hi);
+        const uint2* wideLo = reinterpret_cast<const uint2*>(lo);
+        const uint2 h00 = __ldg(wideHi + hiTaps.o00), h01 = __ldg(wideHi + hiTaps.o01);
+        const uint2 h10 = __ldg(wideHi + hiTaps.o10), h11 = __ldg(wideHi + hiTaps.o11);
+        const uint2 l00 = __ldg(wideLo + loTaps.o00), l01 = __ldg(wideLo + loTaps.o01);
+        const uint2 l10 = __ldg(wideLo + loTaps.o10), l11 = __ldg(wideLo + loTaps.o11);
+        blend(0, 0, h00.x, h01.x, h10.x, h11.x);
+        blend(0, 1, h00.x >> 16, h01.x >> 16, h10.x >> 16, h11.x >> 16);
+        blend(0, 2, h00.y, h01.y, h10.y, h11.y);
+        if (numLayers == 4)
+            blend(0, 3, h00.y >> 16, h01.y >> 16, h10.y >> 16, h11.y >> 16);
+        blend(1, 0, l00.x, l01.x, l10.x, l11.x);
+        blend(1, 1, l00.x >> 16, l01.x >> 16, l10.x >> 16, l11.x >> 16);
+        blend(1, 2, l00.y, l01.y, l10.y, l11.y);
+        if (numLayers == 4)
+            blend(1, 3, l00.y >> 16, l01.y >> 16, l10.y >> 16, l11.y >> 16);
+    }
+    else if (numLayers == 2)
+    {
+        const uint32_t* wideHi = reinterpret_cast<const uint32_t*>(hi);
+        const uint32_t* wideLo = reinterpret_cast<const uint32_t*>(lo);
+        const uint32_t h00 = __ldg(wideHi + hiTaps.o00), h01 = __ldg(wideHi + hiTaps.o01);
+        const uint32_t h10 = __ldg(wideHi + hiTaps.o10), h11 = __ldg(wideHi + hiTaps.o11);
+        const uint32_t l00 = __ldg(wideLo + loTaps.o00), l01 = __ldg(wideLo + loTaps.o01);
+        const uint32_t l10 = __ldg(wideLo + loTaps.o10), l11 = __ldg(wideLo + loTaps.o11);
+        blend(0, 0, h00, h01, h10, h11);
+        blend(0, 1, h00 >> 16, h01 >> 16, h10 >> 16, h11 >> 16);
+        blend(1, 0, l00, l01, l10, l11);
+        blend(1, 1, l00 >> 16, l01 >> 16, l10 >> 16, l11 >> 16);
+    }
+    else
+    {
+        blend(0, 0, __ldg(hi + hiTaps.o00), __ldg(hi + hiTaps.o01), __ldg(hi + hiTaps.o10), __ldg(hi + hiTaps.o11));
+        blend(1, 0, __ldg(lo + loTaps.o00), __ldg(lo + loTaps.o01), __ldg(lo + loTaps.o10), __ldg(lo + loTaps.o11));
+    }
 }
 
 // Per-tile lookup tables of the bilinear taps: tap position and weights are separable in x and y, so
@@ -307,10 +364,11 @@ __device__ __forceinline__ void GatherGrid(const KernelParams& params, const Ker
     }
 }
 
-// Inputs 0..31 of one texel with the taps read straight from global memory.
+// Inputs 0..31 of one texel with the taps read straight from global memory (`interleaved`: from the pixel-major
+// copy ntcb_interleave_latents makes instead of the file's planes; the mip's offsets then refer to that copy).
 template <bool kFp8, bool kReferenceDivision>
 __device__ __forceinline__ void SampleGridsDirect(const uint16_t* __restrict__ latents, int numLayers, const KernelMip& mip,
-    int x, int y, const uint32_t* __restrict__ latentTable, uint32_t* words)
+    int x, int y, const uint32_t* __restrict__ latentTable, uint32_t* words, bool interleaved = false)
 {
     // src/Inference.cu:52-53
     const float u = TexelCoordinate<kReferenceDivision>(x, mip.width, mip.invWidth);
@@ -318,6 +376,16 @@ __device__ __forceinline__ void SampleGridsDirect(const uint16_t* __restrict__ l
     GridTaps taps;
     SetupTaps(u, v, mip.hiWidth, mip.hiHeight, taps);
     const uint16_t* hi = latents + mip.hiOffset;
+    if (interleaved)
+    {
+        GridTaps lowTaps;
+        SetupTaps(u, v, mip.loWidth, mip.loHeight, lowTaps);
+        SampleInterleaved(hi, latents + mip.loOffset, numLayers, taps, lowTaps,
+            [&](int grid, int layer, uint32_t p00, uint32_t p01, uint32_t p10, uint32_t p11) {
+                words[4 * grid + layer] = BlendLayer<kFp8>(p00, p01, p10, p11, grid ? lowTaps : taps, latentTable);
+            });
+        return;
+    }
 #pragma unroll
     for (int layer = 0; layer < 4; ++layer)
         if (layer < numLayers)

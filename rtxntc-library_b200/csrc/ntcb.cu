@@ -689,6 +689,16 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
         SetError("ntcb_sample: unknown numerics %d.", p->numerics);
         return NTCB_ERR_INVALID_ARGUMENT;
     }
+    if (p->latentLayout != NTCB_LATENTS_PLANAR && p->latentLayout != NTCB_LATENTS_INTERLEAVED)
+    {
+        SetError("ntcb_sample: unknown latent layout %d.", p->latentLayout);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (p->latentLayout == NTCB_LATENTS_INTERLEAVED && (reinterpret_cast<uintptr_t>(p->latents) & 7))
+    {
+        SetError("ntcb_sample: interleaved latents must be 8-byte aligned.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
     const bool reference = p->numerics == NTCB_NUMERICS_REFERENCE;
     if ((reinterpret_cast<uintptr_t>(p->network) & 15) || (reinterpret_cast<uintptr_t>(p->out) & 3) ||
         (reinterpret_cast<uintptr_t>(p->queries) & 3))
@@ -706,6 +716,7 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
     k.numMips = p->numMips;
     k.numLayers = p->numFeatures / 4;
     k.channels = p->channels;
+    k.interleaved = p->latentLayout == NTCB_LATENTS_INTERLEAVED;
     for (int i = 0; i < p->numMips; ++i)
     {
         NtcbMipDesc m = p->mips[i];
@@ -718,6 +729,18 @@ int ntcb_sample(const NtcbSampleParams* p, void* stream)
             return NTCB_ERR_INVALID_ARGUMENT;
         }
         FillKernelMip(m, k.numLayers, k.mips[i]);
+        if (k.interleaved)
+        {
+            // the grid's place in the pixel-major copy: slots of 1, 2 or 4 elements per pixel
+            const unsigned long long layers = (unsigned long long)k.numLayers, slot = k.numLayers == 3 ? 4 : layers;
+            if (m.hiOffset % layers || m.loOffset % layers)
+            {
+                SetError("ntcb_sample: mip %d: the offset of a grid is not a multiple of the layer count.", i);
+                return NTCB_ERR_INVALID_ARGUMENT;
+            }
+            k.mips[i].hiOffset = m.hiOffset / layers * slot;
+            k.mips[i].loOffset = m.loOffset / layers * slot;
+        }
     }
     k.loadWaitPolls = g_networkWaitPolls.load(std::memory_order_relaxed);
     ClearError();

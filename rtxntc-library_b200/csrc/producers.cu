@@ -244,6 +244,41 @@ __global__ void __launch_bounds__(kColumns) QuantizeNetworkKernel(const Quantize
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Latents re-laid for inference on sample: pixel-major, the layers of a pixel side by side
+// ---------------------------------------------------------------------------------------------
+
+constexpr int kMaxGrids = 2 * NTCB_MAX_MIPS;
+
+struct InterleaveArguments
+{
+    const uint16_t* planar;
+    uint16_t* interleaved;
+    int numGrids, numLayers, slot;                // slot: elements per pixel in the copy (1, 2 or 4)
+    unsigned long long firstPixel[kMaxGrids + 1]; // running pixel count: grid g owns [firstPixel[g], firstPixel[g + 1])
+    unsigned long long offset[kMaxGrids];         // element offset of the grid in the planar buffer
+    unsigned long long plane[kMaxGrids];          // elements between the layers of the planar grid
+};
+
+// One thread per latent pixel: reads its layers from the planes (coalesced over the warp, layer by layer) and
+// writes its slot (contiguous over the warp); the fourth element of a three-layer slot is zero.
+__global__ void InterleaveLatentsKernel(const __grid_constant__ InterleaveArguments args)
+{
+    const unsigned long long total = args.firstPixel[args.numGrids];
+    for (unsigned long long index = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; index < total;
+         index += (unsigned long long)gridDim.x * blockDim.x)
+    {
+        int grid = 0;
+        while (grid + 1 < args.numGrids && index >= args.firstPixel[grid + 1])
+            ++grid;
+        const unsigned long long pixel = index - args.firstPixel[grid];
+        const uint16_t* source = args.planar + args.offset[grid] + pixel;
+        uint16_t* target = args.interleaved + args.offset[grid] / args.numLayers * args.slot + pixel * (unsigned long long)args.slot;
+        for (int layer = 0; layer < args.slot; ++layer)
+            target[layer] = layer < args.numLayers ? __ldg(source + (unsigned long long)layer * args.plane[grid]) : uint16_t(0);
+    }
+}
+
 } // namespace
 } // namespace ntcb
 
@@ -296,6 +331,80 @@ extern "C" int ntcb_pack_latents(const void* latents, int width, int height, int
     error = cudaGetLastError();
     if (error != cudaSuccess)
         return CudaFailure("PackLatentsKernel", error);
+    ClearError();
+    return NTCB_OK;
+}
+
+extern "C" int ntcb_interleave_latents(const uint16_t* latents, uint16_t* interleaved, const NtcbMipDesc* mips, int numMips,
+    int numFeatures, void* stream)
+{
+    if (!latents || !interleaved || !mips || latents == interleaved)
+    {
+        SetError("ntcb_interleave_latents: latents, interleaved (another buffer) and mips must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (numMips < 1 || numMips > NTCB_MAX_MIPS || numFeatures < 4 || numFeatures > 16 || (numFeatures & 3))
+    {
+        SetError("ntcb_interleave_latents: invalid mip count (%d) or feature count (%d).", numMips, numFeatures);
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    if (reinterpret_cast<uintptr_t>(interleaved) & 7)
+    {
+        SetError("ntcb_interleave_latents: interleaved must be 8-byte aligned.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    InterleaveArguments args{};
+    args.planar = latents;
+    args.interleaved = interleaved;
+    args.numLayers = numFeatures / 4;
+    args.slot = args.numLayers == 3 ? 4 : args.numLayers;
+    // the colour mips of a neural mip share its grids: each distinct grid once
+    auto addGrid = [&](uint64_t offset, uint64_t plane, int width, int height) -> int {
+        const uint64_t pixels = uint64_t(width) * uint64_t(height);
+        if (width < 1 || height < 1 || plane < pixels)
+        {
+            SetError("ntcb_interleave_latents: a grid of %d x %d pixels with %llu elements between its layers.", width, height,
+                static_cast<unsigned long long>(plane));
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        if (offset % uint64_t(args.numLayers))
+        {
+            SetError("ntcb_interleave_latents: the offset of a grid (%llu) is not a multiple of the layer count (%d).",
+                static_cast<unsigned long long>(offset), args.numLayers);
+            return NTCB_ERR_INVALID_ARGUMENT;
+        }
+        for (int g = 0; g < args.numGrids; ++g)
+            if (args.offset[g] == offset)
+                return NTCB_OK;
+        args.offset[args.numGrids] = offset;
+        args.plane[args.numGrids] = plane;
+        args.firstPixel[args.numGrids + 1] = args.firstPixel[args.numGrids] + pixels;
+        ++args.numGrids;
+        return NTCB_OK;
+    };
+    for (int m = 0; m < numMips; ++m)
+    {
+        int status = addGrid(mips[m].hiOffset, mips[m].hiPlane, mips[m].hiWidth, mips[m].hiHeight);
+        if (status == NTCB_OK)
+            status = addGrid(mips[m].loOffset, mips[m].loPlane, mips[m].loWidth, mips[m].loHeight);
+        if (status != NTCB_OK)
+            return status;
+    }
+    int device = 0, sms = 0;
+    cudaError_t error = cudaGetDevice(&device);
+    if (error == cudaSuccess)
+        error = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (error != cudaSuccess)
+        return CudaFailure("cudaDeviceGetAttribute", error);
+    const int threads = 256;
+    const uint64_t wanted = (args.firstPixel[args.numGrids] + threads - 1) / threads;
+    const uint64_t resident = uint64_t(sms) * 8 * 4;
+    const unsigned grid = unsigned(wanted < resident ? wanted : resident);
+    InterleaveLatentsKernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(args);
+    CountLaunch();
+    error = cudaGetLastError();
+    if (error != cudaSuccess)
+        return CudaFailure("InterleaveLatentsKernel", error);
     ClearError();
     return NTCB_OK;
 }

@@ -458,6 +458,53 @@ def test_inference_on_sample_matches_contract(oracle, shape, numerics):
     assert resident.sample(device_queries[:0], True).shape[0] == 0
 
 
+@BOTH_NUMERICS
+@pytest.mark.parametrize("shape", [(256, 256, 12, 0, 4, 16), (512, 384, 12, 0, 4, 12), (200, 136, 6, 0, 2, 8), (96, 40, 6, 0, 3, 12),
+                                   (33, 17, 2, 0, 1, 4)])
+def test_inference_on_sample_reads_interleaved_latents(shape, numerics):
+    """ntcb_interleave_latents makes the pixel-major copy - layer l of pixel p of the grid at `offset` at element
+    offset / layers * slot + p * slot + l, slot = 1, 2, 4, 4 elements for 1 - 4 layers, a zero behind three - and a
+    query answered from that copy (NTCB_LATENTS_INTERLEAVED: one aligned load per tap) has the bits of the query
+    answered from the file's planes.  Enough queries for several tiles per CTA."""
+    import torch
+
+    w, h, c, mips, g, f = shape
+    data = synthetic.make_texture_set(synthetic.TextureSetSpec(w, h, c, mips, g, f, seed=5, network="unit"))
+    geo = data.geometry
+    resident = binding.ResidentTextureSet.from_synthetic(data, numerics=numerics)
+    planar = resident.latents.cpu().numpy()
+    relaid = resident.interleave_latents().cpu().numpy()
+    _sync()
+    layers = f // 4
+    slot = 4 if layers == 3 else layers
+    assert relaid.size == planar.size // layers * slot
+    params = binding.fill_params(geo, 0, 0, 0, 0, binding.WEIGHTS_INT8)
+    seen = set()
+    for m in range(params.numMips):
+        mip = params.mips[m]
+        for offset, plane, gw, gh in ((mip.hiOffset, mip.hiPlane, mip.hiWidth, mip.hiHeight),
+                                      (mip.loOffset, mip.loPlane, mip.loWidth, mip.loHeight)):
+            if offset in seen:
+                continue
+            seen.add(offset)
+            pixels = gw * gh
+            want = np.zeros((pixels, slot), dtype=planar.dtype)
+            for l in range(layers):
+                want[:, l] = planar[offset + l * plane:offset + l * plane + pixels]
+            first = offset // layers * slot
+            assert np.array_equal(relaid[first:first + pixels * slot].reshape(pixels, slot), want), (m, offset)
+    queries = synthetic.make_queries(700000, max_lod=geo.mips + 0.5, seed=11)
+    queries[:4] = [[0, 0, 0], [0.999999, 0.999999, 0], [1.0, 1.0, 1.0], [0.0, 1.0, geo.mips - 1]]
+    device_queries = torch.from_numpy(queries).cuda()
+    for use_int8 in (True, False):
+        for count in (700000, 1000, 1):
+            from_planes = resident.sample(device_queries[:count], use_int8).cpu().numpy()
+            from_copy = resident.sample(device_queries[:count], use_int8, interleaved=True).cpu().numpy()
+            _sync()
+            resident.check_status()
+            assert np.array_equal(from_planes.view(np.uint16), from_copy.view(np.uint16)), (use_int8, count)
+
+
 @pytest.mark.parametrize("numerics", [binding.NUMERICS_REFERENCE, binding.NUMERICS_EXACT], ids=["reference", "exact"])
 def test_decode_launches_replay_from_a_cuda_graph(numerics):
     """ntcb_decode only queues work on the stream it is given, so a batch of decodes can be captured once

@@ -118,3 +118,8 @@ def test_configuration_4_matches_a_gather_from_the_live_reference(live):
     expected = chain[offsets[mip] + y * w + x]
     assert torch.equal(got.view(torch.int16), expected.view(torch.int16)), \
         "%d of %d values differ" % (int((got.view(torch.int16) != expected.view(torch.int16)).sum()), got.numel())
+    # the same from the pixel-major copy of the latents (12 features: slots of four elements, one load per tap)
+    again = resident.sample(queries, False, interleaved=True)
+    torch.cuda.synchronize()
+    resident.check_status()
+    assert torch.equal(again.view(torch.int16), expected.view(torch.int16))

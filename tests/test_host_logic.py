@@ -313,6 +313,41 @@ def test_decode_validates_arguments_before_touching_the_gpu():
     assert lib.ntcb_decode(ctypes.byref(good), None) == -1
 
 
+def test_sample_and_interleave_validate_arguments_before_touching_the_gpu():
+    lib = binding.lib()
+    geo = synthetic.TextureSetSpec(64, 64, 4, 1, 2, 8, seed=0).geometry()
+    decode = binding.fill_params(geo, 0x1000, 0x2000, 0x3000, 0x4000, binding.WEIGHTS_INT8)
+    params = binding.SampleParams()
+    params.latents, params.network, params.queries, params.out, params.status = 0x1000, 0x2000, 0x5000, 0x3000, 0x4000
+    params.numQueries, params.numMips, params.numFeatures, params.channels = 16, decode.numMips, 8, 4
+    params.weightMode, params.numerics = binding.WEIGHTS_INT8, binding.NUMERICS_REFERENCE
+    for i in range(decode.numMips):
+        params.mips[i] = decode.mips[i]
+    params.latentLayout = 2
+    assert lib.ntcb_sample(ctypes.byref(params), None) == -1
+    assert b"latent layout" in lib.ntcb_last_error()
+    params.latentLayout = binding.LATENTS_INTERLEAVED
+    params.latents = 0x1004
+    assert lib.ntcb_sample(ctypes.byref(params), None) == -1
+    assert b"8-byte aligned" in lib.ntcb_last_error()
+    # ntcb_interleave_latents: NULL, aliased or misaligned buffers, bad counts, a grid larger than its plane,
+    # an offset that is not a multiple of the layer count
+    mips = decode.mips
+    assert lib.ntcb_interleave_latents(None, ctypes.c_void_p(0x1000), mips, 1, 8, None) == -1
+    assert lib.ntcb_interleave_latents(ctypes.c_void_p(0x1000), ctypes.c_void_p(0x1000), mips, 1, 8, None) == -1
+    assert lib.ntcb_interleave_latents(ctypes.c_void_p(0x1000), ctypes.c_void_p(0x9004), mips, 1, 8, None) == -1
+    assert lib.ntcb_interleave_latents(ctypes.c_void_p(0x1000), ctypes.c_void_p(0x9000), mips, 0, 8, None) == -1
+    assert lib.ntcb_interleave_latents(ctypes.c_void_p(0x1000), ctypes.c_void_p(0x9000), mips, 1, 6, None) == -1
+    broken = (binding.MipDesc * 1)(decode.mips[0])
+    broken[0].hiPlane = 1
+    assert lib.ntcb_interleave_latents(ctypes.c_void_p(0x1000), ctypes.c_void_p(0x9000), broken, 1, 8, None) == -1
+    assert b"between its layers" in lib.ntcb_last_error()
+    broken = (binding.MipDesc * 1)(decode.mips[0])
+    broken[0].loOffset = decode.mips[0].loOffset + 1
+    assert lib.ntcb_interleave_latents(ctypes.c_void_p(0x1000), ctypes.c_void_p(0x9000), broken, 1, 8, None) == -1
+    assert b"multiple of the layer count" in lib.ntcb_last_error()
+
+
 def test_misaligned_and_oversized_requests_are_refused_on_the_host():
     """Requests that would make a kernel issue a misaligned vector access, or overflow its 32-bit
     element index, are refused before anything is launched (the addresses here are never touched)."""
