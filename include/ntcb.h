@@ -382,6 +382,18 @@ int ntcb_texture_set_load_from_memory(NtcbTextureSet* textureSet, const void* da
 /* The textures of a loaded set: see ntcb_probe_container_texture. */
 int ntcb_texture_set_get_texture(NtcbTextureSet* textureSet, int index, NtcbTextureDesc* outTexture, int* outCount);
 
+/* Inference on sample at the texture-set level: `deviceQueries` (numQueries x 3 floats: u, v, lod) and `deviceOut`
+   (numQueries x channels binary16 values) lie in the memory of the set's device; query q selects a texel as
+   ntcb_sample describes and receives the bits ntcb_texture_set_decompress would write there.  The compressed
+   data is uploaded when the device copy is not current (first use, after ntcb_texture_set_load_from_memory), and
+   its pixel-major copy (ntcb_interleave_latents) is made then too, so a set that is sampled again and again pays
+   for neither; the call runs on the set's stream and waits for the answers (NTCB_ERR_DEVICE_TIMEOUT if a bounded
+   wait inside the kernel expired).  The reference offers sampling to shaders only (NtcSampleTextureSet,
+   include/libntc/shaders/Inference.hlsli:282-357, with the data of IContext::MakeInferenceData,
+   src/Context.cpp:864-922). */
+int ntcb_texture_set_sample(NtcbTextureSet* textureSet, const float* deviceQueries, uint64_t numQueries, void* deviceOut,
+    int useInt8Weights);
+
 /* Waits for everything queued on the texture set's stream. */
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet);
 

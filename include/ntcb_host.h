@@ -81,6 +81,13 @@ public:
     // ITextureSet::LoadFromMemory: another compressed set of the same dimensions and latent shape into this
     // one's buffers (FileIncompatible otherwise, and nothing changes); the texels must be decompressed again.
     virtual Status LoadFromMemory(void const* pData, size_t size) = 0;
+    // Inference on sample (the reference offers it to shaders only: NtcSampleTextureSet,
+    // include/libntc/shaders/Inference.hlsli:282-357, fed by IContext::MakeInferenceData).  `deviceQueries`: numQueries
+    // x (u, v, lod) floats, `deviceOut`: numQueries x channels binary16 values, both in the memory of the set's
+    // device; query q selects a texel as ntcb_sample describes and receives the bits Decompress would write there.
+    // The compressed data is uploaded when the device copy is not current (first use, LoadFromMemory), its
+    // pixel-major copy is made then too; the call waits for the answers.
+    virtual Status Sample(float const* deviceQueries, uint64_t numQueries, void* deviceOut, bool useInt8Weights) = 0;
     virtual Status Synchronize() = 0;
     virtual ~ITextureSet() = default;
 };

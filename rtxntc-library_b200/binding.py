@@ -176,6 +176,7 @@ def lib():
         handle.ntcb_stage_network_reference.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode.argtypes = [ctypes.POINTER(DecodeParams), ctypes.c_void_p]
         handle.ntcb_sample.argtypes = [ctypes.POINTER(SampleParams), ctypes.c_void_p]
+        handle.ntcb_texture_set_sample.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_int]
         handle.ntcb_interleave_latents.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(MipDesc), ctypes.c_int,
                                                    ctypes.c_int, ctypes.c_void_p]
         handle.ntcb_decode_resident_ctas.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
@@ -795,6 +796,18 @@ class TextureSet:
         pointer, size = ctypes.c_void_p(), ctypes.c_size_t()
         check(lib().ntcb_texture_set_device_mip(self.handle, mip, ctypes.byref(pointer), ctypes.byref(size)))
         return int(pointer.value), int(size.value)
+
+    def sample(self, queries, use_int8: bool):
+        """ntcb_texture_set_sample: `queries` is a float32 CUDA tensor [n][3] of (u, v, lod) on the set's device;
+        returns a float16 CUDA tensor [n][channels] with the bits a decompress would write to the selected texels.
+        The call waits for the answers."""
+        import torch
+
+        queries = queries.contiguous()
+        out = torch.empty((queries.shape[0], self.desc.channels), dtype=torch.float16, device=queries.device)
+        check(lib().ntcb_texture_set_sample(self.handle, ctypes.c_void_p(queries.data_ptr()), queries.shape[0],
+                                            ctypes.c_void_p(out.data_ptr()), 1 if use_int8 else 0))
+        return out
 
     def synchronize(self) -> None:
         check(lib().ntcb_texture_set_synchronize(self.handle))

@@ -92,6 +92,7 @@ public:
         void const* blockData, size_t blockDataSize, size_t rowPitch) override;
     Status BlockCompressTexture(int textureIndex, int mipLevel, float alphaThreshold, void* deviceBlocks, size_t rowPitch) override;
     Status LoadFromMemory(void const* pData, size_t size) override;
+    Status Sample(float const* deviceQueries, uint64_t numQueries, void* deviceOut, bool useInt8Weights) override;
     Status Synchronize() override;
 
     const SetGeometry& Geometry() const { return m_geometry; }
@@ -129,6 +130,10 @@ private:
     std::vector<std::vector<void*>> m_deviceModeBuffers; // [texture][mip]: device copies of the BC7 mode bitmaps, made on first use
     uint8_t* m_staging = nullptr;     // grown on demand by ReadChannels to host with padded strides
     size_t m_stagingBytes = 0;
+    // Inference on sample keeps the compressed data resident: whether m_deviceUpload holds what m_hostUpload holds
+    // (as far as the work queued on m_stream is concerned), and the pixel-major copy of the latents made from it
+    bool m_deviceCurrent = false, m_pixelMajorCurrent = false;
+    uint16_t* m_pixelMajor = nullptr;
     cudaEvent_t m_eventStart = nullptr, m_eventStop = nullptr;
     bool m_decoded = false;
 
@@ -396,6 +401,7 @@ Status TextureSet::LoadFromMemory(void const* pData, size_t size)
     if (err != cudaSuccess)
         return CudaFailure("cudaStreamSynchronize", err);
     m_decoded = false;
+    m_deviceCurrent = m_pixelMajorCurrent = false;
     status = FillUpload(loaded);
     if (status != NTCB_OK)
         return status;
@@ -427,6 +433,9 @@ void TextureSet::Release()
             copy = nullptr;
         }
     if (m_staging) cudaFree(m_staging);
+    if (m_pixelMajor) cudaFree(m_pixelMajor);
+    m_pixelMajor = nullptr;
+    m_deviceCurrent = m_pixelMajorCurrent = false;
     if (m_status) cudaFree(m_status);
     if (m_hostStatus) cudaFreeHost(m_hostStatus);
     if (m_texels) cudaFree(m_texels);
@@ -610,6 +619,7 @@ Status TextureSet::DecodeInto(const int32_t* rowRanges, DecompressionStats* pOut
     cudaError_t err = cudaMemcpyAsync(m_deviceUpload, m_hostUpload, m_uploadBytes, cudaMemcpyHostToDevice, m_stream);
     if (err != cudaSuccess)
         return CudaFailure("cudaMemcpyAsync (compressed data)", err);
+    m_deviceCurrent = true;
     err = cudaMemsetAsync(m_status, 0, NTCB_STATUS_WORDS * sizeof(uint32_t), m_stream);
     if (err != cudaSuccess)
         return CudaFailure("cudaMemsetAsync (status)", err);
@@ -712,6 +722,108 @@ Status TextureSet::DecodeInto(const int32_t* rowRanges, DecompressionStats* pOut
         if (status != NTCB_OK)
             return status;
     }
+    ClearError();
+    return NTCB_OK;
+}
+
+Status TextureSet::Sample(float const* deviceQueries, uint64_t numQueries, void* deviceOut, bool useInt8Weights)
+{
+    if (useInt8Weights ? !m_hasInt8 : !m_hasFp8)
+    {
+        SetError("The texture set has no %s network; it cannot be sampled with these weights.", useInt8Weights ? "Int8" : "FP8");
+        return NTCB_ERR_INVALID_STATE;
+    }
+    if (numQueries == 0)
+    {
+        ClearError();
+        return NTCB_OK;
+    }
+    if (!deviceQueries || !deviceOut)
+    {
+        SetError("deviceQueries and deviceOut must not be NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    DeviceGuard guard(m_device);
+    if (!guard.Success())
+        return NTCB_ERR_CUDA;
+
+    cudaError_t err = cudaSuccess;
+    if (!m_deviceCurrent)
+    {
+        err = cudaMemcpyAsync(m_deviceUpload, m_hostUpload, m_uploadBytes, cudaMemcpyHostToDevice, m_stream);
+        if (err != cudaSuccess)
+            return CudaFailure("cudaMemcpyAsync (compressed data)", err);
+        m_deviceCurrent = true;
+        m_pixelMajorCurrent = false;
+    }
+    NtcbSampleParams params{};
+    params.numMips = m_geometry.mips;
+    params.numFeatures = m_geometry.numFeatures;
+    for (int mip = 0; mip < m_geometry.mips; ++mip)
+    {
+        // the per-mip parameters TextureSet::Decompress fills (src/TextureSet.cpp:1806-1829)
+        const int lod = m_geometry.neuralLod[mip];
+        NtcbMipDesc& d = params.mips[mip];
+        d.width = m_geometry.mipWidth[mip];
+        d.height = m_geometry.mipHeight[mip];
+        d.hiWidth = m_geometry.latentWidth[lod];
+        d.hiHeight = m_geometry.latentHeight[lod];
+        d.loWidth = m_geometry.latentWidth[lod + 1];
+        d.loHeight = m_geometry.latentHeight[lod + 1];
+        d.hiOffset = m_geometry.latentPixelOffset[lod] * m_geometry.numLayers;
+        d.loOffset = m_geometry.latentPixelOffset[lod + 1] * m_geometry.numLayers;
+        d.hiPlane = uint64_t(d.hiWidth) * d.hiHeight;
+        d.loPlane = uint64_t(d.loWidth) * d.loHeight;
+        d.positionScale = m_geometry.positionScale[mip];
+        d.positionLod = m_geometry.positionLod[mip];
+        d.rowEnd = d.height;
+    }
+    if (!m_pixelMajorCurrent)
+    {
+        // the pixel-major copy of the latents: slots of 1, 2 or 4 elements per latent pixel
+        const size_t slot = m_geometry.numLayers == 3 ? 4 : size_t(m_geometry.numLayers);
+        if (!m_pixelMajor)
+        {
+            const size_t layers = size_t(m_geometry.numLayers), elements = m_latentBytes / 2;
+            err = cudaMalloc(&m_pixelMajor, (elements + layers - 1) / layers * slot * 2);
+            if (err != cudaSuccess)
+            {
+                m_pixelMajor = nullptr;
+                CudaFailure("cudaMalloc (pixel-major latents)", err);
+                return NTCB_ERR_OUT_OF_MEMORY;
+            }
+        }
+        Status status = ntcb_interleave_latents(reinterpret_cast<const uint16_t*>(m_deviceUpload), m_pixelMajor, params.mips,
+            m_geometry.mips, m_geometry.numFeatures, m_stream);
+        if (status != NTCB_OK)
+            return status;
+        m_pixelMajorCurrent = true;
+    }
+    err = cudaMemsetAsync(m_status, 0, NTCB_STATUS_WORDS * sizeof(uint32_t), m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaMemsetAsync (status)", err);
+    params.latents = m_pixelMajor;
+    params.latentLayout = NTCB_LATENTS_INTERLEAVED;
+    params.network = m_deviceUpload + m_latentBytes + (useInt8Weights ? 0 : m_networkBytes);
+    params.queries = deviceQueries;
+    params.out = deviceOut;
+    params.status = m_status;
+    params.numQueries = numQueries;
+    params.channels = m_geometry.channels;
+    params.weightMode = useInt8Weights ? NTCB_WEIGHTS_INT8 : NTCB_WEIGHTS_FP8;
+    params.numerics = m_numerics;
+    Status status = ntcb_sample(&params, m_stream);
+    if (status != NTCB_OK)
+        return status;
+    err = cudaMemcpyAsync(m_hostStatus, m_status, NTCB_STATUS_WORDS * sizeof(uint32_t), cudaMemcpyDeviceToHost, m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaMemcpyAsync (status)", err);
+    err = cudaStreamSynchronize(m_stream);
+    if (err != cudaSuccess)
+        return CudaFailure("cudaStreamSynchronize", err);
+    status = CheckKernelStatus();
+    if (status != NTCB_OK)
+        return status;
     ClearError();
     return NTCB_OK;
 }
@@ -1453,6 +1565,17 @@ int ntcb_texture_set_get_texture(NtcbTextureSet* textureSet, int index, NtcbText
         *outCount = textureSet->impl->GetTextureCount();
     NtcbTextureDesc scratch;
     return textureSet->impl->GetTexture(index, outTexture ? *outTexture : scratch);
+}
+
+int ntcb_texture_set_sample(NtcbTextureSet* textureSet, const float* deviceQueries, uint64_t numQueries, void* deviceOut,
+    int useInt8Weights)
+{
+    if (!textureSet)
+    {
+        ntcb::SetError("textureSet is NULL.");
+        return NTCB_ERR_INVALID_ARGUMENT;
+    }
+    return ntcb::Guarded(__func__, [&]() { return textureSet->impl->Sample(deviceQueries, numQueries, deviceOut, useInt8Weights != 0); });
 }
 
 int ntcb_texture_set_synchronize(NtcbTextureSet* textureSet)

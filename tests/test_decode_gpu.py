@@ -505,6 +505,48 @@ def test_inference_on_sample_reads_interleaved_latents(shape, numerics):
             assert np.array_equal(from_planes.view(np.uint16), from_copy.view(np.uint16)), (use_int8, count)
 
 
+@BOTH_NUMERICS
+def test_texture_set_sample_answers_with_the_decompressed_texels(numerics):
+    """ntcb_texture_set_sample: before any decompress (the call uploads the compressed data and makes its
+    pixel-major copy), after one, and after LoadFromMemory put another set into the same buffers (both copies
+    stale) - every answer is the texel a decompress of the set currently loaded writes."""
+    import torch
+
+    specs = [synthetic.TextureSetSpec(200, 136, 6, 0, 2, 12, seed=41, network="unit"),
+             synthetic.TextureSetSpec(200, 136, 6, 0, 2, 12, seed=42, network="unit")]
+    sets = [synthetic.make_texture_set(spec) for spec in specs]
+    geo = sets[0].geometry
+    queries = synthetic.make_queries(30000, max_lod=geo.mips + 0.5, seed=13)
+    queries[:3] = [[0, 0, 0], [0.999999, 0.999999, 0], [1.0, 1.0, geo.mips - 1]]
+    device_queries = torch.from_numpy(queries).cuda()
+
+    def expected(texture_set, use_int8):
+        texture_set.decompress(use_int8)
+        mips = [texture_set.read_mip(m) for m in range(geo.mips)]
+        want = np.zeros((queries.shape[0], geo.channels), dtype=np.float16)
+        for q in range(queries.shape[0]):
+            mip = int(max(0, min(geo.mips - 1, np.floor(queries[q, 2]))))
+            cm = geo.color_mips[mip]
+            x = int(max(0, min(cm.width - 1, np.floor(np.float32(queries[q, 0]) * np.float32(cm.width)))))
+            y = int(max(0, min(cm.height - 1, np.floor(np.float32(queries[q, 1]) * np.float32(cm.height)))))
+            want[q] = mips[mip][y, x]
+        return want
+
+    with binding.Context() as context:
+        texture_set = context.create_texture_set(sets[0].container, numerics=numerics)
+        first = {use_int8: texture_set.sample(device_queries, use_int8).cpu().numpy() for use_int8 in (True, False)}
+        for use_int8 in (True, False):
+            assert np.array_equal(first[use_int8].view(np.uint16), expected(texture_set, use_int8).view(np.uint16))
+            again = texture_set.sample(device_queries, use_int8).cpu().numpy()
+            assert np.array_equal(again.view(np.uint16), first[use_int8].view(np.uint16))
+        texture_set.load_from_memory(sets[1].container)
+        other = texture_set.sample(device_queries, True).cpu().numpy()
+        assert not np.array_equal(other.view(np.uint16), first[True].view(np.uint16))
+        assert np.array_equal(other.view(np.uint16), expected(texture_set, True).view(np.uint16))
+        assert texture_set.sample(device_queries[:0], True).shape[0] == 0
+        texture_set.close()
+
+
 @pytest.mark.parametrize("numerics", [binding.NUMERICS_REFERENCE, binding.NUMERICS_EXACT], ids=["reference", "exact"])
 def test_decode_launches_replay_from_a_cuda_graph(numerics):
     """ntcb_decode only queues work on the stream it is given, so a batch of decodes can be captured once
