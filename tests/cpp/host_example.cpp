@@ -126,8 +126,32 @@ int main(int argc, char** argv)
     std::vector<uint16_t> again(texels.size());
     read.pOutData = again.data();
     CHECK(textureSet->ReadChannels(read));
-    std::printf("bc7 %016llx mode_bytes %zu reloaded %s\n", static_cast<unsigned long long>(Fnv1a(blocks7.data(), blocks7.size())),
-        modeBytes, again == texels ? "same" : "DIFFERENT");
+    // ITextureSet::Sample: one query at the centre of every texel of mip 0, in row order, must give mip 0 back
+    const size_t numQueries = size_t(desc.width) * desc.height;
+    std::vector<float> queries(numQueries * 3);
+    for (int y = 0; y < desc.height; ++y)
+        for (int x = 0; x < desc.width; ++x)
+        {
+            float* query = &queries[(size_t(y) * desc.width + x) * 3];
+            query[0] = (float(x) + 0.5f) / float(desc.width);
+            query[1] = (float(y) + 0.5f) / float(desc.height);
+            query[2] = 0.25f;
+        }
+    float* deviceQueries = nullptr;
+    void* deviceAnswers = nullptr;
+    if (cudaMalloc(&deviceQueries, queries.size() * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&deviceAnswers, texels.size() * 2) != cudaSuccess ||
+        cudaMemcpy(deviceQueries, queries.data(), queries.size() * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+        return 1;
+    CHECK(textureSet->Sample(deviceQueries, numQueries, deviceAnswers, /*useInt8Weights*/ false));
+    std::vector<uint16_t> answers(texels.size());
+    if (cudaMemcpy(answers.data(), deviceAnswers, answers.size() * 2, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return 1;
+    cudaFree(deviceQueries);
+    cudaFree(deviceAnswers);
+
+    std::printf("bc7 %016llx mode_bytes %zu reloaded %s sampled %s\n", static_cast<unsigned long long>(Fnv1a(blocks7.data(), blocks7.size())),
+        modeBytes, again == texels ? "same" : "DIFFERENT", answers == texels ? "same" : "DIFFERENT");
 
     std::printf("texels %016llx bc4 %016llx size %dx%dx%d mips %d gpu_ms %.4f\n",
         static_cast<unsigned long long>(Fnv1a(texels.data(), texels.size() * 2)),

@@ -85,7 +85,7 @@ def test_cpp_client_matches_the_c_abi(tmp_path):
         blocks = texture_set.block_compress(0, binding.BLOCK_FORMAT_BC4, 0).cpu().numpy()
         blocks7 = texture_set.block_compress_texture(1, 0).cpu().numpy()
         texture_set.close()
-    assert int(bc7[1], 16) == _fnv1a(blocks7.tobytes()) and bc7[3] == str(_mode_bitmap(12, 6).nbytes) and bc7[5] == "same"
+    assert int(bc7[1], 16) == _fnv1a(blocks7.tobytes()) and bc7[3] == str(_mode_bitmap(12, 6).nbytes) and bc7[5] == "same" and bc7[7] == "same"
     assert np.array_equal(binding.make_bc7_mode_buffer(blocks7), _mode_bitmap(12, 6))  # every block in the mode it was given
     assert int(fields[1], 16) == _fnv1a(np.ascontiguousarray(texels).tobytes())
     assert int(fields[3], 16) == _fnv1a(blocks.tobytes())
