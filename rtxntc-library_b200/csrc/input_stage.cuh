@@ -203,8 +203,12 @@ __device__ __forceinline__ void PrepareTaps(const KernelParams& params, const Ke
     if (tablesValid)
     {
         // only the footprint's origin depends on the tile, and it moves by whole latent pixels per tile step
-        const int4 origin = taps.origin[grid];
         const int4 footprint = taps.footprint[grid];
+        // a warp whose first footprint pixel lies beyond the footprint has nothing to stage (with a grid at a
+        // quarter of the mip's resolution a footprint has 40 pixels: two of the grid's four warps)
+        if (32 * (warp >> 1) >= footprint.z)
+            return;
+        const int4 origin = taps.origin[grid];
         fx0 = origin.x + ((tileX0 - origin.z) >> 5) * (grid ? mip.loStepX : mip.hiStepX);
         fy0 = origin.y + ((tileY0 - origin.w) >> 3) * (grid ? mip.loStepY : mip.hiStepY);
         footW = footprint.x;
