@@ -9,16 +9,20 @@
 // chains per tile, weights resident in shared memory, accumulators in tensor memory.
 //
 // What differs from decode_kernel.cu:
-//   * the A operand holds binary16 values (the de-quantised network inputs / activations), 128 bytes
-//     per row.  Layers 0 and 1 read it from shared memory, written by the threads in K-major
+//   * the A operand holds binary16 values (the de-quantised network inputs / activations), up to 128
+//     bytes per row.  Layer 0 reads it from shared memory, written by the threads in K-major
 //     core-matrix order (16-byte chunk j, 8 halves, of row r at j * 2048 + r * 16); layers 2 and 3 read
 //     it from tensor memory, where the activation step stores it (columns 32.. of the chain's 64,
-//     beside those layers' accumulators);
+//     beside those layers' accumulators); layer 1 reads its first two K steps from shared memory and
+//     its last two from the 16 tensor-memory columns its 48 accumulators leave free;
 //   * between the layers of a tile the two chains do not wait for each other (LayerBarrier,
 //     kernel_parts.cuh);
-//   * each layer starts with a "bias step": an MMA whose A operand is a constant region with rows
-//     (1, 0, ..., 0) and whose B operand holds the bias in column 0, which sets the accumulators to
-//     the binary16 bias exactly; the K = 16 steps of the layer then accumulate onto it;
+//   * each layer starts with a "bias step": an MMA whose A operand has constant rows - a unit vector -
+//     and whose B operand holds the bias in the column the unit vector picks, which sets the
+//     accumulators to the binary16 bias exactly; the K = 16 steps of the layer then accumulate onto it.
+//     (Int8 networks: ONE 64 x 8 matrix of biases, column l for layer l, and the rows e_l as one 8-row
+//     core matrix that every row group reads - descriptor stride 0; FP8 networks: an N x 16 matrix per
+//     layer with the bias in column 0 and 128 rows (1, 0, ..., 0).);
 //   * the accumulators come back as binary16 (tcgen05.ld ... pack::16b: two per register), ready for
 //     the packed-half activation; there is no scale, no integer bias, no conversion;
 //   * activations are re-quantised and immediately de-quantised (e4m3, or the int8 grid k * 0.0125),
